@@ -1,0 +1,179 @@
+// Python bindings: tensor checks here, raw-pointer launchers in the .cu files.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "launchers.h"
+
+namespace {
+
+using torch::Tensor;
+using OptTensor = c10::optional<torch::Tensor>;
+
+inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream(); }
+inline int num_sms() { return at::cuda::getCurrentDeviceProperties()->multiProcessorCount; }
+
+inline void check_bf16(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, ": CUDA tensor required");
+  TORCH_CHECK(t.scalar_type() == torch::kBFloat16, name, ": bf16 required");
+}
+inline void check_f32(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, ": CUDA tensor required");
+  TORCH_CHECK(t.scalar_type() == torch::kFloat32, name, ": fp32 required");
+}
+inline void check_i32(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, ": CUDA tensor required");
+  TORCH_CHECK(t.scalar_type() == torch::kInt32, name, ": int32 required");
+}
+template <typename T>
+inline T* opt_ptr(const OptTensor& t) {
+  return (t.has_value() && t->defined()) ? reinterpret_cast<T*>(t->data_ptr()) : nullptr;
+}
+
+void gemm_bf16(const Tensor& a, const Tensor& b, Tensor& d, bool a_mn, bool b_mn, const OptTensor& bias, double alpha,
+               bool accumulate, const OptTensor& status) {
+  check_bf16(a, "gemm a");
+  check_bf16(b, "gemm b");
+  TORCH_CHECK(d.is_cuda() && (d.scalar_type() == torch::kBFloat16 || d.scalar_type() == torch::kFloat32), "gemm d");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && d.dim() == 2, "gemm: 2-D tensors");
+  TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && d.stride(1) == 1, "gemm: inner stride must be 1");
+  const c10::cuda::CUDAGuard guard(a.device());
+  const int64_t M = a_mn ? a.size(1) : a.size(0);
+  const int64_t K = a_mn ? a.size(0) : a.size(1);
+  const int64_t N = b_mn ? b.size(1) : b.size(0);
+  const int64_t Kb = b_mn ? b.size(0) : b.size(1);
+  TORCH_CHECK(K == Kb, "gemm: K mismatch ", K, " vs ", Kb);
+  TORCH_CHECK(d.size(0) == M && d.size(1) == N, "gemm: output shape mismatch");
+  if (M == 0 || N == 0) return;
+  TORCH_CHECK(K > 0, "gemm: K must be positive");
+  TORCH_CHECK(a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0, "gemm: row pitch must be a multiple of 8 elements");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(a.data_ptr()) & 15) == 0 && (reinterpret_cast<uintptr_t>(b.data_ptr()) & 15) == 0,
+              "gemm: operands must be 16-byte aligned");
+  if (bias.has_value() && bias->defined()) {
+    check_bf16(*bias, "gemm bias");
+    TORCH_CHECK(bias->numel() == N && bias->is_contiguous(), "gemm: bias must be contiguous [N]");
+  }
+  if (status.has_value() && status->defined()) check_i32(*status, "gemm status");
+  agrpo::launch_gemm_bf16(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), d.data_ptr(), d.stride(0), (int)M, (int)N,
+                          (int)K, a_mn, b_mn, opt_ptr<void>(bias), (float)alpha, d.scalar_type() == torch::kFloat32,
+                          accumulate, opt_ptr<int>(status), num_sms(), cur_stream());
+}
+
+void embedding_fwd(const Tensor& ids, const Tensor& table, Tensor& out) {
+  check_i32(ids, "ids"); check_bf16(table, "table"); check_bf16(out, "out");
+  TORCH_CHECK(table.is_contiguous() && out.is_contiguous() && table.size(1) % 8 == 0, "embedding_fwd layout");
+  const c10::cuda::CUDAGuard guard(table.device());
+  agrpo::launch_embedding_fwd(ids.data_ptr<int>(), table.data_ptr(), out.data_ptr(), (int)ids.numel(), (int)table.size(1),
+                              (int)table.size(0), cur_stream());
+}
+void embedding_bwd(const Tensor& ids, const Tensor& dout, Tensor& dtable) {
+  check_i32(ids, "ids"); check_bf16(dout, "dout"); check_f32(dtable, "dtable");
+  TORCH_CHECK(dtable.is_contiguous() && dout.is_contiguous(), "embedding_bwd layout");
+  const c10::cuda::CUDAGuard guard(dout.device());
+  agrpo::launch_embedding_bwd(ids.data_ptr<int>(), dout.data_ptr(), dtable.data_ptr<float>(), (int)ids.numel(),
+                              (int)dtable.size(1), (int)dtable.size(0), cur_stream());
+}
+void rmsnorm_fwd(const Tensor& x, const Tensor& w, Tensor& y, const OptTensor& rstd, double eps) {
+  check_bf16(x, "x"); check_bf16(w, "w"); check_bf16(y, "y");
+  TORCH_CHECK(x.is_contiguous() && y.is_contiguous() && w.is_contiguous() && x.size(-1) % 8 == 0, "rmsnorm_fwd layout");
+  const int H = (int)x.size(-1);
+  const int T = (int)(x.numel() / H);
+  const c10::cuda::CUDAGuard guard(x.device());
+  agrpo::launch_rmsnorm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), opt_ptr<float>(rstd), T, H, (float)eps, cur_stream());
+}
+void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd, Tensor& dx, const OptTensor& dw,
+                 bool accumulate_dx) {
+  check_bf16(dy, "dy"); check_bf16(x, "x"); check_bf16(w, "w"); check_f32(rstd, "rstd"); check_bf16(dx, "dx");
+  TORCH_CHECK(x.is_contiguous() && dy.is_contiguous() && dx.is_contiguous(), "rmsnorm_bwd layout");
+  const int H = (int)x.size(-1);
+  const int T = (int)(x.numel() / H);
+  const c10::cuda::CUDAGuard guard(x.device());
+  agrpo::launch_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(),
+                            opt_ptr<float>(dw), T, H, accumulate_dx, cur_stream());
+}
+void colsum(const Tensor& a, Tensor& out) {
+  check_bf16(a, "a"); check_f32(out, "out");
+  TORCH_CHECK(a.dim() == 2 && a.stride(1) == 1 && a.stride(0) % 2 == 0 && out.numel() == a.size(1), "colsum layout");
+  const c10::cuda::CUDAGuard guard(a.device());
+  agrpo::launch_colsum(a.data_ptr(), out.data_ptr<float>(), (int)a.size(0), (int)a.size(1), a.stride(0), cur_stream());
+}
+void rope_inplace(Tensor& qkv, const Tensor& pos, const Tensor& cos_t, const Tensor& sin_t, int64_t n_rot_heads,
+                  int64_t head_dim, bool backward) {
+  check_bf16(qkv, "qkv"); check_i32(pos, "pos"); check_f32(cos_t, "cos"); check_f32(sin_t, "sin");
+  TORCH_CHECK(qkv.dim() == 2 && qkv.stride(1) == 1, "rope: qkv [T, C]");
+  TORCH_CHECK(cos_t.is_contiguous() && sin_t.is_contiguous() && cos_t.size(1) == head_dim / 2, "rope tables");
+  TORCH_CHECK(n_rot_heads * head_dim <= qkv.size(1), "rope: heads exceed row");
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  agrpo::launch_rope(qkv.data_ptr(), pos.data_ptr<int>(), cos_t.data_ptr<float>(), sin_t.data_ptr<float>(),
+                     (int)qkv.size(0), (int)n_rot_heads, (int)head_dim, qkv.stride(0), (int)cos_t.size(0), backward,
+                     cur_stream());
+}
+void swiglu_fwd(const Tensor& gu, Tensor& out) {
+  check_bf16(gu, "gu"); check_bf16(out, "out");
+  TORCH_CHECK(gu.is_contiguous() && out.is_contiguous() && gu.size(-1) == 2 * out.size(-1) && out.size(-1) % 8 == 0, "swiglu layout");
+  const int F = (int)out.size(-1);
+  const c10::cuda::CUDAGuard guard(gu.device());
+  agrpo::launch_swiglu_fwd(gu.data_ptr(), out.data_ptr(), (int)(out.numel() / F), F, cur_stream());
+}
+void swiglu_bwd(const Tensor& gu, const Tensor& dout, Tensor& dgu) {
+  check_bf16(gu, "gu"); check_bf16(dout, "dout"); check_bf16(dgu, "dgu");
+  TORCH_CHECK(gu.is_contiguous() && dout.is_contiguous() && dgu.is_contiguous(), "swiglu_bwd layout");
+  const int F = (int)dout.size(-1);
+  const c10::cuda::CUDAGuard guard(gu.device());
+  agrpo::launch_swiglu_bwd(gu.data_ptr(), dout.data_ptr(), dgu.data_ptr(), (int)(dout.numel() / F), F, cur_stream());
+}
+void add_bf16(const Tensor& a, const Tensor& b, Tensor& out) {
+  check_bf16(a, "a"); check_bf16(b, "b"); check_bf16(out, "out");
+  TORCH_CHECK(a.is_contiguous() && b.is_contiguous() && out.is_contiguous() && a.numel() == b.numel() && a.numel() % 8 == 0, "add layout");
+  const c10::cuda::CUDAGuard guard(a.device());
+  agrpo::launch_add_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), cur_stream());
+}
+void sumsq(const Tensor& g, double scale, Tensor& out) {
+  check_f32(g, "g"); check_f32(out, "out");
+  TORCH_CHECK(g.is_contiguous(), "sumsq layout");
+  const c10::cuda::CUDAGuard guard(g.device());
+  agrpo::launch_sumsq(g.data_ptr<float>(), g.numel(), (float)scale, out.data_ptr<float>(), cur_stream());
+}
+void adamw_step(Tensor& p, Tensor& m, Tensor& v, Tensor& g, const OptTensor& p16, double lr, double beta1, double beta2,
+                double eps, double wd, int64_t step, double grad_scale, const OptTensor& norm_sq, double max_norm,
+                bool zero_grad) {
+  check_f32(p, "p"); check_f32(m, "m"); check_f32(v, "v"); check_f32(g, "g");
+  TORCH_CHECK(p.is_contiguous() && m.is_contiguous() && v.is_contiguous() && g.is_contiguous(), "adamw layout");
+  TORCH_CHECK(p.numel() == m.numel() && p.numel() == v.numel() && p.numel() == g.numel(), "adamw sizes");
+  if (p16.has_value() && p16->defined()) { check_bf16(*p16, "p16"); TORCH_CHECK(p16->numel() == p.numel() && p16->is_contiguous(), "p16"); }
+  const c10::cuda::CUDAGuard guard(p.device());
+  agrpo::launch_adamw(p.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), g.data_ptr<float>(), opt_ptr<void>(p16),
+                      p.numel(), (float)lr, (float)beta1, (float)beta2, (float)eps, (float)wd, (int)step, (float)grad_scale,
+                      opt_ptr<float>(norm_sq), (float)max_norm, zero_grad, cur_stream());
+}
+void cast_f32_bf16(const Tensor& in, Tensor& out) {
+  check_f32(in, "in"); check_bf16(out, "out");
+  TORCH_CHECK(in.is_contiguous() && out.is_contiguous() && in.numel() == out.numel(), "cast layout");
+  const c10::cuda::CUDAGuard guard(in.device());
+  agrpo::launch_cast_f32_bf16(in.data_ptr<float>(), out.data_ptr(), in.numel(), cur_stream());
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm_bf16", &gemm_bf16, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("a_mn") = false,
+        py::arg("b_mn") = false, py::arg("bias") = py::none(), py::arg("alpha") = 1.0, py::arg("accumulate") = false,
+        py::arg("status") = py::none());
+  m.def("embedding_fwd", &embedding_fwd);
+  m.def("embedding_bwd", &embedding_bwd);
+  m.def("rmsnorm_fwd", &rmsnorm_fwd, py::arg("x"), py::arg("w"), py::arg("y"), py::arg("rstd") = py::none(),
+        py::arg("eps") = 1e-6);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd, py::arg("dy"), py::arg("x"), py::arg("w"), py::arg("rstd"), py::arg("dx"),
+        py::arg("dw") = py::none(), py::arg("accumulate_dx") = false);
+  m.def("colsum", &colsum);
+  m.def("rope_inplace", &rope_inplace);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("add_bf16", &add_bf16);
+  m.def("sumsq", &sumsq);
+  m.def("adamw_step", &adamw_step, py::arg("p"), py::arg("m"), py::arg("v"), py::arg("g"), py::arg("p16") = py::none(),
+        py::arg("lr") = 1e-6, py::arg("beta1") = 0.9, py::arg("beta2") = 0.999, py::arg("eps") = 1e-8,
+        py::arg("wd") = 0.0, py::arg("step") = 1, py::arg("grad_scale") = 1.0, py::arg("norm_sq") = py::none(),
+        py::arg("max_norm") = 0.0, py::arg("zero_grad") = false);
+  m.def("cast_f32_bf16", &cast_f32_bf16);
+}

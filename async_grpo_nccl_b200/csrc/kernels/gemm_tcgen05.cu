@@ -1,0 +1,61 @@
+// Host launcher for the tcgen05 GEMM (kernel in gemm_tcgen05.cuh).
+#include "../common/tensormap.h"
+#include "../launchers.h"
+#include "gemm_tcgen05.cuh"
+
+namespace agrpo {
+
+namespace {
+
+template <int BN, bool A_MN, bool B_MN>
+void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int num_sms, cudaStream_t stream) {
+  using S = GemmSmem<BN>;
+  auto kernel = gemm_tcgen05_kernel<BN, A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal), "gemm smem attr");
+    configured = true;
+  }
+  const int tiles = ((p.M + kGemmBM - 1) / kGemmBM) * ((p.N + BN - 1) / BN);
+  const int grid = tiles < num_sms ? tiles : num_sms;
+  kernel<<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, p);
+  check_cuda(cudaGetLastError(), "gemm_tcgen05 launch");
+}
+
+template <int BN>
+void dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int sms,
+                    cudaStream_t s) {
+  if (!a_mn && !b_mn) return launch_gemm<BN, false, false>(ta, tb, p, sms, s);
+  if (!a_mn && b_mn) return launch_gemm<BN, false, true>(ta, tb, p, sms, s);
+  if (a_mn && b_mn) return launch_gemm<BN, true, true>(ta, tb, p, sms, s);
+  return launch_gemm<BN, true, false>(ta, tb, p, sms, s);
+}
+
+}  // namespace
+
+// d[M,N] = alpha * op(a) . op(b)^T (+ bias) (+ d); see launchers.h for the operand conventions.
+void launch_gemm_bf16(const void* a, long long lda, const void* b, long long ldb, void* d, long long ldd, int M, int N,
+                      int K, bool a_mn, bool b_mn, const void* bias, float alpha, bool out_fp32, bool accumulate,
+                      int* status, int num_sms, cudaStream_t stream) {
+  // Narrow outputs use the 128-wide tile so that more CTAs are busy.
+  const bool wide = N > 128 && ((long long)M * N) >= (long long)128 * 256 * 64;
+  const int BN = wide ? 256 : 128;
+  CUtensorMap ta, tb;
+  if (!a_mn) ta = make_tmap_2d(a, K, M, lda, 64, kGemmBM);
+  else       ta = make_tmap_2d(a, M, K, lda, 64, 64);
+  if (!b_mn) tb = make_tmap_2d(b, K, N, ldb, 64, BN);
+  else       tb = make_tmap_2d(b, N, K, ldb, 64, 64);
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.D = d;
+  p.ldd = ldd;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.alpha = alpha;
+  p.out_fp32 = out_fp32 ? 1 : 0;
+  p.accumulate = accumulate ? 1 : 0;
+  p.status = status;
+  if (BN == 256) dispatch_major<256>(a_mn, b_mn, ta, tb, p, num_sms, stream);
+  else           dispatch_major<128>(a_mn, b_mn, ta, tb, p, num_sms, stream);
+}
+
+}  // namespace agrpo

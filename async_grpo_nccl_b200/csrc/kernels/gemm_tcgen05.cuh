@@ -1,0 +1,266 @@
+// Persistent warp-specialised bf16 GEMM for sm_100a: TMA -> shared-memory ring -> tcgen05.mma with the
+// accumulator in tensor memory -> tcgen05.ld epilogue.
+//
+//   D[M, N] = alpha * (A . B^T) (+ bias[N]) (+ D)          A is M x K, B is N x K (logical)
+//
+// Either operand may be stored K-major (row-major [rows, K]) or MN-major (row-major [K, rows]); the
+// three combinations a transformer needs are forward y = x W^T (K,K), input gradient dx = dy W
+// (K,MN) and weight gradient dW = dy^T x (MN,MN). This replaces the cuBLAS calls behind the
+// reference's HF linear layers (gpu_process_worker.py:988-1041 runs them under bf16 autocast).
+//
+// CTA = 6 warps: warp 0 issues TMA loads, warp 1 issues MMAs (and owns the TMEM allocation), warps
+// 2-5 run the epilogue, one TMEM lane quarter each. Two accumulator buffers of BN columns let the
+// epilogue of tile i overlap the main loop of tile i+1.
+#pragma once
+#include "../common/ptx.cuh"
+
+namespace agrpo {
+
+struct GemmParams {
+  int M, N, K;
+  void* D;            // bf16 or fp32, row-major
+  long long ldd;      // elements
+  const __nv_bfloat16* bias;  // [N] or nullptr
+  float alpha;
+  int out_fp32;       // 1: D is fp32
+  int accumulate;     // 1: D += result (read-modify-write in the epilogue)
+  int* status;        // error word, may be nullptr
+};
+
+static constexpr int kGemmBM = 128;
+static constexpr int kGemmBK = 64;
+static constexpr int kGemmThreads = 192;
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int kABytes = kGemmBM * kGemmBK * 2;
+  static constexpr int kBBytes = BN * kGemmBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+};
+
+// Tile order: bands of 16 row-tiles, column-tile fastest across a band, so that the CTAs running at
+// the same time share A and B tiles through L2.
+__device__ __forceinline__ void gemm_tile_coords(int idx, int tiles_m, int tiles_n, int& tm, int& tn) {
+  constexpr int kBand = 16;
+  const int per_band = kBand * tiles_n;
+  const int band = idx / per_band;
+  const int rem = idx - band * per_band;
+  const int band_rows = min(kBand, tiles_m - band * kBand);
+  tm = band * kBand + rem % band_rows;
+  tn = rem / band_rows;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const GemmParams p) {
+  using S = GemmSmem<BN>;
+  constexpr int kStages = S::kStages;
+  constexpr uint32_t kTmemCols = 2 * BN;
+  constexpr uint32_t kIdesc = umma_idesc_bf16(kGemmBM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * S::kStageBytes);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tfull_bar = empty_bar + kStages;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + kGemmBM - 1) / kGemmBM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (p.K + kGemmBK - 1) / kGemmBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull_bar[b], 1);
+      mbar_init(&tempty_bar[b], 4);
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        gemm_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        const int m0 = tm * kGemmBM, n0 = tn * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
+            report_status(p.status, kStatusWaitEmptyTimeout);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * S::kStageBytes;
+          uint8_t* sb = sa + S::kABytes;
+          mbar_expect_tx(&full_bar[stage], S::kStageBytes);
+          const int k0 = kb * kGemmBK;
+          if constexpr (!A_MN) {
+            tma_load_2d(sa, &tmA, &full_bar[stage], k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kGemmBM / 64; ++j) tma_load_2d(sa + j * 8192, &tmA, &full_bar[stage], m0 + j * 64, k0);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d(sb, &tmB, &full_bar[stage], k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tmB, &full_bar[stage], n0 + j * 64, k0);
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int buf = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&tempty_bar[buf], acc_phase ^ 1)) {
+          report_status(p.status, kStatusWaitTmemEmptyTimeout);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase)) {
+            report_status(p.status, kStatusWaitFullTimeout);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * S::kStageBytes);
+          const uint32_t sb = sa + S::kABytes;
+#pragma unroll
+          for (int k = 0; k < kGemmBK / 16; ++k) {
+            const uint64_t da = A_MN ? umma_smem_desc(sa + k * 2048, 8192, 1024) : umma_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? umma_smem_desc(sb + k * 2048, 8192, 1024) : umma_smem_desc(sb + k * 32, 16, 1024);
+            tc_mma_f16(tmem_d, da, db, kIdesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[stage]);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) tc_commit(&tfull_bar[buf]);
+      }
+    }
+  } else {
+    // ------------------------------ Epilogue ------------------------------
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32)
+    int local = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      int tm, tn;
+      gemm_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      const int buf = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      if (!mbar_wait(&tfull_bar[buf], acc_phase)) {
+        report_status(p.status, kStatusWaitTmemFullTimeout);
+        break;
+      }
+      tc_fence_after();
+      const int row = tm * kGemmBM + quarter * 32 + lane;
+      const int n0 = tn * BN;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tc_wait_ld();
+        const int col0 = n0 + c * 32;
+        if (row < p.M && col0 < p.N) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) v[i] += __bfloat162float(p.bias[col0 + i]);
+          }
+          const bool full = (col0 + 32 <= p.N);
+          if (p.out_fp32) {
+            float* d = reinterpret_cast<float*>(p.D) + static_cast<long long>(row) * p.ldd + col0;
+            if (full && ((reinterpret_cast<uintptr_t>(d) & 15) == 0)) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                if (p.accumulate) {
+                  const float4 old = *reinterpret_cast<const float4*>(d + i);
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                *reinterpret_cast<float4*>(d + i) = o;
+              }
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < p.N) d[i] = p.accumulate ? d[i] + v[i] : v[i];
+            }
+          } else {
+            __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<long long>(row) * p.ldd + col0;
+            if (full && !p.accumulate && ((reinterpret_cast<uintptr_t>(d) & 15) == 0)) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                uint4 o;
+                o.x = pack_bf16x2(v[i], v[i + 1]);
+                o.y = pack_bf16x2(v[i + 2], v[i + 3]);
+                o.z = pack_bf16x2(v[i + 4], v[i + 5]);
+                o.w = pack_bf16x2(v[i + 6], v[i + 7]);
+                *reinterpret_cast<uint4*>(d + i) = o;
+              }
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < p.N) {
+                  const float o = p.accumulate ? __bfloat162float(d[i]) + v[i] : v[i];
+                  d[i] = __float2bfloat16(o);
+                }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace agrpo

@@ -1,0 +1,48 @@
+// Raw-pointer launchers implemented in the .cu files. They include no torch header so that nvcc
+// only sees CUDA code; bindings.cpp (host compiler) wraps them for Python.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <stdexcept>
+#include <string>
+
+namespace agrpo {
+
+inline void check_cuda(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+// d[M,N] = alpha * A . B^T (+ bias[N]) (+ d). bf16 operands, fp32 accumulation on tcgen05.
+//   a_mn = false: a is [M, K] row-major with pitch lda; a_mn = true: a is [K, M] row-major
+//   b_mn = false: b is [N, K] row-major with pitch ldb; b_mn = true: b is [K, N] row-major
+// Pitches are in elements and must be multiples of 8; base pointers 16-byte aligned.
+void launch_gemm_bf16(const void* a, long long lda, const void* b, long long ldb, void* d, long long ldd, int M, int N,
+                      int K, bool a_mn, bool b_mn, const void* bias, float alpha, bool out_fp32, bool accumulate,
+                      int* status, int num_sms, cudaStream_t stream);
+
+
+// ---- bandwidth-bound decoder ops (elementwise.cu); bf16 activations, H and F multiples of 8 ----
+void launch_embedding_fwd(const int* ids, const void* table, void* out, int T, int H, int V, cudaStream_t s);
+void launch_embedding_bwd(const int* ids, const void* dout, float* dtable, int T, int H, int V, cudaStream_t s);
+void launch_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int T, int H, float eps, cudaStream_t s);
+// dw (fp32 [H], may be nullptr) is accumulated with atomic adds.
+void launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw, int T,
+                        int H, bool accumulate_dx, cudaStream_t s);
+// out[c] += sum over rows of a[r, c]; a has row pitch lda (elements).
+void launch_colsum(const void* a, float* out, int T, int C, long long lda, cudaStream_t s);
+void launch_rope(void* qkv, const int* pos, const float* cos_t, const float* sin_t, int T, int n_rot_heads, int D,
+                 long long row_pitch, int max_pos, bool backward, cudaStream_t s);
+void launch_swiglu_fwd(const void* gu, void* out, int T, int F, cudaStream_t s);
+void launch_swiglu_bwd(const void* gu, const void* dout, void* dgu, int T, int F, cudaStream_t s);
+void launch_add_bf16(const void* a, const void* b, void* out, long long n, cudaStream_t s);
+
+// ---- optimizer (optimizer.cu) ----
+// *out += scale^2 * sum(g^2)
+void launch_sumsq(const float* g, long long n, float scale, float* out, cudaStream_t s);
+void launch_adamw(float* p, float* m, float* v, float* g, void* p16, long long n, float lr, float beta1, float beta2,
+                  float eps, float wd, int step, float grad_scale, const float* norm_sq, float max_norm, bool zero_grad,
+                  cudaStream_t s);
+void launch_cast_f32_bf16(const float* in, void* out, long long n, cudaStream_t s);
+
+}  // namespace agrpo
