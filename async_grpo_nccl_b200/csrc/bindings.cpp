@@ -153,6 +153,24 @@ void cast_f32_bf16(const Tensor& in, Tensor& out) {
   agrpo::launch_cast_f32_bf16(in.data_ptr<float>(), out.data_ptr(), in.numel(), cur_stream());
 }
 
+// qkv: [T, (Hq + 2*Hkv) * D] fused projection output (q heads, then k heads, then v heads).
+void attn_varlen_fwd(const Tensor& qkv, Tensor& out, const OptTensor& lse, const Tensor& tiles, int64_t Hq, int64_t Hkv,
+                     int64_t D, double softmax_scale, const OptTensor& status) {
+  check_bf16(qkv, "qkv"); check_bf16(out, "out"); check_i32(tiles, "tiles");
+  TORCH_CHECK(qkv.dim() == 2 && qkv.stride(1) == 1 && qkv.size(1) == (Hq + 2 * Hkv) * D, "attn: qkv shape");
+  TORCH_CHECK(out.dim() == 2 && out.stride(1) == 1 && out.size(1) == Hq * D && out.size(0) == qkv.size(0), "attn: out shape");
+  TORCH_CHECK(tiles.is_contiguous() && tiles.dim() == 2 && tiles.size(1) == 4, "attn: tiles [n,4]");
+  TORCH_CHECK(qkv.stride(0) % 8 == 0 && out.stride(0) % 8 == 0, "attn: pitches must be multiples of 8");
+  if (lse.has_value() && lse->defined()) { check_f32(*lse, "lse"); TORCH_CHECK(lse->is_contiguous() && lse->numel() == Hq * qkv.size(0), "attn: lse [Hq,T]"); }
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  const int T = (int)qkv.size(0);
+  const int C = (int)qkv.size(1);
+  agrpo::launch_attn_varlen_fwd(qkv.data_ptr(), qkv.stride(0), C, qkv.data_ptr(), qkv.stride(0), C, qkv.data_ptr(),
+                                qkv.stride(0), C, 0, (int)(Hq * D), (int)((Hq + Hkv) * D), out.data_ptr(), out.stride(0),
+                                opt_ptr<float>(lse), tiles.data_ptr<int>(), (int)tiles.size(0), T, (int)Hq, (int)Hkv, (int)D,
+                                (float)softmax_scale, opt_ptr<int>(status), cur_stream());
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -170,6 +188,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("add_bf16", &add_bf16);
+  m.def("attn_varlen_fwd", &attn_varlen_fwd, py::arg("qkv"), py::arg("out"), py::arg("lse"), py::arg("tiles"),
+        py::arg("Hq"), py::arg("Hkv"), py::arg("D"), py::arg("softmax_scale"), py::arg("status") = py::none());
   m.def("sumsq", &sumsq);
   m.def("adamw_step", &adamw_step, py::arg("p"), py::arg("m"), py::arg("v"), py::arg("g"), py::arg("p16") = py::none(),
         py::arg("lr") = 1e-6, py::arg("beta1") = 0.9, py::arg("beta2") = 0.999, py::arg("eps") = 1e-8,

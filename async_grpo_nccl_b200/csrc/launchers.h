@@ -37,6 +37,16 @@ void launch_swiglu_fwd(const void* gu, void* out, int T, int F, cudaStream_t s);
 void launch_swiglu_bwd(const void* gu, const void* dout, void* dgu, int T, int F, cudaStream_t s);
 void launch_add_bf16(const void* a, const void* b, void* out, long long n, cudaStream_t s);
 
+// ---- attention (attn_varlen_*.cu) ----
+// Causal varlen attention over packed rows. q/k/v are row-major matrices with T rows (they may be the
+// same fused qkv buffer); head h of q occupies columns [q_col0 + h*D, q_col0 + (h+1)*D), likewise
+// k / v with kv heads. tiles: int32 [n_tiles, 4] = {seq_start, seq_len, q0, 0}, q0 a multiple of 128.
+// lse: fp32 [Hq, T] (natural log), may be nullptr.
+void launch_attn_varlen_fwd(const void* q, long long ldq, int q_cols, const void* k, long long ldk, int k_cols,
+                            const void* v, long long ldv, int v_cols, int q_col0, int k_col0, int v_col0, void* out,
+                            long long ldo, float* lse, const int* tiles, int n_tiles, int T, int Hq, int Hkv, int D,
+                            float softmax_scale, int* status, cudaStream_t s);
+
 // ---- optimizer (optimizer.cu) ----
 // *out += scale^2 * sum(g^2)
 void launch_sumsq(const float* g, long long n, float scale, float* out, cudaStream_t s);
