@@ -171,6 +171,31 @@ void attn_varlen_fwd(const Tensor& qkv, Tensor& out, const OptTensor& lse, const
                                 (float)softmax_scale, opt_ptr<int>(status), cur_stream());
 }
 
+// dqkv: [T, (Hq + 2*Hkv) * D] receives dq | dk | dv. delta [Hq, T] and dq_acc [T, Hq*D] are fp32 scratch.
+void attn_varlen_bwd(const Tensor& qkv, const Tensor& out, const Tensor& dout, const Tensor& lse, Tensor& delta,
+                     Tensor& dq_acc, Tensor& dqkv, const Tensor& tiles, int64_t Hq, int64_t Hkv, int64_t D,
+                     double softmax_scale, const OptTensor& status) {
+  check_bf16(qkv, "qkv"); check_bf16(out, "out"); check_bf16(dout, "dout"); check_bf16(dqkv, "dqkv");
+  check_f32(lse, "lse"); check_f32(delta, "delta"); check_f32(dq_acc, "dq_acc"); check_i32(tiles, "tiles");
+  const int64_t T = qkv.size(0), C = (Hq + 2 * Hkv) * D;
+  TORCH_CHECK(qkv.dim() == 2 && qkv.stride(1) == 1 && qkv.size(1) == C, "attn_bwd: qkv shape");
+  TORCH_CHECK(dqkv.dim() == 2 && dqkv.stride(1) == 1 && dqkv.size(1) == C && dqkv.size(0) == T, "attn_bwd: dqkv shape");
+  TORCH_CHECK(out.size(0) == T && out.size(1) == Hq * D && out.stride(1) == 1, "attn_bwd: out shape");
+  TORCH_CHECK(dout.size(0) == T && dout.size(1) == Hq * D && dout.stride(1) == 1, "attn_bwd: dout shape");
+  TORCH_CHECK(lse.is_contiguous() && lse.numel() == Hq * T && delta.is_contiguous() && delta.numel() == Hq * T, "attn_bwd: lse/delta");
+  TORCH_CHECK(dq_acc.is_contiguous() && dq_acc.numel() == T * Hq * D, "attn_bwd: dq_acc");
+  TORCH_CHECK(tiles.is_contiguous() && tiles.dim() == 2 && tiles.size(1) == 4, "attn_bwd: tiles [n,4]");
+  TORCH_CHECK(qkv.stride(0) % 8 == 0 && dout.stride(0) % 8 == 0 && dqkv.stride(0) % 8 == 0, "attn_bwd: pitches");
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  agrpo::launch_attn_varlen_bwd(qkv.data_ptr(), qkv.stride(0), (int)C, qkv.data_ptr(), qkv.stride(0), (int)C, qkv.data_ptr(),
+                                qkv.stride(0), (int)C, 0, (int)(Hq * D), (int)((Hq + Hkv) * D), out.data_ptr(), out.stride(0),
+                                dout.data_ptr(), dout.stride(0), lse.data_ptr<float>(), delta.data_ptr<float>(),
+                                dq_acc.data_ptr<float>(), dqkv.data_ptr(), dqkv.stride(0), dqkv.data_ptr(), dqkv.stride(0),
+                                (int)(Hq * D), dqkv.data_ptr(), dqkv.stride(0), (int)((Hq + Hkv) * D), tiles.data_ptr<int>(),
+                                (int)tiles.size(0), (int)T, (int)Hq, (int)Hkv, (int)D, (float)softmax_scale,
+                                opt_ptr<int>(status), cur_stream());
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -190,6 +215,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("add_bf16", &add_bf16);
   m.def("attn_varlen_fwd", &attn_varlen_fwd, py::arg("qkv"), py::arg("out"), py::arg("lse"), py::arg("tiles"),
         py::arg("Hq"), py::arg("Hkv"), py::arg("D"), py::arg("softmax_scale"), py::arg("status") = py::none());
+  m.def("attn_varlen_bwd", &attn_varlen_bwd, py::arg("qkv"), py::arg("out"), py::arg("dout"), py::arg("lse"),
+        py::arg("delta"), py::arg("dq_acc"), py::arg("dqkv"), py::arg("tiles"), py::arg("Hq"), py::arg("Hkv"), py::arg("D"),
+        py::arg("softmax_scale"), py::arg("status") = py::none());
   m.def("sumsq", &sumsq);
   m.def("adamw_step", &adamw_step, py::arg("p"), py::arg("m"), py::arg("v"), py::arg("g"), py::arg("p16") = py::none(),
         py::arg("lr") = 1e-6, py::arg("beta1") = 0.9, py::arg("beta2") = 0.999, py::arg("eps") = 1e-8,

@@ -47,6 +47,16 @@ void launch_attn_varlen_fwd(const void* q, long long ldq, int q_cols, const void
                             long long ldo, float* lse, const int* tiles, int n_tiles, int T, int Hq, int Hkv, int D,
                             float softmax_scale, int* status, cudaStream_t s);
 
+// Backward of the above. out/dout: [T, Hq*D] rows. delta: fp32 [Hq, T] scratch, dq_acc: fp32 [T, Hq*D]
+// scratch (zeroed here). dq (pitch ld_dq, columns [0, Hq*D)), dk / dv (head h at column d*_col0 + h*D)
+// are bf16 and may alias one fused [T, (Hq+2Hkv)*D] gradient buffer.
+void launch_attn_varlen_bwd(const void* q, long long ldq, int q_cols, const void* k, long long ldk, int k_cols,
+                            const void* v, long long ldv, int v_cols, int q_col0, int k_col0, int v_col0, const void* out,
+                            long long ldo, const void* dout, long long lddo, const float* lse, float* delta, float* dq_acc,
+                            void* dq, long long ld_dq, void* dk, long long ld_dk, int dk_col0, void* dv, long long ld_dv,
+                            int dv_col0, const int* tiles, int n_tiles, int T, int Hq, int Hkv, int D, float softmax_scale,
+                            int* status, cudaStream_t s);
+
 // ---- optimizer (optimizer.cu) ----
 // *out += scale^2 * sum(g^2)
 void launch_sumsq(const float* g, long long n, float scale, float* out, cudaStream_t s);
