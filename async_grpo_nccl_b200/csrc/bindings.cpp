@@ -196,6 +196,65 @@ void attn_varlen_bwd(const Tensor& qkv, const Tensor& out, const Tensor& dout, c
                                 opt_ptr<int>(status), cur_stream());
 }
 
+int64_t lmhead_num_groups(int64_t V, int64_t T) { return agrpo::lmhead_num_groups((int)V, (int)T); }
+int64_t grpo_num_loss_stats() { return agrpo::grpo_num_loss_stats(); }
+
+void lmhead_logprob(const Tensor& hidden, const Tensor& weight, const Tensor& labels, double temperature, Tensor& partials,
+                    Tensor& label_logit, const OptTensor& logp, const OptTensor& entropy, const OptTensor& lse,
+                    const OptTensor& status) {
+  check_bf16(hidden, "hidden"); check_bf16(weight, "weight"); check_i32(labels, "labels");
+  check_f32(partials, "partials"); check_f32(label_logit, "label_logit");
+  TORCH_CHECK(hidden.dim() == 2 && weight.dim() == 2 && hidden.stride(1) == 1 && weight.stride(1) == 1, "lmhead: 2-D");
+  const int64_t T = hidden.size(0), H = hidden.size(1), V = weight.size(0);
+  TORCH_CHECK(weight.size(1) == H && labels.numel() == T && labels.is_contiguous(), "lmhead: shapes");
+  TORCH_CHECK(hidden.stride(0) % 8 == 0 && weight.stride(0) % 8 == 0, "lmhead: pitches");
+  TORCH_CHECK(partials.numel() >= 3 * agrpo::lmhead_num_groups((int)V, (int)T) * T && label_logit.numel() >= T, "lmhead: scratch");
+  for (const OptTensor* o : {&logp, &entropy, &lse})
+    if (o->has_value() && (*o)->defined()) { check_f32(**o, "lmhead out"); TORCH_CHECK((*o)->numel() == T && (*o)->is_contiguous(), "lmhead out [T]"); }
+  const c10::cuda::CUDAGuard guard(hidden.device());
+  agrpo::launch_lmhead_logprob(hidden.data_ptr(), hidden.stride(0), weight.data_ptr(), weight.stride(0), labels.data_ptr<int>(),
+                               (int)T, (int)H, (int)V, (float)temperature, partials.data_ptr<float>(),
+                               label_logit.data_ptr<float>(), opt_ptr<float>(logp), opt_ptr<float>(entropy), opt_ptr<float>(lse),
+                               opt_ptr<int>(status), num_sms(), cur_stream());
+}
+
+void grpo_token_loss(const Tensor& logp, const OptTensor& old_logp, const OptTensor& ref_logp, const Tensor& adv,
+                     const Tensor& labels, const OptTensor& entropy, const OptTensor& old_entropy, double clip_low,
+                     double clip_high, double clip_c, double kl_beta, double grad_weight, const OptTensor& dlogp,
+                     Tensor& stats) {
+  check_f32(logp, "logp"); check_f32(adv, "adv"); check_i32(labels, "labels"); check_f32(stats, "stats");
+  const int64_t T = logp.numel();
+  TORCH_CHECK(adv.numel() == T && labels.numel() == T && stats.numel() >= agrpo::grpo_num_loss_stats(), "grpo_token_loss shapes");
+  for (const OptTensor* o : {&old_logp, &ref_logp, &entropy, &old_entropy, &dlogp})
+    if (o->has_value() && (*o)->defined()) { check_f32(**o, "grpo_token_loss opt"); TORCH_CHECK((*o)->numel() == T, "grpo_token_loss opt [T]"); }
+  const c10::cuda::CUDAGuard guard(logp.device());
+  agrpo::launch_grpo_token_loss(logp.data_ptr<float>(), opt_ptr<float>(old_logp), opt_ptr<float>(ref_logp), adv.data_ptr<float>(),
+                                labels.data_ptr<int>(), opt_ptr<float>(entropy), opt_ptr<float>(old_entropy), (int)T,
+                                (float)clip_low, (float)clip_high, (float)clip_c, (float)kl_beta, (float)grad_weight,
+                                opt_ptr<float>(dlogp), stats.data_ptr<float>(), cur_stream());
+}
+
+void lmhead_backward(const Tensor& hidden, const Tensor& weight, const Tensor& labels, const Tensor& lse, const Tensor& dlogp,
+                     double temperature, Tensor& dz_chunk, Tensor& dh_acc, const OptTensor& dweight, const OptTensor& status) {
+  check_bf16(hidden, "hidden"); check_bf16(weight, "weight"); check_i32(labels, "labels"); check_f32(lse, "lse");
+  check_f32(dlogp, "dlogp"); check_bf16(dz_chunk, "dz_chunk"); check_f32(dh_acc, "dh_acc");
+  const int64_t T = hidden.size(0), H = hidden.size(1), V = weight.size(0);
+  TORCH_CHECK(dz_chunk.dim() == 2 && dz_chunk.is_contiguous() && dz_chunk.size(0) >= T && dz_chunk.size(1) % 256 == 0, "lmhead_bwd: dz_chunk [T, 256k]");
+  TORCH_CHECK(dh_acc.is_contiguous() && dh_acc.numel() == T * H, "lmhead_bwd: dh_acc");
+  TORCH_CHECK(hidden.stride(1) == 1 && weight.stride(1) == 1 && hidden.stride(0) % 8 == 0 && weight.stride(0) % 8 == 0, "lmhead_bwd: layout");
+  float* dw = nullptr; long long ld_dw = 0;
+  if (dweight.has_value() && dweight->defined()) {
+    check_f32(*dweight, "dweight");
+    TORCH_CHECK(dweight->dim() == 2 && dweight->size(0) == V && dweight->size(1) == H && dweight->stride(1) == 1, "lmhead_bwd: dweight");
+    dw = dweight->data_ptr<float>(); ld_dw = dweight->stride(0);
+  }
+  const c10::cuda::CUDAGuard guard(hidden.device());
+  agrpo::launch_lmhead_backward(hidden.data_ptr(), hidden.stride(0), weight.data_ptr(), weight.stride(0), labels.data_ptr<int>(),
+                                lse.data_ptr<float>(), dlogp.data_ptr<float>(), (int)T, (int)H, (int)V, (float)temperature,
+                                dz_chunk.data_ptr(), (int)dz_chunk.size(1), dh_acc.data_ptr<float>(), dw, ld_dw,
+                                opt_ptr<int>(status), num_sms(), cur_stream());
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -218,6 +277,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attn_varlen_bwd", &attn_varlen_bwd, py::arg("qkv"), py::arg("out"), py::arg("dout"), py::arg("lse"),
         py::arg("delta"), py::arg("dq_acc"), py::arg("dqkv"), py::arg("tiles"), py::arg("Hq"), py::arg("Hkv"), py::arg("D"),
         py::arg("softmax_scale"), py::arg("status") = py::none());
+  m.def("lmhead_num_groups", &lmhead_num_groups);
+  m.def("grpo_num_loss_stats", &grpo_num_loss_stats);
+  m.def("lmhead_logprob", &lmhead_logprob, py::arg("hidden"), py::arg("weight"), py::arg("labels"), py::arg("temperature"),
+        py::arg("partials"), py::arg("label_logit"), py::arg("logp") = py::none(), py::arg("entropy") = py::none(),
+        py::arg("lse") = py::none(), py::arg("status") = py::none());
+  m.def("grpo_token_loss", &grpo_token_loss, py::arg("logp"), py::arg("old_logp"), py::arg("ref_logp"), py::arg("adv"),
+        py::arg("labels"), py::arg("entropy"), py::arg("old_entropy"), py::arg("clip_low"), py::arg("clip_high"),
+        py::arg("clip_c"), py::arg("kl_beta"), py::arg("grad_weight"), py::arg("dlogp"), py::arg("stats"));
+  m.def("lmhead_backward", &lmhead_backward, py::arg("hidden"), py::arg("weight"), py::arg("labels"), py::arg("lse"),
+        py::arg("dlogp"), py::arg("temperature"), py::arg("dz_chunk"), py::arg("dh_acc"), py::arg("dweight") = py::none(),
+        py::arg("status") = py::none());
   m.def("sumsq", &sumsq);
   m.def("adamw_step", &adamw_step, py::arg("p"), py::arg("m"), py::arg("v"), py::arg("g"), py::arg("p16") = py::none(),
         py::arg("lr") = 1e-6, py::arg("beta1") = 0.9, py::arg("beta2") = 0.999, py::arg("eps") = 1e-8,

@@ -7,28 +7,13 @@ namespace agrpo {
 
 namespace {
 
-template <int BN, bool A_MN, bool B_MN>
-void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int num_sms, cudaStream_t stream) {
-  using S = GemmSmem<BN>;
-  auto kernel = gemm_tcgen05_kernel<BN, A_MN, B_MN>;
-  static bool configured = false;
-  if (!configured) {
-    check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal), "gemm smem attr");
-    configured = true;
-  }
-  const int tiles = ((p.M + kGemmBM - 1) / kGemmBM) * ((p.N + BN - 1) / BN);
-  const int grid = tiles < num_sms ? tiles : num_sms;
-  kernel<<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, p);
-  check_cuda(cudaGetLastError(), "gemm_tcgen05 launch");
-}
-
 template <int BN>
-void dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int sms,
-                    cudaStream_t s) {
-  if (!a_mn && !b_mn) return launch_gemm<BN, false, false>(ta, tb, p, sms, s);
-  if (!a_mn && b_mn) return launch_gemm<BN, false, true>(ta, tb, p, sms, s);
-  if (a_mn && b_mn) return launch_gemm<BN, true, true>(ta, tb, p, sms, s);
-  return launch_gemm<BN, true, false>(ta, tb, p, sms, s);
+void dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmShape& p,
+                    const StoreEpilogue& e, int sms, cudaStream_t s) {
+  if (!a_mn && !b_mn) return gemm_launch<BN, false, false>(ta, tb, p, e, sms, s);
+  if (!a_mn && b_mn) return gemm_launch<BN, false, true>(ta, tb, p, e, sms, s);
+  if (a_mn && b_mn) return gemm_launch<BN, true, true>(ta, tb, p, e, sms, s);
+  return gemm_launch<BN, true, false>(ta, tb, p, e, sms, s);
 }
 
 }  // namespace
@@ -45,17 +30,19 @@ void launch_gemm_bf16(const void* a, long long lda, const void* b, long long ldb
   else       ta = make_tmap_2d(a, M, K, lda, 64, 64);
   if (!b_mn) tb = make_tmap_2d(b, K, N, ldb, 64, BN);
   else       tb = make_tmap_2d(b, N, K, ldb, 64, 64);
-  GemmParams p;
+  GemmShape p;
   p.M = M; p.N = N; p.K = K;
-  p.D = d;
-  p.ldd = ldd;
-  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
-  p.alpha = alpha;
-  p.out_fp32 = out_fp32 ? 1 : 0;
-  p.accumulate = accumulate ? 1 : 0;
+  p.group_n = 1;
   p.status = status;
-  if (BN == 256) dispatch_major<256>(a_mn, b_mn, ta, tb, p, num_sms, stream);
-  else           dispatch_major<128>(a_mn, b_mn, ta, tb, p, num_sms, stream);
+  StoreEpilogue e;
+  e.D = d;
+  e.ldd = ldd;
+  e.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  e.alpha = alpha;
+  e.out_fp32 = out_fp32 ? 1 : 0;
+  e.accumulate = accumulate ? 1 : 0;
+  if (BN == 256) dispatch_major<256>(a_mn, b_mn, ta, tb, p, e, num_sms, stream);
+  else           dispatch_major<128>(a_mn, b_mn, ta, tb, p, e, num_sms, stream);
 }
 
 }  // namespace agrpo

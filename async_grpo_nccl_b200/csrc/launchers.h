@@ -57,6 +57,29 @@ void launch_attn_varlen_bwd(const void* q, long long ldq, int q_cols, const void
                             int dv_col0, const int* tiles, int n_tiles, int T, int Hq, int Hkv, int D, float softmax_scale,
                             int* status, cudaStream_t s);
 
+// ---- fused lm_head + GRPO loss (lmhead_loss.cu) ----
+// Number of partial-statistics groups the forward writes for a [T, V] problem.
+int lmhead_num_groups(int V, int T);
+// logits z = hidden . weight^T / temperature never reach memory. labels[t] is the target token of row t
+// (already shifted), negative = masked. partials: fp32 [3 * groups * T] scratch; label_logit: fp32 [T] scratch.
+// Outputs (each may be nullptr): logp[t] = z[label] - lse (0 on masked rows), entropy[t], lse[t].
+void launch_lmhead_logprob(const void* hidden, long long ldh, const void* weight, long long ldw, const int* labels, int T,
+                           int H, int V, float temperature, float* partials, float* label_logit, float* logp,
+                           float* entropy, float* lse, int* status, int num_sms, cudaStream_t stream);
+// Per-token dual-clip GRPO objective (+ kl_beta * k3 KL against ref_logp), its derivative w.r.t. logp scaled by
+// grad_weight, and sums over valid tokens in stats[grpo_num_loss_stats()] (atomic adds; zero it first).
+void launch_grpo_token_loss(const float* logp, const float* old_logp, const float* ref_logp, const float* adv,
+                            const int* labels, const float* entropy, const float* old_entropy, int T, float clip_low,
+                            float clip_high, float clip_c, float kl_beta, float grad_weight, float* dlogp, float* stats,
+                            cudaStream_t stream);
+int grpo_num_loss_stats();
+// dh_acc (fp32 [T, H]) = d loss / d hidden; dweight (fp32, pitch ld_dw, may be nullptr) += d loss / d weight.
+// dz_chunk: bf16 [T, chunk_cols] scratch, chunk_cols a multiple of 256.
+void launch_lmhead_backward(const void* hidden, long long ldh, const void* weight, long long ldw, const int* labels,
+                            const float* lse, const float* dlogp, int T, int H, int V, float temperature, void* dz_chunk,
+                            int chunk_cols, float* dh_acc, float* dweight, long long ld_dw, int* status, int num_sms,
+                            cudaStream_t stream);
+
 // ---- optimizer (optimizer.cu) ----
 // *out += scale^2 * sum(g^2)
 void launch_sumsq(const float* g, long long n, float scale, float* out, cudaStream_t s);
