@@ -255,6 +255,59 @@ void lmhead_backward(const Tensor& hidden, const Tensor& weight, const Tensor& l
                                 opt_ptr<int>(status), num_sms(), cur_stream());
 }
 
+void kv_cache_write(const Tensor& qkv, const Tensor& slots, Tensor& k_cache, Tensor& v_cache, int64_t Hq, int64_t Hkv, int64_t D) {
+  check_bf16(qkv, "qkv"); check_i32(slots, "slots"); check_bf16(k_cache, "k_cache"); check_bf16(v_cache, "v_cache");
+  TORCH_CHECK(qkv.dim() == 2 && qkv.stride(1) == 1 && qkv.size(1) == (Hq + 2 * Hkv) * D && qkv.stride(0) % 8 == 0, "kv_cache_write: qkv");
+  TORCH_CHECK(k_cache.dim() == 4 && k_cache.is_contiguous() && v_cache.is_contiguous() && k_cache.size(1) == Hkv && k_cache.size(3) == D, "kv_cache_write: cache [blocks, Hkv, bs, D]");
+  TORCH_CHECK(slots.numel() == qkv.size(0), "kv_cache_write: slots");
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  agrpo::launch_kv_cache_write(qkv.data_ptr(), qkv.stride(0), (int)(Hq * D), (int)((Hq + Hkv) * D), slots.data_ptr<int>(),
+                               k_cache.data_ptr(), v_cache.data_ptr(), (int)qkv.size(0), (int)Hkv, (int)D, (int)k_cache.size(2),
+                               cur_stream());
+}
+
+void paged_decode_attn(const Tensor& qkv, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_tables,
+                       const Tensor& seq_lens, Tensor& out, int64_t Hq, int64_t Hkv, int64_t D, double softmax_scale,
+                       int64_t splits, const OptTensor& part_o, const OptTensor& part_ml, const OptTensor& status) {
+  check_bf16(qkv, "qkv"); check_bf16(k_cache, "k_cache"); check_bf16(v_cache, "v_cache"); check_bf16(out, "out");
+  check_i32(block_tables, "block_tables"); check_i32(seq_lens, "seq_lens");
+  const int64_t B = qkv.size(0);
+  TORCH_CHECK(qkv.dim() == 2 && qkv.stride(1) == 1 && qkv.size(1) >= Hq * D, "decode: qkv");
+  TORCH_CHECK(out.dim() == 2 && out.size(0) == B && out.size(1) == Hq * D && out.stride(1) == 1, "decode: out");
+  TORCH_CHECK(block_tables.dim() == 2 && block_tables.is_contiguous() && block_tables.size(0) == B && seq_lens.numel() == B, "decode: tables");
+  TORCH_CHECK(k_cache.dim() == 4 && k_cache.is_contiguous() && v_cache.is_contiguous(), "decode: cache");
+  if (splits > 1) {
+    TORCH_CHECK(part_o.has_value() && part_ml.has_value(), "decode: split scratch required");
+    check_f32(*part_o, "part_o"); check_f32(*part_ml, "part_ml");
+    TORCH_CHECK(part_o->numel() >= B * Hkv * splits * 8 * D && part_ml->numel() >= B * Hkv * splits * 16, "decode: scratch size");
+  }
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  agrpo::launch_paged_decode_attn(qkv.data_ptr(), qkv.stride(0), 0, k_cache.data_ptr(), v_cache.data_ptr(),
+                                  block_tables.data_ptr<int>(), seq_lens.data_ptr<int>(), (int)B, (int)block_tables.size(1),
+                                  (int)k_cache.size(0), (int)Hq, (int)Hkv, (int)D, (int)k_cache.size(2), (float)softmax_scale,
+                                  (int)splits, out.data_ptr(), out.stride(0), opt_ptr<float>(part_o), opt_ptr<float>(part_ml),
+                                  opt_ptr<int>(status), cur_stream());
+}
+
+int64_t lm_sample_num_groups(int64_t V, int64_t rows) { return agrpo::lm_sample_num_groups((int)V, (int)rows); }
+
+void lm_sample(const Tensor& hidden, const Tensor& weight, double temperature, const Tensor& seeds, Tensor& part_f,
+               Tensor& part_i, Tensor& tokens, const OptTensor& logprobs, const OptTensor& status) {
+  check_bf16(hidden, "hidden"); check_bf16(weight, "weight"); check_f32(part_f, "part_f"); check_i32(part_i, "part_i");
+  check_i32(tokens, "tokens");
+  TORCH_CHECK(seeds.is_cuda() && seeds.scalar_type() == torch::kInt64 && seeds.is_contiguous(), "lm_sample: seeds int64");
+  const int64_t R = hidden.size(0), H = hidden.size(1), V = weight.size(0);
+  TORCH_CHECK(hidden.stride(1) == 1 && weight.stride(1) == 1 && hidden.stride(0) % 8 == 0 && weight.stride(0) % 8 == 0 && weight.size(1) == H, "lm_sample: layout");
+  const int64_t groups = agrpo::lm_sample_num_groups((int)V, (int)R);
+  TORCH_CHECK(seeds.numel() >= R && tokens.numel() >= R && part_f.numel() >= 4 * groups * R && part_i.numel() >= groups * R, "lm_sample: sizes");
+  if (logprobs.has_value() && logprobs->defined()) { check_f32(*logprobs, "logprobs"); TORCH_CHECK(logprobs->numel() >= R, "lm_sample: logprobs"); }
+  const c10::cuda::CUDAGuard guard(hidden.device());
+  agrpo::launch_lm_sample(hidden.data_ptr(), hidden.stride(0), weight.data_ptr(), weight.stride(0), (int)R, (int)H, (int)V,
+                          (float)temperature, reinterpret_cast<const unsigned long long*>(seeds.data_ptr<int64_t>()),
+                          part_f.data_ptr<float>(), part_i.data_ptr<int>(), tokens.data_ptr<int>(), opt_ptr<float>(logprobs),
+                          opt_ptr<int>(status), num_sms(), cur_stream());
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -287,6 +340,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("clip_c"), py::arg("kl_beta"), py::arg("grad_weight"), py::arg("dlogp"), py::arg("stats"));
   m.def("lmhead_backward", &lmhead_backward, py::arg("hidden"), py::arg("weight"), py::arg("labels"), py::arg("lse"),
         py::arg("dlogp"), py::arg("temperature"), py::arg("dz_chunk"), py::arg("dh_acc"), py::arg("dweight") = py::none(),
+        py::arg("status") = py::none());
+  m.def("kv_cache_write", &kv_cache_write);
+  m.def("paged_decode_attn", &paged_decode_attn, py::arg("qkv"), py::arg("k_cache"), py::arg("v_cache"),
+        py::arg("block_tables"), py::arg("seq_lens"), py::arg("out"), py::arg("Hq"), py::arg("Hkv"), py::arg("D"),
+        py::arg("softmax_scale"), py::arg("splits") = 1, py::arg("part_o") = py::none(), py::arg("part_ml") = py::none(),
+        py::arg("status") = py::none());
+  m.def("lm_sample_num_groups", &lm_sample_num_groups);
+  m.def("lm_sample", &lm_sample, py::arg("hidden"), py::arg("weight"), py::arg("temperature"), py::arg("seeds"),
+        py::arg("part_f"), py::arg("part_i"), py::arg("tokens"), py::arg("logprobs") = py::none(),
         py::arg("status") = py::none());
   m.def("sumsq", &sumsq);
   m.def("adamw_step", &adamw_step, py::arg("p"), py::arg("m"), py::arg("v"), py::arg("g"), py::arg("p16") = py::none(),

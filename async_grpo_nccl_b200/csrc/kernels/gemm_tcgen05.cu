@@ -22,9 +22,19 @@ void dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorM
 void launch_gemm_bf16(const void* a, long long lda, const void* b, long long ldb, void* d, long long ldd, int M, int N,
                       int K, bool a_mn, bool b_mn, const void* bias, float alpha, bool out_fp32, bool accumulate,
                       int* status, int num_sms, cudaStream_t stream) {
-  // Narrow outputs use the 128-wide tile so that more CTAs are busy.
-  const bool wide = N > 128 && ((long long)M * N) >= (long long)128 * 256 * 64;
-  const int BN = wide ? 256 : 128;
+  // Widest column tile that still yields about one work item per SM; the 64 / 32 wide tiles serve
+  // skinny decode-time GEMMs (K-major operands only) where the weight stream must be spread over all SMs.
+  const int tiles_m = (M + kGemmBM - 1) / kGemmBM;
+  const bool plain = !a_mn && !b_mn;
+  const int cands[4] = {256, 128, 64, 32};
+  int BN = plain ? 32 : 128;
+  for (int i = 0; i < (plain ? 4 : 2); ++i) {
+    const int bn = cands[i];
+    if ((long long)tiles_m * ((N + bn - 1) / bn) >= 120) {
+      BN = bn;
+      break;
+    }
+  }
   CUtensorMap ta, tb;
   if (!a_mn) ta = make_tmap_2d(a, K, M, lda, 64, kGemmBM);
   else       ta = make_tmap_2d(a, M, K, lda, 64, 64);
@@ -42,7 +52,9 @@ void launch_gemm_bf16(const void* a, long long lda, const void* b, long long ldb
   e.out_fp32 = out_fp32 ? 1 : 0;
   e.accumulate = accumulate ? 1 : 0;
   if (BN == 256) dispatch_major<256>(a_mn, b_mn, ta, tb, p, e, num_sms, stream);
-  else           dispatch_major<128>(a_mn, b_mn, ta, tb, p, e, num_sms, stream);
+  else if (BN == 128) dispatch_major<128>(a_mn, b_mn, ta, tb, p, e, num_sms, stream);
+  else if (BN == 64) gemm_launch<64, false, false>(ta, tb, p, e, num_sms, stream);
+  else gemm_launch<32, false, false>(ta, tb, p, e, num_sms, stream);
 }
 
 }  // namespace agrpo

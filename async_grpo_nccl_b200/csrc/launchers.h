@@ -80,6 +80,23 @@ void launch_lmhead_backward(const void* hidden, long long ldh, const void* weigh
                             int chunk_cols, float* dh_acc, float* dweight, long long ld_dw, int* status, int num_sms,
                             cudaStream_t stream);
 
+// ---- rollout engine (rollout.cu) ----
+// KV cache layout per layer: [num_blocks, Hkv, block_size, D] (K and V separately). slots[t] < 0 skips token t.
+void launch_kv_cache_write(const void* qkv, long long row_pitch, int k_col0, int v_col0, const int* slots, void* k_cache,
+                           void* v_cache, int T, int Hkv, int D, int block_size, cudaStream_t s);
+// One query token per sequence against the paged cache. part_o: fp32 [B, Hkv, splits, 8, D], part_ml: fp32
+// [B, Hkv, splits, 8, 2] (only touched when splits > 1).
+void launch_paged_decode_attn(const void* q, long long ldq, int q_col0, const void* k_cache, const void* v_cache,
+                              const int* block_tables, const int* seq_lens, int B, int max_blocks, int num_cache_blocks,
+                              int Hq, int Hkv, int D, int block_size, float softmax_scale, int splits, void* out,
+                              long long ldo, float* part_o, float* part_ml, int* status, cudaStream_t s);
+int lm_sample_num_groups(int V, int rows);
+// tokens[r] ~ softmax(hidden[r] . weight^T / temperature) (argmax when temperature <= 0); logprobs may be nullptr.
+// part_f: fp32 [4 * groups * rows], part_i: int32 [groups * rows] scratch.
+void launch_lm_sample(const void* hidden, long long ldh, const void* weight, long long ldw, int rows, int H, int V,
+                      float temperature, const unsigned long long* seeds, float* part_f, int* part_i, int* tokens,
+                      float* logprobs, int* status, int num_sms, cudaStream_t stream);
+
 // ---- optimizer (optimizer.cu) ----
 // *out += scale^2 * sum(g^2)
 void launch_sumsq(const float* g, long long n, float scale, float* out, cudaStream_t s);
