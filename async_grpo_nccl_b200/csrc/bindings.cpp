@@ -3,6 +3,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include "host/packer.h"
 #include "launchers.h"
 
 namespace {
@@ -31,7 +32,7 @@ inline T* opt_ptr(const OptTensor& t) {
 }
 
 void gemm_bf16(const Tensor& a, const Tensor& b, Tensor& d, bool a_mn, bool b_mn, const OptTensor& bias, double alpha,
-               bool accumulate, const OptTensor& status) {
+               bool accumulate, const OptTensor& status, const OptTensor& residual) {
   check_bf16(a, "gemm a");
   check_bf16(b, "gemm b");
   TORCH_CHECK(d.is_cuda() && (d.scalar_type() == torch::kBFloat16 || d.scalar_type() == torch::kFloat32), "gemm d");
@@ -54,9 +55,15 @@ void gemm_bf16(const Tensor& a, const Tensor& b, Tensor& d, bool a_mn, bool b_mn
     TORCH_CHECK(bias->numel() == N && bias->is_contiguous(), "gemm: bias must be contiguous [N]");
   }
   if (status.has_value() && status->defined()) check_i32(*status, "gemm status");
+  long long ldr = 0;
+  if (residual.has_value() && residual->defined()) {
+    check_bf16(*residual, "gemm residual");
+    TORCH_CHECK(residual->dim() == 2 && residual->size(0) == M && residual->size(1) == N && residual->stride(1) == 1, "gemm: residual [M, N]");
+    ldr = residual->stride(0);
+  }
   agrpo::launch_gemm_bf16(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), d.data_ptr(), d.stride(0), (int)M, (int)N,
                           (int)K, a_mn, b_mn, opt_ptr<void>(bias), (float)alpha, d.scalar_type() == torch::kFloat32,
-                          accumulate, opt_ptr<int>(status), num_sms(), cur_stream());
+                          accumulate, opt_ptr<int>(status), num_sms(), cur_stream(), opt_ptr<void>(residual), ldr);
 }
 
 void embedding_fwd(const Tensor& ids, const Tensor& table, Tensor& out) {
@@ -160,6 +167,7 @@ void attn_varlen_fwd(const Tensor& qkv, Tensor& out, const OptTensor& lse, const
   TORCH_CHECK(qkv.dim() == 2 && qkv.stride(1) == 1 && qkv.size(1) == (Hq + 2 * Hkv) * D, "attn: qkv shape");
   TORCH_CHECK(out.dim() == 2 && out.stride(1) == 1 && out.size(1) == Hq * D && out.size(0) == qkv.size(0), "attn: out shape");
   TORCH_CHECK(tiles.is_contiguous() && tiles.dim() == 2 && tiles.size(1) == 4, "attn: tiles [n,4]");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(tiles.data_ptr()) & 15) == 0, "attn: tile table must be 16-byte aligned");
   TORCH_CHECK(qkv.stride(0) % 8 == 0 && out.stride(0) % 8 == 0, "attn: pitches must be multiples of 8");
   if (lse.has_value() && lse->defined()) { check_f32(*lse, "lse"); TORCH_CHECK(lse->is_contiguous() && lse->numel() == Hq * qkv.size(0), "attn: lse [Hq,T]"); }
   const c10::cuda::CUDAGuard guard(qkv.device());
@@ -185,6 +193,7 @@ void attn_varlen_bwd(const Tensor& qkv, const Tensor& out, const Tensor& dout, c
   TORCH_CHECK(lse.is_contiguous() && lse.numel() == Hq * T && delta.is_contiguous() && delta.numel() == Hq * T, "attn_bwd: lse/delta");
   TORCH_CHECK(dq_acc.is_contiguous() && dq_acc.numel() == T * Hq * D, "attn_bwd: dq_acc");
   TORCH_CHECK(tiles.is_contiguous() && tiles.dim() == 2 && tiles.size(1) == 4, "attn_bwd: tiles [n,4]");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(tiles.data_ptr()) & 15) == 0, "attn_bwd: tile table must be 16-byte aligned");
   TORCH_CHECK(qkv.stride(0) % 8 == 0 && dout.stride(0) % 8 == 0 && dqkv.stride(0) % 8 == 0, "attn_bwd: pitches");
   const c10::cuda::CUDAGuard guard(qkv.device());
   agrpo::launch_attn_varlen_bwd(qkv.data_ptr(), qkv.stride(0), (int)C, qkv.data_ptr(), qkv.stride(0), (int)C, qkv.data_ptr(),
@@ -308,12 +317,50 @@ void lm_sample(const Tensor& hidden, const Tensor& weight, double temperature, c
                           opt_ptr<int>(status), num_sms(), cur_stream());
 }
 
+// ---- host packer (CPU tensors) ----
+inline void check_cpu(const Tensor& t, torch::ScalarType st, const char* name) {
+  TORCH_CHECK(!t.is_cuda() && t.scalar_type() == st && t.is_contiguous(), name, ": contiguous CPU tensor of the right dtype");
+}
+int64_t pack_count_tiles(const Tensor& in_lens, const Tensor& out_lens, int64_t tile) {
+  check_cpu(in_lens, torch::kInt32, "in_lens"); check_cpu(out_lens, torch::kInt32, "out_lens");
+  return agrpo::count_tiles(in_lens.data_ptr<int>(), out_lens.data_ptr<int>(), (int)in_lens.numel(), (int)tile);
+}
+void pack_microbatch(const Tensor& ids, const Tensor& in_lens, const Tensor& out_lens, const Tensor& adv,
+                     const OptTensor& logprobs, const OptTensor& entropies, const OptTensor& ref_logprobs, int64_t tile,
+                     Tensor& out_int, Tensor& out_float) {
+  check_cpu(ids, torch::kInt32, "ids"); check_cpu(in_lens, torch::kInt32, "in_lens"); check_cpu(out_lens, torch::kInt32, "out_lens");
+  check_cpu(adv, torch::kFloat32, "adv"); check_cpu(out_int, torch::kInt32, "out_int"); check_cpu(out_float, torch::kFloat32, "out_float");
+  const int n = (int)in_lens.numel();
+  const long long T = ids.numel();
+  long long total_out = 0, total = 0;
+  for (int i = 0; i < n; ++i) { total_out += out_lens.data_ptr<int>()[i]; total += in_lens.data_ptr<int>()[i] + out_lens.data_ptr<int>()[i]; }
+  TORCH_CHECK(total == T, "pack: lengths do not add up to the number of ids");
+  const long long n_tiles = agrpo::count_tiles(in_lens.data_ptr<int>(), out_lens.data_ptr<int>(), n, (int)tile);
+  TORCH_CHECK(out_int.numel() >= agrpo::pack_tiles_offset(T, n, total_out) + 4 * n_tiles, "pack: out_int too small");
+  TORCH_CHECK(out_float.numel() >= 5 * T, "pack: out_float too small");
+  auto fp = [&](const OptTensor& t, const char* name) -> const float* {
+    if (!t.has_value() || !t->defined()) return nullptr;
+    check_cpu(*t, torch::kFloat32, name);
+    TORCH_CHECK(t->numel() == T, name, ": expected one value per token");
+    return t->data_ptr<float>();
+  };
+  agrpo::pack_microbatch(ids.data_ptr<int>(), in_lens.data_ptr<int>(), out_lens.data_ptr<int>(), adv.data_ptr<float>(),
+                         fp(logprobs, "logprobs"), fp(entropies, "entropies"), fp(ref_logprobs, "ref_logprobs"), n, (int)tile,
+                         out_int.data_ptr<int>(), out_float.data_ptr<float>(), T, total_out, n_tiles);
+}
+Tensor normalize_rewards_cpu(const Tensor& rewards) {
+  check_cpu(rewards, torch::kFloat32, "rewards");
+  Tensor out = torch::empty_like(rewards);
+  agrpo::normalize_rewards(rewards.data_ptr<float>(), (int)rewards.numel(), out.data_ptr<float>());
+  return out;
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_bf16", &gemm_bf16, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("a_mn") = false,
         py::arg("b_mn") = false, py::arg("bias") = py::none(), py::arg("alpha") = 1.0, py::arg("accumulate") = false,
-        py::arg("status") = py::none());
+        py::arg("status") = py::none(), py::arg("residual") = py::none());
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
   m.def("rmsnorm_fwd", &rmsnorm_fwd, py::arg("x"), py::arg("w"), py::arg("y"), py::arg("rstd") = py::none(),
@@ -350,6 +397,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("lm_sample", &lm_sample, py::arg("hidden"), py::arg("weight"), py::arg("temperature"), py::arg("seeds"),
         py::arg("part_f"), py::arg("part_i"), py::arg("tokens"), py::arg("logprobs") = py::none(),
         py::arg("status") = py::none());
+  m.def("pack_count_tiles", &pack_count_tiles);
+  m.def("pack_microbatch", &pack_microbatch);
+  m.def("normalize_rewards", &normalize_rewards_cpu);
   m.def("sumsq", &sumsq);
   m.def("adamw_step", &adamw_step, py::arg("p"), py::arg("m"), py::arg("v"), py::arg("g"), py::arg("p16") = py::none(),
         py::arg("lr") = 1e-6, py::arg("beta1") = 0.9, py::arg("beta2") = 0.999, py::arg("eps") = 1e-8,

@@ -21,7 +21,7 @@ void dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorM
 // d[M,N] = alpha * op(a) . op(b)^T (+ bias) (+ d); see launchers.h for the operand conventions.
 void launch_gemm_bf16(const void* a, long long lda, const void* b, long long ldb, void* d, long long ldd, int M, int N,
                       int K, bool a_mn, bool b_mn, const void* bias, float alpha, bool out_fp32, bool accumulate,
-                      int* status, int num_sms, cudaStream_t stream) {
+                      int* status, int num_sms, cudaStream_t stream, const void* residual, long long ldr) {
   // Widest column tile that still yields about one work item per SM; the 64 / 32 wide tiles serve
   // skinny decode-time GEMMs (K-major operands only) where the weight stream must be spread over all SMs.
   const int tiles_m = (M + kGemmBM - 1) / kGemmBM;
@@ -48,6 +48,8 @@ void launch_gemm_bf16(const void* a, long long lda, const void* b, long long ldb
   e.D = d;
   e.ldd = ldd;
   e.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  e.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  e.ldr = ldr;
   e.alpha = alpha;
   e.out_fp32 = out_fp32 ? 1 : 0;
   e.accumulate = accumulate ? 1 : 0;

@@ -33,6 +33,8 @@ struct StoreEpilogue {
   void* D;            // bf16 or fp32, row-major
   long long ldd;      // elements
   const __nv_bfloat16* bias;  // [N] or nullptr
+  const __nv_bfloat16* residual;  // [M, ldr] added to the result, or nullptr
+  long long ldr;
   float alpha;
   int out_fp32;       // 1: D is fp32
   int accumulate;     // 1: D += result (read-modify-write)
@@ -50,6 +52,25 @@ struct StoreEpilogue {
         if (col0 + i < N) v[i] += __bfloat162float(bias[col0 + i]);
     }
     const bool full = (col0 + 32 <= N);
+    if (residual != nullptr) {
+      const __nv_bfloat16* rp = residual + static_cast<long long>(row) * ldr + col0;
+      if (full && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0)) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          const uint4 w = *reinterpret_cast<const uint4*>(rp + i);
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&w);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h[j]);
+            v[i + 2 * j] += f.x;
+            v[i + 2 * j + 1] += f.y;
+          }
+        }
+      } else {
+        for (int i = 0; i < 32; ++i)
+          if (col0 + i < N) v[i] += __bfloat162float(rp[i]);
+      }
+    }
     if (out_fp32) {
       float* d = reinterpret_cast<float*>(D) + static_cast<long long>(row) * ldd + col0;
       if (full && ((reinterpret_cast<uintptr_t>(d) & 15) == 0)) {

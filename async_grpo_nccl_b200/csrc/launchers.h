@@ -17,9 +17,10 @@ inline void check_cuda(cudaError_t e, const char* what) {
 //   a_mn = false: a is [M, K] row-major with pitch lda; a_mn = true: a is [K, M] row-major
 //   b_mn = false: b is [N, K] row-major with pitch ldb; b_mn = true: b is [K, N] row-major
 // Pitches are in elements and must be multiples of 8; base pointers 16-byte aligned.
+// residual (bf16 [M, ldr], optional) is added to the result, e.g. the skip connection of a decoder block.
 void launch_gemm_bf16(const void* a, long long lda, const void* b, long long ldb, void* d, long long ldd, int M, int N,
                       int K, bool a_mn, bool b_mn, const void* bias, float alpha, bool out_fp32, bool accumulate,
-                      int* status, int num_sms, cudaStream_t stream);
+                      int* status, int num_sms, cudaStream_t stream, const void* residual = nullptr, long long ldr = 0);
 
 
 // ---- bandwidth-bound decoder ops (elementwise.cu); bf16 activations, H and F multiples of 8 ----
