@@ -3,6 +3,9 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <pybind11/stl.h>
+
+#include "host/kv_allocator.h"
 #include "host/packer.h"
 #include "launchers.h"
 
@@ -275,6 +278,20 @@ void kv_cache_write(const Tensor& qkv, const Tensor& slots, Tensor& k_cache, Ten
                                cur_stream());
 }
 
+void kv_cache_write_decode(const Tensor& qkv, const Tensor& block_tables, const Tensor& seq_lens, Tensor& k_cache,
+                           Tensor& v_cache, int64_t Hq, int64_t Hkv, int64_t D, const OptTensor& status) {
+  check_bf16(qkv, "qkv"); check_i32(block_tables, "block_tables"); check_i32(seq_lens, "seq_lens");
+  check_bf16(k_cache, "k_cache"); check_bf16(v_cache, "v_cache");
+  TORCH_CHECK(qkv.dim() == 2 && qkv.stride(1) == 1 && qkv.size(1) == (Hq + 2 * Hkv) * D && qkv.stride(0) % 8 == 0, "kv_write_decode: qkv");
+  TORCH_CHECK(block_tables.dim() == 2 && block_tables.stride(1) == 1 && block_tables.size(0) >= qkv.size(0) && seq_lens.numel() >= qkv.size(0), "kv_write_decode: tables");
+  TORCH_CHECK(k_cache.dim() == 4 && k_cache.is_contiguous() && v_cache.is_contiguous(), "kv_write_decode: cache");
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  agrpo::launch_kv_cache_write_decode(qkv.data_ptr(), qkv.stride(0), (int)(Hq * D), (int)((Hq + Hkv) * D),
+                                      block_tables.data_ptr<int>(), (int)block_tables.stride(0), seq_lens.data_ptr<int>(),
+                                      k_cache.data_ptr(), v_cache.data_ptr(), (int)qkv.size(0), (int)Hkv, (int)D,
+                                      (int)k_cache.size(2), (int)k_cache.size(0), opt_ptr<int>(status), cur_stream());
+}
+
 void paged_decode_attn(const Tensor& qkv, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_tables,
                        const Tensor& seq_lens, Tensor& out, int64_t Hq, int64_t Hkv, int64_t D, double softmax_scale,
                        int64_t splits, const OptTensor& part_o, const OptTensor& part_ml, const OptTensor& status) {
@@ -283,7 +300,7 @@ void paged_decode_attn(const Tensor& qkv, const Tensor& k_cache, const Tensor& v
   const int64_t B = qkv.size(0);
   TORCH_CHECK(qkv.dim() == 2 && qkv.stride(1) == 1 && qkv.size(1) >= Hq * D, "decode: qkv");
   TORCH_CHECK(out.dim() == 2 && out.size(0) == B && out.size(1) == Hq * D && out.stride(1) == 1, "decode: out");
-  TORCH_CHECK(block_tables.dim() == 2 && block_tables.is_contiguous() && block_tables.size(0) == B && seq_lens.numel() == B, "decode: tables");
+  TORCH_CHECK(block_tables.dim() == 2 && block_tables.stride(1) == 1 && block_tables.size(0) >= B && seq_lens.numel() >= B, "decode: tables");
   TORCH_CHECK(k_cache.dim() == 4 && k_cache.is_contiguous() && v_cache.is_contiguous(), "decode: cache");
   if (splits > 1) {
     TORCH_CHECK(part_o.has_value() && part_ml.has_value(), "decode: split scratch required");
@@ -292,7 +309,7 @@ void paged_decode_attn(const Tensor& qkv, const Tensor& k_cache, const Tensor& v
   }
   const c10::cuda::CUDAGuard guard(qkv.device());
   agrpo::launch_paged_decode_attn(qkv.data_ptr(), qkv.stride(0), 0, k_cache.data_ptr(), v_cache.data_ptr(),
-                                  block_tables.data_ptr<int>(), seq_lens.data_ptr<int>(), (int)B, (int)block_tables.size(1),
+                                  block_tables.data_ptr<int>(), seq_lens.data_ptr<int>(), (int)B, (int)block_tables.stride(0),
                                   (int)k_cache.size(0), (int)Hq, (int)Hkv, (int)D, (int)k_cache.size(2), (float)softmax_scale,
                                   (int)splits, out.data_ptr(), out.stride(0), opt_ptr<float>(part_o), opt_ptr<float>(part_ml),
                                   opt_ptr<int>(status), cur_stream());
@@ -357,7 +374,71 @@ Tensor normalize_rewards_cpu(const Tensor& rewards) {
 
 }  // namespace
 
+namespace {
+py::dict prefill_plan_to_dict(const agrpo::PrefillPlan& p) {
+  py::dict d;
+  d["group_ids"] = p.group_ids;
+  d["prompt_lens"] = p.prompt_lens;
+  d["slot_mapping"] = p.slot_mapping;
+  d["seq_ids"] = p.seq_ids;
+  d["seq_slots"] = p.seq_slots;
+  d["copy_src"] = p.copy_src;
+  d["copy_dst"] = p.copy_dst;
+  std::vector<int> us, ui, ub;
+  for (const auto& u : p.updates) { us.push_back(u.slot); ui.push_back(u.index); ub.push_back(u.block); }
+  d["upd_slot"] = us; d["upd_index"] = ui; d["upd_block"] = ub;
+  return d;
+}
+py::dict decode_plan_to_dict(const agrpo::DecodePlan& p) {
+  py::dict d;
+  d["batch_rows"] = p.batch_rows;
+  d["num_active"] = p.num_active;
+  d["active_slots"] = p.active_slots;
+  d["preempted"] = p.preempted;
+  std::vector<int> us, ui, ub;
+  for (const auto& u : p.updates) { us.push_back(u.slot); ui.push_back(u.index); ub.push_back(u.block); }
+  d["upd_slot"] = us; d["upd_index"] = ui; d["upd_block"] = ub;
+  return d;
+}
+}  // namespace
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  py::class_<agrpo::BlockAllocator>(m, "BlockAllocator")
+      .def(py::init<int>())
+      .def("alloc", &agrpo::BlockAllocator::alloc)
+      .def("incref", &agrpo::BlockAllocator::incref)
+      .def("release", &agrpo::BlockAllocator::release)
+      .def("refcount", &agrpo::BlockAllocator::refcount)
+      .def_property_readonly("num_free", &agrpo::BlockAllocator::num_free)
+      .def_property_readonly("num_blocks", &agrpo::BlockAllocator::num_blocks);
+  py::class_<agrpo::Scheduler>(m, "Scheduler")
+      .def(py::init<int, int, int, int, int>(), py::arg("num_blocks"), py::arg("block_size"), py::arg("max_seqs"),
+           py::arg("max_blocks_per_seq"), py::arg("max_prefill_tokens"))
+      .def("add_group",
+           [](agrpo::Scheduler& s, long long group_id, int prompt_len, int n, int max_new_tokens, std::vector<int> forced) {
+             agrpo::GroupRequest g{group_id, prompt_len, n, max_new_tokens, std::move(forced)};
+             s.add_group(g);
+           },
+           py::arg("group_id"), py::arg("prompt_len"), py::arg("n"), py::arg("max_new_tokens"),
+           py::arg("forced_new_tokens") = std::vector<int>())
+      .def("plan_prefill", [](agrpo::Scheduler& s) { return prefill_plan_to_dict(s.plan_prefill()); })
+      .def("plan_decode", [](agrpo::Scheduler& s) { return decode_plan_to_dict(s.plan_decode()); })
+      .def("finish", &agrpo::Scheduler::finish)
+      .def("seq_info",
+           [](const agrpo::Scheduler& s, long long id) -> py::object {
+             const agrpo::SeqState* q = s.seq(id);
+             if (!q) return py::none();
+             py::dict d;
+             d["seq_id"] = q->seq_id; d["group_id"] = q->group_id; d["child"] = q->child; d["slot"] = q->slot;
+             d["prompt_len"] = q->prompt_len; d["len"] = q->len; d["max_len"] = q->max_len; d["forced_len"] = q->forced_len;
+             d["blocks"] = q->blocks;
+             return d;
+           })
+      .def_property_readonly("num_waiting", &agrpo::Scheduler::num_waiting)
+      .def_property_readonly("num_running", &agrpo::Scheduler::num_running)
+      .def_property_readonly("num_free_blocks", &agrpo::Scheduler::num_free_blocks)
+      .def_property_readonly("num_free_slots", &agrpo::Scheduler::num_free_slots);
+
   m.def("gemm_bf16", &gemm_bf16, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("a_mn") = false,
         py::arg("b_mn") = false, py::arg("bias") = py::none(), py::arg("alpha") = 1.0, py::arg("accumulate") = false,
         py::arg("status") = py::none(), py::arg("residual") = py::none());
@@ -389,6 +470,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("dlogp"), py::arg("temperature"), py::arg("dz_chunk"), py::arg("dh_acc"), py::arg("dweight") = py::none(),
         py::arg("status") = py::none());
   m.def("kv_cache_write", &kv_cache_write);
+  m.def("kv_cache_write_decode", &kv_cache_write_decode, py::arg("qkv"), py::arg("block_tables"), py::arg("seq_lens"),
+        py::arg("k_cache"), py::arg("v_cache"), py::arg("Hq"), py::arg("Hkv"), py::arg("D"), py::arg("status") = py::none());
   m.def("paged_decode_attn", &paged_decode_attn, py::arg("qkv"), py::arg("k_cache"), py::arg("v_cache"),
         py::arg("block_tables"), py::arg("seq_lens"), py::arg("out"), py::arg("Hq"), py::arg("Hkv"), py::arg("D"),
         py::arg("softmax_scale"), py::arg("splits") = 1, py::arg("part_o") = py::none(), py::arg("part_ml") = py::none(),

@@ -1,0 +1,105 @@
+// Paged KV-cache block allocator and continuous-batching scheduler for the native rollout engine
+// (host side, no CUDA). They take over the parts of vLLM's engine core that the reference relies on
+// for generation (vllm_worker.py:203-284): block accounting with reference counts so that the n
+// samples of one prompt share the prompt's blocks, admission control, slot assignment, preemption
+// when the pool runs dry, and per-step block-table updates.
+#pragma once
+#include <cstdint>
+#include <deque>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+namespace agrpo {
+
+class BlockAllocator {
+ public:
+  explicit BlockAllocator(int num_blocks);
+  int num_blocks() const { return (int)ref_.size(); }
+  int num_free() const { return (int)free_.size(); }
+  // Returns a block id with refcount 1, or -1 when the pool is empty.
+  int alloc();
+  void incref(int block);
+  // Drops one reference; the block returns to the pool when the count reaches zero.
+  void release(int block);
+  int refcount(int block) const { return ref_[block]; }
+
+ private:
+  std::vector<int> ref_;
+  std::vector<int> free_;
+};
+
+struct SeqState {
+  long long seq_id = -1;
+  long long group_id = -1;     // request (prompt) this sequence belongs to
+  int child = 0;               // index within the group
+  int slot = -1;               // row in the decode batch, -1 while waiting
+  int prompt_len = 0;
+  int len = 0;                 // tokens whose KV is (or is about to be) in the cache
+  int max_len = 0;             // prompt_len + max new tokens
+  int forced_len = -1;         // total length at which generation is cut (EOS forced), -1 = none
+  bool finished = false;
+  std::vector<int> blocks;
+};
+
+struct TableUpdate { int slot, index, block; };
+
+struct GroupRequest {
+  long long group_id;
+  int prompt_len;
+  int n;
+  int max_new_tokens;
+  std::vector<int> forced_new_tokens;  // per child, empty = none
+};
+
+struct PrefillPlan {
+  std::vector<long long> group_ids;     // prompts to prefill this step
+  std::vector<int> prompt_lens;
+  std::vector<int> slot_mapping;        // cache slot of every prompt token, prompts concatenated
+  std::vector<long long> seq_ids;       // children created, n per group in order
+  std::vector<int> seq_slots;           // decode-batch row of each child
+  std::vector<int> copy_src, copy_dst;  // partial last prompt block: copy src -> dst for children 1..n-1
+  std::vector<TableUpdate> updates;     // block-table entries to write on the device
+};
+
+struct DecodePlan {
+  int batch_rows = 0;                   // highest active slot + 1
+  int num_active = 0;
+  std::vector<TableUpdate> updates;     // new blocks for sequences crossing a block boundary
+  std::vector<int> active_slots;
+  std::vector<long long> preempted;     // sequences evicted to make room (caller re-queues their groups)
+};
+
+class Scheduler {
+ public:
+  Scheduler(int num_blocks, int block_size, int max_seqs, int max_blocks_per_seq, int max_prefill_tokens);
+
+  void add_group(const GroupRequest& req);
+  int num_waiting() const { return (int)waiting_.size(); }
+  int num_running() const { return num_running_; }
+  int num_free_blocks() const { return alloc_.num_free(); }
+  int num_free_slots() const { return (int)free_slots_.size(); }
+
+  // Admits as many waiting groups as fit (slots, blocks, prefill-token budget). Empty plan = nothing admitted.
+  PrefillPlan plan_prefill();
+  // Accounts for one more token per running sequence and allocates blocks where a boundary is crossed.
+  DecodePlan plan_decode();
+  // Marks a sequence finished and frees its slot and blocks.
+  void finish(long long seq_id);
+  const SeqState* seq(long long seq_id) const;
+  const SeqState* seq_at_slot(int slot) const;
+  int seq_len_at_slot(int slot) const;
+
+ private:
+  void release_seq(SeqState& s);
+  BlockAllocator alloc_;
+  int block_size_, max_seqs_, max_blocks_per_seq_, max_prefill_tokens_;
+  std::deque<GroupRequest> waiting_;
+  std::unordered_map<long long, SeqState> seqs_;
+  std::vector<long long> slot_owner_;
+  std::vector<int> free_slots_;
+  int num_running_ = 0;
+  long long next_seq_id_ = 0;
+};
+
+}  // namespace agrpo

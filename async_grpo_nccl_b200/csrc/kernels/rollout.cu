@@ -35,6 +35,35 @@ __global__ void kv_cache_write_kernel(const __nv_bfloat16* __restrict__ qkv, lon
   }
 }
 
+// Decode-time variant: row b is the newest token of batch row b, written at position seq_lens[b] - 1 of the
+// sequence whose block table is row b. Rows with seq_lens[b] <= 0 are idle.
+__global__ void kv_cache_write_decode_kernel(const __nv_bfloat16* __restrict__ qkv, long long row_pitch, int k_col0,
+                                             int v_col0, const int* __restrict__ block_tables, int max_blocks,
+                                             const int* __restrict__ seq_lens, __nv_bfloat16* __restrict__ k_cache,
+                                             __nv_bfloat16* __restrict__ v_cache, int B, int Hkv, int D, int block_size,
+                                             int num_cache_blocks, int* status) {
+  const int b = blockIdx.x;
+  if (b >= B) return;
+  const int len = seq_lens[b];
+  if (len <= 0) return;
+  const int pos = len - 1;
+  const int blk = block_tables[(long long)b * max_blocks + pos / block_size];
+  if (blk < 0 || blk >= num_cache_blocks) {
+    if (threadIdx.x == 0) report_status(status, kStatusBadIndex);
+    return;
+  }
+  const int off = pos % block_size;
+  const int per_row = Hkv * D / 8;
+  for (int i = threadIdx.x; i < 2 * per_row; i += blockDim.x) {
+    const bool is_v = i >= per_row;
+    const int j = is_v ? i - per_row : i;
+    const int h = j / (D / 8), c = j % (D / 8);
+    const uint4 val = *reinterpret_cast<const uint4*>(qkv + (long long)b * row_pitch + (is_v ? v_col0 : k_col0) + h * D + c * 8);
+    __nv_bfloat16* dst = (is_v ? v_cache : k_cache) + (((long long)blk * Hkv + h) * block_size + off) * D + c * 8;
+    *reinterpret_cast<uint4*>(dst) = val;
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 // Paged decode attention (one query token per sequence), D = 128, block_size = 16, G = Hq/Hkv <= 8.
 // CTA = (split, kv head, sequence), 4 warps; a warp owns whole 16-token blocks: cp.async double
@@ -395,6 +424,16 @@ void launch_kv_cache_write(const void* qkv, long long row_pitch, int k_col0, int
   kv_cache_write_kernel<<<T, 64, 0, s>>>((const __nv_bfloat16*)qkv, row_pitch, k_col0, v_col0, slots, (__nv_bfloat16*)k_cache,
                                          (__nv_bfloat16*)v_cache, T, Hkv, D, block_size);
   check_cuda(cudaGetLastError(), "kv_cache_write");
+}
+
+void launch_kv_cache_write_decode(const void* qkv, long long row_pitch, int k_col0, int v_col0, const int* block_tables,
+                                  int max_blocks, const int* seq_lens, void* k_cache, void* v_cache, int B, int Hkv, int D,
+                                  int block_size, int num_cache_blocks, int* status, cudaStream_t s) {
+  if (B == 0) return;
+  kv_cache_write_decode_kernel<<<B, 64, 0, s>>>((const __nv_bfloat16*)qkv, row_pitch, k_col0, v_col0, block_tables, max_blocks,
+                                                seq_lens, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, B, Hkv, D,
+                                                block_size, num_cache_blocks, status);
+  check_cuda(cudaGetLastError(), "kv_cache_write_decode");
 }
 
 void launch_paged_decode_attn(const void* q, long long ldq, int q_col0, const void* k_cache, const void* v_cache,

@@ -85,6 +85,9 @@ void launch_lmhead_backward(const void* hidden, long long ldh, const void* weigh
 // KV cache layout per layer: [num_blocks, Hkv, block_size, D] (K and V separately). slots[t] < 0 skips token t.
 void launch_kv_cache_write(const void* qkv, long long row_pitch, int k_col0, int v_col0, const int* slots, void* k_cache,
                            void* v_cache, int T, int Hkv, int D, int block_size, cudaStream_t s);
+void launch_kv_cache_write_decode(const void* qkv, long long row_pitch, int k_col0, int v_col0, const int* block_tables,
+                                  int max_blocks, const int* seq_lens, void* k_cache, void* v_cache, int B, int Hkv, int D,
+                                  int block_size, int num_cache_blocks, int* status, cudaStream_t s);
 // One query token per sequence against the paged cache. part_o: fp32 [B, Hkv, splits, 8, D], part_ml: fp32
 // [B, Hkv, splits, 8, 2] (only touched when splits > 1).
 void launch_paged_decode_attn(const void* q, long long ldq, int q_col0, const void* k_cache, const void* v_cache,

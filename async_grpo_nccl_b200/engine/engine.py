@@ -1,0 +1,533 @@
+"""Native rollout engine: continuous batching over a paged KV cache.
+
+It provides what the reference gets from vLLM's ``AsyncLLM`` (vllm_worker.py:203-284, 709-737): one
+request per prompt with ``n`` samples, temperature sampling with a per-request seed, a cap on new
+tokens, EOS stopping, and prompt-prefix sharing between the ``n`` samples of a group (the prompt is
+prefetched once; only its partial last block is copied per sample).
+
+* scheduling / block accounting: C++ (``csrc/host/kv_allocator.cpp``)
+* prefill: packed varlen forward through the same decoder kernels as training, K/V written to the pages
+* decode: one fused step per token for all running sequences (skinny tcgen05 GEMMs, paged-KV GQA
+  attention, lm_head + Gumbel-max sampling without materialising logits), optionally replayed from a
+  CUDA graph (preset ``throughput``)
+
+``OracleEngine`` offers the same API on any device with plain PyTorch (used by the CPU plumbing
+configuration and as the greedy-decoding oracle in tests).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..models.config import ModelConfig
+from ..models.decoder import NativeDecoder, OracleDecoder
+from ..models.layout import ParamLayout
+from ..packing import PackedBatch, pack_samples
+
+GOLDEN = 0x9E3779B97F4A7C15
+
+
+@dataclass
+class FinishedSequence:
+    request_id: Any
+    child: int
+    output_ids: np.ndarray  # int32
+    finish_reason: str  # "stop" (EOS) | "length"
+    prompt_len: int
+
+
+@dataclass
+class _Request:
+    request_id: Any
+    prompt: np.ndarray
+    n: int
+    max_new_tokens: int
+    temperature: float
+    seed: int
+    forced_new_tokens: Optional[List[int]]
+    ignore_eos: bool
+    group_id: int = -1
+    child_map: Optional[List[int]] = None  # original child indices when a request is a re-queued remainder
+
+
+def _mix_seed(seed: int, child: int) -> int:
+    x = (seed * 0x2545F4914F6CDD1D + (child + 1) * GOLDEN) & 0xFFFFFFFFFFFFFFFF
+    x ^= x >> 29
+    return x & 0x7FFFFFFFFFFFFFFF
+
+
+class RolloutEngine:
+    def __init__(self, cfg: ModelConfig, layout: ParamLayout, params: torch.Tensor, *, max_seqs: int = 256,
+                 max_model_len: Optional[int] = None, num_blocks: Optional[int] = None, block_size: int = 16,
+                 kv_memory_bytes: Optional[int] = None, max_prefill_tokens: int = 16384, use_cuda_graph: bool = False,
+                 eos_token_id: Optional[int] = None):
+        from ..ops import native
+
+        assert params.is_cuda and params.dtype == torch.bfloat16
+        if block_size != 16 or cfg.head_dim != 128:
+            raise ValueError("the native engine supports block_size 16 and head_dim 128")
+        self.C = native()
+        self.cfg, self.layout, self.params = cfg, layout, params
+        self.dev = params.device
+        self.dec = NativeDecoder(cfg, layout, params)
+        self.status = self.dec.status
+        self.block_size = block_size
+        self.max_seqs = int(max_seqs)
+        self.max_model_len = int(max_model_len or cfg.max_position_embeddings)
+        self.max_blocks_per_seq = (self.max_model_len + block_size - 1) // block_size
+        self.eos = cfg.eos_token_id if eos_token_id is None else int(eos_token_id)
+        per_block = cfg.num_hidden_layers * 2 * cfg.num_key_value_heads * block_size * cfg.head_dim * 2
+        if num_blocks is None:
+            if kv_memory_bytes is None:
+                free, _ = torch.cuda.mem_get_info(self.dev)
+                kv_memory_bytes = int(free * 0.6)
+            num_blocks = max(64, kv_memory_bytes // per_block)
+        self.num_blocks = int(num_blocks)
+        self.cache = torch.zeros(cfg.num_hidden_layers, 2, self.num_blocks, cfg.num_key_value_heads, block_size,
+                                 cfg.head_dim, dtype=torch.bfloat16, device=self.dev)
+        self.sched = self.C.Scheduler(self.num_blocks, block_size, self.max_seqs, self.max_blocks_per_seq,
+                                      int(max_prefill_tokens))
+        self.dec.ensure_rope(min(self.max_model_len, cfg.max_position_embeddings))
+        S, H = self.max_seqs, cfg.hidden_size
+        i32 = dict(dtype=torch.int32, device=self.dev)
+        bf = dict(dtype=torch.bfloat16, device=self.dev)
+        self.block_tables = torch.zeros(S, self.max_blocks_per_seq, **i32)
+        self.seq_lens = torch.zeros(S, **i32)
+        self.positions = torch.zeros(S, **i32)
+        self.last_tokens = torch.zeros(S, **i32)
+        self.gen_index = torch.zeros(S, dtype=torch.int64, device=self.dev)
+        self.base_seeds = torch.zeros(S, dtype=torch.int64, device=self.dev)
+        self.step_seeds = torch.zeros(S, dtype=torch.int64, device=self.dev)
+        self.row_ids = torch.arange(S, dtype=torch.int64, device=self.dev)
+        self.hist_cap = self.max_model_len
+        self.history = torch.zeros(S, self.hist_cap, **i32)
+        # decode activations (persistent: no allocation inside a step, required for graph capture)
+        self.b_x = torch.empty(S, H, **bf)
+        self.b_x1 = torch.empty(S, H, **bf)
+        self.b_h = torch.empty(S, H, **bf)
+        self.b_qkv = torch.empty(S, cfg.qkv_dim, **bf)
+        self.b_attn = torch.empty(S, cfg.q_dim, **bf)
+        self.b_gu = torch.empty(S, 2 * cfg.intermediate_size, **bf)
+        self.b_act = torch.empty(S, cfg.intermediate_size, **bf)
+        self.b_tokens = torch.zeros(S, **i32)
+        self.max_splits = 8
+        self.b_part_o = torch.empty(S * cfg.num_key_value_heads * self.max_splits * 8 * cfg.head_dim, dtype=torch.float32,
+                                    device=self.dev)
+        self.b_part_ml = torch.empty(S * cfg.num_key_value_heads * self.max_splits * 16, dtype=torch.float32, device=self.dev)
+        groups = int(self.C.lm_sample_num_groups(cfg.vocab_size, S))
+        g_small = max(groups, int(self.C.lm_sample_num_groups(cfg.vocab_size, 1)))
+        self.b_sample_f = torch.empty(4 * g_small * S, dtype=torch.float32, device=self.dev)
+        self.b_sample_i = torch.empty(g_small * S, **i32)
+        # host mirrors
+        self.h_lens = np.zeros(S, np.int32)
+        self.h_gen = np.zeros(S, np.int64)
+        # The host runs ahead of the device (always with graphs): every step's lengths go through their own pinned
+        # staging buffer, reused only after the copy that read it has completed.
+        self.h_lens_ring = [torch.zeros(S, dtype=torch.int32).pin_memory() for _ in range(8)]
+        self.h_lens_events: List[Optional[torch.cuda.Event]] = [None] * 8
+        self.h_tok_pin = [torch.zeros(S, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.tok_events = [torch.cuda.Event(), torch.cuda.Event()]
+        self.tok_pending: List[Optional[List[Tuple[int, int, int]]]] = [None, None]
+        self.step_count = 0
+        self.use_cuda_graph = use_cuda_graph
+        self.graphs: Dict[Tuple[int, float, int], torch.cuda.CUDAGraph] = {}
+        self.requests: Dict[int, _Request] = {}
+        self.slot_info: Dict[int, Dict[str, Any]] = {}
+        self.pending: List[_Request] = []
+        self.next_group = 0
+        self.temperature: Optional[float] = None
+        self.tokens_generated = 0
+        self.launches = 0
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, request_id: Any, prompt_ids: Sequence[int], n: int = 1, max_new_tokens: int = 128,
+                    temperature: float = 1.0, seed: int = 0, forced_new_tokens: Optional[Sequence[int]] = None,
+                    ignore_eos: bool = False) -> None:
+        prompt = np.ascontiguousarray(np.asarray(prompt_ids, dtype=np.int32))
+        room = self.max_model_len - len(prompt) - 1
+        max_new = max(1, min(int(max_new_tokens), room))
+        forced = None
+        if forced_new_tokens is not None:
+            forced = [max(1, min(int(f), max_new)) for f in forced_new_tokens]
+        self.pending.append(_Request(request_id, prompt, int(n), max_new, float(temperature), int(seed), forced,
+                                     bool(ignore_eos or forced is not None)))
+
+    def has_work(self) -> bool:
+        return bool(self.pending) or self.sched.num_waiting > 0 or self.sched.num_running > 0
+
+    def _admit_pending(self) -> None:
+        keep = []
+        for r in self.pending:
+            if self.temperature is None or self.sched.num_running == 0 and self.sched.num_waiting == 0:
+                self.temperature = r.temperature
+            if r.temperature != self.temperature:
+                keep.append(r)
+                continue
+            r.group_id = self.next_group
+            self.next_group += 1
+            self.requests[r.group_id] = r
+            self.sched.add_group(r.group_id, len(r.prompt), r.n, r.max_new_tokens, r.forced_new_tokens or [])
+        self.pending = keep
+
+    # ------------------------------------------------------------------ model pieces
+    def _kc(self, i: int) -> torch.Tensor:
+        return self.cache[i, 0]
+
+    def _vc(self, i: int) -> torch.Tensor:
+        return self.cache[i, 1]
+
+    def _apply_table_updates(self, plan: Dict[str, Any]) -> None:
+        n = len(plan["upd_slot"])
+        if n == 0:
+            return
+        u = torch.tensor([plan["upd_slot"], plan["upd_index"], plan["upd_block"]], dtype=torch.int64).pin_memory()
+        ud = u.to(self.dev, non_blocking=True)
+        self.block_tables.index_put_((ud[0], ud[1]), ud[2].to(torch.int32))
+
+    def _sample(self, hidden: torch.Tensor, rows: int, seeds: torch.Tensor, tokens: torch.Tensor, temperature: float) -> None:
+        wl = self.layout.view(self.params, self.layout.lm_head_name())
+        self.C.lm_sample(hidden[:rows], wl, temperature, seeds, self.b_sample_f, self.b_sample_i, tokens, None, self.status)
+        self.launches += 2
+
+    def _prefill(self, plan: Dict[str, Any]) -> None:
+        cfg, C, dec = self.cfg, self.C, self.dec
+        gids = plan["group_ids"]
+        reqs = [self.requests[g] for g in gids]
+        samples = [{"sample_ids": r.prompt, "input_len": len(r.prompt), "output_len": 0, "advantage": 0.0} for r in reqs]
+        batch = pack_samples(samples, pin=True).to_device(self.dev)
+        slots = torch.tensor(plan["slot_mapping"], dtype=torch.int32).pin_memory().to(self.dev, non_blocking=True)
+        self._apply_table_updates(plan)
+        cos_t, sin_t = dec.rope_tables(1)
+        T = batch.T
+        x = torch.empty(T, cfg.hidden_size, dtype=torch.bfloat16, device=self.dev)
+        C.embedding_fwd(batch.ids, dec.w("embed"), x)
+        for i in range(cfg.num_hidden_layers):
+            x = dec._layer_fwd(i, x, batch, cos_t, sin_t, None, kv_write=(self._kc(i), self._vc(i), slots))
+        last = (batch.cu_seqlens[1:] - 1).long()
+        xl = x.index_select(0, last)
+        hn = torch.empty_like(xl)
+        C.rmsnorm_fwd(xl, dec.w("final_norm"), hn, None, cfg.rms_norm_eps)
+        if plan["copy_src"]:
+            src = torch.tensor(plan["copy_src"], dtype=torch.int64).pin_memory().to(self.dev, non_blocking=True)
+            dst = torch.tensor(plan["copy_dst"], dtype=torch.int64).pin_memory().to(self.dev, non_blocking=True)
+            self.cache[:, :, dst] = self.cache[:, :, src]
+        # one sampling row per child
+        rep = torch.tensor([r.n for r in reqs], dtype=torch.int64, device=self.dev)
+        hrep = hn.repeat_interleave(rep, dim=0).contiguous()
+        seq_slots = plan["seq_slots"]
+        n_rows = len(seq_slots)
+        seeds_host = []
+        k = 0
+        for r in reqs:
+            for c in range(r.n):
+                seeds_host.append(_mix_seed(r.seed, r.child_map[c] if r.child_map else c))
+                slot = seq_slots[k]
+                forced = r.forced_new_tokens[c] if r.forced_new_tokens else None
+                child = r.child_map[c] if r.child_map else c
+                self.slot_info[slot] = {"seq_id": plan["seq_ids"][k], "req": r, "child": child, "forced": forced, "eos_at": None}
+                self.h_lens[slot] = len(r.prompt)
+                self.h_gen[slot] = 1
+                k += 1
+        seeds = torch.tensor(seeds_host, dtype=torch.int64).pin_memory().to(self.dev, non_blocking=True)
+        slot_idx = torch.tensor(seq_slots, dtype=torch.int64).pin_memory().to(self.dev, non_blocking=True)
+        toks = torch.empty(n_rows, dtype=torch.int32, device=self.dev)
+        # rows are processed in pieces of at most max_seqs so the scratch buffers suffice
+        for s in range(0, n_rows, self.max_seqs):
+            e = min(n_rows, s + self.max_seqs)
+            self._sample(hrep[s:e], e - s, seeds[s:e], toks[s:e], self.temperature or 0.0)
+        self.base_seeds.index_copy_(0, slot_idx, seeds)
+        self.last_tokens.index_copy_(0, slot_idx, toks)
+        self.history[slot_idx, 0] = toks
+        self.gen_index.index_fill_(0, slot_idx, 1)
+        self.tokens_generated += n_rows
+        self.launches += dec.launches
+        dec.launches = 0
+        if not all(r.ignore_eos for r in reqs):
+            th = toks.cpu().numpy()
+            for j, slot in enumerate(seq_slots):
+                info = self.slot_info[slot]
+                if not info["req"].ignore_eos and int(th[j]) == self.eos:
+                    info["eos_at"] = 0
+
+    def _decode_forward(self, B: int, temperature: float, splits: int) -> None:
+        cfg, C, dec = self.cfg, self.C, self.dec
+        cos_t, sin_t = dec.rope_tables(1)
+        x, x1, h, qkv, attn, gu, act = (self.b_x[:B], self.b_x1[:B], self.b_h[:B], self.b_qkv[:B], self.b_attn[:B],
+                                        self.b_gu[:B], self.b_act[:B])
+        bt, sl = self.block_tables, self.seq_lens
+        scale = 1.0 / math.sqrt(cfg.head_dim)
+        C.embedding_fwd(self.last_tokens[:B], dec.w("embed"), x)
+        for i in range(cfg.num_hidden_layers):
+            p = f"layers.{i}."
+            C.rmsnorm_fwd(x, dec.w(p + "ln1"), h, None, cfg.rms_norm_eps)
+            C.gemm_bf16(h, dec.w(p + "wqkv"), qkv, False, False, dec.w(p + "bqkv") if cfg.attention_bias else None, 1.0, False,
+                        self.status, None)
+            C.rope_inplace(qkv, self.positions[:B], cos_t, sin_t, cfg.num_attention_heads + cfg.num_key_value_heads,
+                           cfg.head_dim, False)
+            C.kv_cache_write_decode(qkv, bt, sl, self._kc(i), self._vc(i), cfg.num_attention_heads, cfg.num_key_value_heads,
+                                    cfg.head_dim, self.status)
+            C.paged_decode_attn(qkv, self._kc(i), self._vc(i), bt, sl, attn, cfg.num_attention_heads, cfg.num_key_value_heads,
+                                cfg.head_dim, scale, splits, self.b_part_o, self.b_part_ml, self.status)
+            C.gemm_bf16(attn, dec.w(p + "wo"), x1, False, False, None, 1.0, False, self.status, x)
+            C.rmsnorm_fwd(x1, dec.w(p + "ln2"), h, None, cfg.rms_norm_eps)
+            C.gemm_bf16(h, dec.w(p + "wgu"), gu, False, False, None, 1.0, False, self.status, None)
+            C.swiglu_fwd(gu, act)
+            C.gemm_bf16(act, dec.w(p + "wd"), x, False, False, None, 1.0, False, self.status, x1)
+        C.rmsnorm_fwd(x, dec.w("final_norm"), h, None, cfg.rms_norm_eps)
+        wl = self.layout.view(self.params, self.layout.lm_head_name())
+        C.lm_sample(h, wl, temperature, self.step_seeds, self.b_sample_f, self.b_sample_i, self.b_tokens, None, self.status)
+        # feed the sampled token back and record it
+        self.last_tokens[:B].copy_(self.b_tokens[:B])
+        self.history[self.row_ids[:B], torch.clamp(self.gen_index[:B], max=self.hist_cap - 1)] = self.b_tokens[:B]
+        self.gen_index[:B].add_(1)
+
+    def _launch_count_decode(self, splits: int) -> int:
+        per_layer = 10 + (1 if splits > 1 else 0)
+        return 1 + per_layer * self.cfg.num_hidden_layers + 3
+
+    def _decode(self, plan: Dict[str, Any]) -> None:
+        rows = int(plan["batch_rows"])
+        if rows == 0:
+            return
+        B = min(self.max_seqs, (rows + 63) // 64 * 64)
+        active = plan["active_slots"]
+        self._apply_table_updates(plan)
+        for s in active:
+            self.h_lens[s] += 1
+        ri = self.step_count % len(self.h_lens_ring)
+        if self.h_lens_events[ri] is not None:
+            self.h_lens_events[ri].synchronize()
+        self.h_lens_ring[ri].copy_(torch.from_numpy(self.h_lens))
+        self.seq_lens.copy_(self.h_lens_ring[ri], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.h_lens_events[ri] = ev
+        torch.sub(self.seq_lens, 1, out=self.positions)
+        self.positions.clamp_(min=0)
+        self.step_count += 1
+        torch.add(self.base_seeds, (self.step_count * 0x632BE5AB) & 0x7FFFFFFF, out=self.step_seeds)
+        max_len = int(self.h_lens[:B].max())
+        want = (148 * 3) // max(1, len(active) * self.cfg.num_key_value_heads)
+        splits = int(max(1, min(self.max_splits, want, max(1, max_len // 256))))
+        temperature = float(self.temperature or 0.0)
+        if self.use_cuda_graph:
+            key = (B, temperature, splits)
+            g = self.graphs.get(key)
+            if g is None:
+                # Warm up outside capture (sets function attributes, fills tensor-map caches), then put back what the
+                # warm-up step changed so that the captured step starts from the same state.
+                keep_tok, keep_gen = self.last_tokens.clone(), self.gen_index.clone()
+                self._decode_forward(B, temperature, splits)
+                torch.cuda.synchronize(self.dev)
+                self.last_tokens.copy_(keep_tok)
+                self.gen_index.copy_(keep_gen)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self._decode_forward(B, temperature, splits)
+                self.graphs[key] = g
+            g.replay()
+        else:
+            self._decode_forward(B, temperature, splits)
+        self.launches += self._launch_count_decode(splits)
+        self.tokens_generated += len(active)
+        for s in active:
+            self.h_gen[s] += 1
+        # asynchronous token read-back for EOS detection (one step of lag)
+        need_eos = any(not self.slot_info[s]["req"].ignore_eos for s in active)
+        ring = self.step_count & 1
+        if need_eos:
+            self.h_tok_pin[ring].copy_(self.b_tokens, non_blocking=True)
+            self.tok_events[ring].record()
+            # (slot, sequence id, index of the token this step produced)
+            self.tok_pending[ring] = [(s, self.slot_info[s]["seq_id"], int(self.h_gen[s]) - 1) for s in active]
+        else:
+            self.tok_pending[ring] = None
+
+    def _check_lagged_eos(self, ring: int) -> None:
+        pend = self.tok_pending[ring]
+        if pend is None:
+            return
+        self.tok_events[ring].synchronize()
+        toks = self.h_tok_pin[ring].numpy()
+        for s, seq_id, gen_at in pend:
+            info = self.slot_info.get(s)
+            if info is None or info["seq_id"] != seq_id or info["req"].ignore_eos or info["eos_at"] is not None:
+                continue
+            if int(toks[s]) == self.eos:
+                info["eos_at"] = gen_at
+        self.tok_pending[ring] = None
+
+    def _collect_finished(self, force_eos_check: bool) -> List[FinishedSequence]:
+        out: List[FinishedSequence] = []
+        done_slots = []
+        for slot, info in list(self.slot_info.items()):
+            r: _Request = info["req"]
+            gen = int(self.h_gen[slot])
+            limit = info["forced"] if info["forced"] is not None else r.max_new_tokens
+            reason = None
+            n_out = gen
+            if info["eos_at"] is not None:
+                reason, n_out = "stop", info["eos_at"] + 1
+            elif gen >= limit:
+                reason, n_out = "length", limit
+            if reason is None:
+                continue
+            done_slots.append((slot, info, n_out, reason))
+        if not done_slots:
+            return out
+        idx = torch.tensor([d[0] for d in done_slots], dtype=torch.int64, device=self.dev)
+        width = max(d[2] for d in done_slots)
+        rows = self.history[:, :width].index_select(0, idx).cpu().numpy()
+        for j, (slot, info, n_out, reason) in enumerate(done_slots):
+            r = info["req"]
+            ids = rows[j, :n_out].astype(np.int32).copy()
+            if info["forced"] is not None:
+                ids[-1] = self.eos  # EOS forced at the drawn length
+                reason = "stop"
+            out.append(FinishedSequence(r.request_id, info["child"], ids, reason, len(r.prompt)))
+            self.sched.finish(info["seq_id"])
+            self.h_lens[slot] = 0
+            self.h_gen[slot] = 0
+            del self.slot_info[slot]
+        return out
+
+    # ------------------------------------------------------------------ stepping
+    def step(self) -> List[FinishedSequence]:
+        self._admit_pending()
+        did = False
+        if self.sched.num_waiting > 0 and self.sched.num_free_slots > 0:
+            plan = self.sched.plan_prefill()
+            if plan["group_ids"]:
+                self._prefill(plan)
+                did = True
+        if not did and self.sched.num_running > 0:
+            plan = self.sched.plan_decode()
+            if plan["preempted"]:
+                self._requeue_preempted(plan["preempted"])
+            # EOS results of the previous step are examined while this step runs
+            self._decode(plan)
+            self._check_lagged_eos((self.step_count - 1) & 1)
+        return self._collect_finished(False)
+
+    def _requeue_preempted(self, seq_ids: List[int]) -> None:
+        # A preempted sample restarts from its prompt with the same seed stream (its progress is dropped).
+        for slot, info in list(self.slot_info.items()):
+            if info["seq_id"] in seq_ids:
+                r: _Request = info["req"]
+                forced = [info["forced"]] if info["forced"] is not None else None
+                self.pending.append(_Request(r.request_id, r.prompt, 1, r.max_new_tokens, r.temperature, r.seed, forced,
+                                             r.ignore_eos, child_map=[info["child"]]))
+                self.h_lens[slot] = 0
+                self.h_gen[slot] = 0
+                del self.slot_info[slot]
+
+    def run_until_done(self) -> List[FinishedSequence]:
+        out: List[FinishedSequence] = []
+        while self.has_work():
+            out.extend(self.step())
+        # drain the last lagged EOS check
+        for ring in (0, 1):
+            self._check_lagged_eos(ring)
+        out.extend(self._collect_finished(True))
+        return out
+
+    def check_status(self) -> None:
+        self.dec.check_status()
+
+    def update_weights_done(self) -> None:
+        """Called after new weights were written into ``params`` in place; captured graphs stay valid
+        because they reference the same buffers."""
+        return
+
+
+# =====================================================================================================
+class OracleEngine:
+    """Same interface, plain PyTorch, full recompute per step. For tiny models on CPU and as a test oracle."""
+
+    def __init__(self, cfg: ModelConfig, layout: ParamLayout, params: torch.Tensor, *, max_seqs: int = 64,
+                 max_model_len: Optional[int] = None, eos_token_id: Optional[int] = None, **_: Any):
+        self.cfg, self.layout, self.params = cfg, layout, params
+        self.dec = OracleDecoder(cfg, layout, params)
+        self.max_model_len = int(max_model_len or cfg.max_position_embeddings)
+        self.eos = cfg.eos_token_id if eos_token_id is None else int(eos_token_id)
+        self.pending: List[_Request] = []
+        self.max_seqs = max_seqs
+        self.tokens_generated = 0
+        self.launches = 0
+
+    def add_request(self, request_id: Any, prompt_ids: Sequence[int], n: int = 1, max_new_tokens: int = 128,
+                    temperature: float = 1.0, seed: int = 0, forced_new_tokens: Optional[Sequence[int]] = None,
+                    ignore_eos: bool = False) -> None:
+        prompt = np.ascontiguousarray(np.asarray(prompt_ids, dtype=np.int32))
+        room = self.max_model_len - len(prompt) - 1
+        max_new = max(1, min(int(max_new_tokens), room))
+        forced = [max(1, min(int(f), max_new)) for f in forced_new_tokens] if forced_new_tokens is not None else None
+        self.pending.append(_Request(request_id, prompt, int(n), max_new, float(temperature), int(seed), forced,
+                                     bool(ignore_eos or forced is not None)))
+
+    def has_work(self) -> bool:
+        return bool(self.pending)
+
+    @torch.no_grad()
+    def _generate_group(self, r: _Request) -> List[FinishedSequence]:
+        dev = self.params.device
+        seqs = [list(map(int, r.prompt)) for _ in range(r.n)]
+        done: List[Optional[str]] = [None] * r.n
+        gens = [torch.Generator(device="cpu").manual_seed(_mix_seed(r.seed, c) & 0x7FFFFFFF) for c in range(r.n)]
+        wl = self.layout.view(self.params, self.layout.lm_head_name())
+        for _ in range(r.max_new_tokens):
+            live = [c for c in range(r.n) if done[c] is None]
+            if not live:
+                break
+            ids = torch.tensor(sum((seqs[c] for c in live), []), dtype=torch.int32, device=dev)
+            pos = torch.tensor(sum((list(range(len(seqs[c]))) for c in live), []), dtype=torch.int32, device=dev)
+            cu = [0]
+            for c in live:
+                cu.append(cu[-1] + len(seqs[c]))
+            hn = self.dec.hidden(ids, pos, cu)
+            last = torch.tensor([x - 1 for x in cu[1:]], dtype=torch.long, device=dev)
+            z = hn[last].float() @ wl.float().t()
+            for j, c in enumerate(live):
+                if r.temperature <= 0:
+                    tok = int(z[j].argmax())
+                else:
+                    p = torch.softmax(z[j] / r.temperature, -1).cpu()
+                    tok = int(torch.multinomial(p, 1, generator=gens[c]))
+                seqs[c].append(tok)
+                self.tokens_generated += 1
+                n_new = len(seqs[c]) - len(r.prompt)
+                limit = r.forced_new_tokens[c] if r.forced_new_tokens else r.max_new_tokens
+                if not r.ignore_eos and tok == self.eos:
+                    done[c] = "stop"
+                elif n_new >= limit:
+                    done[c] = "length"
+        out = []
+        for c in range(r.n):
+            ids = np.asarray(seqs[c][len(r.prompt):], dtype=np.int32)
+            reason = done[c] or "length"
+            if r.forced_new_tokens:
+                ids[-1] = self.eos
+                reason = "stop"
+            out.append(FinishedSequence(r.request_id, c, ids, reason, len(r.prompt)))
+        return out
+
+    def step(self) -> List[FinishedSequence]:
+        if not self.pending:
+            return []
+        return self._generate_group(self.pending.pop(0))
+
+    def run_until_done(self) -> List[FinishedSequence]:
+        out: List[FinishedSequence] = []
+        while self.has_work():
+            out.extend(self.step())
+        return out
+
+    def check_status(self) -> None:
+        return
+
+    def update_weights_done(self) -> None:
+        return

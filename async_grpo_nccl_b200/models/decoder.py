@@ -132,9 +132,9 @@ class NativeDecoder:
     def w(self, name: str) -> torch.Tensor:
         return self.layout.view(self.params, name)
 
-    def rope_tables(self, need: int):
+    def rope_tables(self, need: int = 1):
         if self._rope is None or self._rope[0].shape[0] < need:
-            n = max(need, min(self.cfg.max_position_embeddings, 8192))
+            n = max(need, min(self.cfg.max_position_embeddings, 131072))
             cos_t, sin_t = R.rope_tables(self.cfg.head_dim, n, self.cfg.rope_theta, "cpu")
             self._rope = (cos_t.to(self.dev), sin_t.to(self.dev))
         return self._rope
@@ -154,7 +154,8 @@ class NativeDecoder:
         return torch.empty(shape, dtype=dtype, device=self.dev)
 
     # ---- layer forward ----
-    def _layer_fwd(self, i: int, x: torch.Tensor, batch: PackedBatch, cos_t, sin_t, save: Optional[dict]):
+    def _layer_fwd(self, i: int, x: torch.Tensor, batch: PackedBatch, cos_t, sin_t, save: Optional[dict],
+                   kv_write: Optional[tuple] = None):
         cfg, C = self.cfg, self.C
         T = x.shape[0]
         p = f"layers.{i}."
@@ -164,6 +165,10 @@ class NativeDecoder:
         qkv = self._new(T, cfg.qkv_dim)
         self._gemm(h1, self.w(p + "wqkv"), qkv, bias=self.w(p + "bqkv") if cfg.attention_bias else None)
         C.rope_inplace(qkv, batch.pos, cos_t, sin_t, cfg.num_attention_heads + cfg.num_key_value_heads, cfg.head_dim, False)
+        if kv_write is not None:  # rollout prefill: K/V of every prompt token go to their cache slots
+            k_cache, v_cache, slots = kv_write
+            C.kv_cache_write(qkv, slots, k_cache, v_cache, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim)
+            self.launches += 1
         attn = self._new(T, cfg.q_dim)
         lse = self._new(cfg.num_attention_heads, T, dtype=torch.float32)
         C.attn_varlen_fwd(qkv, attn, lse, batch.tiles, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
@@ -226,7 +231,7 @@ class NativeDecoder:
         """Returns (normed final hidden, pre-norm hidden, final rstd)."""
         cfg, C = self.cfg, self.C
         T = batch.T
-        cos_t, sin_t = self.rope_tables(cfg.max_position_embeddings if cfg.max_position_embeddings <= 8192 else 8192)
+        cos_t, sin_t = self.rope_tables()
         x = self._new(T, cfg.hidden_size)
         C.embedding_fwd(batch.ids, self.w("embed"), x)
         for i in range(cfg.num_hidden_layers):
@@ -270,7 +275,7 @@ class NativeDecoder:
         stats[loss_sum] / max(1, stats[count]) * loss_scale; nothing here synchronises with the host."""
         cfg, C = self.cfg, self.C
         T = batch.T
-        cos_t, sin_t = self.rope_tables(8192)
+        cos_t, sin_t = self.rope_tables()
         saves: List[dict] = []
         hn, x_last, rstd_f = self.hidden(batch, saves)
         wl_name = self.layout.lm_head_name()
