@@ -1,0 +1,126 @@
+"""Old-policy logprob role with dynamic token-budget batching.
+
+Behaviour of the reference's ``LogProbFSDPWorker`` + ``LogProbGPUWorker`` (logprob_worker.py:136-216,
+gpu_process_worker.py:1663-1709): requests queue up; a centralizer takes one request and keeps adding
+while the packed token count stays below ``max_tokens_per_gpu``, waiting up to 10 ms for each further
+request and carrying over the one that did not fit; the batch is packed 1 x T, the eval-mode forward
+returns per-token logprob and entropy on the logit-position grid, which are attached to each sample as
+``sample_logprobs`` / ``sample_entropies``. Results are matched to requests by position, not by the
+token tuple (the reference's keying collapses identical samples, logprob_worker.py:127-131).
+"""
+from __future__ import annotations
+
+import asyncio
+import concurrent.futures
+import time
+from typing import Any, Dict, List, Optional, Tuple
+
+import numpy as np
+import torch
+
+from ..packing import pack_for_logprob
+
+
+class LogProbWorker:
+    def __init__(self, config: Any, model_cfg: Any, decoder: Any, device: torch.device, temperature: Optional[float] = None,
+                 fill_window_s: float = 0.010, stream: Optional[torch.cuda.Stream] = None):
+        self.config, self.mcfg, self.decoder, self.device = config, model_cfg, decoder, torch.device(device)
+        self.temperature = float(config.temperature if temperature is None else temperature) or 1.0
+        self.max_tokens = int(config.max_tokens_per_gpu)
+        self.fill_window_s = fill_window_s
+        self.stream = stream
+        self._queue: Optional[asyncio.Queue] = None
+        self._task: Optional[asyncio.Task] = None
+        self._pool = concurrent.futures.ThreadPoolExecutor(max_workers=1, thread_name_prefix="logprob")
+        self._carry: Optional[Tuple[asyncio.Future, Dict[str, Any]]] = None
+        self.tokens_processed = 0
+        self.batches = 0
+        self.busy_seconds = 0.0
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    def _ensure_started(self) -> None:
+        if self._queue is None:
+            self._queue = asyncio.Queue()
+            self._task = asyncio.ensure_future(self._centralize())
+
+    async def inference(self, sample: Dict[str, Any]) -> Dict[str, Any]:
+        self._ensure_started()
+        fut: asyncio.Future = asyncio.get_running_loop().create_future()
+        await self._queue.put((fut, sample))
+        return await fut
+
+    # ---- batching loop ----
+    async def _centralize(self) -> None:
+        loop = asyncio.get_running_loop()
+        while True:
+            first = self._carry or await self._queue.get()
+            self._carry = None
+            batch = [first]
+            tokens = len(first[1]["sample_ids"])
+            while tokens < self.max_tokens:
+                try:
+                    nxt = await asyncio.wait_for(self._queue.get(), self.fill_window_s)
+                except asyncio.TimeoutError:
+                    break
+                n = len(nxt[1]["sample_ids"])
+                if tokens + n > self.max_tokens:
+                    self._carry = nxt  # goes first in the next batch
+                    break
+                batch.append(nxt)
+                tokens += n
+            samples = [s for _, s in batch]
+            try:
+                results = await loop.run_in_executor(self._pool, self._compute, samples)
+                for (fut, s), (lp, ent) in zip(batch, results):
+                    if not fut.done():
+                        out = dict(s)
+                        out["sample_logprobs"] = lp
+                        out["sample_entropies"] = ent
+                        fut.set_result(out)
+            except Exception as e:
+                for fut, _ in batch:
+                    if not fut.done():
+                        fut.set_exception(e)
+                await asyncio.sleep(1.0)
+
+    # ---- compute (worker thread) ----
+    def _compute(self, samples: List[Dict[str, Any]]) -> List[Tuple[np.ndarray, np.ndarray]]:
+        t0 = time.time()
+        ctx = torch.cuda.stream(self.stream) if self.stream is not None else _null()
+        with ctx, torch.no_grad():
+            host = pack_for_logprob(samples, pin=self.device.type == "cuda")
+            self.h2d_bytes += host.h2d_bytes()
+            batch = host.to_device(self.device)
+            logp, ent = self.decoder.logprobs(batch, self.temperature)
+            both = torch.stack([logp.float(), ent.float()]).cpu().numpy()  # one device-to-host copy per batch
+            self.d2h_bytes += both.nbytes
+        out = []
+        off = 0
+        for s in samples:
+            L = len(s["sample_ids"])
+            out.append((both[0, off:off + L].copy(), both[1, off:off + L].copy()))
+            off += L
+        self.tokens_processed += off
+        self.batches += 1
+        self.busy_seconds += time.time() - t0
+        return out
+
+    async def is_ready(self) -> bool:
+        return True
+
+    def stats(self) -> Dict[str, float]:
+        return {"tokens": float(self.tokens_processed), "batches": float(self.batches), "busy_seconds": self.busy_seconds,
+                "launches": float(getattr(self.decoder, "launches", 0))}
+
+    def run_blocking(self, fn, *args):
+        """Runs ``fn`` on the compute thread (used by the weight sync so it is ordered with inference)."""
+        return self._pool.submit(fn, *args).result()
+
+
+class _null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False

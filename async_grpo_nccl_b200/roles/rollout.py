@@ -1,0 +1,211 @@
+"""Generation role: owns one rollout engine, builds the per-sample fields, sends every sample through the
+verifier pool, and computes group-normalised advantages.
+
+It covers the reference's ``GenerationVLLMWorker`` (vllm_worker.py:128-805): ``inference(sample, n,
+temperature, max_tokens)`` -> ``(samples, metrics)``, ``batch_inference_for_evaluation``,
+``generate_with_logprobs`` and ``sync_weights``. The engine runs in its own thread; requests from many
+concurrent ``inference`` coroutines are batched continuously by the engine's scheduler.
+"""
+from __future__ import annotations
+
+import asyncio
+import hashlib
+import threading
+import time
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..ops.reference import normalize_rewards
+from ..protocol import build_sample
+
+
+def _uid_seed(uid: Any, base: int) -> int:
+    h = hashlib.sha256(repr(uid).encode()).digest()
+    return (int.from_bytes(h[:8], "little") ^ (base * 0x9E3779B97F4A7C15)) & 0x7FFFFFFFFFFFFFFF
+
+
+class GenerationWorker:
+    def __init__(self, config: Any, model_cfg: Any, engine: Any, verifier_pool: Any, tokenizer: Any = None,
+                 stream: Optional[torch.cuda.Stream] = None):
+        self.config, self.mcfg, self.engine, self.verifier = config, model_cfg, engine, verifier_pool
+        self.tokenizer = tokenizer
+        self.stream = stream
+        self._lock = threading.Lock()
+        self._incoming: List[Tuple[Any, ...]] = []
+        self._futures: Dict[Any, Tuple[asyncio.AbstractEventLoop, asyncio.Future, int, List[Any]]] = {}
+        self._wake = threading.Event()
+        self._stop = False
+        self._paused = threading.Event()
+        self._idle = threading.Event()
+        self._idle.set()
+        self._thread = threading.Thread(target=self._engine_loop, name="rollout-engine", daemon=True)
+        self._thread.start()
+        self._req_counter = 0
+        self.total_tokens = 0
+        self.busy_seconds = 0.0
+
+    # ------------------------------------------------------------------ engine thread
+    def _engine_loop(self) -> None:
+        ctx = torch.cuda.stream(self.stream) if self.stream is not None else _null()
+        with ctx:
+            while not self._stop:
+                with self._lock:
+                    new, self._incoming = self._incoming, []
+                for args in new:
+                    self.engine.add_request(*args[0], **args[1])
+                if self._paused.is_set() or not self.engine.has_work():
+                    self._idle.set()
+                    self._wake.wait(timeout=0.05)
+                    self._wake.clear()
+                    continue
+                self._idle.clear()
+                t0 = time.time()
+                try:
+                    finished = self.engine.step()
+                except Exception as e:  # fail every waiter instead of hanging them
+                    self._fail_all(e)
+                    continue
+                self.busy_seconds += time.time() - t0
+                for f in finished:
+                    self._deliver(f)
+
+    def _deliver(self, f: Any) -> None:
+        entry = self._futures.get(f.request_id)
+        if entry is None:
+            return
+        loop, fut, n, got = entry
+        got.append(f)
+        if len(got) == n:
+            del self._futures[f.request_id]
+            loop.call_soon_threadsafe(lambda: fut.done() or fut.set_result(sorted(got, key=lambda x: x.child)))
+
+    def _fail_all(self, e: Exception) -> None:
+        for rid, (loop, fut, _, _) in list(self._futures.items()):
+            loop.call_soon_threadsafe(lambda fut=fut: fut.done() or fut.set_exception(RuntimeError(f"engine failure: {e!r}")))
+        self._futures.clear()
+
+    async def _generate(self, prompt_ids: np.ndarray, n: int, max_new: int, temperature: float, seed: int,
+                        forced: Optional[Sequence[int]] = None, ignore_eos: bool = False) -> List[Any]:
+        loop = asyncio.get_running_loop()
+        fut: asyncio.Future = loop.create_future()
+        with self._lock:
+            self._req_counter += 1
+            rid = self._req_counter
+            self._futures[rid] = (loop, fut, n, [])
+            self._incoming.append(((rid, prompt_ids), dict(n=n, max_new_tokens=max_new, temperature=temperature, seed=seed,
+                                                          forced_new_tokens=forced, ignore_eos=ignore_eos)))
+        self._wake.set()
+        return await fut
+
+    # ------------------------------------------------------------------ public API
+    def get_max_tokens(self, prompt_len: int, max_tokens: Optional[int]) -> int:
+        """min(requested, max_model_len) - len(prompt) - 1 (vllm_worker.py:394-401)."""
+        cap = int(getattr(self.engine, "max_model_len", self.mcfg.max_position_embeddings))
+        req = int(max_tokens) if max_tokens else cap
+        return max(1, min(min(req, cap), cap - prompt_len - 1))
+
+    def _decode(self, ids: np.ndarray) -> str:
+        if self.tokenizer is None:
+            return ""
+        return self.tokenizer.decode(ids.tolist(), skip_special_tokens=False)
+
+    async def inference(self, sample: Dict[str, Any], n: int = 1, temperature: float = 1.0,
+                        max_tokens: Optional[int] = None) -> Tuple[List[Dict[str, Any]], Dict[str, float]]:
+        t0 = time.time()
+        prompt = np.asarray(sample["input_token_ids"], dtype=np.int32)
+        max_new = self.get_max_tokens(len(prompt), max_tokens)
+        forced = sample.get("forced_output_lens")
+        seed = _uid_seed(sample.get("__uid__", self._req_counter), int(getattr(self.config, "seed", 0)))
+        finished = await self._generate(prompt, int(n), max_new, float(temperature), seed, forced)
+        row = {k: v for k, v in sample.items() if k != "forced_output_lens"}
+        out: List[Dict[str, Any]] = []
+        eos = int(getattr(self.engine, "eos", self.mcfg.eos_token_id))
+        for f in finished:
+            s = build_sample(row, prompt, f.output_ids, eos)
+            s["sample_index"] = f.child
+            s["vocab_size"] = self.mcfg.vocab_size
+            s["sample_text"] = self._decode(s["sample_ids"])
+            out.append(s)
+        cap = self.get_max_tokens(len(prompt), max_tokens)
+        verified = await asyncio.gather(*[self.verifier.verify(s, max_gen_length=cap) for s in out])
+        rewards = [float(v.get("reward", 0.0)) for v in verified]
+        adv = normalize_rewards(rewards)
+        mx = max(rewards) if rewards else 0.0
+        for v, a in zip(verified, adv):
+            v["advantage"] = float(a)
+            v["max_reward_in_group"] = mx
+        total_tokens = int(sum(len(f.output_ids) for f in finished))
+        self.total_tokens += total_tokens
+        metrics = {
+            "generation/total_tokens_generated": float(total_tokens),
+            "generation/inference_duration_sec": time.time() - t0,
+            "generation/num_samples_generated": float(len(finished)),
+        }
+        return list(verified), metrics
+
+    async def batch_inference_for_evaluation(self, prompts: Sequence[Any], answers: Sequence[Any], max_tokens: int = 1024,
+                                             temperature: float = 0.0) -> List[Dict[str, Any]]:
+        """Greedy (by default) completions with worker-side reward (vllm_worker.py:525-668)."""
+        async def one(i: int, prompt: Any, answer: Any) -> Dict[str, Any]:
+            if isinstance(prompt, str):
+                if self.tokenizer is None:
+                    raise RuntimeError("a tokenizer is required for text prompts")
+                ids = np.asarray(self.tokenizer.encode(prompt, add_special_tokens=False), dtype=np.int32)
+                text = prompt
+            else:
+                ids = np.asarray(prompt, dtype=np.int32)
+                text = self._decode(ids)
+            fin = await self._generate(ids, 1, self.get_max_tokens(len(ids), max_tokens), float(temperature), _uid_seed(("eval", i), 0))
+            eos = int(getattr(self.engine, "eos", self.mcfg.eos_token_id))
+            s = build_sample({"input": text, "input_token_ids": ids, "answer": answer}, ids, fin[0].output_ids, eos)
+            s["sample_text"] = self._decode(s["sample_ids"])
+            s["vocab_size"] = self.mcfg.vocab_size
+            v = await self.verifier.verify(s)
+            return {"prompt": text, "completion": self._decode(fin[0].output_ids), "answer": answer,
+                    "reward": float(v.get("reward", 0.0)), "output_len": int(len(fin[0].output_ids))}
+
+        return list(await asyncio.gather(*[one(i, p, a) for i, (p, a) in enumerate(zip(prompts, answers))]))
+
+    async def generate_with_logprobs(self, prompt_ids: Sequence[int], max_tokens: int = 32, temperature: float = 1.0,
+                                     seed: int = 0) -> Dict[str, Any]:
+        """Probe: sampled token ids so that trainer / logprob-worker values can be compared with the engine's
+        (vllm_worker.py:286-392)."""
+        ids = np.asarray(prompt_ids, dtype=np.int32)
+        fin = await self._generate(ids, 1, self.get_max_tokens(len(ids), max_tokens), float(temperature), int(seed))
+        return {"output_token_ids": fin[0].output_ids, "finish_reason": fin[0].finish_reason}
+
+    # ------------------------------------------------------------------ weight sync (receiver side)
+    async def pause_for_sync(self) -> bool:
+        """Stops stepping after the current step; returns once the engine thread is idle."""
+        self._paused.set()
+        self._wake.set()
+        while not self._idle.is_set():
+            await asyncio.sleep(0.001)
+        return True
+
+    async def resume_after_sync(self) -> bool:
+        self.engine.update_weights_done()
+        self._paused.clear()
+        self._wake.set()
+        return True
+
+    async def is_ready(self) -> bool:
+        return True
+
+    def stats(self) -> Dict[str, float]:
+        return {"total_tokens": float(self.total_tokens), "busy_seconds": self.busy_seconds,
+                "launches": float(getattr(self.engine, "launches", 0))}
+
+    def shutdown(self) -> None:
+        self._stop = True
+        self._wake.set()
+
+
+class _null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False

@@ -1,0 +1,450 @@
+"""Trainer rank: sharded optimizer state, microbatch forward/backward, optimizer step, checkpoints.
+
+Behaviour follows the reference's ``TrainerGPUWorker`` (gpu_process_worker.py:801-1640):
+``compute_gradients`` per MICROBATCH with the loss scaled so that the update is the mean over all
+samples of the minibatch on all ranks, ``apply_gradients`` per GRADIENT_STEP (global-norm clip 1.0,
+AdamW, LR schedule, zero grads), token-weighted metric aggregation per BATCH_DONE, HF-format
+checkpoints plus optimizer / scheduler state, and being the source of the weight sync.
+
+B200-first differences:
+* parameters live in one flat buffer (see models/layout.py); fp32 master weights and Adam moments are
+  sharded over the trainer ranks, the bf16 compute copy is resident on every rank when it fits in HBM
+  (ZeRO-2 style: 180 GB per GPU make re-gathering every layer twice per microbatch unnecessary for
+  models up to ~30B parameters);
+* gradients accumulate locally in fp32 over all microbatches of an optimizer step and are reduced ONCE
+  per step (the reference's FSDP2 reduces every microbatch, gpu_process_worker.py:1041);
+* the diagnostics are sums produced by the loss kernel and read with one device-to-host copy per
+  optimizer step instead of ~15 ``.item()`` syncs per microbatch (grpo_loss.py:410-483);
+* the reference's per-step summaries are zeroed before they are aggregated
+  (gpu_process_worker.py:1412-1415); here they are aggregated first.
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+import time
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..config import GRPOConfig
+from ..models.config import ModelConfig
+from ..models.decoder import GradSink, LossConfig, NativeDecoder, OracleDecoder
+from ..models.layout import ParamLayout
+from ..ops import reference as R
+from ..packing import PackedBatch, make_dummy_batch, pack_samples
+
+
+def lr_factor(step: int, warmup: int, total: int, kind: str) -> float:
+    """Linear warm-up, then constant or cosine decay (gpu_process_worker.py:734-741)."""
+    if warmup > 0 and step < warmup:
+        return float(step + 1) / float(warmup)
+    if kind == "cosine" and total > warmup:
+        prog = min(1.0, float(step - warmup) / float(max(1, total - warmup)))
+        return 0.5 * (1.0 + math.cos(math.pi * prog))
+    return 1.0
+
+
+class TrainerCore:
+    def __init__(self, cfg: GRPOConfig, mcfg: ModelConfig, device: torch.device, rank: int = 0, world: int = 1,
+                 group: Any = None, init_flat_fp32: Optional[torch.Tensor] = None, seed: int = 0,
+                 symm: Any = None):
+        self.cfg, self.mcfg = cfg, mcfg
+        self.device = torch.device(device)
+        self.rank, self.world, self.group = rank, world, group
+        self.native = self.device.type == "cuda"
+        self.layout = ParamLayout(mcfg, shard_world=world)
+        self.compute_dtype = torch.bfloat16 if self.native else torch.float32
+        L = self.layout
+        if init_flat_fp32 is None:
+            init_flat_fp32 = torch.empty(L.total, dtype=torch.float32)
+            L.init_random_(init_flat_fp32, seed)
+        assert init_flat_fp32.numel() == L.total
+        # resident compute copy (bf16 on GPU). `symm` may hand in a buffer that peers can write (weight push).
+        if symm is not None and getattr(symm, "param_buffer", None) is not None:
+            self.params = symm.param_buffer
+            self.params.copy_(init_flat_fp32.to(self.compute_dtype))
+        else:
+            self.params = init_flat_fp32.to(self.device, dtype=self.compute_dtype)
+        self.symm = symm
+        # sharded fp32 master + moments
+        self.shard_map = L.local_to_global_ranges(rank)
+        n = L.shard_numel()
+        self.master = torch.empty(n, dtype=torch.float32, device=self.device)
+        for lo, gs, ln in self.shard_map:
+            self.master[lo:lo + ln].copy_(init_flat_fp32[gs:gs + ln])
+        self.exp_avg = torch.zeros_like(self.master)
+        self.exp_avg_sq = torch.zeros_like(self.master)
+        self.grad_shard = torch.zeros_like(self.master) if world > 1 else None
+        self.sink = GradSink(L, self.device)
+        recompute = cfg.activation_recompute == "full"
+        if self.native:
+            self.decoder = NativeDecoder(mcfg, L, self.params, recompute=recompute)
+            self.norm_sq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        else:
+            self._oracle_params = self.params.clone().requires_grad_(True)
+            self.decoder = OracleDecoder(mcfg, L, self._oracle_params)
+            self.norm_sq = torch.zeros(1, dtype=torch.float32)
+        self.loss_cfg = LossConfig(cfg.clip_low, cfg.clip_high, cfg.clip_ratio_c, cfg.kl_beta, cfg.temperature,
+                                   cfg.entropy_coeff, cfg.apply_entropy_bonus)
+        self.opt_step = 0
+        self.base_lr = cfg.learning_rate
+        n_stats = len(R.LOSS_STAT_NAMES)
+        self._stats_step = torch.zeros(n_stats, dtype=torch.float32, device=self.device)
+        self._stats_mb: List[Tuple[torch.Tensor, Dict[str, float]]] = []
+        self._mb_step_buffer: List[Dict[str, float]] = []
+        self._reset_batch_accumulators()
+        self.last_grad_norm = 0.0
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    # ------------------------------------------------------------------ metrics plumbing
+    def _reset_batch_accumulators(self) -> None:
+        self._mb_summaries: List[Dict[str, float]] = []
+        self._step_summaries: List[Dict[str, float]] = []
+        self._mb_pending: List[Dict[str, Any]] = []
+        self._grad_norms: List[float] = []
+        self._grad_steps = 0
+        self._clipped_steps = 0
+
+    def current_lr(self) -> float:
+        return self.base_lr * lr_factor(self.opt_step, self.cfg.lr_warmup_steps, self.cfg.total_steps(), self.cfg.lr_scheduler)
+
+    # ------------------------------------------------------------------ MICROBATCH
+    def compute_gradients(self, samples: Sequence[Dict[str, Any]]) -> None:
+        """Forward + backward of one microbatch; gradients accumulate locally. No host sync on the native path."""
+        real = [s for s in samples if not s.get("dummy", False)]
+        n_real = len(real)
+        if n_real == 0 and self.world == 1:
+            return  # single rank, nothing to do (gpu_process_worker.py:975-985)
+        batch_host = pack_samples(samples if n_real else [{"dummy": True}], pin=self.native)
+        self.h2d_bytes += batch_host.h2d_bytes()
+        batch = batch_host.to_device(self.device)
+        # scale so that the sum over microbatches and ranks is (1/N) * sum_mb n_mb * tokenmean_mb
+        loss_scale = float(n_real) / float(self.cfg.train_minibatch_sample_size)
+        if self.native:
+            stats = self.decoder.forward_backward(batch, self.loss_cfg, loss_scale, self.sink)
+        else:
+            loss, stats = self.decoder.loss(batch, self.loss_cfg, loss_scale)
+            if n_real > 0 and batch.total_out > 0:
+                loss.backward()
+                self.sink.flat.add_(self._oracle_params.grad.float())
+                self._oracle_params.grad = None
+        rewards = [float(s.get("reward", 0.0)) for s in real]
+        self._mb_pending.append({"stats": stats, "num_samples": n_real, "total_reward": float(sum(rewards)),
+                                 "index": len(self._mb_pending) + len(self._mb_summaries)})
+
+    def _drain_pending(self) -> None:
+        """One device-to-host copy for all microbatches since the last drain."""
+        if not self._mb_pending:
+            return
+        stacked = torch.stack([p["stats"].float() for p in self._mb_pending]).cpu().numpy()
+        self.d2h_bytes += stacked.nbytes
+        for row, p in zip(stacked, self._mb_pending):
+            n_tok = float(row[0])
+            token_mean = float(row[1]) / max(1.0, n_tok)
+            m = R.stats_to_metrics(row, token_mean, p["num_samples"], self.cfg.entropy_coeff)
+            summ = {
+                "tokens": n_tok, "loss_sum": token_mean * n_tok, "kl_mean": m["kl_div"], "entropy_mean": m["entropy"],
+                "minibatch_index": p["index"], "log_ratio_mean": m["log_ratio_mean"], "log_ratio_std": m["log_ratio_std"],
+                "clipfrac_upper": m["clipfrac_upper"], "clipfrac_lower": m["clipfrac_lower"], "adv_mean": m["adv_mean"],
+                "adv_std": m["adv_std"], "adv_pos_frac": m["adv_pos_frac"], "adv_zero_frac": m["adv_zero_frac"],
+                "old_policy_entropy": m["old_policy_entropy"], "approx_kl": m["approx_kl"], "kl_ref": m["kl_ref"],
+                "avg_reward": p["total_reward"] / p["num_samples"] if p["num_samples"] else 0.0,
+                "total_reward": p["total_reward"], "total_samples": p["num_samples"],
+            }
+            self._mb_summaries.append(summ)
+            self._mb_step_buffer.append(summ)
+        self._mb_pending = []
+
+    # ------------------------------------------------------------------ GRADIENT_STEP
+    def _reduce_gradients(self) -> torch.Tensor:
+        """Returns this rank's fp32 gradient shard (sum over ranks)."""
+        if self.world == 1:
+            return self.sink.flat
+        import torch.distributed as dist
+
+        if self.symm is not None and getattr(self.symm, "reduce_scatter", None) is not None:
+            self.symm.reduce_scatter(self.sink.flat, self.grad_shard, self.layout, self.rank)
+            return self.grad_shard
+        for u, (lo, gs, ln) in enumerate(self.shard_map):
+            s, e = self.layout.unit_ranges[u]
+            dist.reduce_scatter_tensor(self.grad_shard[lo:lo + ln], self.sink.flat[s:e], op=dist.ReduceOp.SUM, group=self.group)
+        return self.grad_shard
+
+    def _gather_params(self) -> None:
+        """Publishes the updated bf16 shard into every trainer rank's resident parameter buffer."""
+        if self.world == 1:
+            return
+        import torch.distributed as dist
+
+        if self.symm is not None and getattr(self.symm, "push_params", None) is not None:
+            self.symm.push_params(self)
+            return
+        for u, (lo, gs, ln) in enumerate(self.shard_map):
+            s, e = self.layout.unit_ranges[u]
+            dist.all_gather_into_tensor(self.params[s:e], self._shard16[lo:lo + ln], group=self.group)
+
+    def apply_gradients(self) -> Dict[str, float]:
+        """Clip by global norm, AdamW on the local shard, refresh the bf16 compute copy, zero gradients."""
+        cfg = self.cfg
+        self.opt_step += 1
+        lr = self.base_lr * lr_factor(self.opt_step - 1, cfg.lr_warmup_steps, cfg.total_steps(), cfg.lr_scheduler)
+        g = self._reduce_gradients()
+        self.norm_sq.zero_()
+        if self.native:
+            C = self.decoder.C
+            C.sumsq(g, 1.0, self.norm_sq)
+            if self.world > 1:
+                import torch.distributed as dist
+
+                dist.all_reduce(self.norm_sq, group=self.group)
+            if self.world == 1:
+                shard16 = self.params  # the master covers the whole buffer: write the compute copy in place
+            else:
+                if not hasattr(self, "_shard16"):
+                    self._shard16 = torch.empty(self.master.numel(), dtype=torch.bfloat16, device=self.device)
+                shard16 = self._shard16
+            C.adamw_step(self.master, self.exp_avg, self.exp_avg_sq, g, shard16, lr, cfg.adam_beta1, cfg.adam_beta2,
+                         cfg.adam_eps, cfg.weight_decay, self.opt_step, 1.0, self.norm_sq, cfg.max_grad_norm, True)
+            self.decoder.launches += 2
+            if self.world > 1:
+                self.sink.zero_()
+        else:
+            self.norm_sq.add_(g.pow(2).sum())
+            if self.world > 1:
+                import torch.distributed as dist
+
+                dist.all_reduce(self.norm_sq, group=self.group)
+            R.adamw_step_(self.master, self.exp_avg, self.exp_avg_sq, g, lr, cfg.adam_beta1, cfg.adam_beta2, cfg.adam_eps,
+                          cfg.weight_decay, self.opt_step, 1.0, cfg.max_grad_norm, self.norm_sq)
+            if self.world == 1:
+                self.params.copy_(self.master.to(self.compute_dtype))
+            else:
+                self._shard16 = self.master.to(self.compute_dtype)
+            self.sink.zero_()
+            if self.world > 1 and self.grad_shard is not None:
+                self.grad_shard.zero_()
+        self._gather_params()
+        if not self.native:
+            with torch.no_grad():
+                self._oracle_params.copy_(self.params)
+        # one small read per optimizer step: grad norm + the microbatch statistics
+        self._mb_step_buffer = []
+        self._drain_pending()
+        grad_norm = float(self.norm_sq.sqrt().item())
+        self.d2h_bytes += 4
+        self.last_grad_norm = grad_norm
+        self._grad_norms.append(grad_norm)
+        self._grad_steps += 1
+        if cfg.max_grad_norm > 0 and grad_norm > cfg.max_grad_norm:
+            self._clipped_steps += 1
+        step_summary = self._aggregate(self._mb_step_buffer)
+        step_summary.update(grad_norm=grad_norm, lr=lr, optimizer_step=self.opt_step)
+        self._step_summaries.append(step_summary)
+        if self.native:
+            self.decoder.check_status()
+        return step_summary
+
+    # ------------------------------------------------------------------ BATCH_DONE
+    @staticmethod
+    def _aggregate(summaries: Sequence[Dict[str, float]]) -> Dict[str, float]:
+        """Token-weighted means; mean/std pairs are merged through second moments (gpu_process_worker.py:831-900)."""
+        denom = sum(s["tokens"] for s in summaries)
+        out: Dict[str, float] = {"tokens": float(denom), "num_microbatches": float(len(summaries))}
+        if denom <= 0:
+            for k in ("loss", "kl_div", "entropy", "log_ratio_mean", "log_ratio_std", "clipfrac_upper", "clipfrac_lower",
+                      "adv_mean", "adv_std", "adv_pos_frac", "adv_zero_frac", "old_policy_entropy", "approx_kl", "kl_ref"):
+                out[k] = 0.0
+            out["total_reward"] = sum(s.get("total_reward", 0.0) for s in summaries)
+            out["total_samples"] = sum(s.get("total_samples", 0) for s in summaries)
+            out["avg_reward"] = out["total_reward"] / out["total_samples"] if out["total_samples"] else 0.0
+            return out
+
+        def wmean(key: str) -> float:
+            return sum(s.get(key, 0.0) * s["tokens"] for s in summaries) / denom
+
+        def merged_std(mean_key: str, std_key: str) -> Tuple[float, float]:
+            mean = wmean(mean_key)
+            second = sum((s.get(std_key, 0.0) ** 2 + s.get(mean_key, 0.0) ** 2) * s["tokens"] for s in summaries) / denom
+            return mean, math.sqrt(max(0.0, second - mean * mean))
+
+        out["loss"] = sum(s["loss_sum"] for s in summaries) / denom
+        out["kl_div"] = wmean("kl_mean")
+        out["entropy"] = wmean("entropy_mean")
+        out["log_ratio_mean"], out["log_ratio_std"] = merged_std("log_ratio_mean", "log_ratio_std")
+        out["adv_mean"], out["adv_std"] = merged_std("adv_mean", "adv_std")
+        for k in ("clipfrac_upper", "clipfrac_lower", "adv_pos_frac", "adv_zero_frac", "old_policy_entropy", "approx_kl", "kl_ref"):
+            out[k] = wmean(k)
+        out["total_reward"] = sum(s.get("total_reward", 0.0) for s in summaries)
+        out["total_samples"] = sum(s.get("total_samples", 0) for s in summaries)
+        out["avg_reward"] = out["total_reward"] / out["total_samples"] if out["total_samples"] else 0.0
+        return out
+
+    def finish_batch(self, batch_done_data: Optional[Dict[str, Any]], iteration: int) -> Dict[str, Any]:
+        """Completion payload for the orchestrator (keys as in gpu_process_worker.py:1521-1534)."""
+        self._drain_pending()
+        data = batch_done_data or {}
+        agg = self._aggregate(self._mb_summaries)
+        metrics = {
+            "loss": agg["loss"], "loss_per_token": agg["loss"], "kl_div": agg["kl_div"], "entropy": agg["entropy"],
+            "token_count": int(agg["tokens"]), "log_ratio_mean": agg["log_ratio_mean"], "log_ratio_std": agg["log_ratio_std"],
+            "clipfrac_upper": agg["clipfrac_upper"], "clipfrac_lower": agg["clipfrac_lower"], "adv_mean": agg["adv_mean"],
+            "adv_std": agg["adv_std"], "adv_pos_frac": agg["adv_pos_frac"], "adv_zero_frac": agg["adv_zero_frac"],
+            "old_policy_entropy": agg["old_policy_entropy"], "approx_kl": agg["approx_kl"], "kl_ref": agg["kl_ref"],
+            "grad_norm": sum(self._grad_norms) / len(self._grad_norms) if self._grad_norms else 0.0,
+            "lr": self.current_lr(),
+        }
+        batch_metrics = {"avg_reward": agg["avg_reward"], "total_reward": agg["total_reward"],
+                         "total_samples": agg["total_samples"]}
+        exp = data.get("batch_metrics", {}) or {}
+        for k in ("reward_mean", "reward_std", "reward_min", "reward_max", "group_reward_std_mean",
+                  "group_reward_std_zero_frac", "nonzero_reward_frac", "avg_completion_length"):
+            if k in exp:
+                batch_metrics[k] = exp[k]
+        payload = {
+            "gpu_rank": self.rank,
+            "metrics": metrics,
+            "batch_metrics": batch_metrics,
+            "gen_logprob_metrics": data.get("gen_logprob_metrics", {}),
+            "iteration": iteration,
+            "optimizer_steps_in_batch": self._grad_steps,
+            "grad_clip_steps_in_batch": self._clipped_steps,
+            "grad_clip_ratio_in_batch": self._clipped_steps / self._grad_steps if self._grad_steps else 0.0,
+            "exp_batch_metrics": exp,
+            "minibatch_summaries": [dict(s) for s in self._step_summaries],
+        }
+        self._reset_batch_accumulators()
+        return payload
+
+    # ------------------------------------------------------------------ weights / checkpoints
+    def full_master_fp32(self) -> Optional[torch.Tensor]:
+        """Full fp32 parameters on rank 0 (collective when world > 1), None on other ranks."""
+        if self.world == 1:
+            return self.master
+        import torch.distributed as dist
+
+        full = torch.empty(self.layout.total, dtype=torch.float32, device=self.device)
+        for u, (lo, gs, ln) in enumerate(self.shard_map):
+            s, e = self.layout.unit_ranges[u]
+            dist.all_gather_into_tensor(full[s:e], self.master[lo:lo + ln].contiguous(), group=self.group)
+        return full if self.rank == 0 else None
+
+    def weights_info(self):
+        return self.layout.weights_info()
+
+    def optimizer_state(self) -> Dict[str, Any]:
+        return {"master": self.master, "exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq}
+
+    def scheduler_state(self) -> Dict[str, Any]:
+        return {"opt_step": self.opt_step, "base_lr": self.base_lr, "lr_scheduler": self.cfg.lr_scheduler,
+                "lr_warmup_steps": self.cfg.lr_warmup_steps, "total_steps": self.cfg.total_steps()}
+
+    def load_scheduler_state(self, st: Dict[str, Any]) -> None:
+        self.opt_step = int(st.get("opt_step", 0))
+        self.base_lr = float(st.get("base_lr", self.base_lr))
+
+    def load_master_from_full(self, full_fp32: torch.Tensor) -> None:
+        for lo, gs, ln in self.shard_map:
+            self.master[lo:lo + ln].copy_(full_fp32[gs:gs + ln])
+        self.params.copy_(full_fp32.to(self.device, dtype=self.compute_dtype))
+        if not self.native:
+            with torch.no_grad():
+                self._oracle_params.copy_(self.params)
+
+
+class TrainerWorker:
+    """Message loop of one trainer rank (gpu_process_worker.py:1233-1564): pulls MICROBATCH / GRADIENT_STEP /
+    BATCH_DONE messages from the ExperienceManager and pushes the completion payload back. All device work
+    runs on one worker thread so the asyncio loop keeps serving RPCs."""
+
+    def __init__(self, core: TrainerCore, stream: Optional[torch.cuda.Stream] = None):
+        import concurrent.futures
+
+        self.core = core
+        self.stream = stream
+        self._pool = concurrent.futures.ThreadPoolExecutor(max_workers=1, thread_name_prefix="trainer")
+        self.manager: Any = None
+        self.rank_in_manager = core.rank
+        self.iteration = 0
+        self._loop_task: Any = None
+        self.running = False
+        self.busy_seconds = 0.0
+        self.last_error: Optional[str] = None
+
+    def _run(self, fn, *args):
+        t0 = time.time()
+        try:
+            if self.stream is not None:
+                with torch.cuda.stream(self.stream):
+                    return fn(*args)
+            return fn(*args)
+        finally:
+            self.busy_seconds += time.time() - t0
+
+    async def _exec(self, fn, *args):
+        import asyncio
+
+        return await asyncio.get_running_loop().run_in_executor(self._pool, self._run, fn, *args)
+
+    def set_orchestrator(self, manager: Any, rank: int) -> bool:
+        self.manager, self.rank_in_manager = manager, rank
+        return True
+
+    async def start_training_loop(self) -> bool:
+        import asyncio
+
+        if self._loop_task is None or self._loop_task.done():
+            self.running = True
+            self._loop_task = asyncio.ensure_future(self._training_loop())
+        return True
+
+    async def _training_loop(self) -> None:
+        from ..protocol import Message, MessageType
+
+        try:
+            while self.running:
+                msg = await self.manager.get_batch(self.rank_in_manager)
+                if isinstance(msg, dict):
+                    msg = Message.from_wire(msg)
+                if msg.type == MessageType.MICROBATCH:
+                    await self._exec(self.core.compute_gradients, msg.data)
+                elif msg.type == MessageType.GRADIENT_STEP:
+                    await self._exec(self.core.apply_gradients)
+                elif msg.type == MessageType.BATCH_DONE:
+                    self.iteration += 1
+                    payload = await self._exec(self.core.finish_batch, msg.data, self.iteration)
+                    await self.manager.put_completion(self.rank_in_manager, payload)
+                elif msg.type == MessageType.SHUTDOWN:
+                    self.running = False
+        except Exception as e:  # surface the failure: the orchestrator's completion wait will see it
+            import traceback
+
+            self.last_error = f"{e!r}\n{traceback.format_exc()}"
+            self.running = False
+            try:
+                await self.manager.put_completion(self.rank_in_manager, {"gpu_rank": self.core.rank, "error": self.last_error})
+            except Exception:
+                pass
+
+    async def stop(self) -> bool:
+        self.running = False
+        if self._loop_task is not None:
+            self._loop_task.cancel()
+        return True
+
+    async def is_ready(self) -> bool:
+        return self.last_error is None
+
+    async def get_trainer_weights_info(self):
+        return self.core.weights_info()
+
+    def stats(self) -> Dict[str, float]:
+        return {"busy_seconds": self.busy_seconds, "opt_step": float(self.core.opt_step),
+                "launches": float(getattr(self.core.decoder, "launches", 0)), "h2d_bytes": float(self.core.h2d_bytes),
+                "d2h_bytes": float(self.core.d2h_bytes)}
+
+    def run_blocking(self, fn, *args):
+        return self._pool.submit(self._run, fn, *args).result()

@@ -1,0 +1,41 @@
+"""End-to-end GRPO on CPU with the PyTorch oracle ops: 1 trainer, 1 logprob and 1 generation role on the tiny
+Qwen2-style decoder, synthetic token-match reward, weight sync after every macro-batch."""
+import numpy as np
+import torch
+
+from async_grpo_nccl_b200.config import make_config
+from async_grpo_nccl_b200.data import synthetic_prompt_rows
+from async_grpo_nccl_b200.launch import build_inprocess_runtime
+from async_grpo_nccl_b200.orchestrator import Orchestrator
+
+
+def _cfg(tmp_path, **kw):
+    base = dict(model_name_or_path="tiny", batch_size=4, samples_per_question=4, num_epochs=1, train_minibatch_sample_size=8,
+                max_generation_tokens=12, max_tokens_per_gpu=256, reward_fns=["token_match"], global_num_verifiers=0,
+                num_training_gpu_workers=1, learning_rate=1e-3, kl_beta=0.001, clip_low=0.2, clip_high=0.2,
+                output_dir=str(tmp_path), min_samples_per_checkpoint=10 ** 9, eval_at_start=False)
+    base.update(kw)
+    return make_config(base)
+
+
+def test_cpu_end_to_end_two_macro_batches(tmp_path):
+    cfg = _cfg(tmp_path)
+    rows = synthetic_prompt_rows(8, 1024, 16, 32, seed=0)
+    rt = build_inprocess_runtime(cfg, device="cpu")
+    orch = Orchestrator(cfg, runtime=rt, dataset=rows)
+    out = orch.run()
+    assert out["global_step"] == 2
+    assert out["total_samples_seen"] == 2 * 4 * 4
+    rec = out["steps"][-1]
+    # 16 samples per macro-batch, minibatch 8 -> two optimizer steps per macro-batch
+    assert rec["training/optimizer_steps_in_batch"] == 2
+    assert rec["training/batch_total_samples"] == 16
+    assert rec["generation/total_tokens_generated"] > 0
+    assert np.isfinite(rec["training/avg_loss"]) and np.isfinite(rec["training/grad_norm"])
+    assert rec["training/grad_norm"] >= 0
+    # weights were pushed: trainer, logprob and rollout copies are identical after the last sync
+    core = rt.trainer.core
+    assert torch.equal(core.params, rt.logprob_params) and torch.equal(core.params, rt.rollout_params)
+    assert core.opt_step == 4
+    # metrics JSONL was written
+    assert (tmp_path / "training_metrics.jsonl").exists()
