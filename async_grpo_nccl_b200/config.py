@@ -90,6 +90,9 @@ class GRPOConfig:
     system_metrics_interval_sec: float = 10.0
     # ---- new: engine behaviour ----
     weight_sync_every: int = 1  # macro-batches between trainer -> rollout/logprob pushes
+    # Feed finished samples to the microbatch planner right away instead of waiting for a whole minibatch: the
+    # same samples end up in the same optimizer step, but forward/backward overlaps the rest of the generation.
+    eager_microbatch_dispatch: bool = False
     kernel_checks: bool = False  # kernels validate indices and report through a status word
     activation_recompute: str = "auto"  # "none" | "full" | "auto" (by memory estimate)
     fsdp_reshard_after_forward: Optional[bool] = None  # None: decide from model size vs HBM

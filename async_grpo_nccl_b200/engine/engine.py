@@ -142,6 +142,8 @@ class RolloutEngine:
         self.temperature: Optional[float] = None
         self.tokens_generated = 0
         self.launches = 0
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
 
     # ------------------------------------------------------------------ requests
     def add_request(self, request_id: Any, prompt_ids: Sequence[int], n: int = 1, max_new_tokens: int = 128,
@@ -186,6 +188,7 @@ class RolloutEngine:
             return
         u = torch.tensor([plan["upd_slot"], plan["upd_index"], plan["upd_block"]], dtype=torch.int64).pin_memory()
         ud = u.to(self.dev, non_blocking=True)
+        self.h2d_bytes += u.numel() * 8
         self.block_tables.index_put_((ud[0], ud[1]), ud[2].to(torch.int32))
 
     def _sample(self, hidden: torch.Tensor, rows: int, seeds: torch.Tensor, tokens: torch.Tensor, temperature: float) -> None:
@@ -198,8 +201,10 @@ class RolloutEngine:
         gids = plan["group_ids"]
         reqs = [self.requests[g] for g in gids]
         samples = [{"sample_ids": r.prompt, "input_len": len(r.prompt), "output_len": 0, "advantage": 0.0} for r in reqs]
-        batch = pack_samples(samples, pin=True).to_device(self.dev)
+        host_batch = pack_samples(samples, pin=True)
+        batch = host_batch.to_device(self.dev)
         slots = torch.tensor(plan["slot_mapping"], dtype=torch.int32).pin_memory().to(self.dev, non_blocking=True)
+        self.h2d_bytes += host_batch.h2d_bytes() + slots.numel() * 4 + 16 * len(plan["seq_slots"])
         self._apply_table_updates(plan)
         cos_t, sin_t = dec.rope_tables(1)
         T = batch.T
@@ -303,6 +308,7 @@ class RolloutEngine:
             self.h_lens_events[ri].synchronize()
         self.h_lens_ring[ri].copy_(torch.from_numpy(self.h_lens))
         self.seq_lens.copy_(self.h_lens_ring[ri], non_blocking=True)
+        self.h2d_bytes += self.max_seqs * 4
         ev = torch.cuda.Event()
         ev.record()
         self.h_lens_events[ri] = ev
@@ -341,6 +347,7 @@ class RolloutEngine:
         ring = self.step_count & 1
         if need_eos:
             self.h_tok_pin[ring].copy_(self.b_tokens, non_blocking=True)
+            self.d2h_bytes += self.max_seqs * 4
             self.tok_events[ring].record()
             # (slot, sequence id, index of the token this step produced)
             self.tok_pending[ring] = [(s, self.slot_info[s]["seq_id"], int(self.h_gen[s]) - 1) for s in active]
@@ -382,6 +389,7 @@ class RolloutEngine:
         idx = torch.tensor([d[0] for d in done_slots], dtype=torch.int64, device=self.dev)
         width = max(d[2] for d in done_slots)
         rows = self.history[:, :width].index_select(0, idx).cpu().numpy()
+        self.d2h_bytes += rows.nbytes
         for j, (slot, info, n_out, reason) in enumerate(done_slots):
             r = info["req"]
             ids = rows[j, :n_out].astype(np.int32).copy()

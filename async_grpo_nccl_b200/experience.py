@@ -266,7 +266,7 @@ class ExperienceManager:
                 continue
             self._account(samples, gen_metrics, timing)
             self.ready.extend(samples)
-            if len(self.ready) >= self.minibatch_size:
+            if len(self.ready) >= self.minibatch_size or getattr(self.config, "eager_microbatch_dispatch", False):
                 await self._flush_ready()
         if self.ready:
             await self._flush_ready()

@@ -46,11 +46,15 @@ def load_tokenizer(config: GRPOConfig) -> Any:
     return None
 
 
-def initial_weights(config: GRPOConfig, mcfg: ModelConfig, layout: ParamLayout) -> torch.Tensor:
+def initial_weights(config: GRPOConfig, mcfg: ModelConfig, layout: ParamLayout, device: Any = None) -> torch.Tensor:
     """Flat fp32 parameters: from an HF checkpoint directory when there is one, else seeded random init."""
     path = config.model_name_or_path
     if path and os.path.isdir(path) and any(f.endswith(".safetensors") for f in os.listdir(path)):
         return ckpt.load_hf_model(path, layout)
+    if device is not None and torch.device(device).type == "cuda" and layout.total > (1 << 26):
+        flat = torch.empty(layout.total, dtype=torch.float32, device=device)
+        layout.init_random_device_(flat, config.seed)
+        return flat
     flat = torch.empty(layout.total, dtype=torch.float32)
     layout.init_random_(flat, config.seed)
     return flat
@@ -85,7 +89,7 @@ class InProcessRuntime:
         self.mcfg = resolve_model_config(cfg.model_name_or_path, cfg.model_config)
         mcfg = self.mcfg
         probe_layout = ParamLayout(mcfg, 1)
-        flat32 = initial_weights(cfg, mcfg, probe_layout)
+        flat32 = initial_weights(cfg, mcfg, probe_layout, self.device)
         if self.native:
             torch.cuda.set_device(self.device)
             total = torch.cuda.get_device_properties(self.device).total_memory
@@ -188,6 +192,37 @@ class InProcessRuntime:
             ckpt.save_optimizer_shard(path, 0, 1, core.layout, core.optimizer_state(), core.scheduler_state())
 
         await asyncio.get_running_loop().run_in_executor(None, self.trainer.run_blocking, _save)
+
+    # ---- measurement hooks used by bench.py ----
+    async def barrier_and_sync(self) -> None:
+        if self.native:
+            torch.cuda.synchronize(self.device)
+
+    async def record_event(self, name: str) -> None:
+        if not hasattr(self, "_events"):
+            self._events: Dict[str, Any] = {}
+            self._walls: Dict[str, float] = {}
+        self._walls[name] = time.time()
+        if self.native:
+            torch.cuda.synchronize(self.device)  # roles run on their own streams: make the default stream see them all
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self._events[name] = ev
+
+    async def elapsed_ms(self, a: str, b: str) -> float:
+        if self.native:
+            torch.cuda.synchronize(self.device)
+            return float(self._events[a].elapsed_time(self._events[b]))
+        return (self._walls[b] - self._walls[a]) * 1000.0
+
+    async def collect_stats(self) -> Dict[str, float]:
+        core = self.trainer.core
+        eng = self.engine
+        return {
+            "launches": float(getattr(core.decoder, "launches", 0) + getattr(self.logprob.decoder, "launches", 0) + getattr(eng, "launches", 0)),
+            "h2d_bytes": float(core.h2d_bytes + self.logprob.h2d_bytes + getattr(eng, "h2d_bytes", 0)),
+            "d2h_bytes": float(core.d2h_bytes + self.logprob.d2h_bytes + getattr(eng, "d2h_bytes", 0)),
+        }
 
     async def shutdown(self) -> None:
         if self.trainer is not None:

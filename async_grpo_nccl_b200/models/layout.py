@@ -126,6 +126,22 @@ class ParamLayout:
                     blk = torch.randn((r1 - r0,) + tuple(seg.shape[1:]), generator=gen, dtype=torch.float32) * std
                     dst[r0:r1].copy_(blk)
 
+    def init_random_device_(self, flat: torch.Tensor, seed: int = 0) -> None:
+        """Same distribution as ``init_random_`` generated on ``flat``'s device (fast for multi-billion-parameter
+        models). Ranks that pass the same seed on the same device type get identical values."""
+        gen = torch.Generator(device=flat.device).manual_seed(seed)
+        flat.zero_()
+        std = self.cfg.initializer_range
+        for name, seg in self.segments.items():
+            dst = flat[seg.offset: seg.offset + seg.numel]
+            leaf = name.split(".")[-1]
+            if leaf in ("ln1", "ln2", "final_norm"):
+                dst.fill_(1.0)
+            elif leaf == "bqkv":
+                dst.zero_()
+            else:
+                dst.normal_(0.0, std, generator=gen)
+
     # ---- HF checkpoint boundary ----
     def hf_items(self, flat: torch.Tensor) -> Iterator[Tuple[str, torch.Tensor]]:
         """Yield (hf_name, tensor view) pairs in HF naming; fused matrices are split into row ranges."""
