@@ -334,6 +334,56 @@ void lm_sample(const Tensor& hidden, const Tensor& weight, double temperature, c
                           opt_ptr<int>(status), num_sms(), cur_stream());
 }
 
+// ---- peer-memory kernels ----
+using PtrList = std::vector<int64_t>;
+inline const long long* lptr(const PtrList& v) { return reinterpret_cast<const long long*>(v.data()); }
+
+void wait_flag_probe(const Tensor& flag, int64_t want, double budget_s, Tensor& status) {
+  TORCH_CHECK(flag.is_cuda() && flag.scalar_type() == torch::kInt64, "flag: int64 cuda");
+  check_i32(status, "status");
+  const c10::cuda::CUDAGuard guard(flag.device());
+  agrpo::launch_wait_flag_probe(flag.data_ptr(), (unsigned long long)want, budget_s, status.data_ptr<int>(), cur_stream());
+}
+void flag_barrier(const PtrList& flag_ptrs, int64_t my_rank, int64_t epoch, double budget_s, Tensor& status) {
+  check_i32(status, "status");
+  const c10::cuda::CUDAGuard guard(status.device());
+  agrpo::launch_flag_barrier(lptr(flag_ptrs), (int)flag_ptrs.size(), (int)my_rank, (unsigned long long)epoch, budget_s,
+                             status.data_ptr<int>(), cur_stream());
+}
+void weight_push(const Tensor& src, int64_t local_off, int64_t global_off, int64_t n, const PtrList& dst_ptrs) {
+  TORCH_CHECK(src.is_cuda() && src.is_contiguous() && (src.scalar_type() == torch::kFloat32 || src.scalar_type() == torch::kBFloat16), "weight_push: src");
+  TORCH_CHECK(local_off >= 0 && local_off + n <= src.numel() && local_off % 8 == 0 && global_off % 8 == 0, "weight_push: range");
+  const c10::cuda::CUDAGuard guard(src.device());
+  agrpo::launch_weight_push(src.data_ptr(), src.scalar_type() == torch::kFloat32, local_off, global_off, n, lptr(dst_ptrs),
+                            (int)dst_ptrs.size(), cur_stream());
+}
+void rs_pull_sumsq(const PtrList& grad_ptrs, int64_t my_rank, int64_t global_off, int64_t local_off, int64_t n, Tensor& out,
+                   Tensor& norm_sq) {
+  check_f32(out, "out"); check_f32(norm_sq, "norm_sq");
+  TORCH_CHECK(out.is_contiguous() && local_off + n <= out.numel() && local_off % 4 == 0 && global_off % 4 == 0 && n % 4 == 0, "rs_pull: range");
+  const c10::cuda::CUDAGuard guard(out.device());
+  agrpo::launch_rs_pull_sumsq(lptr(grad_ptrs), (int)grad_ptrs.size(), (int)my_rank, global_off, local_off, n,
+                              out.data_ptr<float>(), norm_sq.data_ptr<float>(), cur_stream());
+}
+void publish_norm(const Tensor& norm_sq, const PtrList& table_ptrs, int64_t my_rank) {
+  check_f32(norm_sq, "norm_sq");
+  const c10::cuda::CUDAGuard guard(norm_sq.device());
+  agrpo::launch_publish_norm(norm_sq.data_ptr<float>(), lptr(table_ptrs), (int)table_ptrs.size(), (int)my_rank, cur_stream());
+}
+void adamw_push(Tensor& p, Tensor& m, Tensor& v, Tensor& g, int64_t local_off, int64_t global_off, int64_t n, double lr,
+                double beta1, double beta2, double eps, double wd, int64_t step, double grad_scale, const OptTensor& partials,
+                double max_norm, const PtrList& dst_ptrs) {
+  check_f32(p, "p"); check_f32(m, "m"); check_f32(v, "v"); check_f32(g, "g");
+  TORCH_CHECK(local_off + n <= p.numel() && n % 2 == 0 && local_off % 2 == 0 && global_off % 2 == 0, "adamw_push: range");
+  int np = 0;
+  if (partials.has_value() && partials->defined()) { check_f32(*partials, "partials"); np = (int)partials->numel(); }
+  const c10::cuda::CUDAGuard guard(p.device());
+  agrpo::launch_adamw_push(p.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), g.data_ptr<float>(), local_off,
+                           global_off, n, (float)lr, (float)beta1, (float)beta2, (float)eps, (float)wd, (int)step,
+                           (float)grad_scale, opt_ptr<float>(partials), np, (float)max_norm, lptr(dst_ptrs),
+                           (int)dst_ptrs.size(), cur_stream());
+}
+
 // ---- host packer (CPU tensors) ----
 inline void check_cpu(const Tensor& t, torch::ScalarType st, const char* name) {
   TORCH_CHECK(!t.is_cuda() && t.scalar_type() == st && t.is_contiguous(), name, ": contiguous CPU tensor of the right dtype");
@@ -483,6 +533,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("pack_count_tiles", &pack_count_tiles);
   m.def("pack_microbatch", &pack_microbatch);
   m.def("normalize_rewards", &normalize_rewards_cpu);
+  m.def("wait_flag_probe", &wait_flag_probe);
+  m.def("flag_barrier", &flag_barrier);
+  m.def("weight_push", &weight_push);
+  m.def("rs_pull_sumsq", &rs_pull_sumsq);
+  m.def("publish_norm", &publish_norm);
+  m.def("adamw_push", &adamw_push);
   m.def("sumsq", &sumsq);
   m.def("adamw_step", &adamw_step, py::arg("p"), py::arg("m"), py::arg("v"), py::arg("g"), py::arg("p16") = py::none(),
         py::arg("lr") = 1e-6, py::arg("beta1") = 0.9, py::arg("beta2") = 0.999, py::arg("eps") = 1e-8,

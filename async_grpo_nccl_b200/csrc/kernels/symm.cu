@@ -1,0 +1,217 @@
+// Peer-memory kernels over NVLink 5 / NVSwitch. Every rank maps every peer's symmetric buffer, so a kernel
+// on one GPU can load from and store to the others directly; the collectives below are fused into the
+// compute that surrounds them instead of being separate NCCL calls:
+//
+//  * weight_push       trainer -> rollout / logprob / trainer peers: read the local fp32 (or bf16) shard, cast
+//                      to bf16, write it straight into every destination's flat parameter buffer. Replaces
+//                      the reference's per-tensor full_tensor() all-gather + broadcast + load_weights
+//                      (gpu_process_worker.py:1609-1637, 1716-1753, 1888-1915).
+//  * rs_pull_sumsq     gradient reduce-scatter: the owner of a shard sums that slice out of every peer's fp32
+//                      gradient buffer (peer loads) and accumulates the squared norm of the result. Replaces
+//                      FSDP2's reduce-scatter + the norm pass of clip_grad_norm_ (gpu_process_worker.py:1056-1065).
+//  * adamw_push        AdamW on the local shard with the clip coefficient taken from the summed per-rank norm
+//                      partials, the bf16 result written to every destination (all-gather + weight sync in
+//                      the same pass as the optimizer).
+//  * flag_barrier      epoch flags in the symmetric buffers, release-stores to peers, bounded acquire-spin.
+//
+// All waits are bounded (see ptx.cuh); a wait that runs out records kStatusPeerFlagTimeout / kStatusBarrierTimeout
+// in the status word and the kernel returns.
+#include <cuda_bf16.h>
+
+#include "../common/ptx.cuh"
+#include "../launchers.h"
+
+namespace agrpo {
+
+namespace {
+
+constexpr int kMaxPeers = 16;
+
+struct PeerPtrs {
+  void* p[kMaxPeers];
+  int n;
+};
+
+__global__ void wait_flag_probe_kernel(const uint64_t* flag, uint64_t want, long long budget, int* status) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    if (!wait_flag_ge(flag, want, budget)) report_status(status, kStatusPeerFlagTimeout);
+  }
+}
+
+// Each rank: flags[my_rank] of every peer <- epoch (release), then wait until all of my flags[r] >= epoch.
+__global__ void flag_barrier_kernel(PeerPtrs flags, int my_rank, uint64_t epoch, long long budget, int* status) {
+  const int r = threadIdx.x;
+  if (r < flags.n) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<uint64_t*>(flags.p[r]) + my_rank, epoch);
+  }
+  __syncthreads();
+  if (r < flags.n) {
+    const uint64_t* mine = reinterpret_cast<const uint64_t*>(flags.p[my_rank]) + r;
+    if (!wait_flag_ge(mine, epoch, budget)) report_status(status, kStatusBarrierTimeout);
+  }
+}
+
+// dst[d][global_off + i] = bf16(src[local_off + i]) for every destination d. SrcT = float or bf16.
+template <typename SrcT>
+__global__ void weight_push_kernel(const SrcT* __restrict__ src, long long local_off, long long global_off, long long n,
+                                   PeerPtrs dst) {
+  const long long n8 = n / 8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    uint4 w;
+    if constexpr (sizeof(SrcT) == 4) {
+      const float4 a = reinterpret_cast<const float4*>(src + local_off)[2 * i];
+      const float4 b = reinterpret_cast<const float4*>(src + local_off)[2 * i + 1];
+      w.x = pack_bf16x2(a.x, a.y);
+      w.y = pack_bf16x2(a.z, a.w);
+      w.z = pack_bf16x2(b.x, b.y);
+      w.w = pack_bf16x2(b.z, b.w);
+    } else {
+      w = reinterpret_cast<const uint4*>(src + local_off)[i];
+    }
+#pragma unroll 1
+    for (int d = 0; d < dst.n; ++d) reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dst.p[d]) + global_off)[i] = w;
+  }
+  // tail (n is a multiple of 8 for every layout unit, kept for safety)
+  for (long long i = n8 * 8 + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const __nv_bfloat16 v = __float2bfloat16(static_cast<float>(src[local_off + i]));
+    for (int d = 0; d < dst.n; ++d) reinterpret_cast<__nv_bfloat16*>(dst.p[d])[global_off + i] = v;
+  }
+}
+
+// out[local_off + i] = sum_r grads[r][global_off + i]; *norm_sq += sum(out^2). Peers are visited starting with
+// (my_rank + 1) so that ranks do not all read the same source at the same time.
+__global__ void rs_pull_sumsq_kernel(PeerPtrs grads, int my_rank, long long global_off, long long local_off, long long n,
+                                     float* __restrict__ out, float* __restrict__ norm_sq) {
+  float acc2 = 0.f;
+  const long long n4 = n / 4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+    for (int k = 0; k < grads.n; ++k) {
+      const int r = (my_rank + 1 + k) % grads.n;
+      const float4 v = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + global_off)[i];
+      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
+    reinterpret_cast<float4*>(out + local_off)[i] = s;
+    acc2 += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc2 += __shfl_xor_sync(0xffffffffu, acc2, o);
+  __shared__ float sm[32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) sm[warp] = acc2;
+  __syncthreads();
+  if (warp == 0) {
+    acc2 = lane < (int)(blockDim.x >> 5) ? sm[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc2 += __shfl_xor_sync(0xffffffffu, acc2, o);
+    if (lane == 0 && acc2 != 0.f) atomicAdd(norm_sq, acc2);
+  }
+}
+
+// Publishes this rank's squared-norm partial into slot my_rank of every peer's partial table.
+__global__ void publish_norm_kernel(const float* norm_sq, PeerPtrs tables, int my_rank) {
+  const int r = threadIdx.x;
+  if (r < tables.n) reinterpret_cast<float*>(tables.p[r])[my_rank] = *norm_sq;
+}
+
+// AdamW on [local_off, local_off + n) of the shard; bf16 result to dst[d][global_off + i] for every destination.
+__global__ void adamw_push_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v, float* __restrict__ g,
+                                  long long local_off, long long global_off, long long n, float lr, float beta1, float beta2,
+                                  float eps, float wd, float bc1, float bc2, float grad_scale, const float* __restrict__ partials,
+                                  int n_partials, float max_norm, PeerPtrs dst) {
+  float coef = grad_scale;
+  if (max_norm > 0.f && partials != nullptr) {
+    float tot = 0.f;
+    for (int r = 0; r < n_partials; ++r) tot += partials[r];
+    coef *= fminf(1.f, max_norm / (sqrtf(tot) + 1e-6f));
+  }
+  const float inv_bc1 = 1.f / bc1, inv_sqrt_bc2 = rsqrtf(bc2);
+  const long long n2 = n / 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n2; i += (long long)gridDim.x * blockDim.x) {
+    float r2[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const long long k = local_off + 2 * i + j;
+      const float gi = g[k] * coef;
+      float pi = p[k] * (1.f - lr * wd);
+      const float mi = beta1 * m[k] + (1.f - beta1) * gi;
+      const float vi = beta2 * v[k] + (1.f - beta2) * gi * gi;
+      pi -= lr * inv_bc1 * mi / (sqrtf(vi) * inv_sqrt_bc2 + eps);
+      p[k] = pi;
+      m[k] = mi;
+      v[k] = vi;
+      g[k] = 0.f;
+      r2[j] = pi;
+    }
+    const uint32_t w = pack_bf16x2(r2[0], r2[1]);
+#pragma unroll 1
+    for (int d = 0; d < dst.n; ++d) reinterpret_cast<uint32_t*>(reinterpret_cast<__nv_bfloat16*>(dst.p[d]) + global_off)[i] = w;
+  }
+}
+
+inline PeerPtrs make_peers(const long long* ptrs, int n) {
+  if (n > kMaxPeers) throw std::runtime_error("too many peers");
+  PeerPtrs pp;
+  pp.n = n;
+  for (int i = 0; i < kMaxPeers; ++i) pp.p[i] = i < n ? reinterpret_cast<void*>(ptrs[i]) : nullptr;
+  return pp;
+}
+
+inline int blocks_for(long long work, int cap = 148 * 8) {
+  long long b = (work + 255) / 256;
+  if (b < 1) b = 1;
+  return (int)(b > cap ? cap : b);
+}
+
+inline long long ticks_for(double seconds) { return (long long)(seconds * 1.9e9); }
+
+}  // namespace
+
+void launch_wait_flag_probe(const void* flag, unsigned long long want, double budget_s, int* status, cudaStream_t s) {
+  wait_flag_probe_kernel<<<1, 32, 0, s>>>(reinterpret_cast<const uint64_t*>(flag), want, ticks_for(budget_s), status);
+  check_cuda(cudaGetLastError(), "wait_flag_probe");
+}
+
+void launch_flag_barrier(const long long* flag_ptrs, int world, int my_rank, unsigned long long epoch, double budget_s,
+                         int* status, cudaStream_t s) {
+  flag_barrier_kernel<<<1, 32, 0, s>>>(make_peers(flag_ptrs, world), my_rank, epoch, ticks_for(budget_s), status);
+  check_cuda(cudaGetLastError(), "flag_barrier");
+}
+
+void launch_weight_push(const void* src, bool src_fp32, long long local_off, long long global_off, long long n,
+                        const long long* dst_ptrs, int n_dst, cudaStream_t s) {
+  if (n == 0 || n_dst == 0) return;
+  const PeerPtrs d = make_peers(dst_ptrs, n_dst);
+  if (src_fp32) weight_push_kernel<float><<<blocks_for(n / 8), 256, 0, s>>>((const float*)src, local_off, global_off, n, d);
+  else weight_push_kernel<__nv_bfloat16><<<blocks_for(n / 8), 256, 0, s>>>((const __nv_bfloat16*)src, local_off, global_off, n, d);
+  check_cuda(cudaGetLastError(), "weight_push");
+}
+
+void launch_rs_pull_sumsq(const long long* grad_ptrs, int world, int my_rank, long long global_off, long long local_off,
+                          long long n, float* out, float* norm_sq, cudaStream_t s) {
+  if (n == 0) return;
+  rs_pull_sumsq_kernel<<<blocks_for(n / 4), 256, 0, s>>>(make_peers(grad_ptrs, world), my_rank, global_off, local_off, n, out,
+                                                         norm_sq);
+  check_cuda(cudaGetLastError(), "rs_pull_sumsq");
+}
+
+void launch_publish_norm(const float* norm_sq, const long long* table_ptrs, int world, int my_rank, cudaStream_t s) {
+  publish_norm_kernel<<<1, 32, 0, s>>>(norm_sq, make_peers(table_ptrs, world), my_rank);
+  check_cuda(cudaGetLastError(), "publish_norm");
+}
+
+void launch_adamw_push(float* p, float* m, float* v, float* g, long long local_off, long long global_off, long long n, float lr,
+                       float beta1, float beta2, float eps, float wd, int step, float grad_scale, const float* partials,
+                       int n_partials, float max_norm, const long long* dst_ptrs, int n_dst, cudaStream_t s) {
+  if (n == 0) return;
+  const float bc1 = 1.f - powf(beta1, (float)step);
+  const float bc2 = 1.f - powf(beta2, (float)step);
+  adamw_push_kernel<<<blocks_for(n / 2, 148 * 16), 256, 0, s>>>(p, m, v, g, local_off, global_off, n, lr, beta1, beta2, eps, wd,
+                                                               bc1, bc2, grad_scale, partials, n_partials, max_norm,
+                                                               make_peers(dst_ptrs, n_dst));
+  check_cuda(cudaGetLastError(), "adamw_push");
+}
+
+}  // namespace agrpo

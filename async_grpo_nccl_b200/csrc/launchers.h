@@ -101,6 +101,20 @@ void launch_lm_sample(const void* hidden, long long ldh, const void* weight, lon
                       float temperature, const unsigned long long* seeds, float* part_f, int* part_i, int* tokens,
                       float* logprobs, int* status, int num_sms, cudaStream_t stream);
 
+// ---- peer-memory collectives fused with their compute (symm.cu) ----
+// Pointer tables are device addresses (as integers) of the peers' symmetric buffers, one per rank / destination.
+void launch_wait_flag_probe(const void* flag, unsigned long long want, double budget_s, int* status, cudaStream_t s);
+void launch_flag_barrier(const long long* flag_ptrs, int world, int my_rank, unsigned long long epoch, double budget_s,
+                         int* status, cudaStream_t s);
+void launch_weight_push(const void* src, bool src_fp32, long long local_off, long long global_off, long long n,
+                        const long long* dst_ptrs, int n_dst, cudaStream_t s);
+void launch_rs_pull_sumsq(const long long* grad_ptrs, int world, int my_rank, long long global_off, long long local_off,
+                          long long n, float* out, float* norm_sq, cudaStream_t s);
+void launch_publish_norm(const float* norm_sq, const long long* table_ptrs, int world, int my_rank, cudaStream_t s);
+void launch_adamw_push(float* p, float* m, float* v, float* g, long long local_off, long long global_off, long long n, float lr,
+                       float beta1, float beta2, float eps, float wd, int step, float grad_scale, const float* partials,
+                       int n_partials, float max_norm, const long long* dst_ptrs, int n_dst, cudaStream_t s);
+
 // ---- optimizer (optimizer.cu) ----
 // *out += scale^2 * sum(g^2)
 void launch_sumsq(const float* g, long long n, float scale, float* out, cudaStream_t s);
