@@ -98,9 +98,9 @@ class GradSink:
     """Where weight gradients go. ``unit_grads(u)`` returns an fp32 buffer covering unit ``u`` of the layout
     (kernels accumulate into it); ``unit_done(u)`` tells the owner that the unit's backward has finished."""
 
-    def __init__(self, layout: ParamLayout, device):
+    def __init__(self, layout: ParamLayout, device, flat: Optional[torch.Tensor] = None):
         self.layout = layout
-        self.flat = torch.zeros(layout.total, dtype=torch.float32, device=device)
+        self.flat = flat if flat is not None else torch.zeros(layout.total, dtype=torch.float32, device=device)
 
     def view(self, name: str) -> torch.Tensor:
         return self.layout.view(self.flat, name)

@@ -1,0 +1,206 @@
+"""Symmetric (peer-mapped) device buffers and the collectives built on them.
+
+Every rank of a group allocates the same buffers through ``torch.distributed._symmetric_memory`` (CUDA VMM
+allocations whose handles are exchanged between the processes), so each rank holds a device pointer to every
+peer's copy. The kernels in ``csrc/kernels/symm.cu`` then move data themselves:
+
+* ``TrainerComm.reduce_scatter``  owner pulls its shard out of every peer's fp32 gradient buffer (+ norm partial)
+* ``TrainerComm.adamw_and_publish`` AdamW on the shard, bf16 result stored into every trainer rank's resident
+  parameter buffer (this IS the parameter all-gather)
+* ``WeightSync.push``             trainer shard -> every rollout / logprob rank's parameter buffer
+* ``barrier``                     epoch flags with bounded waits
+
+They replace the NCCL calls of the reference: FSDP2's reduce-scatter / all-gather and ``clip_grad_norm_``'s
+all-reduce (gpu_process_worker.py:696-713, 1052-1079) and the per-tensor broadcast of the weight sync
+(gpu_process_worker.py:1609-1637). ``CollectiveFallback`` implements the same operations with
+``torch.distributed`` collectives (NCCL on GPUs, gloo on CPU ranks); it is the measured baseline and the path
+taken when symmetric memory is unavailable.
+"""
+from __future__ import annotations
+
+import logging
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+logger = logging.getLogger(__name__)
+
+WAIT_BUDGET_S = 20.0  # a barrier partner may legitimately be busy for seconds (long backward); bounded all the same
+
+
+class SymmetricBuffer:
+    def __init__(self, local: torch.Tensor, peer_ptrs: List[int], handle: Any):
+        self.local, self.peer_ptrs, self.handle = local, peer_ptrs, handle
+
+
+def symmetric_available() -> bool:
+    try:
+        import torch.distributed._symmetric_memory as sm  # noqa: F401
+
+        return torch.cuda.is_available()
+    except Exception:
+        return False
+
+
+def alloc_symmetric(numel: int, dtype: torch.dtype, device: torch.device, group: Any) -> SymmetricBuffer:
+    """Collective over ``group``: every rank gets its local tensor and the device addresses of all peers' tensors."""
+    import torch.distributed._symmetric_memory as sm
+
+    name = group.group_name if hasattr(group, "group_name") else group
+    try:
+        sm.enable_symm_mem_for_group(name)
+    except Exception:
+        pass
+    t = sm.empty(numel, dtype=dtype, device=device)
+    try:
+        hdl = sm.rendezvous(t, group=name)
+    except TypeError:
+        hdl = sm.rendezvous(t, name)
+    t.zero_()
+    return SymmetricBuffer(t, [int(p) for p in hdl.buffer_ptrs], hdl)
+
+
+class PeerGroup:
+    """Flags + barrier over one process group."""
+
+    def __init__(self, group: Any, device: torch.device, C: Any):
+        self.group, self.device, self.C = group, device, C
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.flags = alloc_symmetric(64, torch.int64, device, group)
+        self.epoch = 0
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def barrier(self) -> None:
+        """Enqueues a device-side barrier on the current stream (no host synchronisation)."""
+        self.epoch += 1
+        self.C.flag_barrier(self.flags.peer_ptrs, self.rank, self.epoch, WAIT_BUDGET_S, self.status)
+
+    def check(self) -> None:
+        code = int(self.status.item())
+        if code != 0:
+            self.status.zero_()
+            raise RuntimeError(f"peer barrier / flag wait ran out (status {code}): a rank of the group did not arrive")
+
+
+class TrainerComm:
+    """Peer-memory gradient reduce-scatter, norm exchange and AdamW + parameter publish for the trainer group."""
+
+    def __init__(self, group: Any, device: torch.device, layout: Any, C: Any):
+        self.pg = PeerGroup(group, device, C)
+        self.layout, self.C, self.device = layout, C, device
+        self.rank, self.world = self.pg.rank, self.pg.world
+        self.grads = alloc_symmetric(layout.total, torch.float32, device, group)
+        self.params = alloc_symmetric(layout.total, torch.bfloat16, device, group)
+        self.norm_tab = alloc_symmetric(64, torch.float32, device, group)
+        self.norm_local = torch.zeros(1, dtype=torch.float32, device=device)
+
+    @property
+    def param_buffer(self) -> torch.Tensor:
+        return self.params.local
+
+    @property
+    def grad_buffer(self) -> torch.Tensor:
+        return self.grads.local
+
+    def reduce_scatter(self, grad_shard: torch.Tensor) -> None:
+        """grad_shard <- sum over ranks of this rank's slice of every unit; norm partial published to all peers."""
+        C, L = self.C, self.layout
+        self.pg.barrier()  # every rank's backward has finished and its gradients are visible
+        self.norm_local.zero_()
+        for u, (lo, gs, ln) in enumerate(L.local_to_global_ranges(self.rank)):
+            C.rs_pull_sumsq(self.grads.peer_ptrs, self.rank, gs, lo, ln, grad_shard, self.norm_local)
+        C.publish_norm(self.norm_local, self.norm_tab.peer_ptrs, self.rank)
+        self.pg.barrier()  # all partials have landed; all peers are done reading my gradient buffer
+        self.grads.local.zero_()
+
+    def adamw_and_publish(self, master, exp_avg, exp_avg_sq, grad_shard, lr, beta1, beta2, eps, wd, step, max_norm,
+                          extra_dst_ptrs: Sequence[int] = ()) -> torch.Tensor:
+        """Returns the device tensor holding the per-rank squared-norm partials (sum = global squared norm)."""
+        C, L = self.C, self.layout
+        dsts = list(self.params.peer_ptrs) + list(extra_dst_ptrs)
+        partials = self.norm_tab.local[: self.world]
+        for u, (lo, gs, ln) in enumerate(L.local_to_global_ranges(self.rank)):
+            C.adamw_push(master, exp_avg, exp_avg_sq, grad_shard, lo, gs, ln, lr, beta1, beta2, eps, wd, step, 1.0, partials,
+                         max_norm, dsts)
+        self.pg.barrier()  # every rank's bf16 shard is in my parameter buffer before the next forward reads it
+        return partials
+
+
+class WeightSync:
+    """Trainer shards -> inference parameter buffers over a group that spans trainer and inference ranks."""
+
+    def __init__(self, world_group: Any, device: torch.device, layout: Any, C: Any, trainer_ranks: Sequence[int],
+                 infer_ranks: Sequence[int]):
+        self.pg = PeerGroup(world_group, device, C)
+        self.layout, self.C = layout, C
+        self.trainer_ranks, self.infer_ranks = list(trainer_ranks), list(infer_ranks)
+        self.infer_params = alloc_symmetric(layout.total, torch.bfloat16, device, world_group)
+
+    @property
+    def buffer(self) -> torch.Tensor:
+        return self.infer_params.local
+
+    def push(self, src_params: Optional[torch.Tensor], trainer_index: Optional[int]) -> None:
+        """Collective over the world group. Trainer ranks pass their resident bf16 parameters and their index in the
+        trainer group; the others pass None and only take part in the barriers."""
+        self.pg.barrier()  # inference ranks are idle (paused by the orchestrator) and trainers finished their step
+        if src_params is not None and trainer_index is not None:
+            dsts = [self.infer_params.peer_ptrs[r] for r in self.infer_ranks]
+            for u in range(len(self.layout.unit_ranges)):
+                s, e = self.layout.shard_range(u, trainer_index)
+                self.C.weight_push(src_params, s, s, e - s, dsts)
+        self.pg.barrier()  # all shards have landed everywhere
+
+
+class CollectiveFallback:
+    """The same three operations on ``torch.distributed`` collectives (NCCL / gloo)."""
+
+    def __init__(self, group: Any, layout: Any, rank: int, world: int):
+        self.group, self.layout, self.rank, self.world = group, layout, rank, world
+        self.backend = dist.get_backend(group)
+
+    def reduce_scatter(self, full_grad: torch.Tensor, grad_shard: torch.Tensor) -> None:
+        for u, (lo, gs, ln) in enumerate(self.layout.local_to_global_ranges(self.rank)):
+            s, e = self.layout.unit_ranges[u]
+            if self.backend == "gloo":
+                buf = full_grad[s:e].clone()
+                dist.all_reduce(buf, group=self.group)
+                grad_shard[lo:lo + ln].copy_(buf[gs - s: gs - s + ln])
+            else:
+                dist.reduce_scatter_tensor(grad_shard[lo:lo + ln], full_grad[s:e], op=dist.ReduceOp.SUM, group=self.group)
+
+    def all_gather_params(self, shard: torch.Tensor, full: torch.Tensor) -> None:
+        for u, (lo, gs, ln) in enumerate(self.layout.local_to_global_ranges(self.rank)):
+            s, e = self.layout.unit_ranges[u]
+            if self.backend == "gloo":
+                parts = [torch.empty(ln, dtype=shard.dtype) for _ in range(self.world)]
+                dist.all_gather(parts, shard[lo:lo + ln].contiguous(), group=self.group)
+                full[s:e].copy_(torch.cat(parts))
+            else:
+                dist.all_gather_into_tensor(full[s:e], shard[lo:lo + ln].contiguous(), group=self.group)
+
+    def all_reduce_scalar(self, t: torch.Tensor) -> None:
+        dist.all_reduce(t, group=self.group)
+
+
+def broadcast_weights(params: torch.Tensor, layout: Any, world_group: Any, trainer_global_ranks: Sequence[int],
+                      is_trainer_index: Optional[int], dst: Optional[torch.Tensor]) -> None:
+    """NCCL / gloo weight sync: every trainer rank broadcasts its shard of every unit to the whole world group.
+    Ranks that hold inference parameters copy the received ranges into ``dst``. This mirrors the reference's
+    broadcast-based sync (one broadcast per shard range instead of one per tensor)."""
+    t = len(trainer_global_ranks)
+    for u in range(len(layout.unit_ranges)):
+        s, e = layout.unit_ranges[u]
+        n = (e - s) // t
+        for ti, gr in enumerate(trainer_global_ranks):
+            a, b = s + ti * n, s + (ti + 1) * n
+            if is_trainer_index == ti:
+                buf = params[a:b]
+            else:
+                buf = dst[a:b] if dst is not None else torch.empty(b - a, dtype=params.dtype if params is not None else torch.bfloat16,
+                                                                  device=(dst.device if dst is not None else params.device))
+            dist.broadcast(buf, src=gr, group=world_group)
+            if is_trainer_index == ti and dst is not None:
+                dst[a:b].copy_(buf)

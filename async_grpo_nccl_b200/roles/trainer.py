@@ -50,7 +50,7 @@ def lr_factor(step: int, warmup: int, total: int, kind: str) -> float:
 class TrainerCore:
     def __init__(self, cfg: GRPOConfig, mcfg: ModelConfig, device: torch.device, rank: int = 0, world: int = 1,
                  group: Any = None, init_flat_fp32: Optional[torch.Tensor] = None, seed: int = 0,
-                 symm: Any = None):
+                 comm: Any = None):
         self.cfg, self.mcfg = cfg, mcfg
         self.device = torch.device(device)
         self.rank, self.world, self.group = rank, world, group
@@ -62,13 +62,19 @@ class TrainerCore:
             init_flat_fp32 = torch.empty(L.total, dtype=torch.float32)
             L.init_random_(init_flat_fp32, seed)
         assert init_flat_fp32.numel() == L.total
-        # resident compute copy (bf16 on GPU). `symm` may hand in a buffer that peers can write (weight push).
-        if symm is not None and getattr(symm, "param_buffer", None) is not None:
-            self.params = symm.param_buffer
+        # resident compute copy (bf16 on GPU). With a peer-memory communicator (parallel/symm.py::TrainerComm) the
+        # parameter and gradient buffers are symmetric allocations that the other trainer ranks read and write.
+        self.comm = comm
+        if comm is not None:
+            self.params = comm.param_buffer
             self.params.copy_(init_flat_fp32.to(self.compute_dtype))
         else:
             self.params = init_flat_fp32.to(self.device, dtype=self.compute_dtype)
-        self.symm = symm
+        self.fallback = None
+        if world > 1 and comm is None:
+            from ..parallel.symm import CollectiveFallback
+
+            self.fallback = CollectiveFallback(group, L, rank, world)
         # sharded fp32 master + moments
         self.shard_map = L.local_to_global_ranges(rank)
         n = L.shard_numel()
@@ -78,7 +84,7 @@ class TrainerCore:
         self.exp_avg = torch.zeros_like(self.master)
         self.exp_avg_sq = torch.zeros_like(self.master)
         self.grad_shard = torch.zeros_like(self.master) if world > 1 else None
-        self.sink = GradSink(L, self.device)
+        self.sink = GradSink(L, self.device, flat=comm.grad_buffer if comm is not None else None)
         recompute = cfg.activation_recompute == "full"
         if self.native:
             self.decoder = NativeDecoder(mcfg, L, self.params, recompute=recompute)
@@ -160,81 +166,67 @@ class TrainerCore:
         self._mb_pending = []
 
     # ------------------------------------------------------------------ GRADIENT_STEP
-    def _reduce_gradients(self) -> torch.Tensor:
-        """Returns this rank's fp32 gradient shard (sum over ranks)."""
-        if self.world == 1:
-            return self.sink.flat
-        import torch.distributed as dist
-
-        if self.symm is not None and getattr(self.symm, "reduce_scatter", None) is not None:
-            self.symm.reduce_scatter(self.sink.flat, self.grad_shard, self.layout, self.rank)
-            return self.grad_shard
-        for u, (lo, gs, ln) in enumerate(self.shard_map):
-            s, e = self.layout.unit_ranges[u]
-            dist.reduce_scatter_tensor(self.grad_shard[lo:lo + ln], self.sink.flat[s:e], op=dist.ReduceOp.SUM, group=self.group)
-        return self.grad_shard
-
-    def _gather_params(self) -> None:
-        """Publishes the updated bf16 shard into every trainer rank's resident parameter buffer."""
-        if self.world == 1:
-            return
-        import torch.distributed as dist
-
-        if self.symm is not None and getattr(self.symm, "push_params", None) is not None:
-            self.symm.push_params(self)
-            return
-        for u, (lo, gs, ln) in enumerate(self.shard_map):
-            s, e = self.layout.unit_ranges[u]
-            dist.all_gather_into_tensor(self.params[s:e], self._shard16[lo:lo + ln], group=self.group)
-
     def apply_gradients(self) -> Dict[str, float]:
-        """Clip by global norm, AdamW on the local shard, refresh the bf16 compute copy, zero gradients."""
+        """Reduce gradients over the trainer ranks, clip by global norm, AdamW on the local shard, publish the bf16
+        result into every rank's resident parameter buffer, zero gradients."""
         cfg = self.cfg
         self.opt_step += 1
         lr = self.base_lr * lr_factor(self.opt_step - 1, cfg.lr_warmup_steps, cfg.total_steps(), cfg.lr_scheduler)
-        g = self._reduce_gradients()
-        self.norm_sq.zero_()
-        if self.native:
-            C = self.decoder.C
-            C.sumsq(g, 1.0, self.norm_sq)
-            if self.world > 1:
-                import torch.distributed as dist
-
-                dist.all_reduce(self.norm_sq, group=self.group)
-            if self.world == 1:
-                shard16 = self.params  # the master covers the whole buffer: write the compute copy in place
+        hp = (lr, cfg.adam_beta1, cfg.adam_beta2, cfg.adam_eps, cfg.weight_decay, self.opt_step)
+        if self.world == 1:
+            g = self.sink.flat
+            self.norm_sq.zero_()
+            if self.native:
+                C = self.decoder.C
+                C.sumsq(g, 1.0, self.norm_sq)
+                # the master covers the whole buffer: the kernel writes the bf16 compute copy in place and zeroes g
+                C.adamw_step(self.master, self.exp_avg, self.exp_avg_sq, g, self.params, *hp, 1.0, self.norm_sq,
+                             cfg.max_grad_norm, True)
+                self.decoder.launches += 2
             else:
-                if not hasattr(self, "_shard16"):
-                    self._shard16 = torch.empty(self.master.numel(), dtype=torch.bfloat16, device=self.device)
-                shard16 = self._shard16
-            C.adamw_step(self.master, self.exp_avg, self.exp_avg_sq, g, shard16, lr, cfg.adam_beta1, cfg.adam_beta2,
-                         cfg.adam_eps, cfg.weight_decay, self.opt_step, 1.0, self.norm_sq, cfg.max_grad_norm, True)
-            self.decoder.launches += 2
-            if self.world > 1:
-                self.sink.zero_()
-        else:
-            self.norm_sq.add_(g.pow(2).sum())
-            if self.world > 1:
-                import torch.distributed as dist
-
-                dist.all_reduce(self.norm_sq, group=self.group)
-            R.adamw_step_(self.master, self.exp_avg, self.exp_avg_sq, g, lr, cfg.adam_beta1, cfg.adam_beta2, cfg.adam_eps,
-                          cfg.weight_decay, self.opt_step, 1.0, cfg.max_grad_norm, self.norm_sq)
-            if self.world == 1:
+                self.norm_sq.add_(g.pow(2).sum())
+                R.adamw_step_(self.master, self.exp_avg, self.exp_avg_sq, g, *hp, 1.0, cfg.max_grad_norm, self.norm_sq)
                 self.params.copy_(self.master.to(self.compute_dtype))
+                self.sink.zero_()
+            norm_sq_dev = self.norm_sq
+        elif self.comm is not None:
+            # peer-memory path: pull-reduce my shard out of every rank's gradient buffer, exchange norm partials,
+            # AdamW + store the bf16 shard into every rank's parameter buffer - three fused kernels, no NCCL call
+            self.comm.reduce_scatter(self.grad_shard)
+            partials = self.comm.adamw_and_publish(self.master, self.exp_avg, self.exp_avg_sq, self.grad_shard, *hp,
+                                                   cfg.max_grad_norm)
+            self.decoder.launches += 2 * len(self.shard_map) + 4
+            norm_sq_dev = partials.sum()
+        else:
+            fb = self.fallback
+            fb.reduce_scatter(self.sink.flat, self.grad_shard)
+            self.norm_sq.zero_()
+            if self.native:
+                C = self.decoder.C
+                C.sumsq(self.grad_shard, 1.0, self.norm_sq)
             else:
-                self._shard16 = self.master.to(self.compute_dtype)
-            self.sink.zero_()
-            if self.world > 1 and self.grad_shard is not None:
+                self.norm_sq.add_(self.grad_shard.pow(2).sum())
+            fb.all_reduce_scalar(self.norm_sq)
+            if not hasattr(self, "_shard16") or self._shard16 is None:
+                self._shard16 = torch.empty(self.master.numel(), dtype=self.compute_dtype, device=self.device)
+            if self.native:
+                C.adamw_step(self.master, self.exp_avg, self.exp_avg_sq, self.grad_shard, self._shard16, *hp, 1.0, self.norm_sq,
+                             cfg.max_grad_norm, True)
+                self.decoder.launches += 2
+            else:
+                R.adamw_step_(self.master, self.exp_avg, self.exp_avg_sq, self.grad_shard, *hp, 1.0, cfg.max_grad_norm, self.norm_sq)
+                self._shard16.copy_(self.master.to(self.compute_dtype))
                 self.grad_shard.zero_()
-        self._gather_params()
+            fb.all_gather_params(self._shard16, self.params)
+            self.sink.zero_()
+            norm_sq_dev = self.norm_sq
         if not self.native:
             with torch.no_grad():
                 self._oracle_params.copy_(self.params)
         # one small read per optimizer step: grad norm + the microbatch statistics
         self._mb_step_buffer = []
         self._drain_pending()
-        grad_norm = float(self.norm_sq.sqrt().item())
+        grad_norm = float(norm_sq_dev.sqrt().item())
         self.d2h_bytes += 4
         self.last_grad_norm = grad_norm
         self._grad_norms.append(grad_norm)
@@ -246,6 +238,8 @@ class TrainerCore:
         self._step_summaries.append(step_summary)
         if self.native:
             self.decoder.check_status()
+            if self.comm is not None:
+                self.comm.pg.check()
         return step_summary
 
     # ------------------------------------------------------------------ BATCH_DONE
