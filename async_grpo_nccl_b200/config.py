@@ -93,6 +93,7 @@ class GRPOConfig:
     # Feed finished samples to the microbatch planner right away instead of waiting for a whole minibatch: the
     # same samples end up in the same optimizer step, but forward/backward overlaps the rest of the generation.
     eager_microbatch_dispatch: bool = False
+    comm_backend: str = "auto"  # "auto" (peer-memory kernels when available) | "peer" | "nccl" (library collectives)
     kernel_checks: bool = False  # kernels validate indices and report through a status word
     activation_recompute: str = "auto"  # "none" | "full" | "auto" (by memory estimate)
     fsdp_reshard_after_forward: Optional[bool] = None  # None: decide from model size vs HBM

@@ -333,8 +333,7 @@ class RolloutEngine:
                 self.gen_index.copy_(keep_gen)
                 g = torch.cuda.CUDAGraph()
                 # thread-local capture: the trainer / logprob threads keep allocating while this thread captures
-                with torch.cuda.graph(g, stream=torch.cuda.current_stream(self.dev) if torch.cuda.current_stream(self.dev) != torch.cuda.default_stream(self.dev) else None,
-                                      capture_error_mode="thread_local"):
+                with torch.cuda.graph(g, capture_error_mode="thread_local"):
                     self._decode_forward(B, temperature, splits)
                 self.graphs[key] = g
             g.replay()

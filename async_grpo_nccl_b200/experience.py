@@ -29,6 +29,16 @@ from .protocol import DUMMY_TRAIN_SAMPLE, Message, MessageType, sample_token_cou
 logger = logging.getLogger(__name__)
 
 
+_TRAIN_KEYS = ("sample_ids", "input_len", "output_len", "advantage", "sample_logprobs", "sample_entropies", "ref_logprobs",
+               "reward", "num_non_masked_output_tokens", "total_non_masked_output_tokens", "truncated_sample",
+               "max_reward_in_group", "modified_reward", "delimiter_not_found", "__uid__", "dummy")
+
+
+def slim_for_training(sample: Dict[str, Any]) -> Dict[str, Any]:
+    """What a trainer rank needs from a sample; text, labels and position ids are rebuilt or unused there."""
+    return {k: sample[k] for k in _TRAIN_KEYS if k in sample}
+
+
 class MicrobatchPlanner:
     """Token-budgeted, rank-balanced microbatch planner.
 
@@ -225,7 +235,7 @@ class ExperienceManager:
             if kind == "microbatch":
                 for rank, samples in payload.items():
                     if rank in self.queues:
-                        await self.queues[rank].put(Message(MessageType.MICROBATCH, samples))
+                        await self.queues[rank].put(Message(MessageType.MICROBATCH, [slim_for_training(x) for x in samples]))
             else:
                 await self.dispatch_signal(MessageType.GRADIENT_STEP)
 

@@ -235,3 +235,473 @@ class InProcessRuntime:
 
 def build_inprocess_runtime(config: GRPOConfig, device: Optional[str] = None, **kw: Any) -> InProcessRuntime:
     return InProcessRuntime(config, device, **kw)
+
+
+# =====================================================================================================
+# One process per GPU
+# =====================================================================================================
+class _RemoteGeneration:
+    def __init__(self, proxy: Any):
+        self._p = proxy
+
+    async def inference(self, sample, n=1, temperature=1.0, max_tokens=None):
+        samples, metrics = await self._p.gen_inference(sample, n, temperature, max_tokens)
+        return samples, metrics
+
+    async def batch_inference_for_evaluation(self, prompts, answers, max_tokens=1024, temperature=0.0):
+        return await self._p.gen_eval(list(prompts), list(answers), max_tokens, temperature)
+
+
+class _RemoteLogprob:
+    def __init__(self, proxy: Any):
+        self._p = proxy
+
+    async def inference(self, sample):
+        return await self._p.lp_inference(sample)
+
+
+class _RemoteManager:
+    """What a trainer rank sees of the ExperienceManager that lives on rank 0."""
+
+    def __init__(self, proxy: Any):
+        self._p = proxy
+
+    async def get_batch(self, rank: int):
+        return await self._p.em_get_batch(rank)
+
+    async def put_completion(self, rank: int, data: Any):
+        return await self._p.em_put_completion(rank, data)
+
+
+class RoleHost:
+    """RPC surface of one rank: thin forwards to the role objects that live in this process."""
+
+    def __init__(self, rt: "DistributedRuntime"):
+        self.rt = rt
+
+    async def gen_inference(self, sample, n, temperature, max_tokens):
+        return await self.rt.generation.inference(sample, n=n, temperature=temperature, max_tokens=max_tokens)
+
+    async def gen_eval(self, prompts, answers, max_tokens, temperature):
+        return await self.rt.generation.batch_inference_for_evaluation(prompts, answers, max_tokens, temperature)
+
+    async def lp_inference(self, sample):
+        return await self.rt.logprob.inference(sample)
+
+    async def trainer_start(self):
+        return await self.rt.start_local_trainer()
+
+    async def trainer_ready(self):
+        return self.rt.trainer is None or await self.rt.trainer.is_ready()
+
+    async def sync_weights(self):
+        return await self.rt.local_sync_weights()
+
+    async def verify_sync(self):
+        return await self.rt.local_checksum()
+
+    async def save_checkpoint(self, path):
+        return await self.rt.local_save_checkpoint(path)
+
+    async def stats(self):
+        return self.rt.local_stats()
+
+    async def barrier_sync(self):
+        if self.rt.native:
+            torch.cuda.synchronize(self.rt.device)
+        return True
+
+    async def record_event(self, name):
+        return self.rt.local_record_event(name)
+
+    async def elapsed(self, a, b):
+        return self.rt.local_elapsed(a, b)
+
+    async def shutdown(self):
+        self.rt.stop_event.set()
+        return True
+
+    async def em_get_batch(self, rank):
+        return await self.rt.experience_manager.get_batch(rank)
+
+    async def em_put_completion(self, rank, data):
+        return await self.rt.experience_manager.put_completion(rank, data)
+
+
+class DistributedRuntime:
+    """Created on EVERY rank (collective construction). Rank 0 then runs the orchestrator against it, the other
+    ranks call ``serve_forever``."""
+
+    def __init__(self, config: GRPOConfig, backend: Optional[str] = None):
+        import torch.distributed as dist
+
+        self.config = config
+        self.dist = dist
+        cuda = torch.cuda.is_available()
+        if not dist.is_initialized():
+            import datetime
+
+            dist.init_process_group(backend or ("nccl" if cuda else "gloo"),
+                                    timeout=datetime.timedelta(seconds=float(os.environ.get("TORCH_DIST_TIMEOUT_S", config.dist_timeout_s))))
+        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        self.native = cuda
+        if cuda:
+            self.device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", self.rank % torch.cuda.device_count())))
+            torch.cuda.set_device(self.device)
+        else:
+            self.device = torch.device("cpu")
+        place = config.resolved_placement()
+        self.place = place
+        self.trainer_ranks = list(place["trainer"])
+        self.logprob_ranks = list(place["logprob"])
+        self.rollout_ranks = list(place["rollout"])
+        self.infer_ranks = sorted(set(self.logprob_ranks) | set(self.rollout_ranks))
+        assert max(self.trainer_ranks + self.infer_ranks) < self.world, "placement names a rank beyond the world size"
+        self.is_trainer = self.rank in self.trainer_ranks
+        self.trainer_index = self.trainer_ranks.index(self.rank) if self.is_trainer else None
+        self.mcfg = resolve_model_config(config.model_name_or_path, config.model_config)
+        t = len(self.trainer_ranks)
+        self.layout = ParamLayout(self.mcfg, shard_world=t)
+        self.trainer_group = dist.new_group(self.trainer_ranks)  # every rank must call new_group
+        self.world_group = dist.group.WORLD
+        # ---- communication plane (collective construction) ----
+        self.C = None
+        self.trainer_comm = None
+        self.weight_sync = None
+        use_peer = False
+        if self.native:
+            from .ops import native as _native
+            from .parallel import symm
+
+            self.C = _native()
+            use_peer = config.comm_backend in ("auto", "peer") and symm.symmetric_available()
+            if use_peer:
+                try:
+                    if self.is_trainer and t > 1:
+                        self.trainer_comm = symm.TrainerComm(self.trainer_group, self.device, self.layout, self.C)
+                    self.weight_sync = symm.WeightSync(self.world_group, self.device, self.layout, self.C, self.trainer_ranks,
+                                                       self.infer_ranks)
+                except Exception as e:
+                    if config.comm_backend == "peer":
+                        raise
+                    logger.warning("symmetric memory unavailable (%r): falling back to library collectives", e)
+                    self.trainer_comm, self.weight_sync, use_peer = None, None, False
+        self.use_peer = use_peer
+        # ---- roles of this rank ----
+        self.trainer: Optional[TrainerWorker] = None
+        self.logprob: Optional[LogProbWorker] = None
+        self.generation: Optional[GenerationWorker] = None
+        self.engine = None
+        self.experience_manager: Optional[ExperienceManager] = ExperienceManager(config) if self.rank == 0 else None
+        self.streams = ({k: torch.cuda.Stream(self.device) for k in ("trainer", "logprob", "rollout")} if self.native
+                        else {"trainer": None, "logprob": None, "rollout": None})
+        flat32 = initial_weights(config, self.mcfg, self.layout, self.device if self.native else None)
+        if self.is_trainer:
+            core = TrainerCore(config, self.mcfg, self.device, self.trainer_index, t, self.trainer_group, flat32, config.seed,
+                               comm=self.trainer_comm)
+            self.trainer = TrainerWorker(core, self.streams["trainer"])
+        if self.rank in self.infer_ranks:
+            dtype = torch.bfloat16 if self.native else torch.float32
+            if self.weight_sync is not None:
+                self.infer_params = self.weight_sync.buffer
+                self.infer_params.copy_(flat32.to(dtype))
+            else:
+                self.infer_params = flat32.to(self.device, dtype=dtype).clone()
+        else:
+            self.infer_params = None
+        del flat32
+        if self.rank in self.logprob_ranks:
+            dec = (NativeDecoder if self.native else OracleDecoder)(self.mcfg, self.layout, self.infer_params)
+            self.logprob = LogProbWorker(config, self.mcfg, dec, self.device, stream=self.streams["logprob"])
+        if self.rank in self.rollout_ranks:
+            self.verifier = get_or_create_verifier_pool(config.global_num_verifiers, config.write_failed_generation_samples,
+                                                        config.reward_fns, config.output_dir, name=f"verifier_pool_{self.rank}",
+                                                        timeout_s=config.verifier_timeout_s)
+            if self.native:
+                from .engine.engine import RolloutEngine
+
+                free, _ = torch.cuda.mem_get_info(self.device)
+                share = 0.35 if (self.is_trainer or self.rank in self.logprob_ranks) else 0.75
+                max_len = min(self.mcfg.max_position_embeddings, config.max_generation_tokens + 4096)
+                self.engine = RolloutEngine(self.mcfg, self.layout, self.infer_params, max_seqs=config.max_num_seqs,
+                                            max_model_len=max_len, kv_memory_bytes=int(free * share),
+                                            use_cuda_graph=config.vllm_engine_preset == "throughput", block_size=config.kv_block_size)
+            else:
+                from .engine.engine import OracleEngine
+
+                self.engine = OracleEngine(self.mcfg, self.layout, self.infer_params, max_seqs=config.max_num_seqs,
+                                           max_model_len=min(self.mcfg.max_position_embeddings, config.max_generation_tokens + 2048))
+            self.generation = GenerationWorker(config, self.mcfg, self.engine, self.verifier, load_tokenizer(config),
+                                               stream=self.streams["rollout"])
+        import concurrent.futures
+
+        self._comm_pool = concurrent.futures.ThreadPoolExecutor(max_workers=1, thread_name_prefix="comm")
+        self.host = RoleHost(self)
+        self.server: Any = None
+        self.clients: Dict[int, Any] = {}
+        self.stop_event: Any = None
+        self._events: Dict[str, Any] = {}
+        self._walls: Dict[str, float] = {}
+        self.generation_controllers: List[Any] = []
+        self.logprob_controllers: List[Any] = []
+        dist.barrier()
+
+    # ------------------------------------------------------------------ servers / clients
+    def _store(self):
+        from torch.distributed.distributed_c10d import _get_default_store
+
+        return _get_default_store()
+
+    async def _start_server(self) -> None:
+        from .rpc import RpcServer
+
+        self.stop_event = asyncio.Event()
+        self.server = RpcServer(self.host, "127.0.0.1", 0)
+        port = await self.server.start()
+        self._store().set(f"agrpo_rpc_port_{self.rank}", str(port))
+
+    async def _client(self, rank: int) -> Any:
+        from .rpc import RpcClient
+
+        if rank not in self.clients:
+            loop = asyncio.get_running_loop()
+            port = int(await loop.run_in_executor(None, lambda: self._store().get(f"agrpo_rpc_port_{rank}").decode()))
+            self.clients[rank] = await RpcClient("127.0.0.1", port, name=f"rank{rank}").connect()
+        return self.clients[rank]
+
+    def serve_forever(self) -> None:
+        async def _serve() -> None:
+            await self._start_server()
+            await self.stop_event.wait()
+            await self._close()
+
+        asyncio.run(_serve())
+
+    async def _close(self) -> None:
+        if self.trainer is not None:
+            await self.trainer.stop()
+        if self.generation is not None:
+            self.generation.shutdown()
+        if getattr(self, "verifier", None) is not None:
+            self.verifier.close()
+        for c in self.clients.values():
+            await c.close()
+        if self.server is not None:
+            await self.server.close()
+
+    # ------------------------------------------------------------------ rank-0 API used by the orchestrator
+    async def initialize(self, orch: Any = None) -> None:
+        assert self.rank == 0, "the orchestrator runs on rank 0"
+        await self._start_server()
+        self.generation_controllers = []
+        for r in self.rollout_ranks:
+            self.generation_controllers.append(self.generation if r == 0 else _RemoteGeneration((await self._client(r)).proxy()))
+        self.logprob_controllers = []
+        for r in self.logprob_ranks:
+            self.logprob_controllers.append(self.logprob if r == 0 else _RemoteLogprob((await self._client(r)).proxy()))
+        for r in range(1, self.world):
+            await self._client(r)
+
+    async def _all(self, method: str, *args: Any, ranks: Optional[Sequence[int]] = None) -> List[Any]:
+        ranks = list(range(self.world)) if ranks is None else list(ranks)
+        coros = []
+        for r in ranks:
+            if r == self.rank:
+                coros.append(getattr(self.host, method)(*args))
+            else:
+                coros.append((await self._client(r)).call(method, *args))
+        return list(await asyncio.gather(*coros))
+
+    async def start_trainers(self) -> None:
+        await self._all("trainer_start", ranks=self.trainer_ranks)
+
+    async def start_local_trainer(self) -> bool:
+        if self.trainer is None:
+            return False
+        if self.rank == 0:
+            mgr: Any = self.experience_manager
+        else:
+            mgr = _RemoteManager((await self._client(0)).proxy())
+        self.trainer.set_orchestrator(mgr, self.rank)
+        await self.trainer.start_training_loop()
+        return True
+
+    async def ping_trainers(self) -> List[bool]:
+        out = []
+        for r in self.trainer_ranks:
+            try:
+                out.append(bool((await self._all("trainer_ready", ranks=[r]))[0]))
+            except Exception:
+                out.append(False)
+        return out
+
+    async def sync_weights(self) -> None:
+        await self._all("sync_weights")
+
+    async def verify_weight_sync(self) -> List[str]:
+        sums = await self._all("verify_sync")
+        ref = sums[self.trainer_ranks[0]]["trainer"]
+        bad = []
+        for r, s in enumerate(sums):
+            for k, v in s.items():
+                if v is not None and abs(v - ref) > 0:
+                    bad.append(f"rank{r}:{k}")
+        return bad
+
+    async def save_checkpoint(self, path: str) -> None:
+        await self._all("save_checkpoint", path, ranks=self.trainer_ranks)
+
+    async def barrier_and_sync(self) -> None:
+        await self._all("barrier_sync")
+
+    async def record_event(self, name: str) -> None:
+        await self._all("record_event", name)
+
+    async def elapsed_ms(self, a: str, b: str) -> float:
+        return max(await self._all("elapsed", a, b))
+
+    async def collect_stats(self) -> Dict[str, float]:
+        tot: Dict[str, float] = {}
+        for s in await self._all("stats"):
+            for k, v in s.items():
+                tot[k] = tot.get(k, 0.0) + float(v)
+        return tot
+
+    async def shutdown(self) -> None:
+        for r in range(1, self.world):
+            try:
+                await (await self._client(r)).call("shutdown", timeout=10.0)
+            except Exception:
+                pass
+        await self._close()
+
+    # ------------------------------------------------------------------ rank-local halves of collective operations
+    def _sync_on_device(self) -> None:
+        """Runs on this rank's communication thread; every rank of the world executes it once per sync."""
+        core = self.trainer.core if self.trainer is not None else None
+        if self.weight_sync is not None:
+            self.weight_sync.push(core.params if core is not None else None, self.trainer_index)
+            torch.cuda.synchronize(self.device)
+            self.weight_sync.pg.check()
+        else:
+            from .parallel.symm import broadcast_weights
+
+            if self.world == 1:
+                self.infer_params.copy_(core.params)
+            else:
+                src = core.params if core is not None else None
+                if src is None and self.infer_params is None:
+                    src = torch.empty(0)
+                broadcast_weights(src if src is not None else self.infer_params, self.layout, self.world_group, self.trainer_ranks,
+                                  self.trainer_index, self.infer_params)
+            if self.native:
+                torch.cuda.synchronize(self.device)
+
+    async def local_sync_weights(self) -> bool:
+        if self.generation is not None:
+            await self.generation.pause_for_sync()
+        if self.native:
+            torch.cuda.synchronize(self.device)
+        loop = asyncio.get_running_loop()
+        await loop.run_in_executor(self._comm_pool, self._sync_on_device)
+        if self.generation is not None:
+            await self.generation.resume_after_sync()
+        return True
+
+    async def local_checksum(self) -> Dict[str, Optional[float]]:
+        out: Dict[str, Optional[float]] = {"trainer": None, "infer": None}
+        if self.trainer is not None:
+            out["trainer"] = float(self.trainer.core.params.double().sum().item())
+        if self.infer_params is not None:
+            out["infer"] = float(self.infer_params.double().sum().item())
+        return out
+
+    async def local_save_checkpoint(self, path: str) -> bool:
+        core = self.trainer.core
+
+        def _save() -> None:
+            full = core.full_master_fp32()  # collective over the trainer group
+            if core.rank == 0:
+                ckpt.save_hf_model(path, self.mcfg, core.layout, full, tokenizer_src=self.config.model_name_or_path)
+            ckpt.save_optimizer_shard(path, core.rank, core.world, core.layout, core.optimizer_state(), core.scheduler_state())
+
+        await asyncio.get_running_loop().run_in_executor(None, self.trainer.run_blocking, _save)
+        return True
+
+    def local_stats(self) -> Dict[str, float]:
+        s = {"launches": 0.0, "h2d_bytes": 0.0, "d2h_bytes": 0.0}
+        if self.trainer is not None:
+            c = self.trainer.core
+            s["launches"] += float(getattr(c.decoder, "launches", 0))
+            s["h2d_bytes"] += float(c.h2d_bytes)
+            s["d2h_bytes"] += float(c.d2h_bytes)
+        if self.logprob is not None:
+            s["launches"] += float(getattr(self.logprob.decoder, "launches", 0))
+            s["h2d_bytes"] += float(self.logprob.h2d_bytes)
+            s["d2h_bytes"] += float(self.logprob.d2h_bytes)
+        if self.engine is not None:
+            s["launches"] += float(getattr(self.engine, "launches", 0))
+            s["h2d_bytes"] += float(getattr(self.engine, "h2d_bytes", 0))
+            s["d2h_bytes"] += float(getattr(self.engine, "d2h_bytes", 0))
+        return s
+
+    def local_record_event(self, name: str) -> bool:
+        self._walls[name] = time.time()
+        if self.native:
+            torch.cuda.synchronize(self.device)
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self._events[name] = ev
+        return True
+
+    def local_elapsed(self, a: str, b: str) -> float:
+        if self.native:
+            torch.cuda.synchronize(self.device)
+            return float(self._events[a].elapsed_time(self._events[b]))
+        return (self._walls[b] - self._walls[a]) * 1000.0
+
+
+def build_distributed_runtime(config: GRPOConfig, backend: Optional[str] = None) -> DistributedRuntime:
+    return DistributedRuntime(config, backend)
+
+
+def _spawn_entry(rank: int, world: int, port: int, cfg_dict: Dict[str, Any], rows: Any, max_batches: Optional[int], out_q: Any) -> None:
+    os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank), "MASTER_ADDR": "127.0.0.1",
+                       "MASTER_PORT": str(port)})
+    from .config import make_config
+    from .orchestrator import Orchestrator, configure_logging
+
+    configure_logging()
+    cfg = make_config(cfg_dict)
+    rt = DistributedRuntime(cfg)
+    if rank != 0:
+        rt.serve_forever()
+        return
+    orch = Orchestrator(cfg, runtime=rt, dataset=rows)
+    orch.max_macro_batches = max_batches
+    result = asyncio.run(orch.run_async())
+    out_q.put({"global_step": result["global_step"], "total_samples_seen": result["total_samples_seen"],
+               "last": {k: v for k, v in result["steps"][-1].items() if isinstance(v, (int, float))}})
+
+
+def spawn(config_dict: Dict[str, Any], rows: Any, world: int, max_macro_batches: Optional[int] = None, port: int = 29640,
+          timeout_s: float = 600.0) -> Dict[str, Any]:
+    """Starts ``world`` role processes on this node (one per GPU, or CPU ranks over gloo) and runs the orchestrator on
+    rank 0. This is the counterpart of the reference's placement-group launch for users who do not use torchrun."""
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_spawn_entry, args=(r, world, port, config_dict, rows, max_macro_batches, q), daemon=False)
+             for r in range(world)]
+    for p in procs:
+        p.start()
+    try:
+        result = q.get(timeout=timeout_s)
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+        for p in procs:
+            if p.is_alive():
+                p.kill()
+    return result

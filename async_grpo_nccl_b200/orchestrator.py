@@ -196,6 +196,8 @@ class Orchestrator:
         sync_ms = 0.0
         if self.macro_batch_count % cfg.weight_sync_every == 0:
             sync_ms = await self.sync_all_weights()
+            if cfg.verify_weight_sync_during_init:  # debug flag: re-check after every sync as well
+                await self._verify_trainer_logprob_sync()
         total_time = time.time() - t_start
         glm = completions[0].get("gen_logprob_metrics", {}) if completions else {}
         gen_tokens = float(glm.get("generation/total_tokens_generated", 0.0))
