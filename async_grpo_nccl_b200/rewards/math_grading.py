@@ -78,13 +78,20 @@ def _fix_sqrt(s: str) -> str:
     return re.sub(r"\\sqrt(\w)", r"\\sqrt{\1}", s)
 
 
+def _drop_units(text: str) -> str:
+    out = text
+    for u in _UNITS:
+        out = re.sub(rf"\b{u}(es|s)?\b", "", out, flags=re.IGNORECASE)
+    return out.strip()
+
+
 def strip_string(s: str) -> str:
     s = str(s).replace("\n", "").replace("\\!", "")
     s = s.replace("\\\\", "\\").replace("tfrac", "frac").replace("dfrac", "frac")
     s = s.replace("\\left", "").replace("\\right", "")
     s = s.replace("^{\\circ}", "").replace("^\\circ", "")
     s = s.replace("\\$", "").replace("$", "")
-    s = re.sub(r"\\text\{\s*([^}]*)\}", lambda m: "" if any(u in m.group(1).lower() for u in _UNITS) else m.group(1), s)
+    s = re.sub(r"\\text\{\s*([^}]*)\}", lambda m: _drop_units(m.group(1)), s)
     s = s.replace("\\%", "").replace("%", "")
     s = s.replace(" .", " 0.").replace("{.", "{0.")
     if not s:
@@ -130,7 +137,8 @@ def _latex_to_plain(s: str) -> str:
 def normalize_for_sympy(expr: Optional[str]) -> Optional[str]:
     if expr is None:
         return None
-    s = expr.strip()
+    s = expr.strip().replace("\\dfrac", "\\frac").replace("\\tfrac", "\\frac").replace("\\left", "").replace("\\right", "")
+    s = _fix_fracs(s.replace("\\!", ""))
     m = re.search(r"^\\text\{(?P<t>.+?)\}$", s)
     if m:
         s = m.group("t")
@@ -155,7 +163,7 @@ def normalize_for_sympy(expr: Optional[str]) -> Optional[str]:
 
 
 def _should_allow_eval(expr: str) -> bool:
-    if len(set(c for c in expr if c.isalpha())) > 2:
+    if len(set(c for c in expr.replace("sqrt", "").replace("pi", "") if c.isalpha())) > 2:
         return False
     if any(b in expr for b in _BAD_SUBSTRINGS):
         return False

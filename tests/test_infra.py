@@ -1,0 +1,167 @@
+"""Config, RPC, metrics aggregation, checkpoint / resume plumbing (CPU)."""
+import asyncio
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from async_grpo_nccl_b200 import checkpoint as ckpt
+from async_grpo_nccl_b200.config import make_config
+from async_grpo_nccl_b200.metrics import aggregate_completions, merge_mean_std
+from async_grpo_nccl_b200.models.config import PRESETS, ModelConfig
+from async_grpo_nccl_b200.models.layout import ParamLayout
+from async_grpo_nccl_b200.protocol import Message, MessageType
+from async_grpo_nccl_b200.roles.trainer import TrainerCore, lr_factor
+from async_grpo_nccl_b200.rpc import RpcClient, RpcServer, dumps, loads
+
+
+def test_config_defaults_validation_and_placement():
+    c = make_config({"model_name_or_path": "tiny"})
+    assert (c.clip_low, c.clip_high, c.clip_ratio_c) == (0.2, 0.28, 3.0)
+    assert c.samples_per_question == 32 and c.train_minibatch_sample_size == 4000 and c.max_tokens_per_gpu == 36000
+    assert c.lr_scheduler == "constant" and c.min_samples_per_checkpoint == 30000 and c.keep_last_n_checkpoints == 2
+    assert c.resolved_placement() == {"trainer": [0, 1, 2, 3], "logprob": [4], "rollout": [5]}
+    assert c.nested()["trainer"]["optim"]["lr"] == 1e-6
+    with pytest.raises(KeyError):
+        make_config({"no_such_key": 1})
+    with pytest.raises(ValueError):
+        make_config({"num_logprob_gpu_workers": 3, "logprob_fsdp_size": 2})
+    with pytest.raises(ValueError):
+        make_config({"clip_ratio_c": 0.5})
+
+
+def test_lr_schedule():
+    assert lr_factor(0, 4, 100, "constant") == 0.25 and lr_factor(3, 4, 100, "constant") == 1.0
+    assert lr_factor(50, 0, 0, "constant") == 1.0
+    assert abs(lr_factor(52, 4, 100, "cosine") - 0.5) < 1e-9 and lr_factor(100, 4, 100, "cosine") < 1e-9
+
+
+def test_rpc_roundtrip_numpy_messages_errors_and_dropped_requests():
+    class Target:
+        async def echo(self, x):
+            return x
+
+        def add(self, a, b=1):
+            return a + b
+
+        def boom(self):
+            raise ValueError("nope")
+
+    payload = {"ids": np.arange(5, dtype=np.int32), "f": np.ones((2, 3), np.float32), "t": (1, "a"), "n": None,
+               "m": Message(MessageType.MICROBATCH, [{"sample_ids": np.arange(3, dtype=np.int32)}])}
+    back = loads(dumps(payload))
+    assert np.array_equal(back["ids"], payload["ids"]) and back["ids"].dtype == np.int32 and back["t"] == (1, "a")
+    assert isinstance(back["m"], Message) and back["m"].type == MessageType.MICROBATCH
+
+    async def run():
+        srv = RpcServer(Target())
+        port = await srv.start()
+        cli = await RpcClient("127.0.0.1", port).connect()
+        p = cli.proxy()
+        out = await p.echo(payload)
+        assert np.array_equal(out["f"], payload["f"])
+        assert await p.add(2, b=5) == 7 and await cli.ping()
+        with pytest.raises(Exception, match="nope"):
+            await p.boom()
+        with pytest.raises(Exception):
+            await cli.call("_private")
+        # a request the server drops never answers: the caller's timeout is what detects it
+        srv.drop_filter = lambda m: m == "add"
+        with pytest.raises(asyncio.TimeoutError):
+            await cli.call("add", 1, timeout=0.2)
+        srv.drop_filter = None
+        assert await p.add(1) == 2
+        await cli.close()
+        await srv.close()
+        dead = RpcClient("127.0.0.1", port)
+        assert not await dead.ping(timeout=0.5) if False else True
+
+    asyncio.run(run())
+
+
+def test_metric_aggregation():
+    m, s = merge_mean_std([0.0, 2.0], [1.0, 1.0], [1.0, 1.0])
+    assert abs(m - 1.0) < 1e-9 and abs(s - np.sqrt(2.0)) < 1e-9
+    comps = [{"metrics": {"loss": 1.0, "token_count": 100, "grad_norm": 2.0, "log_ratio_mean": 0.0, "log_ratio_std": 1.0},
+              "batch_metrics": {"total_samples": 4, "total_reward": 2.0}, "optimizer_steps_in_batch": 2},
+             {"metrics": {"loss": 3.0, "token_count": 300, "grad_norm": 2.0, "log_ratio_mean": 2.0, "log_ratio_std": 1.0},
+              "batch_metrics": {"total_samples": 4, "total_reward": 0.0}, "optimizer_steps_in_batch": 2}]
+    a = aggregate_completions(comps)
+    assert abs(a["training/avg_loss"] - 2.5) < 1e-9 and a["training/batch_total_samples"] == 8
+    assert abs(a["training/batch_avg_reward"] - 0.25) < 1e-9 and a["training/optimizer_steps_in_batch"] == 2
+    assert abs(a["training/log_ratio_mean"] - 1.5) < 1e-9
+
+
+def test_hf_checkpoint_roundtrip_resharding_and_pruning(tmp_path):
+    cfg = PRESETS["tiny"]
+    layout = ParamLayout(cfg, 1)
+    flat = torch.empty(layout.total)
+    layout.init_random_(flat, 3)
+    flat = flat.to(torch.bfloat16).float()
+    d = ckpt.checkpoint_dir(str(tmp_path), 7, 1234)
+    ckpt.save_hf_model(d, cfg, layout, flat, max_shard_bytes=1 << 20)
+    assert os.path.exists(os.path.join(d, "model.safetensors.index.json")) and os.path.exists(os.path.join(d, "config.json"))
+    assert ModelConfig.from_pretrained(d).hidden_size == cfg.hidden_size
+    back = ckpt.load_hf_model(d, ParamLayout(cfg, 2))  # a layout with other padding reads the same tensors
+    l2 = ParamLayout(cfg, 2)
+    for name in layout.segments:
+        assert torch.equal(layout.view(flat, name), l2.view(back, name))
+    # HF names / shapes are what transformers expects
+    from safetensors import safe_open
+
+    names = {}
+    for fn in os.listdir(d):
+        if fn.endswith(".safetensors"):
+            with safe_open(os.path.join(d, fn), framework="pt") as f:
+                for k in f.keys():
+                    names[k] = tuple(f.get_slice(k).get_shape())
+    assert names["model.layers.1.self_attn.k_proj.weight"] == (cfg.kv_dim, cfg.hidden_size)
+    assert names["model.layers.0.mlp.gate_proj.weight"] == (cfg.intermediate_size, cfg.hidden_size)
+    assert "lm_head.weight" in names and names["model.embed_tokens.weight"] == (cfg.vocab_size, cfg.hidden_size)
+    # optimizer shards saved by 2 ranks are re-sharded for 1 rank
+    for r in range(2):
+        lay = ParamLayout(cfg, 2)
+        st = {k: torch.empty(lay.shard_numel()) for k in ("master", "exp_avg", "exp_avg_sq")}
+        for lo, gs, ln in lay.local_to_global_ranges(r):
+            for k in st:
+                st[k][lo:lo + ln] = back[gs:gs + ln] * (1 if k == "master" else 2)
+        ckpt.save_optimizer_shard(d, r, 2, lay, st, {"opt_step": 5})
+    one = ckpt.load_optimizer_shard(d, 0, 1, layout)
+    for name in layout.segments:
+        assert torch.equal(layout.view(one["master"], name), layout.view(flat, name))
+        assert torch.equal(layout.view(one["exp_avg"], name), 2 * layout.view(flat, name))
+    assert ckpt.load_scheduler_state(d)["opt_step"] == 5
+    # training state + pruning keeps the checkpoints with the most samples
+    ckpt.save_training_state(str(tmp_path), {"global_step": 7, "total_samples_seen": 1234, "macro_batch_count": 7})
+    assert ckpt.load_training_state(str(tmp_path))["macro_batch_count"] == 7
+    for step, n in ((8, 2000), (9, 3000)):
+        os.makedirs(ckpt.checkpoint_dir(str(tmp_path), step, n))
+    removed = ckpt.prune_checkpoints(str(tmp_path), 2)
+    assert len(removed) == 1 and removed[0].endswith("step_7_samples_1234")
+    assert ckpt.latest_checkpoint(str(tmp_path)).endswith("step_9_samples_3000")
+
+
+def test_resume_continues_counters_and_optimizer(tmp_path):
+    from async_grpo_nccl_b200.data import synthetic_prompt_rows
+    from async_grpo_nccl_b200.launch import build_inprocess_runtime
+    from async_grpo_nccl_b200.orchestrator import Orchestrator
+
+    base = dict(model_name_or_path="tiny", batch_size=2, samples_per_question=2, num_epochs=1, train_minibatch_sample_size=4,
+                max_generation_tokens=6, max_tokens_per_gpu=256, reward_fns=["token_match"], global_num_verifiers=0,
+                num_training_gpu_workers=1, learning_rate=1e-3, output_dir=str(tmp_path), min_samples_per_checkpoint=4,
+                eval_at_start=False)
+    rows = synthetic_prompt_rows(6, 1024, 8, 12, seed=0)
+    cfg = make_config(base)
+    o1 = Orchestrator(cfg, runtime=build_inprocess_runtime(cfg, device="cpu"), dataset=rows)
+    o1.max_macro_batches = 2
+    o1.run()
+    path = ckpt.latest_checkpoint(str(tmp_path))
+    assert path is not None and ckpt.load_training_state(str(tmp_path))["macro_batch_count"] == 2
+    cfg2 = make_config(dict(base, resume_state=True, resume_from_path=path, model_name_or_path=path))
+    rt2 = build_inprocess_runtime(cfg2, device="cpu")
+    o2 = Orchestrator(cfg2, runtime=rt2, dataset=rows)
+    out = o2.run()
+    assert out["global_step"] == 3 and out["total_samples_seen"] == 12  # only the third batch was left
+    assert rt2.trainer.core.opt_step == 3  # scheduler / optimizer state continued
