@@ -1,0 +1,335 @@
+// Skinny bf16 GEMM for decode-time shapes (M <= 256 rows, weights streamed once): split-K across a thread-block
+// cluster with the reduction done through distributed shared memory.
+//
+//   D[M, N] = A[M, K] . B[N, K]^T (+ bias) (+ residual), bf16 in / bf16 out, fp32 accumulation
+//
+// With a handful of rows the GEMM is bound by streaming B (the weights) from HBM, and a 128 x BN output tile
+// per CTA leaves most SMs idle when N is small (N = 1536 gives 12 tiles on 148 SMs). Here the S CTAs of a
+// cluster share one output tile and split K between them: each runs the usual TMA -> tcgen05.mma pipeline over
+// its K slice into TMEM, parks its fp32 partial tile in its own shared memory, and then CTA r reduces columns
+// [r * BN / S, (r + 1) * BN / S) by reading every peer's partial through ld.shared::cluster, applies the
+// epilogue and stores bf16. No partial ever goes to global memory and no TMA cluster-multicast load is used.
+// Cross-CTA hand-off uses remote mbarrier arrives and bounded local waits.
+#include <cuda_bf16.h>
+
+#include "../common/ptx.cuh"
+#include "../common/tensormap.h"
+#include "../launchers.h"
+
+namespace agrpo {
+
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kThreads = 192;
+
+struct SkParams {
+  int M, N, K;
+  __nv_bfloat16* D;
+  long long ldd;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  long long ldr;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t remote_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    if (clock64() - t0 > kWaitBudgetTicks) return false;
+  }
+  return true;
+}
+__device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void fence_cluster_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  // only used once at start-up (barrier initialisation must be visible before any remote arrive); the hardware
+  // cluster barrier cannot stall here because every CTA of a cluster is resident and reaches it unconditionally
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// MT row-tiles of 128 per CTA (M <= 128 * MT), BN columns per cluster, S = cluster size = K splits.
+template <int BN, int MT, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const SkParams p,
+                           const int S) {
+  constexpr int kABytes = MT * kBM * kBK * 2;
+  constexpr int kBBytes = BN * kBK * 2;
+  constexpr int kStageBytes = kABytes + kBBytes;
+  constexpr uint32_t kTmemCols = (MT * BN) < 32 ? 32 : (MT * BN);
+  constexpr uint32_t kIdesc = umma_idesc_bf16(kBM, BN, 0, 0);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* part = reinterpret_cast<float*>(smem + STAGES * kStageBytes);  // [BN][MT * 128] (column-major tile)
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(part) + (size_t)BN * MT * kBM * 4);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_bar = empty_bar + STAGES;
+  uint64_t* parts_ready = acc_bar + 1;   // S remote arrives: every peer's partial tile is in its shared memory
+  uint64_t* reads_done = parts_ready + 1;  // S remote arrives: every peer finished reading my partial tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(reads_done + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t crank = cluster_ctarank();
+  const int n0 = blockIdx.y * BN;
+  const int num_kb = (p.K + kBK - 1) / kBK;
+  const int kb0 = (int)((long long)num_kb * crank / S);
+  const int kb1 = (int)((long long)num_kb * (crank + 1) / S);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(acc_bar, 1);
+    mbar_init(parts_ready, S);
+    mbar_init(reads_done, S);
+    fence_cluster_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
+          report_status(p.status, kStatusWaitEmptyTimeout);
+          break;
+        }
+        uint8_t* sa = smem + stage * kStageBytes;
+        uint8_t* sb = sa + kABytes;
+        mbar_expect_tx(&full_bar[stage], kStageBytes);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) tma_load_2d(sa + mt * (kBM * kBK * 2), &tmA, &full_bar[stage], kb * kBK, mt * kBM);
+        tma_load_2d(sb, &tmB, &full_bar[stage], kb * kBK, n0);
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait(&full_bar[stage], phase)) {
+          report_status(p.status, kStatusWaitFullTimeout);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + stage * kStageBytes);
+        const uint32_t sb = sa + kABytes;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k)
+            tc_mma_f16(tmem_base + mt * BN, umma_smem_desc(sa + mt * (kBM * kBK * 2) + k * 32, 16, 1024),
+                       umma_smem_desc(sb + k * 32, 16, 1024), kIdesc, (kb > kb0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(&empty_bar[stage]);
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (ok) tc_commit(acc_bar);
+    }
+  } else {
+    // ---- epilogue warps: TMEM -> own shared memory (column-major), cluster hand-off, slice reduction ----
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    bool ok = true;
+    if (kb1 > kb0) {
+      if (!mbar_wait(acc_bar, 0)) {
+        report_status(p.status, kStatusWaitTmemFullTimeout);
+        ok = false;
+      }
+    }
+    tc_fence_after();
+#pragma unroll 1
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        if (kb1 > kb0 && ok) {
+          tmem_ld_32x32(tmem_base + lane_off + mt * BN + c * 32, r);
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) part[(size_t)(c * 32 + i) * (MT * kBM) + mt * kBM + row_in_tile] = __uint_as_float(r[i]);
+      }
+    }
+    // all 128 epilogue threads have written; one thread tells every CTA of the cluster (release at cluster scope)
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (warp == 2 && lane < S) mbar_arrive_remote(mapa_shared(smem_u32(parts_ready), lane));
+    if (!mbar_wait_cluster(parts_ready, 0)) {
+      report_status(p.status, kStatusBarrierTimeout);
+      ok = false;
+    }
+    // reduce my column slice over all peers
+    const int w = BN / S;              // columns per CTA (BN is a multiple of 8 * S by construction)
+    const int c0 = (int)crank * w;
+    if (ok) {
+      const uint32_t part_addr = smem_u32(part);
+#pragma unroll 1
+      for (int mt = 0; mt < MT; ++mt) {
+        const int row = mt * kBM + row_in_tile;
+#pragma unroll 1
+        for (int cb = 0; cb < w; cb += 8) {
+          float acc[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+          for (int peer = 0; peer < S; ++peer) {
+            const uint32_t base = mapa_shared(part_addr, (uint32_t)peer);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              acc[i] += ld_dsmem_f32(base + (uint32_t)(((size_t)(c0 + cb + i) * (MT * kBM) + row) * 4));
+          }
+          const int col = n0 + c0 + cb;
+          if (row < p.M && col < p.N) {
+            if (p.bias != nullptr) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                if (col + i < p.N) acc[i] += __bfloat162float(p.bias[col + i]);
+            }
+            if (p.residual != nullptr) {
+              const __nv_bfloat16* rp = p.residual + (long long)row * p.ldr + col;
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                if (col + i < p.N) acc[i] += __bfloat162float(rp[i]);
+            }
+            __nv_bfloat16* dst = p.D + (long long)row * p.ldd + col;
+            if (col + 8 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+              uint4 o;
+              o.x = pack_bf16x2(acc[0], acc[1]);
+              o.y = pack_bf16x2(acc[2], acc[3]);
+              o.z = pack_bf16x2(acc[4], acc[5]);
+              o.w = pack_bf16x2(acc[6], acc[7]);
+              *reinterpret_cast<uint4*>(dst) = o;
+            } else {
+              for (int i = 0; i < 8; ++i)
+                if (col + i < p.N) dst[i] = __float2bfloat16(acc[i]);
+            }
+          }
+        }
+      }
+    }
+    // tell every peer that I am done with its shared memory, then wait until everyone is done with mine
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (warp == 2 && lane < S) mbar_arrive_remote(mapa_shared(smem_u32(reads_done), lane));
+    if (!mbar_wait_cluster(reads_done, 0)) report_status(p.status, kStatusBarrierTimeout);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int BN, int MT, int STAGES>
+void launch_sk(const CUtensorMap& ta, const CUtensorMap& tb, const SkParams& p, int S, int n_tiles, cudaStream_t stream) {
+  constexpr int smem = STAGES * (MT * kBM * kBK * 2 + BN * kBK * 2) + BN * MT * kBM * 4 + 256 + 1024;
+  auto kernel = gemm_splitk_cluster_kernel<BN, MT, STAGES>;
+  static bool configured = false;
+  if (!configured) {
+    check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "gemm_splitk smem attr");
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(S, n_tiles, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = S;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  check_cuda(cudaLaunchKernelEx(&cfg, kernel, ta, tb, p, S), "gemm_splitk launch");
+}
+
+}  // namespace
+
+// Returns false when the shape is not one this kernel serves (the caller then uses the general GEMM).
+bool launch_gemm_skinny(const void* a, long long lda, const void* b, long long ldb, void* d, long long ldd, int M, int N, int K,
+                        const void* bias, const void* residual, long long ldr, int* status, int num_sms, cudaStream_t stream) {
+  if (M > 256 || K < 512 || N < 64) return false;
+  const int MT = M <= 128 ? 1 : 2;
+  const int BN = MT == 1 ? 128 : 64;
+  const int n_tiles = (N + BN - 1) / BN;
+  const int num_kb = (K + kBK - 1) / kBK;
+  int S = 8;
+  while (S > 1 && (n_tiles * S > (num_sms * 3) / 2 || num_kb / S < 2)) S >>= 1;
+  if (S == 1) return false;
+  const CUtensorMap ta = make_tmap_2d(a, K, M, lda, 64, kBM);
+  const CUtensorMap tb = make_tmap_2d(b, K, N, ldb, 64, BN);
+  SkParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.D = reinterpret_cast<__nv_bfloat16*>(d);
+  p.ldd = ldd;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  p.ldr = ldr;
+  p.status = status;
+  if (MT == 1) launch_sk<128, 1, 4>(ta, tb, p, S, n_tiles, stream);
+  else         launch_sk<64, 2, 3>(ta, tb, p, S, n_tiles, stream);
+  return true;
+}
+
+}  // namespace agrpo

@@ -22,6 +22,9 @@ void dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorM
 void launch_gemm_bf16(const void* a, long long lda, const void* b, long long ldb, void* d, long long ldd, int M, int N,
                       int K, bool a_mn, bool b_mn, const void* bias, float alpha, bool out_fp32, bool accumulate,
                       int* status, int num_sms, cudaStream_t stream, const void* residual, long long ldr) {
+  if (!a_mn && !b_mn && !out_fp32 && !accumulate && alpha == 1.f && M <= 256 &&
+      launch_gemm_skinny(a, lda, b, ldb, d, ldd, M, N, K, bias, residual, ldr, status, num_sms, stream))
+    return;
   // Widest column tile that still yields about one work item per SM; the 64 / 32 wide tiles serve
   // skinny decode-time GEMMs (K-major operands only) where the weight stream must be spread over all SMs.
   const int tiles_m = (M + kGemmBM - 1) / kGemmBM;

@@ -390,30 +390,56 @@ struct LmSampleEpilogue {
   }
 };
 
+// One warp per row: lanes stride over the column groups, then a warp reduction (argmax of the perturbed value, and
+// the usual (max, sum) merge for the log-sum-exp).
 __global__ void lm_sample_combine_kernel(const float* __restrict__ part_best, const int* __restrict__ part_idx,
                                          const float* __restrict__ part_z, const float* __restrict__ part_m,
                                          const float* __restrict__ part_s, int groups, int rows, int* __restrict__ tokens,
                                          float* __restrict__ logprobs) {
-  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (r >= rows) return;
-  float best = -INFINITY, bz = 0.f, M = -INFINITY;
-  int bi = 0;
-  for (int g = 0; g < groups; ++g) {
+  const int lane = threadIdx.x & 31;
+  float best = -INFINITY, bz = 0.f, M = -INFINITY, S = 0.f;
+  int bi = 0x7fffffff;
+  for (int g = lane; g < groups; g += 32) {
     const long long o = (long long)g * rows + r;
-    if (part_best[o] > best) {
-      best = part_best[o];
-      bi = part_idx[o];
+    const float v = part_best[o];
+    const int idx = part_idx[o];
+    if (v > best || (v == best && idx < bi)) {
+      best = v;
+      bi = idx;
       bz = part_z[o];
     }
-    M = fmaxf(M, part_m[o]);
+    const float m = part_m[o];
+    if (m > M) {
+      S = S * ((M == -INFINITY) ? 0.f : __expf(M - m)) + part_s[o];
+      M = m;
+    } else if (m != -INFINITY) {
+      S += part_s[o] * __expf(m - M);
+    }
   }
-  float S = 0.f;
-  for (int g = 0; g < groups; ++g) {
-    const long long o = (long long)g * rows + r;
-    S += part_s[o] * __expf(part_m[o] - M);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+    const float oz = __shfl_xor_sync(0xffffffffu, bz, off);
+    if (ob > best || (ob == best && oi < bi)) {
+      best = ob;
+      bi = oi;
+      bz = oz;
+    }
+    const float om = __shfl_xor_sync(0xffffffffu, M, off);
+    const float os = __shfl_xor_sync(0xffffffffu, S, off);
+    const float nm = fmaxf(M, om);
+    const float sa = (M == -INFINITY) ? 0.f : S * __expf(M - nm);
+    const float sb = (om == -INFINITY) ? 0.f : os * __expf(om - nm);
+    S = sa + sb;
+    M = nm;
   }
-  tokens[r] = bi;
-  if (logprobs != nullptr) logprobs[r] = bz - (M + logf(S));
+  if (lane == 0) {
+    tokens[r] = bi == 0x7fffffff ? 0 : bi;
+    if (logprobs != nullptr) logprobs[r] = bz - (M + logf(S));
+  }
 }
 
 }  // namespace
@@ -509,7 +535,7 @@ void launch_lm_sample(const void* hidden, long long ldh, const void* weight, lon
   e.part_idx = part_i;
   e.best = 0.f; e.best_z = 0.f; e.m = 0.f; e.s = 0.f; e.best_idx = 0; e.seed_lo = 0; e.seed_hi = 0;
   gemm_launch<256, false, false>(ta, tb, p, e, num_sms, stream);
-  lm_sample_combine_kernel<<<(rows + 127) / 128, 128, 0, stream>>>(e.part_best, e.part_idx, e.part_z, e.part_m, e.part_s,
+  lm_sample_combine_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(e.part_best, e.part_idx, e.part_z, e.part_m, e.part_s,
                                                                  groups, rows, tokens, logprobs);
   check_cuda(cudaGetLastError(), "lm_sample_combine");
 }

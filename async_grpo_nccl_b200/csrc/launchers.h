@@ -23,6 +23,11 @@ void launch_gemm_bf16(const void* a, long long lda, const void* b, long long ldb
                       int* status, int num_sms, cudaStream_t stream, const void* residual = nullptr, long long ldr = 0);
 
 
+// Decode-time shapes (M <= 256): split-K over a thread-block cluster, reduction through distributed shared memory.
+// Returns false (nothing launched) when the shape is outside what it serves.
+bool launch_gemm_skinny(const void* a, long long lda, const void* b, long long ldb, void* d, long long ldd, int M, int N, int K,
+                        const void* bias, const void* residual, long long ldr, int* status, int num_sms, cudaStream_t stream);
+
 // ---- bandwidth-bound decoder ops (elementwise.cu); bf16 activations, H and F multiples of 8 ----
 void launch_embedding_fwd(const int* ids, const void* table, void* out, int T, int H, int V, cudaStream_t s);
 void launch_embedding_bwd(const int* ids, const void* dout, float* dtable, int T, int H, int V, cudaStream_t s);

@@ -1,0 +1,317 @@
+"""Component benchmarks (device-timed with CUDA events, warm-up first, inputs larger than L2 or L2 flushed between runs).
+
+    python -m async_grpo_nccl_b200.utils.microbench gemm
+    python -m async_grpo_nccl_b200.utils.microbench attn
+    python -m async_grpo_nccl_b200.utils.microbench lmhead
+    python -m async_grpo_nccl_b200.utils.microbench decode --batch 128 --context 1024 --steps 20 [--graph]
+    python -m async_grpo_nccl_b200.utils.microbench train --tokens 16384
+    python -m async_grpo_nccl_b200.utils.microbench elementwise
+
+Each line of output is a JSON record with the achieved rate and, where a library kernel exists in the image
+(cuBLAS through torch.matmul, flash-attn 2), the same measurement for it. Roofline denominators come from
+MEASURED_PEAKS.json at the repository root when present.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+import time
+
+import numpy as np
+import torch
+
+
+def _peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d.get("hbm_gbs"), "bf16_tflops": d.get("bf16_tflops"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+_FLUSH = None
+
+
+def flush_l2():
+    global _FLUSH
+    if _FLUSH is None:
+        _FLUSH = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    _FLUSH.zero_()
+
+
+def timeit(fn, iters=10, warmup=3, flush=False):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if flush:
+            flush_l2()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def out(rec):
+    print(json.dumps(rec), flush=True)
+
+
+def bench_gemm(args):
+    from ..ops import native
+
+    C = native()
+    pk = _peaks()
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    shapes = [(8192, 8192, 8192, False, False), (32768, 2048, 1536, False, False), (32768, 17920, 1536, False, False),
+              (32768, 1536, 8960, False, False), (32768, 1536, 8960, False, True), (1536, 8960, 32768, True, True),
+              (128, 2048, 1536, False, False), (128, 1536, 1536, False, False), (128, 17920, 1536, False, False),
+              (128, 1536, 8960, False, False), (256, 2048, 1536, False, False), (256, 17920, 1536, False, False),
+              (256, 1536, 8960, False, False)]
+    for M, N, K, am, bm in shapes:
+        a = torch.randn((K, M) if am else (M, K), device="cuda", dtype=torch.bfloat16)
+        b = torch.randn((K, N) if bm else (N, K), device="cuda", dtype=torch.bfloat16)
+        d = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        A, B = (a.t() if am else a), (b.t() if bm else b)
+        small = M <= 512
+        t = timeit(lambda: C.gemm_bf16(a, b, d, am, bm, None, 1.0, False, st, None), flush=small)
+        t2 = timeit(lambda: torch.matmul(A, B.t(), out=d), flush=small)
+        fl = 2.0 * M * N * K
+        rec = {"bench": "gemm", "M": M, "N": N, "K": K, "a_mn": am, "b_mn": bm, "ms": t, "tflops": fl / t / 1e9,
+               "cublas_ms": t2, "cublas_tflops": fl / t2 / 1e9, "frac_of_peak": fl / t / 1e9 / pk["bf16_tflops"], "peak": pk["source"]}
+        if small:
+            rec["weight_gbs"] = N * K * 2 / t / 1e6
+            rec["frac_of_hbm"] = rec["weight_gbs"] / pk["hbm_gbs"]
+        out(rec)
+    assert int(st.item()) == 0
+
+
+def _tiles(lens):
+    tiles, start = [], 0
+    for L in lens:
+        for q0 in range(0, L, 128):
+            tiles.append((start, L, q0, 0))
+        start += L
+    tiles.sort(key=lambda t: -t[2])
+    return torch.tensor(tiles, dtype=torch.int32, device="cuda")
+
+
+def bench_attn(args):
+    from ..ops import native
+
+    C = native()
+    pk = _peaks()
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    Hq, Hkv, D = 12, 2, 128
+    for lens in ([4096] * 8, [16384] * 2, [512] * 64, [2048] * 16):
+        T, Cc = sum(lens), (Hq + 2 * Hkv) * D
+        qkv = torch.randn(T, Cc, device="cuda").to(torch.bfloat16)
+        dout = torch.randn(T, Hq * D, device="cuda").to(torch.bfloat16)
+        o = torch.zeros(T, Hq * D, device="cuda", dtype=torch.bfloat16)
+        lse = torch.zeros(Hq, T, device="cuda")
+        tiles = _tiles(lens)
+        sc = 1 / math.sqrt(D)
+        tf = timeit(lambda: C.attn_varlen_fwd(qkv, o, lse, tiles, Hq, Hkv, D, sc, st))
+        delta, dq_acc = torch.empty(Hq, T, device="cuda"), torch.empty(T, Hq * D, device="cuda")
+        dqkv = torch.zeros(T, Cc, device="cuda", dtype=torch.bfloat16)
+        tb = timeit(lambda: C.attn_varlen_bwd(qkv, o, dout, lse, delta, dq_acc, dqkv, tiles, Hq, Hkv, D, sc, st))
+        flf = sum(4.0 * L * L / 2 * Hq * D for L in lens)
+        rec = {"bench": "attn_varlen", "lens": f"{lens[0]}x{len(lens)}", "Hq": Hq, "Hkv": Hkv, "D": D, "fwd_ms": tf,
+               "fwd_tflops": flf / tf / 1e9, "bwd_ms": tb, "bwd_tflops": 2.5 * flf / tb / 1e9,
+               "fwd_frac_of_peak": flf / tf / 1e9 / pk["bf16_tflops"], "peak": pk["source"]}
+        try:
+            from flash_attn import flash_attn_varlen_func
+
+            q = qkv[:, :Hq * D].reshape(T, Hq, D).clone().requires_grad_(True)
+            k = qkv[:, Hq * D:(Hq + Hkv) * D].reshape(T, Hkv, D).clone().requires_grad_(True)
+            v = qkv[:, (Hq + Hkv) * D:].reshape(T, Hkv, D).clone().requires_grad_(True)
+            cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32, device="cuda")
+            t2 = timeit(lambda: flash_attn_varlen_func(q, k, v, cu, cu, max(lens), max(lens), causal=True))
+            oo = flash_attn_varlen_func(q, k, v, cu, cu, max(lens), max(lens), causal=True)
+            do = dout.view(T, Hq, D)
+            t3 = timeit(lambda: torch.autograd.grad(oo, (q, k, v), do, retain_graph=True))
+            rec.update(fa2_fwd_ms=t2, fa2_fwd_tflops=flf / t2 / 1e9, fa2_bwd_ms=t3, fa2_bwd_tflops=2.5 * flf / t3 / 1e9)
+        except Exception as e:  # flash-attn not importable
+            rec["fa2"] = repr(e)
+        out(rec)
+    assert int(st.item()) == 0
+
+
+def bench_lmhead(args):
+    from ..ops import native
+
+    C = native()
+    pk = _peaks()
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    H, V = 1536, 151936
+    for T in (4096, 16384):
+        h = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+        W = (torch.randn(V, H, device="cuda") * 0.02).to(torch.bfloat16)
+        labels = torch.randint(0, V, (T,), device="cuda", dtype=torch.int32)
+        groups = C.lmhead_num_groups(V, T)
+        partials, ll = torch.empty(3 * groups * T, device="cuda"), torch.zeros(T, device="cuda")
+        logp, ent, lse = (torch.empty(T, device="cuda") for _ in range(3))
+        dlogp = torch.randn(T, device="cuda") / T
+        dz = torch.empty(T, 4096, device="cuda", dtype=torch.bfloat16)
+        dh, dW = torch.empty(T, H, device="cuda"), torch.zeros(V, H, device="cuda")
+        tf = timeit(lambda: C.lmhead_logprob(h, W, labels, 1.0, partials, ll, logp, ent, lse, st), iters=5)
+        tb = timeit(lambda: C.lmhead_backward(h, W, labels, lse, dlogp, 1.0, dz, dh, dW, st), iters=5)
+
+        def torch_fwd():
+            for s in range(0, T, 2048):
+                z = (h[s:s + 2048] @ W.t()).float()
+                torch.logsumexp(z, -1)
+                z.gather(1, labels[s:s + 2048].long()[:, None])
+
+        tt = timeit(torch_fwd, iters=3)
+        fl = 2.0 * T * H * V
+        out({"bench": "lmhead_loss", "T": T, "H": H, "V": V, "fwd_ms": tf, "fwd_tflops": fl / tf / 1e9, "bwd_ms": tb,
+             "bwd_tflops": 3 * fl / tb / 1e9, "torch_chunked_fwd_ms": tt, "fwd_frac_of_peak": fl / tf / 1e9 / pk["bf16_tflops"],
+             "peak": pk["source"]})
+    assert int(st.item()) == 0
+
+
+def bench_elementwise(args):
+    from ..ops import native
+
+    C = native()
+    pk = _peaks()
+    T, H, F = 32768, 1536, 8960
+    x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+    w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+    y, rstd = torch.empty_like(x), torch.empty(T, device="cuda")
+    t = timeit(lambda: C.rmsnorm_fwd(x, w, y, rstd, 1e-6))
+    out({"bench": "rmsnorm_fwd", "T": T, "H": H, "ms": t, "gbs": 2 * T * H * 2 / t / 1e6, "frac_of_hbm": 2 * T * H * 2 / t / 1e6 / pk["hbm_gbs"]})
+    gu = torch.randn(T, 2 * F, device="cuda").to(torch.bfloat16)
+    act = torch.empty(T, F, device="cuda", dtype=torch.bfloat16)
+    t = timeit(lambda: C.swiglu_fwd(gu, act))
+    out({"bench": "swiglu_fwd", "T": T, "F": F, "ms": t, "gbs": 3 * T * F * 2 / t / 1e6, "frac_of_hbm": 3 * T * F * 2 / t / 1e6 / pk["hbm_gbs"]})
+    n = 1_543_000_000 // 4
+    p, m, v, g = (torch.zeros(n, device="cuda") for _ in range(4))
+    p16 = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    ns = torch.ones(1, device="cuda")
+    t = timeit(lambda: C.adamw_step(p, m, v, g, p16, 1e-6, 0.9, 0.999, 1e-8, 0.0, 1, 1.0, ns, 1.0, True), iters=5)
+    by = n * (4 * 4 + 4 * 4 + 2)
+    out({"bench": "adamw", "n": n, "ms": t, "gbs": by / t / 1e6, "frac_of_hbm": by / t / 1e6 / pk["hbm_gbs"]})
+
+
+def _engine(args, graph):
+    from ..engine.engine import RolloutEngine
+    from ..models.config import PRESETS
+    from ..models.layout import ParamLayout
+
+    cfg = PRESETS[args.model]
+    layout = ParamLayout(cfg)
+    params = (torch.randn(layout.total, device="cuda") * 0.02).to(torch.bfloat16)
+    eng = RolloutEngine(cfg, layout, params, max_seqs=max(64, args.batch), max_model_len=args.context + args.steps + 64,
+                        num_blocks=(args.batch * (args.context + args.steps + 64)) // 16 + 1024, use_cuda_graph=graph)
+    return cfg, eng
+
+
+def bench_decode(args):
+    pk = _peaks()
+    cfg, eng = _engine(args, args.graph)
+    rng = np.random.default_rng(0)
+    n = 8
+    for i in range(args.batch // n):
+        eng.add_request(i, rng.integers(0, cfg.vocab_size, args.context).astype(np.int32), n=n, max_new_tokens=args.steps + 8,
+                        temperature=1.0, seed=i, forced_new_tokens=[args.steps + 8] * n)
+    while eng.sched.num_waiting > 0 or eng.pending:
+        eng.step()  # prefill
+    for _ in range(3):
+        eng.step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        eng.step()
+    e1.record()
+    torch.cuda.synchronize()
+    eng.check_status()
+    ms = e0.elapsed_time(e1) / args.steps
+    layout_bytes = eng.layout.total * 2
+    kv_bytes = args.batch * (args.context + args.steps // 2) * cfg.num_hidden_layers * 2 * cfg.num_key_value_heads * cfg.head_dim * 2
+    out({"bench": "decode_step", "model": args.model, "batch": args.batch, "context": args.context, "graph": bool(args.graph),
+         "ms_per_step": ms, "tokens_per_s": args.batch / ms * 1e3, "weight_bytes": layout_bytes, "kv_bytes": kv_bytes,
+         "ideal_ms": (layout_bytes + kv_bytes) / pk["hbm_gbs"] / 1e6, "frac_of_hbm": (layout_bytes + kv_bytes) / ms / 1e6 / pk["hbm_gbs"],
+         "peak": pk["source"]})
+
+
+def bench_train(args):
+    from ..config import make_config
+    from ..models.config import PRESETS
+    from ..roles.trainer import TrainerCore
+
+    pk = _peaks()
+    mcfg = PRESETS[args.model]
+    cfg = make_config({"model_name_or_path": args.model, "train_minibatch_sample_size": 8, "global_num_verifiers": 0,
+                       "activation_recompute": "full" if args.recompute else "none"})
+    from ..launch import initial_weights
+    from ..models.layout import ParamLayout
+
+    flat = initial_weights(cfg, mcfg, ParamLayout(mcfg), "cuda")
+    core = TrainerCore(cfg, mcfg, torch.device("cuda"), init_flat_fp32=flat)
+    del flat
+    rng = np.random.default_rng(0)
+    n = 8
+    per = args.tokens // n
+    samples = []
+    for _ in range(n):
+        li = 256
+        L = per
+        samples.append({"sample_ids": rng.integers(0, mcfg.vocab_size, L).astype(np.int32), "input_len": li, "output_len": L - li,
+                        "advantage": float(rng.normal()), "sample_logprobs": np.full(L, -11.9, np.float32),
+                        "sample_entropies": np.zeros(L, np.float32), "reward": 1.0})
+
+    def step():
+        core.compute_gradients(samples)
+        core.apply_gradients()
+
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.iters):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.iters
+    T = per * n
+    nparam = mcfg.num_parameters() - (0 if mcfg.tie_word_embeddings else 0)
+    fl = 6.0 * T * (nparam - mcfg.vocab_size * mcfg.hidden_size * (0 if mcfg.tie_word_embeddings else 1))
+    fl += 3 * sum(4.0 * per * per / 2 * mcfg.num_attention_heads * mcfg.head_dim for _ in range(n)) * mcfg.num_hidden_layers
+    if args.recompute:
+        fl *= 4.0 / 3.0
+    out({"bench": "train_step", "model": args.model, "tokens": T, "recompute": bool(args.recompute), "ms": ms,
+         "tokens_per_s": T / ms * 1e3, "model_tflops": fl / ms / 1e9, "frac_of_peak": fl / ms / 1e9 / pk["bf16_tflops"],
+         "peak": pk["source"], "max_mem_gb": torch.cuda.max_memory_allocated() / 1e9})
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "attn", "lmhead", "elementwise", "decode", "train"])
+    ap.add_argument("--model", default="qwen2.5-1.5b")
+    ap.add_argument("--batch", type=int, default=128)
+    ap.add_argument("--context", type=int, default=1024)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--graph", action="store_true")
+    ap.add_argument("--tokens", type=int, default=16384)
+    ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--recompute", action="store_true")
+    args = ap.parse_args()
+    {"gemm": bench_gemm, "attn": bench_attn, "lmhead": bench_lmhead, "elementwise": bench_elementwise, "decode": bench_decode,
+     "train": bench_train}[args.what](args)
+
+
+if __name__ == "__main__":
+    main()

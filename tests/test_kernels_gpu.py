@@ -311,3 +311,22 @@ def test_bounded_wait_reports_status_instead_of_hanging():
     C.wait_flag_probe(flag, 2, 0.05, st)
     torch.cuda.synchronize()
     assert int(st.item()) == 0
+
+
+@pytest.mark.parametrize("M", [1, 64, 128, 200, 256])
+@pytest.mark.parametrize("N,K", [(1536, 1536), (2048, 1536), (1536, 8960), (200, 520), (17920, 1536)])
+def test_gemm_skinny_cluster_split_k(M, N, K):
+    """Decode-time shapes take the cluster split-K kernel (reduction through distributed shared memory)."""
+    C = native()
+    torch.manual_seed(M * 7 + N)
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    res = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    d = torch.full((M, N), 7.0, device=DEV, dtype=torch.bfloat16)
+    st = status_word()
+    C.gemm_bf16(a, b, d, False, False, bias, 1.0, False, st, res)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    ref = a.float() @ b.float().t() + bias.float() + res.float()
+    assert rel_err(d, ref) < 1e-2

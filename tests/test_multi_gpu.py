@@ -1,0 +1,110 @@
+"""Peer-memory collectives on 2+ GPUs against torch.distributed (NCCL) results.
+
+Runs as child processes, one per GPU, with NVLS disabled in NCCL and plain peer loads / stores in our kernels.
+Data movement (weight push) must be bit-exact; reductions are compared with a tolerance. The last case lets a
+barrier run out on purpose by having one rank skip it: the waiting rank's kernel must return an error status within
+its budget while the context stays usable (no fault, no hang)."""
+import os
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, q):
+    os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank), "MASTER_ADDR": "127.0.0.1",
+                       "MASTER_PORT": str(port), "NCCL_NVLS_ENABLE": "0"})
+    import torch.distributed as dist
+
+    from async_grpo_nccl_b200.models.config import PRESETS
+    from async_grpo_nccl_b200.models.layout import ParamLayout
+    from async_grpo_nccl_b200.ops import native
+    from async_grpo_nccl_b200.parallel import symm
+
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world)
+    try:
+        C = native()
+        cfg = PRESETS["tiny128"]
+        layout = ParamLayout(cfg, shard_world=world)
+        group = dist.group.WORLD
+        comm = symm.TrainerComm(group, dev, layout, C)
+        # ---- reduce-scatter + norm ----
+        g = torch.Generator(device=dev).manual_seed(100 + rank)
+        comm.grad_buffer.copy_(torch.randn(layout.total, device=dev, generator=g))
+        full = comm.grad_buffer.clone()
+        dist.all_reduce(full)
+        shard = torch.zeros(layout.shard_numel(), device=dev)
+        comm.reduce_scatter(shard)
+        torch.cuda.synchronize()
+        comm.pg.check()
+        want = torch.cat([full[gs:gs + ln] for lo, gs, ln in layout.local_to_global_ranges(rank)])
+        assert torch.allclose(shard, want, rtol=1e-5, atol=1e-5), "reduce-scatter mismatch"
+        norm_sq = comm.norm_tab.local[:world].sum().item()
+        assert abs(norm_sq - full.double().pow(2).sum().item()) / full.double().pow(2).sum().item() < 1e-4
+        assert float(comm.grad_buffer.abs().max()) == 0.0  # zeroed for the next accumulation
+        # ---- AdamW + publish: every rank's parameter buffer equals the gathered bf16 shards ----
+        master = torch.cat([torch.full((ln,), float(rank + 1), device=dev) for lo, gs, ln in layout.local_to_global_ranges(rank)])
+        m, v = torch.zeros_like(master), torch.zeros_like(master)
+        comm.adamw_and_publish(master, m, v, shard.clone(), 1e-2, 0.9, 0.999, 1e-8, 0.0, 1, 1.0)
+        torch.cuda.synchronize()
+        comm.pg.check()
+        gathered = [torch.empty_like(master) for _ in range(world)]
+        dist.all_gather(gathered, master)
+        ref = torch.zeros(layout.total, device=dev)
+        for r in range(world):
+            for lo, gs, ln in layout.local_to_global_ranges(r):
+                ref[gs:gs + ln] = gathered[r][lo:lo + ln]
+        assert torch.equal(comm.param_buffer, ref.to(torch.bfloat16)), "published parameters differ"
+        # first Adam step moves by lr * sign(g) (clip coefficient applied to g only changes magnitude of g)
+        assert torch.allclose((master - (rank + 1)).abs(), torch.full_like(master, 1e-2), atol=1e-4)
+        # ---- weight push to inference buffers: bit-exact ----
+        ws = symm.WeightSync(group, dev, layout, C, trainer_ranks=list(range(world)), infer_ranks=list(range(world)))
+        ws.push(comm.param_buffer, rank)
+        torch.cuda.synchronize()
+        ws.pg.check()
+        assert torch.equal(ws.buffer, comm.param_buffer), "pushed weights differ"
+        # ---- a barrier partner that never arrives: bounded wait -> error status, context still usable ----
+        dist.barrier()
+        symm_budget = symm.WAIT_BUDGET_S
+        symm.WAIT_BUDGET_S = 0.3
+        pg = symm.PeerGroup(group, dev, C)
+        if rank == 0:
+            pg.barrier()  # rank 1 does not join this one
+            torch.cuda.synchronize()
+            try:
+                pg.check()
+                raised = False
+            except RuntimeError:
+                raised = True
+            assert raised, "the lone rank's barrier must report a timeout"
+        symm.WAIT_BUDGET_S = symm_budget
+        x = torch.ones(4, device=dev)
+        dist.all_reduce(x)
+        assert x[0].item() == world  # the context and the communicator still work
+        q.put((rank, "ok"))
+    except Exception as e:  # report instead of leaving the parent waiting
+        import traceback
+
+        q.put((rank, f"FAILED: {e!r}\n{traceback.format_exc()}"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_peer_memory_collectives_match_nccl():
+    import torch.multiprocessing as mp
+
+    world = min(4, torch.cuda.device_count())
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, 29733, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, msg in results:
+        assert msg == "ok", f"rank {rank}: {msg}"
