@@ -48,10 +48,14 @@ def alloc_symmetric(numel: int, dtype: torch.dtype, device: torch.device, group:
     import torch.distributed._symmetric_memory as sm
 
     name = group.group_name if hasattr(group, "group_name") else group
-    try:
-        sm.enable_symm_mem_for_group(name)
-    except Exception:
-        pass
+    import warnings
+
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        try:
+            sm.enable_symm_mem_for_group(name)  # needed by older torch releases, a no-op on newer ones
+        except Exception:
+            pass
     t = sm.empty(numel, dtype=dtype, device=device)
     try:
         hdl = sm.rendezvous(t, group=name)

@@ -165,3 +165,23 @@ def test_resume_continues_counters_and_optimizer(tmp_path):
     out = o2.run()
     assert out["global_step"] == 3 and out["total_samples_seen"] == 12  # only the third batch was left
     assert rt2.trainer.core.opt_step == 3  # scheduler / optimizer state continued
+
+
+def test_plot_tools_and_phase_timer(tmp_path):
+    from async_grpo_nccl_b200.utils.plot import main, moving_average, parse_experiment_logs
+    from async_grpo_nccl_b200.utils.timing import PhaseTimer, record_function
+
+    p = tmp_path / "training_metrics.jsonl"
+    with open(p, "w") as f:
+        for i in range(20):
+            f.write(json.dumps({"trainer_step": i, "training/avg_loss": 1.0 / (i + 1), "note": "text"}) + "\n")
+    ser = parse_experiment_logs(str(p))
+    assert len(ser["training/avg_loss"]) == 20 and "note" not in ser
+    assert moving_average([1, 2, 3, 4], 3) == [1.5, 2.0, 3.0, 3.5]
+    assert main(["info", str(p)]) == 0
+    assert main(["plot", str(p), "-v", "training/avg_loss", "-o", str(tmp_path / "o.svg")]) == 0
+    assert any(fn.startswith("o.") for fn in os.listdir(tmp_path))
+    t = PhaseTimer()
+    with t.phase("a"), record_function("inner"):
+        sum(range(1000))
+    assert "a" in t.summary()
