@@ -292,6 +292,21 @@ void kv_cache_write_decode(const Tensor& qkv, const Tensor& block_tables, const 
                                       (int)k_cache.size(2), (int)k_cache.size(0), opt_ptr<int>(status), cur_stream());
 }
 
+void rope_kv_write_decode(Tensor& qkv, const Tensor& cos_t, const Tensor& sin_t, const Tensor& block_tables, const Tensor& seq_lens,
+                          Tensor& k_cache, Tensor& v_cache, int64_t Hq, int64_t Hkv, int64_t D, const OptTensor& status) {
+  check_bf16(qkv, "qkv"); check_f32(cos_t, "cos"); check_f32(sin_t, "sin"); check_i32(block_tables, "block_tables");
+  check_i32(seq_lens, "seq_lens"); check_bf16(k_cache, "k_cache"); check_bf16(v_cache, "v_cache");
+  TORCH_CHECK(qkv.dim() == 2 && qkv.stride(1) == 1 && qkv.size(1) == (Hq + 2 * Hkv) * D && qkv.stride(0) % 8 == 0, "rope_kv_write: qkv");
+  TORCH_CHECK(cos_t.is_contiguous() && sin_t.is_contiguous() && cos_t.size(1) == D / 2, "rope_kv_write: tables");
+  TORCH_CHECK(block_tables.dim() == 2 && block_tables.stride(1) == 1 && block_tables.size(0) >= qkv.size(0) && seq_lens.numel() >= qkv.size(0), "rope_kv_write: block tables");
+  TORCH_CHECK(k_cache.dim() == 4 && k_cache.is_contiguous() && v_cache.is_contiguous(), "rope_kv_write: cache");
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  agrpo::launch_rope_kv_write_decode(qkv.data_ptr(), qkv.stride(0), cos_t.data_ptr<float>(), sin_t.data_ptr<float>(), (int)cos_t.size(0),
+                                     block_tables.data_ptr<int>(), (int)block_tables.stride(0), seq_lens.data_ptr<int>(),
+                                     k_cache.data_ptr(), v_cache.data_ptr(), (int)qkv.size(0), (int)Hq, (int)Hkv, (int)D,
+                                     (int)k_cache.size(2), (int)k_cache.size(0), opt_ptr<int>(status), cur_stream());
+}
+
 void paged_decode_attn(const Tensor& qkv, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_tables,
                        const Tensor& seq_lens, Tensor& out, int64_t Hq, int64_t Hkv, int64_t D, double softmax_scale,
                        int64_t splits, const OptTensor& part_o, const OptTensor& part_ml, const OptTensor& status) {
@@ -522,6 +537,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("kv_cache_write", &kv_cache_write);
   m.def("kv_cache_write_decode", &kv_cache_write_decode, py::arg("qkv"), py::arg("block_tables"), py::arg("seq_lens"),
         py::arg("k_cache"), py::arg("v_cache"), py::arg("Hq"), py::arg("Hkv"), py::arg("D"), py::arg("status") = py::none());
+  m.def("rope_kv_write_decode", &rope_kv_write_decode, py::arg("qkv"), py::arg("cos"), py::arg("sin"), py::arg("block_tables"),
+        py::arg("seq_lens"), py::arg("k_cache"), py::arg("v_cache"), py::arg("Hq"), py::arg("Hkv"), py::arg("D"),
+        py::arg("status") = py::none());
   m.def("paged_decode_attn", &paged_decode_attn, py::arg("qkv"), py::arg("k_cache"), py::arg("v_cache"),
         py::arg("block_tables"), py::arg("seq_lens"), py::arg("out"), py::arg("Hq"), py::arg("Hkv"), py::arg("D"),
         py::arg("softmax_scale"), py::arg("splits") = 1, py::arg("part_o") = py::none(), py::arg("part_ml") = py::none(),

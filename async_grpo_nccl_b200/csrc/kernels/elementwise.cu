@@ -285,6 +285,7 @@ inline int grid_for(long long work, int block, int cap = 148 * 16) {
 
 void launch_embedding_fwd(const int* ids, const void* table, void* out, int T, int H, int V, cudaStream_t s) {
   if (T == 0) return;
+  AGRPO_PREFER_SMEM(embedding_fwd_kernel);
   embedding_fwd_kernel<<<(T + 7) / 8, 256, 0, s>>>(ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, T, H, V);
   check_cuda(cudaGetLastError(), "embedding_fwd");
 }
@@ -295,6 +296,7 @@ void launch_embedding_bwd(const int* ids, const void* dout, float* dtable, int T
 }
 void launch_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int T, int H, float eps, cudaStream_t s) {
   if (T == 0) return;
+  AGRPO_PREFER_SMEM(rmsnorm_fwd_kernel);
   rmsnorm_fwd_kernel<<<(T + 7) / 8, 256, 0, s>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
                                                  rstd, T, H, eps);
   check_cuda(cudaGetLastError(), "rmsnorm_fwd");
@@ -325,12 +327,14 @@ void launch_rope(void* qkv, const int* pos, const float* cos_t, const float* sin
                  long long row_pitch, int max_pos, bool backward, cudaStream_t s) {
   if (T == 0) return;
   const long long work = (long long)T * n_rot_heads * (D / 2);
+  AGRPO_PREFER_SMEM(rope_kernel);
   rope_kernel<<<grid_for(work, 256), 256, 0, s>>>((__nv_bfloat16*)qkv, pos, cos_t, sin_t, T, n_rot_heads, D, row_pitch,
                                                   max_pos, backward ? -1.f : 1.f);
   check_cuda(cudaGetLastError(), "rope");
 }
 void launch_swiglu_fwd(const void* gu, void* out, int T, int F, cudaStream_t s) {
   if (T == 0) return;
+  AGRPO_PREFER_SMEM(swiglu_fwd_kernel);
   swiglu_fwd_kernel<<<grid_for((long long)T * (F / 8), 256), 256, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out,
                                                                            T, F);
   check_cuda(cudaGetLastError(), "swiglu_fwd");

@@ -64,6 +64,48 @@ __global__ void kv_cache_write_decode_kernel(const __nv_bfloat16* __restrict__ q
   }
 }
 
+// Decode-time RoPE + KV write in one pass: rotates the q and k heads of row b in place (position seq_lens[b] - 1)
+// and stores the rotated k and the v of that token into the sequence's cache page.
+__global__ void rope_kv_write_decode_kernel(__nv_bfloat16* __restrict__ qkv, long long row_pitch, const float* __restrict__ cos_t,
+                                            const float* __restrict__ sin_t, int max_pos, const int* __restrict__ block_tables,
+                                            int max_blocks, const int* __restrict__ seq_lens, __nv_bfloat16* __restrict__ k_cache,
+                                            __nv_bfloat16* __restrict__ v_cache, int B, int Hq, int Hkv, int D, int block_size,
+                                            int num_cache_blocks, int* status) {
+  const int b = blockIdx.x;
+  if (b >= B) return;
+  const int len = seq_lens[b];
+  const int pos = len > 0 ? len - 1 : 0;
+  const int p = pos >= max_pos ? max_pos - 1 : pos;
+  const int half = D / 2;
+  __nv_bfloat16* row = qkv + (long long)b * row_pitch;
+  // rotate q and k heads (pairs (i, i + D/2))
+  for (int idx = threadIdx.x; idx < (Hq + Hkv) * half; idx += blockDim.x) {
+    const int h = idx / half, i = idx % half;
+    const float c = cos_t[(size_t)p * half + i], s = sin_t[(size_t)p * half + i];
+    __nv_bfloat16* base = row + (size_t)h * D;
+    const float x1 = __bfloat162float(base[i]), x2 = __bfloat162float(base[i + half]);
+    base[i] = __float2bfloat16(x1 * c - x2 * s);
+    base[i + half] = __float2bfloat16(x2 * c + x1 * s);
+  }
+  if (len <= 0) return;
+  __syncthreads();
+  const int blk = block_tables[(long long)b * max_blocks + pos / block_size];
+  if (blk < 0 || blk >= num_cache_blocks) {
+    if (threadIdx.x == 0) report_status(status, kStatusBadIndex);
+    return;
+  }
+  const int off = pos % block_size;
+  const int per_row = Hkv * D / 8;
+  for (int i = threadIdx.x; i < 2 * per_row; i += blockDim.x) {
+    const bool is_v = i >= per_row;
+    const int j = is_v ? i - per_row : i;
+    const int h = j / (D / 8), c = j % (D / 8);
+    const uint4 val = *reinterpret_cast<const uint4*>(row + (size_t)(Hq + (is_v ? Hkv : 0)) * D + (size_t)h * D + c * 8);
+    __nv_bfloat16* dst = (is_v ? v_cache : k_cache) + (((long long)blk * Hkv + h) * block_size + off) * D + c * 8;
+    *reinterpret_cast<uint4*>(dst) = val;
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 // Paged decode attention (one query token per sequence), D = 128, block_size = 16, G = Hq/Hkv <= 8.
 // CTA = (split, kv head, sequence), 4 warps; a warp owns whole 16-token blocks: cp.async double
@@ -447,6 +489,7 @@ __global__ void lm_sample_combine_kernel(const float* __restrict__ part_best, co
 void launch_kv_cache_write(const void* qkv, long long row_pitch, int k_col0, int v_col0, const int* slots, void* k_cache,
                            void* v_cache, int T, int Hkv, int D, int block_size, cudaStream_t s) {
   if (T == 0) return;
+  AGRPO_PREFER_SMEM(kv_cache_write_kernel);
   kv_cache_write_kernel<<<T, 64, 0, s>>>((const __nv_bfloat16*)qkv, row_pitch, k_col0, v_col0, slots, (__nv_bfloat16*)k_cache,
                                          (__nv_bfloat16*)v_cache, T, Hkv, D, block_size);
   check_cuda(cudaGetLastError(), "kv_cache_write");
@@ -456,10 +499,22 @@ void launch_kv_cache_write_decode(const void* qkv, long long row_pitch, int k_co
                                   int max_blocks, const int* seq_lens, void* k_cache, void* v_cache, int B, int Hkv, int D,
                                   int block_size, int num_cache_blocks, int* status, cudaStream_t s) {
   if (B == 0) return;
+  AGRPO_PREFER_SMEM(kv_cache_write_decode_kernel);
   kv_cache_write_decode_kernel<<<B, 64, 0, s>>>((const __nv_bfloat16*)qkv, row_pitch, k_col0, v_col0, block_tables, max_blocks,
                                                 seq_lens, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, B, Hkv, D,
                                                 block_size, num_cache_blocks, status);
   check_cuda(cudaGetLastError(), "kv_cache_write_decode");
+}
+
+void launch_rope_kv_write_decode(void* qkv, long long row_pitch, const float* cos_t, const float* sin_t, int max_pos,
+                                 const int* block_tables, int max_blocks, const int* seq_lens, void* k_cache, void* v_cache, int B,
+                                 int Hq, int Hkv, int D, int block_size, int num_cache_blocks, int* status, cudaStream_t s) {
+  if (B == 0) return;
+  AGRPO_PREFER_SMEM(rope_kv_write_decode_kernel);
+  rope_kv_write_decode_kernel<<<B, 128, 0, s>>>((__nv_bfloat16*)qkv, row_pitch, cos_t, sin_t, max_pos, block_tables, max_blocks,
+                                                seq_lens, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, B, Hq, Hkv, D, block_size,
+                                                num_cache_blocks, status);
+  check_cuda(cudaGetLastError(), "rope_kv_write_decode");
 }
 
 void launch_paged_decode_attn(const void* q, long long ldq, int q_col0, const void* k_cache, const void* v_cache,
@@ -499,11 +554,13 @@ void launch_paged_decode_attn(const void* q, long long ldq, int q_col0, const vo
     configured = true;
   }
   dim3 grid(splits, Hkv, B);
+  AGRPO_PREFER_SMEM(paged_decode_attn_kernel);
   paged_decode_attn_kernel<<<grid, kDecWarps * 32, smem, s>>>(p);
   check_cuda(cudaGetLastError(), "paged_decode_attn");
   if (splits > 1) {
     dim3 g2(Hkv, B);
-    paged_decode_combine_kernel<<<g2, 128, 0, s>>>(part_o, part_ml, splits, Hkv, G, (__nv_bfloat16*)out, ldo);
+    AGRPO_PREFER_SMEM(paged_decode_combine_kernel);
+  paged_decode_combine_kernel<<<g2, 128, 0, s>>>(part_o, part_ml, splits, Hkv, G, (__nv_bfloat16*)out, ldo);
     check_cuda(cudaGetLastError(), "paged_decode_combine");
   }
 }
@@ -535,6 +592,7 @@ void launch_lm_sample(const void* hidden, long long ldh, const void* weight, lon
   e.part_idx = part_i;
   e.best = 0.f; e.best_z = 0.f; e.m = 0.f; e.s = 0.f; e.best_idx = 0; e.seed_lo = 0; e.seed_hi = 0;
   gemm_launch<256, false, false>(ta, tb, p, e, num_sms, stream);
+  AGRPO_PREFER_SMEM(lm_sample_combine_kernel);
   lm_sample_combine_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(e.part_best, e.part_idx, e.part_z, e.part_m, e.part_s,
                                                                  groups, rows, tokens, logprobs);
   check_cuda(cudaGetLastError(), "lm_sample_combine");

@@ -13,6 +13,22 @@ inline void check_cuda(cudaError_t e, const char* what) {
   if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
 }
 
+// The GEMM / attention kernels need ~200 KB of shared memory per SM. A kernel that prefers a large L1 instead makes
+// the SM re-partition its L1 / shared memory when it follows or precedes them, which costs microseconds per switch in a
+// decode step of ~280 short kernels. Every small kernel therefore asks for the same (maximum shared) carve-out once.
+template <typename K>
+inline void prefer_max_shared(K kernel) {
+  cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+}
+#define AGRPO_PREFER_SMEM(kernel)                        \
+  do {                                                    \
+    static bool agrpo_once_ = false;                      \
+    if (!agrpo_once_) {                                   \
+      ::agrpo::prefer_max_shared(kernel);                 \
+      agrpo_once_ = true;                                 \
+    }                                                     \
+  } while (0)
+
 // d[M,N] = alpha * A . B^T (+ bias[N]) (+ d). bf16 operands, fp32 accumulation on tcgen05.
 //   a_mn = false: a is [M, K] row-major with pitch lda; a_mn = true: a is [K, M] row-major
 //   b_mn = false: b is [N, K] row-major with pitch ldb; b_mn = true: b is [K, N] row-major
@@ -93,6 +109,10 @@ void launch_kv_cache_write(const void* qkv, long long row_pitch, int k_col0, int
 void launch_kv_cache_write_decode(const void* qkv, long long row_pitch, int k_col0, int v_col0, const int* block_tables,
                                   int max_blocks, const int* seq_lens, void* k_cache, void* v_cache, int B, int Hkv, int D,
                                   int block_size, int num_cache_blocks, int* status, cudaStream_t s);
+// RoPE on the q / k heads of each row (position seq_lens[b] - 1) and the KV write of that token, in one kernel.
+void launch_rope_kv_write_decode(void* qkv, long long row_pitch, const float* cos_t, const float* sin_t, int max_pos,
+                                 const int* block_tables, int max_blocks, const int* seq_lens, void* k_cache, void* v_cache, int B,
+                                 int Hq, int Hkv, int D, int block_size, int num_cache_blocks, int* status, cudaStream_t s);
 // One query token per sequence against the paged cache. part_o: fp32 [B, Hkv, splits, 8, D], part_ml: fp32
 // [B, Hkv, splits, 8, 2] (only touched when splits > 1).
 void launch_paged_decode_attn(const void* q, long long ldq, int q_col0, const void* k_cache, const void* v_cache,

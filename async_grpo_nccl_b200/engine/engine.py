@@ -271,10 +271,8 @@ class RolloutEngine:
             C.rmsnorm_fwd(x, dec.w(p + "ln1"), h, None, cfg.rms_norm_eps)
             C.gemm_bf16(h, dec.w(p + "wqkv"), qkv, False, False, dec.w(p + "bqkv") if cfg.attention_bias else None, 1.0, False,
                         self.status, None)
-            C.rope_inplace(qkv, self.positions[:B], cos_t, sin_t, cfg.num_attention_heads + cfg.num_key_value_heads,
-                           cfg.head_dim, False)
-            C.kv_cache_write_decode(qkv, bt, sl, self._kc(i), self._vc(i), cfg.num_attention_heads, cfg.num_key_value_heads,
-                                    cfg.head_dim, self.status)
+            C.rope_kv_write_decode(qkv, cos_t, sin_t, bt, sl, self._kc(i), self._vc(i), cfg.num_attention_heads,
+                                   cfg.num_key_value_heads, cfg.head_dim, self.status)
             C.paged_decode_attn(qkv, self._kc(i), self._vc(i), bt, sl, attn, cfg.num_attention_heads, cfg.num_key_value_heads,
                                 cfg.head_dim, scale, splits, self.b_part_o, self.b_part_ml, self.status)
             C.gemm_bf16(attn, dec.w(p + "wo"), x1, False, False, None, 1.0, False, self.status, x)
@@ -291,7 +289,7 @@ class RolloutEngine:
         self.gen_index[:B].add_(1)
 
     def _launch_count_decode(self, splits: int) -> int:
-        per_layer = 10 + (1 if splits > 1 else 0)
+        per_layer = 9 + (1 if splits > 1 else 0)
         return 1 + per_layer * self.cfg.num_hidden_layers + 3
 
     def _decode(self, plan: Dict[str, Any]) -> None:

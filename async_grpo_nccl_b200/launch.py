@@ -377,10 +377,10 @@ class DistributedRuntime:
             use_peer = config.comm_backend in ("auto", "peer") and symm.symmetric_available()
             if use_peer:
                 try:
-                    if self.is_trainer and t > 1:
-                        self.trainer_comm = symm.TrainerComm(self.trainer_group, self.device, self.layout, self.C)
-                    self.weight_sync = symm.WeightSync(self.world_group, self.device, self.layout, self.C, self.trainer_ranks,
-                                                       self.infer_ranks)
+                    # every rank allocates every symmetric buffer, in the same order, over the WORLD group
+                    self.plane = symm.SymmetricPlane(self.device, self.layout, self.C, self.trainer_ranks, self.infer_ranks)
+                    self.trainer_comm = self.plane.trainer_comm()
+                    self.weight_sync = self.plane.weight_sync()
                 except Exception as e:
                     if config.comm_backend == "peer":
                         raise

@@ -66,20 +66,28 @@ def alloc_symmetric(numel: int, dtype: torch.dtype, device: torch.device, group:
 
 
 class PeerGroup:
-    """Flags + barrier over one process group."""
+    """Epoch flags + device-side barrier among ``members`` (global ranks). The flag words live in a symmetric buffer
+    allocated over the WORLD group: symmetric allocations are always made by every rank of the job, in the same
+    order, so that no rank waits in a rendezvous that others never enter; sub-groups are index subsets of it."""
 
-    def __init__(self, group: Any, device: torch.device, C: Any):
-        self.group, self.device, self.C = group, device, C
-        self.rank = dist.get_rank(group)
-        self.world = dist.get_world_size(group)
-        self.flags = alloc_symmetric(64, torch.int64, device, group)
+    def __init__(self, flags: SymmetricBuffer, members: Sequence[int], my_global_rank: int, device: torch.device, C: Any,
+                 slot_base: int = 0):
+        self.members = list(members)
+        self.is_member = my_global_rank in self.members
+        self.rank = self.members.index(my_global_rank) if self.is_member else -1
+        self.world = len(self.members)
+        self.C, self.device = C, device
+        # every member's flag block starts slot_base words into its flag buffer (8 bytes per word)
+        self.ptrs = [flags.peer_ptrs[r] + 8 * slot_base for r in self.members]
         self.epoch = 0
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
 
     def barrier(self) -> None:
         """Enqueues a device-side barrier on the current stream (no host synchronisation)."""
+        if not self.is_member:
+            return
         self.epoch += 1
-        self.C.flag_barrier(self.flags.peer_ptrs, self.rank, self.epoch, WAIT_BUDGET_S, self.status)
+        self.C.flag_barrier(self.ptrs, self.rank, self.epoch, WAIT_BUDGET_S, self.status)
 
     def check(self) -> None:
         code = int(self.status.item())
@@ -88,25 +96,56 @@ class PeerGroup:
             raise RuntimeError(f"peer barrier / flag wait ran out (status {code}): a rank of the group did not arrive")
 
 
-class TrainerComm:
-    """Peer-memory gradient reduce-scatter, norm exchange and AdamW + parameter publish for the trainer group."""
+class SymmetricPlane:
+    """All symmetric buffers of a job, allocated collectively over the WORLD group by every rank in a fixed order."""
 
-    def __init__(self, group: Any, device: torch.device, layout: Any, C: Any):
-        self.pg = PeerGroup(group, device, C)
-        self.layout, self.C, self.device = layout, C, device
+    def __init__(self, device: torch.device, layout: Any, C: Any, trainer_ranks: Sequence[int], infer_ranks: Sequence[int],
+                 world_group: Any = None):
+        self.device, self.layout, self.C = device, layout, C
+        self.group = world_group if world_group is not None else dist.group.WORLD
+        self.my_rank = dist.get_rank()
+        self.trainer_ranks, self.infer_ranks = list(trainer_ranks), list(infer_ranks)
+        need_train = len(self.trainer_ranks) > 1
+        self.flags = alloc_symmetric(128, torch.int64, device, self.group)          # [0,64): trainer barrier, [64,128): world
+        self.norm_tab = alloc_symmetric(64, torch.float32, device, self.group)
+        self.infer_params = alloc_symmetric(layout.total, torch.bfloat16, device, self.group)
+        self.train_params = alloc_symmetric(layout.total, torch.bfloat16, device, self.group) if need_train else None
+        self.grads = alloc_symmetric(layout.total, torch.float32, device, self.group) if need_train else None
+
+    def trainer_comm(self) -> Optional["TrainerComm"]:
+        if self.grads is None or self.my_rank not in self.trainer_ranks:
+            return None
+        return TrainerComm(self)
+
+    def weight_sync(self) -> "WeightSync":
+        return WeightSync(self)
+
+
+class TrainerComm:
+    """Peer-memory gradient reduce-scatter, norm exchange and AdamW + parameter publish for the trainer ranks."""
+
+    def __init__(self, plane: SymmetricPlane):
+        self.plane = plane
+        self.layout, self.C, self.device = plane.layout, plane.C, plane.device
+        self.pg = PeerGroup(plane.flags, plane.trainer_ranks, plane.my_rank, plane.device, plane.C, slot_base=0)
         self.rank, self.world = self.pg.rank, self.pg.world
-        self.grads = alloc_symmetric(layout.total, torch.float32, device, group)
-        self.params = alloc_symmetric(layout.total, torch.bfloat16, device, group)
-        self.norm_tab = alloc_symmetric(64, torch.float32, device, group)
-        self.norm_local = torch.zeros(1, dtype=torch.float32, device=device)
+        tr = plane.trainer_ranks
+        self.grad_ptrs = [plane.grads.peer_ptrs[r] for r in tr]
+        self.param_ptrs = [plane.train_params.peer_ptrs[r] for r in tr]
+        self.norm_ptrs = [plane.norm_tab.peer_ptrs[r] for r in tr]
+        self.norm_local = torch.zeros(1, dtype=torch.float32, device=plane.device)
 
     @property
     def param_buffer(self) -> torch.Tensor:
-        return self.params.local
+        return self.plane.train_params.local
 
     @property
     def grad_buffer(self) -> torch.Tensor:
-        return self.grads.local
+        return self.plane.grads.local
+
+    @property
+    def norm_partials(self) -> torch.Tensor:
+        return self.plane.norm_tab.local[: self.world]
 
     def reduce_scatter(self, grad_shard: torch.Tensor) -> None:
         """grad_shard <- sum over ranks of this rank's slice of every unit; norm partial published to all peers."""
@@ -114,17 +153,17 @@ class TrainerComm:
         self.pg.barrier()  # every rank's backward has finished and its gradients are visible
         self.norm_local.zero_()
         for u, (lo, gs, ln) in enumerate(L.local_to_global_ranges(self.rank)):
-            C.rs_pull_sumsq(self.grads.peer_ptrs, self.rank, gs, lo, ln, grad_shard, self.norm_local)
-        C.publish_norm(self.norm_local, self.norm_tab.peer_ptrs, self.rank)
+            C.rs_pull_sumsq(self.grad_ptrs, self.rank, gs, lo, ln, grad_shard, self.norm_local)
+        C.publish_norm(self.norm_local, self.norm_ptrs, self.rank)
         self.pg.barrier()  # all partials have landed; all peers are done reading my gradient buffer
-        self.grads.local.zero_()
+        self.grad_buffer.zero_()
 
     def adamw_and_publish(self, master, exp_avg, exp_avg_sq, grad_shard, lr, beta1, beta2, eps, wd, step, max_norm,
                           extra_dst_ptrs: Sequence[int] = ()) -> torch.Tensor:
         """Returns the device tensor holding the per-rank squared-norm partials (sum = global squared norm)."""
         C, L = self.C, self.layout
-        dsts = list(self.params.peer_ptrs) + list(extra_dst_ptrs)
-        partials = self.norm_tab.local[: self.world]
+        dsts = list(self.param_ptrs) + list(extra_dst_ptrs)
+        partials = self.norm_partials
         for u, (lo, gs, ln) in enumerate(L.local_to_global_ranges(self.rank)):
             C.adamw_push(master, exp_avg, exp_avg_sq, grad_shard, lo, gs, ln, lr, beta1, beta2, eps, wd, step, 1.0, partials,
                          max_norm, dsts)
@@ -133,28 +172,31 @@ class TrainerComm:
 
 
 class WeightSync:
-    """Trainer shards -> inference parameter buffers over a group that spans trainer and inference ranks."""
+    """Trainer shards -> inference parameter buffers; barriers span every rank of the job."""
 
-    def __init__(self, world_group: Any, device: torch.device, layout: Any, C: Any, trainer_ranks: Sequence[int],
-                 infer_ranks: Sequence[int]):
-        self.pg = PeerGroup(world_group, device, C)
-        self.layout, self.C = layout, C
-        self.trainer_ranks, self.infer_ranks = list(trainer_ranks), list(infer_ranks)
-        self.infer_params = alloc_symmetric(layout.total, torch.bfloat16, device, world_group)
+    def __init__(self, plane: SymmetricPlane):
+        self.plane = plane
+        self.layout, self.C = plane.layout, plane.C
+        self.trainer_ranks, self.infer_ranks = plane.trainer_ranks, plane.infer_ranks
+        world = list(range(dist.get_world_size()))
+        self.pg = PeerGroup(plane.flags, world, plane.my_rank, plane.device, plane.C, slot_base=64)
+        self.dst_ptrs = [plane.infer_params.peer_ptrs[r] for r in self.infer_ranks]
 
     @property
     def buffer(self) -> torch.Tensor:
-        return self.infer_params.local
+        return self.plane.infer_params.local
 
     def push(self, src_params: Optional[torch.Tensor], trainer_index: Optional[int]) -> None:
-        """Collective over the world group. Trainer ranks pass their resident bf16 parameters and their index in the
-        trainer group; the others pass None and only take part in the barriers."""
+        """Collective over all ranks. Trainer ranks pass their resident bf16 parameters and their index among the
+        trainers; the others pass None and only take part in the barriers."""
         self.pg.barrier()  # inference ranks are idle (paused by the orchestrator) and trainers finished their step
         if src_params is not None and trainer_index is not None:
-            dsts = [self.infer_params.peer_ptrs[r] for r in self.infer_ranks]
+            t = len(self.trainer_ranks)
             for u in range(len(self.layout.unit_ranges)):
-                s, e = self.layout.shard_range(u, trainer_index)
-                self.C.weight_push(src_params, s, s, e - s, dsts)
+                s, e = self.layout.unit_ranges[u]
+                n = (e - s) // t
+                a = s + trainer_index * n
+                self.C.weight_push(src_params, a, a, n, self.dst_ptrs)
         self.pg.barrier()  # all shards have landed everywhere
 
 

@@ -25,24 +25,42 @@ def _worker(rank, world, port, q):
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world)
+    trainer_group = dist.new_group(list(range(world)) if world == 2 else list(range(world - 1)))
     try:
         C = native()
         cfg = PRESETS["tiny128"]
-        layout = ParamLayout(cfg, shard_world=world)
-        group = dist.group.WORLD
-        comm = symm.TrainerComm(group, dev, layout, C)
+        # trainers = every rank but the last when there are more than two GPUs (exercises the sub-group indexing)
+        trainers = list(range(world)) if world == 2 else list(range(world - 1))
+        layout = ParamLayout(cfg, shard_world=len(trainers))
+        plane = symm.SymmetricPlane(dev, layout, C, trainer_ranks=trainers, infer_ranks=list(range(world)))
+        comm = plane.trainer_comm()
+        ws = plane.weight_sync()
+        if comm is None:  # pure inference rank: takes part in the weight push only
+            ws.push(None, None)
+            torch.cuda.synchronize()
+            ws.pg.check()
+            full = torch.empty(layout.total, dtype=torch.bfloat16, device=dev)
+            dist.broadcast(full, src=0)
+            assert torch.equal(ws.buffer, full), "pushed weights differ on the inference rank"
+            dist.barrier()
+            x = torch.ones(4, device=dev)
+            dist.all_reduce(x)
+            q.put((rank, "ok"))
+            return
+        tgroup_world = len(trainers)
         # ---- reduce-scatter + norm ----
         g = torch.Generator(device=dev).manual_seed(100 + rank)
         comm.grad_buffer.copy_(torch.randn(layout.total, device=dev, generator=g))
         full = comm.grad_buffer.clone()
-        dist.all_reduce(full)
+        tg = trainer_group
+        dist.all_reduce(full, group=tg)
         shard = torch.zeros(layout.shard_numel(), device=dev)
         comm.reduce_scatter(shard)
         torch.cuda.synchronize()
         comm.pg.check()
         want = torch.cat([full[gs:gs + ln] for lo, gs, ln in layout.local_to_global_ranges(rank)])
         assert torch.allclose(shard, want, rtol=1e-5, atol=1e-5), "reduce-scatter mismatch"
-        norm_sq = comm.norm_tab.local[:world].sum().item()
+        norm_sq = comm.norm_partials.sum().item()
         assert abs(norm_sq - full.double().pow(2).sum().item()) / full.double().pow(2).sum().item() < 1e-4
         assert float(comm.grad_buffer.abs().max()) == 0.0  # zeroed for the next accumulation
         # ---- AdamW + publish: every rank's parameter buffer equals the gathered bf16 shards ----
@@ -51,10 +69,10 @@ def _worker(rank, world, port, q):
         comm.adamw_and_publish(master, m, v, shard.clone(), 1e-2, 0.9, 0.999, 1e-8, 0.0, 1, 1.0)
         torch.cuda.synchronize()
         comm.pg.check()
-        gathered = [torch.empty_like(master) for _ in range(world)]
-        dist.all_gather(gathered, master)
+        gathered = [torch.empty_like(master) for _ in range(tgroup_world)]
+        dist.all_gather(gathered, master, group=tg)
         ref = torch.zeros(layout.total, device=dev)
-        for r in range(world):
+        for r in range(tgroup_world):
             for lo, gs, ln in layout.local_to_global_ranges(r):
                 ref[gs:gs + ln] = gathered[r][lo:lo + ln]
         assert torch.equal(comm.param_buffer, ref.to(torch.bfloat16)), "published parameters differ"
@@ -62,16 +80,17 @@ def _worker(rank, world, port, q):
         moved = (master - (rank + 1)).abs()
         assert ((moved - 1e-2).abs() < 1e-4).float().mean().item() > 0.98  # near-zero gradients move less
         # ---- weight push to inference buffers: bit-exact ----
-        ws = symm.WeightSync(group, dev, layout, C, trainer_ranks=list(range(world)), infer_ranks=list(range(world)))
-        ws.push(comm.param_buffer, rank)
+        ws.push(comm.param_buffer, comm.rank)
         torch.cuda.synchronize()
         ws.pg.check()
         assert torch.equal(ws.buffer, comm.param_buffer), "pushed weights differ"
+        if world > 2:
+            dist.broadcast(comm.param_buffer.clone() if rank == 0 else torch.empty(layout.total, dtype=torch.bfloat16, device=dev), src=0)
         # ---- a barrier partner that never arrives: bounded wait -> error status, context still usable ----
         dist.barrier()
         symm_budget = symm.WAIT_BUDGET_S
         symm.WAIT_BUDGET_S = 0.3
-        pg = symm.PeerGroup(group, dev, C)
+        pg = symm.PeerGroup(plane.flags, list(range(world)), rank, dev, C, slot_base=100)
         if rank == 0:
             pg.barrier()  # rank 1 does not join this one
             torch.cuda.synchronize()
