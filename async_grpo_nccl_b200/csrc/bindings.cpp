@@ -69,6 +69,16 @@ void gemm_bf16(const Tensor& a, const Tensor& b, Tensor& d, bool a_mn, bool b_mn
                           accumulate, opt_ptr<int>(status), num_sms(), cur_stream(), opt_ptr<void>(residual), ldr);
 }
 
+// Runs the skinny split-K GEMM with its phase tracer on; returns false when the shape is not served by that kernel.
+bool gemm_skinny_trace(const Tensor& a, const Tensor& b, Tensor& d, Tensor& trace) {
+  check_bf16(a, "a"); check_bf16(b, "b"); check_bf16(d, "d");
+  TORCH_CHECK(trace.is_cuda() && trace.scalar_type() == torch::kInt64 && trace.numel() >= 16, "trace: int64[16] cuda");
+  const c10::cuda::CUDAGuard guard(a.device());
+  return agrpo::launch_gemm_skinny(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), d.data_ptr(), d.stride(0), (int)a.size(0),
+                                   (int)b.size(0), (int)a.size(1), nullptr, nullptr, 0, nullptr, num_sms(), cur_stream(),
+                                   reinterpret_cast<long long*>(trace.data_ptr<int64_t>()));
+}
+
 void embedding_fwd(const Tensor& ids, const Tensor& table, Tensor& out) {
   check_i32(ids, "ids"); check_bf16(table, "table"); check_bf16(out, "out");
   TORCH_CHECK(table.is_contiguous() && out.is_contiguous() && table.size(1) % 8 == 0, "embedding_fwd layout");
@@ -365,6 +375,101 @@ void flag_barrier(const PtrList& flag_ptrs, int64_t my_rank, int64_t epoch, doub
   agrpo::launch_flag_barrier(lptr(flag_ptrs), (int)flag_ptrs.size(), (int)my_rank, (unsigned long long)epoch, budget_s,
                              status.data_ptr<int>(), cur_stream());
 }
+agrpo::GatherArgs gather_args(const PtrList& src_ptrs, int64_t my_rank, Tensor& staging, int64_t n_per_owner, Tensor& flags,
+                              int64_t epoch, int64_t chunk_elems) {
+  check_bf16(staging, "gather staging");
+  TORCH_CHECK(staging.is_contiguous(), "gather: staging must be contiguous");
+  TORCH_CHECK(flags.is_cuda() && flags.scalar_type() == torch::kInt64 && flags.is_contiguous(), "gather: flags int64 cuda");
+  const int64_t world = (int64_t)src_ptrs.size();
+  TORCH_CHECK(world >= 1 && world <= 8, "gather: 1..8 owners");
+  TORCH_CHECK(n_per_owner > 0 && n_per_owner % 8 == 0 && chunk_elems > 0 && chunk_elems % 8 == 0, "gather: sizes must be multiples of 8");
+  TORCH_CHECK(staging.numel() >= world * n_per_owner, "gather: staging too small");
+  TORCH_CHECK(flags.numel() >= (world * n_per_owner + chunk_elems - 1) / chunk_elems, "gather: too few flags");
+  for (auto p : src_ptrs) TORCH_CHECK(p != 0 && (p & 15) == 0, "gather: shard pointers must be 16-byte aligned");
+  agrpo::GatherArgs g{};
+  for (int64_t r = 0; r < world; ++r) g.src[r] = reinterpret_cast<const void*>(src_ptrs[r]);
+  g.dst = staging.data_ptr();
+  g.n_per_owner = n_per_owner;
+  g.world = (int)world;
+  g.my_rank = (int)my_rank;
+  g.flags = flags.data_ptr();
+  g.epoch = (unsigned long long)epoch;
+  g.chunk_elems = (int)chunk_elems;
+  return g;
+}
+// d = a . b^T (+ bias, + residual) with an all-gather of one sharded unit in the same launch. When b is a view of
+// `staging` the GEMM consumes what the launch gathers; otherwise the gather is a prefetch for later launches.
+void ag_gemm(const Tensor& a, const Tensor& b, Tensor& d, bool a_mn, bool b_mn, const OptTensor& bias, bool accumulate,
+             const OptTensor& status, const OptTensor& residual, const PtrList& src_ptrs, int64_t my_rank, Tensor& staging,
+             int64_t n_per_owner, Tensor& flags, int64_t epoch, int64_t chunk_elems, int64_t n_copy) {
+  check_bf16(a, "ag_gemm a"); check_bf16(b, "ag_gemm b");
+  TORCH_CHECK(d.is_cuda() && (d.scalar_type() == torch::kBFloat16 || d.scalar_type() == torch::kFloat32), "ag_gemm d");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && d.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && d.stride(1) == 1, "ag_gemm: 2-D, inner stride 1");
+  const c10::cuda::CUDAGuard guard(a.device());
+  const int64_t M = a_mn ? a.size(1) : a.size(0), K = a_mn ? a.size(0) : a.size(1);
+  const int64_t N = b_mn ? b.size(1) : b.size(0), Kb = b_mn ? b.size(0) : b.size(1);
+  TORCH_CHECK(K == Kb && d.size(0) == M && d.size(1) == N && M > 0 && N > 0 && K > 0, "ag_gemm: shape mismatch");
+  TORCH_CHECK(a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0, "ag_gemm: row pitch must be a multiple of 8 elements");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(a.data_ptr()) & 15) == 0 && (reinterpret_cast<uintptr_t>(b.data_ptr()) & 15) == 0, "ag_gemm: 16-byte alignment");
+  if (status.has_value() && status->defined()) check_i32(*status, "ag_gemm status");
+  long long ldr = 0;
+  if (residual.has_value() && residual->defined()) { check_bf16(*residual, "ag_gemm residual"); ldr = residual->stride(0); }
+  agrpo::GatherArgs g = gather_args(src_ptrs, my_rank, staging, n_per_owner, flags, epoch, chunk_elems);
+  const char* sb = reinterpret_cast<const char*>(staging.data_ptr());
+  const char* bb = reinterpret_cast<const char*>(b.data_ptr());
+  long long b_off = -1;
+  if (bb >= sb && bb < sb + staging.numel() * 2) b_off = (bb - sb) / 2;
+  const bool ok = agrpo::launch_ag_gemm_bf16(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), d.data_ptr(), d.stride(0), (int)M,
+                                             (int)N, (int)K, a_mn, b_mn, opt_ptr<void>(bias), 1.f, d.scalar_type() == torch::kFloat32,
+                                             accumulate, opt_ptr<int>(status), num_sms(), cur_stream(), opt_ptr<void>(residual), ldr,
+                                             g, (int)n_copy, b_off);
+  TORCH_CHECK(ok, "ag_gemm: arguments not served");
+}
+agrpo::ScatterArgs scatter_args(const PtrList& dst_ptrs, int64_t n_per_owner) {
+  TORCH_CHECK(dst_ptrs.size() >= 1 && dst_ptrs.size() <= 8, "scatter: 1..8 owners");
+  TORCH_CHECK(n_per_owner > 0 && n_per_owner % 128 == 0, "scatter: n_per_owner must be a positive multiple of 128");
+  agrpo::ScatterArgs sc{};
+  for (size_t r = 0; r < dst_ptrs.size(); ++r) {
+    TORCH_CHECK(dst_ptrs[r] != 0 && (dst_ptrs[r] & 15) == 0, "scatter: shard pointers must be 16-byte aligned");
+    sc.dst[r] = reinterpret_cast<void*>(dst_ptrs[r]);
+  }
+  sc.n_per_owner = n_per_owner;
+  sc.world = (int)dst_ptrs.size();
+  return sc;
+}
+// owners' gradient shards += op(a) . op(b)^T, the [M, N] result living unit_rel elements into an evenly sharded unit
+// with row pitch ldd (see ScatterReduceEpilogue).
+void gemm_rs(const Tensor& a, const Tensor& b, bool a_mn, bool b_mn, double alpha, const PtrList& dst_ptrs, int64_t n_per_owner,
+             int64_t unit_rel, int64_t ldd, const OptTensor& status) {
+  check_bf16(a, "gemm_rs a"); check_bf16(b, "gemm_rs b");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1, "gemm_rs: 2-D, inner stride 1");
+  const c10::cuda::CUDAGuard guard(a.device());
+  const int64_t M = a_mn ? a.size(1) : a.size(0), K = a_mn ? a.size(0) : a.size(1);
+  const int64_t N = b_mn ? b.size(1) : b.size(0), Kb = b_mn ? b.size(0) : b.size(1);
+  TORCH_CHECK(K == Kb && M > 0 && N > 0 && K > 0 && ldd >= N, "gemm_rs: shape mismatch");
+  TORCH_CHECK(a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0, "gemm_rs: row pitch must be a multiple of 8 elements");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(a.data_ptr()) & 15) == 0 && (reinterpret_cast<uintptr_t>(b.data_ptr()) & 15) == 0, "gemm_rs: 16-byte alignment");
+  if (status.has_value() && status->defined()) check_i32(*status, "gemm_rs status");
+  const agrpo::ScatterArgs sc = scatter_args(dst_ptrs, n_per_owner);
+  TORCH_CHECK(agrpo::launch_gemm_rs_bf16(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), (int)M, (int)N, (int)K, a_mn, b_mn,
+                                         (float)alpha, sc, unit_rel, ldd, opt_ptr<int>(status), num_sms(), cur_stream()),
+              "gemm_rs: arguments not served (offsets must be multiples of 4 and inside the unit)");
+}
+void scatter_add_f32(Tensor& src, int64_t unit_rel, const PtrList& dst_ptrs, int64_t n_per_owner, bool zero_src) {
+  check_f32(src, "scatter_add src");
+  TORCH_CHECK(src.is_contiguous() && unit_rel >= 0 && unit_rel % 4 == 0, "scatter_add: contiguous source, offset multiple of 4");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(src.data_ptr()) & 15) == 0, "scatter_add: 16-byte alignment");
+  TORCH_CHECK(unit_rel + src.numel() <= n_per_owner * (int64_t)dst_ptrs.size(), "scatter_add: range exceeds the unit");
+  const c10::cuda::CUDAGuard guard(src.device());
+  agrpo::launch_scatter_add_f32(src.data_ptr<float>(), src.numel(), unit_rel, scatter_args(dst_ptrs, n_per_owner), zero_src,
+                                cur_stream());
+}
+void unit_gather(const PtrList& src_ptrs, int64_t my_rank, Tensor& staging, int64_t n_per_owner, Tensor& flags, int64_t epoch,
+                 int64_t chunk_elems, int64_t n_ctas) {
+  const c10::cuda::CUDAGuard guard(staging.device());
+  agrpo::GatherArgs g = gather_args(src_ptrs, my_rank, staging, n_per_owner, flags, epoch, chunk_elems);
+  TORCH_CHECK(agrpo::launch_unit_gather(g, (int)n_ctas, cur_stream()), "unit_gather: arguments not served");
+}
 void weight_push(const Tensor& src, int64_t local_off, int64_t global_off, int64_t n, const PtrList& dst_ptrs) {
   TORCH_CHECK(src.is_cuda() && src.is_contiguous() && (src.scalar_type() == torch::kFloat32 || src.scalar_type() == torch::kBFloat16), "weight_push: src");
   TORCH_CHECK(local_off >= 0 && local_off + n <= src.numel() && local_off % 8 == 0 && global_off % 8 == 0, "weight_push: range");
@@ -507,6 +612,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_bf16", &gemm_bf16, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("a_mn") = false,
         py::arg("b_mn") = false, py::arg("bias") = py::none(), py::arg("alpha") = 1.0, py::arg("accumulate") = false,
         py::arg("status") = py::none(), py::arg("residual") = py::none());
+  m.def("gemm_skinny_trace", &gemm_skinny_trace);
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
   m.def("rmsnorm_fwd", &rmsnorm_fwd, py::arg("x"), py::arg("w"), py::arg("y"), py::arg("rstd") = py::none(),
@@ -554,6 +660,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("wait_flag_probe", &wait_flag_probe);
   m.def("flag_barrier", &flag_barrier);
   m.def("weight_push", &weight_push);
+  m.def("ag_gemm", &ag_gemm, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("a_mn") = false, py::arg("b_mn") = false,
+        py::arg("bias") = py::none(), py::arg("accumulate") = false, py::arg("status") = py::none(),
+        py::arg("residual") = py::none(), py::arg("src_ptrs"), py::arg("my_rank"), py::arg("staging"),
+        py::arg("n_per_owner"), py::arg("flags"), py::arg("epoch"), py::arg("chunk_elems") = 262144, py::arg("n_copy") = 16);
+  m.def("gemm_rs", &gemm_rs, py::arg("a"), py::arg("b"), py::arg("a_mn"), py::arg("b_mn"), py::arg("alpha"), py::arg("dst_ptrs"),
+        py::arg("n_per_owner"), py::arg("unit_rel"), py::arg("ldd"), py::arg("status") = py::none());
+  m.def("scatter_add_f32", &scatter_add_f32, py::arg("src"), py::arg("unit_rel"), py::arg("dst_ptrs"), py::arg("n_per_owner"),
+        py::arg("zero_src") = true);
+  m.def("unit_gather", &unit_gather, py::arg("src_ptrs"), py::arg("my_rank"), py::arg("staging"), py::arg("n_per_owner"),
+        py::arg("flags"), py::arg("epoch"), py::arg("chunk_elems") = 262144, py::arg("n_ctas") = 32);
   m.def("rs_pull_sumsq", &rs_pull_sumsq);
   m.def("publish_norm", &publish_norm);
   m.def("adamw_push", &adamw_push);

@@ -32,7 +32,13 @@ struct SkParams {
   const __nv_bfloat16* residual;
   long long ldr;
   int* status;
+  long long* trace;  // optional: clock64 stamps of the phases of cluster 0 / CTA 0 (16 slots), nullptr = off
 };
+
+#define SK_STAMP(slot)                                                         \
+  do {                                                                         \
+    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0) p.trace[slot] = clock64(); \
+  } while (0)
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -70,7 +76,14 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
 }
 __device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
   float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  // no memory clobber: the loads of one reduction step are independent and must be allowed to overlap; ordering
+  // against the hand-off is given by the acquire wait (a volatile asm with a memory clobber) that precedes them
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
   return v;
 }
 __device__ __forceinline__ void fence_cluster_barrier_init() {
@@ -95,7 +108,8 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float* part = reinterpret_cast<float*>(smem + STAGES * kStageBytes);  // [BN][MT * 128] (column-major tile)
+  // partial tile as float4 groups of 4 consecutive columns: part4[col / 4][row] (16-byte, conflict-free accesses)
+  float4* part = reinterpret_cast<float4*>(smem + STAGES * kStageBytes);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(part) + (size_t)BN * MT * kBM * 4);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* acc_bar = empty_bar + STAGES;
@@ -105,10 +119,12 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t crank = cluster_ctarank();
+  if (threadIdx.x == 0) SK_STAMP(0);
   const int n0 = blockIdx.y * BN;
   const int num_kb = (p.K + kBK - 1) / kBK;
   const int kb0 = (int)((long long)num_kb * crank / S);
   const int kb1 = (int)((long long)num_kb * (crank + 1) / S);
+  const int n_pre = (kb1 - kb0) < STAGES ? (kb1 - kb0) : STAGES;  // loads issued during the prologue
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -119,8 +135,16 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
     mbar_init(parts_ready, S);
     mbar_init(reads_done, S);
     fence_cluster_barrier_init();
-    tma_prefetch_desc(&tmA);
-    tma_prefetch_desc(&tmB);
+    // The first loads do not depend on anything another thread or CTA sets up: issue them before the CTA / cluster
+    // synchronisation so that the ~2 us cold first-load latency overlaps the rest of the prologue.
+    for (int i = 0; i < n_pre; ++i) {
+      uint8_t* sa = smem + i * kStageBytes;
+      mbar_expect_tx(&full_bar[i], kStageBytes);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) tma_load_2d(sa + mt * (kBM * kBK * 2), &tmA, &full_bar[i], (kb0 + i) * kBK, mt * kBM);
+      tma_load_2d(sa + kABytes, &tmB, &full_bar[i], (kb0 + i) * kBK, n0);
+    }
+    SK_STAMP(3);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -128,15 +152,17 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
   }
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) SK_STAMP(1);
   cluster_sync_all();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) SK_STAMP(2);
 
   if (warp == 0) {
     if (elect_one()) {
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int kb = kb0; kb < kb1; ++kb) {
+      int stage = n_pre == STAGES ? 0 : n_pre;
+      uint32_t phase = n_pre == STAGES ? 1 : 0;
+      for (int kb = kb0 + n_pre; kb < kb1; ++kb) {
         if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
           report_status(p.status, kStatusWaitEmptyTimeout);
           break;
@@ -165,6 +191,7 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
           break;
         }
         tc_fence_after();
+        if (kb == kb0) SK_STAMP(4);
         const uint32_t sa = smem_u32(smem + stage * kStageBytes);
         const uint32_t sb = sa + kABytes;
 #pragma unroll
@@ -181,6 +208,7 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
         }
       }
       if (ok) tc_commit(acc_bar);
+      SK_STAMP(5);
     }
   } else {
     // ---- epilogue warps: TMEM -> own shared memory (column-major), cluster hand-off, slice reduction ----
@@ -195,6 +223,7 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
       }
     }
     tc_fence_after();
+    if (threadIdx.x == 64) SK_STAMP(6);
 #pragma unroll 1
     for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll 1
@@ -208,16 +237,20 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
           for (int i = 0; i < 32; ++i) r[i] = 0u;
         }
 #pragma unroll
-        for (int i = 0; i < 32; ++i) part[(size_t)(c * 32 + i) * (MT * kBM) + mt * kBM + row_in_tile] = __uint_as_float(r[i]);
+        for (int i = 0; i < 32; i += 4)
+          part[(size_t)(c * 8 + i / 4) * (MT * kBM) + mt * kBM + row_in_tile] =
+              make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
       }
     }
     // all 128 epilogue threads have written; one thread tells every CTA of the cluster (release at cluster scope)
     asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (threadIdx.x == 64) SK_STAMP(7);
     if (warp == 2 && lane < S) mbar_arrive_remote(mapa_shared(smem_u32(parts_ready), lane));
     if (!mbar_wait_cluster(parts_ready, 0)) {
       report_status(p.status, kStatusBarrierTimeout);
       ok = false;
     }
+    if (threadIdx.x == 64) SK_STAMP(8);
     // reduce my column slice over all peers
     const int w = BN / S;              // columns per CTA (BN is a multiple of 8 * S by construction)
     const int c0 = (int)crank * w;
@@ -228,14 +261,22 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
         const int row = mt * kBM + row_in_tile;
 #pragma unroll 1
         for (int cb = 0; cb < w; cb += 8) {
+          float4 v[8][2];
+#pragma unroll
+          for (int peer = 0; peer < 8; ++peer) {
+            const uint32_t base = mapa_shared(part_addr, (uint32_t)(peer < S ? peer : 0));
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+              v[peer][i] = (peer < S) ? ld_dsmem_f32x4(base + (uint32_t)(((size_t)((c0 + cb) / 4 + i) * (MT * kBM) + row) * 16))
+                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
           float acc[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-          for (int peer = 0; peer < S; ++peer) {
-            const uint32_t base = mapa_shared(part_addr, (uint32_t)peer);
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-              acc[i] += ld_dsmem_f32(base + (uint32_t)(((size_t)(c0 + cb + i) * (MT * kBM) + row) * 4));
+          for (int peer = 0; peer < 8; ++peer) {
+            acc[0] += v[peer][0].x; acc[1] += v[peer][0].y; acc[2] += v[peer][0].z; acc[3] += v[peer][0].w;
+            acc[4] += v[peer][1].x; acc[5] += v[peer][1].y; acc[6] += v[peer][1].z; acc[7] += v[peer][1].w;
           }
           const int col = n0 + c0 + cb;
           if (row < p.M && col < p.N) {
@@ -268,8 +309,10 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
     }
     // tell every peer that I am done with its shared memory, then wait until everyone is done with mine
     asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (threadIdx.x == 64) SK_STAMP(9);
     if (warp == 2 && lane < S) mbar_arrive_remote(mapa_shared(smem_u32(reads_done), lane));
     if (!mbar_wait_cluster(reads_done, 0)) report_status(p.status, kStatusBarrierTimeout);
+    if (threadIdx.x == 64) SK_STAMP(10);
   }
 
   tc_fence_before();
@@ -278,6 +321,7 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (threadIdx.x == 0) SK_STAMP(11);
 }
 
 template <int BN, int MT, int STAGES>
@@ -308,7 +352,8 @@ void launch_sk(const CUtensorMap& ta, const CUtensorMap& tb, const SkParams& p, 
 
 // Returns false when the shape is not one this kernel serves (the caller then uses the general GEMM).
 bool launch_gemm_skinny(const void* a, long long lda, const void* b, long long ldb, void* d, long long ldd, int M, int N, int K,
-                        const void* bias, const void* residual, long long ldr, int* status, int num_sms, cudaStream_t stream) {
+                        const void* bias, const void* residual, long long ldr, int* status, int num_sms, cudaStream_t stream,
+                        long long* trace) {
   if (M > 256 || K < 512 || N < 64) return false;
   const int MT = M <= 128 ? 1 : 2;
   const int BN = MT == 1 ? 128 : 64;
@@ -327,6 +372,7 @@ bool launch_gemm_skinny(const void* a, long long lda, const void* b, long long l
   p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   p.ldr = ldr;
   p.status = status;
+  p.trace = trace;
   if (MT == 1) launch_sk<128, 1, 4>(ta, tb, p, S, n_tiles, stream);
   else         launch_sk<64, 2, 3>(ta, tb, p, S, n_tiles, stream);
   return true;

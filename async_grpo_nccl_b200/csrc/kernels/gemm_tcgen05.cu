@@ -7,24 +7,20 @@ namespace agrpo {
 
 namespace {
 
-template <int BN>
+template <int BN, class Epi, class Gather>
 void dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmShape& p,
-                    const StoreEpilogue& e, int sms, cudaStream_t s) {
-  if (!a_mn && !b_mn) return gemm_launch<BN, false, false>(ta, tb, p, e, sms, s);
-  if (!a_mn && b_mn) return gemm_launch<BN, false, true>(ta, tb, p, e, sms, s);
-  if (a_mn && b_mn) return gemm_launch<BN, true, true>(ta, tb, p, e, sms, s);
-  return gemm_launch<BN, true, false>(ta, tb, p, e, sms, s);
+                    const Epi& e, int sms, cudaStream_t s, const Gather& gj) {
+  if (!a_mn && !b_mn) return gemm_launch<BN, false, false>(ta, tb, p, e, sms, s, gj);
+  if (!a_mn && b_mn) return gemm_launch<BN, false, true>(ta, tb, p, e, sms, s, gj);
+  if (a_mn && b_mn) return gemm_launch<BN, true, true>(ta, tb, p, e, sms, s, gj);
+  return gemm_launch<BN, true, false>(ta, tb, p, e, sms, s, gj);
 }
 
-}  // namespace
-
-// d[M,N] = alpha * op(a) . op(b)^T (+ bias) (+ d); see launchers.h for the operand conventions.
-void launch_gemm_bf16(const void* a, long long lda, const void* b, long long ldb, void* d, long long ldd, int M, int N,
+template <class Gather>
+void launch_gemm_impl(const void* a, long long lda, const void* b, long long ldb, void* d, long long ldd, int M, int N,
                       int K, bool a_mn, bool b_mn, const void* bias, float alpha, bool out_fp32, bool accumulate,
-                      int* status, int num_sms, cudaStream_t stream, const void* residual, long long ldr) {
-  if (!a_mn && !b_mn && !out_fp32 && !accumulate && alpha == 1.f && M <= 256 &&
-      launch_gemm_skinny(a, lda, b, ldb, d, ldd, M, N, K, bias, residual, ldr, status, num_sms, stream))
-    return;
+                      int* status, int num_sms, cudaStream_t stream, const void* residual, long long ldr,
+                      const Gather& gj) {
   // Widest column tile that still yields about one work item per SM; the 64 / 32 wide tiles serve
   // skinny decode-time GEMMs (K-major operands only) where the weight stream must be spread over all SMs.
   const int tiles_m = (M + kGemmBM - 1) / kGemmBM;
@@ -56,10 +52,112 @@ void launch_gemm_bf16(const void* a, long long lda, const void* b, long long ldb
   e.alpha = alpha;
   e.out_fp32 = out_fp32 ? 1 : 0;
   e.accumulate = accumulate ? 1 : 0;
-  if (BN == 256) dispatch_major<256>(a_mn, b_mn, ta, tb, p, e, num_sms, stream);
-  else if (BN == 128) dispatch_major<128>(a_mn, b_mn, ta, tb, p, e, num_sms, stream);
-  else if (BN == 64) gemm_launch<64, false, false>(ta, tb, p, e, num_sms, stream);
-  else gemm_launch<32, false, false>(ta, tb, p, e, num_sms, stream);
+  if (BN == 256) dispatch_major<256>(a_mn, b_mn, ta, tb, p, e, num_sms, stream, gj);
+  else if (BN == 128) dispatch_major<128>(a_mn, b_mn, ta, tb, p, e, num_sms, stream, gj);
+  else if (BN == 64) gemm_launch<64, false, false>(ta, tb, p, e, num_sms, stream, gj);
+  else gemm_launch<32, false, false>(ta, tb, p, e, num_sms, stream, gj);
+}
+
+// Copies one sharded unit out of its owners' memory with no GEMM to ride on (the first unit of a pass).
+__global__ void __launch_bounds__(kGemmThreads) unit_gather_kernel(const GatherJob gj) {
+  gj.copy_role((int)blockIdx.x, nullptr);
+}
+
+}  // namespace
+
+// d[M,N] = alpha * op(a) . op(b)^T (+ bias) (+ d); see launchers.h for the operand conventions.
+void launch_gemm_bf16(const void* a, long long lda, const void* b, long long ldb, void* d, long long ldd, int M, int N,
+                      int K, bool a_mn, bool b_mn, const void* bias, float alpha, bool out_fp32, bool accumulate,
+                      int* status, int num_sms, cudaStream_t stream, const void* residual, long long ldr) {
+  if (!a_mn && !b_mn && !out_fp32 && !accumulate && alpha == 1.f && M <= 256 &&
+      launch_gemm_skinny(a, lda, b, ldb, d, ldd, M, N, K, bias, residual, ldr, status, num_sms, stream))
+    return;
+  launch_gemm_impl(a, lda, b, ldb, d, ldd, M, N, K, a_mn, b_mn, bias, alpha, out_fp32, accumulate, status, num_sms,
+                   stream, residual, ldr, NoGather{0});
+}
+
+namespace {
+GatherJob make_gather_job(const GatherArgs& g, int n_copy) {
+  GatherJob gj{};
+  gj.n_copy = n_copy;
+  for (int r = 0; r < g.world && r < GatherJob::kMaxOwners; ++r)
+    gj.src[r] = reinterpret_cast<const __nv_bfloat16*>(g.src[r]);
+  gj.dst = reinterpret_cast<__nv_bfloat16*>(g.dst);
+  gj.unit_elems = g.n_per_owner * g.world;
+  gj.n_per_owner = g.n_per_owner;
+  gj.world = g.world;
+  gj.my_rank = g.my_rank;
+  gj.flags = reinterpret_cast<unsigned long long*>(g.flags);
+  gj.epoch = g.epoch;
+  gj.chunk_elems = g.chunk_elems;
+  gj.b_unit_offset = -1;
+  gj.b_row_elems = 0;
+  gj.b_total_elems = 0;
+  return gj;
+}
+bool gather_args_ok(const GatherArgs& g) {
+  return g.world >= 1 && g.world <= GatherJob::kMaxOwners && g.n_per_owner > 0 && g.n_per_owner % 8 == 0 &&
+         g.chunk_elems > 0 && g.chunk_elems % 8 == 0 && g.dst && g.flags;
+}
+}  // namespace
+
+// GEMM with an all-gather job in the same launch (see GatherJob in gemm_tcgen05.cuh). `b_unit_offset` >= 0 says that
+// B lives inside the unit being gathered, at that element offset of the staging buffer: the producer warp then waits
+// for the chunks under each tile before it loads them. With b_unit_offset < 0 the job is a prefetch for later GEMMs.
+bool launch_ag_gemm_bf16(const void* a, long long lda, const void* b, long long ldb, void* d, long long ldd, int M,
+                         int N, int K, bool a_mn, bool b_mn, const void* bias, float alpha, bool out_fp32,
+                         bool accumulate, int* status, int num_sms, cudaStream_t stream, const void* residual,
+                         long long ldr, const GatherArgs& g, int n_copy, long long b_unit_offset) {
+  if (!gather_args_ok(g) || n_copy < 1 || n_copy > num_sms / 2) return false;
+  GatherJob gj = make_gather_job(g, n_copy);
+  if (b_unit_offset >= 0) {
+    gj.b_unit_offset = b_unit_offset;
+    gj.b_row_elems = ldb;
+    // an MN-major B is read across all of its rows by every tile: wait for the whole matrix
+    gj.b_total_elems = b_mn ? (long long)(K - 1) * ldb + N : 0;
+  }
+  launch_gemm_impl(a, lda, b, ldb, d, ldd, M, N, K, a_mn, b_mn, bias, alpha, out_fp32, accumulate, status, num_sms,
+                   stream, residual, ldr, gj);
+  return true;
+}
+
+// d_owner[flat] += alpha * op(a) . op(b)^T, every element added into the gradient shard of the rank that owns it.
+bool launch_gemm_rs_bf16(const void* a, long long lda, const void* b, long long ldb, int M, int N, int K, bool a_mn, bool b_mn,
+                         float alpha, const ScatterArgs& sc, long long unit_rel, long long ldd, int* status, int num_sms,
+                         cudaStream_t stream) {
+  if (sc.world < 1 || sc.world > ScatterReduceEpilogue::kMaxOwners || sc.n_per_owner <= 0 || sc.n_per_owner % 128 != 0 ||
+      unit_rel % 4 != 0 || ldd % 4 != 0 || unit_rel < 0 ||
+      unit_rel + (long long)(M - 1) * ldd + N > sc.n_per_owner * sc.world)
+    return false;
+  const int tiles_m = (M + kGemmBM - 1) / kGemmBM;
+  const int BN = ((long long)tiles_m * ((N + 255) / 256) >= 120) ? 256 : 128;
+  CUtensorMap ta, tb;
+  if (!a_mn) ta = make_tmap_2d(a, K, M, lda, 64, kGemmBM);
+  else       ta = make_tmap_2d(a, M, K, lda, 64, 64);
+  if (!b_mn) tb = make_tmap_2d(b, K, N, ldb, 64, BN);
+  else       tb = make_tmap_2d(b, N, K, ldb, 64, 64);
+  GemmShape p;
+  p.M = M; p.N = N; p.K = K;
+  p.group_n = 1;
+  p.status = status;
+  ScatterReduceEpilogue e;
+  for (int r = 0; r < ScatterReduceEpilogue::kMaxOwners; ++r)
+    e.dst[r] = r < sc.world ? reinterpret_cast<float*>(sc.dst[r]) : nullptr;
+  e.n_per_owner = sc.n_per_owner;
+  e.unit_rel = unit_rel;
+  e.ldd = ldd;
+  e.alpha = alpha;
+  if (BN == 256) dispatch_major<256>(a_mn, b_mn, ta, tb, p, e, num_sms, stream, NoGather{0});
+  else dispatch_major<128>(a_mn, b_mn, ta, tb, p, e, num_sms, stream, NoGather{0});
+  return true;
+}
+
+bool launch_unit_gather(const GatherArgs& g, int n_ctas, cudaStream_t stream) {
+  if (!gather_args_ok(g) || n_ctas < 1) return false;
+  GatherJob gj = make_gather_job(g, n_ctas);
+  unit_gather_kernel<<<n_ctas, kGemmThreads, 0, stream>>>(gj);
+  check_cuda(cudaGetLastError(), "unit_gather_kernel");
+  return true;
 }
 
 }  // namespace agrpo

@@ -124,6 +124,129 @@ struct GemmSmem {
   static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
 };
 
+// GEMM -> reduce-scatter in one kernel (FSDP / ZeRO-3 gradient path; replaces the per-block reduce-scatter that
+// FSDP2 issues after each block's backward, gpu_process_worker.py:415-418, 696-713). The fp32 result tile is not
+// stored locally: every element is added, with a vector `red` over NVLink, straight into the slice of the gradient
+// shard that its OWNER rank holds. The unit is sharded evenly in flat order, owner r holding elements
+// [r * n_per_owner, (r + 1) * n_per_owner) of the unit; `unit_rel` is where the weight matrix starts inside its unit.
+// Reductions from all ranks and all microbatches meet in the owner's shard; the only synchronisation is one barrier
+// before the optimizer reads it. Offsets and pitches are multiples of 4 elements and n_per_owner a multiple of 128,
+// so a 16-byte group never straddles two owners.
+struct ScatterReduceEpilogue {
+  static constexpr int kMaxOwners = 8;
+  float* dst[kMaxOwners];   // owner r's gradient shard, already offset to the unit's slice (peer addresses)
+  long long n_per_owner;
+  long long unit_rel;       // element offset of D[0, 0] inside the unit
+  long long ldd;            // row pitch of the weight matrix in elements
+  float alpha;
+
+  // selects instead of a dynamic index, which would copy the pointer table to local memory
+  __device__ __forceinline__ float* owner_base(int owner) const {
+    float* b = dst[0];
+#pragma unroll
+    for (int r = 1; r < kMaxOwners; ++r)
+      if (owner == r) b = dst[r];
+    return b;
+  }
+  __device__ __forceinline__ void item_begin(int, int, int) {}
+  __device__ __forceinline__ void item_end(int, int, int, int) {}
+  __device__ __forceinline__ void chunk(int row, int col0, const uint32_t (&r)[32], int M, int N) {
+    if (row >= M || col0 >= N) return;
+    const long long flat = unit_rel + static_cast<long long>(row) * ldd + col0;
+    int owner = static_cast<int>(flat / n_per_owner);
+    long long off = flat - static_cast<long long>(owner) * n_per_owner;
+    float* base = owner_base(owner);
+    if (col0 + 32 <= N) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        if (off >= n_per_owner) { off -= n_per_owner; base = owner_base(++owner); }
+        float* d = base + off;
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(d), "f"(__uint_as_float(r[i]) * alpha),
+                     "f"(__uint_as_float(r[i + 1]) * alpha), "f"(__uint_as_float(r[i + 2]) * alpha),
+                     "f"(__uint_as_float(r[i + 3]) * alpha)
+                     : "memory");
+        off += 4;
+      }
+    } else {
+      for (int i = 0; i < 32 && col0 + i < N; ++i) {
+        if (off >= n_per_owner) { off -= n_per_owner; base = owner_base(++owner); }
+        atomicAdd(base + off, __uint_as_float(r[i]) * alpha);
+        off += 1;
+      }
+    }
+  }
+};
+
+// Optional all-gather job fused into a GEMM launch (FSDP / ZeRO-3 parameter gather, the reference's FSDP2
+// all-gather before each block, gpu_process_worker.py:415-418). The first `n_copy` CTAs of the grid do not compute:
+// they pull the unit's shards out of every owner's memory over NVLink (plain peer loads) into a local staging
+// buffer, chunk by chunk in flat order, and publish a ready flag per chunk. The GEMM CTAs of the SAME launch wait
+// (bounded) for the chunks that cover the B rows of their tile before the first TMA load of that tile, so the
+// transfer overlaps the math tile by tile. A launch may also gather a unit that a later GEMM consumes (prefetch).
+struct NoGather {
+  static constexpr bool kEnabled = false;
+  int n_copy;
+};
+
+struct GatherJob {
+  static constexpr bool kEnabled = true;
+  static constexpr int kMaxOwners = 8;
+  int n_copy;                              // copier CTAs at the front of the grid (0: wait-only launch)
+  const __nv_bfloat16* src[kMaxOwners];    // owner r's slice of the unit (n_per_owner elements), peer addresses
+  __nv_bfloat16* dst;                      // local staging buffer of the whole unit
+  long long unit_elems;                    // world * n_per_owner
+  long long n_per_owner;
+  int world;
+  int my_rank;
+  unsigned long long* flags;               // [ceil(unit_elems / chunk_elems)] ready flags of dst
+  unsigned long long epoch;                // value that marks "ready" for this gather
+  int chunk_elems;                         // elements per flag (multiple of 8)
+  long long b_unit_offset;                 // element offset of the GEMM's B matrix inside the unit; < 0: B is not in the unit
+  long long b_row_elems;                   // row pitch of B in elements
+  long long b_total_elems;                 // > 0: every tile waits for [b_unit_offset, b_unit_offset + b_total_elems)
+
+  __device__ __forceinline__ void copy_role(int cta, int* status) const {
+    const long long n_chunks = (unit_elems + chunk_elems - 1) / chunk_elems;
+    for (long long c = cta; c < n_chunks; c += n_copy) {
+      const long long a = c * chunk_elems;
+      const long long b = (a + chunk_elems < unit_elems) ? a + chunk_elems : unit_elems;
+      for (long long i = a + (long long)threadIdx.x * 8; i < b; i += (long long)blockDim.x * 8) {
+        const int owner = (int)(i / n_per_owner);
+        const long long off = i - (long long)owner * n_per_owner;
+        const uint4 v = *reinterpret_cast<const uint4*>(src[owner] + off);
+        *reinterpret_cast<uint4*>(dst + i) = v;
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence();
+        asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(flags + c), "l"(epoch) : "memory");
+      }
+    }
+  }
+  // Called by the TMA-issuing thread before it loads B rows [n0, n0 + rows).
+  __device__ __forceinline__ bool wait_rows(int n0, int rows, int n_total) const {
+    if (b_unit_offset < 0) return true;
+    const int last_row = (n0 + rows < n_total ? n0 + rows : n_total);
+    const long long a = b_unit_offset + (b_total_elems > 0 ? 0 : (long long)n0 * b_row_elems);
+    const long long b = b_unit_offset + (b_total_elems > 0 ? b_total_elems : (long long)last_row * b_row_elems) - 1;
+    const long long c0 = a / chunk_elems, c1 = b / chunk_elems;
+    for (long long c = c0; c <= c1; ++c) {
+      unsigned long long v;
+      asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(flags + c) : "memory");
+      if (v >= epoch) continue;
+      const long long t0 = clock64();
+      while (true) {
+        asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(flags + c) : "memory");
+        if (v >= epoch) break;
+        if (clock64() - t0 > kWaitBudgetTicks) return false;
+        __nanosleep(100);
+      }
+    }
+    fence_proxy_async_all();  // staged by generic-proxy stores, read next by TMA (async proxy)
+    return true;
+  }
+};
+
 // Work-item order.
 //  group_n == 1: bands of 16 row-tiles, column-tile fastest across a band, so that the CTAs running at
 //                the same time share A and B tiles through L2.
@@ -152,10 +275,10 @@ __host__ __device__ inline int gemm_num_items(int M, int N, int BN, int group_n)
   return tiles_m * ((tiles_n + g - 1) / g);
 }
 
-template <int BN, bool A_MN, bool B_MN, class Epi>
+template <int BN, bool A_MN, bool B_MN, class Epi, class Gather = NoGather>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const GemmShape p, Epi epi) {
+                    const GemmShape p, Epi epi, const Gather gj) {
   using S = GemmSmem<BN>;
   constexpr int kStages = S::kStages;
   constexpr uint32_t kTmemCols = 2 * BN;
@@ -197,19 +320,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // with a gather job the first n_copy CTAs are copiers and the work items are spread over the others
+  const int first_cta = Gather::kEnabled ? gj.n_copy : 0;
+  const int my_cta = (int)blockIdx.x - first_cta;
+  const int cta_stride = (int)gridDim.x - first_cta;
 
-  if (warp == 0) {
+  if constexpr (Gather::kEnabled) {
+    if (my_cta < 0) gj.copy_role((int)blockIdx.x, p.status);
+  }
+  if (my_cta < 0) {
+    // copier CTA: nothing else to do
+  } else if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (elect_one()) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+      for (int item = my_cta; item < num_items && ok; item += cta_stride) {
         int tm, tn0, count;
         gemm_item_coords(item, tiles_m, tiles_n, p.group_n, tm, tn0, count);
         const int m0 = tm * kGemmBM;
         for (int t = 0; t < count && ok; ++t) {
           const int n0 = (tn0 + t) * BN;
+          if constexpr (Gather::kEnabled) {
+            if (!gj.wait_rows(n0, BN, p.N)) {
+              report_status(p.status, kStatusPeerFlagTimeout);
+              ok = false;
+              break;
+            }
+          }
           for (int kb = 0; kb < num_kb; ++kb) {
             if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
               report_status(p.status, kStatusWaitEmptyTimeout);
@@ -247,7 +386,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+      for (int item = my_cta; item < num_items && ok; item += cta_stride) {
         int tm, tn0, count;
         gemm_item_coords(item, tiles_m, tiles_n, p.group_n, tm, tn0, count);
         for (int t = 0; t < count && ok; ++t, ++local) {
@@ -290,7 +429,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32)
     int local = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+    for (int item = my_cta; item < num_items && ok; item += cta_stride) {
       int tm, tn0, count;
       gemm_item_coords(item, tiles_m, tiles_n, p.group_n, tm, tn0, count);
       const int row = tm * kGemmBM + quarter * 32 + lane;
@@ -330,11 +469,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 }
 
 // Host-side launch of the generic kernel with any epilogue functor.
-template <int BN, bool A_MN, bool B_MN, class Epi>
+template <int BN, bool A_MN, bool B_MN, class Epi, class Gather = NoGather>
 inline void gemm_launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmShape& p, const Epi& epi, int num_sms,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, const Gather& gj = Gather{0}) {
   using S = GemmSmem<BN>;
-  auto kernel = gemm_tcgen05_kernel<BN, A_MN, B_MN, Epi>;
+  auto kernel = gemm_tcgen05_kernel<BN, A_MN, B_MN, Epi, Gather>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
@@ -342,8 +481,11 @@ inline void gemm_launch(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
     configured = true;
   }
   const int items = gemm_num_items(p.M, p.N, BN, p.group_n);
-  const int grid = items < num_sms ? items : num_sms;
-  kernel<<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, p, epi);
+  // every CTA of the grid must be resident at once when CTAs wait on one another (copiers + workers <= SMs)
+  const int n_copy = Gather::kEnabled ? gj.n_copy : 0;
+  const int workers = items < num_sms - n_copy ? items : num_sms - n_copy;
+  const int grid = workers + n_copy;
+  kernel<<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, p, epi, gj);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string("gemm_tcgen05 launch: ") + cudaGetErrorString(e));
 }

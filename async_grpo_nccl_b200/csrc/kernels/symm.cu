@@ -79,6 +79,30 @@ __global__ void weight_push_kernel(const SrcT* __restrict__ src, long long local
   }
 }
 
+// dst[owner(i)][...] += src[i] for a local fp32 vector that sits unit_rel elements into an evenly sharded unit; the
+// source is zeroed afterwards when asked. Serves the gradients that no GEMM epilogue produces (norm weights, biases,
+// the embedding group).
+__global__ void scatter_add_f32_kernel(float* __restrict__ src, long long n, long long unit_rel, PeerPtrs dst,
+                                       long long n_per_owner, int zero_src) {
+  const long long n4 = n / 4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    const float4 v = reinterpret_cast<const float4*>(src)[i];
+    if (zero_src) reinterpret_cast<float4*>(src)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (v.x == 0.f && v.y == 0.f && v.z == 0.f && v.w == 0.f) continue;  // untouched embedding rows
+    const long long flat = unit_rel + 4 * i;
+    const int owner = (int)(flat / n_per_owner);
+    float* d = reinterpret_cast<float*>(dst.p[owner]) + (flat - (long long)owner * n_per_owner);
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(d), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+  }
+  for (long long i = n4 * 4 + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float v = src[i];
+    if (zero_src) src[i] = 0.f;
+    const long long flat = unit_rel + i;
+    const int owner = (int)(flat / n_per_owner);
+    atomicAdd(reinterpret_cast<float*>(dst.p[owner]) + (flat - (long long)owner * n_per_owner), v);
+  }
+}
+
 // out[local_off + i] = sum_r grads[r][global_off + i]; *norm_sq += sum(out^2). Peers are visited starting with
 // (my_rank + 1) so that ranks do not all read the same source at the same time.
 __global__ void rs_pull_sumsq_kernel(PeerPtrs grads, int my_rank, long long global_off, long long local_off, long long n,
@@ -187,6 +211,16 @@ void launch_weight_push(const void* src, bool src_fp32, long long local_off, lon
   if (src_fp32) weight_push_kernel<float><<<blocks_for(n / 8), 256, 0, s>>>((const float*)src, local_off, global_off, n, d);
   else weight_push_kernel<__nv_bfloat16><<<blocks_for(n / 8), 256, 0, s>>>((const __nv_bfloat16*)src, local_off, global_off, n, d);
   check_cuda(cudaGetLastError(), "weight_push");
+}
+
+void launch_scatter_add_f32(float* src, long long n, long long unit_rel, const ScatterArgs& sc, bool zero_src,
+                            cudaStream_t s) {
+  if (n == 0) return;
+  PeerPtrs d;
+  d.n = sc.world;
+  for (int r = 0; r < sc.world; ++r) d.p[r] = sc.dst[r];
+  scatter_add_f32_kernel<<<blocks_for(n / 4 + 1), 256, 0, s>>>(src, n, unit_rel, d, sc.n_per_owner, zero_src ? 1 : 0);
+  check_cuda(cudaGetLastError(), "scatter_add_f32");
 }
 
 void launch_rs_pull_sumsq(const long long* grad_ptrs, int world, int my_rank, long long global_off, long long local_off,

@@ -38,11 +38,49 @@ void launch_gemm_bf16(const void* a, long long lda, const void* b, long long ldb
                       int K, bool a_mn, bool b_mn, const void* bias, float alpha, bool out_fp32, bool accumulate,
                       int* status, int num_sms, cudaStream_t stream, const void* residual = nullptr, long long ldr = 0);
 
+// All-gather of one sharded parameter unit (FSDP / ZeRO-3: every rank owns n_per_owner contiguous elements of it)
+// into a local staging buffer. src[r] is rank r's slice (peer addresses for r != my_rank); flags has one 64-bit word
+// per chunk_elems elements of the unit and receives `epoch` when the chunk is staged.
+struct GatherArgs {
+  const void* src[8];
+  void* dst;
+  long long n_per_owner;
+  int world;
+  int my_rank;
+  void* flags;
+  unsigned long long epoch;
+  int chunk_elems;
+};
+// GEMM whose first n_copy CTAs run the gather while the others compute; b_unit_offset >= 0 when B itself is inside the
+// unit being gathered (the element offset of B in the staging buffer), < 0 when the job prefetches for later GEMMs.
+// Returns false (nothing launched) for arguments it does not serve.
+bool launch_ag_gemm_bf16(const void* a, long long lda, const void* b, long long ldb, void* d, long long ldd, int M,
+                         int N, int K, bool a_mn, bool b_mn, const void* bias, float alpha, bool out_fp32,
+                         bool accumulate, int* status, int num_sms, cudaStream_t stream, const void* residual,
+                         long long ldr, const GatherArgs& g, int n_copy, long long b_unit_offset);
+// GEMM -> reduce-scatter: the fp32 result is added element by element into the gradient shard of the rank that owns
+// it (vector red over NVLink) instead of being stored. dst[r] is owner r's shard already offset to the unit; the result
+// matrix starts unit_rel elements into the unit and has row pitch ldd.
+struct ScatterArgs {
+  void* dst[8];
+  long long n_per_owner;
+  int world;
+};
+bool launch_gemm_rs_bf16(const void* a, long long lda, const void* b, long long ldb, int M, int N, int K, bool a_mn, bool b_mn,
+                         float alpha, const ScatterArgs& sc, long long unit_rel, long long ldd, int* status, int num_sms,
+                         cudaStream_t stream);
+// src[0, n) (fp32, local) is added into the owners' shards at unit offset unit_rel and then zeroed when zero_src is set.
+void launch_scatter_add_f32(float* src, long long n, long long unit_rel, const ScatterArgs& sc, bool zero_src,
+                            cudaStream_t stream);
+// The gather alone, for a unit with no GEMM to ride on.
+bool launch_unit_gather(const GatherArgs& g, int n_ctas, cudaStream_t stream);
 
 // Decode-time shapes (M <= 256): split-K over a thread-block cluster, reduction through distributed shared memory.
-// Returns false (nothing launched) when the shape is outside what it serves.
+// Returns false (nothing launched) when the shape is outside what it serves. trace (optional, 16 int64 words on the
+// device) receives clock64 stamps of the kernel's phases for the first CTA: a built-in phase tracer.
 bool launch_gemm_skinny(const void* a, long long lda, const void* b, long long ldb, void* d, long long ldd, int M, int N, int K,
-                        const void* bias, const void* residual, long long ldr, int* status, int num_sms, cudaStream_t stream);
+                        const void* bias, const void* residual, long long ldr, int* status, int num_sms, cudaStream_t stream,
+                        long long* trace = nullptr);
 
 // ---- bandwidth-bound decoder ops (elementwise.cu); bf16 activations, H and F multiples of 8 ----
 void launch_embedding_fwd(const int* ids, const void* table, void* out, int T, int H, int V, cudaStream_t s);

@@ -378,7 +378,8 @@ class DistributedRuntime:
             if use_peer:
                 try:
                     # every rank allocates every symmetric buffer, in the same order, over the WORLD group
-                    self.plane = symm.SymmetricPlane(self.device, self.layout, self.C, self.trainer_ranks, self.infer_ranks)
+                    self.plane = symm.SymmetricPlane(self.device, self.layout, self.C, self.trainer_ranks, self.infer_ranks,
+                                                     zero3=config.param_sharding == "zero3")
                     self.trainer_comm = self.plane.trainer_comm()
                     self.weight_sync = self.plane.weight_sync()
                 except Exception as e:
@@ -540,6 +541,11 @@ class DistributedRuntime:
 
     async def verify_weight_sync(self) -> List[str]:
         sums = await self._all("verify_sync")
+        if self.config.param_sharding == "zero3" and len(self.trainer_ranks) > 1 and self.use_peer:
+            # fully sharded trainers each hold a slice: their partial sums add up to the checksum of the whole vector
+            ref = sum(sums[r]["trainer"] for r in self.trainer_ranks)
+            tol = 1e-9 * max(1.0, abs(ref)) + 1e-6
+            return [f"rank{r}:infer" for r, s in enumerate(sums) if s["infer"] is not None and abs(s["infer"] - ref) > tol]
         ref = sums[self.trainer_ranks[0]]["trainer"]
         bad = []
         for r, s in enumerate(sums):
@@ -580,7 +586,8 @@ class DistributedRuntime:
         """Runs on this rank's communication thread; every rank of the world executes it once per sync."""
         core = self.trainer.core if self.trainer is not None else None
         if self.weight_sync is not None:
-            self.weight_sync.push(core.params if core is not None else None, self.trainer_index)
+            src, sharded = core.sync_source() if core is not None else (None, False)
+            self.weight_sync.push(src, self.trainer_index, sharded_src=sharded)
             torch.cuda.synchronize(self.device)
             self.weight_sync.pg.check()
         else:
@@ -611,7 +618,7 @@ class DistributedRuntime:
     async def local_checksum(self) -> Dict[str, Optional[float]]:
         out: Dict[str, Optional[float]] = {"trainer": None, "infer": None}
         if self.trainer is not None:
-            out["trainer"] = float(self.trainer.core.params.double().sum().item())
+            out["trainer"] = self.trainer.core.param_checksum()
         if self.infer_params is not None:
             out["infer"] = float(self.infer_params.double().sum().item())
         return out

@@ -16,7 +16,7 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass
-from typing import Callable, Dict, List, Optional, Tuple
+from typing import Any, Callable, Dict, List, Optional, Tuple
 
 import torch
 
@@ -113,14 +113,21 @@ class GradSink:
 
 
 class NativeDecoder:
-    def __init__(self, cfg: ModelConfig, layout: ParamLayout, params: torch.Tensor, recompute: bool = False,
-                 lmhead_chunk: int = 4096):
+    def __init__(self, cfg: ModelConfig, layout: ParamLayout, params: Optional[torch.Tensor], recompute: bool = False,
+                 lmhead_chunk: int = 4096, weights: Any = None):
+        """``params`` is the resident flat bf16 parameter buffer. With ``weights`` (parallel/zero3.py::ShardedWeights)
+        there is no resident copy: each unit is gathered from its owners just before use, the gather of the next unit
+        riding on a GEMM launch of the current one."""
         from ..ops import native
 
-        assert params.is_cuda and params.dtype == torch.bfloat16
         self.C = native()
+        self.weights = weights
+        if weights is None:
+            assert params is not None and params.is_cuda and params.dtype == torch.bfloat16
+            self.dev = params.device
+        else:
+            self.dev = weights.device
         self.cfg, self.layout, self.params = cfg, layout, params
-        self.dev = params.device
         self.recompute = recompute
         self.lmhead_chunk = lmhead_chunk
         self.status = torch.zeros(1, dtype=torch.int32, device=self.dev)
@@ -130,7 +137,15 @@ class NativeDecoder:
 
     # ---- helpers ----
     def w(self, name: str) -> torch.Tensor:
+        if self.weights is not None:
+            return self.weights.view(name)
         return self.layout.view(self.params, name)
+
+    def _enter_unit(self, unit: int, then: Optional[int]) -> None:
+        """Sharded weights only: ``unit`` must be staged now; ``then`` is the unit needed after it (prefetched by the
+        next large GEMM launch)."""
+        if self.weights is not None:
+            self.launches += self.weights.enter(unit, then)
 
     def rope_tables(self, need: int = 1):
         if self._rope is None or self._rope[0].shape[0] < need:
@@ -146,19 +161,32 @@ class NativeDecoder:
             raise RuntimeError(f"device kernel reported status {code} (bounded wait ran out or bad index)")
 
     def _gemm(self, a, b, out, a_mn=False, b_mn=False, bias=None, accumulate=False, residual=None):
-        self.C.gemm_bf16(a, b, out, a_mn, b_mn, bias, 1.0, accumulate, self.status, residual)
+        if self.weights is not None and self.weights.pending is not None and a.shape[0] >= 1024:
+            self.weights.gemm_with_prefetch(a, b, out, a_mn, b_mn, bias, accumulate, self.status, residual)
+        else:
+            self.C.gemm_bf16(a, b, out, a_mn, b_mn, bias, 1.0, accumulate, self.status, residual)
         self.launches += 1
         return out
+
+    def _wgrad(self, dy, x, name: str, sink) -> None:
+        """dW[name] += dy^T x. A scatter sink adds the tile straight into the owners' gradient shards (GEMM fused with
+        the reduce-scatter); the plain sink accumulates into the local fp32 buffer."""
+        if getattr(sink, "scatter", False):
+            sink.wgrad(dy, x, name, self.status)
+        else:
+            self.C.gemm_bf16(dy, x, sink.view(name), True, True, None, 1.0, True, self.status, None)
+        self.launches += 1
 
     def _new(self, *shape, dtype=torch.bfloat16):
         return torch.empty(shape, dtype=dtype, device=self.dev)
 
     # ---- layer forward ----
     def _layer_fwd(self, i: int, x: torch.Tensor, batch: PackedBatch, cos_t, sin_t, save: Optional[dict],
-                   kv_write: Optional[tuple] = None):
+                   kv_write: Optional[tuple] = None, next_unit: Optional[int] = None):
         cfg, C = self.cfg, self.C
         T = x.shape[0]
         p = f"layers.{i}."
+        self._enter_unit(i + 1, next_unit)
         h1 = self._new(T, cfg.hidden_size)
         rstd1 = self._new(T, dtype=torch.float32)
         C.rmsnorm_fwd(x, self.w(p + "ln1"), h1, rstd1, cfg.rms_norm_eps)
@@ -194,22 +222,23 @@ class NativeDecoder:
         cfg, C = self.cfg, self.C
         T = dx.shape[0]
         p = f"layers.{i}."
+        self._enter_unit(i + 1, i if i > 0 else None)
         # ---- MLP ----
         dact = self._new(T, cfg.intermediate_size)
         self._gemm(dx, self.w(p + "wd"), dact, b_mn=True)
-        self._gemm(dx, s["act"], sink.view(p + "wd"), a_mn=True, b_mn=True, accumulate=True)
+        self._wgrad(dx, s["act"], p + "wd", sink)
         dgu = self._new(T, 2 * cfg.intermediate_size)
         C.swiglu_bwd(s["gu"], dact, dgu)
         del dact
         dh2 = self._new(T, cfg.hidden_size)
         self._gemm(dgu, self.w(p + "wgu"), dh2, b_mn=True)
-        self._gemm(dgu, s["h2"], sink.view(p + "wgu"), a_mn=True, b_mn=True, accumulate=True)
+        self._wgrad(dgu, s["h2"], p + "wgu", sink)
         del dgu
         C.rmsnorm_bwd(dh2, s["x1"], self.w(p + "ln2"), s["rstd2"], dx, sink.view(p + "ln2"), True)
         # ---- attention ----
         dattn = self._new(T, cfg.q_dim)
         self._gemm(dx, self.w(p + "wo"), dattn, b_mn=True)
-        self._gemm(dx, s["attn"], sink.view(p + "wo"), a_mn=True, b_mn=True, accumulate=True)
+        self._wgrad(dx, s["attn"], p + "wo", sink)
         dqkv = self._new(T, cfg.qkv_dim)
         delta = self._new(cfg.num_attention_heads, T, dtype=torch.float32)
         dq_acc = self._new(T, cfg.q_dim, dtype=torch.float32)
@@ -221,7 +250,7 @@ class NativeDecoder:
             C.colsum(dqkv, sink.view(p + "bqkv"))
         dh1 = dh2  # reuse
         self._gemm(dqkv, self.w(p + "wqkv"), dh1, b_mn=True)
-        self._gemm(dqkv, s["h1"], sink.view(p + "wqkv"), a_mn=True, b_mn=True, accumulate=True)
+        self._wgrad(dqkv, s["h1"], p + "wqkv", sink)
         C.rmsnorm_bwd(dh1, s["x"], self.w(p + "ln1"), s["rstd1"], dx, sink.view(p + "ln1"), True)
         self.launches += 11
         sink.unit_done(i + 1)
@@ -233,14 +262,17 @@ class NativeDecoder:
         T = batch.T
         cos_t, sin_t = self.rope_tables()
         x = self._new(T, cfg.hidden_size)
+        self._enter_unit(0, None)
         C.embedding_fwd(batch.ids, self.w("embed"), x)
-        for i in range(cfg.num_hidden_layers):
+        n_layers = cfg.num_hidden_layers
+        for i in range(n_layers):
             save = None
             if saves is not None:
                 save = {}
                 saves.append(save)
             x_in = x
-            x = self._layer_fwd(i, x, batch, cos_t, sin_t, save if not self.recompute else None)
+            x = self._layer_fwd(i, x, batch, cos_t, sin_t, save if not self.recompute else None,
+                                next_unit=i + 2 if i + 1 < n_layers else None)
             if saves is not None and self.recompute:
                 save["x"] = x_in
         hn = self._new(T, cfg.hidden_size)
@@ -311,7 +343,7 @@ class NativeDecoder:
             s = saves[i]
             if self.recompute:
                 full: dict = {}
-                self._layer_fwd(i, s["x"], batch, cos_t, sin_t, full)
+                self._layer_fwd(i, s["x"], batch, cos_t, sin_t, full, next_unit=i if i > 0 else None)
                 s = full
             self._layer_bwd(i, dx, s, batch, cos_t, sin_t, sink)
             saves[i] = None  # free activations of this layer

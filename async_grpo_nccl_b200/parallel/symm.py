@@ -100,7 +100,7 @@ class SymmetricPlane:
     """All symmetric buffers of a job, allocated collectively over the WORLD group by every rank in a fixed order."""
 
     def __init__(self, device: torch.device, layout: Any, C: Any, trainer_ranks: Sequence[int], infer_ranks: Sequence[int],
-                 world_group: Any = None):
+                 world_group: Any = None, zero3: bool = False):
         self.device, self.layout, self.C = device, layout, C
         self.group = world_group if world_group is not None else dist.group.WORLD
         self.my_rank = dist.get_rank()
@@ -109,11 +109,25 @@ class SymmetricPlane:
         self.flags = alloc_symmetric(128, torch.int64, device, self.group)          # [0,64): trainer barrier, [64,128): world
         self.norm_tab = alloc_symmetric(64, torch.float32, device, self.group)
         self.infer_params = alloc_symmetric(layout.total, torch.bfloat16, device, self.group)
-        self.train_params = alloc_symmetric(layout.total, torch.bfloat16, device, self.group) if need_train else None
-        self.grads = alloc_symmetric(layout.total, torch.float32, device, self.group) if need_train else None
+        self.zero3 = bool(zero3) and need_train
+        self.train_params = self.grads = self.shard16 = self.grad_shard = None
+        if self.zero3:
+            # fully sharded: every rank holds 1/W of the bf16 parameters and of the fp32 gradients, nothing else
+            n = layout.shard_numel()
+            self.shard16 = alloc_symmetric(n, torch.bfloat16, device, self.group)
+            self.grad_shard = alloc_symmetric(n, torch.float32, device, self.group)
+        elif need_train:
+            self.train_params = alloc_symmetric(layout.total, torch.bfloat16, device, self.group)
+            self.grads = alloc_symmetric(layout.total, torch.float32, device, self.group)
 
-    def trainer_comm(self) -> Optional["TrainerComm"]:
-        if self.grads is None or self.my_rank not in self.trainer_ranks:
+    def trainer_comm(self) -> Optional[Any]:
+        if self.my_rank not in self.trainer_ranks:
+            return None
+        if self.zero3:
+            from .zero3 import Zero3Comm
+
+            return Zero3Comm(self)
+        if self.grads is None:
             return None
         return TrainerComm(self)
 
@@ -186,17 +200,20 @@ class WeightSync:
     def buffer(self) -> torch.Tensor:
         return self.plane.infer_params.local
 
-    def push(self, src_params: Optional[torch.Tensor], trainer_index: Optional[int]) -> None:
-        """Collective over all ranks. Trainer ranks pass their resident bf16 parameters and their index among the
-        trainers; the others pass None and only take part in the barriers."""
+    def push(self, src_params: Optional[torch.Tensor], trainer_index: Optional[int], sharded_src: bool = False) -> None:
+        """Collective over all ranks. Trainer ranks pass their bf16 parameters (the resident flat buffer, or with
+        ``sharded_src`` just their own slices back to back) and their index among the trainers; the others pass None
+        and only take part in the barriers."""
         self.pg.barrier()  # inference ranks are idle (paused by the orchestrator) and trainers finished their step
         if src_params is not None and trainer_index is not None:
             t = len(self.trainer_ranks)
+            lo = 0
             for u in range(len(self.layout.unit_ranges)):
                 s, e = self.layout.unit_ranges[u]
                 n = (e - s) // t
                 a = s + trainer_index * n
-                self.C.weight_push(src_params, a, a, n, self.dst_ptrs)
+                self.C.weight_push(src_params, lo if sharded_src else a, a, n, self.dst_ptrs)
+                lo += n
         self.pg.barrier()  # all shards have landed everywhere
 
 

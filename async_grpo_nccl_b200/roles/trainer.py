@@ -65,7 +65,10 @@ class TrainerCore:
         # resident compute copy (bf16 on GPU). With a peer-memory communicator (parallel/symm.py::TrainerComm) the
         # parameter and gradient buffers are symmetric allocations that the other trainer ranks read and write.
         self.comm = comm
-        if comm is not None:
+        self.zero3 = bool(getattr(comm, "zero3", False))
+        if self.zero3:
+            self.params = None  # fully sharded: no resident copy, units are gathered on use (parallel/zero3.py)
+        elif comm is not None:
             self.params = comm.param_buffer
             self.params.copy_(init_flat_fp32.to(self.compute_dtype))
         else:
@@ -83,10 +86,20 @@ class TrainerCore:
             self.master[lo:lo + ln].copy_(init_flat_fp32[gs:gs + ln])
         self.exp_avg = torch.zeros_like(self.master)
         self.exp_avg_sq = torch.zeros_like(self.master)
-        self.grad_shard = torch.zeros_like(self.master) if world > 1 else None
-        self.sink = GradSink(L, self.device, flat=comm.grad_buffer if comm is not None else None)
         recompute = cfg.activation_recompute == "full"
-        if self.native:
+        if self.zero3:
+            assert self.native, "fully sharded mode runs on GPUs"
+            self.grad_shard = comm.grad_shard
+            self.sink = comm.sink
+            comm.shard16.copy_(self.master)  # fp32 -> bf16 slice that the peers gather from
+            comm.publish_initial()
+        else:
+            self.grad_shard = torch.zeros_like(self.master) if world > 1 else None
+            self.sink = GradSink(L, self.device, flat=comm.grad_buffer if comm is not None else None)
+        if self.zero3:
+            self.decoder = NativeDecoder(mcfg, L, None, recompute=recompute, weights=comm.weights)
+            self.norm_sq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        elif self.native:
             self.decoder = NativeDecoder(mcfg, L, self.params, recompute=recompute)
             self.norm_sq = torch.zeros(1, dtype=torch.float32, device=self.device)
         else:
@@ -189,6 +202,12 @@ class TrainerCore:
                 self.params.copy_(self.master.to(self.compute_dtype))
                 self.sink.zero_()
             norm_sq_dev = self.norm_sq
+        elif self.zero3:
+            # fully sharded path: the gradient shard already holds the sum over ranks and microbatches (GEMM epilogues
+            # reduced into it); barrier, norm exchange, AdamW on the shard, barrier
+            partials = self.comm.step(self.master, self.exp_avg, self.exp_avg_sq, *hp, cfg.max_grad_norm)
+            self.decoder.launches += 6
+            norm_sq_dev = partials.sum()
         elif self.comm is not None:
             # peer-memory path: pull-reduce my shard out of every rank's gradient buffer, exchange norm partials,
             # AdamW + store the bf16 shard into every rank's parameter buffer - three fused kernels, no NCCL call
@@ -326,6 +345,17 @@ class TrainerCore:
             dist.all_gather_into_tensor(full[s:e], self.master[lo:lo + ln].contiguous(), group=self.group)
         return full if self.rank == 0 else None
 
+    def sync_source(self) -> Tuple[Optional[torch.Tensor], bool]:
+        """(bf16 tensor the weight sync reads from, whether it holds only this rank's slices)."""
+        if self.zero3:
+            return self.comm.shard16, True
+        return self.params, False
+
+    def param_checksum(self) -> float:
+        if self.zero3:
+            return float(self.comm.shard16.double().sum().item())
+        return float(self.params.double().sum().item())
+
     def weights_info(self):
         return self.layout.weights_info()
 
@@ -343,6 +373,10 @@ class TrainerCore:
     def load_master_from_full(self, full_fp32: torch.Tensor) -> None:
         for lo, gs, ln in self.shard_map:
             self.master[lo:lo + ln].copy_(full_fp32[gs:gs + ln])
+        if self.zero3:
+            self.comm.shard16.copy_(self.master)
+            self.comm.publish_initial()
+            return
         self.params.copy_(full_fp32.to(self.device, dtype=self.compute_dtype))
         if not self.native:
             with torch.no_grad():

@@ -192,3 +192,65 @@ def test_engine_forced_lengths_and_eos():
         else:
             assert len(o.output_ids) == 200 and (o.output_ids != 5).all()
     assert eng.sched.num_free_blocks == 512 and eng.sched.num_running == 0
+
+
+@pytest.mark.parametrize("W,recompute", [(2, False), (4, True)])
+def test_fully_sharded_decoder_matches_resident(W, recompute):
+    """Sharded weights (gathered per layer, gathers riding on GEMM launches) + scatter sink (weight-gradient GEMMs
+    reducing straight into owners' shards) against the resident-parameter path. The W owners are separate buffers of
+    this one GPU; every kernel is a single launch, so nothing waits on another launch."""
+    from async_grpo_nccl_b200.models.config import PRESETS
+    from async_grpo_nccl_b200.models.decoder import GradSink, LossConfig, NativeDecoder
+    from async_grpo_nccl_b200.models.layout import ParamLayout
+    from async_grpo_nccl_b200.ops import native
+    from async_grpo_nccl_b200.packing import pack_samples
+    from async_grpo_nccl_b200.parallel.zero3 import ScatterSink, ShardedWeights
+
+    cfg = PRESETS["tiny128"]
+    layout = ParamLayout(cfg, shard_world=W)
+    p32 = torch.empty(layout.total)
+    layout.init_random_(p32, 0)
+    p16 = p32.to(torch.bfloat16).to(DEV)
+    rng = np.random.default_rng(5)
+    pb = pack_samples(_samples(cfg, 12, rng, 100, 300), pin=False).to_device(DEV)  # > 1024 rows: prefetch rides on GEMMs
+    assert pb.T >= 1024
+    lc = LossConfig(kl_beta=0.0, temperature=1.0)
+    ref = NativeDecoder(cfg, layout, p16, recompute=recompute)
+    with torch.no_grad():
+        lp0, _ = ref.logprobs(pb, 1.0)
+    pb.old_logprobs.copy_(lp0 + 0.02 * torch.randn_like(lp0))
+    sink_ref = GradSink(layout, DEV)
+    stats_ref = ref.forward_backward(pb, lc, 0.5, sink_ref)
+    stats_ref = ref.forward_backward(pb, lc, 0.5, sink_ref)  # two microbatches accumulate
+    # owners' slices, unit by unit, exactly as a rank of a W-rank job would hold them
+    shards16, gshards = [], []
+    for r in range(W):
+        parts = [p16[gs:gs + ln] for _, gs, ln in layout.local_to_global_ranges(r)]
+        shards16.append(torch.cat(parts).contiguous())
+        gshards.append(torch.zeros(layout.shard_numel(), dtype=torch.float32, device=DEV))
+    C = native()
+    weights = ShardedWeights(layout, C, torch.device(DEV), 0, [t.data_ptr() for t in shards16], n_copy=8, chunk_elems=8192)
+    weights.invalidate()
+    sink = ScatterSink(layout, C, torch.device(DEV), 0, [g.data_ptr() for g in gshards])
+    dec = NativeDecoder(cfg, layout, None, recompute=recompute, weights=weights)
+    stats = dec.forward_backward(pb, lc, 0.5, sink)
+    stats = dec.forward_backward(pb, lc, 0.5, sink)
+    torch.cuda.synchronize()
+    dec.check_status()
+    assert weights.gathers_fused > 0, "no gather rode on a GEMM launch"
+    assert torch.allclose(stats, stats_ref, rtol=1e-4, atol=1e-4)
+    full = torch.empty_like(p16)
+    weights.gather_full(full)
+    torch.cuda.synchronize()
+    assert torch.equal(full, p16)
+    # reassemble the flat gradient from the owners' shards
+    got = torch.zeros(layout.total, dtype=torch.float32, device=DEV)
+    for r in range(W):
+        for lo, gs, ln in layout.local_to_global_ranges(r):
+            got[gs:gs + ln] = gshards[r][lo:lo + ln]
+    for name in layout.segments:
+        a, b = layout.view(got, name), layout.view(sink_ref.flat, name)
+        assert (a - b).abs().max().item() <= 5e-3 * b.abs().max().item() + 1e-6, name
+    # logprob-only forward through the sharded weights
+    lpn, _ = dec.logprobs(pb, 1.0)
+    assert (lpn - lp0).abs().max().item() < 1e-5

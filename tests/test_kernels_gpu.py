@@ -330,3 +330,83 @@ def test_gemm_skinny_cluster_split_k(M, N, K):
     assert int(st.item()) == 0
     ref = a.float() @ b.float().t() + bias.float() + res.float()
     assert rel_err(d, ref) < 1e-2
+
+
+# ---- fused compute + collective kernels, owners emulated by separate buffers of one GPU (one launch: no kernel waits
+# on another launch). The 2-GPU test in test_multi_gpu.py runs the same kernels over real peer memory. ----
+@pytest.mark.parametrize("W,b_mn", [(1, False), (4, False), (2, True)])
+def test_ag_gemm_emulated_owners(W, b_mn):
+    C = native()
+    torch.manual_seed(3)
+    M, N, K = 1024, 2048, 1536
+    rel = 1536 * 3  # B starts after some other parameters of the unit
+    n_unit = ((rel + N * K + 4096 + 128 * W - 1) // (128 * W)) * (128 * W)
+    n_per = n_unit // W
+    unit = torch.randn(n_unit, device=DEV, dtype=torch.bfloat16)
+    shards = [unit[r * n_per:(r + 1) * n_per].clone() for r in range(W)]
+    staging = torch.zeros(n_unit, device=DEV, dtype=torch.bfloat16)
+    chunk = 65536
+    flags = torch.zeros((n_unit + chunk - 1) // chunk, device=DEV, dtype=torch.int64)
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    bshape = (K, N) if b_mn else (N, K)
+    b = staging[rel:rel + N * K].view(bshape)
+    d = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    st = status_word()
+    C.ag_gemm(a, b, d, False, b_mn, None, False, st, None, src_ptrs=[s.data_ptr() for s in shards], my_rank=0,
+              staging=staging, n_per_owner=n_per, flags=flags, epoch=1, chunk_elems=chunk, n_copy=8)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert torch.equal(staging, unit)
+    assert bool((flags == 1).all())
+    Bm = unit[rel:rel + N * K].view(bshape).float()
+    ref = a.float() @ (Bm if b_mn else Bm.t())
+    assert rel_err(d, ref) < 1e-2
+    # prefetch mode: B is elsewhere, the launch gathers a second unit for later launches
+    unit2 = torch.randn(n_unit, device=DEV, dtype=torch.bfloat16)
+    shards2 = [unit2[r * n_per:(r + 1) * n_per].clone() for r in range(W)]
+    staging2 = torch.zeros_like(staging)
+    flags2 = torch.zeros_like(flags)
+    b2 = Bm.to(torch.bfloat16).contiguous()
+    d2 = torch.empty_like(d)
+    C.ag_gemm(a, b2, d2, False, b_mn, None, False, st, None, src_ptrs=[s.data_ptr() for s in shards2], my_rank=0,
+              staging=staging2, n_per_owner=n_per, flags=flags2, epoch=7, chunk_elems=chunk, n_copy=16)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert torch.equal(staging2, unit2) and bool((flags2 == 7).all())
+    assert torch.equal(d2, d)
+    # the gather alone
+    staging3 = torch.zeros_like(staging)
+    C.unit_gather([s.data_ptr() for s in shards2], 0, staging3, n_per, flags2, 8, chunk, 32)
+    torch.cuda.synchronize()
+    assert torch.equal(staging3, unit2) and bool((flags2 == 8).all())
+
+
+@pytest.mark.parametrize("W", [1, 4])
+def test_gemm_reduce_scatter_emulated_owners(W):
+    C = native()
+    torch.manual_seed(4)
+    T, No, Ki = 2048, 1536, 1024       # dW[No, Ki] = dy[T, No]^T . x[T, Ki]
+    rel = 1536 + 128
+    n_unit = ((rel + No * Ki + 1000 + 128 * W - 1) // (128 * W)) * (128 * W)
+    n_per = n_unit // W
+    dy = torch.randn(T, No, device=DEV, dtype=torch.bfloat16)
+    x = torch.randn(T, Ki, device=DEV, dtype=torch.bfloat16)
+    before = torch.randn(n_unit, device=DEV, dtype=torch.float32)
+    shards = [before[r * n_per:(r + 1) * n_per].clone() for r in range(W)]
+    st = status_word()
+    C.gemm_rs(dy, x, True, True, 0.5, [s.data_ptr() for s in shards], n_per, rel, Ki, st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    got = torch.cat(shards)
+    want = before.clone()
+    want[rel:rel + No * Ki] += 0.5 * (dy.float().t() @ x.float()).reshape(-1)
+    assert rel_err(got, want) < 1e-4
+    # small vectors and the embedding group take the elementwise scatter
+    src = torch.randn(5000, device=DEV, dtype=torch.float32)
+    src[100:400] = 0
+    keep = src.clone()
+    C.scatter_add_f32(src, 128, [s.data_ptr() for s in shards], n_per, True)
+    torch.cuda.synchronize()
+    want[128:128 + 5000] += keep
+    assert rel_err(torch.cat(shards), want) < 1e-4
+    assert float(src.abs().max()) == 0.0
