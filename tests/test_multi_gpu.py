@@ -128,3 +128,109 @@ def test_peer_memory_collectives_match_nccl():
         p.join(timeout=60)
     for rank, msg in results:
         assert msg == "ok", f"rank {rank}: {msg}"
+
+
+def _worker_sharded(rank, world, port, q):
+    """Fully sharded trainer (ag_gemm / gemm_rs over real peer memory) against the resident-parameter trainer: same
+    microbatches, two optimizer steps, then the weight push from the slices."""
+    os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank), "MASTER_ADDR": "127.0.0.1",
+                       "MASTER_PORT": str(port), "NCCL_NVLS_ENABLE": "0"})
+    import numpy as np
+    import torch.distributed as dist
+
+    from async_grpo_nccl_b200.config import make_config
+    from async_grpo_nccl_b200.models.config import PRESETS
+    from async_grpo_nccl_b200.models.layout import ParamLayout
+    from async_grpo_nccl_b200.ops import native
+    from async_grpo_nccl_b200.packing import pack_for_logprob
+    from async_grpo_nccl_b200.parallel import symm
+    from async_grpo_nccl_b200.roles.trainer import TrainerCore
+
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world)
+    try:
+        C = native()
+        mcfg = PRESETS["tiny128"]
+        cfg = make_config({"model_name_or_path": "tiny128", "train_minibatch_sample_size": 12 * world, "learning_rate": 1e-3,
+                           "global_num_verifiers": 0, "max_grad_norm": 1.0})
+        ranks = list(range(world))
+        layout = ParamLayout(mcfg, shard_world=world)
+        plane_ref = symm.SymmetricPlane(dev, layout, C, trainer_ranks=ranks, infer_ranks=ranks)
+        plane_z3 = symm.SymmetricPlane(dev, layout, C, trainer_ranks=ranks, infer_ranks=ranks, zero3=True)
+        flat = torch.empty(layout.total)
+        layout.init_random_(flat, 0)
+        flat = flat.to(torch.bfloat16).float()
+        ref = TrainerCore(cfg, mcfg, dev, rank, world, None, flat.clone(), comm=plane_ref.trainer_comm())
+        z3 = TrainerCore(cfg, mcfg, dev, rank, world, None, flat.clone(), comm=plane_z3.trainer_comm())
+        assert z3.zero3 and z3.params is None
+        rng = np.random.default_rng(10 + rank)
+
+        def samples(n):
+            out = []
+            for _ in range(n):
+                li, lo = int(rng.integers(4, 40)), int(rng.integers(100, 300))
+                L = li + lo
+                out.append(dict(sample_ids=rng.integers(0, mcfg.vocab_size, L).astype(np.int32), input_len=li, output_len=lo,
+                                advantage=float(rng.normal()), sample_logprobs=np.zeros(L, np.float32),
+                                sample_entropies=np.zeros(L, np.float32), reward=1.0))
+            return out
+
+        for step in range(2):
+            mb = samples(12)
+            pb = pack_for_logprob(mb, pin=False).to_device(dev)
+            lp, ent = ref.decoder.logprobs(pb, 1.0)
+            lp, ent, off = lp.cpu().numpy(), ent.cpu().numpy(), 0
+            for s in mb:
+                L = len(s["sample_ids"])
+                s["sample_logprobs"], s["sample_entropies"] = lp[off:off + L].copy(), ent[off:off + L].copy()
+                off += L
+            ref.compute_gradients(mb)
+            z3.compute_gradients(mb)
+            sr, sz = ref.apply_gradients(), z3.apply_gradients()
+            assert abs(sr["grad_norm"] - sz["grad_norm"]) < 1e-3 * sr["grad_norm"], (sr["grad_norm"], sz["grad_norm"])
+            assert abs(sr["loss"] - sz["loss"]) < 1e-4 * max(1.0, abs(sr["loss"]))
+            # the same slice of the fp32 master on both paths. Adam's early steps move by about lr * sign(g), so an
+            # element whose gradient is at the noise level of the summation order may go the other way: compare most
+            diff = (ref.master - z3.master).abs()
+            assert (diff < 1e-5).float().mean().item() > 0.97, (diff < 1e-5).float().mean().item()
+        assert z3.comm.weights.gathers_fused > 0
+        # gathered slices equal the resident copy of the reference path wherever the masters agree bit for bit
+        full = torch.empty(layout.total, dtype=torch.bfloat16, device=dev)
+        z3.comm.weights.gather_full(full)
+        torch.cuda.synchronize()
+        same = ((full.float() - ref.params.float()).abs() < 1e-4).float().mean().item()
+        assert same > 0.97, same
+        # weight push straight from the slices
+        ws = plane_z3.weight_sync()
+        src, sharded = z3.sync_source()
+        ws.push(src, rank, sharded_src=sharded)
+        torch.cuda.synchronize()
+        ws.pg.check()
+        assert torch.equal(ws.buffer, full), "weights pushed from slices differ from the gathered parameters"
+        z3.decoder.check_status()
+        z3.comm.pg.check()
+        q.put((rank, "ok"))
+    except Exception as e:
+        import traceback
+
+        q.put((rank, f"FAILED: {e!r}\n{traceback.format_exc()}"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_fully_sharded_trainer_matches_resident_trainer():
+    import torch.multiprocessing as mp
+
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker_sharded, args=(r, world, 29741, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, msg in results:
+        assert msg == "ok", f"rank {rank}: {msg}"
