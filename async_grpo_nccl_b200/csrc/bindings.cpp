@@ -465,10 +465,11 @@ void scatter_add_f32(Tensor& src, int64_t unit_rel, const PtrList& dst_ptrs, int
                                 cur_stream());
 }
 void unit_gather(const PtrList& src_ptrs, int64_t my_rank, Tensor& staging, int64_t n_per_owner, Tensor& flags, int64_t epoch,
-                 int64_t chunk_elems, int64_t n_ctas) {
+                 int64_t chunk_elems, int64_t n_ctas, const OptTensor& status) {
+  if (status.has_value() && status->defined()) check_i32(*status, "unit_gather status");
   const c10::cuda::CUDAGuard guard(staging.device());
   agrpo::GatherArgs g = gather_args(src_ptrs, my_rank, staging, n_per_owner, flags, epoch, chunk_elems);
-  TORCH_CHECK(agrpo::launch_unit_gather(g, (int)n_ctas, cur_stream()), "unit_gather: arguments not served");
+  TORCH_CHECK(agrpo::launch_unit_gather(g, (int)n_ctas, opt_ptr<int>(status), cur_stream()), "unit_gather: arguments not served");
 }
 void weight_push(const Tensor& src, int64_t local_off, int64_t global_off, int64_t n, const PtrList& dst_ptrs) {
   TORCH_CHECK(src.is_cuda() && src.is_contiguous() && (src.scalar_type() == torch::kFloat32 || src.scalar_type() == torch::kBFloat16), "weight_push: src");
@@ -669,7 +670,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("scatter_add_f32", &scatter_add_f32, py::arg("src"), py::arg("unit_rel"), py::arg("dst_ptrs"), py::arg("n_per_owner"),
         py::arg("zero_src") = true);
   m.def("unit_gather", &unit_gather, py::arg("src_ptrs"), py::arg("my_rank"), py::arg("staging"), py::arg("n_per_owner"),
-        py::arg("flags"), py::arg("epoch"), py::arg("chunk_elems") = 262144, py::arg("n_ctas") = 32);
+        py::arg("flags"), py::arg("epoch"), py::arg("chunk_elems") = 262144, py::arg("n_ctas") = 32, py::arg("status") = py::none());
   m.def("rs_pull_sumsq", &rs_pull_sumsq);
   m.def("publish_norm", &publish_norm);
   m.def("adamw_push", &adamw_push);

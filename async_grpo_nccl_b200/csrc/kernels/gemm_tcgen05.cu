@@ -59,8 +59,24 @@ void launch_gemm_impl(const void* a, long long lda, const void* b, long long ldb
 }
 
 // Copies one sharded unit out of its owners' memory with no GEMM to ride on (the first unit of a pass).
-__global__ void __launch_bounds__(kGemmThreads) unit_gather_kernel(const GatherJob gj) {
-  gj.copy_role((int)blockIdx.x, nullptr);
+constexpr int kGatherSlots = 8;
+constexpr uint32_t kGatherPiece = 16384;
+constexpr int kGatherSmem = kGatherSlots * kGatherPiece + 1024 + 256;
+
+__global__ void __launch_bounds__(64) unit_gather_kernel(const GatherJob gj, int* status) {
+  extern __shared__ uint8_t gather_smem_raw[];
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gather_smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(ring + kGatherSlots * kGatherPiece);
+  uint64_t* empty = full + kGatherSlots;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kGatherSlots; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    fence_mbar_init();
+  }
+  __syncthreads();
+  gj.copy_role((int)blockIdx.x, ring, kGatherPiece, kGatherSlots, full, empty, status);
 }
 
 }  // namespace
@@ -152,10 +168,15 @@ bool launch_gemm_rs_bf16(const void* a, long long lda, const void* b, long long 
   return true;
 }
 
-bool launch_unit_gather(const GatherArgs& g, int n_ctas, cudaStream_t stream) {
+bool launch_unit_gather(const GatherArgs& g, int n_ctas, int* status, cudaStream_t stream) {
   if (!gather_args_ok(g) || n_ctas < 1) return false;
   GatherJob gj = make_gather_job(g, n_ctas);
-  unit_gather_kernel<<<n_ctas, kGemmThreads, 0, stream>>>(gj);
+  static bool configured = false;
+  if (!configured) {
+    check_cuda(cudaFuncSetAttribute(unit_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGatherSmem), "unit_gather attr");
+    configured = true;
+  }
+  unit_gather_kernel<<<n_ctas, 64, kGatherSmem, stream>>>(gj, status);
   check_cuda(cudaGetLastError(), "unit_gather_kernel");
   return true;
 }

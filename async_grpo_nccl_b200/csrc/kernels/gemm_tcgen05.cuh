@@ -205,19 +205,67 @@ struct GatherJob {
   long long b_row_elems;                   // row pitch of B in elements
   long long b_total_elems;                 // > 0: every tile waits for [b_unit_offset, b_unit_offset + b_total_elems)
 
-  __device__ __forceinline__ void copy_role(int cta, int* status) const {
+  __device__ __forceinline__ const __nv_bfloat16* src_of(int owner) const {
+    const __nv_bfloat16* b = src[0];
+#pragma unroll
+    for (int r = 1; r < kMaxOwners; ++r)
+      if (owner == r) b = src[r];
+    return b;
+  }
+  // Copier CTA: one thread streams pieces of the owners' slices into a shared-memory ring with bulk loads (the source
+  // is peer memory for the other owners), a second thread drains the ring into the local staging buffer with bulk
+  // stores and publishes the ready flag of each finished chunk. `full` / `empty` are mbarriers initialised to one
+  // arrival each; every wait is bounded.
+  __device__ __forceinline__ void copy_role(int cta, uint8_t* ring, uint32_t piece_bytes, int n_slots, uint64_t* full,
+                                            uint64_t* empty, int* status) const {
+    const int warp = threadIdx.x >> 5;
+    if ((threadIdx.x & 31) != 0 || warp > 1) return;
+    const long long piece_elems = piece_bytes / 2;
     const long long n_chunks = (unit_elems + chunk_elems - 1) / chunk_elems;
+    int slot = 0;
+    uint32_t phase = 0;
+    int held = -1;  // storer: slot whose bulk store may still be reading shared memory
     for (long long c = cta; c < n_chunks; c += n_copy) {
       const long long a = c * chunk_elems;
       const long long b = (a + chunk_elems < unit_elems) ? a + chunk_elems : unit_elems;
-      for (long long i = a + (long long)threadIdx.x * 8; i < b; i += (long long)blockDim.x * 8) {
+      long long i = a;
+      while (i < b) {
         const int owner = (int)(i / n_per_owner);
         const long long off = i - (long long)owner * n_per_owner;
-        const uint4 v = *reinterpret_cast<const uint4*>(src[owner] + off);
-        *reinterpret_cast<uint4*>(dst + i) = v;
+        long long n = n_per_owner - off;  // a piece stays inside one owner's slice and one chunk
+        if (n > b - i) n = b - i;
+        if (n > piece_elems) n = piece_elems;
+        const uint32_t bytes = (uint32_t)(n * 2);
+        uint8_t* buf = ring + (size_t)slot * piece_bytes;
+        if (warp == 0) {
+          if (!mbar_wait(&empty[slot], phase ^ 1)) {
+            report_status(status, kStatusPeerFlagTimeout);
+            return;
+          }
+          mbar_expect_tx(&full[slot], bytes);
+          bulk_load_g2s(buf, src_of(owner) + off, bytes, &full[slot]);
+        } else {
+          if (!mbar_wait(&full[slot], phase)) {
+            report_status(status, kStatusPeerFlagTimeout);
+            bulk_wait_all<0>();
+            return;
+          }
+          bulk_store_s2g(dst + i, buf, bytes);
+          bulk_commit();
+          bulk_wait_read<1>();  // every store but the newest has finished reading its slot
+          if (held >= 0) mbar_arrive(&empty[held]);
+          held = slot;
+        }
+        i += n;
+        if (++slot == n_slots) {
+          slot = 0;
+          phase ^= 1;
+        }
       }
-      __syncthreads();
-      if (threadIdx.x == 0) {
+      if (warp == 1) {
+        bulk_wait_all<0>();  // the chunk's stores are complete
+        if (held >= 0) mbar_arrive(&empty[held]);
+        held = -1;
         __threadfence();
         asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(flags + c), "l"(epoch) : "memory");
       }
@@ -326,7 +374,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int cta_stride = (int)gridDim.x - first_cta;
 
   if constexpr (Gather::kEnabled) {
-    if (my_cta < 0) gj.copy_role((int)blockIdx.x, p.status);
+    // the ring reuses the operand stages; one stage-sized piece may be as large as 32 KB
+    constexpr uint32_t kPiece = S::kStageBytes >= 32768 ? 32768u : 16384u;
+    if (my_cta < 0) gj.copy_role((int)blockIdx.x, smem, kPiece, kStages, full_bar, empty_bar, p.status);
   }
   if (my_cta < 0) {
     // copier CTA: nothing else to do

@@ -73,7 +73,7 @@ bool launch_gemm_rs_bf16(const void* a, long long lda, const void* b, long long 
 void launch_scatter_add_f32(float* src, long long n, long long unit_rel, const ScatterArgs& sc, bool zero_src,
                             cudaStream_t stream);
 // The gather alone, for a unit with no GEMM to ride on.
-bool launch_unit_gather(const GatherArgs& g, int n_ctas, cudaStream_t stream);
+bool launch_unit_gather(const GatherArgs& g, int n_ctas, int* status, cudaStream_t stream);
 
 // Decode-time shapes (M <= 256): split-K over a thread-block cluster, reduction through distributed shared memory.
 // Returns false (nothing launched) when the shape is outside what it serves. trace (optional, 16 int64 words on the

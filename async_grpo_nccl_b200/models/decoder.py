@@ -131,6 +131,8 @@ class NativeDecoder:
         self.recompute = recompute
         self.lmhead_chunk = lmhead_chunk
         self.status = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        if weights is not None:
+            weights.status = self.status
         self._rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
         self.n_stats = int(self.C.grpo_num_loss_stats())
         self.launches = 0  # kernels of this package launched (bench bookkeeping)
@@ -161,7 +163,7 @@ class NativeDecoder:
             raise RuntimeError(f"device kernel reported status {code} (bounded wait ran out or bad index)")
 
     def _gemm(self, a, b, out, a_mn=False, b_mn=False, bias=None, accumulate=False, residual=None):
-        if self.weights is not None and self.weights.pending is not None and a.shape[0] >= 1024:
+        if self.weights is not None and self.weights.wants_ride(a, b):
             self.weights.gemm_with_prefetch(a, b, out, a_mn, b_mn, bias, accumulate, self.status, residual)
         else:
             self.C.gemm_bf16(a, b, out, a_mn, b_mn, bias, 1.0, accumulate, self.status, residual)

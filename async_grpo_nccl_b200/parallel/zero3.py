@@ -30,7 +30,7 @@ class ShardedWeights:
     """Just-in-time all-gather of layout units into local staging buffers."""
 
     def __init__(self, layout: Any, C: Any, device: torch.device, my_rank: int, shard_ptrs: Sequence[int],
-                 n_copy: int = 16, chunk_elems: int = 1 << 18):
+                 n_copy: int = 8, chunk_elems: int = 1 << 18):
         self.layout, self.C, self.device = layout, C, torch.device(device)
         self.rank, self.world = int(my_rank), len(shard_ptrs)
         assert self.world == layout.shard_world, "the layout must be padded for this many owners"
@@ -51,6 +51,7 @@ class ShardedWeights:
         self.version = 0
         self.epoch = 0
         self.pending: Optional[int] = None
+        self.status: Optional[torch.Tensor] = None  # error word of the decoder that uses these weights
         self.gathers_standalone = 0
         self.gathers_fused = 0
 
@@ -87,11 +88,18 @@ class ShardedWeights:
         if not self.is_resident(unit):
             j = self._job(unit)
             self.C.unit_gather(j["src_ptrs"], j["my_rank"], j["staging"], j["n_per_owner"], j["flags"], j["epoch"],
-                               j["chunk_elems"], 64)
+                               j["chunk_elems"], 64, self.status)
             self.gathers_standalone += 1
             n = 1
         self.pending = then if (then is not None and not self.is_resident(then)) else None
         return n
+
+    def wants_ride(self, a: torch.Tensor, b: torch.Tensor) -> bool:
+        """A pending gather rides on the largest GEMM of a block (the gate/up projection or its input-gradient GEMM):
+        the launch lasts as long as the slower of its math and the copy, so a small GEMM would be stretched."""
+        if self.pending is None or a.shape[0] < 1024:
+            return False
+        return b.numel() * 5 >= 2 * self.unit_n[self.pending]
 
     def gemm_with_prefetch(self, a, b, out, a_mn, b_mn, bias, accumulate, status, residual) -> None:
         unit = self.pending

@@ -6,6 +6,7 @@
     python -m async_grpo_nccl_b200.utils.microbench decode --batch 128 --context 1024 --steps 20 [--graph]
     python -m async_grpo_nccl_b200.utils.microbench train --tokens 16384
     python -m async_grpo_nccl_b200.utils.microbench elementwise
+    python -m async_grpo_nccl_b200.utils.microbench fused --tokens 16384
 
 Each line of output is a JSON record with the achieved rate and, where a library kernel exists in the image
 (cuBLAS through torch.matmul, flash-attn 2), the same measurement for it. Roofline denominators come from
@@ -92,6 +93,77 @@ def bench_gemm(args):
             rec["weight_gbs"] = N * K * 2 / t / 1e6
             rec["frac_of_hbm"] = rec["weight_gbs"] / pk["hbm_gbs"]
         out(rec)
+    assert int(st.item()) == 0
+
+
+def bench_fused(args):
+    """Fused compute + collective kernels on ONE GPU, the owners being separate local buffers: measures what the copier
+    CTAs and the reduce-scatter epilogue cost next to the plain kernels. With --world > 1 under torchrun the same
+    kernels run over real peer memory (symmetric allocations)."""
+    from ..ops import native
+
+    C = native()
+    pk = _peaks()
+    W = 4
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    T, H, F = args.tokens, 1536, 8960
+    unit_n = (46_800_000 // (128 * W)) * 128 * W        # one Qwen2.5-1.5B block
+    n_per = unit_n // W
+    shards = [torch.randn(n_per, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
+    staging = torch.empty(unit_n, device="cuda", dtype=torch.bfloat16)
+    chunk = 1 << 18
+    flags = torch.zeros((unit_n + chunk - 1) // chunk, dtype=torch.int64, device="cuda")
+    ptrs = [s_.data_ptr() for s_ in shards]
+    a = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(2 * F, H, device="cuda", dtype=torch.bfloat16)
+    d = torch.empty(T, 2 * F, device="cuda", dtype=torch.bfloat16)
+    ep = [0]
+
+    def fused(n_copy):
+        ep[0] += 1
+        C.ag_gemm(a, b, d, False, False, None, False, st, None, src_ptrs=ptrs, my_rank=0, staging=staging, n_per_owner=n_per,
+                  flags=flags, epoch=ep[0], chunk_elems=chunk, n_copy=n_copy)
+
+    def serial():
+        ep[0] += 1
+        C.unit_gather(ptrs, 0, staging, n_per, flags, ep[0], chunk, 64)
+        C.gemm_bf16(a, b, d, False, False, None, 1.0, False, st, None)
+
+    def gather_only():
+        ep[0] += 1
+        C.unit_gather(ptrs, 0, staging, n_per, flags, ep[0], chunk, 64)
+
+    t_plain = timeit(lambda: C.gemm_bf16(a, b, d, False, False, None, 1.0, False, st, None))
+    t_gather = timeit(gather_only)
+    t_serial = timeit(serial)
+    fl = 2.0 * T * 2 * F * H
+    for n_copy in (2, 4, 8, 16):
+        t = timeit(lambda: fused(n_copy))
+        out({"bench": "ag_gemm_prefetch", "M": T, "N": 2 * F, "K": H, "unit_mb": unit_n * 2 / 1e6, "n_copy": n_copy, "ms": t,
+             "gemm_alone_ms": t_plain, "gather_alone_ms": t_gather, "serial_ms": t_serial, "hidden_frac": (t_serial - t) / t_gather,
+             "tflops": fl / t / 1e9, "gather_gbs": unit_n * 2 / t_gather / 1e6})
+    # the GEMM consumes the unit being gathered (tile-by-tile waits)
+    rel = 4096
+    bview = staging[rel: rel + 2 * F * H].view(2 * F, H)
+
+    def fused_self():
+        ep[0] += 1
+        C.ag_gemm(a, bview, d, False, False, None, False, st, None, src_ptrs=ptrs, my_rank=0, staging=staging, n_per_owner=n_per,
+                  flags=flags, epoch=ep[0], chunk_elems=chunk, n_copy=16)
+
+    t = timeit(fused_self)
+    out({"bench": "ag_gemm_consume", "M": T, "N": 2 * F, "K": H, "ms": t, "gemm_alone_ms": t_plain, "gather_alone_ms": t_gather,
+         "serial_ms": t_serial})
+    # weight gradient: local fp32 accumulate vs reduce-scatter epilogue
+    dy = torch.randn(T, 2 * F, device="cuda", dtype=torch.bfloat16)
+    acc = torch.zeros(2 * F, H, device="cuda", dtype=torch.float32)
+    gsh = [torch.zeros(n_per, device="cuda", dtype=torch.float32) for _ in range(W)]
+    gp = [g.data_ptr() for g in gsh]
+    t_acc = timeit(lambda: C.gemm_bf16(dy, a, acc, True, True, None, 1.0, True, st, None))
+    t_rs = timeit(lambda: C.gemm_rs(dy, a, True, True, 1.0, gp, n_per, rel, H, st))
+    out({"bench": "gemm_rs", "M": 2 * F, "N": H, "K": T, "ms": t_rs, "local_accumulate_ms": t_acc, "tflops": fl / t_rs / 1e9,
+         "local_tflops": fl / t_acc / 1e9, "frac_of_peak": fl / t_rs / 1e9 / pk["bf16_tflops"], "peak": pk["source"]})
+    torch.cuda.synchronize()
     assert int(st.item()) == 0
 
 
@@ -299,7 +371,7 @@ def bench_train(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn", "lmhead", "elementwise", "decode", "train"])
+    ap.add_argument("what", choices=["gemm", "attn", "lmhead", "elementwise", "decode", "train", "fused"])
     ap.add_argument("--model", default="qwen2.5-1.5b")
     ap.add_argument("--batch", type=int, default=128)
     ap.add_argument("--context", type=int, default=1024)
@@ -310,7 +382,7 @@ def main():
     ap.add_argument("--recompute", action="store_true")
     args = ap.parse_args()
     {"gemm": bench_gemm, "attn": bench_attn, "lmhead": bench_lmhead, "elementwise": bench_elementwise, "decode": bench_decode,
-     "train": bench_train}[args.what](args)
+     "train": bench_train, "fused": bench_fused}[args.what](args)
 
 
 if __name__ == "__main__":
