@@ -86,6 +86,59 @@ void embedding_fwd(const Tensor& ids, const Tensor& table, Tensor& out) {
   agrpo::launch_embedding_fwd(ids.data_ptr<int>(), table.data_ptr(), out.data_ptr(), (int)ids.numel(), (int)table.size(1),
                               (int)table.size(0), cur_stream());
 }
+void embedding_sumsq(const Tensor& ids, const Tensor& table, Tensor& out, Tensor& ss) {
+  check_i32(ids, "ids"); check_bf16(table, "table"); check_bf16(out, "out"); check_f32(ss, "ss");
+  TORCH_CHECK(table.is_contiguous() && out.is_contiguous() && table.size(1) % 8 == 0, "embedding_sumsq layout");
+  TORCH_CHECK(ss.dim() == 2 && ss.stride(1) == 1 && ss.size(1) >= ids.numel(), "embedding_sumsq: ss [n, >= rows]");
+  const c10::cuda::CUDAGuard guard(table.device());
+  agrpo::launch_embedding_sumsq(ids.data_ptr<int>(), table.data_ptr(), out.data_ptr(), ss.data_ptr<float>(), (int)ss.size(0),
+                                (int)ss.stride(0), (int)ids.numel(), (int)table.size(1), (int)table.size(0), cur_stream());
+}
+void fold_norm_weight(const Tensor& w, const Tensor& g, Tensor& out) {
+  check_bf16(w, "w"); check_bf16(g, "g"); check_bf16(out, "out");
+  TORCH_CHECK(w.dim() == 2 && w.is_contiguous() && out.is_contiguous() && out.numel() == w.numel() && g.is_contiguous() &&
+              g.numel() == w.size(1) && w.size(1) % 8 == 0, "fold_norm_weight layout");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(w.data_ptr()) & 15) == 0 && (reinterpret_cast<uintptr_t>(out.data_ptr()) & 15) == 0 &&
+              (reinterpret_cast<uintptr_t>(g.data_ptr()) & 15) == 0, "fold_norm_weight: 16-byte alignment");
+  const c10::cuda::CUDAGuard guard(w.device());
+  agrpo::launch_fold_norm_weight(w.data_ptr(), g.data_ptr(), out.data_ptr(), w.size(0), (int)w.size(1), cur_stream());
+}
+// Decode-step GEMMs (M <= 256, K-major operands). gemm_decode runs the cluster split-K kernel with the optional folded
+// RMSNorm row scale (ss_in) and row sum-of-squares output (ss_out); it returns false, having launched nothing, when
+// that kernel does not serve the shape. gemm_swiglu fuses the gate/up projection with SwiGLU.
+bool gemm_decode(const Tensor& a, const Tensor& b, Tensor& d, const OptTensor& bias, const OptTensor& residual, const OptTensor& ss_in,
+                 const OptTensor& ss_out, double eps, const OptTensor& status) {
+  check_bf16(a, "gemm_decode a"); check_bf16(b, "gemm_decode b"); check_bf16(d, "gemm_decode d");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && d.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && d.stride(1) == 1, "gemm_decode: 2-D");
+  const int64_t M = a.size(0), K = a.size(1), N = b.size(0);
+  TORCH_CHECK(b.size(1) == K && d.size(0) == M && d.size(1) == N, "gemm_decode: shape mismatch");
+  TORCH_CHECK(a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0, "gemm_decode: row pitch must be a multiple of 8 elements");
+  if (ss_in.has_value() && ss_in->defined()) { check_f32(*ss_in, "ss_in"); TORCH_CHECK(ss_in->numel() >= M && ss_in->is_contiguous(), "ss_in [M]"); }
+  if (ss_out.has_value() && ss_out->defined()) { check_f32(*ss_out, "ss_out"); TORCH_CHECK(ss_out->numel() >= M && ss_out->is_contiguous(), "ss_out [M]"); }
+  if (status.has_value() && status->defined()) check_i32(*status, "gemm_decode status");
+  long long ldr = 0;
+  if (residual.has_value() && residual->defined()) { check_bf16(*residual, "residual"); ldr = residual->stride(0); }
+  if (bias.has_value() && bias->defined()) check_bf16(*bias, "bias");
+  const c10::cuda::CUDAGuard guard(a.device());
+  return agrpo::launch_gemm_skinny(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), d.data_ptr(), d.stride(0), (int)M, (int)N,
+                                   (int)K, opt_ptr<void>(bias), opt_ptr<void>(residual), ldr, opt_ptr<int>(status), num_sms(),
+                                   cur_stream(), nullptr, opt_ptr<float>(ss_in), opt_ptr<float>(ss_out), (float)eps);
+}
+int64_t gemm_skinny_splits(int64_t M, int64_t N, int64_t K) { return agrpo::gemm_skinny_splits((int)M, (int)N, (int)K, num_sms()); }
+void gemm_swiglu(const Tensor& a, const Tensor& b, Tensor& d, const OptTensor& ss_in, double eps, const OptTensor& status) {
+  check_bf16(a, "gemm_swiglu a"); check_bf16(b, "gemm_swiglu b"); check_bf16(d, "gemm_swiglu d");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && d.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && d.stride(1) == 1, "gemm_swiglu: 2-D");
+  const int64_t M = a.size(0), K = a.size(1), F = d.size(1);
+  TORCH_CHECK(b.size(0) == 2 * F && b.size(1) == K && d.size(0) == M, "gemm_swiglu: b must be the stacked [2F, K] gate/up weight");
+  TORCH_CHECK(a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0 && F % 8 == 0, "gemm_swiglu: pitches and F must be multiples of 8");
+  if (ss_in.has_value() && ss_in->defined()) { check_f32(*ss_in, "ss_in"); TORCH_CHECK(ss_in->numel() >= M && ss_in->is_contiguous(), "ss_in [M]"); }
+  if (status.has_value() && status->defined()) check_i32(*status, "gemm_swiglu status");
+  const c10::cuda::CUDAGuard guard(a.device());
+  TORCH_CHECK(agrpo::launch_gemm_swiglu_bf16(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), d.data_ptr(), d.stride(0), (int)M,
+                                             (int)F, (int)K, opt_ptr<float>(ss_in), (float)eps, opt_ptr<int>(status), num_sms(),
+                                             cur_stream()),
+              "gemm_swiglu: arguments not served");
+}
 void embedding_bwd(const Tensor& ids, const Tensor& dout, Tensor& dtable) {
   check_i32(ids, "ids"); check_bf16(dout, "dout"); check_f32(dtable, "dtable");
   TORCH_CHECK(dtable.is_contiguous() && dout.is_contiguous(), "embedding_bwd layout");
@@ -616,6 +669,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_skinny_trace", &gemm_skinny_trace);
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
+  m.def("set_pdl", [](bool on) { agrpo::pdl_flag() = on; },
+        "Programmatic dependent launch for the kernels this THREAD launches next (used around the decode step).");
+  m.def("embedding_sumsq", &embedding_sumsq);
+  m.def("fold_norm_weight", &fold_norm_weight);
+  m.def("gemm_decode", &gemm_decode, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("bias") = py::none(),
+        py::arg("residual") = py::none(), py::arg("ss_in") = py::none(), py::arg("ss_out") = py::none(), py::arg("eps") = 1e-6,
+        py::arg("status") = py::none());
+  m.def("gemm_skinny_splits", &gemm_skinny_splits);
+  m.def("gemm_swiglu", &gemm_swiglu, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("ss_in") = py::none(), py::arg("eps") = 1e-6,
+        py::arg("status") = py::none());
   m.def("rmsnorm_fwd", &rmsnorm_fwd, py::arg("x"), py::arg("w"), py::arg("y"), py::arg("rstd") = py::none(),
         py::arg("eps") = 1e-6);
   m.def("rmsnorm_bwd", &rmsnorm_bwd, py::arg("dy"), py::arg("x"), py::arg("w"), py::arg("rstd"), py::arg("dx"),

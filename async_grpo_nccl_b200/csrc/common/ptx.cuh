@@ -88,6 +88,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // ----------------------------------------------------------------------------------------------
+// Programmatic dependent launch. pdl_wait() returns once the preceding kernel of the stream has completed and its
+// writes are visible (at once when the kernel was launched without the attribute); everything before it overlaps the
+// predecessor's tail. pdl_launch() lets the next kernel of the stream begin its own prologue. Every kernel calls
+// pdl_launch() only after pdl_wait(), so that a kernel never starts before the kernel two places ahead has finished.
+// ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ----------------------------------------------------------------------------------------------
 // Untiled bulk copies (addresses 16-byte aligned, size a multiple of 16 bytes). The source of a load may be a peer
 // GPU's memory; each load has exactly one destination CTA.
 // ----------------------------------------------------------------------------------------------

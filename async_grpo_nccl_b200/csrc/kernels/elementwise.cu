@@ -4,6 +4,7 @@
 // All activations are bf16 with fp32 math; 16-byte vector accesses; rows are processed by one warp.
 #include <cuda_bf16.h>
 
+#include "../common/ptx.cuh"
 #include "../launchers.h"
 
 namespace agrpo {
@@ -35,6 +36,58 @@ __global__ void embedding_fwd_kernel(const int* __restrict__ ids, const __nv_bfl
   for (int i = lane; i < H / 8; i += 32) dst[i] = src[i];
 }
 
+// Decode-step variant: besides the lookup it writes the row's sum of squares to ss[0][row] and clears ss[1..n_ss)[row],
+// the per-layer statistics that the folded-norm GEMMs of the step accumulate into (ss is [n_ss, ss_stride] fp32).
+__global__ void embedding_sumsq_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
+                                       __nv_bfloat16* __restrict__ out, float* __restrict__ ss, int n_ss, int ss_stride, int T,
+                                       int H, int V) {
+  pdl_wait();
+  pdl_launch();
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= T) return;
+  const int lane = threadIdx.x & 31;
+  int id = ids[row];
+  id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+  const Bf16x8* src = reinterpret_cast<const Bf16x8*>(table + (size_t)id * H);
+  Bf16x8* dst = reinterpret_cast<Bf16x8*>(out + (size_t)row * H);
+  float acc = 0.f;
+  for (int i = lane; i < H / 8; i += 32) {
+    const Bf16x8 v = src[i];
+    dst[i] = v;
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(h[j]);
+      acc += f.x * f.x + f.y * f.y;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) ss[row] = acc;
+  for (int k = 1 + lane; k < n_ss; k += 32) ss[(size_t)k * ss_stride + row] = 0.f;
+}
+
+// out[n, k] = w[n, k] * g[k]: an RMSNorm weight folded into the columns of the matrix that consumes the normalised rows.
+__global__ void fold_norm_weight_kernel(const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ g,
+                                        __nv_bfloat16* __restrict__ out, long long n_rows, int K) {
+  const long long total = n_rows * (long long)(K / 8);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int kc = (int)(i % (K / 8));
+    const Bf16x8 a = reinterpret_cast<const Bf16x8*>(w)[i];
+    const Bf16x8 b = reinterpret_cast<const Bf16x8*>(g)[kc];
+    const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&b);
+    Bf16x8 o;
+    __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 fa = __bfloat1622float2(ha[j]), fb = __bfloat1622float2(hb[j]);
+      ho[j] = __floats2bfloat162_rn(fa.x * fb.x, fa.y * fb.y);
+    }
+    reinterpret_cast<Bf16x8*>(out)[i] = o;
+  }
+}
+
 __global__ void embedding_bwd_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ dout,
                                      float* __restrict__ dtable, int T, int H, int V) {
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -57,6 +110,8 @@ __global__ void embedding_bwd_kernel(const int* __restrict__ ids, const __nv_bfl
 __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                    __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out, int T, int H,
                                    float eps) {
+  pdl_wait();
+  pdl_launch();
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= T) return;
   const int lane = threadIdx.x & 31;
@@ -289,6 +344,20 @@ void launch_embedding_fwd(const int* ids, const void* table, void* out, int T, i
   embedding_fwd_kernel<<<(T + 7) / 8, 256, 0, s>>>(ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, T, H, V);
   check_cuda(cudaGetLastError(), "embedding_fwd");
 }
+void launch_embedding_sumsq(const int* ids, const void* table, void* out, float* ss, int n_ss, int ss_stride, int T, int H,
+                            int V, cudaStream_t s) {
+  if (T == 0) return;
+  AGRPO_PREFER_SMEM(embedding_sumsq_kernel);
+  launch_kernel(embedding_sumsq_kernel, dim3((T + 7) / 8), dim3(256), 0, s, "embedding_sumsq", ids, (const __nv_bfloat16*)table,
+                (__nv_bfloat16*)out, ss, n_ss, ss_stride, T, H, V);
+}
+void launch_fold_norm_weight(const void* w, const void* g, void* out, long long n_rows, int K, cudaStream_t s) {
+  if (n_rows == 0) return;
+  const long long total = n_rows * (K / 8);
+  const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+  fold_norm_weight_kernel<<<blocks, 256, 0, s>>>((const __nv_bfloat16*)w, (const __nv_bfloat16*)g, (__nv_bfloat16*)out, n_rows, K);
+  check_cuda(cudaGetLastError(), "fold_norm_weight");
+}
 void launch_embedding_bwd(const int* ids, const void* dout, float* dtable, int T, int H, int V, cudaStream_t s) {
   if (T == 0) return;
   embedding_bwd_kernel<<<(T + 7) / 8, 256, 0, s>>>(ids, (const __nv_bfloat16*)dout, dtable, T, H, V);
@@ -297,9 +366,8 @@ void launch_embedding_bwd(const int* ids, const void* dout, float* dtable, int T
 void launch_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int T, int H, float eps, cudaStream_t s) {
   if (T == 0) return;
   AGRPO_PREFER_SMEM(rmsnorm_fwd_kernel);
-  rmsnorm_fwd_kernel<<<(T + 7) / 8, 256, 0, s>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
-                                                 rstd, T, H, eps);
-  check_cuda(cudaGetLastError(), "rmsnorm_fwd");
+  launch_kernel(rmsnorm_fwd_kernel, dim3((T + 7) / 8), dim3(256), 0, s, "rmsnorm_fwd", (const __nv_bfloat16*)x,
+                (const __nv_bfloat16*)w, (__nv_bfloat16*)y, rstd, T, H, eps);
 }
 void launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw, int T,
                         int H, bool accumulate_dx, cudaStream_t s) {

@@ -1,7 +1,11 @@
 // Skinny bf16 GEMM for decode-time shapes (M <= 256 rows, weights streamed once): split-K across a thread-block
 // cluster with the reduction done through distributed shared memory.
 //
-//   D[M, N] = A[M, K] . B[N, K]^T (+ bias) (+ residual), bf16 in / bf16 out, fp32 accumulation
+//   D[M, N] = rs[m] * (A[M, K] . B[N, K]^T) (+ bias) (+ residual), bf16 in / bf16 out, fp32 accumulation
+//
+// rs[m] = rsqrt(ss_in[m] / K + eps) is optional: with the RMSNorm weight folded into B's columns it makes the GEMM
+// consume the un-normalised residual stream directly (the norm kernel disappears from the decode step). ss_out,
+// also optional, receives the row sums of squares of the result, i.e. the statistic the NEXT folded GEMM needs.
 //
 // With a handful of rows the GEMM is bound by streaming B (the weights) from HBM, and a 128 x BN output tile
 // per CTA leaves most SMs idle when N is small (N = 1536 gives 12 tiles on 148 SMs). Here the S CTAs of a
@@ -31,6 +35,10 @@ struct SkParams {
   const __nv_bfloat16* bias;
   const __nv_bfloat16* residual;
   long long ldr;
+  const float* ss_in;   // [M] sum of squares of each row of A, or nullptr
+  float* ss_out;        // [M] += sum of squares of each row of D (atomic), or nullptr
+  float inv_k;          // 1 / K
+  float eps;
   int* status;
   long long* trace;  // optional: clock64 stamps of the phases of cluster 0 / CTA 0 (16 slots), nullptr = off
 };
@@ -135,14 +143,18 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
     mbar_init(parts_ready, S);
     mbar_init(reads_done, S);
     fence_cluster_barrier_init();
-    // The first loads do not depend on anything another thread or CTA sets up: issue them before the CTA / cluster
-    // synchronisation so that the ~2 us cold first-load latency overlaps the rest of the prologue.
+    // The first weight (B) loads depend on nothing that another thread, CTA or the preceding kernel produces: issue
+    // them before any synchronisation so that their ~2 us cold latency overlaps the prologue and, under programmatic
+    // dependent launch, the tail of the previous kernel. The activation (A) loads follow once that kernel is complete.
+    for (int i = 0; i < n_pre; ++i) {
+      mbar_expect_tx(&full_bar[i], kStageBytes);
+      tma_load_2d(smem + i * kStageBytes + kABytes, &tmB, &full_bar[i], (kb0 + i) * kBK, n0);
+    }
+    pdl_wait();
     for (int i = 0; i < n_pre; ++i) {
       uint8_t* sa = smem + i * kStageBytes;
-      mbar_expect_tx(&full_bar[i], kStageBytes);
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) tma_load_2d(sa + mt * (kBM * kBK * 2), &tmA, &full_bar[i], (kb0 + i) * kBK, mt * kBM);
-      tma_load_2d(sa + kABytes, &tmB, &full_bar[i], (kb0 + i) * kBK, n0);
     }
     SK_STAMP(3);
   }
@@ -155,6 +167,8 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
   if (threadIdx.x == 0) SK_STAMP(1);
   cluster_sync_all();
   tc_fence_after();
+  pdl_wait();
+  pdl_launch();
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) SK_STAMP(2);
 
@@ -259,6 +273,8 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
 #pragma unroll 1
       for (int mt = 0; mt < MT; ++mt) {
         const int row = mt * kBM + row_in_tile;
+        const float rs = (p.ss_in != nullptr && row < p.M) ? rsqrtf(p.ss_in[row] * p.inv_k + p.eps) : 1.f;
+        float sq = 0.f;
 #pragma unroll 1
         for (int cb = 0; cb < w; cb += 8) {
           float4 v[8][2];
@@ -280,6 +296,8 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
           }
           const int col = n0 + c0 + cb;
           if (row < p.M && col < p.N) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] *= rs;
             if (p.bias != nullptr) {
 #pragma unroll
               for (int i = 0; i < 8; ++i)
@@ -291,6 +309,9 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
               for (int i = 0; i < 8; ++i)
                 if (col + i < p.N) acc[i] += __bfloat162float(rp[i]);
             }
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if (col + i < p.N) sq += acc[i] * acc[i];
             __nv_bfloat16* dst = p.D + (long long)row * p.ldd + col;
             if (col + 8 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
               uint4 o;
@@ -305,6 +326,7 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
             }
           }
         }
+        if (p.ss_out != nullptr && row < p.M) atomicAdd(p.ss_out + row, sq);
       }
     }
     // tell every peer that I am done with its shared memory, then wait until everyone is done with mine
@@ -338,30 +360,40 @@ void launch_sk(const CUtensorMap& ta, const CUtensorMap& tb, const SkParams& p, 
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = S;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl_flag() ? 2 : 1;
   check_cuda(cudaLaunchKernelEx(&cfg, kernel, ta, tb, p, S), "gemm_splitk launch");
 }
 
 }  // namespace
 
-// Returns false when the shape is not one this kernel serves (the caller then uses the general GEMM).
-bool launch_gemm_skinny(const void* a, long long lda, const void* b, long long ldb, void* d, long long ldd, int M, int N, int K,
-                        const void* bias, const void* residual, long long ldr, int* status, int num_sms, cudaStream_t stream,
-                        long long* trace) {
-  if (M > 256 || K < 512 || N < 64) return false;
-  const int MT = M <= 128 ? 1 : 2;
-  const int BN = MT == 1 ? 128 : 64;
+// Number of K splits (= cluster size) the skinny kernel would use, 0 when it does not serve the shape.
+int gemm_skinny_splits(int M, int N, int K, int num_sms) {
+  if (M > 256 || K < 512 || N < 64) return 0;
+  const int BN = M <= 128 ? 128 : 64;
   const int n_tiles = (N + BN - 1) / BN;
   const int num_kb = (K + kBK - 1) / kBK;
   int S = 8;
   while (S > 1 && (n_tiles * S > (num_sms * 3) / 2 || num_kb / S < 2)) S >>= 1;
-  if (S == 1) return false;
+  return S == 1 ? 0 : S;
+}
+
+// Returns false when the shape is not one this kernel serves (the caller then uses the general GEMM).
+bool launch_gemm_skinny(const void* a, long long lda, const void* b, long long ldb, void* d, long long ldd, int M, int N, int K,
+                        const void* bias, const void* residual, long long ldr, int* status, int num_sms, cudaStream_t stream,
+                        long long* trace, const float* ss_in, float* ss_out, float eps) {
+  const int S = gemm_skinny_splits(M, N, K, num_sms);
+  if (S == 0) return false;
+  const int MT = M <= 128 ? 1 : 2;
+  const int BN = MT == 1 ? 128 : 64;
+  const int n_tiles = (N + BN - 1) / BN;
   const CUtensorMap ta = make_tmap_2d(a, K, M, lda, 64, kBM);
   const CUtensorMap tb = make_tmap_2d(b, K, N, ldb, 64, BN);
   SkParams p;
@@ -371,6 +403,10 @@ bool launch_gemm_skinny(const void* a, long long lda, const void* b, long long l
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   p.ldr = ldr;
+  p.ss_in = ss_in;
+  p.ss_out = ss_out;
+  p.inv_k = 1.f / (float)K;
+  p.eps = eps;
   p.status = status;
   p.trace = trace;
   if (MT == 1) launch_sk<128, 1, 4>(ta, tb, p, S, n_tiles, stream);

@@ -168,6 +168,32 @@ bool launch_gemm_rs_bf16(const void* a, long long lda, const void* b, long long 
   return true;
 }
 
+// act[M, F] = silu(rs * (a . Wg^T)) * (rs * (a . Wu^T)) with b = [Wg; Wu] stacked ([2F, K], the fused gate/up weight).
+bool launch_gemm_swiglu_bf16(const void* a, long long lda, const void* b, long long ldb, void* d, long long ldd, int M, int F,
+                             int K, const float* ss_in, float eps, int* status, int num_sms, cudaStream_t stream) {
+  if (F % 8 != 0 || M <= 0 || F <= 0) return false;
+  const int tiles_m = (M + kGemmBM - 1) / kGemmBM;
+  const int BN = ((long long)tiles_m * ((2 * F + 127) / 128) >= 120) ? 128 : 64;
+  const CUtensorMap ta = make_tmap_2d(a, K, M, lda, 64, kGemmBM);
+  const CUtensorMap tb = make_tmap_2d(b, K, 2 * F, ldb, 64, BN / 2);
+  GemmShape p;
+  p.M = M; p.N = 2 * ((F + BN / 2 - 1) / (BN / 2)) * (BN / 2); p.K = K;
+  p.group_n = 1;
+  p.status = status;
+  p.dual_b = F;
+  SwigluEpilogue e;
+  e.D = reinterpret_cast<__nv_bfloat16*>(d);
+  e.ldd = ldd;
+  e.F = F;
+  e.bn = BN;
+  e.ss_in = ss_in;
+  e.inv_k = 1.f / (float)K;
+  e.eps = eps;
+  if (BN == 128) gemm_launch<128, false, false>(ta, tb, p, e, num_sms, stream);
+  else gemm_launch<64, false, false>(ta, tb, p, e, num_sms, stream);
+  return true;
+}
+
 bool launch_unit_gather(const GatherArgs& g, int n_ctas, int* status, cudaStream_t stream) {
   if (!gather_args_ok(g) || n_ctas < 1) return false;
   GatherJob gj = make_gather_job(g, n_ctas);

@@ -16,6 +16,7 @@
 #include <string>
 
 #include "../common/ptx.cuh"
+#include "../launchers.h"
 
 namespace agrpo {
 
@@ -26,6 +27,10 @@ struct GemmShape {
   int M, N, K;
   int group_n;        // column-tiles per work item (1 for a plain GEMM)
   int* status;        // error word, may be nullptr
+  // > 0 (K-major B only): a column tile is made of two half tiles of B rows, [t * BN/2, ...) and
+  // [dual_b + t * BN/2, ...): accumulator columns [0, BN/2) and [BN/2, BN) of tile t then hold the two projections of
+  // the same output columns (gate and up of a SwiGLU MLP). N counts both halves (2 * dual_b).
+  int dual_b = 0;
 };
 
 // Default epilogue: D = alpha * acc (+ bias) (+ D), bf16 or fp32 output.
@@ -106,6 +111,66 @@ struct StoreEpilogue {
             d[i] = __float2bfloat16(o);
           }
       }
+    }
+  }
+};
+
+// SwiGLU epilogue for a dual-B GEMM (GemmShape::dual_b): out[m, j] = silu(rs * g) * (rs * u) where g and u are the two
+// halves of the accumulator tile and rs[m] = rsqrt(ss_in[m] / K + eps) is the optional folded-RMSNorm row scale (see
+// gemm_splitk.cu). Replaces the gate/up GEMM + separate SwiGLU kernel (and the norm kernel before them) in the
+// decode step; bn is the kernel's column tile (64 or 128).
+struct SwigluEpilogue {
+  __nv_bfloat16* D;     // [M, F]
+  long long ldd;
+  int F;
+  int bn;
+  const float* ss_in;   // [M] or nullptr
+  float inv_k;
+  float eps;
+  float g0[32], g1[32];
+  float rs;
+
+  __device__ __forceinline__ void item_begin(int row, int M, int) {
+    rs = (ss_in != nullptr && row < M) ? rsqrtf(ss_in[row] * inv_k + eps) : 1.f;
+  }
+  __device__ __forceinline__ void item_end(int, int, int, int) {}
+  __device__ __forceinline__ void chunk(int row, int col0, const uint32_t (&r)[32], int M, int) {
+    const int half = bn >> 1;
+    const int j = col0 % bn;
+    if (j < half) {
+      if (j == 0) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) g0[i] = __uint_as_float(r[i]) * rs;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) g1[i] = __uint_as_float(r[i]) * rs;
+      }
+      return;
+    }
+    const int jj = j - half;
+    const int col = (col0 / bn) * half + jj;
+    if (row >= M || col >= F) return;
+    float o[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float g = jj == 0 ? g0[i] : g1[i];
+      const float u = __uint_as_float(r[i]) * rs;
+      o[i] = g / (1.f + __expf(-g)) * u;
+    }
+    __nv_bfloat16* d = D + static_cast<long long>(row) * ldd + col;
+    if (col + 32 <= F && ((reinterpret_cast<uintptr_t>(d) & 15) == 0)) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 8) {
+        uint4 w;
+        w.x = pack_bf16x2(o[i], o[i + 1]);
+        w.y = pack_bf16x2(o[i + 2], o[i + 3]);
+        w.z = pack_bf16x2(o[i + 4], o[i + 5]);
+        w.w = pack_bf16x2(o[i + 6], o[i + 7]);
+        *reinterpret_cast<uint4*>(d + i) = w;
+      }
+    } else {
+      for (int i = 0; i < 32; ++i)
+        if (col + i < F) d[i] = __float2bfloat16(o[i]);
     }
   }
 };
@@ -367,6 +432,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  // everything above (barriers, tensor-map prefetch, TMEM allocation) overlapped the previous kernel's tail
+  pdl_wait();
+  pdl_launch();
   const uint32_t tmem_base = *tmem_slot;
   // with a gather job the first n_copy CTAs are copiers and the work items are spread over the others
   const int first_cta = Gather::kEnabled ? gj.n_copy : 0;
@@ -416,7 +484,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               for (int j = 0; j < kGemmBM / 64; ++j) tma_load_2d(sa + j * 8192, &tmA, &full_bar[stage], m0 + j * 64, k0);
             }
             if constexpr (!B_MN) {
-              tma_load_2d(sb, &tmB, &full_bar[stage], k0, n0);
+              if (p.dual_b > 0) {  // the tensor map's box is BN/2 rows high in this mode
+                tma_load_2d(sb, &tmB, &full_bar[stage], k0, n0 / 2);
+                tma_load_2d(sb + (BN / 2) * (kGemmBK * 2), &tmB, &full_bar[stage], k0, p.dual_b + n0 / 2);
+              } else {
+                tma_load_2d(sb, &tmB, &full_bar[stage], k0, n0);
+              }
             } else {
 #pragma unroll
               for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tmB, &full_bar[stage], n0 + j * 64, k0);
@@ -535,7 +608,17 @@ inline void gemm_launch(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
   const int n_copy = Gather::kEnabled ? gj.n_copy : 0;
   const int workers = items < num_sms - n_copy ? items : num_sms - n_copy;
   const int grid = workers + n_copy;
-  kernel<<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, p, epi, gj);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = S::kTotal;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_flag() ? 1 : 0;
+  check_cuda(cudaLaunchKernelEx(&cfg, kernel, ta, tb, p, epi, gj), "gemm_tcgen05 launch");
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string("gemm_tcgen05 launch: ") + cudaGetErrorString(e));
 }

@@ -71,6 +71,8 @@ __global__ void rope_kv_write_decode_kernel(__nv_bfloat16* __restrict__ qkv, lon
                                             int max_blocks, const int* __restrict__ seq_lens, __nv_bfloat16* __restrict__ k_cache,
                                             __nv_bfloat16* __restrict__ v_cache, int B, int Hq, int Hkv, int D, int block_size,
                                             int num_cache_blocks, int* status) {
+  pdl_wait();
+  pdl_launch();
   const int b = blockIdx.x;
   if (b >= B) return;
   const int len = seq_lens[b];
@@ -171,6 +173,8 @@ __device__ __forceinline__ uint8_t* tile_chunk(uint8_t* tile, int row, int chunk
 __global__ void __launch_bounds__(kDecWarps * 32)
 paged_decode_attn_kernel(const DecodeParams p) {
   extern __shared__ __align__(128) uint8_t dsm[];
+  pdl_wait();
+  pdl_launch();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int seq_len = p.seq_lens[b];
@@ -336,6 +340,8 @@ paged_decode_attn_kernel(const DecodeParams p) {
 
 __global__ void paged_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int splits,
                                             int Hkv, int G, __nv_bfloat16* __restrict__ out, long long ldo) {
+  pdl_wait();
+  pdl_launch();
   const int b = blockIdx.y, kvh = blockIdx.x;
   for (int idx = threadIdx.x; idx < G * kDecD; idx += blockDim.x) {
     const int g = idx / kDecD, d = idx % kDecD;
@@ -438,6 +444,8 @@ __global__ void lm_sample_combine_kernel(const float* __restrict__ part_best, co
                                          const float* __restrict__ part_z, const float* __restrict__ part_m,
                                          const float* __restrict__ part_s, int groups, int rows, int* __restrict__ tokens,
                                          float* __restrict__ logprobs) {
+  pdl_wait();
+  pdl_launch();
   const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (r >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -511,10 +519,9 @@ void launch_rope_kv_write_decode(void* qkv, long long row_pitch, const float* co
                                  int Hq, int Hkv, int D, int block_size, int num_cache_blocks, int* status, cudaStream_t s) {
   if (B == 0) return;
   AGRPO_PREFER_SMEM(rope_kv_write_decode_kernel);
-  rope_kv_write_decode_kernel<<<B, 128, 0, s>>>((__nv_bfloat16*)qkv, row_pitch, cos_t, sin_t, max_pos, block_tables, max_blocks,
-                                                seq_lens, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, B, Hq, Hkv, D, block_size,
-                                                num_cache_blocks, status);
-  check_cuda(cudaGetLastError(), "rope_kv_write_decode");
+  launch_kernel(rope_kv_write_decode_kernel, dim3(B), dim3(128), 0, s, "rope_kv_write_decode", (__nv_bfloat16*)qkv, row_pitch, cos_t,
+                sin_t, max_pos, block_tables, max_blocks, seq_lens, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, B, Hq, Hkv, D,
+                block_size, num_cache_blocks, status);
 }
 
 void launch_paged_decode_attn(const void* q, long long ldq, int q_col0, const void* k_cache, const void* v_cache,
@@ -555,13 +562,12 @@ void launch_paged_decode_attn(const void* q, long long ldq, int q_col0, const vo
   }
   dim3 grid(splits, Hkv, B);
   AGRPO_PREFER_SMEM(paged_decode_attn_kernel);
-  paged_decode_attn_kernel<<<grid, kDecWarps * 32, smem, s>>>(p);
-  check_cuda(cudaGetLastError(), "paged_decode_attn");
+  launch_kernel(paged_decode_attn_kernel, grid, dim3(kDecWarps * 32), smem, s, "paged_decode_attn", p);
   if (splits > 1) {
     dim3 g2(Hkv, B);
     AGRPO_PREFER_SMEM(paged_decode_combine_kernel);
-  paged_decode_combine_kernel<<<g2, 128, 0, s>>>(part_o, part_ml, splits, Hkv, G, (__nv_bfloat16*)out, ldo);
-    check_cuda(cudaGetLastError(), "paged_decode_combine");
+    launch_kernel(paged_decode_combine_kernel, g2, dim3(128), 0, s, "paged_decode_combine", (const float*)part_o,
+                  (const float*)part_ml, splits, Hkv, G, (__nv_bfloat16*)out, ldo);
   }
 }
 
@@ -593,9 +599,9 @@ void launch_lm_sample(const void* hidden, long long ldh, const void* weight, lon
   e.best = 0.f; e.best_z = 0.f; e.m = 0.f; e.s = 0.f; e.best_idx = 0; e.seed_lo = 0; e.seed_hi = 0;
   gemm_launch<256, false, false>(ta, tb, p, e, num_sms, stream);
   AGRPO_PREFER_SMEM(lm_sample_combine_kernel);
-  lm_sample_combine_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(e.part_best, e.part_idx, e.part_z, e.part_m, e.part_s,
-                                                                 groups, rows, tokens, logprobs);
-  check_cuda(cudaGetLastError(), "lm_sample_combine");
+  launch_kernel(lm_sample_combine_kernel, dim3((rows + 3) / 4), dim3(128), 0, stream, "lm_sample_combine", (const float*)e.part_best,
+                (const int*)e.part_idx, (const float*)e.part_z, (const float*)e.part_m, (const float*)e.part_s, groups, rows, tokens,
+                logprobs);
 }
 
 }  // namespace agrpo

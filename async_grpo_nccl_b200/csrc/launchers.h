@@ -29,6 +29,30 @@ inline void prefer_max_shared(K kernel) {
     }                                                     \
   } while (0)
 
+// Programmatic dependent launch is a per-thread switch: the rollout engine turns it on around its decode step, whose
+// ~170 short kernels then overlap each prologue (barrier set-up, TMEM allocation, first weight loads) with the tail
+// of the kernel before. Kernels launched through launch_kernel() contain griddepcontrol.wait, so they are correct
+// with the switch on or off.
+inline bool& pdl_flag() {
+  static thread_local bool on = false;
+  return on;
+}
+template <typename... KArgs, typename... Args>
+inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, const char* what,
+                          Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_flag() ? 1 : 0;
+  check_cuda(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...), what);
+}
+
 // d[M,N] = alpha * A . B^T (+ bias[N]) (+ d). bf16 operands, fp32 accumulation on tcgen05.
 //   a_mn = false: a is [M, K] row-major with pitch lda; a_mn = true: a is [K, M] row-major
 //   b_mn = false: b is [N, K] row-major with pitch ldb; b_mn = true: b is [K, N] row-major
@@ -75,16 +99,27 @@ void launch_scatter_add_f32(float* src, long long n, long long unit_rel, const S
 // The gather alone, for a unit with no GEMM to ride on.
 bool launch_unit_gather(const GatherArgs& g, int n_ctas, int* status, cudaStream_t stream);
 
+// Fused gate/up projection + SwiGLU (+ folded RMSNorm row scale, ss_in = row sums of squares of a, may be nullptr):
+// b is the stacked [2F, K] weight, d the [M, F] activation.
+bool launch_gemm_swiglu_bf16(const void* a, long long lda, const void* b, long long ldb, void* d, long long ldd, int M, int F,
+                             int K, const float* ss_in, float eps, int* status, int num_sms, cudaStream_t stream);
+
 // Decode-time shapes (M <= 256): split-K over a thread-block cluster, reduction through distributed shared memory.
 // Returns false (nothing launched) when the shape is outside what it serves. trace (optional, 16 int64 words on the
 // device) receives clock64 stamps of the kernel's phases for the first CTA: a built-in phase tracer.
 bool launch_gemm_skinny(const void* a, long long lda, const void* b, long long ldb, void* d, long long ldd, int M, int N, int K,
                         const void* bias, const void* residual, long long ldr, int* status, int num_sms, cudaStream_t stream,
-                        long long* trace = nullptr);
+                        long long* trace = nullptr, const float* ss_in = nullptr, float* ss_out = nullptr, float eps = 0.f);
+int gemm_skinny_splits(int M, int N, int K, int num_sms);
 
 // ---- bandwidth-bound decoder ops (elementwise.cu); bf16 activations, H and F multiples of 8 ----
 void launch_embedding_fwd(const int* ids, const void* table, void* out, int T, int H, int V, cudaStream_t s);
 void launch_embedding_bwd(const int* ids, const void* dout, float* dtable, int T, int H, int V, cudaStream_t s);
+// Lookup + ss[0][row] = sum of squares of the row, ss[1..n_ss)[row] = 0 (ss is [n_ss, ss_stride] fp32).
+void launch_embedding_sumsq(const int* ids, const void* table, void* out, float* ss, int n_ss, int ss_stride, int T, int H,
+                            int V, cudaStream_t s);
+// out[n, k] = w[n, k] * g[k] (bf16, K a multiple of 8).
+void launch_fold_norm_weight(const void* w, const void* g, void* out, long long n_rows, int K, cudaStream_t s);
 void launch_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int T, int H, float eps, cudaStream_t s);
 // dw (fp32 [H], may be nullptr) is accumulated with atomic adds.
 void launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw, int T,

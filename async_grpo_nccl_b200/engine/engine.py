@@ -17,6 +17,7 @@ configuration and as the greedy-decoding oracle in tests).
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
@@ -133,7 +134,23 @@ class RolloutEngine:
         self.tok_events = [torch.cuda.Event(), torch.cuda.Event()]
         self.tok_pending: List[Optional[List[Tuple[int, int, int]]]] = [None, None]
         self.step_count = 0
+        self.launches = 0
+        # ---- fused decode path (batches of up to 256 rows) ----
+        # RMSNorm weights are folded into the columns of the matrices that consume the normalised rows (private copies
+        # of wqkv and wgu, refreshed after every weight sync); the row scale rsqrt(mean(x^2) + eps) is applied in those
+        # GEMMs' epilogues from sums of squares that the producing GEMMs' epilogues accumulate. Together with the fused
+        # gate/up + SwiGLU GEMM a layer is 6 kernels instead of 9.
+        L, F, Q = cfg.num_hidden_layers, cfg.intermediate_size, cfg.qkv_dim
+        self.fused_rows = min(256, self.max_seqs)
+        self.fused_decode = F % 8 == 0 and all(
+            int(self.C.gemm_skinny_splits(m, n, k)) > 0
+            for m in range(64, self.fused_rows + 1, 64) for n, k in ((Q, H), (H, cfg.q_dim), (H, F)))
+        if self.fused_decode:
+            self.folded = torch.empty(L * (Q + 2 * F) * H, **bf)
+            self.b_ss = torch.zeros(2 * L + 1, S, dtype=torch.float32, device=self.dev)
+            self.refold_weights()
         self.use_cuda_graph = use_cuda_graph
+        self.use_pdl = os.environ.get("AGRPO_DECODE_PDL", "1") != "0"
         self.graphs: Dict[Tuple[int, float, int], torch.cuda.CUDAGraph] = {}
         self.requests: Dict[int, _Request] = {}
         self.slot_info: Dict[int, Dict[str, Any]] = {}
@@ -141,7 +158,6 @@ class RolloutEngine:
         self.next_group = 0
         self.temperature: Optional[float] = None
         self.tokens_generated = 0
-        self.launches = 0
         self.h2d_bytes = 0
         self.d2h_bytes = 0
 
@@ -259,6 +275,13 @@ class RolloutEngine:
                     info["eos_at"] = 0
 
     def _decode_forward(self, B: int, temperature: float, splits: int) -> None:
+        if self.fused_decode and B <= self.fused_rows:
+            # short kernels back to back: let each prologue overlap the tail of the kernel before (this thread only)
+            self.C.set_pdl(self.use_pdl)
+            try:
+                return self._decode_forward_fused(B, temperature, splits)
+            finally:
+                self.C.set_pdl(False)
         cfg, C, dec = self.cfg, self.C, self.dec
         cos_t, sin_t = dec.rope_tables(1)
         x, x1, h, qkv, attn, gu, act = (self.b_x[:B], self.b_x1[:B], self.b_h[:B], self.b_qkv[:B], self.b_attn[:B],
@@ -288,8 +311,58 @@ class RolloutEngine:
         self.history[self.row_ids[:B], torch.clamp(self.gen_index[:B], max=self.hist_cap - 1)] = self.b_tokens[:B]
         self.gen_index[:B].add_(1)
 
-    def _launch_count_decode(self, splits: int) -> int:
-        per_layer = 9 + (1 if splits > 1 else 0)
+    # ---- fused decode path ----
+    def _folded(self, i: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        cfg = self.cfg
+        H, F, Q = cfg.hidden_size, cfg.intermediate_size, cfg.qkv_dim
+        per = (Q + 2 * F) * H
+        base = i * per
+        return (self.folded[base: base + Q * H].view(Q, H), self.folded[base + Q * H: base + per].view(2 * F, H))
+
+    def refold_weights(self) -> None:
+        """Recomputes the norm-folded copies of wqkv and wgu from the current parameters (2 small kernels per layer)."""
+        if not self.fused_decode:
+            return
+        dec, C = self.dec, self.C
+        for i in range(self.cfg.num_hidden_layers):
+            p = f"layers.{i}."
+            fq, fg = self._folded(i)
+            C.fold_norm_weight(dec.w(p + "wqkv"), dec.w(p + "ln1"), fq)
+            C.fold_norm_weight(dec.w(p + "wgu"), dec.w(p + "ln2"), fg)
+        self.launches += 2 * self.cfg.num_hidden_layers
+
+    def _decode_forward_fused(self, B: int, temperature: float, splits: int) -> None:
+        cfg, C, dec = self.cfg, self.C, self.dec
+        cos_t, sin_t = dec.rope_tables(1)
+        x, x1, h, qkv, attn, act = (self.b_x[:B], self.b_x1[:B], self.b_h[:B], self.b_qkv[:B], self.b_attn[:B], self.b_act[:B])
+        bt, sl, ss = self.block_tables, self.seq_lens, self.b_ss
+        scale = 1.0 / math.sqrt(cfg.head_dim)
+        eps = cfg.rms_norm_eps
+        st = self.status
+        C.embedding_sumsq(self.last_tokens[:B], dec.w("embed"), x, ss)
+        for i in range(cfg.num_hidden_layers):
+            p = f"layers.{i}."
+            fq, fg = self._folded(i)
+            ok = C.gemm_decode(x, fq, qkv, dec.w(p + "bqkv") if cfg.attention_bias else None, None, ss[2 * i], None, eps, st)
+            C.rope_kv_write_decode(qkv, cos_t, sin_t, bt, sl, self._kc(i), self._vc(i), cfg.num_attention_heads,
+                                   cfg.num_key_value_heads, cfg.head_dim, st)
+            C.paged_decode_attn(qkv, self._kc(i), self._vc(i), bt, sl, attn, cfg.num_attention_heads, cfg.num_key_value_heads,
+                                cfg.head_dim, scale, splits, self.b_part_o, self.b_part_ml, st)
+            ok = C.gemm_decode(attn, dec.w(p + "wo"), x1, None, x, None, ss[2 * i + 1], eps, st) and ok
+            C.gemm_swiglu(x1, fg, act, ss[2 * i + 1], eps, st)
+            ok = C.gemm_decode(act, dec.w(p + "wd"), x, None, x1, None, ss[2 * i + 2], eps, st) and ok
+            if not ok:
+                raise RuntimeError("fused decode step: a GEMM shape is not served by the split-K kernel")
+        C.rmsnorm_fwd(x, dec.w("final_norm"), h, None, eps)
+        wl = self.layout.view(self.params, self.layout.lm_head_name())
+        C.lm_sample(h, wl, temperature, self.step_seeds, self.b_sample_f, self.b_sample_i, self.b_tokens, None, st)
+        self.last_tokens[:B].copy_(self.b_tokens[:B])
+        self.history[self.row_ids[:B], torch.clamp(self.gen_index[:B], max=self.hist_cap - 1)] = self.b_tokens[:B]
+        self.gen_index[:B].add_(1)
+
+    def _launch_count_decode(self, splits: int, B: int = 0) -> int:
+        fused = self.fused_decode and 0 < B <= self.fused_rows
+        per_layer = (6 if fused else 9) + (1 if splits > 1 else 0)
         return 1 + per_layer * self.cfg.num_hidden_layers + 3
 
     def _decode(self, plan: Dict[str, Any]) -> None:
@@ -337,7 +410,7 @@ class RolloutEngine:
             g.replay()
         else:
             self._decode_forward(B, temperature, splits)
-        self.launches += self._launch_count_decode(splits)
+        self.launches += self._launch_count_decode(splits, B)
         self.tokens_generated += len(active)
         for s in active:
             self.h_gen[s] += 1
@@ -447,8 +520,11 @@ class RolloutEngine:
 
     def update_weights_done(self) -> None:
         """Called after new weights were written into ``params`` in place; captured graphs stay valid
-        because they reference the same buffers."""
-        return
+        because they reference the same buffers. The norm-folded copies of the fused decode path are refreshed
+        here, and the caller's stream is drained so that the engine thread's next step sees them."""
+        if self.fused_decode:
+            self.refold_weights()
+            torch.cuda.current_stream(self.dev).synchronize()
 
 
 # =====================================================================================================

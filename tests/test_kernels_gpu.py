@@ -410,3 +410,55 @@ def test_gemm_reduce_scatter_emulated_owners(W):
     want[128:128 + 5000] += keep
     assert rel_err(torch.cat(shards), want) < 1e-4
     assert float(src.abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("M,H,F", [(64, 1536, 8960), (128, 512, 1408), (200, 1536, 8960)])
+def test_decode_fused_gemms_match_unfused_layer_math(M, H, F):
+    """Folded-norm split-K GEMM (row scale in, row sum of squares out) and the gate/up + SwiGLU GEMM against the plain
+    sequence rmsnorm -> linear -> swiglu in fp32."""
+    C = native()
+    torch.manual_seed(7)
+    x = torch.randn(M, H, device=DEV, dtype=torch.bfloat16) * 3
+    ln = (1 + 0.1 * torch.randn(H, device=DEV)).to(torch.bfloat16)
+    wq = (torch.randn(2048, H, device=DEV) * 0.03).to(torch.bfloat16)
+    wgu = (torch.randn(2 * F, H, device=DEV) * 0.03).to(torch.bfloat16)
+    bias = torch.randn(2048, device=DEV, dtype=torch.bfloat16)
+    res = torch.randn(M, H, device=DEV, dtype=torch.bfloat16)
+    wd = (torch.randn(H, F, device=DEV) * 0.03).to(torch.bfloat16)
+    eps = 1e-6
+    st = status_word()
+    fq, fgu = torch.empty_like(wq), torch.empty_like(wgu)
+    C.fold_norm_weight(wq, ln, fq)
+    C.fold_norm_weight(wgu, ln, fgu)
+    assert rel_err(fq, wq.float() * ln.float()) < 5e-3
+    xf = x.float()
+    ss = (xf * xf).sum(-1)
+    hn = xf * torch.rsqrt(ss / H + eps)[:, None] * ln.float()
+    # qkv-style GEMM with folded norm and bias
+    qkv = torch.empty(M, 2048, device=DEV, dtype=torch.bfloat16)
+    assert C.gemm_decode(x, fq, qkv, bias, None, ss.contiguous(), None, eps, st)
+    assert rel_err(qkv, hn @ wq.float().t() + bias.float()) < 1.5e-2
+    # gate/up + swiglu with folded norm
+    act = torch.empty(M, F, device=DEV, dtype=torch.bfloat16)
+    C.gemm_swiglu(x, fgu, act, ss.contiguous(), eps, st)
+    gu = hn @ wgu.float().t()
+    ref_act = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]
+    assert rel_err(act, ref_act) < 2e-2
+    # down-style GEMM with residual and sum-of-squares output
+    out = torch.empty(M, H, device=DEV, dtype=torch.bfloat16)
+    ss_out = torch.zeros(M, device=DEV, dtype=torch.float32)
+    assert C.gemm_decode(act, wd, out, None, res, None, ss_out, eps, st)
+    ref_out = act.float() @ wd.float().t() + res.float()
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert rel_err(out, ref_out) < 1e-2
+    assert rel_err(ss_out, (ref_out * ref_out).sum(-1)) < 1e-2
+    # embedding lookup with the statistic
+    table = torch.randn(1000, H, device=DEV, dtype=torch.bfloat16)
+    ids = torch.randint(0, 1000, (M,), device=DEV, dtype=torch.int32)
+    ssb = torch.full((5, 256), 7.0, device=DEV, dtype=torch.float32)
+    xo = torch.empty(M, H, device=DEV, dtype=torch.bfloat16)
+    C.embedding_sumsq(ids, table, xo, ssb)
+    assert torch.equal(xo, table[ids.long()])
+    assert rel_err(ssb[0, :M], (xo.float() ** 2).sum(-1)) < 1e-5
+    assert float(ssb[1:, :M].abs().max()) == 0.0 and float(ssb[1:, M:].min()) == 7.0
