@@ -626,6 +626,10 @@ py::dict decode_plan_to_dict(const agrpo::DecodePlan& p) {
 }
 }  // namespace
 
+// Kernel launchers run without the interpreter lock: the trainer, logprob and rollout threads of one process launch
+// concurrently, and a decode step must not wait for another thread's launch sequence to yield.
+#define NOGIL py::call_guard<py::gil_scoped_release>()
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   py::class_<agrpo::BlockAllocator>(m, "BlockAllocator")
       .def(py::init<int>())
@@ -665,82 +669,82 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
 
   m.def("gemm_bf16", &gemm_bf16, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("a_mn") = false,
         py::arg("b_mn") = false, py::arg("bias") = py::none(), py::arg("alpha") = 1.0, py::arg("accumulate") = false,
-        py::arg("status") = py::none(), py::arg("residual") = py::none());
+        py::arg("status") = py::none(), py::arg("residual") = py::none(), NOGIL);
   m.def("gemm_skinny_trace", &gemm_skinny_trace);
-  m.def("embedding_fwd", &embedding_fwd);
-  m.def("embedding_bwd", &embedding_bwd);
+  m.def("embedding_fwd", &embedding_fwd, NOGIL);
+  m.def("embedding_bwd", &embedding_bwd, NOGIL);
   m.def("set_pdl", [](bool on) { agrpo::pdl_flag() = on; },
         "Programmatic dependent launch for the kernels this THREAD launches next (used around the decode step).");
-  m.def("embedding_sumsq", &embedding_sumsq);
-  m.def("fold_norm_weight", &fold_norm_weight);
+  m.def("embedding_sumsq", &embedding_sumsq, NOGIL);
+  m.def("fold_norm_weight", &fold_norm_weight, NOGIL);
   m.def("gemm_decode", &gemm_decode, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("bias") = py::none(),
         py::arg("residual") = py::none(), py::arg("ss_in") = py::none(), py::arg("ss_out") = py::none(), py::arg("eps") = 1e-6,
-        py::arg("status") = py::none());
+        py::arg("status") = py::none(), NOGIL);
   m.def("gemm_skinny_splits", &gemm_skinny_splits);
   m.def("gemm_swiglu", &gemm_swiglu, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("ss_in") = py::none(), py::arg("eps") = 1e-6,
-        py::arg("status") = py::none());
+        py::arg("status") = py::none(), NOGIL);
   m.def("rmsnorm_fwd", &rmsnorm_fwd, py::arg("x"), py::arg("w"), py::arg("y"), py::arg("rstd") = py::none(),
-        py::arg("eps") = 1e-6);
+        py::arg("eps") = 1e-6, NOGIL);
   m.def("rmsnorm_bwd", &rmsnorm_bwd, py::arg("dy"), py::arg("x"), py::arg("w"), py::arg("rstd"), py::arg("dx"),
-        py::arg("dw") = py::none(), py::arg("accumulate_dx") = false);
-  m.def("colsum", &colsum);
-  m.def("rope_inplace", &rope_inplace);
-  m.def("swiglu_fwd", &swiglu_fwd);
-  m.def("swiglu_bwd", &swiglu_bwd);
-  m.def("add_bf16", &add_bf16);
+        py::arg("dw") = py::none(), py::arg("accumulate_dx") = false, NOGIL);
+  m.def("colsum", &colsum, NOGIL);
+  m.def("rope_inplace", &rope_inplace, NOGIL);
+  m.def("swiglu_fwd", &swiglu_fwd, NOGIL);
+  m.def("swiglu_bwd", &swiglu_bwd, NOGIL);
+  m.def("add_bf16", &add_bf16, NOGIL);
   m.def("attn_varlen_fwd", &attn_varlen_fwd, py::arg("qkv"), py::arg("out"), py::arg("lse"), py::arg("tiles"),
-        py::arg("Hq"), py::arg("Hkv"), py::arg("D"), py::arg("softmax_scale"), py::arg("status") = py::none());
+        py::arg("Hq"), py::arg("Hkv"), py::arg("D"), py::arg("softmax_scale"), py::arg("status") = py::none(), NOGIL);
   m.def("attn_varlen_bwd", &attn_varlen_bwd, py::arg("qkv"), py::arg("out"), py::arg("dout"), py::arg("lse"),
         py::arg("delta"), py::arg("dq_acc"), py::arg("dqkv"), py::arg("tiles"), py::arg("Hq"), py::arg("Hkv"), py::arg("D"),
-        py::arg("softmax_scale"), py::arg("status") = py::none());
+        py::arg("softmax_scale"), py::arg("status") = py::none(), NOGIL);
   m.def("lmhead_num_groups", &lmhead_num_groups);
   m.def("grpo_num_loss_stats", &grpo_num_loss_stats);
   m.def("lmhead_logprob", &lmhead_logprob, py::arg("hidden"), py::arg("weight"), py::arg("labels"), py::arg("temperature"),
         py::arg("partials"), py::arg("label_logit"), py::arg("logp") = py::none(), py::arg("entropy") = py::none(),
-        py::arg("lse") = py::none(), py::arg("status") = py::none());
+        py::arg("lse") = py::none(), py::arg("status") = py::none(), NOGIL);
   m.def("grpo_token_loss", &grpo_token_loss, py::arg("logp"), py::arg("old_logp"), py::arg("ref_logp"), py::arg("adv"),
         py::arg("labels"), py::arg("entropy"), py::arg("old_entropy"), py::arg("clip_low"), py::arg("clip_high"),
-        py::arg("clip_c"), py::arg("kl_beta"), py::arg("grad_weight"), py::arg("dlogp"), py::arg("stats"));
+        py::arg("clip_c"), py::arg("kl_beta"), py::arg("grad_weight"), py::arg("dlogp"), py::arg("stats"), NOGIL);
   m.def("lmhead_backward", &lmhead_backward, py::arg("hidden"), py::arg("weight"), py::arg("labels"), py::arg("lse"),
         py::arg("dlogp"), py::arg("temperature"), py::arg("dz_chunk"), py::arg("dh_acc"), py::arg("dweight") = py::none(),
-        py::arg("status") = py::none());
-  m.def("kv_cache_write", &kv_cache_write);
+        py::arg("status") = py::none(), NOGIL);
+  m.def("kv_cache_write", &kv_cache_write, NOGIL);
   m.def("kv_cache_write_decode", &kv_cache_write_decode, py::arg("qkv"), py::arg("block_tables"), py::arg("seq_lens"),
-        py::arg("k_cache"), py::arg("v_cache"), py::arg("Hq"), py::arg("Hkv"), py::arg("D"), py::arg("status") = py::none());
+        py::arg("k_cache"), py::arg("v_cache"), py::arg("Hq"), py::arg("Hkv"), py::arg("D"), py::arg("status") = py::none(), NOGIL);
   m.def("rope_kv_write_decode", &rope_kv_write_decode, py::arg("qkv"), py::arg("cos"), py::arg("sin"), py::arg("block_tables"),
         py::arg("seq_lens"), py::arg("k_cache"), py::arg("v_cache"), py::arg("Hq"), py::arg("Hkv"), py::arg("D"),
-        py::arg("status") = py::none());
+        py::arg("status") = py::none(), NOGIL);
   m.def("paged_decode_attn", &paged_decode_attn, py::arg("qkv"), py::arg("k_cache"), py::arg("v_cache"),
         py::arg("block_tables"), py::arg("seq_lens"), py::arg("out"), py::arg("Hq"), py::arg("Hkv"), py::arg("D"),
         py::arg("softmax_scale"), py::arg("splits") = 1, py::arg("part_o") = py::none(), py::arg("part_ml") = py::none(),
-        py::arg("status") = py::none());
+        py::arg("status") = py::none(), NOGIL);
   m.def("lm_sample_num_groups", &lm_sample_num_groups);
   m.def("lm_sample", &lm_sample, py::arg("hidden"), py::arg("weight"), py::arg("temperature"), py::arg("seeds"),
         py::arg("part_f"), py::arg("part_i"), py::arg("tokens"), py::arg("logprobs") = py::none(),
-        py::arg("status") = py::none());
+        py::arg("status") = py::none(), NOGIL);
   m.def("pack_count_tiles", &pack_count_tiles);
   m.def("pack_microbatch", &pack_microbatch);
   m.def("normalize_rewards", &normalize_rewards_cpu);
   m.def("wait_flag_probe", &wait_flag_probe);
-  m.def("flag_barrier", &flag_barrier);
-  m.def("weight_push", &weight_push);
+  m.def("flag_barrier", &flag_barrier, NOGIL);
+  m.def("weight_push", &weight_push, NOGIL);
   m.def("ag_gemm", &ag_gemm, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("a_mn") = false, py::arg("b_mn") = false,
         py::arg("bias") = py::none(), py::arg("accumulate") = false, py::arg("status") = py::none(),
         py::arg("residual") = py::none(), py::arg("src_ptrs"), py::arg("my_rank"), py::arg("staging"),
-        py::arg("n_per_owner"), py::arg("flags"), py::arg("epoch"), py::arg("chunk_elems") = 262144, py::arg("n_copy") = 16);
+        py::arg("n_per_owner"), py::arg("flags"), py::arg("epoch"), py::arg("chunk_elems") = 262144, py::arg("n_copy") = 16, NOGIL);
   m.def("gemm_rs", &gemm_rs, py::arg("a"), py::arg("b"), py::arg("a_mn"), py::arg("b_mn"), py::arg("alpha"), py::arg("dst_ptrs"),
-        py::arg("n_per_owner"), py::arg("unit_rel"), py::arg("ldd"), py::arg("status") = py::none());
+        py::arg("n_per_owner"), py::arg("unit_rel"), py::arg("ldd"), py::arg("status") = py::none(), NOGIL);
   m.def("scatter_add_f32", &scatter_add_f32, py::arg("src"), py::arg("unit_rel"), py::arg("dst_ptrs"), py::arg("n_per_owner"),
-        py::arg("zero_src") = true);
+        py::arg("zero_src") = true, NOGIL);
   m.def("unit_gather", &unit_gather, py::arg("src_ptrs"), py::arg("my_rank"), py::arg("staging"), py::arg("n_per_owner"),
-        py::arg("flags"), py::arg("epoch"), py::arg("chunk_elems") = 262144, py::arg("n_ctas") = 32, py::arg("status") = py::none());
-  m.def("rs_pull_sumsq", &rs_pull_sumsq);
-  m.def("publish_norm", &publish_norm);
-  m.def("adamw_push", &adamw_push);
-  m.def("sumsq", &sumsq);
+        py::arg("flags"), py::arg("epoch"), py::arg("chunk_elems") = 262144, py::arg("n_ctas") = 32, py::arg("status") = py::none(), NOGIL);
+  m.def("rs_pull_sumsq", &rs_pull_sumsq, NOGIL);
+  m.def("publish_norm", &publish_norm, NOGIL);
+  m.def("adamw_push", &adamw_push, NOGIL);
+  m.def("sumsq", &sumsq, NOGIL);
   m.def("adamw_step", &adamw_step, py::arg("p"), py::arg("m"), py::arg("v"), py::arg("g"), py::arg("p16") = py::none(),
         py::arg("lr") = 1e-6, py::arg("beta1") = 0.9, py::arg("beta2") = 0.999, py::arg("eps") = 1e-8,
         py::arg("wd") = 0.0, py::arg("step") = 1, py::arg("grad_scale") = 1.0, py::arg("norm_sq") = py::none(),
-        py::arg("max_norm") = 0.0, py::arg("zero_grad") = false);
-  m.def("cast_f32_bf16", &cast_f32_bf16);
+        py::arg("max_norm") = 0.0, py::arg("zero_grad") = false, NOGIL);
+  m.def("cast_f32_bf16", &cast_f32_bf16, NOGIL);
 }

@@ -10,10 +10,12 @@
 // With a handful of rows the GEMM is bound by streaming B (the weights) from HBM, and a 128 x BN output tile
 // per CTA leaves most SMs idle when N is small (N = 1536 gives 12 tiles on 148 SMs). Here the S CTAs of a
 // cluster share one output tile and split K between them: each runs the usual TMA -> tcgen05.mma pipeline over
-// its K slice into TMEM, parks its fp32 partial tile in its own shared memory, and then CTA r reduces columns
-// [r * BN / S, (r + 1) * BN / S) by reading every peer's partial through ld.shared::cluster, applies the
-// epilogue and stores bf16. No partial ever goes to global memory and no TMA cluster-multicast load is used.
-// Cross-CTA hand-off uses remote mbarrier arrives and bounded local waits.
+// its K slice into TMEM and then PUSHES its fp32 partial tile, column slice by column slice, into the shared memory of
+// the CTA that owns the slice (st.async through distributed shared memory, completing on the owner's mbarrier).
+// CTA r owns columns [r * BN / S, (r + 1) * BN / S): once the bytes of all S contributions have landed in its inbox it
+// sums them from its own shared memory, applies the epilogue and stores bf16. No partial ever goes to global memory,
+// nobody reads a peer's memory (so no CTA has to outlive its peers' reads), and no TMA load targets more than one
+// CTA. The only cross-CTA waits are the start-up cluster barrier and the bounded wait on the inbox barrier.
 #include <cuda_bf16.h>
 
 #include "../common/ptx.cuh"
@@ -94,6 +96,12 @@ __device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t addr) {
   asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
   return v;
 }
+// 16 bytes into a peer's shared memory; the peer's mbarrier counts them (complete_tx) when they land.
+__device__ __forceinline__ void st_async_f32x4(uint32_t remote_addr, float a, float b, float c, float d, uint32_t remote_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(remote_addr),
+               "f"(a), "f"(b), "f"(c), "f"(d), "r"(remote_bar)
+               : "memory");
+}
 __device__ __forceinline__ void fence_cluster_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
@@ -116,14 +124,14 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  // partial tile as float4 groups of 4 consecutive columns: part4[col / 4][row] (16-byte, conflict-free accesses)
+  // inbox: the S contributions to my column slice, as float4 groups of 4 consecutive columns:
+  // part[(peer * (w / 4) + group) * rows + row] with w = BN / S columns per owner (16-byte, conflict-free accesses)
   float4* part = reinterpret_cast<float4*>(smem + STAGES * kStageBytes);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(part) + (size_t)BN * MT * kBM * 4);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* acc_bar = empty_bar + STAGES;
-  uint64_t* parts_ready = acc_bar + 1;   // S remote arrives: every peer's partial tile is in its shared memory
-  uint64_t* reads_done = parts_ready + 1;  // S remote arrives: every peer finished reading my partial tile
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(reads_done + 1);
+  uint64_t* inbox_bar = acc_bar + 1;   // completes when all BN * MT * 128 * 4 bytes of my inbox have landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(inbox_bar + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t crank = cluster_ctarank();
@@ -140,9 +148,11 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(acc_bar, 1);
-    mbar_init(parts_ready, S);
-    mbar_init(reads_done, S);
+    mbar_init(inbox_bar, 1);
     fence_cluster_barrier_init();
+    // only warps that hold rows below M push (32 rows each): the inbox expects exactly their bytes
+    const int rows_pushed = (((p.M < MT * kBM ? p.M : MT * kBM) + 31) / 32) * 32;
+    mbar_expect_tx(inbox_bar, (uint32_t)(BN * 4 * rows_pushed));
     // The first weight (B) loads depend on nothing that another thread, CTA or the preceding kernel produces: issue
     // them before any synchronisation so that their ~2 us cold latency overlaps the prologue and, under programmatic
     // dependent launch, the tail of the previous kernel. The activation (A) loads follow once that kernel is complete.
@@ -225,10 +235,14 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
       SK_STAMP(5);
     }
   } else {
-    // ---- epilogue warps: TMEM -> own shared memory (column-major), cluster hand-off, slice reduction ----
+    // ---- epilogue warps: TMEM -> owners' inboxes (push), wait for my inbox, sum my slice, store ----
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const int w = BN / S;              // columns per owner (a power of two, at least 8)
+    const int w_shift = __ffs(w) - 1;
+    const int gpo = w / 4;             // float4 groups per owner
+    constexpr int kRows = MT * kBM;
     bool ok = true;
     if (kb1 > kb0) {
       if (!mbar_wait(acc_bar, 0)) {
@@ -238,61 +252,63 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
     }
     tc_fence_after();
     if (threadIdx.x == 64) SK_STAMP(6);
+    {
+      const uint32_t part_local = smem_u32(part);
+      const uint32_t bar_local = smem_u32(inbox_bar);
 #pragma unroll 1
-    for (int mt = 0; mt < MT; ++mt) {
+      for (int mt = 0; mt < MT; ++mt) {
+        if (mt * kBM + quarter * 32 >= p.M) continue;  // this warp's 32 rows are all padding
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        if (kb1 > kb0 && ok) {
-          tmem_ld_32x32(tmem_base + lane_off + mt * BN + c * 32, r);
-          tc_wait_ld();
-        } else {
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          if (kb1 > kb0 && ok) {
+            tmem_ld_32x32(tmem_base + lane_off + mt * BN + c * 32, r);
+            tc_wait_ld();
+          } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = 0u;
+            for (int i = 0; i < 32; ++i) r[i] = 0u;
+          }
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const int col = c * 32 + i;
+            const uint32_t owner = (uint32_t)(col >> w_shift);
+            const int g = (col - (int)owner * w) >> 2;
+            const uint32_t off = (uint32_t)((((int)crank * gpo + g) * kRows + mt * kBM + row_in_tile) * 16);
+            st_async_f32x4(mapa_shared(part_local + off, owner), __uint_as_float(r[i]), __uint_as_float(r[i + 1]),
+                           __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]), mapa_shared(bar_local, owner));
+          }
         }
-#pragma unroll
-        for (int i = 0; i < 32; i += 4)
-          part[(size_t)(c * 8 + i / 4) * (MT * kBM) + mt * kBM + row_in_tile] =
-              make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
       }
     }
-    // all 128 epilogue threads have written; one thread tells every CTA of the cluster (release at cluster scope)
-    asm volatile("bar.sync 1, 128;" ::: "memory");
     if (threadIdx.x == 64) SK_STAMP(7);
-    if (warp == 2 && lane < S) mbar_arrive_remote(mapa_shared(smem_u32(parts_ready), lane));
-    if (!mbar_wait_cluster(parts_ready, 0)) {
+    // every contribution to my slice (my own included) is counted in bytes by my inbox barrier
+    if (!mbar_wait_cluster(inbox_bar, 0)) {
       report_status(p.status, kStatusBarrierTimeout);
       ok = false;
     }
     if (threadIdx.x == 64) SK_STAMP(8);
-    // reduce my column slice over all peers
-    const int w = BN / S;              // columns per CTA (BN is a multiple of 8 * S by construction)
+    // sum my column slice over the S contributions (local shared memory)
     const int c0 = (int)crank * w;
     if (ok) {
-      const uint32_t part_addr = smem_u32(part);
 #pragma unroll 1
       for (int mt = 0; mt < MT; ++mt) {
+        if (mt * kBM + quarter * 32 >= p.M) continue;
         const int row = mt * kBM + row_in_tile;
         const float rs = (p.ss_in != nullptr && row < p.M) ? rsqrtf(p.ss_in[row] * p.inv_k + p.eps) : 1.f;
         float sq = 0.f;
 #pragma unroll 1
         for (int cb = 0; cb < w; cb += 8) {
-          float4 v[8][2];
-#pragma unroll
-          for (int peer = 0; peer < 8; ++peer) {
-            const uint32_t base = mapa_shared(part_addr, (uint32_t)(peer < S ? peer : 0));
-#pragma unroll
-            for (int i = 0; i < 2; ++i)
-              v[peer][i] = (peer < S) ? ld_dsmem_f32x4(base + (uint32_t)(((size_t)((c0 + cb) / 4 + i) * (MT * kBM) + row) * 16))
-                                      : make_float4(0.f, 0.f, 0.f, 0.f);
-          }
           float acc[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) acc[i] = 0.f;
 #pragma unroll
           for (int peer = 0; peer < 8; ++peer) {
-            acc[0] += v[peer][0].x; acc[1] += v[peer][0].y; acc[2] += v[peer][0].z; acc[3] += v[peer][0].w;
-            acc[4] += v[peer][1].x; acc[5] += v[peer][1].y; acc[6] += v[peer][1].z; acc[7] += v[peer][1].w;
+            if (peer < S) {
+              const float4 v0 = part[(size_t)(peer * gpo + cb / 4) * kRows + row];
+              const float4 v1 = part[(size_t)(peer * gpo + cb / 4 + 1) * kRows + row];
+              acc[0] += v0.x; acc[1] += v0.y; acc[2] += v0.z; acc[3] += v0.w;
+              acc[4] += v1.x; acc[5] += v1.y; acc[6] += v1.z; acc[7] += v1.w;
+            }
           }
           const int col = n0 + c0 + cb;
           if (row < p.M && col < p.N) {
@@ -329,12 +345,7 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
         if (p.ss_out != nullptr && row < p.M) atomicAdd(p.ss_out + row, sq);
       }
     }
-    // tell every peer that I am done with its shared memory, then wait until everyone is done with mine
-    asm volatile("bar.sync 1, 128;" ::: "memory");
     if (threadIdx.x == 64) SK_STAMP(9);
-    if (warp == 2 && lane < S) mbar_arrive_remote(mapa_shared(smem_u32(reads_done), lane));
-    if (!mbar_wait_cluster(reads_done, 0)) report_status(p.status, kStatusBarrierTimeout);
-    if (threadIdx.x == 64) SK_STAMP(10);
   }
 
   tc_fence_before();

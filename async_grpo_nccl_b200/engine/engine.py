@@ -144,7 +144,7 @@ class RolloutEngine:
         self.fused_rows = min(256, self.max_seqs)
         self.fused_decode = F % 8 == 0 and all(
             int(self.C.gemm_skinny_splits(m, n, k)) > 0
-            for m in range(64, self.fused_rows + 1, 64) for n, k in ((Q, H), (H, cfg.q_dim), (H, F)))
+            for m in range(32, self.fused_rows + 1, 32) for n, k in ((Q, H), (H, cfg.q_dim), (H, F)))
         if self.fused_decode:
             self.folded = torch.empty(L * (Q + 2 * F) * H, **bf)
             self.b_ss = torch.zeros(2 * L + 1, S, dtype=torch.float32, device=self.dev)
@@ -369,7 +369,7 @@ class RolloutEngine:
         rows = int(plan["batch_rows"])
         if rows == 0:
             return
-        B = min(self.max_seqs, (rows + 63) // 64 * 64)
+        B = min(self.max_seqs, (rows + 31) // 32 * 32)  # one captured graph per row count rounded to a warp of rows
         active = plan["active_slots"]
         self._apply_table_updates(plan)
         for s in active:

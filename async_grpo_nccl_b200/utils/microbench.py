@@ -7,6 +7,9 @@
     python -m async_grpo_nccl_b200.utils.microbench train --tokens 16384
     python -m async_grpo_nccl_b200.utils.microbench elementwise
     python -m async_grpo_nccl_b200.utils.microbench fused --tokens 16384
+    python -m async_grpo_nccl_b200.utils.microbench one --kernel attn_fwd      (small case for an ncu capture)
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29777 \
+        -m async_grpo_nccl_b200.utils.microbench sync --trainers 1 --model qwen2.5-1.5b,qwen2.5-7b
 
 Each line of output is a JSON record with the achieved rate and, where a library kernel exists in the image
 (cuBLAS through torch.matmul, flash-attn 2), the same measurement for it. Roofline denominators come from
@@ -165,6 +168,152 @@ def bench_fused(args):
          "local_tflops": fl / t_acc / 1e9, "frac_of_peak": fl / t_rs / 1e9 / pk["bf16_tflops"], "peak": pk["source"]})
     torch.cuda.synchronize()
     assert int(st.item()) == 0
+
+
+def bench_sync(args):
+    """Trainer -> inference weight sync over N GPUs (run under torchrun, one rank per GPU): the first --trainers ranks
+    hold the shards, the others receive. Times the peer-memory push (barrier, push kernels, barrier) and the library
+    baseline (one NCCL broadcast per shard range) on the device, max over ranks."""
+    import torch.distributed as dist
+
+    from ..models.config import PRESETS
+    from ..models.layout import ParamLayout
+    from ..ops import native
+    from ..parallel import symm
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dist.init_process_group("nccl")
+    C = native()
+    t = max(1, min(args.trainers, world - 1))
+    trainers, infer = list(range(t)), list(range(t, world))
+    for model in args.model.split(","):
+        cfg = PRESETS[model]
+        layout = ParamLayout(cfg, shard_world=t)
+        flags = symm.alloc_symmetric(128, torch.int64, dev, dist.group.WORLD)
+        dst = symm.alloc_symmetric(layout.total, torch.bfloat16, dev, dist.group.WORLD)
+
+        class _Plane:  # the two buffers a weight sync needs
+            pass
+
+        pl = _Plane()
+        pl.layout, pl.C, pl.trainer_ranks, pl.infer_ranks, pl.my_rank, pl.device = layout, C, trainers, infer, rank, dev
+        pl.flags, pl.infer_params = flags, dst
+        ws = symm.WeightSync(pl)
+        src = None
+        if rank in trainers:
+            src = (torch.randn(layout.total, device=dev) * 0.02).to(torch.bfloat16)
+        ti = trainers.index(rank) if rank in trainers else None
+
+        def timed(fn, iters=5):
+            best = []
+            for i in range(iters + 2):
+                dist.barrier()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                if i >= 2:
+                    best.append(e0.elapsed_time(e1))
+            ms = torch.tensor([sorted(best)[len(best) // 2]], device=dev)
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            return float(ms.item())
+
+        ms_push = timed(lambda: ws.push(src, ti))
+        ws.pg.check()
+        ms_nccl = timed(lambda: symm.broadcast_weights(src if src is not None else dst.local, layout, dist.group.WORLD, trainers, ti,
+                                                       dst.local if rank in infer else None))
+        if rank == 0:
+            gb = layout.total * 2 / 1e9
+            out({"bench": "weight_sync", "model": model, "trainers": t, "receivers": len(infer), "param_gb": gb,
+                 "peer_push_ms": ms_push, "peer_push_gbs_per_receiver": gb / ms_push * 1e3, "nccl_broadcast_ms": ms_nccl,
+                 "nccl_gbs_per_receiver": gb / ms_nccl * 1e3, "nvlink_peer_copy_gbs_measured": 770.0,
+                 "lower_bound_ms": gb / 770.0 * 1e3})
+        del ws, dst, src
+        torch.cuda.empty_cache()
+    dist.destroy_process_group()
+
+
+def bench_one(args):
+    """One kernel, three launches, a small case (operands of a few hundred MB at most): the program to put under
+    `ncu --set full -k regex:<kernel> -c 2`. Prints the device time of the third launch."""
+    from ..ops import native
+
+    C = native()
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    dev, bf = "cuda", torch.bfloat16
+    k = args.kernel
+    if k == "gemm":
+        a = torch.randn(8192, 8192, device=dev, dtype=bf)
+        b = torch.randn(8192, 8192, device=dev, dtype=bf)
+        d = torch.empty(8192, 8192, device=dev, dtype=bf)
+        fn = lambda: C.gemm_bf16(a, b, d, False, False, None, 1.0, False, st, None)
+    elif k in ("attn_fwd", "attn_bwd"):
+        Hq, Hkv, D, lens = 12, 2, 128, [8192, 8192]
+        T, Cc = sum(lens), (Hq + 2 * Hkv) * D
+        qkv = torch.randn(T, Cc, device=dev).to(bf)
+        o = torch.zeros(T, Hq * D, device=dev, dtype=bf)
+        lse = torch.zeros(Hq, T, device=dev)
+        tiles = _tiles(lens)
+        sc = 1 / math.sqrt(D)
+        C.attn_varlen_fwd(qkv, o, lse, tiles, Hq, Hkv, D, sc, st)
+        if k == "attn_fwd":
+            fn = lambda: C.attn_varlen_fwd(qkv, o, lse, tiles, Hq, Hkv, D, sc, st)
+        else:
+            dout = torch.randn(T, Hq * D, device=dev).to(bf)
+            delta, dq_acc = torch.empty(Hq, T, device=dev), torch.empty(T, Hq * D, device=dev)
+            dqkv = torch.zeros(T, Cc, device=dev, dtype=bf)
+            fn = lambda: C.attn_varlen_bwd(qkv, o, dout, lse, delta, dq_acc, dqkv, tiles, Hq, Hkv, D, sc, st)
+    elif k in ("lmhead_fwd", "lmhead_bwd"):
+        T, H, V = 8192, 1536, 151936
+        h = torch.randn(T, H, device=dev).to(bf)
+        W = (torch.randn(V, H, device=dev) * 0.02).to(bf)
+        labels = torch.randint(0, V, (T,), device=dev, dtype=torch.int32)
+        groups = C.lmhead_num_groups(V, T)
+        partials, ll = torch.empty(3 * groups * T, device=dev), torch.zeros(T, device=dev)
+        logp, ent, lse = (torch.empty(T, device=dev) for _ in range(3))
+        C.lmhead_logprob(h, W, labels, 1.0, partials, ll, logp, ent, lse, st)
+        if k == "lmhead_fwd":
+            fn = lambda: C.lmhead_logprob(h, W, labels, 1.0, partials, ll, logp, ent, lse, st)
+        else:
+            dlogp = torch.randn(T, device=dev) / T
+            dz = torch.empty(T, 4096, device=dev, dtype=bf)
+            dh, dW = torch.empty(T, H, device=dev), torch.zeros(V, H, device=dev)
+            fn = lambda: C.lmhead_backward(h, W, labels, lse, dlogp, 1.0, dz, dh, dW, st)
+    elif k in ("splitk", "swiglu"):
+        M, H, F = 128, 1536, 8960
+        x = torch.randn(M, F if k == "splitk" else H, device=dev, dtype=bf)
+        ss = torch.full((M,), float(H), device=dev)
+        if k == "splitk":
+            w, d = torch.randn(H, F, device=dev, dtype=bf), torch.empty(M, H, device=dev, dtype=bf)
+            res = torch.randn(M, H, device=dev, dtype=bf)
+            sso = torch.zeros(M, device=dev)
+            fn = lambda: C.gemm_decode(x, w, d, None, res, None, sso, 1e-6, st)
+        else:
+            w, d = torch.randn(2 * F, H, device=dev, dtype=bf), torch.empty(M, F, device=dev, dtype=bf)
+            fn = lambda: C.gemm_swiglu(x, w, d, ss, 1e-6, st)
+    elif k == "gemm_rs":
+        T, No, Ki, W = 16384, 17920, 1536, 4
+        n_per = (No * Ki + 4096 + 128 * W - 1) // (128 * W) * 128
+        dy, x = torch.randn(T, No, device=dev, dtype=bf), torch.randn(T, Ki, device=dev, dtype=bf)
+        sh = [torch.zeros(n_per, device=dev) for _ in range(W)]
+        ptrs = [t.data_ptr() for t in sh]
+        fn = lambda: C.gemm_rs(dy, x, True, True, 1.0, ptrs, n_per, 4096, Ki, st)
+    else:
+        raise SystemExit(f"unknown kernel {k}")
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    fn()
+    e1.record()
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    out({"bench": "one", "kernel": k, "ms": e0.elapsed_time(e1)})
 
 
 def _tiles(lens):
@@ -371,7 +520,10 @@ def bench_train(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn", "lmhead", "elementwise", "decode", "train", "fused"])
+    ap.add_argument("what", choices=["gemm", "attn", "lmhead", "elementwise", "decode", "train", "fused", "one", "sync"])
+    ap.add_argument("--kernel", default="gemm", help="for 'one': gemm | attn_fwd | attn_bwd | lmhead_fwd | lmhead_bwd | splitk | "
+                    "swiglu | gemm_rs")
+    ap.add_argument("--trainers", type=int, default=1, help="for 'sync': ranks that hold shards (the rest receive)")
     ap.add_argument("--model", default="qwen2.5-1.5b")
     ap.add_argument("--batch", type=int, default=128)
     ap.add_argument("--context", type=int, default=1024)
@@ -382,7 +534,7 @@ def main():
     ap.add_argument("--recompute", action="store_true")
     args = ap.parse_args()
     {"gemm": bench_gemm, "attn": bench_attn, "lmhead": bench_lmhead, "elementwise": bench_elementwise, "decode": bench_decode,
-     "train": bench_train, "fused": bench_fused}[args.what](args)
+     "train": bench_train, "fused": bench_fused, "one": bench_one, "sync": bench_sync}[args.what](args)
 
 
 if __name__ == "__main__":
