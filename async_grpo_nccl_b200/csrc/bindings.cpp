@@ -531,6 +531,22 @@ void weight_push(const Tensor& src, int64_t local_off, int64_t global_off, int64
   agrpo::launch_weight_push(src.data_ptr(), src.scalar_type() == torch::kFloat32, local_off, global_off, n, lptr(dst_ptrs),
                             (int)dst_ptrs.size(), cur_stream());
 }
+void weight_push_mc(const Tensor& src, int64_t local_off, int64_t global_off, int64_t n, int64_t mc_ptr) {
+  TORCH_CHECK(src.is_cuda() && src.is_contiguous() && (src.scalar_type() == torch::kFloat32 || src.scalar_type() == torch::kBFloat16), "weight_push_mc: src");
+  TORCH_CHECK(local_off >= 0 && local_off + n <= src.numel() && local_off % 8 == 0 && global_off % 8 == 0 && n % 8 == 0, "weight_push_mc: range");
+  TORCH_CHECK(mc_ptr != 0 && (mc_ptr & 15) == 0, "weight_push_mc: multicast address");
+  const c10::cuda::CUDAGuard guard(src.device());
+  agrpo::launch_weight_push_mc(src.data_ptr(), src.scalar_type() == torch::kFloat32, local_off, global_off, n,
+                               reinterpret_cast<void*>(mc_ptr), cur_stream());
+}
+void rs_pull_sumsq_mc(int64_t mc_ptr, int64_t global_off, int64_t local_off, int64_t n, Tensor& out, Tensor& norm_sq) {
+  check_f32(out, "out"); check_f32(norm_sq, "norm_sq");
+  TORCH_CHECK(out.is_contiguous() && local_off + n <= out.numel() && local_off % 4 == 0 && global_off % 4 == 0 && n % 4 == 0, "rs_pull_mc: range");
+  TORCH_CHECK(mc_ptr != 0 && (mc_ptr & 15) == 0, "rs_pull_mc: multicast address");
+  const c10::cuda::CUDAGuard guard(out.device());
+  agrpo::launch_rs_pull_sumsq_mc(reinterpret_cast<const void*>(mc_ptr), global_off, local_off, n, out.data_ptr<float>(),
+                                 norm_sq.data_ptr<float>(), cur_stream());
+}
 void rs_pull_sumsq(const PtrList& grad_ptrs, int64_t my_rank, int64_t global_off, int64_t local_off, int64_t n, Tensor& out,
                    Tensor& norm_sq) {
   check_f32(out, "out"); check_f32(norm_sq, "norm_sq");
@@ -738,6 +754,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("zero_src") = true, NOGIL);
   m.def("unit_gather", &unit_gather, py::arg("src_ptrs"), py::arg("my_rank"), py::arg("staging"), py::arg("n_per_owner"),
         py::arg("flags"), py::arg("epoch"), py::arg("chunk_elems") = 262144, py::arg("n_ctas") = 32, py::arg("status") = py::none(), NOGIL);
+  m.def("weight_push_mc", &weight_push_mc, NOGIL);
+  m.def("rs_pull_sumsq_mc", &rs_pull_sumsq_mc, NOGIL);
   m.def("rs_pull_sumsq", &rs_pull_sumsq, NOGIL);
   m.def("publish_norm", &publish_norm, NOGIL);
   m.def("adamw_push", &adamw_push, NOGIL);

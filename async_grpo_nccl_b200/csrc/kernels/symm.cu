@@ -134,6 +134,65 @@ __global__ void rs_pull_sumsq_kernel(PeerPtrs grads, int my_rank, long long glob
   }
 }
 
+// NVSwitch multicast (NVLS) variants. `mc` is the multicast address of a symmetric buffer: one store to it lands in
+// every rank's copy, one ld_reduce from it returns the sum over every rank's copy, both done inside the switch.
+//
+// Weight push: each 16-byte group is written once and replicated by the switch, so the source's egress does not grow
+// with the number of receivers.
+template <typename SrcT>
+__global__ void weight_push_mc_kernel(const SrcT* __restrict__ src, long long local_off, long long global_off, long long n,
+                                      __nv_bfloat16* mc) {
+  const long long n8 = n / 8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    uint4 w;
+    if constexpr (sizeof(SrcT) == 4) {
+      const float4 a = reinterpret_cast<const float4*>(src + local_off)[2 * i];
+      const float4 b = reinterpret_cast<const float4*>(src + local_off)[2 * i + 1];
+      w.x = pack_bf16x2(a.x, a.y);
+      w.y = pack_bf16x2(a.z, a.w);
+      w.z = pack_bf16x2(b.x, b.y);
+      w.w = pack_bf16x2(b.z, b.w);
+    } else {
+      w = reinterpret_cast<const uint4*>(src + local_off)[i];
+    }
+    uint4* d = reinterpret_cast<uint4*>(mc + global_off) + i;
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(d), "f"(__uint_as_float(w.x)),
+                 "f"(__uint_as_float(w.y)), "f"(__uint_as_float(w.z)), "f"(__uint_as_float(w.w))
+                 : "memory");
+  }
+  __threadfence_system();
+}
+
+// Gradient reduce-scatter with the addition done in the switch: out[local_off + i] = sum over ALL ranks of the
+// multicast group of grads[global_off + i] (ranks that are not trainers hold zeros); *norm_sq += sum(out^2).
+__global__ void rs_pull_sumsq_mc_kernel(const float* mc, long long global_off, long long local_off, long long n,
+                                        float* __restrict__ out, float* __restrict__ norm_sq) {
+  float acc2 = 0.f;
+  const long long n4 = n / 4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    float4 s;
+    const float4* a = reinterpret_cast<const float4*>(mc + global_off) + i;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(s.x), "=f"(s.y), "=f"(s.z), "=f"(s.w)
+                 : "l"(a)
+                 : "memory");
+    reinterpret_cast<float4*>(out + local_off)[i] = s;
+    acc2 += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc2 += __shfl_xor_sync(0xffffffffu, acc2, o);
+  __shared__ float sm[32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) sm[warp] = acc2;
+  __syncthreads();
+  if (warp == 0) {
+    acc2 = lane < (int)(blockDim.x >> 5) ? sm[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc2 += __shfl_xor_sync(0xffffffffu, acc2, o);
+    if (lane == 0 && acc2 != 0.f) atomicAdd(norm_sq, acc2);
+  }
+}
+
 // Publishes this rank's squared-norm partial into slot my_rank of every peer's partial table.
 __global__ void publish_norm_kernel(const float* norm_sq, PeerPtrs tables, int my_rank) {
   const int r = threadIdx.x;
@@ -221,6 +280,21 @@ void launch_scatter_add_f32(float* src, long long n, long long unit_rel, const S
   for (int r = 0; r < sc.world; ++r) d.p[r] = sc.dst[r];
   scatter_add_f32_kernel<<<blocks_for(n / 4 + 1), 256, 0, s>>>(src, n, unit_rel, d, sc.n_per_owner, zero_src ? 1 : 0);
   check_cuda(cudaGetLastError(), "scatter_add_f32");
+}
+
+void launch_weight_push_mc(const void* src, bool src_fp32, long long local_off, long long global_off, long long n, void* mc,
+                           cudaStream_t s) {
+  if (n == 0) return;
+  if (src_fp32) weight_push_mc_kernel<float><<<blocks_for(n / 8), 256, 0, s>>>((const float*)src, local_off, global_off, n, (__nv_bfloat16*)mc);
+  else weight_push_mc_kernel<__nv_bfloat16><<<blocks_for(n / 8), 256, 0, s>>>((const __nv_bfloat16*)src, local_off, global_off, n, (__nv_bfloat16*)mc);
+  check_cuda(cudaGetLastError(), "weight_push_mc");
+}
+
+void launch_rs_pull_sumsq_mc(const void* mc, long long global_off, long long local_off, long long n, float* out, float* norm_sq,
+                             cudaStream_t s) {
+  if (n == 0) return;
+  rs_pull_sumsq_mc_kernel<<<blocks_for(n / 4), 256, 0, s>>>((const float*)mc, global_off, local_off, n, out, norm_sq);
+  check_cuda(cudaGetLastError(), "rs_pull_sumsq_mc");
 }
 
 void launch_rs_pull_sumsq(const long long* grad_ptrs, int world, int my_rank, long long global_off, long long local_off,

@@ -206,6 +206,12 @@ void launch_flag_barrier(const long long* flag_ptrs, int world, int my_rank, uns
                          int* status, cudaStream_t s);
 void launch_weight_push(const void* src, bool src_fp32, long long local_off, long long global_off, long long n,
                         const long long* dst_ptrs, int n_dst, cudaStream_t s);
+// NVSwitch multicast variants (mc = multicast address of the symmetric buffer): the push is replicated by the switch,
+// the reduce-scatter adds inside the switch over every rank of the multicast group.
+void launch_weight_push_mc(const void* src, bool src_fp32, long long local_off, long long global_off, long long n, void* mc,
+                           cudaStream_t s);
+void launch_rs_pull_sumsq_mc(const void* mc, long long global_off, long long local_off, long long n, float* out, float* norm_sq,
+                             cudaStream_t s);
 void launch_rs_pull_sumsq(const long long* grad_ptrs, int world, int my_rank, long long global_off, long long local_off,
                           long long n, float* out, float* norm_sq, cudaStream_t s);
 void launch_publish_norm(const float* norm_sq, const long long* table_ptrs, int world, int my_rank, cudaStream_t s);

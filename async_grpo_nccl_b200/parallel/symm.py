@@ -32,6 +32,20 @@ WAIT_BUDGET_S = 20.0  # a barrier partner may legitimately be busy for seconds (
 class SymmetricBuffer:
     def __init__(self, local: torch.Tensor, peer_ptrs: List[int], handle: Any):
         self.local, self.peer_ptrs, self.handle = local, peer_ptrs, handle
+        # NVSwitch multicast address of the buffer (0 when the fabric or the driver offers none): one store to it
+        # lands in every rank's copy, one ld_reduce from it sums every rank's copy inside the switch
+        try:
+            self.mc_ptr = int(getattr(handle, "multicast_ptr", 0) or 0)
+        except Exception:
+            self.mc_ptr = 0
+
+
+def multicast_enabled() -> bool:
+    """NVLS (multimem) variants of the weight push and the gradient reduce-scatter are used when the symmetric
+    allocation comes with a multicast address, unless AGRPO_MULTICAST=0."""
+    import os
+
+    return os.environ.get("AGRPO_MULTICAST", "1") != "0"
 
 
 def symmetric_available() -> bool:
@@ -148,6 +162,9 @@ class TrainerComm:
         self.param_ptrs = [plane.train_params.peer_ptrs[r] for r in tr]
         self.norm_ptrs = [plane.norm_tab.peer_ptrs[r] for r in tr]
         self.norm_local = torch.zeros(1, dtype=torch.float32, device=plane.device)
+        # in-switch reduction: valid because every rank of the job holds a gradient buffer of the same shape and the
+        # ranks that do not train never write theirs (it stays zero)
+        self.grads_mc = plane.grads.mc_ptr if multicast_enabled() else 0
 
     @property
     def param_buffer(self) -> torch.Tensor:
@@ -167,7 +184,10 @@ class TrainerComm:
         self.pg.barrier()  # every rank's backward has finished and its gradients are visible
         self.norm_local.zero_()
         for u, (lo, gs, ln) in enumerate(L.local_to_global_ranges(self.rank)):
-            C.rs_pull_sumsq(self.grad_ptrs, self.rank, gs, lo, ln, grad_shard, self.norm_local)
+            if self.grads_mc:
+                C.rs_pull_sumsq_mc(self.grads_mc, gs, lo, ln, grad_shard, self.norm_local)
+            else:
+                C.rs_pull_sumsq(self.grad_ptrs, self.rank, gs, lo, ln, grad_shard, self.norm_local)
         C.publish_norm(self.norm_local, self.norm_ptrs, self.rank)
         self.pg.barrier()  # all partials have landed; all peers are done reading my gradient buffer
         self.grad_buffer.zero_()
@@ -195,6 +215,9 @@ class WeightSync:
         world = list(range(dist.get_world_size()))
         self.pg = PeerGroup(plane.flags, world, plane.my_rank, plane.device, plane.C, slot_base=64)
         self.dst_ptrs = [plane.infer_params.peer_ptrs[r] for r in self.infer_ranks]
+        # multicast push: the switch replicates every store into all ranks' buffers (also into the unused copies of
+        # ranks that host no inference role), so a trainer's egress does not grow with the number of receivers
+        self.dst_mc = plane.infer_params.mc_ptr if (multicast_enabled() and len(self.infer_ranks) > 1) else 0
 
     @property
     def buffer(self) -> torch.Tensor:
@@ -212,7 +235,10 @@ class WeightSync:
                 s, e = self.layout.unit_ranges[u]
                 n = (e - s) // t
                 a = s + trainer_index * n
-                self.C.weight_push(src_params, lo if sharded_src else a, a, n, self.dst_ptrs)
+                if self.dst_mc:
+                    self.C.weight_push_mc(src_params, lo if sharded_src else a, a, n, self.dst_mc)
+                else:
+                    self.C.weight_push(src_params, lo if sharded_src else a, a, n, self.dst_ptrs)
                 lo += n
         self.pg.barrier()  # all shards have landed everywhere
 

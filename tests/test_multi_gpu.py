@@ -13,8 +13,9 @@ pytestmark = pytest.mark.gpu
 
 
 def _worker(rank, world, port, q):
+    # this worker ends with a failure-detection case: NVLS off in NCCL and plain peer loads in our own kernels
     os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank), "MASTER_ADDR": "127.0.0.1",
-                       "MASTER_PORT": str(port), "NCCL_NVLS_ENABLE": "0"})
+                       "MASTER_PORT": str(port), "NCCL_NVLS_ENABLE": "0", "AGRPO_MULTICAST": "0"})
     import torch.distributed as dist
 
     from async_grpo_nccl_b200.models.config import PRESETS
@@ -232,5 +233,80 @@ def test_fully_sharded_trainer_matches_resident_trainer():
     results = [q.get(timeout=300) for _ in range(world)]
     for p in procs:
         p.join(timeout=60)
+    for rank, msg in results:
+        assert msg == "ok", f"rank {rank}: {msg}"
+
+
+def _worker_multicast(rank, world, port, q):
+    """NVSwitch multicast variants (multimem.st push, multimem.ld_reduce reduce-scatter) against plain tensors. Not a
+    failure test: every rank stays to the end."""
+    os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank), "MASTER_ADDR": "127.0.0.1",
+                       "MASTER_PORT": str(port)})
+    import torch.distributed as dist
+
+    from async_grpo_nccl_b200.ops import native
+    from async_grpo_nccl_b200.parallel import symm
+
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world)
+    try:
+        C = native()
+        n = 1 << 22
+        flags = symm.alloc_symmetric(128, torch.int64, dev, dist.group.WORLD)
+        wbuf = symm.alloc_symmetric(n, torch.bfloat16, dev, dist.group.WORLD)
+        gbuf = symm.alloc_symmetric(n, torch.float32, dev, dist.group.WORLD)
+        if not wbuf.mc_ptr or not gbuf.mc_ptr:
+            q.put((rank, "skip: no multicast address on this fabric"))
+            return
+        pg = symm.PeerGroup(flags, list(range(world)), rank, dev, C)
+        # push: rank r owns the r-th slice and writes it once through the multicast address
+        per = n // world
+        src = torch.randn(n, device=dev, generator=torch.Generator(device=dev).manual_seed(7)).to(torch.bfloat16)  # same on all ranks
+        pg.barrier()
+        C.weight_push_mc(src, rank * per, rank * per, per, wbuf.mc_ptr)
+        pg.barrier()
+        torch.cuda.synchronize()
+        pg.check()
+        assert torch.equal(wbuf.local, src), "multicast push is not bit-exact"
+        # in-switch reduction of every rank's gradient buffer
+        g = torch.randn(n, device=dev, generator=torch.Generator(device=dev).manual_seed(100 + rank))
+        gbuf.local.copy_(g)
+        total = g.clone()
+        dist.all_reduce(total)
+        pg.barrier()
+        out = torch.zeros(per, device=dev)
+        nsq = torch.zeros(1, device=dev)
+        C.rs_pull_sumsq_mc(gbuf.mc_ptr, rank * per, 0, per, out, nsq)
+        pg.barrier()
+        torch.cuda.synchronize()
+        pg.check()
+        want = total[rank * per:(rank + 1) * per]
+        assert torch.allclose(out, want, rtol=1e-5, atol=1e-5), "in-switch reduce-scatter mismatch"
+        assert abs(nsq.item() - want.double().pow(2).sum().item()) < 1e-3 * want.double().pow(2).sum().item()
+        q.put((rank, "ok"))
+    except Exception as e:
+        import traceback
+
+        q.put((rank, f"FAILED: {e!r}\n{traceback.format_exc()}"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_multicast_push_and_in_switch_reduce():
+    import torch.multiprocessing as mp
+
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker_multicast, args=(r, world, 29751, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    if all(msg.startswith("skip") for _, msg in results):
+        pytest.skip(results[0][1])
     for rank, msg in results:
         assert msg == "ok", f"rank {rank}: {msg}"
