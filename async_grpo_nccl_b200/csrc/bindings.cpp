@@ -372,10 +372,15 @@ void rope_kv_write_decode(Tensor& qkv, const Tensor& cos_t, const Tensor& sin_t,
 
 void paged_decode_attn(const Tensor& qkv, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_tables,
                        const Tensor& seq_lens, Tensor& out, int64_t Hq, int64_t Hkv, int64_t D, double softmax_scale,
-                       int64_t splits, const OptTensor& part_o, const OptTensor& part_ml, const OptTensor& status) {
+                       int64_t splits, const OptTensor& part_o, const OptTensor& part_ml, const OptTensor& status,
+                       const OptTensor& tickets) {
   check_bf16(qkv, "qkv"); check_bf16(k_cache, "k_cache"); check_bf16(v_cache, "v_cache"); check_bf16(out, "out");
   check_i32(block_tables, "block_tables"); check_i32(seq_lens, "seq_lens");
   const int64_t B = qkv.size(0);
+  if (tickets.has_value() && tickets->defined()) {
+    check_i32(*tickets, "tickets");
+    TORCH_CHECK(tickets->is_contiguous() && tickets->numel() >= B * Hkv, "decode: tickets [B, Hkv]");
+  }
   TORCH_CHECK(qkv.dim() == 2 && qkv.stride(1) == 1 && qkv.size(1) >= Hq * D, "decode: qkv");
   TORCH_CHECK(out.dim() == 2 && out.size(0) == B && out.size(1) == Hq * D && out.stride(1) == 1, "decode: out");
   TORCH_CHECK(block_tables.dim() == 2 && block_tables.stride(1) == 1 && block_tables.size(0) >= B && seq_lens.numel() >= B, "decode: tables");
@@ -390,7 +395,7 @@ void paged_decode_attn(const Tensor& qkv, const Tensor& k_cache, const Tensor& v
                                   block_tables.data_ptr<int>(), seq_lens.data_ptr<int>(), (int)B, (int)block_tables.stride(0),
                                   (int)k_cache.size(0), (int)Hq, (int)Hkv, (int)D, (int)k_cache.size(2), (float)softmax_scale,
                                   (int)splits, out.data_ptr(), out.stride(0), opt_ptr<float>(part_o), opt_ptr<float>(part_ml),
-                                  opt_ptr<int>(status), cur_stream());
+                                  opt_ptr<int>(status), cur_stream(), opt_ptr<int>(tickets));
 }
 
 int64_t lm_sample_num_groups(int64_t V, int64_t rows) { return agrpo::lm_sample_num_groups((int)V, (int)rows); }
@@ -733,7 +738,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("paged_decode_attn", &paged_decode_attn, py::arg("qkv"), py::arg("k_cache"), py::arg("v_cache"),
         py::arg("block_tables"), py::arg("seq_lens"), py::arg("out"), py::arg("Hq"), py::arg("Hkv"), py::arg("D"),
         py::arg("softmax_scale"), py::arg("splits") = 1, py::arg("part_o") = py::none(), py::arg("part_ml") = py::none(),
-        py::arg("status") = py::none(), NOGIL);
+        py::arg("status") = py::none(), py::arg("tickets") = py::none(), NOGIL);
   m.def("lm_sample_num_groups", &lm_sample_num_groups);
   m.def("lm_sample", &lm_sample, py::arg("hidden"), py::arg("weight"), py::arg("temperature"), py::arg("seeds"),
         py::arg("part_f"), py::arg("part_i"), py::arg("tokens"), py::arg("logprobs") = py::none(),

@@ -163,6 +163,7 @@ struct DecodeParams {
   float* part_ml;           // [B, Hkv, splits, 8, 2]
   int num_cache_blocks;
   int* status;
+  int* tickets;             // [B, Hkv] zero-initialised arrival counters, or nullptr: the last split CTA to finish merges
 };
 
 // Shared-memory tile of one 16-token block: 16 rows x 256 bytes, 16-byte chunk c of row r stored at c ^ (r & 7).
@@ -333,6 +334,38 @@ paged_decode_attn_kernel(const DecodeParams p) {
       if (d == 0) {
         p.part_ml[base * 2] = M;
         p.part_ml[base * 2 + 1] = L;
+      }
+    }
+  }
+  // Split-KV merge without a second kernel: every split CTA of a (sequence, kv head) takes a ticket after its
+  // partials are visible device-wide; the one that draws the last ticket merges all of them and re-arms the counter.
+  if (p.splits > 1 && p.tickets != nullptr) {
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int* t = p.tickets + (long long)b * p.Hkv + kvh;
+      const int ticket = atomicAdd(t, 1);
+      s_last = (ticket == p.splits - 1) ? 1 : 0;
+      if (s_last) *t = 0;
+    }
+    __syncthreads();
+    if (s_last) {
+      __threadfence();
+      for (int idx = threadIdx.x; idx < p.G * kDecD; idx += blockDim.x) {
+        const int g = idx / kDecD, d = idx % kDecD;
+        const long long base0 = (((long long)b * p.Hkv + kvh) * p.splits) * 8 + g;
+        float M = -INFINITY;
+        for (int s = 0; s < p.splits; ++s) M = fmaxf(M, __ldcg(p.part_ml + (base0 + (long long)s * 8) * 2));
+        float L = 0.f, acc = 0.f;
+        for (int s = 0; s < p.splits; ++s) {
+          const long long bs = base0 + (long long)s * 8;
+          const float ms = __ldcg(p.part_ml + bs * 2);
+          const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
+          L += __ldcg(p.part_ml + bs * 2 + 1) * w;
+          acc += __ldcg(p.part_o + bs * kDecD + d) * w;
+        }
+        p.out[(long long)b * p.ldo + (long long)(kvh * p.G + g) * kDecD + d] = __float2bfloat16(L > 0.f ? acc / L : 0.f);
       }
     }
   }
@@ -527,7 +560,7 @@ void launch_rope_kv_write_decode(void* qkv, long long row_pitch, const float* co
 void launch_paged_decode_attn(const void* q, long long ldq, int q_col0, const void* k_cache, const void* v_cache,
                               const int* block_tables, const int* seq_lens, int B, int max_blocks, int num_cache_blocks,
                               int Hq, int Hkv, int D, int block_size, float softmax_scale, int splits, void* out,
-                              long long ldo, float* part_o, float* part_ml, int* status, cudaStream_t s) {
+                              long long ldo, float* part_o, float* part_ml, int* status, cudaStream_t s, int* tickets) {
   if (B == 0) return;
   if (D != kDecD || block_size != kDecBlock) throw std::runtime_error("paged_decode_attn: head_dim 128 and block_size 16 only");
   const int G = Hq / Hkv;
@@ -553,6 +586,7 @@ void launch_paged_decode_attn(const void* q, long long ldq, int q_col0, const vo
   p.part_ml = part_ml;
   p.num_cache_blocks = num_cache_blocks;
   p.status = status;
+  p.tickets = tickets;
   constexpr int smem = kDecWarps * 2 * 2 * 4096;  // 64 KB staging (>= merge area of 16.6 KB)
   static bool configured = false;
   if (!configured) {
@@ -563,7 +597,7 @@ void launch_paged_decode_attn(const void* q, long long ldq, int q_col0, const vo
   dim3 grid(splits, Hkv, B);
   AGRPO_PREFER_SMEM(paged_decode_attn_kernel);
   launch_kernel(paged_decode_attn_kernel, grid, dim3(kDecWarps * 32), smem, s, "paged_decode_attn", p);
-  if (splits > 1) {
+  if (splits > 1 && tickets == nullptr) {
     dim3 g2(Hkv, B);
     AGRPO_PREFER_SMEM(paged_decode_combine_kernel);
     launch_kernel(paged_decode_combine_kernel, g2, dim3(128), 0, s, "paged_decode_combine", (const float*)part_o,

@@ -187,11 +187,13 @@ void launch_rope_kv_write_decode(void* qkv, long long row_pitch, const float* co
                                  const int* block_tables, int max_blocks, const int* seq_lens, void* k_cache, void* v_cache, int B,
                                  int Hq, int Hkv, int D, int block_size, int num_cache_blocks, int* status, cudaStream_t s);
 // One query token per sequence against the paged cache. part_o: fp32 [B, Hkv, splits, 8, D], part_ml: fp32
-// [B, Hkv, splits, 8, 2] (only touched when splits > 1).
+// [B, Hkv, splits, 8, 2] (only touched when splits > 1). tickets (int32 [B, Hkv], all zero between launches) lets the
+// last split CTA of each (sequence, kv head) merge the partials itself; without it a second kernel does the merge.
 void launch_paged_decode_attn(const void* q, long long ldq, int q_col0, const void* k_cache, const void* v_cache,
                               const int* block_tables, const int* seq_lens, int B, int max_blocks, int num_cache_blocks,
                               int Hq, int Hkv, int D, int block_size, float softmax_scale, int splits, void* out,
-                              long long ldo, float* part_o, float* part_ml, int* status, cudaStream_t s);
+                              long long ldo, float* part_o, float* part_ml, int* status, cudaStream_t s,
+                              int* tickets = nullptr);
 int lm_sample_num_groups(int V, int rows);
 // tokens[r] ~ softmax(hidden[r] . weight^T / temperature) (argmax when temperature <= 0); logprobs may be nullptr.
 // part_f: fp32 [4 * groups * rows], part_i: int32 [groups * rows] scratch.

@@ -119,6 +119,8 @@ class RolloutEngine:
         self.b_part_o = torch.empty(S * cfg.num_key_value_heads * self.max_splits * 8 * cfg.head_dim, dtype=torch.float32,
                                     device=self.dev)
         self.b_part_ml = torch.empty(S * cfg.num_key_value_heads * self.max_splits * 16, dtype=torch.float32, device=self.dev)
+        # arrival counters of the split-KV merge (the last split CTA merges; counters re-arm themselves)
+        self.b_tickets = torch.zeros(S * cfg.num_key_value_heads, dtype=torch.int32, device=self.dev)
         groups = int(self.C.lm_sample_num_groups(cfg.vocab_size, S))
         g_small = max(groups, int(self.C.lm_sample_num_groups(cfg.vocab_size, 1)))
         self.b_sample_f = torch.empty(4 * g_small * S, dtype=torch.float32, device=self.dev)
@@ -297,7 +299,7 @@ class RolloutEngine:
             C.rope_kv_write_decode(qkv, cos_t, sin_t, bt, sl, self._kc(i), self._vc(i), cfg.num_attention_heads,
                                    cfg.num_key_value_heads, cfg.head_dim, self.status)
             C.paged_decode_attn(qkv, self._kc(i), self._vc(i), bt, sl, attn, cfg.num_attention_heads, cfg.num_key_value_heads,
-                                cfg.head_dim, scale, splits, self.b_part_o, self.b_part_ml, self.status)
+                                cfg.head_dim, scale, splits, self.b_part_o, self.b_part_ml, self.status, self.b_tickets)
             C.gemm_bf16(attn, dec.w(p + "wo"), x1, False, False, None, 1.0, False, self.status, x)
             C.rmsnorm_fwd(x1, dec.w(p + "ln2"), h, None, cfg.rms_norm_eps)
             C.gemm_bf16(h, dec.w(p + "wgu"), gu, False, False, None, 1.0, False, self.status, None)
@@ -347,7 +349,7 @@ class RolloutEngine:
             C.rope_kv_write_decode(qkv, cos_t, sin_t, bt, sl, self._kc(i), self._vc(i), cfg.num_attention_heads,
                                    cfg.num_key_value_heads, cfg.head_dim, st)
             C.paged_decode_attn(qkv, self._kc(i), self._vc(i), bt, sl, attn, cfg.num_attention_heads, cfg.num_key_value_heads,
-                                cfg.head_dim, scale, splits, self.b_part_o, self.b_part_ml, st)
+                                cfg.head_dim, scale, splits, self.b_part_o, self.b_part_ml, st, self.b_tickets)
             ok = C.gemm_decode(attn, dec.w(p + "wo"), x1, None, x, None, ss[2 * i + 1], eps, st) and ok
             C.gemm_swiglu(x1, fg, act, ss[2 * i + 1], eps, st)
             ok = C.gemm_decode(act, dec.w(p + "wd"), x, None, x1, None, ss[2 * i + 2], eps, st) and ok
@@ -362,7 +364,7 @@ class RolloutEngine:
 
     def _launch_count_decode(self, splits: int, B: int = 0) -> int:
         fused = self.fused_decode and 0 < B <= self.fused_rows
-        per_layer = (6 if fused else 9) + (1 if splits > 1 else 0)
+        per_layer = 6 if fused else 9
         return 1 + per_layer * self.cfg.num_hidden_layers + 3
 
     def _decode(self, plan: Dict[str, Any]) -> None:

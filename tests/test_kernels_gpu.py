@@ -253,6 +253,15 @@ def test_paged_decode_and_kv_write():
             s = torch.einsum("hgd,hld->hgl", q, k) / math.sqrt(D)
             ref[b] = torch.einsum("hgl,hld->hgd", torch.softmax(s, -1), v).reshape(Hq, D)
         assert rel_err(out.view(B, Hq, D), ref) < 1.5e-2
+        # split-KV merge done by the last split CTA (arrival tickets) instead of a second kernel: same result, and the
+        # counters are back at zero so that the next launch (second call) starts clean
+        tickets = torch.zeros(B * Hkv, device=DEV, dtype=torch.int32)
+        for _ in range(2):
+            out2 = torch.zeros_like(out)
+            C.paged_decode_attn(qkv, kc, vc, bt, sl, out2, Hq, Hkv, D, 1 / math.sqrt(D), splits, po, pml, st, tickets)
+            torch.cuda.synchronize()
+            assert torch.equal(out2, out)
+            assert int(tickets.abs().max()) == 0 and int(st.item()) == 0
 
 
 def test_lm_sample_greedy_and_distribution():
