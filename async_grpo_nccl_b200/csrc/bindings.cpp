@@ -25,6 +25,13 @@ inline void check_f32(const Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda(), name, ": CUDA tensor required");
   TORCH_CHECK(t.scalar_type() == torch::kFloat32, name, ": fp32 required");
 }
+inline void check_i64(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, ": CUDA tensor required");
+  TORCH_CHECK(t.scalar_type() == torch::kInt64, name, ": int64 required (row sums of squares are fixed point, value * 2^30)");
+}
+inline long long* opt_i64(const OptTensor& t) {
+  return (t.has_value() && t->defined()) ? reinterpret_cast<long long*>(t->data_ptr<int64_t>()) : nullptr;
+}
 inline void check_i32(const Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda(), name, ": CUDA tensor required");
   TORCH_CHECK(t.scalar_type() == torch::kInt32, name, ": int32 required");
@@ -87,11 +94,11 @@ void embedding_fwd(const Tensor& ids, const Tensor& table, Tensor& out) {
                               (int)table.size(0), cur_stream());
 }
 void embedding_sumsq(const Tensor& ids, const Tensor& table, Tensor& out, Tensor& ss) {
-  check_i32(ids, "ids"); check_bf16(table, "table"); check_bf16(out, "out"); check_f32(ss, "ss");
+  check_i32(ids, "ids"); check_bf16(table, "table"); check_bf16(out, "out"); check_i64(ss, "ss");
   TORCH_CHECK(table.is_contiguous() && out.is_contiguous() && table.size(1) % 8 == 0, "embedding_sumsq layout");
   TORCH_CHECK(ss.dim() == 2 && ss.stride(1) == 1 && ss.size(1) >= ids.numel(), "embedding_sumsq: ss [n, >= rows]");
   const c10::cuda::CUDAGuard guard(table.device());
-  agrpo::launch_embedding_sumsq(ids.data_ptr<int>(), table.data_ptr(), out.data_ptr(), ss.data_ptr<float>(), (int)ss.size(0),
+  agrpo::launch_embedding_sumsq(ids.data_ptr<int>(), table.data_ptr(), out.data_ptr(), reinterpret_cast<long long*>(ss.data_ptr<int64_t>()), (int)ss.size(0),
                                 (int)ss.stride(0), (int)ids.numel(), (int)table.size(1), (int)table.size(0), cur_stream());
 }
 void fold_norm_weight(const Tensor& w, const Tensor& g, Tensor& out) {
@@ -113,8 +120,8 @@ bool gemm_decode(const Tensor& a, const Tensor& b, Tensor& d, const OptTensor& b
   const int64_t M = a.size(0), K = a.size(1), N = b.size(0);
   TORCH_CHECK(b.size(1) == K && d.size(0) == M && d.size(1) == N, "gemm_decode: shape mismatch");
   TORCH_CHECK(a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0, "gemm_decode: row pitch must be a multiple of 8 elements");
-  if (ss_in.has_value() && ss_in->defined()) { check_f32(*ss_in, "ss_in"); TORCH_CHECK(ss_in->numel() >= M && ss_in->is_contiguous(), "ss_in [M]"); }
-  if (ss_out.has_value() && ss_out->defined()) { check_f32(*ss_out, "ss_out"); TORCH_CHECK(ss_out->numel() >= M && ss_out->is_contiguous(), "ss_out [M]"); }
+  if (ss_in.has_value() && ss_in->defined()) { check_i64(*ss_in, "ss_in"); TORCH_CHECK(ss_in->numel() >= M && ss_in->is_contiguous(), "ss_in [M]"); }
+  if (ss_out.has_value() && ss_out->defined()) { check_i64(*ss_out, "ss_out"); TORCH_CHECK(ss_out->numel() >= M && ss_out->is_contiguous(), "ss_out [M]"); }
   if (status.has_value() && status->defined()) check_i32(*status, "gemm_decode status");
   long long ldr = 0;
   if (residual.has_value() && residual->defined()) { check_bf16(*residual, "residual"); ldr = residual->stride(0); }
@@ -122,7 +129,7 @@ bool gemm_decode(const Tensor& a, const Tensor& b, Tensor& d, const OptTensor& b
   const c10::cuda::CUDAGuard guard(a.device());
   return agrpo::launch_gemm_skinny(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), d.data_ptr(), d.stride(0), (int)M, (int)N,
                                    (int)K, opt_ptr<void>(bias), opt_ptr<void>(residual), ldr, opt_ptr<int>(status), num_sms(),
-                                   cur_stream(), nullptr, opt_ptr<float>(ss_in), opt_ptr<float>(ss_out), (float)eps);
+                                   cur_stream(), nullptr, opt_i64(ss_in), opt_i64(ss_out), (float)eps);
 }
 int64_t gemm_skinny_splits(int64_t M, int64_t N, int64_t K) { return agrpo::gemm_skinny_splits((int)M, (int)N, (int)K, num_sms()); }
 void gemm_swiglu(const Tensor& a, const Tensor& b, Tensor& d, const OptTensor& ss_in, double eps, const OptTensor& status) {
@@ -131,11 +138,11 @@ void gemm_swiglu(const Tensor& a, const Tensor& b, Tensor& d, const OptTensor& s
   const int64_t M = a.size(0), K = a.size(1), F = d.size(1);
   TORCH_CHECK(b.size(0) == 2 * F && b.size(1) == K && d.size(0) == M, "gemm_swiglu: b must be the stacked [2F, K] gate/up weight");
   TORCH_CHECK(a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0 && F % 8 == 0, "gemm_swiglu: pitches and F must be multiples of 8");
-  if (ss_in.has_value() && ss_in->defined()) { check_f32(*ss_in, "ss_in"); TORCH_CHECK(ss_in->numel() >= M && ss_in->is_contiguous(), "ss_in [M]"); }
+  if (ss_in.has_value() && ss_in->defined()) { check_i64(*ss_in, "ss_in"); TORCH_CHECK(ss_in->numel() >= M && ss_in->is_contiguous(), "ss_in [M]"); }
   if (status.has_value() && status->defined()) check_i32(*status, "gemm_swiglu status");
   const c10::cuda::CUDAGuard guard(a.device());
   TORCH_CHECK(agrpo::launch_gemm_swiglu_bf16(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), d.data_ptr(), d.stride(0), (int)M,
-                                             (int)F, (int)K, opt_ptr<float>(ss_in), (float)eps, opt_ptr<int>(status), num_sms(),
+                                             (int)F, (int)K, opt_i64(ss_in), (float)eps, opt_ptr<int>(status), num_sms(),
                                              cur_stream()),
               "gemm_swiglu: arguments not served");
 }
@@ -368,6 +375,37 @@ void rope_kv_write_decode(Tensor& qkv, const Tensor& cos_t, const Tensor& sin_t,
                                      block_tables.data_ptr<int>(), (int)block_tables.stride(0), seq_lens.data_ptr<int>(),
                                      k_cache.data_ptr(), v_cache.data_ptr(), (int)qkv.size(0), (int)Hq, (int)Hkv, (int)D,
                                      (int)k_cache.size(2), (int)k_cache.size(0), opt_ptr<int>(status), cur_stream());
+}
+
+// Decode-step qkv projection with everything that used to follow it: folded-norm row scale, bias, rotary embedding at
+// position seq_lens[row] - 1 and the write of the new k / v into the paged cache, all in the split-K GEMM's epilogue.
+// Returns false, having launched nothing, when the shape is not served (more than 128 rows, head_dim != 128, ...).
+bool gemm_decode_rope(const Tensor& a, const Tensor& b, Tensor& qkv, const OptTensor& bias, const OptTensor& ss_in, double eps,
+                      const Tensor& cos_t, const Tensor& sin_t, const Tensor& block_tables, const Tensor& seq_lens, Tensor& k_cache,
+                      Tensor& v_cache, int64_t Hq, int64_t Hkv, const OptTensor& status) {
+  check_bf16(a, "a"); check_bf16(b, "b"); check_bf16(qkv, "qkv"); check_f32(cos_t, "cos"); check_f32(sin_t, "sin");
+  check_i32(block_tables, "block_tables"); check_i32(seq_lens, "seq_lens"); check_bf16(k_cache, "k_cache"); check_bf16(v_cache, "v_cache");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && qkv.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && qkv.stride(1) == 1, "gemm_decode_rope: 2-D");
+  const int64_t M = a.size(0), K = a.size(1), N = b.size(0);
+  TORCH_CHECK(b.size(1) == K && qkv.size(0) == M && qkv.size(1) == N, "gemm_decode_rope: shape mismatch");
+  TORCH_CHECK(a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0 && qkv.stride(0) % 8 == 0, "gemm_decode_rope: row pitch multiple of 8");
+  TORCH_CHECK(cos_t.is_contiguous() && sin_t.is_contiguous() && cos_t.dim() == 2 && cos_t.size(1) == 64 && sin_t.sizes() == cos_t.sizes(),
+              "gemm_decode_rope: cos / sin tables [max_pos, 64] (head_dim 128)");
+  TORCH_CHECK(block_tables.dim() == 2 && block_tables.stride(1) == 1 && block_tables.size(0) >= M && seq_lens.numel() >= M, "gemm_decode_rope: block tables");
+  TORCH_CHECK(k_cache.dim() == 4 && k_cache.is_contiguous() && v_cache.is_contiguous() && k_cache.size(3) == 128 && k_cache.size(1) == Hkv &&
+              v_cache.sizes() == k_cache.sizes(), "gemm_decode_rope: cache [blocks, Hkv, block_size, 128]");
+  if (bias.has_value() && bias->defined()) { check_bf16(*bias, "bias"); TORCH_CHECK(bias->numel() == N && bias->is_contiguous(), "bias [N]"); }
+  if (ss_in.has_value() && ss_in->defined()) { check_i64(*ss_in, "ss_in"); TORCH_CHECK(ss_in->numel() >= M && ss_in->is_contiguous(), "ss_in [M]"); }
+  if (status.has_value() && status->defined()) check_i32(*status, "status");
+  agrpo::DecodeRopeArgs r;
+  r.cos_t = cos_t.data_ptr<float>(); r.sin_t = sin_t.data_ptr<float>(); r.max_pos = (int)cos_t.size(0);
+  r.block_tables = block_tables.data_ptr<int>(); r.max_blocks = (int)block_tables.stride(0); r.seq_lens = seq_lens.data_ptr<int>();
+  r.k_cache = k_cache.data_ptr(); r.v_cache = v_cache.data_ptr();
+  r.Hq = (int)Hq; r.Hkv = (int)Hkv; r.block_size = (int)k_cache.size(2); r.num_cache_blocks = (int)k_cache.size(0);
+  const c10::cuda::CUDAGuard guard(a.device());
+  return agrpo::launch_gemm_skinny(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), qkv.data_ptr(), qkv.stride(0), (int)M, (int)N,
+                                   (int)K, opt_ptr<void>(bias), nullptr, 0, opt_ptr<int>(status), num_sms(), cur_stream(), nullptr,
+                                   opt_i64(ss_in), nullptr, (float)eps, &r);
 }
 
 void paged_decode_attn(const Tensor& qkv, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_tables,
@@ -702,6 +740,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("residual") = py::none(), py::arg("ss_in") = py::none(), py::arg("ss_out") = py::none(), py::arg("eps") = 1e-6,
         py::arg("status") = py::none(), NOGIL);
   m.def("gemm_skinny_splits", &gemm_skinny_splits);
+  m.def("gemm_decode_rope", &gemm_decode_rope, NOGIL);
   m.def("gemm_swiglu", &gemm_swiglu, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("ss_in") = py::none(), py::arg("eps") = 1e-6,
         py::arg("status") = py::none(), NOGIL);
   m.def("rmsnorm_fwd", &rmsnorm_fwd, py::arg("x"), py::arg("w"), py::arg("y"), py::arg("rstd") = py::none(),

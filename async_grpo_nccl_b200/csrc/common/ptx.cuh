@@ -88,6 +88,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // ----------------------------------------------------------------------------------------------
+// Row sums of squares travel between decode kernels as 64-bit fixed point (30 fractional bits): integer atomic adds
+// commute exactly, so the statistic - and every token sampled downstream - does not depend on the order in which
+// CTAs finish. Range: sums up to 8.5e9, resolution 9.3e-10.
+// ----------------------------------------------------------------------------------------------
+typedef long long sumsq_t;
+__device__ __forceinline__ sumsq_t sumsq_to_fixed(float v) { return __float2ll_rn(v * 1073741824.f); }
+__device__ __forceinline__ float sumsq_from_fixed(sumsq_t v) { return __ll2float_rn(v) * 9.31322574615478515625e-10f; }
+__device__ __forceinline__ void sumsq_atomic_add(sumsq_t* p, float v) {
+  atomicAdd(reinterpret_cast<unsigned long long*>(p), static_cast<unsigned long long>(sumsq_to_fixed(v)));
+}
+
+// ----------------------------------------------------------------------------------------------
 // Programmatic dependent launch. pdl_wait() returns once the preceding kernel of the stream has completed and its
 // writes are visible (at once when the kernel was launched without the attribute); everything before it overlaps the
 // predecessor's tail. pdl_launch() lets the next kernel of the stream begin its own prologue. Every kernel calls

@@ -39,7 +39,7 @@ __global__ void embedding_fwd_kernel(const int* __restrict__ ids, const __nv_bfl
 // Decode-step variant: besides the lookup it writes the row's sum of squares to ss[0][row] and clears ss[1..n_ss)[row],
 // the per-layer statistics that the folded-norm GEMMs of the step accumulate into (ss is [n_ss, ss_stride] fp32).
 __global__ void embedding_sumsq_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
-                                       __nv_bfloat16* __restrict__ out, float* __restrict__ ss, int n_ss, int ss_stride, int T,
+                                       __nv_bfloat16* __restrict__ out, sumsq_t* __restrict__ ss, int n_ss, int ss_stride, int T,
                                        int H, int V) {
   pdl_wait();
   pdl_launch();
@@ -63,8 +63,8 @@ __global__ void embedding_sumsq_kernel(const int* __restrict__ ids, const __nv_b
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (lane == 0) ss[row] = acc;
-  for (int k = 1 + lane; k < n_ss; k += 32) ss[(size_t)k * ss_stride + row] = 0.f;
+  if (lane == 0) ss[row] = sumsq_to_fixed(acc);
+  for (int k = 1 + lane; k < n_ss; k += 32) ss[(size_t)k * ss_stride + row] = 0;
 }
 
 // out[n, k] = w[n, k] * g[k]: an RMSNorm weight folded into the columns of the matrix that consumes the normalised rows.
@@ -344,7 +344,7 @@ void launch_embedding_fwd(const int* ids, const void* table, void* out, int T, i
   embedding_fwd_kernel<<<(T + 7) / 8, 256, 0, s>>>(ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, T, H, V);
   check_cuda(cudaGetLastError(), "embedding_fwd");
 }
-void launch_embedding_sumsq(const int* ids, const void* table, void* out, float* ss, int n_ss, int ss_stride, int T, int H,
+void launch_embedding_sumsq(const int* ids, const void* table, void* out, long long* ss, int n_ss, int ss_stride, int T, int H,
                             int V, cudaStream_t s) {
   if (T == 0) return;
   AGRPO_PREFER_SMEM(embedding_sumsq_kernel);

@@ -30,15 +30,33 @@ constexpr int kBM = 128;
 constexpr int kBK = 64;
 constexpr int kThreads = 192;
 
+// Optional decode-step epilogue for the fused qkv projection (BN = head_dim = 128, one head per column tile): rotary
+// embedding of the q and k heads at position seq_lens[row] - 1 and the write of the rotated k and of v into the paged
+// KV cache, both on the fp32 sums before they are rounded. Column ownership is then paired: an owner sums columns
+// [j, j + wh) and [64 + j, 64 + j + wh) of the tile so that both elements of every rotation pair meet in one thread.
+struct SkRope {
+  int enabled;
+  const float* cos_t;        // [max_pos, 64]
+  const float* sin_t;
+  int max_pos;
+  const int* block_tables;   // [rows, max_blocks]
+  int max_blocks;
+  const int* seq_lens;       // [rows] tokens in the cache including the current one
+  __nv_bfloat16* k_cache;    // [num_cache_blocks, Hkv, block_size, 128]
+  __nv_bfloat16* v_cache;
+  int Hq, Hkv, block_size, num_cache_blocks;
+};
+
 struct SkParams {
   int M, N, K;
+  SkRope rope;
   __nv_bfloat16* D;
   long long ldd;
   const __nv_bfloat16* bias;
   const __nv_bfloat16* residual;
   long long ldr;
-  const float* ss_in;   // [M] sum of squares of each row of A, or nullptr
-  float* ss_out;        // [M] += sum of squares of each row of D (atomic), or nullptr
+  const sumsq_t* ss_in;  // [M] sum of squares of each row of A (fixed point), or nullptr
+  sumsq_t* ss_out;       // [M] += sum of squares of each row of D (integer atomic), or nullptr
   float inv_k;          // 1 / K
   float eps;
   int* status;
@@ -242,6 +260,7 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
     const int w = BN / S;              // columns per owner (a power of two, at least 8)
     const int w_shift = __ffs(w) - 1;
     const int gpo = w / 4;             // float4 groups per owner
+    const bool paired = p.rope.enabled != 0;
     constexpr int kRows = MT * kBM;
     bool ok = true;
     if (kb1 > kb0) {
@@ -271,8 +290,15 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
             const int col = c * 32 + i;
-            const uint32_t owner = (uint32_t)(col >> w_shift);
-            const int g = (col - (int)owner * w) >> 2;
+            uint32_t owner;
+            int g;
+            if (paired) {  // owner of columns j and 64 + j alike; local order: first-half columns, then second-half
+              owner = (uint32_t)((col & 63) >> (w_shift - 1));
+              g = (((col >> 6) << (w_shift - 1)) + (col & ((w >> 1) - 1))) >> 2;
+            } else {
+              owner = (uint32_t)(col >> w_shift);
+              g = (col - (int)owner * w) >> 2;
+            }
             const uint32_t off = (uint32_t)((((int)crank * gpo + g) * kRows + mt * kBM + row_in_tile) * 16);
             st_async_f32x4(mapa_shared(part_local + off, owner), __uint_as_float(r[i]), __uint_as_float(r[i + 1]),
                            __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]), mapa_shared(bar_local, owner));
@@ -289,12 +315,88 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
     if (threadIdx.x == 64) SK_STAMP(8);
     // sum my column slice over the S contributions (local shared memory)
     const int c0 = (int)crank * w;
-    if (ok) {
+    if (ok && paired) {
+      const SkRope& rp = p.rope;
+      const int wh = w >> 1;                 // columns per half
+      const int tile = blockIdx.y;           // one head per tile: q heads, then k heads, then v heads
+      const int row = row_in_tile;           // MT == 1 in this mode
+      if (quarter * 32 < p.M && row < p.M) {
+        const float rs = p.ss_in != nullptr ? rsqrtf(sumsq_from_fixed(p.ss_in[row]) * p.inv_k + p.eps) : 1.f;
+        const int len = rp.seq_lens[row];
+        const int pos = len > 0 ? len - 1 : 0;
+        const int pp = pos >= rp.max_pos ? rp.max_pos - 1 : pos;
+        const bool is_q = tile < rp.Hq, is_k = !is_q && tile < rp.Hq + rp.Hkv;
+        __nv_bfloat16* cache_row = nullptr;
+        if (!is_q && len > 0) {
+          const int blk = rp.block_tables[(long long)row * rp.max_blocks + pos / rp.block_size];
+          if (blk < 0 || blk >= rp.num_cache_blocks) {
+            report_status(p.status, kStatusBadIndex);
+          } else {
+            const int h = tile - rp.Hq - (is_k ? 0 : rp.Hkv);
+            cache_row = (is_k ? rp.k_cache : rp.v_cache) +
+                        (((long long)blk * rp.Hkv + h) * rp.block_size + pos % rp.block_size) * 128;
+          }
+        }
+#pragma unroll 1
+        for (int cb = 0; cb < wh; cb += 8) {
+          float a1[8], a2[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) a1[i] = a2[i] = 0.f;
+#pragma unroll
+          for (int peer = 0; peer < 8; ++peer) {
+            if (peer < S) {
+              const float4* base = part + (size_t)(peer * gpo) * kRows + row;
+              const float4 u0 = base[(size_t)(cb / 4) * kRows], u1 = base[(size_t)(cb / 4 + 1) * kRows];
+              const float4 v0 = base[(size_t)((wh + cb) / 4) * kRows], v1 = base[(size_t)((wh + cb) / 4 + 1) * kRows];
+              a1[0] += u0.x; a1[1] += u0.y; a1[2] += u0.z; a1[3] += u0.w;
+              a1[4] += u1.x; a1[5] += u1.y; a1[6] += u1.z; a1[7] += u1.w;
+              a2[0] += v0.x; a2[1] += v0.y; a2[2] += v0.z; a2[3] += v0.w;
+              a2[4] += v1.x; a2[5] += v1.y; a2[6] += v1.z; a2[7] += v1.w;
+            }
+          }
+          const int j = (int)crank * wh + cb;   // column inside the head, first half; the partner is j + 64
+          const int col1 = n0 + j, col2 = col1 + 64;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            a1[i] *= rs;
+            a2[i] *= rs;
+          }
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              a1[i] += __bfloat162float(p.bias[col1 + i]);
+              a2[i] += __bfloat162float(p.bias[col2 + i]);
+            }
+          }
+          if (is_q || is_k) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float cs = rp.cos_t[(size_t)pp * 64 + j + i], sn = rp.sin_t[(size_t)pp * 64 + j + i];
+              const float x1 = a1[i], x2 = a2[i];
+              a1[i] = x1 * cs - x2 * sn;
+              a2[i] = x2 * cs + x1 * sn;
+            }
+          }
+          uint4 o1, o2;
+          o1.x = pack_bf16x2(a1[0], a1[1]); o1.y = pack_bf16x2(a1[2], a1[3]);
+          o1.z = pack_bf16x2(a1[4], a1[5]); o1.w = pack_bf16x2(a1[6], a1[7]);
+          o2.x = pack_bf16x2(a2[0], a2[1]); o2.y = pack_bf16x2(a2[2], a2[3]);
+          o2.z = pack_bf16x2(a2[4], a2[5]); o2.w = pack_bf16x2(a2[6], a2[7]);
+          __nv_bfloat16* dst = p.D + (long long)row * p.ldd;
+          *reinterpret_cast<uint4*>(dst + col1) = o1;
+          *reinterpret_cast<uint4*>(dst + col2) = o2;
+          if (cache_row != nullptr) {
+            *reinterpret_cast<uint4*>(cache_row + j) = o1;
+            *reinterpret_cast<uint4*>(cache_row + j + 64) = o2;
+          }
+        }
+      }
+    } else if (ok) {
 #pragma unroll 1
       for (int mt = 0; mt < MT; ++mt) {
         if (mt * kBM + quarter * 32 >= p.M) continue;
         const int row = mt * kBM + row_in_tile;
-        const float rs = (p.ss_in != nullptr && row < p.M) ? rsqrtf(p.ss_in[row] * p.inv_k + p.eps) : 1.f;
+        const float rs = (p.ss_in != nullptr && row < p.M) ? rsqrtf(sumsq_from_fixed(p.ss_in[row]) * p.inv_k + p.eps) : 1.f;
         float sq = 0.f;
 #pragma unroll 1
         for (int cb = 0; cb < w; cb += 8) {
@@ -342,7 +444,7 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
             }
           }
         }
-        if (p.ss_out != nullptr && row < p.M) atomicAdd(p.ss_out + row, sq);
+        if (p.ss_out != nullptr && row < p.M) sumsq_atomic_add(p.ss_out + row, sq);
       }
     }
     if (threadIdx.x == 64) SK_STAMP(9);
@@ -399,9 +501,15 @@ int gemm_skinny_splits(int M, int N, int K, int num_sms) {
 // Returns false when the shape is not one this kernel serves (the caller then uses the general GEMM).
 bool launch_gemm_skinny(const void* a, long long lda, const void* b, long long ldb, void* d, long long ldd, int M, int N, int K,
                         const void* bias, const void* residual, long long ldr, int* status, int num_sms, cudaStream_t stream,
-                        long long* trace, const float* ss_in, float* ss_out, float eps) {
+                        long long* trace, const long long* ss_in, long long* ss_out, float eps, const DecodeRopeArgs* rope) {
   const int S = gemm_skinny_splits(M, N, K, num_sms);
   if (S == 0) return false;
+  if (rope != nullptr) {
+    // one 128-wide head per column tile, one 128-row tile, D and the output 16-byte aligned, no residual
+    if (M > 128 || N != (rope->Hq + 2 * rope->Hkv) * 128 || residual != nullptr || ss_out != nullptr || ldd % 8 != 0 ||
+        (reinterpret_cast<uintptr_t>(d) & 15) != 0 || S > 8)
+      return false;
+  }
   const int MT = M <= 128 ? 1 : 2;
   const int BN = MT == 1 ? 128 : 64;
   const int n_tiles = (N + BN - 1) / BN;
@@ -414,6 +522,16 @@ bool launch_gemm_skinny(const void* a, long long lda, const void* b, long long l
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   p.ldr = ldr;
+  p.rope = SkRope{};
+  if (rope != nullptr) {
+    p.rope.enabled = 1;
+    p.rope.cos_t = rope->cos_t; p.rope.sin_t = rope->sin_t; p.rope.max_pos = rope->max_pos;
+    p.rope.block_tables = rope->block_tables; p.rope.max_blocks = rope->max_blocks; p.rope.seq_lens = rope->seq_lens;
+    p.rope.k_cache = reinterpret_cast<__nv_bfloat16*>(rope->k_cache);
+    p.rope.v_cache = reinterpret_cast<__nv_bfloat16*>(rope->v_cache);
+    p.rope.Hq = rope->Hq; p.rope.Hkv = rope->Hkv; p.rope.block_size = rope->block_size;
+    p.rope.num_cache_blocks = rope->num_cache_blocks;
+  }
   p.ss_in = ss_in;
   p.ss_out = ss_out;
   p.inv_k = 1.f / (float)K;

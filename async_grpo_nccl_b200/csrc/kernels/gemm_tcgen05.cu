@@ -170,7 +170,7 @@ bool launch_gemm_rs_bf16(const void* a, long long lda, const void* b, long long 
 
 // act[M, F] = silu(rs * (a . Wg^T)) * (rs * (a . Wu^T)) with b = [Wg; Wu] stacked ([2F, K], the fused gate/up weight).
 bool launch_gemm_swiglu_bf16(const void* a, long long lda, const void* b, long long ldb, void* d, long long ldd, int M, int F,
-                             int K, const float* ss_in, float eps, int* status, int num_sms, cudaStream_t stream) {
+                             int K, const long long* ss_in, float eps, int* status, int num_sms, cudaStream_t stream) {
   if (F % 8 != 0 || M <= 0 || F <= 0) return false;
   const int tiles_m = (M + kGemmBM - 1) / kGemmBM;
   const int BN = ((long long)tiles_m * ((2 * F + 127) / 128) >= 120) ? 128 : 64;

@@ -124,14 +124,14 @@ struct SwigluEpilogue {
   long long ldd;
   int F;
   int bn;
-  const float* ss_in;   // [M] or nullptr
+  const sumsq_t* ss_in; // [M] fixed-point row sums of squares, or nullptr
   float inv_k;
   float eps;
   float g0[32], g1[32];
   float rs;
 
   __device__ __forceinline__ void item_begin(int row, int M, int) {
-    rs = (ss_in != nullptr && row < M) ? rsqrtf(ss_in[row] * inv_k + eps) : 1.f;
+    rs = (ss_in != nullptr && row < M) ? rsqrtf(sumsq_from_fixed(ss_in[row]) * inv_k + eps) : 1.f;
   }
   __device__ __forceinline__ void item_end(int, int, int, int) {}
   __device__ __forceinline__ void chunk(int row, int col0, const uint32_t (&r)[32], int M, int) {

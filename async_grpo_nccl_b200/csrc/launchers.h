@@ -102,21 +102,36 @@ bool launch_unit_gather(const GatherArgs& g, int n_ctas, int* status, cudaStream
 // Fused gate/up projection + SwiGLU (+ folded RMSNorm row scale, ss_in = row sums of squares of a, may be nullptr):
 // b is the stacked [2F, K] weight, d the [M, F] activation.
 bool launch_gemm_swiglu_bf16(const void* a, long long lda, const void* b, long long ldb, void* d, long long ldd, int M, int F,
-                             int K, const float* ss_in, float eps, int* status, int num_sms, cudaStream_t stream);
+                             int K, const long long* ss_in, float eps, int* status, int num_sms, cudaStream_t stream);
 
 // Decode-time shapes (M <= 256): split-K over a thread-block cluster, reduction through distributed shared memory.
 // Returns false (nothing launched) when the shape is outside what it serves. trace (optional, 16 int64 words on the
 // device) receives clock64 stamps of the kernel's phases for the first CTA: a built-in phase tracer.
+// Decode-step epilogue of the qkv projection: rotary embedding at position seq_lens[row] - 1 and the write of the new
+// token's k / v into the paged cache (head_dim 128; cos / sin tables are [max_pos, 64] fp32).
+struct DecodeRopeArgs {
+  const float* cos_t;
+  const float* sin_t;
+  int max_pos;
+  const int* block_tables;
+  int max_blocks;
+  const int* seq_lens;
+  void* k_cache;
+  void* v_cache;
+  int Hq, Hkv, block_size, num_cache_blocks;
+};
 bool launch_gemm_skinny(const void* a, long long lda, const void* b, long long ldb, void* d, long long ldd, int M, int N, int K,
                         const void* bias, const void* residual, long long ldr, int* status, int num_sms, cudaStream_t stream,
-                        long long* trace = nullptr, const float* ss_in = nullptr, float* ss_out = nullptr, float eps = 0.f);
+                        long long* trace = nullptr, const long long* ss_in = nullptr, long long* ss_out = nullptr, float eps = 0.f,
+                        const DecodeRopeArgs* rope = nullptr);
 int gemm_skinny_splits(int M, int N, int K, int num_sms);
 
 // ---- bandwidth-bound decoder ops (elementwise.cu); bf16 activations, H and F multiples of 8 ----
 void launch_embedding_fwd(const int* ids, const void* table, void* out, int T, int H, int V, cudaStream_t s);
 void launch_embedding_bwd(const int* ids, const void* dout, float* dtable, int T, int H, int V, cudaStream_t s);
-// Lookup + ss[0][row] = sum of squares of the row, ss[1..n_ss)[row] = 0 (ss is [n_ss, ss_stride] fp32).
-void launch_embedding_sumsq(const int* ids, const void* table, void* out, float* ss, int n_ss, int ss_stride, int T, int H,
+// Lookup + ss[0][row] = sum of squares of the row, ss[1..n_ss)[row] = 0. ss is [n_ss, ss_stride] int64: sums of squares
+// in fixed point with 30 fractional bits (value * 2^30), which makes their atomic accumulation order-independent.
+void launch_embedding_sumsq(const int* ids, const void* table, void* out, long long* ss, int n_ss, int ss_stride, int T, int H,
                             int V, cudaStream_t s);
 // out[n, k] = w[n, k] * g[k] (bf16, K a multiple of 8).
 void launch_fold_norm_weight(const void* w, const void* g, void* out, long long n_rows, int K, cudaStream_t s);

@@ -149,7 +149,7 @@ class RolloutEngine:
             for m in range(32, self.fused_rows + 1, 32) for n, k in ((Q, H), (H, cfg.q_dim), (H, F)))
         if self.fused_decode:
             self.folded = torch.empty(L * (Q + 2 * F) * H, **bf)
-            self.b_ss = torch.zeros(2 * L + 1, S, dtype=torch.float32, device=self.dev)
+            self.b_ss = torch.zeros(2 * L + 1, S, dtype=torch.int64, device=self.dev)  # fixed point, value * 2^30
             self.refold_weights()
         self.use_cuda_graph = use_cuda_graph
         self.use_pdl = os.environ.get("AGRPO_DECODE_PDL", "1") != "0"
@@ -345,9 +345,14 @@ class RolloutEngine:
         for i in range(cfg.num_hidden_layers):
             p = f"layers.{i}."
             fq, fg = self._folded(i)
-            ok = C.gemm_decode(x, fq, qkv, dec.w(p + "bqkv") if cfg.attention_bias else None, None, ss[2 * i], None, eps, st)
-            C.rope_kv_write_decode(qkv, cos_t, sin_t, bt, sl, self._kc(i), self._vc(i), cfg.num_attention_heads,
-                                   cfg.num_key_value_heads, cfg.head_dim, st)
+            bq = dec.w(p + "bqkv") if cfg.attention_bias else None
+            # up to 128 rows: rotary embedding and the KV-cache write happen in the qkv GEMM's epilogue
+            ok = B <= 128 and C.gemm_decode_rope(x, fq, qkv, bq, ss[2 * i], eps, cos_t, sin_t, bt, sl, self._kc(i), self._vc(i),
+                                                 cfg.num_attention_heads, cfg.num_key_value_heads, st)
+            if not ok:
+                ok = C.gemm_decode(x, fq, qkv, bq, None, ss[2 * i], None, eps, st)
+                C.rope_kv_write_decode(qkv, cos_t, sin_t, bt, sl, self._kc(i), self._vc(i), cfg.num_attention_heads,
+                                       cfg.num_key_value_heads, cfg.head_dim, st)
             C.paged_decode_attn(qkv, self._kc(i), self._vc(i), bt, sl, attn, cfg.num_attention_heads, cfg.num_key_value_heads,
                                 cfg.head_dim, scale, splits, self.b_part_o, self.b_part_ml, st, self.b_tickets)
             ok = C.gemm_decode(attn, dec.w(p + "wo"), x1, None, x, None, ss[2 * i + 1], eps, st) and ok
@@ -364,7 +369,7 @@ class RolloutEngine:
 
     def _launch_count_decode(self, splits: int, B: int = 0) -> int:
         fused = self.fused_decode and 0 < B <= self.fused_rows
-        per_layer = 6 if fused else 9
+        per_layer = (5 if B <= 128 else 6) if fused else 9
         return 1 + per_layer * self.cfg.num_hidden_layers + 3
 
     def _decode(self, plan: Dict[str, Any]) -> None:

@@ -286,11 +286,11 @@ def bench_one(args):
     elif k in ("splitk", "swiglu"):
         M, H, F = 128, 1536, 8960
         x = torch.randn(M, F if k == "splitk" else H, device=dev, dtype=bf)
-        ss = torch.full((M,), float(H), device=dev)
+        ss = torch.full((M,), int(H) << 30, device=dev, dtype=torch.int64)
         if k == "splitk":
             w, d = torch.randn(H, F, device=dev, dtype=bf), torch.empty(M, H, device=dev, dtype=bf)
             res = torch.randn(M, H, device=dev, dtype=bf)
-            sso = torch.zeros(M, device=dev)
+            sso = torch.zeros(M, device=dev, dtype=torch.int64)
             fn = lambda: C.gemm_decode(x, w, d, None, res, None, sso, 1e-6, st)
         else:
             w, d = torch.randn(2 * F, H, device=dev, dtype=bf), torch.empty(M, F, device=dev, dtype=bf)

@@ -445,29 +445,77 @@ def test_decode_fused_gemms_match_unfused_layer_math(M, H, F):
     hn = xf * torch.rsqrt(ss / H + eps)[:, None] * ln.float()
     # qkv-style GEMM with folded norm and bias
     qkv = torch.empty(M, 2048, device=DEV, dtype=torch.bfloat16)
-    assert C.gemm_decode(x, fq, qkv, bias, None, ss.contiguous(), None, eps, st)
+    ssf = (ss.double() * 2 ** 30).round().to(torch.int64)  # the kernels exchange the statistic in fixed point
+    assert C.gemm_decode(x, fq, qkv, bias, None, ssf, None, eps, st)
     assert rel_err(qkv, hn @ wq.float().t() + bias.float()) < 1.5e-2
     # gate/up + swiglu with folded norm
     act = torch.empty(M, F, device=DEV, dtype=torch.bfloat16)
-    C.gemm_swiglu(x, fgu, act, ss.contiguous(), eps, st)
+    C.gemm_swiglu(x, fgu, act, ssf, eps, st)
     gu = hn @ wgu.float().t()
     ref_act = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]
     assert rel_err(act, ref_act) < 2e-2
     # down-style GEMM with residual and sum-of-squares output
     out = torch.empty(M, H, device=DEV, dtype=torch.bfloat16)
-    ss_out = torch.zeros(M, device=DEV, dtype=torch.float32)
+    ss_out = torch.zeros(M, device=DEV, dtype=torch.int64)
     assert C.gemm_decode(act, wd, out, None, res, None, ss_out, eps, st)
     ref_out = act.float() @ wd.float().t() + res.float()
     torch.cuda.synchronize()
     assert int(st.item()) == 0
     assert rel_err(out, ref_out) < 1e-2
-    assert rel_err(ss_out, (ref_out * ref_out).sum(-1)) < 1e-2
+    assert rel_err(ss_out.double() / 2 ** 30, (ref_out * ref_out).sum(-1)) < 1e-2
     # embedding lookup with the statistic
     table = torch.randn(1000, H, device=DEV, dtype=torch.bfloat16)
     ids = torch.randint(0, 1000, (M,), device=DEV, dtype=torch.int32)
-    ssb = torch.full((5, 256), 7.0, device=DEV, dtype=torch.float32)
+    ssb = torch.full((5, 256), 7, device=DEV, dtype=torch.int64)
     xo = torch.empty(M, H, device=DEV, dtype=torch.bfloat16)
     C.embedding_sumsq(ids, table, xo, ssb)
     assert torch.equal(xo, table[ids.long()])
-    assert rel_err(ssb[0, :M], (xo.float() ** 2).sum(-1)) < 1e-5
-    assert float(ssb[1:, :M].abs().max()) == 0.0 and float(ssb[1:, M:].min()) == 7.0
+    assert rel_err(ssb[0, :M].double() / 2 ** 30, (xo.float() ** 2).sum(-1)) < 1e-5
+    assert int(ssb[1:, :M].abs().max()) == 0 and int(ssb[1:, M:].min()) == 7
+
+
+@pytest.mark.parametrize("M,Hq,Hkv,H", [(32, 12, 2, 1536), (100, 4, 2, 512), (128, 12, 2, 1536)])
+def test_qkv_gemm_with_rope_and_cache_write_epilogue(M, Hq, Hkv, H):
+    """The fused decode qkv projection (folded-norm scale, bias, RoPE, paged KV write in the GEMM epilogue) against
+    the two-kernel sequence gemm_decode -> rope_kv_write_decode."""
+    C = native()
+    torch.manual_seed(11)
+    D, bs, nblk = 128, 16, 64 + M
+    N = (Hq + 2 * Hkv) * D
+    x = torch.randn(M, H, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(N, H, device=DEV) * 0.05).to(torch.bfloat16)
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    ss = ((x.double() ** 2).sum(-1) * 2 ** 30).round().to(torch.int64)
+    max_pos = 512
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, device=DEV).float() / D))
+    ang = torch.arange(max_pos, device=DEV).float()[:, None] * inv[None, :]
+    cos_t, sin_t = ang.cos().contiguous(), ang.sin().contiguous()
+    lens = torch.randint(1, 300, (M,), device=DEV, dtype=torch.int32)
+    lens[0] = 0  # an idle row: rotated at position 0, nothing written to the cache
+    max_blocks = 32
+    perm = torch.randperm(nblk, device=DEV)[:M].to(torch.int32)
+    bt = torch.full((M, max_blocks), -1, device=DEV, dtype=torch.int32)
+    for r in range(M):
+        L = int(lens[r])
+        if L > 0:
+            bt[r, (L - 1) // bs] = perm[r]
+    st = status_word()
+    outs = []
+    for fused in (False, True):
+        kc = torch.zeros(nblk, Hkv, bs, D, device=DEV, dtype=torch.bfloat16)
+        vc = torch.zeros_like(kc)
+        qkv = torch.zeros(M, N, device=DEV, dtype=torch.bfloat16)
+        if fused:
+            assert C.gemm_decode_rope(x, w, qkv, bias, ss, 1e-6, cos_t, sin_t, bt, lens, kc, vc, Hq, Hkv, st)
+        else:
+            assert C.gemm_decode(x, w, qkv, bias, None, ss, None, 1e-6, st)
+            C.rope_kv_write_decode(qkv, cos_t, sin_t, bt, lens, kc, vc, Hq, Hkv, D, st)
+        torch.cuda.synchronize()
+        assert int(st.item()) == 0
+        outs.append((qkv, kc, vc))
+    (q0, k0, v0), (q1, k1, v1) = outs
+    assert rel_err(q1, q0.float()) < 1e-2
+    assert rel_err(k1, k0.float()) < 1e-2 and rel_err(v1, v0.float()) < 1e-2
+    # the same cache cells are written (and only those)
+    assert torch.equal(k1.abs().sum(-1) > 0, k0.abs().sum(-1) > 0)
+    assert torch.equal(v1.abs().sum(-1) > 0, v0.abs().sum(-1) > 0)
