@@ -3,6 +3,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <pybind11/numpy.h>
 #include <pybind11/stl.h>
 
 #include "host/kv_allocator.h"
@@ -377,6 +378,20 @@ void rope_kv_write_decode(Tensor& qkv, const Tensor& cos_t, const Tensor& sin_t,
                                      (int)k_cache.size(2), (int)k_cache.size(0), opt_ptr<int>(status), cur_stream());
 }
 
+void decode_step_inputs(const Tensor& stage, int64_t S, Tensor& seq_lens, Tensor& positions, Tensor& block_tables,
+                        const Tensor& base_seeds, Tensor& step_seeds, const OptTensor& status) {
+  check_i32(stage, "stage"); check_i32(seq_lens, "seq_lens"); check_i32(positions, "positions"); check_i32(block_tables, "block_tables");
+  check_i64(base_seeds, "base_seeds"); check_i64(step_seeds, "step_seeds");
+  TORCH_CHECK(stage.is_contiguous() && stage.numel() >= 3 * S + 4 && seq_lens.numel() >= S && positions.numel() >= S &&
+              base_seeds.numel() >= S && step_seeds.numel() >= S && block_tables.is_contiguous(), "decode_step_inputs: sizes");
+  if (status.has_value() && status->defined()) check_i32(*status, "status");
+  const c10::cuda::CUDAGuard guard(stage.device());
+  agrpo::launch_decode_step_inputs(stage.data_ptr<int>(), (int)S, seq_lens.data_ptr<int>(), positions.data_ptr<int>(),
+                                   block_tables.data_ptr<int>(), block_tables.numel(),
+                                   reinterpret_cast<const long long*>(base_seeds.data_ptr<int64_t>()),
+                                   reinterpret_cast<long long*>(step_seeds.data_ptr<int64_t>()), opt_ptr<int>(status), cur_stream());
+}
+
 // Decode-step qkv projection with everything that used to follow it: folded-norm row scale, bias, rotary embedding at
 // position seq_lens[row] - 1 and the write of the new k / v into the paged cache, all in the split-K GEMM's epilogue.
 // Returns false, having launched nothing, when the shape is not served (more than 128 rows, head_dim != 128, ...).
@@ -676,10 +691,18 @@ py::dict decode_plan_to_dict(const agrpo::DecodePlan& p) {
   py::dict d;
   d["batch_rows"] = p.batch_rows;
   d["num_active"] = p.num_active;
-  d["active_slots"] = p.active_slots;
+  // numpy arrays: the engine's per-step bookkeeping is vectorised, no Python loop over sequences
+  py::array_t<int> act((py::ssize_t)p.active_slots.size());
+  std::copy(p.active_slots.begin(), p.active_slots.end(), act.mutable_data());
+  d["active_slots"] = act;
   d["preempted"] = p.preempted;
-  std::vector<int> us, ui, ub;
-  for (const auto& u : p.updates) { us.push_back(u.slot); ui.push_back(u.index); ub.push_back(u.block); }
+  const py::ssize_t n = (py::ssize_t)p.updates.size();
+  py::array_t<int> us(n), ui(n), ub(n);
+  for (py::ssize_t i = 0; i < n; ++i) {
+    us.mutable_data()[i] = p.updates[i].slot;
+    ui.mutable_data()[i] = p.updates[i].index;
+    ub.mutable_data()[i] = p.updates[i].block;
+  }
   d["upd_slot"] = us; d["upd_index"] = ui; d["upd_block"] = ub;
   return d;
 }
@@ -741,6 +764,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("status") = py::none(), NOGIL);
   m.def("gemm_skinny_splits", &gemm_skinny_splits);
   m.def("gemm_decode_rope", &gemm_decode_rope, NOGIL);
+  m.def("decode_step_inputs", &decode_step_inputs, NOGIL);
   m.def("gemm_swiglu", &gemm_swiglu, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("ss_in") = py::none(), py::arg("eps") = 1e-6,
         py::arg("status") = py::none(), NOGIL);
   m.def("rmsnorm_fwd", &rmsnorm_fwd, py::arg("x"), py::arg("w"), py::arg("y"), py::arg("rstd") = py::none(),

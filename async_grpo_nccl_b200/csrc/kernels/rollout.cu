@@ -64,6 +64,27 @@ __global__ void kv_cache_write_decode_kernel(const __nv_bfloat16* __restrict__ q
   }
 }
 
+// Per-step inputs of the decode graph from ONE staged host buffer (one copy + one launch per step instead of a copy and
+// half a dozen small tensor ops). Staging layout, int32 words, S = max sequences:
+//   [0, S) sequence lengths | [S] number of block-table updates n | [S + 1] seed increment of this step | [S + 2, S + 4) unused
+//   [S + 4, S + 4 + S) flat block-table index of update i | [S + 4 + S, S + 4 + 2 S) block id of update i
+__global__ void decode_step_inputs_kernel(const int* __restrict__ stage, int S, int* __restrict__ seq_lens,
+                                          int* __restrict__ positions, int* __restrict__ block_tables, long long table_elems,
+                                          const long long* __restrict__ base_seeds, long long* __restrict__ step_seeds,
+                                          int* status) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= S) return;
+  const int len = stage[i];
+  seq_lens[i] = len;
+  positions[i] = len > 0 ? len - 1 : 0;
+  step_seeds[i] = base_seeds[i] + static_cast<long long>(stage[S + 1]);
+  if (i < stage[S]) {
+    const int idx = stage[S + 4 + i];
+    if (idx < 0 || idx >= table_elems) report_status(status, kStatusBadIndex);
+    else block_tables[idx] = stage[S + 4 + S + i];
+  }
+}
+
 // Decode-time RoPE + KV write in one pass: rotates the q and k heads of row b in place (position seq_lens[b] - 1)
 // and stores the rotated k and the v of that token into the sequence's cache page.
 __global__ void rope_kv_write_decode_kernel(__nv_bfloat16* __restrict__ qkv, long long row_pitch, const float* __restrict__ cos_t,
@@ -555,6 +576,15 @@ void launch_rope_kv_write_decode(void* qkv, long long row_pitch, const float* co
   launch_kernel(rope_kv_write_decode_kernel, dim3(B), dim3(128), 0, s, "rope_kv_write_decode", (__nv_bfloat16*)qkv, row_pitch, cos_t,
                 sin_t, max_pos, block_tables, max_blocks, seq_lens, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, B, Hq, Hkv, D,
                 block_size, num_cache_blocks, status);
+}
+
+void launch_decode_step_inputs(const int* stage, int S, int* seq_lens, int* positions, int* block_tables, long long table_elems,
+                               const long long* base_seeds, long long* step_seeds, int* status, cudaStream_t s) {
+  if (S == 0) return;
+  AGRPO_PREFER_SMEM(decode_step_inputs_kernel);
+  decode_step_inputs_kernel<<<(S + 255) / 256, 256, 0, s>>>(stage, S, seq_lens, positions, block_tables, table_elems, base_seeds,
+                                                            step_seeds, status);
+  check_cuda(cudaGetLastError(), "decode_step_inputs");
 }
 
 void launch_paged_decode_attn(const void* q, long long ldq, int q_col0, const void* k_cache, const void* v_cache,

@@ -201,6 +201,9 @@ void launch_kv_cache_write_decode(const void* qkv, long long row_pitch, int k_co
 void launch_rope_kv_write_decode(void* qkv, long long row_pitch, const float* cos_t, const float* sin_t, int max_pos,
                                  const int* block_tables, int max_blocks, const int* seq_lens, void* k_cache, void* v_cache, int B,
                                  int Hq, int Hkv, int D, int block_size, int num_cache_blocks, int* status, cudaStream_t s);
+// Scatters one staged host buffer into the decode step's device inputs (layout: see decode_step_inputs_kernel).
+void launch_decode_step_inputs(const int* stage, int S, int* seq_lens, int* positions, int* block_tables, long long table_elems,
+                               const long long* base_seeds, long long* step_seeds, int* status, cudaStream_t s);
 // One query token per sequence against the paged cache. part_o: fp32 [B, Hkv, splits, 8, D], part_ml: fp32
 // [B, Hkv, splits, 8, 2] (only touched when splits > 1). tickets (int32 [B, Hkv], all zero between launches) lets the
 // last split CTA of each (sequence, kv head) merge the partials itself; without it a second kernel does the merge.

@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import math
 import os
+import time
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
@@ -125,18 +126,28 @@ class RolloutEngine:
         g_small = max(groups, int(self.C.lm_sample_num_groups(cfg.vocab_size, 1)))
         self.b_sample_f = torch.empty(4 * g_small * S, dtype=torch.float32, device=self.dev)
         self.b_sample_i = torch.empty(g_small * S, **i32)
-        # host mirrors
+        # host mirrors (one entry per slot); all per-step bookkeeping on them is vectorised
         self.h_lens = np.zeros(S, np.int32)
         self.h_gen = np.zeros(S, np.int64)
-        # The host runs ahead of the device (always with graphs): every step's lengths go through their own pinned
-        # staging buffer, reused only after the copy that read it has completed.
-        self.h_lens_ring = [torch.zeros(S, dtype=torch.int32).pin_memory() for _ in range(8)]
-        self.h_lens_events: List[Optional[torch.cuda.Event]] = [None] * 8
+        self.h_seq = np.full(S, -1, np.int64)            # sequence id living in the slot, -1 = free
+        self.h_limit = np.full(S, 1 << 60, np.int64)     # number of generated tokens at which the sequence ends
+        self.h_watch = np.zeros(S, bool)                  # stop at EOS?
+        self.h_eos_at = np.full(S, -1, np.int64)         # index of the generated EOS token, -1 = none seen
+        self.n_watch = 0
+        # every decode step's inputs (lengths, block-table updates, seed increment) travel in one pinned staging buffer;
+        # the host runs ahead of the device, so there is a ring of them, each reused only after its copy completed
+        self.stage_ring = [torch.zeros(3 * S + 4, dtype=torch.int32).pin_memory() for _ in range(8)]
+        self.stage_np = [t.numpy() for t in self.stage_ring]
+        self.stage_events = [torch.cuda.Event() for _ in range(8)]
+        self.d_stage = torch.zeros(3 * S + 4, dtype=torch.int32, device=self.dev)
         self.h_tok_pin = [torch.zeros(S, dtype=torch.int32).pin_memory() for _ in range(2)]
         self.tok_events = [torch.cuda.Event(), torch.cuda.Event()]
         self.tok_pending: List[Optional[List[Tuple[int, int, int]]]] = [None, None]
         self.step_count = 0
         self.launches = 0
+        # host-side time accounting of the step loop (seconds): where a step's wall time goes on the CPU
+        self.t_plan = self.t_prep = self.t_launch = self.t_post = self.t_prefill = self.t_wait = 0.0
+        self.n_decode_steps = self.n_prefill_steps = 0
         # ---- fused decode path (batches of up to 256 rows) ----
         # RMSNorm weights are folded into the columns of the matrices that consume the normalised rows (private copies
         # of wqkv and wgu, refreshed after every weight sync); the row scale rsqrt(mean(x^2) + eps) is applied in those
@@ -251,9 +262,14 @@ class RolloutEngine:
                 slot = seq_slots[k]
                 forced = r.forced_new_tokens[c] if r.forced_new_tokens else None
                 child = r.child_map[c] if r.child_map else c
-                self.slot_info[slot] = {"seq_id": plan["seq_ids"][k], "req": r, "child": child, "forced": forced, "eos_at": None}
+                self.slot_info[slot] = {"seq_id": plan["seq_ids"][k], "req": r, "child": child, "forced": forced}
                 self.h_lens[slot] = len(r.prompt)
                 self.h_gen[slot] = 1
+                self.h_seq[slot] = plan["seq_ids"][k]
+                self.h_limit[slot] = forced if forced is not None else r.max_new_tokens
+                self.h_watch[slot] = not r.ignore_eos
+                self.h_eos_at[slot] = -1
+                self.n_watch += int(not r.ignore_eos)
                 k += 1
         seeds = torch.tensor(seeds_host, dtype=torch.int64).pin_memory().to(self.dev, non_blocking=True)
         slot_idx = torch.tensor(seq_slots, dtype=torch.int64).pin_memory().to(self.dev, non_blocking=True)
@@ -272,9 +288,8 @@ class RolloutEngine:
         if not all(r.ignore_eos for r in reqs):
             th = toks.cpu().numpy()
             for j, slot in enumerate(seq_slots):
-                info = self.slot_info[slot]
-                if not info["req"].ignore_eos and int(th[j]) == self.eos:
-                    info["eos_at"] = 0
+                if self.h_watch[slot] and int(th[j]) == self.eos:
+                    self.h_eos_at[slot] = 0
 
     def _decode_forward(self, B: int, temperature: float, splits: int) -> None:
         if self.fused_decode and B <= self.fused_rows:
@@ -376,28 +391,36 @@ class RolloutEngine:
         rows = int(plan["batch_rows"])
         if rows == 0:
             return
+        t_begin = time.perf_counter()
         B = min(self.max_seqs, (rows + 31) // 32 * 32)  # one captured graph per row count rounded to a warp of rows
-        active = plan["active_slots"]
-        self._apply_table_updates(plan)
-        for s in active:
-            self.h_lens[s] += 1
-        ri = self.step_count % len(self.h_lens_ring)
-        if self.h_lens_events[ri] is not None:
-            self.h_lens_events[ri].synchronize()
-        self.h_lens_ring[ri].copy_(torch.from_numpy(self.h_lens))
-        self.seq_lens.copy_(self.h_lens_ring[ri], non_blocking=True)
-        self.h2d_bytes += self.max_seqs * 4
-        ev = torch.cuda.Event()
-        ev.record()
-        self.h_lens_events[ri] = ev
-        torch.sub(self.seq_lens, 1, out=self.positions)
-        self.positions.clamp_(min=0)
+        active = plan["active_slots"]  # int32 array of slots
+        S = self.max_seqs
+        ri = self.step_count % len(self.stage_ring)
+        t_w = time.perf_counter()
+        self.stage_events[ri].synchronize()  # the copy that last read this staging buffer has completed
+        self.t_wait += time.perf_counter() - t_w
+        self.h_lens[active] += 1
         self.step_count += 1
-        torch.add(self.base_seeds, (self.step_count * 0x632BE5AB) & 0x7FFFFFFF, out=self.step_seeds)
+        st = self.stage_np[ri]
+        st[:S] = self.h_lens
+        n_upd = len(plan["upd_slot"])
+        st[S] = n_upd
+        st[S + 1] = (self.step_count * 0x632BE5AB) & 0x7FFFFFFF
+        if n_upd:
+            st[S + 4: S + 4 + n_upd] = plan["upd_slot"] * self.max_blocks_per_seq + plan["upd_index"]
+            st[S + 4 + S: S + 4 + S + n_upd] = plan["upd_block"]
+        self.d_stage.copy_(self.stage_ring[ri], non_blocking=True)
+        self.stage_events[ri].record()
+        self.h2d_bytes += self.d_stage.numel() * 4
+        # lengths, positions, seeds and the new block-table entries reach their device buffers in one launch
+        self.C.decode_step_inputs(self.d_stage, S, self.seq_lens, self.positions, self.block_tables, self.base_seeds,
+                                  self.step_seeds, self.status)
         max_len = int(self.h_lens[:B].max())
         want = (148 * 3) // max(1, len(active) * self.cfg.num_key_value_heads)
         splits = int(max(1, min(self.max_splits, want, max(1, max_len // 256))))
         temperature = float(self.temperature or 0.0)
+        t_mid = time.perf_counter()
+        self.t_prep += t_mid - t_begin
         if self.use_cuda_graph:
             key = (B, temperature, splits)
             g = self.graphs.get(key)
@@ -417,19 +440,18 @@ class RolloutEngine:
             g.replay()
         else:
             self._decode_forward(B, temperature, splits)
+        self.t_launch += time.perf_counter() - t_mid
         self.launches += self._launch_count_decode(splits, B)
         self.tokens_generated += len(active)
-        for s in active:
-            self.h_gen[s] += 1
-        # asynchronous token read-back for EOS detection (one step of lag)
-        need_eos = any(not self.slot_info[s]["req"].ignore_eos for s in active)
+        self.h_gen[active] += 1
+        # asynchronous token read-back for EOS detection (one step of lag), only while some sequence stops at EOS
         ring = self.step_count & 1
-        if need_eos:
+        if self.n_watch > 0:
             self.h_tok_pin[ring].copy_(self.b_tokens, non_blocking=True)
             self.d2h_bytes += self.max_seqs * 4
             self.tok_events[ring].record()
-            # (slot, sequence id, index of the token this step produced)
-            self.tok_pending[ring] = [(s, self.slot_info[s]["seq_id"], int(self.h_gen[s]) - 1) for s in active]
+            # (slots, the sequence ids living in them, index of the token this step produced)
+            self.tok_pending[ring] = (active.copy(), self.h_seq[active].copy(), self.h_gen[active] - 1)
         else:
             self.tok_pending[ring] = None
 
@@ -438,33 +460,25 @@ class RolloutEngine:
         if pend is None:
             return
         self.tok_events[ring].synchronize()
+        slots, seqs, gen_at = pend
         toks = self.h_tok_pin[ring].numpy()
-        for s, seq_id, gen_at in pend:
-            info = self.slot_info.get(s)
-            if info is None or info["seq_id"] != seq_id or info["req"].ignore_eos or info["eos_at"] is not None:
-                continue
-            if int(toks[s]) == self.eos:
-                info["eos_at"] = gen_at
+        hit = (toks[slots] == self.eos) & self.h_watch[slots] & (self.h_seq[slots] == seqs) & (self.h_eos_at[slots] < 0)
+        if hit.any():
+            self.h_eos_at[slots[hit]] = gen_at[hit]
         self.tok_pending[ring] = None
 
     def _collect_finished(self, force_eos_check: bool) -> List[FinishedSequence]:
         out: List[FinishedSequence] = []
-        done_slots = []
-        for slot, info in list(self.slot_info.items()):
-            r: _Request = info["req"]
-            gen = int(self.h_gen[slot])
-            limit = info["forced"] if info["forced"] is not None else r.max_new_tokens
-            reason = None
-            n_out = gen
-            if info["eos_at"] is not None:
-                reason, n_out = "stop", info["eos_at"] + 1
-            elif gen >= limit:
-                reason, n_out = "length", limit
-            if reason is None:
-                continue
-            done_slots.append((slot, info, n_out, reason))
-        if not done_slots:
+        done = np.nonzero((self.h_seq >= 0) & ((self.h_eos_at >= 0) | (self.h_gen >= self.h_limit)))[0]
+        if done.size == 0:
             return out
+        done_slots = []
+        for slot in done.tolist():
+            info = self.slot_info[slot]
+            if self.h_eos_at[slot] >= 0:
+                done_slots.append((slot, info, int(self.h_eos_at[slot]) + 1, "stop"))
+            else:
+                done_slots.append((slot, info, int(self.h_limit[slot]), "length"))
         idx = torch.tensor([d[0] for d in done_slots], dtype=torch.int64, device=self.dev)
         width = max(d[2] for d in done_slots)
         rows = self.history[:, :width].index_select(0, idx).cpu().numpy()
@@ -477,13 +491,23 @@ class RolloutEngine:
                 reason = "stop"
             out.append(FinishedSequence(r.request_id, info["child"], ids, reason, len(r.prompt)))
             self.sched.finish(info["seq_id"])
-            self.h_lens[slot] = 0
-            self.h_gen[slot] = 0
-            del self.slot_info[slot]
+            self._free_slot(slot)
         return out
+
+    def _free_slot(self, slot: int) -> None:
+        self.n_watch -= int(self.h_watch[slot])
+        self.h_lens[slot] = 0
+        self.h_gen[slot] = 0
+        self.h_seq[slot] = -1
+        self.h_limit[slot] = 1 << 60
+        self.h_watch[slot] = False
+        self.h_eos_at[slot] = -1
+        del self.slot_info[slot]
 
     # ------------------------------------------------------------------ stepping
     def step(self) -> List[FinishedSequence]:
+        pc = time.perf_counter
+        t0 = pc()
         self._admit_pending()
         did = False
         if self.sched.num_waiting > 0 and self.sched.num_free_slots > 0:
@@ -491,14 +515,29 @@ class RolloutEngine:
             if plan["group_ids"]:
                 self._prefill(plan)
                 did = True
+                self.n_prefill_steps += 1
+                self.t_prefill += pc() - t0
         if not did and self.sched.num_running > 0:
             plan = self.sched.plan_decode()
             if plan["preempted"]:
                 self._requeue_preempted(plan["preempted"])
+            t1 = pc()
+            self.t_plan += t1 - t0
             # EOS results of the previous step are examined while this step runs
             self._decode(plan)
+            t2 = pc()
             self._check_lagged_eos((self.step_count - 1) & 1)
+            out = self._collect_finished(False)
+            self.t_post += pc() - t2
+            self.n_decode_steps += 1
+            return out
         return self._collect_finished(False)
+
+    def timing_stats(self) -> Dict[str, float]:
+        """Host seconds spent per phase of the step loop since construction (planning, staging, launch, bookkeeping)."""
+        return {"engine_decode_steps": float(self.n_decode_steps), "engine_prefill_steps": float(self.n_prefill_steps),
+                "engine_plan_s": self.t_plan, "engine_prep_s": self.t_prep, "engine_launch_s": self.t_launch,
+                "engine_post_s": self.t_post, "engine_prefill_s": self.t_prefill, "engine_wait_s": self.t_wait}
 
     def _requeue_preempted(self, seq_ids: List[int]) -> None:
         # A preempted sample restarts from its prompt with the same seed stream (its progress is dropped).
@@ -508,9 +547,7 @@ class RolloutEngine:
                 forced = [info["forced"]] if info["forced"] is not None else None
                 self.pending.append(_Request(r.request_id, r.prompt, 1, r.max_new_tokens, r.temperature, r.seed, forced,
                                              r.ignore_eos, child_map=[info["child"]]))
-                self.h_lens[slot] = 0
-                self.h_gen[slot] = 0
-                del self.slot_info[slot]
+                self._free_slot(slot)
 
     def run_until_done(self) -> List[FinishedSequence]:
         out: List[FinishedSequence] = []

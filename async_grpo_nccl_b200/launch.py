@@ -241,11 +241,15 @@ class InProcessRuntime:
     async def collect_stats(self) -> Dict[str, float]:
         core = self.trainer.core
         eng = self.engine
-        return {
+        out = {
             "launches": float(getattr(core.decoder, "launches", 0) + getattr(self.logprob.decoder, "launches", 0) + getattr(eng, "launches", 0)),
             "h2d_bytes": float(core.h2d_bytes + self.logprob.h2d_bytes + getattr(eng, "h2d_bytes", 0)),
             "d2h_bytes": float(core.d2h_bytes + self.logprob.d2h_bytes + getattr(eng, "d2h_bytes", 0)),
         }
+        if hasattr(eng, "timing_stats"):
+            out.update(eng.timing_stats())
+            out["engine_busy_s"] = float(self.generation.busy_seconds)
+        return out
 
     async def shutdown(self) -> None:
         if self.trainer is not None:
@@ -677,6 +681,9 @@ class DistributedRuntime:
             s["launches"] += float(getattr(self.engine, "launches", 0))
             s["h2d_bytes"] += float(getattr(self.engine, "h2d_bytes", 0))
             s["d2h_bytes"] += float(getattr(self.engine, "d2h_bytes", 0))
+            if hasattr(self.engine, "timing_stats"):
+                s.update(self.engine.timing_stats())
+                s["engine_busy_s"] = float(self.generation.busy_seconds) if self.generation is not None else 0.0
         return s
 
     def local_record_event(self, name: str) -> bool:

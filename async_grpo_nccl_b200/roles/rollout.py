@@ -195,8 +195,11 @@ class GenerationWorker:
         return True
 
     def stats(self) -> Dict[str, float]:
-        return {"total_tokens": float(self.total_tokens), "busy_seconds": self.busy_seconds,
-                "launches": float(getattr(self.engine, "launches", 0))}
+        out = {"total_tokens": float(self.total_tokens), "busy_seconds": self.busy_seconds,
+               "launches": float(getattr(self.engine, "launches", 0))}
+        if hasattr(self.engine, "timing_stats"):
+            out.update(self.engine.timing_stats())
+        return out
 
     def shutdown(self) -> None:
         self._stop = True

@@ -255,7 +255,9 @@ def run_timed(cfg, runtime, rows, args, n, rank, dist, mcfg):
                         "pinned buffers and copied per microbatch, results (loss statistics, logprobs, generated ids) are read back"},
         "gpu_launches": int(diff.get("launches", 0.0)),
         "extra": {"gen_tokens_per_s": gen_tokens / dev_s, "weight_sync_ms_mean": sum(sync_ms) / max(1, len(sync_ms)),
-                  "samples": samples, "gen_tokens": gen_tokens, "optimizer_steps": sum(r["training/optimizer_steps_in_batch"] for r in recs)},
+                  "samples": samples, "gen_tokens": gen_tokens, "optimizer_steps": sum(r["training/optimizer_steps_in_batch"] for r in recs),
+                  # host seconds of the rollout engines' step loops inside the timed region, summed over engines
+                  "engine_host": {k: round(v, 4) for k, v in diff.items() if k.startswith("engine_")}},
     }
     return out
 
