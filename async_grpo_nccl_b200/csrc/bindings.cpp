@@ -734,6 +734,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("plan_prefill", [](agrpo::Scheduler& s) { return prefill_plan_to_dict(s.plan_prefill()); })
       .def("plan_decode", [](agrpo::Scheduler& s) { return decode_plan_to_dict(s.plan_decode()); })
       .def("finish", &agrpo::Scheduler::finish)
+      .def("compact_slots", &agrpo::Scheduler::compact_slots)
+      .def_property_readonly("highest_slot", &agrpo::Scheduler::highest_slot)
       .def("seq_info",
            [](const agrpo::Scheduler& s, long long id) -> py::object {
              const agrpo::SeqState* q = s.seq(id);

@@ -156,6 +156,37 @@ void Scheduler::release_seq(SeqState& s) {
   s.finished = true;
 }
 
+int Scheduler::highest_slot() const {
+  for (int s = max_seqs_ - 1; s >= 0; --s)
+    if (slot_owner_[s] >= 0) return s;
+  return -1;
+}
+
+std::vector<std::pair<int, int>> Scheduler::compact_slots() {
+  std::vector<std::pair<int, int>> moves;
+  int lo = 0, hi = max_seqs_ - 1;
+  while (true) {
+    while (lo < max_seqs_ && slot_owner_[lo] >= 0) ++lo;  // lowest free slot
+    while (hi >= 0 && slot_owner_[hi] < 0) --hi;           // highest occupied slot
+    if (lo >= hi || hi < 0) break;
+    const long long id = slot_owner_[hi];
+    auto it = seqs_.find(id);
+    if (it == seqs_.end()) {  // stale owner entry: just drop it
+      slot_owner_[hi] = -1;
+      continue;
+    }
+    it->second.slot = lo;
+    slot_owner_[lo] = id;
+    slot_owner_[hi] = -1;
+    moves.emplace_back(hi, lo);
+  }
+  // free list ordered so that the next admission takes the lowest free slot
+  free_slots_.clear();
+  for (int s = max_seqs_ - 1; s >= 0; --s)
+    if (slot_owner_[s] < 0) free_slots_.push_back(s);
+  return moves;
+}
+
 void Scheduler::finish(long long seq_id) {
   auto it = seqs_.find(seq_id);
   if (it == seqs_.end()) return;

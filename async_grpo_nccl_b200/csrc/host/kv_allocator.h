@@ -8,6 +8,7 @@
 #include <deque>
 #include <string>
 #include <unordered_map>
+#include <utility>
 #include <vector>
 
 namespace agrpo {
@@ -86,6 +87,11 @@ class Scheduler {
   DecodePlan plan_decode();
   // Marks a sequence finished and frees its slot and blocks.
   void finish(long long seq_id);
+  // Moves the sequences in the highest slots into the lowest free slots so that the running sequences occupy a dense
+  // prefix of the slot range (the decode batch is as many rows as the highest occupied slot). Returns (from, to) pairs;
+  // the caller moves its per-slot state the same way. Blocks stay with their sequences.
+  std::vector<std::pair<int, int>> compact_slots();
+  int highest_slot() const;
   const SeqState* seq(long long seq_id) const;
   const SeqState* seq_at_slot(int slot) const;
   int seq_len_at_slot(int slot) const;

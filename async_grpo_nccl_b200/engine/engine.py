@@ -164,6 +164,10 @@ class RolloutEngine:
             self.refold_weights()
         self.use_cuda_graph = use_cuda_graph
         self.use_pdl = os.environ.get("AGRPO_DECODE_PDL", "1") != "0"
+        # keep running sequences in a dense prefix of the slots: the decode batch has as many rows as the highest slot
+        self.compact_slots = os.environ.get("AGRPO_COMPACT_SLOTS", "1") != "0"
+        self.n_compactions = 0
+        self._last_rows = self._last_active = 0
         self.graphs: Dict[Tuple[int, float, int], torch.cuda.CUDAGraph] = {}
         self.requests: Dict[int, _Request] = {}
         self.slot_info: Dict[int, Dict[str, Any]] = {}
@@ -494,6 +498,28 @@ class RolloutEngine:
             self._free_slot(slot)
         return out
 
+    def _compact(self) -> None:
+        """Moves the per-slot state of the sequences the scheduler relocates (device rows and host mirrors)."""
+        for ring in (0, 1):  # pending EOS read-backs refer to the old slots: settle them first
+            self._check_lagged_eos(ring)
+        moves = self.sched.compact_slots()
+        if not moves:
+            return
+        self.n_compactions += 1
+        frm = np.asarray([m[0] for m in moves], dtype=np.int64)
+        to = np.asarray([m[1] for m in moves], dtype=np.int64)
+        idx = torch.from_numpy(np.stack([frm, to])).pin_memory().to(self.dev, non_blocking=True)
+        self.h2d_bytes += idx.numel() * 8
+        for t in (self.block_tables, self.last_tokens, self.gen_index, self.base_seeds, self.history):
+            t.index_copy_(0, idx[1], t.index_select(0, idx[0]))
+        self.launches += 10
+        for a, empty in ((self.h_lens, 0), (self.h_gen, 0), (self.h_seq, -1), (self.h_limit, 1 << 60), (self.h_watch, False),
+                         (self.h_eos_at, -1)):
+            a[to] = a[frm]
+            a[frm] = empty
+        for f, t_ in moves:
+            self.slot_info[t_] = self.slot_info.pop(f)
+
     def _free_slot(self, slot: int) -> None:
         self.n_watch -= int(self.h_watch[slot])
         self.h_lens[slot] = 0
@@ -518,7 +544,12 @@ class RolloutEngine:
                 self.n_prefill_steps += 1
                 self.t_prefill += pc() - t0
         if not did and self.sched.num_running > 0:
+            # sequences finish at different times and leave holes; when closing them saves at least 32 rows, move the
+            # sequences from the highest slots down (state judged on the previous step's plan)
+            if self.compact_slots and (self._last_rows + 31) // 32 > (self._last_active + 31) // 32:
+                self._compact()
             plan = self.sched.plan_decode()
+            self._last_rows, self._last_active = int(plan["batch_rows"]), int(plan["num_active"])
             if plan["preempted"]:
                 self._requeue_preempted(plan["preempted"])
             t1 = pc()
@@ -537,7 +568,8 @@ class RolloutEngine:
         """Host seconds spent per phase of the step loop since construction (planning, staging, launch, bookkeeping)."""
         return {"engine_decode_steps": float(self.n_decode_steps), "engine_prefill_steps": float(self.n_prefill_steps),
                 "engine_plan_s": self.t_plan, "engine_prep_s": self.t_prep, "engine_launch_s": self.t_launch,
-                "engine_post_s": self.t_post, "engine_prefill_s": self.t_prefill, "engine_wait_s": self.t_wait}
+                "engine_post_s": self.t_post, "engine_prefill_s": self.t_prefill, "engine_wait_s": self.t_wait,
+                "engine_compactions": float(self.n_compactions)}
 
     def _requeue_preempted(self, seq_ids: List[int]) -> None:
         # A preempted sample restarts from its prompt with the same seed stream (its progress is dropped).

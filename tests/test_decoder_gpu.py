@@ -255,3 +255,41 @@ def test_fully_sharded_decoder_matches_resident(W, recompute):
     # logprob-only forward through the sharded weights
     lpn, _ = dec.logprobs(pb, 1.0)
     assert (lpn - lp0).abs().max().item() < 1e-5
+
+
+def test_engine_slot_compaction_does_not_change_tokens(monkeypatch):
+    """Sequences finish at different times; moving the survivors into the low slots (so the decode batch shrinks) must
+    not change a single sampled token, with EOS stopping and forced lengths alike, eager and with CUDA graphs."""
+    from async_grpo_nccl_b200.engine.engine import RolloutEngine
+    from async_grpo_nccl_b200.models.config import PRESETS
+    from async_grpo_nccl_b200.models.layout import ParamLayout
+
+    cfg = PRESETS["tiny128"]
+    layout = ParamLayout(cfg)
+    p32 = torch.empty(layout.total)
+    layout.init_random_(p32, 0)
+    p16 = (p32 * 3.0).to(torch.bfloat16).to(DEV)
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(6, cfg.vocab_size, int(rng.integers(5, 40))).astype(np.int32) for _ in range(12)]
+    forced = [[int(x) for x in rng.integers(3, 150, 8)] for _ in range(12)]
+
+    def run(compact, graph, use_forced):
+        monkeypatch.setenv("AGRPO_COMPACT_SLOTS", "1" if compact else "0")
+        eng = RolloutEngine(cfg, layout, p16, max_seqs=128, max_model_len=512, num_blocks=2048, use_cuda_graph=graph,
+                            eos_token_id=5)
+        for i, pr in enumerate(prompts):
+            # without forced lengths the requests differ in their length limit, so that they end at different times
+            eng.add_request(i, pr, n=8, max_new_tokens=120 if use_forced else 10 + 10 * i, temperature=1.0, seed=i,
+                            forced_new_tokens=forced[i] if use_forced else None)
+        outs = eng.run_until_done()
+        eng.check_status()
+        assert eng.sched.num_running == 0 and eng.sched.num_free_blocks == 2048
+        return {(o.request_id, o.child): (o.output_ids.tolist(), o.finish_reason) for o in outs}, eng.n_compactions
+
+    for use_forced in (True, False):
+        base, n0 = run(False, False, use_forced)
+        assert n0 == 0 and len(base) == 96
+        for graph in (False, True):
+            got, n = run(True, graph, use_forced)
+            assert n > 0, "the workload must trigger at least one compaction"
+            assert got == base

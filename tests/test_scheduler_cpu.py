@@ -1,0 +1,63 @@
+"""C++ continuous-batching scheduler (csrc/host/kv_allocator.cpp) driven from Python, no GPU: admission, block growth,
+finish, and slot compaction (running sequences are kept in a dense prefix of the slot range)."""
+import numpy as np
+import pytest
+
+
+def _sched(**kw):
+    from async_grpo_nccl_b200.ops import have_native, native
+
+    if not have_native():
+        pytest.skip("extension not built")
+    C = native()  # host-side classes of the extension work without a GPU
+    args = dict(num_blocks=256, block_size=16, max_seqs=16, max_blocks_per_seq=32, max_prefill_tokens=4096)
+    args.update(kw)
+    return C.Scheduler(**args)
+
+
+def test_admission_decode_growth_and_finish():
+    s = _sched()
+    s.add_group(0, 20, 4, 40, [])
+    s.add_group(1, 5, 2, 40, [])
+    plan = s.plan_prefill()
+    assert sorted(plan["group_ids"]) == [0, 1] and len(plan["seq_slots"]) == 6
+    assert s.num_running == 6 and s.num_free_slots == 10
+    free0 = s.num_free_blocks
+    d = s.plan_decode()
+    assert d["num_active"] == 6 and isinstance(d["active_slots"], np.ndarray) and d["active_slots"].dtype == np.int32
+    assert d["batch_rows"] == int(d["active_slots"].max()) + 1
+    for _ in range(20):  # cross block boundaries: every sequence gets new blocks through table updates
+        d = s.plan_decode()
+    assert s.num_free_blocks < free0
+    for sid in plan["seq_ids"]:
+        s.finish(sid)
+    assert s.num_running == 0 and s.num_free_slots == 16 and s.num_free_blocks == 256
+
+
+def test_compaction_moves_high_slots_into_low_holes():
+    s = _sched()
+    s.add_group(0, 8, 8, 100, [])
+    s.add_group(1, 8, 4, 100, [])
+    plan = s.plan_prefill()
+    slots = dict(zip(plan["seq_ids"], plan["seq_slots"]))
+    assert sorted(slots.values()) == list(range(12))
+    # finish the sequences sitting in slots 0, 1, 2 and 5: the survivors in the highest slots move down
+    by_slot = {v: k for k, v in slots.items()}
+    for sl in (0, 1, 2, 5):
+        s.finish(by_slot[sl])
+    assert s.highest_slot == 11 and s.num_running == 8
+    blocks_before = {sid: s.seq_info(sid)["blocks"] for sid in slots if s.seq_info(sid) is not None}
+    moves = s.compact_slots()
+    assert sorted(m[0] for m in moves) == [8, 9, 10, 11] and sorted(m[1] for m in moves) == [0, 1, 2, 5]
+    assert s.highest_slot == 7
+    for frm, to in moves:
+        assert s.seq_info(by_slot[frm])["slot"] == to
+    # blocks stay with their sequences, and a second compaction has nothing to do
+    assert {sid: s.seq_info(sid)["blocks"] for sid in blocks_before} == blocks_before
+    assert s.compact_slots() == []
+    d = s.plan_decode()
+    assert d["batch_rows"] == 8 and sorted(d["active_slots"].tolist()) == list(range(8))
+    # the next admission takes the lowest free slots
+    s.add_group(2, 8, 2, 10, [])
+    p2 = s.plan_prefill()
+    assert sorted(p2["seq_slots"]) == [8, 9]
