@@ -415,6 +415,9 @@ class DistributedRuntime:
                     logger.warning("symmetric memory unavailable (%r): falling back to library collectives", e)
                     self.trainer_comm, self.weight_sync, use_peer = None, None, False
         self.use_peer = use_peer
+        if self.rank == 0 and config.param_sharding == "zero3" and not (use_peer and t > 1):
+            logger.warning("param_sharding=zero3 needs the peer-memory backend and more than one trainer rank; "
+                           "running with resident parameters (zero2) instead")
         if self.rank == 0 and (config.logprob_fsdp_size > 1 or config.generation_tp_size > 1):
             logger.warning("logprob_fsdp_size / generation_tp_size > 1: every logprob and rollout rank runs as a full replica "
                            "(no intra-role sharding); throughput scales with the number of ranks instead")
