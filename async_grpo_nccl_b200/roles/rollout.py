@@ -147,8 +147,21 @@ class GenerationWorker:
 
     async def batch_inference_for_evaluation(self, prompts: Sequence[Any], answers: Sequence[Any], max_tokens: int = 1024,
                                              temperature: float = 0.0) -> List[Dict[str, Any]]:
-        """Greedy (by default) completions with worker-side reward (vllm_worker.py:525-668)."""
+        """Greedy (by default) completions with worker-side reward (vllm_worker.py:525-668). All prompts go to the
+        engine at once (it batches continuously); ASYNC_GRPO_EVAL_CONCURRENCY, when set, bounds how many are in flight
+        (the reference bounds its evaluation RPCs the same way, orchestrator.py:1291)."""
+        import os
+
+        limit = int(os.environ.get("ASYNC_GRPO_EVAL_CONCURRENCY", "0") or 0)
+        gate = asyncio.Semaphore(limit) if limit > 0 else None
+
         async def one(i: int, prompt: Any, answer: Any) -> Dict[str, Any]:
+            if gate is None:
+                return await run_one(i, prompt, answer)
+            async with gate:
+                return await run_one(i, prompt, answer)
+
+        async def run_one(i: int, prompt: Any, answer: Any) -> Dict[str, Any]:
             if isinstance(prompt, str):
                 if self.tokenizer is None:
                     raise RuntimeError("a tokenizer is required for text prompts")
