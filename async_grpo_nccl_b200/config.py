@@ -95,6 +95,7 @@ class GRPOConfig:
     eager_microbatch_dispatch: bool = False
     comm_backend: str = "auto"  # "auto" (peer-memory kernels when available) | "peer" | "nccl" (library collectives)
     kernel_checks: bool = False  # kernels validate indices and report through a status word
+    colocated_sm_limit: int = 0  # > 0: trainer / logprob GEMMs fill at most this many SMs on a GPU they share with a rollout engine
     param_sharding: str = "zero2"  # "zero2": resident bf16 copy per trainer rank | "zero3": fully sharded, gathered per layer
     activation_recompute: str = "auto"  # "none" | "full" | "auto" (by memory estimate)
     fsdp_reshard_after_forward: Optional[bool] = None  # None: decide from model size vs HBM
@@ -170,6 +171,7 @@ class GRPOConfig:
         need(self.temperature >= 0.0, "temperature must be non-negative")
         need(self.lr_scheduler in ("constant", "cosine", "constant_with_warmup"), "unknown lr_scheduler")
         need(self.vllm_engine_preset in ("eager", "throughput"), "vllm_engine_preset must be eager or throughput")
+        need(self.colocated_sm_limit >= 0, "colocated_sm_limit must be >= 0")
         need(self.param_sharding in ("zero2", "zero3"), "param_sharding must be zero2/zero3")
         need(self.activation_recompute in ("none", "full", "auto"), "activation_recompute must be none/full/auto")
         need(self.keep_last_n_checkpoints >= 1, "keep_last_n_checkpoints must be >= 1")

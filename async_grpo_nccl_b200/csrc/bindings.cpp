@@ -16,7 +16,17 @@ using torch::Tensor;
 using OptTensor = c10::optional<torch::Tensor>;
 
 inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream(); }
-inline int num_sms() { return at::cuda::getCurrentDeviceProperties()->multiProcessorCount; }
+// Per-thread cap on the SMs that persistent kernels (GEMMs, lm_head) launched from this thread may fill. A trainer or
+// logprob thread that shares its GPU with a rollout engine can leave a few SMs to the latency-bound decode kernels.
+inline int& sm_limit() {
+  static thread_local int v = 0;
+  return v;
+}
+inline int num_sms() {
+  const int n = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  const int lim = sm_limit();
+  return (lim > 0 && lim < n) ? lim : n;
+}
 
 inline void check_bf16(const Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda(), name, ": CUDA tensor required");
@@ -757,6 +767,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_skinny_trace", &gemm_skinny_trace);
   m.def("embedding_fwd", &embedding_fwd, NOGIL);
   m.def("embedding_bwd", &embedding_bwd, NOGIL);
+  m.def("set_sm_limit", [](int n) { sm_limit() = n; },
+        "Cap (0 = none) on the SMs filled by persistent kernels that this THREAD launches.");
   m.def("set_pdl", [](bool on) { agrpo::pdl_flag() = on; },
         "Programmatic dependent launch for the kernels this THREAD launches next (used around the decode step).");
   m.def("embedding_sumsq", &embedding_sumsq, NOGIL);

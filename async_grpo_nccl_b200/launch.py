@@ -129,7 +129,9 @@ class InProcessRuntime:
             self.streams = {"trainer": None, "logprob": None, "rollout": None}
             kv_bytes = 0
         core = TrainerCore(cfg, mcfg, self.device, 0, 1, None, flat32, cfg.seed)
-        self.trainer = TrainerWorker(core, self.streams["trainer"])
+        # all three roles share this GPU: optionally keep some SMs free for the decode kernels
+        lim = cfg.colocated_sm_limit if self.native else 0
+        self.trainer = TrainerWorker(core, self.streams["trainer"], sm_limit=lim)
         self.layout = core.layout
         # logprob and rollout keep their own copies: they must hold the PREVIOUS policy while the trainer steps
         self.logprob_params = core.params.clone()
@@ -152,7 +154,7 @@ class InProcessRuntime:
         self.verifier = get_or_create_verifier_pool(cfg.global_num_verifiers, cfg.write_failed_generation_samples, cfg.reward_fns,
                                                     cfg.output_dir, name=f"verifier_pool_{id(self)}", timeout_s=cfg.verifier_timeout_s)
         self.tokenizer = load_tokenizer(cfg)
-        self.logprob = LogProbWorker(cfg, mcfg, lp_dec, self.device, stream=self.streams["logprob"])
+        self.logprob = LogProbWorker(cfg, mcfg, lp_dec, self.device, stream=self.streams["logprob"], sm_limit=lim)
         self.generation = GenerationWorker(cfg, mcfg, engine, self.verifier, self.tokenizer, stream=self.streams["rollout"])
         self.generation_controllers = [self.generation]
         self.logprob_controllers = [self.logprob]
@@ -434,7 +436,8 @@ class DistributedRuntime:
         if self.is_trainer:
             core = TrainerCore(config, self.mcfg, self.device, self.trainer_index, t, self.trainer_group, flat32, config.seed,
                                comm=self.trainer_comm)
-            self.trainer = TrainerWorker(core, self.streams["trainer"])
+            self.trainer = TrainerWorker(core, self.streams["trainer"],
+                                         sm_limit=config.colocated_sm_limit if (self.native and self.rank in self.rollout_ranks) else 0)
         if self.rank in self.infer_ranks:
             dtype = torch.bfloat16 if self.native else torch.float32
             if self.weight_sync is not None:
@@ -447,7 +450,8 @@ class DistributedRuntime:
         del flat32
         if self.rank in self.logprob_ranks:
             dec = (NativeDecoder if self.native else OracleDecoder)(self.mcfg, self.layout, self.infer_params)
-            self.logprob = LogProbWorker(config, self.mcfg, dec, self.device, stream=self.streams["logprob"])
+            self.logprob = LogProbWorker(config, self.mcfg, dec, self.device, stream=self.streams["logprob"],
+                                         sm_limit=config.colocated_sm_limit if (self.native and self.rank in self.rollout_ranks) else 0)
         if self.rank in self.rollout_ranks:
             self.verifier = get_or_create_verifier_pool(config.global_num_verifiers, config.write_failed_generation_samples,
                                                         config.reward_fns, config.output_dir, name=f"verifier_pool_{self.rank}",

@@ -23,12 +23,13 @@ from ..packing import pack_for_logprob
 
 class LogProbWorker:
     def __init__(self, config: Any, model_cfg: Any, decoder: Any, device: torch.device, temperature: Optional[float] = None,
-                 fill_window_s: float = 0.010, stream: Optional[torch.cuda.Stream] = None):
+                 fill_window_s: float = 0.010, stream: Optional[torch.cuda.Stream] = None, sm_limit: int = 0):
         self.config, self.mcfg, self.decoder, self.device = config, model_cfg, decoder, torch.device(device)
         self.temperature = float(config.temperature if temperature is None else temperature) or 1.0
         self.max_tokens = int(config.max_tokens_per_gpu)
         self.fill_window_s = fill_window_s
         self.stream = stream
+        self.sm_limit = int(sm_limit)
         self._queue: Optional[asyncio.Queue] = None
         self._task: Optional[asyncio.Task] = None
         self._pool = concurrent.futures.ThreadPoolExecutor(max_workers=1, thread_name_prefix="logprob")
@@ -88,6 +89,8 @@ class LogProbWorker:
     def _compute(self, samples: List[Dict[str, Any]]) -> List[Tuple[np.ndarray, np.ndarray]]:
         t0 = time.time()
         ctx = torch.cuda.stream(self.stream) if self.stream is not None else _null()
+        if self.sm_limit > 0 and self.device.type == "cuda":
+            self.decoder.C.set_sm_limit(self.sm_limit)  # thread-local: this worker thread only
         with ctx, torch.no_grad():
             host = pack_for_logprob(samples, pin=self.device.type == "cuda")
             self.h2d_bytes += host.h2d_bytes()

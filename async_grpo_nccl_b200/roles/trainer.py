@@ -388,11 +388,12 @@ class TrainerWorker:
     BATCH_DONE messages from the ExperienceManager and pushes the completion payload back. All device work
     runs on one worker thread so the asyncio loop keeps serving RPCs."""
 
-    def __init__(self, core: TrainerCore, stream: Optional[torch.cuda.Stream] = None):
+    def __init__(self, core: TrainerCore, stream: Optional[torch.cuda.Stream] = None, sm_limit: int = 0):
         import concurrent.futures
 
         self.core = core
         self.stream = stream
+        self.sm_limit = int(sm_limit)
         self._pool = concurrent.futures.ThreadPoolExecutor(max_workers=1, thread_name_prefix="trainer")
         self.manager: Any = None
         self.rank_in_manager = core.rank
@@ -405,6 +406,8 @@ class TrainerWorker:
     def _run(self, fn, *args):
         t0 = time.time()
         try:
+            if self.sm_limit > 0 and self.core.native:
+                self.core.decoder.C.set_sm_limit(self.sm_limit)  # thread-local: this worker thread only
             if self.stream is not None:
                 with torch.cuda.stream(self.stream):
                     return fn(*args)

@@ -48,6 +48,8 @@ def parse_args():
     ap.add_argument("--preset", default="throughput", choices=["eager", "throughput"])
     ap.add_argument("--param-sharding", default="zero2", choices=["zero2", "zero3"],
                     help="zero3: fully sharded trainers (all-gather / reduce-scatter fused into the GEMM kernels)")
+    ap.add_argument("--colocated-sm-limit", type=int, default=0,
+                    help="SMs that trainer / logprob GEMMs may fill on a GPU shared with a rollout engine (0 = all)")
     ap.add_argument("--placement", default=None, help='JSON role placement overriding the default, e.g. '
                     '\'{"trainer": [0, 1], "logprob": [0], "rollout": [1]}\'')
     return ap.parse_args()
@@ -152,7 +154,7 @@ def main() -> None:
     total_steps = args.warmup + args.steps
     place = json.loads(args.placement) if args.placement else placement_for(n)
     cfg = make_config({
-        "param_sharding": args.param_sharding,
+        "param_sharding": args.param_sharding, "colocated_sm_limit": args.colocated_sm_limit,
         "model_name_or_path": args.model, "batch_size": prompts_per_step, "samples_per_question": spq, "num_epochs": 1,
         "train_minibatch_sample_size": prompts_per_step * spq, "max_generation_tokens": args.gen_max,
         "max_tokens_per_gpu": args.max_tokens_per_gpu, "reward_fns": ["bernoulli"], "global_num_verifiers": 0,
