@@ -67,3 +67,92 @@ def countdown_rows(num: int, tokenizer: Any, seed: int = 0, n_numbers: int = 4, 
         rows.append({"input": text, "input_token_ids": ids, "answer": str(target), "nums": nums, "target": target,
                      "end_token": tokenizer.eos_token})
     return rows
+
+
+MATH_SYSTEM_PROMPT = r"Let's think step by step and output the final answer within \boxed{}."
+
+
+def math_rows(records: Iterable[Dict[str, Any]], tokenizer: Any, system_prompt: Optional[str] = None,
+              skip_indices: Sequence[int] = (), check_round_trip: bool = True) -> List[Dict[str, Any]]:
+    """Math-problem rows (what the reference's process_deepscaler.py prepares from the DeepScaleR dump): every record
+    has ``problem`` and ``answer`` (``solution`` is carried along when present). The prompt is the chat template applied
+    to the problem with the generation prompt appended, tokenised without extra special tokens; records whose ids do
+    not decode back to the prompt text are dropped when ``check_round_trip`` is set (the reference's error filter)."""
+    skip = set(int(i) for i in skip_indices)
+    rows = []
+    for i, rec in enumerate(records):
+        if i in skip:
+            continue
+        msgs = []
+        if system_prompt:
+            msgs.append({"role": "system", "content": system_prompt})
+        msgs.append({"role": "user", "content": rec["problem"]})
+        text = tokenizer.apply_chat_template(msgs, tokenize=False, add_generation_prompt=True)
+        ids = list(tokenizer.encode(text, add_special_tokens=False))
+        if check_round_trip and tokenizer.decode(ids) != text:
+            continue
+        row = {"input": text, "input_token_ids": ids, "answer": str(rec["answer"])}
+        if "solution" in rec:
+            row["solution"] = rec["solution"]
+        rows.append(row)
+    return rows
+
+
+def load_jsonl_or_json(path: str) -> List[Dict[str, Any]]:
+    with open(path) as f:
+        head = f.read(1)
+        f.seek(0)
+        if head == "[":
+            return list(json.load(f))
+        return [json.loads(line) for line in f if line.strip()]
+
+
+def main(argv: Optional[Sequence[str]] = None) -> int:
+    """``python -m async_grpo_nccl_b200.data countdown|math|synthetic ...`` writes a training JSONL file."""
+    import argparse
+
+    ap = argparse.ArgumentParser(prog="data", description="prepare JSONL datasets in the training format")
+    sub = ap.add_subparsers(dest="task", required=True)
+    c = sub.add_parser("countdown", help="countdown arithmetic task")
+    c.add_argument("--tokenizer", required=True)
+    c.add_argument("--num", type=int, default=10000)
+    c.add_argument("--seed", type=int, default=0)
+    c.add_argument("--out", required=True)
+    m = sub.add_parser("math", help="math problems with boxed answers (DeepScaleR-style dump)")
+    m.add_argument("--input", required=True, help="JSON list or JSONL with problem / answer / solution")
+    m.add_argument("--tokenizer", required=True)
+    m.add_argument("--system-prompt", default=None)
+    m.add_argument("--skip", type=int, nargs="*", default=[], help="record indices to drop")
+    m.add_argument("--out", required=True)
+    s = sub.add_parser("synthetic", help="random-token prompts with drawn generation lengths (benchmark workload)")
+    s.add_argument("--num", type=int, default=1024)
+    s.add_argument("--vocab-size", type=int, default=151936)
+    s.add_argument("--prompt-min", type=int, default=64)
+    s.add_argument("--prompt-max", type=int, default=512)
+    s.add_argument("--samples-per-question", type=int, default=8)
+    s.add_argument("--gen-min", type=int, default=256)
+    s.add_argument("--gen-max", type=int, default=8192)
+    s.add_argument("--reward-p", type=float, default=0.3)
+    s.add_argument("--seed", type=int, default=0)
+    s.add_argument("--out", required=True)
+    args = ap.parse_args(argv)
+    if args.task == "synthetic":
+        rows = synthetic_prompt_rows(args.num, args.vocab_size, args.prompt_min, args.prompt_max, seed=args.seed,
+                                     samples_per_question=args.samples_per_question, gen_len_range=(args.gen_min, args.gen_max),
+                                     reward_p=args.reward_p)
+        rows = [{**r, "input_token_ids": [int(t) for t in r["input_token_ids"]]} for r in rows]
+    else:
+        from transformers import AutoTokenizer
+
+        tok = AutoTokenizer.from_pretrained(args.tokenizer)
+        if args.task == "countdown":
+            rows = countdown_rows(args.num, tok, seed=args.seed)
+        else:
+            rows = math_rows(load_jsonl_or_json(args.input), tok, system_prompt=args.system_prompt, skip_indices=args.skip)
+    write_jsonl(args.out, rows)
+    print(f"wrote {len(rows)} rows to {args.out}")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -185,3 +185,35 @@ def test_plot_tools_and_phase_timer(tmp_path):
     with t.phase("a"), record_function("inner"):
         sum(range(1000))
     assert "a" in t.summary()
+
+
+def test_dataset_preparation_cli_and_math_rows(tmp_path):
+    """Dataset preparation: math rows (chat template + round-trip filter + skipped indices) and the synthetic CLI."""
+    import json
+
+    from async_grpo_nccl_b200 import data
+
+    class Tok:
+        eos_token = "<eos>"
+
+        def apply_chat_template(self, msgs, tokenize=False, add_generation_prompt=True):
+            return "".join(f"<{m['role']}>{m['content']}" for m in msgs) + ("<assistant>" if add_generation_prompt else "")
+
+        def encode(self, text, add_special_tokens=False):
+            return [ord(c) for c in text]
+
+        def decode(self, ids):
+            return "".join(chr(i) for i in ids if i != ord("~"))  # "~" does not survive the round trip
+
+    recs = [{"problem": "1+1?", "answer": 2, "solution": "two"}, {"problem": "skipped", "answer": "x"},
+            {"problem": "bad ~ char", "answer": "y"}, {"problem": "2*3?", "answer": "6"}]
+    rows = data.math_rows(recs, Tok(), system_prompt=data.MATH_SYSTEM_PROMPT, skip_indices=[1])
+    assert [r["answer"] for r in rows] == ["2", "6"]
+    assert rows[0]["input"].startswith("<system>") and rows[0]["input"].endswith("<assistant>")
+    assert rows[0]["input_token_ids"] == [ord(c) for c in rows[0]["input"]] and rows[0]["solution"] == "two"
+    out = tmp_path / "syn.jsonl"
+    assert data.main(["synthetic", "--num", "5", "--vocab-size", "100", "--samples-per-question", "4", "--gen-min", "8",
+                      "--gen-max", "64", "--out", str(out)]) == 0
+    lines = [json.loads(x) for x in out.read_text().splitlines()]
+    assert len(lines) == 5 and all(len(r["forced_output_lens"]) == 4 for r in lines)
+    assert all(8 <= n <= 64 for r in lines for n in r["forced_output_lens"])
