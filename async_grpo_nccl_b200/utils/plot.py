@@ -86,6 +86,21 @@ def plot_experiments_variables(paths: Sequence[str], variables: Sequence[str], o
     return output
 
 
+def fetch_if_remote(path: str) -> str:
+    """``host:/path/metrics.jsonl`` is copied with scp into a temporary file first (parse_logs.py:7-41 offers the same);
+    local paths are returned unchanged."""
+    import os
+    import subprocess
+    import tempfile
+
+    if ":" not in path or os.path.exists(path) or path[1:3] == ":\\":
+        return path
+    fd, local = tempfile.mkstemp(suffix=".jsonl", prefix="metrics_")
+    os.close(fd)
+    subprocess.run(["scp", "-q", path, local], check=True)
+    return local
+
+
 def main(argv: Optional[Sequence[str]] = None) -> int:
     ap = argparse.ArgumentParser(prog="plot")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -98,12 +113,12 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     pp.add_argument("-s", "--smooth", type=int, default=10)
     args = ap.parse_args(argv)
     if args.cmd == "info":
-        ser = parse_experiment_logs(args.path)
+        ser = parse_experiment_logs(fetch_if_remote(args.path))
         for k in sorted(ser):
             vals = [v for _, v in ser[k]]
             print(f"{k:50s} n={len(vals):6d} last={vals[-1]:.6g} min={min(vals):.6g} max={max(vals):.6g}")
         return 0
-    print(plot_experiments_variables(args.paths, args.var, args.output, args.smooth))
+    print(plot_experiments_variables([fetch_if_remote(p) for p in args.paths], args.var, args.output, args.smooth))
     return 0
 
 
