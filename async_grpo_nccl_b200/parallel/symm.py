@@ -40,6 +40,17 @@ class SymmetricBuffer:
             self.mc_ptr = 0
 
 
+def _trace(op: str, **kw: Any) -> None:
+    """AGRPO_TRACE_COLLECTIVES=1 logs every collective / barrier this rank enqueues, with its epoch: a mismatched
+    sequence between ranks (the usual cause of a barrier that runs out) shows up by diffing the ranks' logs. The
+    reference has the same aid for torch.distributed calls (gpu_process_worker.py:557-592), also off by default."""
+    import os
+
+    if os.environ.get("AGRPO_TRACE_COLLECTIVES", "0") == "1":
+        rank = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+        logger.info("[collective rank %d] %s %s", rank, op, " ".join(f"{k}={v}" for k, v in kw.items()))
+
+
 def multicast_enabled() -> bool:
     """NVLS (multimem) variants of the weight push and the gradient reduce-scatter are used when the symmetric
     allocation comes with a multicast address, unless AGRPO_MULTICAST=0."""
@@ -101,6 +112,7 @@ class PeerGroup:
         if not self.is_member:
             return
         self.epoch += 1
+        _trace("barrier", members=self.members, epoch=self.epoch)
         self.C.flag_barrier(self.ptrs, self.rank, self.epoch, WAIT_BUDGET_S, self.status)
 
     def check(self) -> None:
@@ -181,6 +193,7 @@ class TrainerComm:
     def reduce_scatter(self, grad_shard: torch.Tensor) -> None:
         """grad_shard <- sum over ranks of this rank's slice of every unit; norm partial published to all peers."""
         C, L = self.C, self.layout
+        _trace("reduce_scatter", multicast=bool(self.grads_mc))
         self.pg.barrier()  # every rank's backward has finished and its gradients are visible
         self.norm_local.zero_()
         for u, (lo, gs, ln) in enumerate(L.local_to_global_ranges(self.rank)):
@@ -196,6 +209,7 @@ class TrainerComm:
                           extra_dst_ptrs: Sequence[int] = ()) -> torch.Tensor:
         """Returns the device tensor holding the per-rank squared-norm partials (sum = global squared norm)."""
         C, L = self.C, self.layout
+        _trace("adamw_and_publish", step=step)
         dsts = list(self.param_ptrs) + list(extra_dst_ptrs)
         partials = self.norm_partials
         for u, (lo, gs, ln) in enumerate(L.local_to_global_ranges(self.rank)):
@@ -227,6 +241,7 @@ class WeightSync:
         """Collective over all ranks. Trainer ranks pass their bf16 parameters (the resident flat buffer, or with
         ``sharded_src`` just their own slices back to back) and their index among the trainers; the others pass None
         and only take part in the barriers."""
+        _trace("weight_push", source=trainer_index, sharded=sharded_src, multicast=bool(self.dst_mc))
         self.pg.barrier()  # inference ranks are idle (paused by the orchestrator) and trainers finished their step
         if src_params is not None and trainer_index is not None:
             t = len(self.trainer_ranks)

@@ -22,3 +22,97 @@ def test_three_process_pipeline(tmp_path):
     last = out["last"]
     assert last["training/optimizer_steps_in_batch"] == 2
     assert np.isfinite(last["training/avg_loss"]) and last["training/grad_norm"] > 0
+
+
+def _samples(vocab, n, seed):
+    rng = np.random.default_rng(seed)
+    out = []
+    for _ in range(n):
+        li, lo = int(rng.integers(3, 12)), int(rng.integers(4, 20))
+        L = li + lo
+        out.append(dict(sample_ids=rng.integers(0, vocab, L).astype(np.int32), input_len=li, output_len=lo,
+                        advantage=float(rng.normal()), sample_logprobs=(-rng.random(L) * 3).astype(np.float32),
+                        sample_entropies=np.zeros(L, np.float32), reward=float(rng.random() < 0.5)))
+    return out
+
+
+def _sharded_rank(rank, world, port, q):
+    import os
+
+    import torch
+    import torch.distributed as dist
+
+    from async_grpo_nccl_b200.config import make_config
+    from async_grpo_nccl_b200.models.config import PRESETS
+    from async_grpo_nccl_b200.models.layout import ParamLayout
+    from async_grpo_nccl_b200.roles.trainer import TrainerCore
+
+    os.environ.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)})
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        mcfg = PRESETS["tiny"]
+        cfg = make_config({"model_name_or_path": "tiny", "train_minibatch_sample_size": 12, "learning_rate": 1e-3,
+                           "global_num_verifiers": 0, "max_grad_norm": 1.0})
+        layout = ParamLayout(mcfg, shard_world=world)
+        flat = torch.empty(layout.total)
+        layout.init_random_(flat, 0)
+        core = TrainerCore(cfg, mcfg, torch.device("cpu"), rank, world, dist.group.WORLD, flat.clone())
+        # rank 0 holds 8 of the 12 samples, rank 1 the other 4; the second dispatch gives rank 1 a dummy microbatch
+        mine = _samples(mcfg.vocab_size, 12, 5)[:8] if rank == 0 else _samples(mcfg.vocab_size, 12, 5)[8:]
+        core.compute_gradients(mine[:4])
+        core.compute_gradients(mine[4:] if rank == 0 else [{"dummy": True}])
+        summary = core.apply_gradients()
+        full = core.full_master_fp32()
+        if rank == 0:
+            q.put(("ok", full.numpy(), summary["grad_norm"], layout.total))
+    except Exception as e:  # report instead of leaving the parent waiting
+        import traceback
+
+        if rank == 0:
+            q.put(("FAILED", f"{e!r}\n{traceback.format_exc()}", 0.0, 0))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(600)
+def test_two_sharded_trainer_ranks_make_the_single_rank_update():
+    """Sharded data-parallel semantics (the reference's FSDP2 + loss scaling): two ranks with different microbatches, a
+    dummy microbatch on the rank that runs out, reduce-scatter, global-norm clip and AdamW on the shards give the same
+    parameters as one rank that sees every sample."""
+    import torch
+    import torch.multiprocessing as mp
+
+    from async_grpo_nccl_b200.config import make_config
+    from async_grpo_nccl_b200.models.config import PRESETS
+    from async_grpo_nccl_b200.models.layout import ParamLayout
+    from async_grpo_nccl_b200.roles.trainer import TrainerCore
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_sharded_rank, args=(r, 2, 29723, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    status, full2, norm2, total2 = q.get(timeout=500)
+    for p in procs:
+        p.join(timeout=60)
+    assert status == "ok", full2
+    mcfg = PRESETS["tiny"]
+    cfg = make_config({"model_name_or_path": "tiny", "train_minibatch_sample_size": 12, "learning_rate": 1e-3,
+                       "global_num_verifiers": 0, "max_grad_norm": 1.0})
+    layout1 = ParamLayout(mcfg, shard_world=1)
+    flat = torch.empty(layout1.total)
+    layout1.init_random_(flat, 0)
+    one = TrainerCore(cfg, mcfg, torch.device("cpu"), init_flat_fp32=flat.clone())
+    alls = _samples(mcfg.vocab_size, 12, 5)
+    for mb in (alls[:4], alls[4:8], alls[8:]):
+        one.compute_gradients(mb)
+    s1 = one.apply_gradients()
+    assert abs(s1["grad_norm"] - norm2) < 1e-4 * max(1.0, s1["grad_norm"])
+    # compare parameter by parameter (the two layouts pad their units differently)
+    layout2 = ParamLayout(mcfg, shard_world=2)
+    assert layout2.total == total2
+    f2 = torch.from_numpy(full2)
+    for name in layout1.segments:
+        a, b = layout1.view(one.master, name), layout2.view(f2, name)
+        assert torch.allclose(a, b, rtol=1e-5, atol=2e-6), name
