@@ -545,7 +545,7 @@ class RolloutEngine:
                 self.t_prefill += pc() - t0
         if not did and self.sched.num_running > 0:
             # sequences finish at different times and leave holes; when closing them saves at least 32 rows, move the
-            # sequences from the highest slots down (state judged on the previous step's plan)
+            # sequences from the highest slots down (decided from the previous step's plan)
             if self.compact_slots and (self._last_rows + 31) // 32 > (self._last_active + 31) // 32:
                 self._compact()
             plan = self.sched.plan_decode()
