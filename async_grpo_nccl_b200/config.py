@@ -95,6 +95,7 @@ class GRPOConfig:
     eager_microbatch_dispatch: bool = False
     comm_backend: str = "auto"  # "auto" (peer-memory kernels when available) | "peer" | "nccl" (library collectives)
     kernel_checks: bool = False  # kernels validate indices and report through a status word
+    stream_logprobs: bool = True  # request a sample's old-policy logprobs when IT finishes, not when its whole group has
     colocated_sm_limit: int = 0  # > 0: trainer / logprob GEMMs fill at most this many SMs on a GPU they share with a rollout engine
     param_sharding: str = "zero2"  # "zero2": resident bf16 copy per trainer rank | "zero3": fully sharded, gathered per layer
     activation_recompute: str = "auto"  # "none" | "full" | "auto" (by memory estimate)

@@ -216,7 +216,13 @@ class ExperienceManager:
             finally:
                 await self._lp_lb.release(lp, 1)
 
-        results = await asyncio.gather(*[one(s) for s in samples], return_exceptions=True)
+        async def keep(sample: Dict[str, Any]):
+            return sample
+
+        # samples whose old-policy log-probabilities the generation worker already attached (requested when each
+        # sample finished) skip this stage
+        results = await asyncio.gather(*[keep(s) if s.get("logprobs_attached") else one(s) for s in samples],
+                                       return_exceptions=True)
         valid = []
         for r in results:
             if isinstance(r, Exception):

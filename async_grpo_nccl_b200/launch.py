@@ -156,6 +156,8 @@ class InProcessRuntime:
         self.tokenizer = load_tokenizer(cfg)
         self.logprob = LogProbWorker(cfg, mcfg, lp_dec, self.device, stream=self.streams["logprob"], sm_limit=lim)
         self.generation = GenerationWorker(cfg, mcfg, engine, self.verifier, self.tokenizer, stream=self.streams["rollout"])
+        if cfg.stream_logprobs:
+            self.generation.logprob_fn = self.logprob.inference
         self.generation_controllers = [self.generation]
         self.logprob_controllers = [self.logprob]
         self.experience_manager = ExperienceManager(cfg)
@@ -472,6 +474,9 @@ class DistributedRuntime:
                                            max_model_len=min(self.mcfg.max_position_embeddings, config.max_generation_tokens + 2048))
             self.generation = GenerationWorker(config, self.mcfg, self.engine, self.verifier, load_tokenizer(config),
                                                stream=self.streams["rollout"])
+            if config.stream_logprobs:
+                self.generation.logprob_fn = self._stream_logprob
+        self._lp_next = 0
         import concurrent.futures
 
         self._comm_pool = concurrent.futures.ThreadPoolExecutor(max_workers=1, thread_name_prefix="comm")
@@ -618,6 +623,15 @@ class DistributedRuntime:
             except Exception:
                 pass
         await self._close()
+
+    async def _stream_logprob(self, sample: Dict[str, Any]) -> Dict[str, Any]:
+        """Old-policy log-probabilities of one finished sample, asked of a logprob rank directly by the rollout rank
+        that produced it (round robin over the logprob ranks; the local worker when this rank hosts one)."""
+        r = self.logprob_ranks[self._lp_next % len(self.logprob_ranks)]
+        self._lp_next += 1
+        if r == self.rank and self.logprob is not None:
+            return await self.logprob.inference(sample)
+        return await (await self._client(r)).call("lp_inference", sample)
 
     # ------------------------------------------------------------------ rank-local halves of collective operations
     def _sync_on_device(self) -> None:

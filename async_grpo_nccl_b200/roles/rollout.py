@@ -9,6 +9,7 @@ concurrent ``inference`` coroutines are batched continuously by the engine's sch
 from __future__ import annotations
 
 import asyncio
+import logging
 import hashlib
 import threading
 import time
@@ -20,6 +21,8 @@ import torch
 from ..ops.reference import normalize_rewards
 from ..protocol import build_sample
 
+
+logger = logging.getLogger(__name__)
 
 def _uid_seed(uid: Any, base: int) -> int:
     h = hashlib.sha256(repr(uid).encode()).digest()
@@ -34,7 +37,13 @@ class GenerationWorker:
         self.stream = stream
         self._lock = threading.Lock()
         self._incoming: List[Tuple[Any, ...]] = []
-        self._futures: Dict[Any, Tuple[asyncio.AbstractEventLoop, asyncio.Future, int, List[Any]]] = {}
+        self._futures: Dict[Any, Tuple[Any, ...]] = {}  # request id -> (loop, future, n, finished children, on_child)
+        # Optional async callable sample -> {"sample_logprobs", "sample_entropies"} (set by the runtime). When present the
+        # old-policy log-probabilities of every sample are requested the moment THAT sample finishes, while its siblings
+        # still generate, instead of for the whole group at its end: the logprob role's work spreads over the
+        # generation phase instead of piling up behind it. The weights it uses are the same either way (they only
+        # change at a weight sync, when generation is paused).
+        self.logprob_fn: Optional[Any] = None
         self._wake = threading.Event()
         self._stop = False
         self._paused = threading.Event()
@@ -75,25 +84,27 @@ class GenerationWorker:
         entry = self._futures.get(f.request_id)
         if entry is None:
             return
-        loop, fut, n, got = entry
+        loop, fut, n, got, on_child = entry
         got.append(f)
+        if on_child is not None:
+            loop.call_soon_threadsafe(on_child, f)  # queued before the group's completion below: runs first
         if len(got) == n:
             del self._futures[f.request_id]
             loop.call_soon_threadsafe(lambda: fut.done() or fut.set_result(sorted(got, key=lambda x: x.child)))
 
     def _fail_all(self, e: Exception) -> None:
-        for rid, (loop, fut, _, _) in list(self._futures.items()):
+        for rid, (loop, fut, *_rest) in list(self._futures.items()):
             loop.call_soon_threadsafe(lambda fut=fut: fut.done() or fut.set_exception(RuntimeError(f"engine failure: {e!r}")))
         self._futures.clear()
 
     async def _generate(self, prompt_ids: np.ndarray, n: int, max_new: int, temperature: float, seed: int,
-                        forced: Optional[Sequence[int]] = None, ignore_eos: bool = False) -> List[Any]:
+                        forced: Optional[Sequence[int]] = None, ignore_eos: bool = False, on_child: Any = None) -> List[Any]:
         loop = asyncio.get_running_loop()
         fut: asyncio.Future = loop.create_future()
         with self._lock:
             self._req_counter += 1
             rid = self._req_counter
-            self._futures[rid] = (loop, fut, n, [])
+            self._futures[rid] = (loop, fut, n, [], on_child)
             self._incoming.append(((rid, prompt_ids), dict(n=n, max_new_tokens=max_new, temperature=temperature, seed=seed,
                                                           forced_new_tokens=forced, ignore_eos=ignore_eos)))
         self._wake.set()
@@ -118,18 +129,38 @@ class GenerationWorker:
         max_new = self.get_max_tokens(len(prompt), max_tokens)
         forced = sample.get("forced_output_lens")
         seed = _uid_seed(sample.get("__uid__", self._req_counter), int(getattr(self.config, "seed", 0)))
-        finished = await self._generate(prompt, int(n), max_new, float(temperature), seed, forced)
         row = {k: v for k, v in sample.items() if k != "forced_output_lens"}
-        out: List[Dict[str, Any]] = []
         eos = int(getattr(self.engine, "eos", self.mcfg.eos_token_id))
-        for f in finished:
+        cap = self.get_max_tokens(len(prompt), max_tokens)
+
+        def build(f: Any) -> Dict[str, Any]:
             s = build_sample(row, prompt, f.output_ids, eos)
             s["sample_index"] = f.child
             s["vocab_size"] = self.mcfg.vocab_size
             s["sample_text"] = self._decode(s["sample_ids"])
-            out.append(s)
-        cap = self.get_max_tokens(len(prompt), max_tokens)
-        verified = await asyncio.gather(*[self.verifier.verify(s, max_gen_length=cap) for s in out])
+            return s
+
+        async def finish_child(s: Dict[str, Any]) -> Dict[str, Any]:
+            """Reward and old-policy log-probabilities of one finished sample, concurrently."""
+            lp_task = asyncio.ensure_future(self.logprob_fn({"sample_ids": s["sample_ids"], "input_len": s["input_len"],
+                                                             "output_len": s["output_len"]}))
+            v = await self.verifier.verify(s, max_gen_length=cap)
+            try:
+                lp = await lp_task
+                v["sample_logprobs"], v["sample_entropies"] = lp["sample_logprobs"], lp["sample_entropies"]
+                v["logprobs_attached"] = True
+            except Exception as e:  # the experience manager's own logprob stage picks the sample up instead
+                logger.warning("streamed logprob request failed (%r); deferring to the group stage", e)
+            return v
+
+        if self.logprob_fn is not None:
+            tasks: Dict[int, Any] = {}
+            finished = await self._generate(prompt, int(n), max_new, float(temperature), seed, forced,
+                                            on_child=lambda f: tasks.__setitem__(f.child, asyncio.ensure_future(finish_child(build(f)))))
+            verified = list(await asyncio.gather(*[tasks[f.child] for f in finished]))
+        else:
+            finished = await self._generate(prompt, int(n), max_new, float(temperature), seed, forced)
+            verified = list(await asyncio.gather(*[self.verifier.verify(build(f), max_gen_length=cap) for f in finished]))
         rewards = [float(v.get("reward", 0.0)) for v in verified]
         adv = normalize_rewards(rewards)
         mx = max(rewards) if rewards else 0.0

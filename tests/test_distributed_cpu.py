@@ -116,3 +116,20 @@ def test_two_sharded_trainer_ranks_make_the_single_rank_update():
     for name in layout1.segments:
         a, b = layout1.view(one.master, name), layout2.view(f2, name)
         assert torch.allclose(a, b, rtol=1e-5, atol=2e-6), name
+
+
+@pytest.mark.timeout(600)
+def test_rollout_rank_streams_logprob_requests_to_another_rank(tmp_path):
+    """Trainer, logprob and rollout each on a rank of their own: the rollout rank asks the logprob rank for a sample's
+    old-policy log-probabilities over RPC as soon as that sample finishes (no hop through rank 0)."""
+    cfg = dict(model_name_or_path="tiny", batch_size=4, samples_per_question=4, num_epochs=1, train_minibatch_sample_size=16,
+               max_generation_tokens=10, max_tokens_per_gpu=400, reward_fns=["token_match"], global_num_verifiers=0,
+               num_training_gpu_workers=1, num_logprob_gpu_workers=1, num_generation_gpu_workers=1,
+               placement={"trainer": [0], "logprob": [1], "rollout": [2]}, learning_rate=1e-3, output_dir=str(tmp_path),
+               min_samples_per_checkpoint=10 ** 9, eval_at_start=False, stream_logprobs=True)
+    rows = synthetic_prompt_rows(8, 1024, 16, 32, seed=0)
+    out = spawn(cfg, rows, world=3, max_macro_batches=2, port=29735, timeout_s=500)
+    assert out["global_step"] == 2 and out["total_samples_seen"] == 32
+    last = out["last"]
+    assert last["training/optimizer_steps_in_batch"] == 1
+    assert np.isfinite(last["training/avg_loss"]) and last["training/grad_norm"] > 0

@@ -39,3 +39,42 @@ def test_cpu_end_to_end_two_macro_batches(tmp_path):
     assert core.opt_step == 4
     # metrics JSONL was written
     assert (tmp_path / "training_metrics.jsonl").exists()
+
+
+def test_streamed_logprobs_match_group_stage(tmp_path, monkeypatch):
+    """Requesting a sample's old-policy log-probabilities when the sample finishes (default) must train exactly like
+    requesting them for the whole group afterwards: same samples, same logprobs, same losses and parameters."""
+    from async_grpo_nccl_b200.experience import ExperienceManager
+    from async_grpo_nccl_b200.roles.logprob import LogProbWorker
+
+    calls = {"n": 0, "attached": 0}
+    orig_lp, orig_proc = LogProbWorker.inference, ExperienceManager._process_single_prompt
+
+    async def counted(self, sample):
+        calls["n"] += 1
+        return await orig_lp(self, sample)
+
+    async def spy(self, q):
+        samples, gm, tm = await orig_proc(self, q)
+        calls["attached"] += sum(1 for s in (samples or []) if s.get("logprobs_attached"))
+        return samples, gm, tm
+
+    monkeypatch.setattr(LogProbWorker, "inference", counted)
+    monkeypatch.setattr(ExperienceManager, "_process_single_prompt", spy)
+    outs = {}
+    for stream in (True, False):
+        calls["n"] = calls["attached"] = 0
+        cfg = _cfg(tmp_path / f"s{int(stream)}", stream_logprobs=stream)
+        rows = synthetic_prompt_rows(8, 1024, 16, 32, seed=0)
+        rt = build_inprocess_runtime(cfg, device="cpu")
+        out = Orchestrator(cfg, runtime=rt, dataset=rows).run()
+        outs[stream] = (out, rt.trainer.core.master.clone(), dict(calls))
+    (o1, m1, c1), (o0, m0, c0) = outs[True], outs[False]
+    assert c1["n"] == c0["n"] == 32            # one logprob request per sample either way
+    assert c1["attached"] == 32 and c0["attached"] == 0
+    assert o1["total_samples_seen"] == o0["total_samples_seen"] == 32
+    for k in ("training/avg_loss", "training/grad_norm", "training/batch_total_samples"):
+        assert abs(o1["steps"][-1][k] - o0["steps"][-1][k]) < 1e-6 * max(1.0, abs(o0["steps"][-1][k])), k
+    # the logprob worker batches the requests differently in the two modes, so its fp32 results differ in the last bits;
+    # Adam's sign-like early steps can turn that into a different direction for elements whose gradient is at that level
+    assert ((m1 - m0).abs() < 1e-5).float().mean().item() > 0.99
