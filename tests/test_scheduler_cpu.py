@@ -61,3 +61,27 @@ def test_compaction_moves_high_slots_into_low_holes():
     s.add_group(2, 8, 2, 10, [])
     p2 = s.plan_prefill()
     assert sorted(p2["seq_slots"]) == [8, 9]
+
+
+def test_block_pool_exhaustion_preempts_the_youngest_sequence():
+    # 6 blocks of 16 tokens: two sequences of 30 prompt tokens take 2 blocks each; both grow until the pool runs dry
+    s = _sched(num_blocks=6, max_seqs=4, max_blocks_per_seq=16)
+    s.add_group(0, 30, 1, 200, [])
+    s.add_group(1, 30, 1, 200, [])
+    plan = s.plan_prefill()
+    ids = list(plan["seq_ids"])
+    assert len(ids) == 2 and s.num_free_blocks == 2
+    preempted, steps = [], 0
+    while not preempted and steps < 100:
+        d = s.plan_decode()
+        preempted = list(d["preempted"])
+        steps += 1
+    assert preempted == [max(ids)], "the youngest running sequence is the victim"
+    # the victim's slot and blocks are free again; the survivor keeps generating alone
+    assert s.num_running == 1 and d["num_active"] == 1
+    assert all(s.seq_info(i) is None or s.seq_info(i)["slot"] >= 0 for i in ids if i != max(ids))
+    survivor_slot = s.seq_info(min(ids))["slot"]
+    assert d["active_slots"].tolist() == [survivor_slot]
+    assert all(int(u) == survivor_slot for u in d["upd_slot"]), "table updates of the evicted sequence are dropped"
+    d2 = s.plan_decode()
+    assert d2["num_active"] == 1 and list(d2["preempted"]) == []
