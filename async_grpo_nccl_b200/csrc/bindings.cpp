@@ -623,6 +623,14 @@ void rs_pull_sumsq(const PtrList& grad_ptrs, int64_t my_rank, int64_t global_off
   agrpo::launch_rs_pull_sumsq(lptr(grad_ptrs), (int)grad_ptrs.size(), (int)my_rank, global_off, local_off, n,
                               out.data_ptr<float>(), norm_sq.data_ptr<float>(), cur_stream());
 }
+void set_comm_guard(const c10::optional<Tensor>& status) {
+  if (status.has_value()) {
+    TORCH_CHECK(status->is_cuda() && status->scalar_type() == torch::kInt32 && status->numel() >= 1, "set_comm_guard: int32 CUDA status word");
+    agrpo::set_comm_guard(status->data_ptr<int>());
+  } else {
+    agrpo::set_comm_guard(nullptr);
+  }
+}
 void publish_norm(const Tensor& norm_sq, const PtrList& table_ptrs, int64_t my_rank) {
   check_f32(norm_sq, "norm_sq");
   const c10::cuda::CUDAGuard guard(norm_sq.device());
@@ -840,6 +848,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rs_pull_sumsq_mc", &rs_pull_sumsq_mc, NOGIL);
   m.def("rs_pull_sumsq", &rs_pull_sumsq, NOGIL);
   m.def("publish_norm", &publish_norm, NOGIL);
+  m.def("set_comm_guard", &set_comm_guard, py::arg("status") = py::none());
   m.def("adamw_push", &adamw_push, NOGIL);
   m.def("sumsq", &sumsq, NOGIL);
   m.def("adamw_step", &adamw_step, py::arg("p"), py::arg("m"), py::arg("v"), py::arg("g"), py::arg("p16") = py::none(),

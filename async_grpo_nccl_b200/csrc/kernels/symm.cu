@@ -32,6 +32,16 @@ struct PeerPtrs {
   int n;
 };
 
+// Status word of the peer group whose barrier precedes the kernels below on this thread's stream (nullptr = none).
+// A barrier that ran out of time has written an error code there; every kernel that would then read buffers peers may
+// still be writing, or overwrite parameters, optimizer state or inference weights, returns at entry instead, so a late
+// rank costs one raised error on the host and not the state of every rank.
+thread_local const int* t_guard = nullptr;
+
+__device__ __forceinline__ bool guard_tripped(const int* guard) {
+  return guard != nullptr && *reinterpret_cast<const volatile int*>(guard) != 0;
+}
+
 __global__ void wait_flag_probe_kernel(const uint64_t* flag, uint64_t want, long long budget, int* status) {
   if (threadIdx.x == 0 && blockIdx.x == 0) {
     if (!wait_flag_ge(flag, want, budget)) report_status(status, kStatusPeerFlagTimeout);
@@ -55,7 +65,8 @@ __global__ void flag_barrier_kernel(PeerPtrs flags, int my_rank, uint64_t epoch,
 // dst[d][global_off + i] = bf16(src[local_off + i]) for every destination d. SrcT = float or bf16.
 template <typename SrcT>
 __global__ void weight_push_kernel(const SrcT* __restrict__ src, long long local_off, long long global_off, long long n,
-                                   PeerPtrs dst) {
+                                   PeerPtrs dst, const int* guard) {
+  if (guard_tripped(guard)) return;
   const long long n8 = n / 8;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
     uint4 w;
@@ -83,7 +94,8 @@ __global__ void weight_push_kernel(const SrcT* __restrict__ src, long long local
 // source is zeroed afterwards when asked. Serves the gradients that no GEMM epilogue produces (norm weights, biases,
 // the embedding group).
 __global__ void scatter_add_f32_kernel(float* __restrict__ src, long long n, long long unit_rel, PeerPtrs dst,
-                                       long long n_per_owner, int zero_src) {
+                                       long long n_per_owner, int zero_src, const int* guard) {
+  if (guard_tripped(guard)) return;
   const long long n4 = n / 4;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
     const float4 v = reinterpret_cast<const float4*>(src)[i];
@@ -106,7 +118,8 @@ __global__ void scatter_add_f32_kernel(float* __restrict__ src, long long n, lon
 // out[local_off + i] = sum_r grads[r][global_off + i]; *norm_sq += sum(out^2). Peers are visited starting with
 // (my_rank + 1) so that ranks do not all read the same source at the same time.
 __global__ void rs_pull_sumsq_kernel(PeerPtrs grads, int my_rank, long long global_off, long long local_off, long long n,
-                                     float* __restrict__ out, float* __restrict__ norm_sq) {
+                                     float* __restrict__ out, float* __restrict__ norm_sq, const int* guard) {
+  if (guard_tripped(guard)) return;
   float acc2 = 0.f;
   const long long n4 = n / 4;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
@@ -141,7 +154,8 @@ __global__ void rs_pull_sumsq_kernel(PeerPtrs grads, int my_rank, long long glob
 // with the number of receivers.
 template <typename SrcT>
 __global__ void weight_push_mc_kernel(const SrcT* __restrict__ src, long long local_off, long long global_off, long long n,
-                                      __nv_bfloat16* mc) {
+                                      __nv_bfloat16* mc, const int* guard) {
+  if (guard_tripped(guard)) return;
   const long long n8 = n / 8;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
     uint4 w;
@@ -166,7 +180,8 @@ __global__ void weight_push_mc_kernel(const SrcT* __restrict__ src, long long lo
 // Gradient reduce-scatter with the addition done in the switch: out[local_off + i] = sum over ALL ranks of the
 // multicast group of grads[global_off + i] (ranks that are not trainers hold zeros); *norm_sq += sum(out^2).
 __global__ void rs_pull_sumsq_mc_kernel(const float* mc, long long global_off, long long local_off, long long n,
-                                        float* __restrict__ out, float* __restrict__ norm_sq) {
+                                        float* __restrict__ out, float* __restrict__ norm_sq, const int* guard) {
+  if (guard_tripped(guard)) return;
   float acc2 = 0.f;
   const long long n4 = n / 4;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
@@ -194,7 +209,8 @@ __global__ void rs_pull_sumsq_mc_kernel(const float* mc, long long global_off, l
 }
 
 // Publishes this rank's squared-norm partial into slot my_rank of every peer's partial table.
-__global__ void publish_norm_kernel(const float* norm_sq, PeerPtrs tables, int my_rank) {
+__global__ void publish_norm_kernel(const float* norm_sq, PeerPtrs tables, int my_rank, const int* guard) {
+  if (guard_tripped(guard)) return;
   const int r = threadIdx.x;
   if (r < tables.n) reinterpret_cast<float*>(tables.p[r])[my_rank] = *norm_sq;
 }
@@ -203,7 +219,8 @@ __global__ void publish_norm_kernel(const float* norm_sq, PeerPtrs tables, int m
 __global__ void adamw_push_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v, float* __restrict__ g,
                                   long long local_off, long long global_off, long long n, float lr, float beta1, float beta2,
                                   float eps, float wd, float bc1, float bc2, float grad_scale, const float* __restrict__ partials,
-                                  int n_partials, float max_norm, PeerPtrs dst) {
+                                  int n_partials, float max_norm, PeerPtrs dst, const int* guard) {
+  if (guard_tripped(guard)) return;
   float coef = grad_scale;
   if (max_norm > 0.f && partials != nullptr) {
     float tot = 0.f;
@@ -252,6 +269,8 @@ inline long long ticks_for(double seconds) { return (long long)(seconds * 1.9e9)
 
 }  // namespace
 
+void set_comm_guard(const int* status) { t_guard = status; }
+
 void launch_wait_flag_probe(const void* flag, unsigned long long want, double budget_s, int* status, cudaStream_t s) {
   wait_flag_probe_kernel<<<1, 32, 0, s>>>(reinterpret_cast<const uint64_t*>(flag), want, ticks_for(budget_s), status);
   check_cuda(cudaGetLastError(), "wait_flag_probe");
@@ -267,8 +286,8 @@ void launch_weight_push(const void* src, bool src_fp32, long long local_off, lon
                         const long long* dst_ptrs, int n_dst, cudaStream_t s) {
   if (n == 0 || n_dst == 0) return;
   const PeerPtrs d = make_peers(dst_ptrs, n_dst);
-  if (src_fp32) weight_push_kernel<float><<<blocks_for(n / 8), 256, 0, s>>>((const float*)src, local_off, global_off, n, d);
-  else weight_push_kernel<__nv_bfloat16><<<blocks_for(n / 8), 256, 0, s>>>((const __nv_bfloat16*)src, local_off, global_off, n, d);
+  if (src_fp32) weight_push_kernel<float><<<blocks_for(n / 8), 256, 0, s>>>((const float*)src, local_off, global_off, n, d, t_guard);
+  else weight_push_kernel<__nv_bfloat16><<<blocks_for(n / 8), 256, 0, s>>>((const __nv_bfloat16*)src, local_off, global_off, n, d, t_guard);
   check_cuda(cudaGetLastError(), "weight_push");
 }
 
@@ -278,22 +297,22 @@ void launch_scatter_add_f32(float* src, long long n, long long unit_rel, const S
   PeerPtrs d;
   d.n = sc.world;
   for (int r = 0; r < sc.world; ++r) d.p[r] = sc.dst[r];
-  scatter_add_f32_kernel<<<blocks_for(n / 4 + 1), 256, 0, s>>>(src, n, unit_rel, d, sc.n_per_owner, zero_src ? 1 : 0);
+  scatter_add_f32_kernel<<<blocks_for(n / 4 + 1), 256, 0, s>>>(src, n, unit_rel, d, sc.n_per_owner, zero_src ? 1 : 0, t_guard);
   check_cuda(cudaGetLastError(), "scatter_add_f32");
 }
 
 void launch_weight_push_mc(const void* src, bool src_fp32, long long local_off, long long global_off, long long n, void* mc,
                            cudaStream_t s) {
   if (n == 0) return;
-  if (src_fp32) weight_push_mc_kernel<float><<<blocks_for(n / 8), 256, 0, s>>>((const float*)src, local_off, global_off, n, (__nv_bfloat16*)mc);
-  else weight_push_mc_kernel<__nv_bfloat16><<<blocks_for(n / 8), 256, 0, s>>>((const __nv_bfloat16*)src, local_off, global_off, n, (__nv_bfloat16*)mc);
+  if (src_fp32) weight_push_mc_kernel<float><<<blocks_for(n / 8), 256, 0, s>>>((const float*)src, local_off, global_off, n, (__nv_bfloat16*)mc, t_guard);
+  else weight_push_mc_kernel<__nv_bfloat16><<<blocks_for(n / 8), 256, 0, s>>>((const __nv_bfloat16*)src, local_off, global_off, n, (__nv_bfloat16*)mc, t_guard);
   check_cuda(cudaGetLastError(), "weight_push_mc");
 }
 
 void launch_rs_pull_sumsq_mc(const void* mc, long long global_off, long long local_off, long long n, float* out, float* norm_sq,
                              cudaStream_t s) {
   if (n == 0) return;
-  rs_pull_sumsq_mc_kernel<<<blocks_for(n / 4), 256, 0, s>>>((const float*)mc, global_off, local_off, n, out, norm_sq);
+  rs_pull_sumsq_mc_kernel<<<blocks_for(n / 4), 256, 0, s>>>((const float*)mc, global_off, local_off, n, out, norm_sq, t_guard);
   check_cuda(cudaGetLastError(), "rs_pull_sumsq_mc");
 }
 
@@ -301,12 +320,12 @@ void launch_rs_pull_sumsq(const long long* grad_ptrs, int world, int my_rank, lo
                           long long n, float* out, float* norm_sq, cudaStream_t s) {
   if (n == 0) return;
   rs_pull_sumsq_kernel<<<blocks_for(n / 4), 256, 0, s>>>(make_peers(grad_ptrs, world), my_rank, global_off, local_off, n, out,
-                                                         norm_sq);
+                                                         norm_sq, t_guard);
   check_cuda(cudaGetLastError(), "rs_pull_sumsq");
 }
 
 void launch_publish_norm(const float* norm_sq, const long long* table_ptrs, int world, int my_rank, cudaStream_t s) {
-  publish_norm_kernel<<<1, 32, 0, s>>>(norm_sq, make_peers(table_ptrs, world), my_rank);
+  publish_norm_kernel<<<1, 32, 0, s>>>(norm_sq, make_peers(table_ptrs, world), my_rank, t_guard);
   check_cuda(cudaGetLastError(), "publish_norm");
 }
 
@@ -318,7 +337,7 @@ void launch_adamw_push(float* p, float* m, float* v, float* g, long long local_o
   const float bc2 = 1.f - powf(beta2, (float)step);
   adamw_push_kernel<<<blocks_for(n / 2, 148 * 16), 256, 0, s>>>(p, m, v, g, local_off, global_off, n, lr, beta1, beta2, eps, wd,
                                                                bc1, bc2, grad_scale, partials, n_partials, max_norm,
-                                                               make_peers(dst_ptrs, n_dst));
+                                                               make_peers(dst_ptrs, n_dst), t_guard);
   check_cuda(cudaGetLastError(), "adamw_push");
 }
 

@@ -235,6 +235,9 @@ void launch_rs_pull_sumsq_mc(const void* mc, long long global_off, long long loc
 void launch_rs_pull_sumsq(const long long* grad_ptrs, int world, int my_rank, long long global_off, long long local_off,
                           long long n, float* out, float* norm_sq, cudaStream_t s);
 void launch_publish_norm(const float* norm_sq, const long long* table_ptrs, int world, int my_rank, cudaStream_t s);
+// Status word (device pointer, or nullptr) that the peer-memory kernels launched from the calling thread test at entry:
+// non-zero (a barrier before them ran out of time) makes them return without touching any buffer.
+void set_comm_guard(const int* status);
 void launch_adamw_push(float* p, float* m, float* v, float* g, long long local_off, long long global_off, long long n, float lr,
                        float beta1, float beta2, float eps, float wd, int step, float grad_scale, const float* partials,
                        int n_partials, float max_norm, const long long* dst_ptrs, int n_dst, cudaStream_t s);

@@ -189,14 +189,22 @@ class InProcessRuntime:
         """Same-device sync: stop the engine between steps, then two device copies of the flat buffer."""
         t0 = time.time()
         await self.generation.pause_for_sync()
+        await asyncio.get_running_loop().run_in_executor(None, self.logprob.pause)  # no logprob batch in flight either
         core = self.trainer.core
-        if self.native:
-            torch.cuda.synchronize(self.device)
-        self.logprob_params.copy_(core.params)
-        self.rollout_params.copy_(core.params)
-        if self.native:
-            torch.cuda.synchronize(self.device)
-        await self.generation.resume_after_sync()
+        try:
+            if self.native:
+                torch.cuda.synchronize(self.device)
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                ev0.record()
+            self.logprob_params.copy_(core.params)
+            self.rollout_params.copy_(core.params)
+            if self.native:
+                ev1.record()
+                torch.cuda.synchronize(self.device)
+                self.sync_device_ms = float(ev0.elapsed_time(ev1))
+        finally:
+            self.logprob.resume()
+            await self.generation.resume_after_sync()
         self.sync_ms_history.append((time.time() - t0) * 1000.0)
 
     async def verify_weight_sync(self) -> List[str]:
@@ -580,7 +588,9 @@ class DistributedRuntime:
         return out
 
     async def sync_weights(self) -> None:
-        await self._all("sync_weights")
+        """Every rank runs its half; the device time of the push (CUDA events, max over ranks) is kept in
+        ``sync_device_ms``."""
+        self.sync_device_ms_max = max(float(x or 0.0) for x in await self._all("sync_weights"))
 
     async def verify_weight_sync(self) -> List[str]:
         sums = await self._all("verify_sync")
@@ -639,8 +649,12 @@ class DistributedRuntime:
         core = self.trainer.core if self.trainer is not None else None
         if self.weight_sync is not None:
             src, sharded = core.sync_source() if core is not None else (None, False)
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
             self.weight_sync.push(src, self.trainer_index, sharded_src=sharded)
+            ev1.record()
             torch.cuda.synchronize(self.device)
+            self.sync_device_ms = float(ev0.elapsed_time(ev1))  # barrier + push kernels + barrier, on this rank's GPU
             self.weight_sync.pg.check()
         else:
             from .parallel.symm import broadcast_weights
@@ -656,16 +670,22 @@ class DistributedRuntime:
             if self.native:
                 torch.cuda.synchronize(self.device)
 
-    async def local_sync_weights(self) -> bool:
+    async def local_sync_weights(self) -> float:
+        loop = asyncio.get_running_loop()
         if self.generation is not None:
             await self.generation.pause_for_sync()
-        if self.native:
-            torch.cuda.synchronize(self.device)
-        loop = asyncio.get_running_loop()
-        await loop.run_in_executor(self._comm_pool, self._sync_on_device)
-        if self.generation is not None:
-            await self.generation.resume_after_sync()
-        return True
+        if self.logprob is not None:
+            await loop.run_in_executor(None, self.logprob.pause)  # the batch in flight finishes, no new one starts
+        try:
+            if self.native:
+                torch.cuda.synchronize(self.device)
+            await loop.run_in_executor(self._comm_pool, self._sync_on_device)
+        finally:
+            if self.logprob is not None:
+                self.logprob.resume()
+            if self.generation is not None:
+                await self.generation.resume_after_sync()
+        return float(getattr(self, "sync_device_ms", 0.0))
 
     async def local_checksum(self) -> Dict[str, Optional[float]]:
         out: Dict[str, Optional[float]] = {"trainer": None, "infer": None}

@@ -216,6 +216,10 @@ class Orchestrator:
             "timing/3_trainer_active_time": trainer_active,
             "timing/4_total_overhead": max(0.0, total_time - wall_gen - trainer_active),
             "timing/weight_sync_ms": sync_ms,
+            # device time of the push itself (CUDA events, max over ranks); the figure above is the host's wall clock
+            # around pausing the roles, the RPC fan-out and the push
+            "timing/weight_sync_device_ms": float(getattr(rt, "sync_device_ms_max", getattr(rt, "sync_device_ms", 0.0)) or 0.0)
+            if sync_ms else 0.0,
             "generation/total_tokens_generated": gen_tokens,
             "generation/inference_duration_sec": float(glm.get("generation/inference_duration_sec", 0.0)),
             "generation/num_samples_generated": float(glm.get("generation/num_samples_generated", 0.0)),

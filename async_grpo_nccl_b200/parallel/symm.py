@@ -194,6 +194,7 @@ class TrainerComm:
         """grad_shard <- sum over ranks of this rank's slice of every unit; norm partial published to all peers."""
         C, L = self.C, self.layout
         _trace("reduce_scatter", multicast=bool(self.grads_mc))
+        C.set_comm_guard(self.pg.status)  # kernels behind a barrier that timed out return without touching anything
         self.pg.barrier()  # every rank's backward has finished and its gradients are visible
         self.norm_local.zero_()
         for u, (lo, gs, ln) in enumerate(L.local_to_global_ranges(self.rank)):
@@ -210,6 +211,7 @@ class TrainerComm:
         """Returns the device tensor holding the per-rank squared-norm partials (sum = global squared norm)."""
         C, L = self.C, self.layout
         _trace("adamw_and_publish", step=step)
+        C.set_comm_guard(self.pg.status)
         dsts = list(self.param_ptrs) + list(extra_dst_ptrs)
         partials = self.norm_partials
         for u, (lo, gs, ln) in enumerate(L.local_to_global_ranges(self.rank)):
@@ -242,6 +244,7 @@ class WeightSync:
         ``sharded_src`` just their own slices back to back) and their index among the trainers; the others pass None
         and only take part in the barriers."""
         _trace("weight_push", source=trainer_index, sharded=sharded_src, multicast=bool(self.dst_mc))
+        self.C.set_comm_guard(self.pg.status)
         self.pg.barrier()  # inference ranks are idle (paused by the orchestrator) and trainers finished their step
         if src_params is not None and trainer_index is not None:
             t = len(self.trainer_ranks)

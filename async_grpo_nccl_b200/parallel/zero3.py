@@ -229,6 +229,7 @@ class Zero3Comm:
     def step(self, master, exp_avg, exp_avg_sq, lr, beta1, beta2, eps, wd, step, max_norm) -> torch.Tensor:
         """Optimizer step on this rank's shard; returns the device tensor of per-rank squared-norm partials."""
         C = self.C
+        C.set_comm_guard(self.pg.status)  # a timed-out barrier turns the update below into a no-op (the host then raises)
         self.pg.barrier()  # every rank's backward has finished: all reductions into my gradient shard have landed
         self.norm_local.zero_()
         C.sumsq(self.grad_shard, 1.0, self.norm_local)

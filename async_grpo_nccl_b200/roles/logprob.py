@@ -116,8 +116,31 @@ class LogProbWorker:
         return {"tokens": float(self.tokens_processed), "batches": float(self.batches), "busy_seconds": self.busy_seconds,
                 "launches": float(getattr(self.decoder, "launches", 0))}
 
+    def pause(self) -> None:
+        """Blocks until the batch in flight (if any) has finished and keeps the compute thread from starting another
+        one until :meth:`resume`. The weight sync brackets its device half with the pair, so that no forward pass runs on
+        parameters that are being overwritten. Call it from a thread that may block."""
+        import threading
+
+        self._hold = threading.Event()
+        started = threading.Event()
+
+        def holder() -> None:
+            started.set()
+            self._hold.wait(timeout=600.0)
+
+        self._pool.submit(holder)
+        started.wait()
+
+    def resume(self) -> None:
+        hold = getattr(self, "_hold", None)
+        if hold is not None:
+            hold.set()
+
     def run_blocking(self, fn, *args):
-        """Runs ``fn`` on the compute thread (used by the weight sync so it is ordered with inference)."""
+        """Runs ``fn`` on the compute thread: it starts after the batch that is being computed and before the next one
+        (the pool has one thread). The weight sync runs its device half through here, so that no forward pass reads
+        parameters that are half written."""
         return self._pool.submit(fn, *args).result()
 
 

@@ -49,6 +49,10 @@ class GenerationWorker:
         self._paused = threading.Event()
         self._idle = threading.Event()
         self._idle.set()
+        # One lock orders "the engine thread decides to step" against "a weight sync asks it to stop": the thread
+        # re-checks the pause flag and clears the idle flag under it, the sync sets the pause flag under it. Either the
+        # sync sees the idle flag cleared and waits for the step to end, or the thread sees the pause flag and stays idle.
+        self._gate = threading.Lock()
         self._thread = threading.Thread(target=self._engine_loop, name="rollout-engine", daemon=True)
         self._thread.start()
         self._req_counter = 0
@@ -64,12 +68,16 @@ class GenerationWorker:
                     new, self._incoming = self._incoming, []
                 for args in new:
                     self.engine.add_request(*args[0], **args[1])
-                if self._paused.is_set() or not self.engine.has_work():
-                    self._idle.set()
+                with self._gate:
+                    go = not self._paused.is_set() and self.engine.has_work()
+                    if go:
+                        self._idle.clear()
+                    else:
+                        self._idle.set()
+                if not go:
                     self._wake.wait(timeout=0.05)
                     self._wake.clear()
                     continue
-                self._idle.clear()
                 t0 = time.time()
                 try:
                     finished = self.engine.step()
@@ -223,7 +231,8 @@ class GenerationWorker:
     # ------------------------------------------------------------------ weight sync (receiver side)
     async def pause_for_sync(self) -> bool:
         """Stops stepping after the current step; returns once the engine thread is idle."""
-        self._paused.set()
+        with self._gate:
+            self._paused.set()
         self._wake.set()
         while not self._idle.is_set():
             await asyncio.sleep(0.001)

@@ -14,7 +14,8 @@ EOS forced at the drawn length, Bernoulli(0.3) reward, packed microbatches of at
 Per-GPU work is fixed as N grows (weak scaling); at N = 8 the placement is 4 trainer + 1 logprob +
 3 rollout ranks and the step is 128 prompts x 8 samples.
 
-Rank 0 prints one JSON line. ``--impl reference`` reports why the reference cannot run here.
+Rank 0 prints one JSON line. ``--impl reference`` runs the same workload through the reference's own workers
+(``baseline/reference_arm.py``).
 """
 from __future__ import annotations
 
@@ -52,6 +53,11 @@ def parse_args():
                     help="SMs that trainer / logprob GEMMs may fill on a GPU shared with a rollout engine (0 = all)")
     ap.add_argument("--placement", default=None, help='JSON role placement overriding the default, e.g. '
                     '\'{"trainer": [0, 1], "logprob": [0], "rollout": [1]}\'')
+    # reference arm only (its own defaults: orchestrator.py:137, 158 of the reference)
+    ap.add_argument("--ref-max-num-seqs", type=int, default=512, help="vLLM max_num_seqs of the reference arm (its default)")
+    ap.add_argument("--ref-loss-chunksize", type=int, default=None, help="loss_chunksize of the reference arm (its default: none)")
+    ap.add_argument("--ref-colocated-mem", type=float, default=0.10,
+                    help="vLLM gpu_memory_utilization where the engine shares a GPU with FSDP workers (0.90 otherwise)")
     return ap.parse_args()
 
 
@@ -104,16 +110,18 @@ class ClockSampler:
 
 
 def reference_arm(args) -> None:
-    why = ("reference is not installable: pip reports neither setup.py nor pyproject.toml in its tree, and its modules "
-           "import ray, omegaconf and peft, none of which are installed in this image")
+    """Runs the unmodified reference workers from ``baseline/_ref`` (see ``baseline/reference_arm.py``); every rank
+    takes part, rank 0 prints the JSON line. Must be entered before ``torch`` is imported (it pins one GPU per process)."""
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
-    if os.path.isdir(ref_dir) and os.listdir(ref_dir):
-        try:
-            sys.path.insert(0, ref_dir)
-            import ray  # noqa: F401
-        except Exception as e:
-            why = f"reference installed but cannot start: {e!r}"
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+    if not (os.path.isdir(ref_dir) and os.path.exists(os.path.join(ref_dir, "gpu_process_worker.py"))):
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref does not hold the reference tree (copy the "
+                              "reference's *.py files there; pip cannot install it: no setup.py / pyproject.toml)"}))
+        return
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_arm as arm
+
+    arm.run(args)
 
 
 def placement_for(n: int):
@@ -133,8 +141,7 @@ def placement_for(n: int):
 def main() -> None:
     args = parse_args()
     if args.impl == "reference":
-        if int(os.environ.get("RANK", "0")) == 0:
-            reference_arm(args)
+        reference_arm(args)
         return
     import torch
 
@@ -237,6 +244,7 @@ def run_timed(cfg, runtime, rows, args, n, rank, dist, mcfg):
     before, after = state["stats"]
     diff = {k: after.get(k, 0.0) - before.get(k, 0.0) for k in after}
     sync_ms = [float(r.get("timing/weight_sync_ms", 0.0)) for r in recs]
+    sync_dev_ms = [float(r.get("timing/weight_sync_device_ms", 0.0)) for r in recs]
     place = cfg.resolved_placement()
     par = f"trainer{len(place['trainer'])}+logprob{len(place['logprob'])}+rollout{len(place['rollout'])}" + (" colocated" if n < 3 else "")
     out = {
@@ -249,7 +257,8 @@ def run_timed(cfg, runtime, rows, args, n, rank, dist, mcfg):
                    "seq_len": f"prompt U[{args.prompt_min},{args.prompt_max}] + generation logU[{args.gen_min},{args.gen_max}]",
                    "parallelism": par, "max_tokens_per_microbatch": cfg.max_tokens_per_gpu,
                    "l2": "working set (3.1 GB of weights, multi-GB KV cache and activations per step) is far larger than the 126 MB L2; no flush needed",
-                   "engine_preset": cfg.vllm_engine_preset},
+                   "engine_preset": cfg.vllm_engine_preset, "max_num_seqs": cfg.max_num_seqs,
+                   "eager_microbatch_dispatch": bool(cfg.eager_microbatch_dispatch), "param_sharding": cfg.param_sharding},
         "clocks": state["clocks"],
         "e2e": {"value": samples / state["wall"], "unit": "samples/s",
                 "h2d_bytes_per_step": diff.get("h2d_bytes", 0.0) / args.steps, "d2h_bytes_per_step": diff.get("d2h_bytes", 0.0) / args.steps,
@@ -257,6 +266,7 @@ def run_timed(cfg, runtime, rows, args, n, rank, dist, mcfg):
                         "pinned buffers and copied per microbatch, results (loss statistics, logprobs, generated ids) are read back"},
         "gpu_launches": int(diff.get("launches", 0.0)),
         "extra": {"gen_tokens_per_s": gen_tokens / dev_s, "weight_sync_ms_mean": sum(sync_ms) / max(1, len(sync_ms)),
+                  "weight_sync_device_ms_mean": sum(sync_dev_ms) / max(1, len(sync_dev_ms)),
                   "samples": samples, "gen_tokens": gen_tokens, "optimizer_steps": sum(r["training/optimizer_steps_in_batch"] for r in recs),
                   # host seconds of the rollout engines' step loops inside the timed region, summed over engines
                   "engine_host": {k: round(v, 4) for k, v in diff.items() if k.startswith("engine_")}},

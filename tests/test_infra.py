@@ -217,3 +217,96 @@ def test_dataset_preparation_cli_and_math_rows(tmp_path):
     lines = [json.loads(x) for x in out.read_text().splitlines()]
     assert len(lines) == 5 and all(len(r["forced_output_lens"]) == 4 for r in lines)
     assert all(8 <= n <= 64 for r in lines for n in r["forced_output_lens"])
+
+
+def test_engine_never_steps_while_a_weight_sync_holds_it_paused():
+    """The rollout role's engine thread and ``pause_for_sync`` hand over under one lock: after the pause returns no step
+    is running and none starts until the resume."""
+    import asyncio
+    import threading
+    import time
+
+    from async_grpo_nccl_b200.roles.rollout import GenerationWorker
+
+    class StubEngine:
+        eos = 0
+        max_model_len = 64
+
+        def __init__(self):
+            self.worker = None
+            self.in_step = threading.Event()
+            self.violations = 0
+            self.steps = 0
+
+        def has_work(self):
+            return True
+
+        def add_request(self, *a, **k):
+            pass
+
+        def step(self):
+            if self.worker._paused.is_set() and self.worker._idle.is_set():
+                self.violations += 1
+            self.in_step.set()
+            time.sleep(0.0005)
+            self.steps += 1
+            self.in_step.clear()
+            return []
+
+        def update_weights_done(self):
+            pass
+
+    eng = StubEngine()
+    w = GenerationWorker(config=None, model_cfg=None, engine=eng, verifier_pool=None)
+    eng.worker = w
+
+    async def body():
+        for _ in range(200):
+            await w.pause_for_sync()
+            assert not eng.in_step.is_set()
+            before = eng.steps
+            await asyncio.sleep(0.002)
+            assert eng.steps == before, "the engine stepped while paused"
+            await w.resume_after_sync()
+            await asyncio.sleep(0.001)
+
+    try:
+        asyncio.run(body())
+    finally:
+        w.shutdown()
+    assert eng.violations == 0 and eng.steps > 0
+
+
+def test_logprob_pause_waits_for_the_batch_in_flight_and_holds_the_next_one():
+    import threading
+    import time
+
+    from async_grpo_nccl_b200.roles.logprob import LogProbWorker
+
+    class Cfg:
+        temperature = 1.0
+        max_tokens_per_gpu = 1000
+
+    w = LogProbWorker(Cfg(), None, decoder=None, device="cpu")
+    order = []
+    gate = threading.Event()
+
+    def slow_batch():
+        order.append("batch-start")
+        gate.wait(timeout=5)
+        order.append("batch-end")
+
+    w._pool.submit(slow_batch)
+    time.sleep(0.05)
+    t = threading.Thread(target=lambda: (w.pause(), order.append("paused")))
+    t.start()
+    time.sleep(0.05)
+    assert order == ["batch-start"], "pause must not return while a batch is being computed"
+    gate.set()
+    t.join(timeout=5)
+    fut = w._pool.submit(lambda: order.append("next-batch"))
+    time.sleep(0.05)
+    order.append("sync-done")
+    w.resume()
+    fut.result(timeout=5)
+    assert order == ["batch-start", "batch-end", "paused", "sync-done", "next-batch"]

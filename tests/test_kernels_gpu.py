@@ -519,3 +519,34 @@ def test_qkv_gemm_with_rope_and_cache_write_epilogue(M, Hq, Hkv, H):
     # the same cache cells are written (and only those)
     assert torch.equal(k1.abs().sum(-1) > 0, k0.abs().sum(-1) > 0)
     assert torch.equal(v1.abs().sum(-1) > 0, v0.abs().sum(-1) > 0)
+
+
+def test_peer_kernels_return_untouched_when_the_group_status_is_set():
+    """A barrier that ran out of time leaves an error code in the group's status word; the kernels queued behind it
+    (weight push, gradient pull, AdamW + publish) must then leave parameters, moments and destinations as they were."""
+    C = native()
+    torch.manual_seed(3)
+    n = 4096
+    st = status_word()
+    src = torch.randn(n, device=DEV, dtype=torch.float32)
+    dst = torch.zeros(n, device=DEV, dtype=torch.bfloat16)
+    p, m, v = src.clone(), torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    g = torch.randn(n, device=DEV)
+    partials = torch.ones(1, device=DEV)
+    out, norm = torch.zeros(n, device=DEV), torch.zeros(1, device=DEV)
+    try:
+        C.set_comm_guard(st)
+        st.fill_(7)  # what a timed-out barrier records
+        C.weight_push(src, 0, 0, n, [dst.data_ptr()])
+        C.adamw_push(p, m, v, g.clone(), 0, 0, n, 1e-2, 0.9, 0.999, 1e-8, 0.0, 1, 1.0, partials, 1.0, [dst.data_ptr()])
+        C.rs_pull_sumsq([g.data_ptr()], 0, 0, 0, n, out, norm)
+        torch.cuda.synchronize()
+        assert dst.abs().sum().item() == 0 and torch.equal(p, src) and m.abs().sum().item() == 0 and v.abs().sum().item() == 0
+        assert out.abs().sum().item() == 0 and norm.item() == 0
+        st.zero_()
+        C.weight_push(src, 0, 0, n, [dst.data_ptr()])
+        C.rs_pull_sumsq([g.data_ptr()], 0, 0, 0, n, out, norm)
+        torch.cuda.synchronize()
+        assert torch.equal(dst, src.to(torch.bfloat16)) and torch.equal(out, g)
+    finally:
+        C.set_comm_guard(None)
