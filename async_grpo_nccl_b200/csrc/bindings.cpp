@@ -433,6 +433,71 @@ bool gemm_decode_rope(const Tensor& a, const Tensor& b, Tensor& qkv, const OptTe
                                    opt_i64(ss_in), nullptr, (float)eps, &r);
 }
 
+// All decoder layers of one decode step in one persistent launch (csrc/kernels/decode_mega.cu). Weights are given as
+// the layer-0 matrices ([rows, K] views into flat buffers) plus the element stride from one layer to the next.
+bool decode_layers_supported(int64_t rows, int64_t H, int64_t Q, int64_t QD, int64_t F, int64_t Hq, int64_t Hkv, int64_t D) {
+  return agrpo::decode_layers_supported((int)rows, (int)H, (int)Q, (int)QD, (int)F, (int)Hq, (int)Hkv, (int)D);
+}
+int64_t decode_layers_scratch_bytes(int64_t rows, int64_t H, int64_t Q, int64_t QD, int64_t F) {
+  return agrpo::decode_layers_scratch_bytes((int)rows, (int)H, (int)Q, (int)QD, (int)F, num_sms());
+}
+int64_t decode_layers_counter_words() { return agrpo::decode_layers_counter_words(); }
+void decode_layers(int64_t L, int64_t B, const Tensor& wqkv0, int64_t wqkv_stride, const Tensor& wo0, int64_t wo_stride,
+                   const Tensor& wgu0, int64_t wgu_stride, const Tensor& wd0, int64_t wd_stride, const OptTensor& bqkv0,
+                   int64_t bqkv_stride, Tensor& x, Tensor& x1, Tensor& qkv, Tensor& attn, Tensor& act, Tensor& ss, double eps,
+                   const Tensor& cos_t, const Tensor& sin_t, const Tensor& block_tables, const Tensor& seq_lens, Tensor& cache,
+                   int64_t Hq, int64_t Hkv, double softmax_scale, int64_t splits, Tensor& part_o, Tensor& part_ml, Tensor& tickets,
+                   Tensor& partials, Tensor& counters, const OptTensor& status) {
+  check_bf16(wqkv0, "wqkv"); check_bf16(wo0, "wo"); check_bf16(wgu0, "wgu"); check_bf16(wd0, "wd");
+  check_bf16(x, "x"); check_bf16(x1, "x1"); check_bf16(qkv, "qkv"); check_bf16(attn, "attn"); check_bf16(act, "act");
+  check_i64(ss, "ss"); check_f32(cos_t, "cos"); check_f32(sin_t, "sin"); check_i32(block_tables, "block_tables");
+  check_i32(seq_lens, "seq_lens"); check_bf16(cache, "cache"); check_f32(part_o, "part_o"); check_f32(part_ml, "part_ml");
+  check_i32(tickets, "tickets"); check_f32(partials, "partials"); check_i32(counters, "counters");
+  const int64_t H = x.size(1), Q = qkv.size(1), QD = attn.size(1), F = act.size(1), rows_alloc = x.size(0);
+  TORCH_CHECK(x.is_contiguous() && x1.is_contiguous() && qkv.is_contiguous() && attn.is_contiguous() && act.is_contiguous(),
+              "decode_layers: activation buffers must be contiguous");
+  TORCH_CHECK(x1.size(0) == rows_alloc && qkv.size(0) == rows_alloc && attn.size(0) == rows_alloc && act.size(0) == rows_alloc &&
+              x1.size(1) == H, "decode_layers: activation buffers must have the same number of rows");
+  const int64_t BT = B <= 32 ? 32 : B <= 64 ? 64 : B <= 128 ? 128 : 256;
+  TORCH_CHECK(B >= 1 && rows_alloc >= BT, "decode_layers: buffers must hold the row tile that covers the batch");
+  TORCH_CHECK(agrpo::decode_layers_supported((int)B, (int)H, (int)Q, (int)QD, (int)F, (int)Hq, (int)Hkv, 128), "decode_layers: shape not served");
+  TORCH_CHECK(wqkv0.dim() == 2 && wqkv0.is_contiguous() && wqkv0.size(0) == Q && wqkv0.size(1) == H, "decode_layers: wqkv [Q, H]");
+  TORCH_CHECK(wo0.dim() == 2 && wo0.is_contiguous() && wo0.size(0) == H && wo0.size(1) == QD, "decode_layers: wo [H, q_dim]");
+  TORCH_CHECK(wgu0.dim() == 2 && wgu0.is_contiguous() && wgu0.size(0) == 2 * F && wgu0.size(1) == H, "decode_layers: wgu [2F, H]");
+  TORCH_CHECK(wd0.dim() == 2 && wd0.is_contiguous() && wd0.size(0) == H && wd0.size(1) == F, "decode_layers: wd [H, F]");
+  TORCH_CHECK(wqkv_stride % 8 == 0 && wo_stride % 8 == 0 && wgu_stride % 8 == 0 && wd_stride % 8 == 0, "decode_layers: layer strides");
+  TORCH_CHECK(ss.dim() == 2 && ss.stride(1) == 1 && ss.size(0) >= 2 * L + 1 && ss.size(1) >= B, "decode_layers: ss [2L+1, >= rows]");
+  TORCH_CHECK(cos_t.is_contiguous() && sin_t.is_contiguous() && cos_t.dim() == 2 && cos_t.size(1) == 64 && sin_t.sizes() == cos_t.sizes(),
+              "decode_layers: cos / sin tables [max_pos, 64]");
+  TORCH_CHECK(block_tables.dim() == 2 && block_tables.stride(1) == 1 && block_tables.size(0) >= B && seq_lens.numel() >= B, "decode_layers: tables");
+  TORCH_CHECK(cache.dim() == 6 && cache.is_contiguous() && cache.size(0) == L && cache.size(1) == 2 && cache.size(3) == Hkv &&
+              cache.size(4) == 16 && cache.size(5) == 128, "decode_layers: cache [L, 2, blocks, Hkv, 16, 128]");
+  TORCH_CHECK(splits >= 1 && splits <= 64, "decode_layers: splits");
+  TORCH_CHECK(part_o.numel() >= B * Hkv * splits * 8 * 128 && part_ml.numel() >= B * Hkv * splits * 16 && tickets.numel() >= B * Hkv,
+              "decode_layers: split-KV scratch");
+  TORCH_CHECK(counters.numel() >= agrpo::decode_layers_counter_words(), "decode_layers: counters");
+  agrpo::DecodeLayersArgs a;
+  a.L = (int)L; a.B = (int)B; a.rows_alloc = (int)rows_alloc; a.H = (int)H; a.Q = (int)Q; a.QD = (int)QD; a.F = (int)F;
+  a.Hq = (int)Hq; a.Hkv = (int)Hkv; a.num_sms = num_sms(); a.splits = (int)splits;
+  a.wqkv = wqkv0.data_ptr(); a.wo = wo0.data_ptr(); a.wgu = wgu0.data_ptr(); a.wd = wd0.data_ptr();
+  a.wqkv_stride = wqkv_stride; a.wo_stride = wo_stride; a.wgu_stride = wgu_stride; a.wd_stride = wd_stride;
+  a.bqkv = nullptr; a.bqkv_stride = bqkv_stride;
+  if (bqkv0.has_value() && bqkv0->defined()) { check_bf16(*bqkv0, "bqkv"); TORCH_CHECK(bqkv0->numel() == Q, "bqkv [Q]"); a.bqkv = bqkv0->data_ptr(); }
+  a.x = x.data_ptr(); a.x1 = x1.data_ptr(); a.qkv = qkv.data_ptr(); a.attn = attn.data_ptr(); a.act = act.data_ptr();
+  a.ss = reinterpret_cast<long long*>(ss.data_ptr<int64_t>()); a.ss_stride = (int)ss.stride(0); a.eps = (float)eps;
+  a.cos_t = cos_t.data_ptr<float>(); a.sin_t = sin_t.data_ptr<float>(); a.max_pos = (int)cos_t.size(0);
+  a.block_tables = block_tables.data_ptr<int>(); a.max_blocks = (int)block_tables.stride(0); a.seq_lens = seq_lens.data_ptr<int>();
+  a.cache = cache.data_ptr(); a.cache_layer_stride = cache.stride(0); a.cache_v_off = cache.stride(1);
+  a.num_cache_blocks = (int)cache.size(2);
+  a.softmax_scale = (float)softmax_scale;
+  a.part_o = part_o.data_ptr<float>(); a.part_ml = part_ml.data_ptr<float>(); a.att_tickets = tickets.data_ptr<int>();
+  a.partials = partials.data_ptr<float>(); a.partials_bytes = partials.numel() * 4;
+  a.counters = reinterpret_cast<unsigned int*>(counters.data_ptr<int>());
+  a.status = opt_ptr<int>(status);
+  const c10::cuda::CUDAGuard guard(x.device());
+  agrpo::launch_decode_layers(a, cur_stream());
+}
+
 void paged_decode_attn(const Tensor& qkv, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_tables,
                        const Tensor& seq_lens, Tensor& out, int64_t Hq, int64_t Hkv, int64_t D, double softmax_scale,
                        int64_t splits, const OptTensor& part_o, const OptTensor& part_ml, const OptTensor& status,
@@ -787,6 +852,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_skinny_splits", &gemm_skinny_splits);
   m.def("gemm_decode_rope", &gemm_decode_rope, NOGIL);
   m.def("decode_step_inputs", &decode_step_inputs, NOGIL);
+  m.def("decode_layers", &decode_layers, NOGIL);
+  m.def("decode_layers_supported", &decode_layers_supported);
+  m.def("decode_layers_scratch_bytes", &decode_layers_scratch_bytes);
+  m.def("decode_layers_counter_words", &decode_layers_counter_words);
   m.def("gemm_swiglu", &gemm_swiglu, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("ss_in") = py::none(), py::arg("eps") = 1e-6,
         py::arg("status") = py::none(), NOGIL);
   m.def("rmsnorm_fwd", &rmsnorm_fwd, py::arg("x"), py::arg("w"), py::arg("y"), py::arg("rstd") = py::none(),

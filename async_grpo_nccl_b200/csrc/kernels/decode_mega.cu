@@ -1,0 +1,667 @@
+// All decoder layers of one decode step in ONE persistent launch (one CTA per SM, cooperative launch).
+//
+// A decode step at small batch is bound by streaming the weights once; as ~140 separate launches each GEMM pays a
+// cold start (first TMA round trip, barrier set-up, TMEM allocation) and a tail that are as long as its streaming time.
+// Here the weight stream never stops: a dedicated warp issues the TMA loads of every weight tile of every phase of every
+// layer in order, limited only by the depth of its shared-memory ring, so the loads of the next phase are in flight
+// while the current phase's results are still being reduced. Only the (small) activation loads wait for the phase before.
+//
+// The GEMMs run "swapped": the weight tile supplies the 128 MMA rows (output features), the batch rows are the MMA N
+// dimension (BT = 32 .. 256), so a small batch costs a small MMA and no padding traffic.
+//
+//   per layer:  qkv = rs(x) * (x . Wqkv'^T) + b, RoPE, KV-cache write      (phase 0, split K)
+//               attention over the paged cache, split-KV                     (compute warps)
+//               x1  = x + attn . Wo^T, row sums of squares                    (phase 1, split K)
+//               act = silu(rs * x1 . Wg'^T) * (rs * x1 . Wu'^T)               (phase 2)
+//               x   = x1 + act . Wd^T, row sums of squares                    (phase 3, split K)
+//   (W' = weight with the RMSNorm weight folded into its columns, rs = 1 / rms of the row.)
+//
+// Work item of a GEMM phase = (128-feature tile, K split). Every item writes its fp32 partial tile to a scratch slot
+// (L2-resident), bumps the tile's arrival counter, waits (bounded) until all S splits of the tile have arrived, then
+// reduces ITS share of the batch rows over the S partials in a fixed order and applies the epilogue: the reduction is
+// spread over all CTAs and its result does not depend on arrival order. A global counter `done` counts finished shares;
+// the activation producer of the next phase waits for the count that says the whole phase is complete.
+//
+// Every wait is bounded; a wait that runs out records a status code, makes the CTA leave through its normal exit (TMEM
+// freed) and the other CTAs follow as soon as they see the status word.
+#include <cuda_bf16.h>
+
+#include "../common/ptx.cuh"
+#include "../common/tensormap.h"
+#include "../launchers.h"
+#include "decode_attn.cuh"
+
+namespace agrpo {
+
+namespace {
+
+constexpr int kMegaThreads = 256;
+constexpr int kFT = 128;                    // features per item (MMA M)
+constexpr int kMBK = 64;                    // K per stage
+constexpr int kWStage = kFT * kMBK * 2;     // 16 KB
+constexpr int kMaxGroups = 512;             // arrival counters per GEMM phase
+
+struct MegaPhase {
+  int n_groups;  // feature tiles
+  int S;         // K splits per tile
+  int num_kb;    // K / 64
+};
+
+struct MegaParams {
+  int L, B, H, Q, QD, F, Hq, Hkv, grid;
+  MegaPhase ph[4];
+  int att_groups, splits;
+  unsigned int per_layer;  // `done` increments per layer
+  __nv_bfloat16 *x, *x1, *qkv, *attn, *act;
+  const __nv_bfloat16* bqkv;
+  long long bqkv_stride;
+  sumsq_t* ss;
+  int ss_stride;
+  float eps, inv_h;
+  const float *cos_t, *sin_t;
+  int max_pos;
+  const int* block_tables;
+  int max_blocks;
+  const int* seq_lens;
+  __nv_bfloat16* cache;
+  long long cache_layer_stride, cache_v_off;
+  int num_cache_blocks;
+  float scale_log2;
+  float *part_o, *part_ml;
+  int* att_tickets;
+  float* partials;
+  unsigned int* arrive;  // [4][kMaxGroups] monotonic arrival counters
+  unsigned int* done;
+  int* status;
+};
+
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_gpu_add(unsigned int* p, unsigned int v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ bool status_set(const int* status) {
+  return status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0;
+}
+// Bounded wait until *ctr >= want. Gives up early when another CTA has already reported a failure.
+__device__ __forceinline__ bool wait_counter(const unsigned int* ctr, unsigned int want, const int* status) {
+  if (ld_acquire_gpu(ctr) >= want) return true;
+  const long long t0 = clock64();
+  int it = 0;
+  while (ld_acquire_gpu(ctr) < want) {
+    if ((++it & 31) == 0) {
+      if (status_set(status)) return false;
+      if (clock64() - t0 > kWaitBudgetTicks) return false;
+    }
+  }
+  return true;
+}
+// mbarrier wait that also gives up when the status word is set.
+__device__ __forceinline__ bool mbar_wait_s(uint64_t* bar, uint32_t parity, const int* status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  int it = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++it & 63) == 0) {
+      if (status_set(status)) return false;
+      if (clock64() - t0 > kWaitBudgetTicks) return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ float4 shfl_xor4(float4 v, int m) {
+  return make_float4(__shfl_xor_sync(0xffffffffu, v.x, m), __shfl_xor_sync(0xffffffffu, v.y, m),
+                     __shfl_xor_sync(0xffffffffu, v.z, m), __shfl_xor_sync(0xffffffffu, v.w, m));
+}
+__device__ __forceinline__ float4 ld_bf16x4(const __nv_bfloat16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void st_bf16x4(__nv_bfloat16* p, float4 v) {
+  uint2 u;
+  u.x = pack_bf16x2(v.x, v.y);
+  u.y = pack_bf16x2(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+template <int BT>
+struct MegaCfg {
+  static constexpr int kXStage = BT * kMBK * 2;
+  static constexpr int kNSW = BT <= 128 ? 8 : 7;
+  static constexpr int kXA = BT <= 128 ? 65536 : 98304;  // activation ring; the attention phase stages K/V tiles here
+  static constexpr int kNSX = (kXA / kXStage) > 8 ? 8 : (kXA / kXStage);
+  static constexpr int kAcc = 2;
+  static constexpr uint32_t kTmemCols = (kAcc * BT) < 32 ? 32 : (kAcc * BT);
+  static constexpr int kSmem = kNSW * kWStage + kXA + 1024 /* barriers */ + 1024 /* alignment */;
+};
+
+// What the roles of one CTA share.
+struct MegaShared {
+  uint64_t full_w[8], empty_w[8], full_x[8], empty_x[8], tmem_full[2], tmem_empty[2], xa_bar;
+  uint32_t tmem_slot;
+  int s_last;
+  int abort;
+};
+
+template <int BT>
+__global__ void __launch_bounds__(kMegaThreads, 1)
+decode_layers_kernel(const __grid_constant__ CUtensorMap tmWqkv, const __grid_constant__ CUtensorMap tmWo,
+                     const __grid_constant__ CUtensorMap tmWgu, const __grid_constant__ CUtensorMap tmWd,
+                     const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmAttn,
+                     const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ CUtensorMap tmAct, const MegaParams p) {
+  using Cfg = MegaCfg<BT>;
+  constexpr int NSW = Cfg::kNSW, NSX = Cfg::kNSX;
+  constexpr uint32_t kIdesc = umma_idesc_bf16(kFT, BT, 0, 0);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* w_ring = smem;
+  uint8_t* xa = smem + NSW * kWStage;
+  MegaShared* sh = reinterpret_cast<MegaShared*>(xa + Cfg::kXA);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cta = blockIdx.x, G = p.grid;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 8; ++s) {
+      mbar_init(&sh->full_w[s], 1);
+      mbar_init(&sh->empty_w[s], 1);
+      mbar_init(&sh->full_x[s], 1);
+      mbar_init(&sh->empty_x[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&sh->tmem_full[a], 1);
+      mbar_init(&sh->tmem_empty[a], 1);
+    }
+    mbar_init(&sh->xa_bar, 128);
+    sh->s_last = 0;
+    sh->abort = 0;
+    fence_mbar_init();
+  }
+  if (warp == 3) {
+    tmem_alloc(&sh->tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sh->tmem_slot;
+
+  // done-counter value at which the inputs of GEMM phase ph of layer l are complete
+  auto target = [&](int l, int ph) -> unsigned int {
+    unsigned int t = (unsigned int)l * p.per_layer;
+    if (ph >= 1) t += (unsigned int)(p.ph[0].n_groups * p.ph[0].S) + (unsigned int)p.att_groups;
+    if (ph >= 2) t += (unsigned int)(p.ph[1].n_groups * p.ph[1].S);
+    if (ph >= 3) t += (unsigned int)(p.ph[2].n_groups * p.ph[2].S);
+    return t;
+  };
+
+  if (warp == 0) {
+    // ================= weight producer: never waits for another CTA =================
+    if (elect_one()) {
+      int st = 0;
+      uint32_t par = 0;
+      bool ok = true;
+      for (int l = 0; l < p.L && ok; ++l) {
+        for (int ph = 0; ph < 4 && ok; ++ph) {
+          const CUtensorMap* tm = ph == 0 ? &tmWqkv : ph == 1 ? &tmWo : ph == 2 ? &tmWgu : &tmWd;
+          const int S = p.ph[ph].S, nkb = p.ph[ph].num_kb, n_items = p.ph[ph].n_groups * S;
+          for (int item = cta; item < n_items && ok; item += G) {
+            const int ft = item / S, ks = item - ft * S;
+            const int kb0 = (int)((long long)nkb * ks / S), kb1 = (int)((long long)nkb * (ks + 1) / S);
+            for (int kb = kb0; kb < kb1; ++kb) {
+              if (!mbar_wait_s(&sh->empty_w[st], par ^ 1, p.status)) {
+                report_status(p.status, kStatusWaitEmptyTimeout);
+                ok = false;
+                break;
+              }
+              uint8_t* dst = w_ring + st * kWStage;
+              mbar_expect_tx(&sh->full_w[st], kWStage);
+              if (ph == 2) {  // 64 gate features on MMA rows 0..63, the matching 64 up features on rows 64..127
+                tma_load_3d(dst, tm, &sh->full_w[st], kb * kMBK, ft * 64, l);
+                tma_load_3d(dst + 64 * kMBK * 2, tm, &sh->full_w[st], kb * kMBK, p.F + ft * 64, l);
+              } else {
+                tma_load_3d(dst, tm, &sh->full_w[st], kb * kMBK, ft * kFT, l);
+              }
+              if (++st == NSW) {
+                st = 0;
+                par ^= 1;
+              }
+            }
+          }
+        }
+      }
+      if (!ok) sh->abort = 1;
+    }
+  } else if (warp == 1) {
+    // ================= activation producer: waits for the phase that writes its operand =================
+    if (elect_one()) {
+      int st = 0;
+      uint32_t par = 0;
+      bool ok = true;
+      for (int l = 0; l < p.L && ok; ++l) {
+        for (int ph = 0; ph < 4 && ok; ++ph) {
+          const CUtensorMap* tm = ph == 0 ? &tmX : ph == 1 ? &tmAttn : ph == 2 ? &tmX1 : &tmAct;
+          const int S = p.ph[ph].S, nkb = p.ph[ph].num_kb, n_items = p.ph[ph].n_groups * S;
+          if (ph == 1) {
+            // the attention phase used this ring's memory through the generic proxy: its threads fenced and arrived
+            if (!mbar_wait_s(&sh->xa_bar, (uint32_t)(l & 1), p.status)) {
+              report_status(p.status, kStatusBarrierTimeout);
+              ok = false;
+              break;
+            }
+          }
+          bool waited = (l == 0 && ph == 0);
+          for (int item = cta; item < n_items && ok; item += G) {
+            if (!waited) {
+              if (!wait_counter(p.done, target(l, ph), p.status)) {
+                report_status(p.status, kStatusPeerFlagTimeout);
+                ok = false;
+                break;
+              }
+              fence_proxy_async_all();  // other SMs wrote the operand with ordinary stores; TMA reads it
+              waited = true;
+            }
+            const int ft = item / S, ks = item - ft * S;
+            const int kb0 = (int)((long long)nkb * ks / S), kb1 = (int)((long long)nkb * (ks + 1) / S);
+            for (int kb = kb0; kb < kb1; ++kb) {
+              if (!mbar_wait_s(&sh->empty_x[st], par ^ 1, p.status)) {
+                report_status(p.status, kStatusWaitEmptyTimeout);
+                ok = false;
+                break;
+              }
+              mbar_expect_tx(&sh->full_x[st], Cfg::kXStage);
+              tma_load_2d(xa + st * Cfg::kXStage, tm, &sh->full_x[st], kb * kMBK, 0);
+              if (++st == NSX) {
+                st = 0;
+                par ^= 1;
+              }
+            }
+          }
+        }
+      }
+      if (!ok) sh->abort = 1;
+    }
+  } else if (warp == 2) {
+    // ================= MMA issuer =================
+    if (elect_one()) {
+      int sw = 0, sx = 0, acc = 0;
+      uint32_t pw = 0, px = 0, pa = 0;
+      bool ok = true;
+      for (int l = 0; l < p.L && ok; ++l) {
+        for (int ph = 0; ph < 4 && ok; ++ph) {
+          const int S = p.ph[ph].S, nkb = p.ph[ph].num_kb, n_items = p.ph[ph].n_groups * S;
+          for (int item = cta; item < n_items && ok; item += G) {
+            const int ft = item / S, ks = item - ft * S;
+            const int kb0 = (int)((long long)nkb * ks / S), kb1 = (int)((long long)nkb * (ks + 1) / S);
+            if (!mbar_wait_s(&sh->tmem_empty[acc], pa ^ 1, p.status)) {
+              report_status(p.status, kStatusWaitTmemEmptyTimeout);
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t d_addr = tmem_base + (uint32_t)(acc * BT);
+            for (int kb = kb0; kb < kb1; ++kb) {
+              if (!mbar_wait_s(&sh->full_w[sw], pw, p.status) || !mbar_wait_s(&sh->full_x[sx], px, p.status)) {
+                report_status(p.status, kStatusWaitFullTimeout);
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+              const uint32_t sa = smem_u32(w_ring + sw * kWStage);
+              const uint32_t sb = smem_u32(xa + sx * Cfg::kXStage);
+#pragma unroll
+              for (int k = 0; k < kMBK / 16; ++k)
+                tc_mma_f16(d_addr, umma_smem_desc(sa + k * 32, 16, 1024), umma_smem_desc(sb + k * 32, 16, 1024), kIdesc,
+                           (kb > kb0 || k > 0) ? 1u : 0u);
+              tc_commit(&sh->empty_w[sw]);
+              tc_commit(&sh->empty_x[sx]);
+              if (++sw == NSW) {
+                sw = 0;
+                pw ^= 1;
+              }
+              if (++sx == NSX) {
+                sx = 0;
+                px ^= 1;
+              }
+            }
+            if (!ok) break;
+            tc_commit(&sh->tmem_full[acc]);
+            if (++acc == Cfg::kAcc) {
+              acc = 0;
+              pa ^= 1;
+            }
+          }
+        }
+      }
+      if (!ok) sh->abort = 1;
+    }
+  } else if (warp >= 4) {
+    // ================= compute warps: GEMM reductions + epilogues, attention =================
+    const int cw = warp - 4;             // TMEM lane quarter (warp % 4)
+    const int tid = threadIdx.x - 128;   // 0..127
+    const uint32_t lane_off = static_cast<uint32_t>(cw * 32) << 16;
+    int acc = 0;
+    uint32_t pa = 0;
+    bool ok = true;
+    const int B = p.B;
+
+    DecodeParams dp;
+    dp.q = p.qkv;
+    dp.ldq = p.Q;
+    dp.q_col0 = 0;
+    dp.block_tables = p.block_tables;
+    dp.seq_lens = p.seq_lens;
+    dp.max_blocks = p.max_blocks;
+    dp.Hq = p.Hq;
+    dp.Hkv = p.Hkv;
+    dp.G = p.Hq / p.Hkv;
+    dp.scale_log2 = p.scale_log2;
+    dp.splits = p.splits;
+    dp.out = p.attn;
+    dp.ldo = p.QD;
+    dp.part_o = p.part_o;
+    dp.part_ml = p.part_ml;
+    dp.num_cache_blocks = p.num_cache_blocks;
+    dp.status = p.status;
+    dp.tickets = p.att_tickets;
+
+    for (int l = 0; l < p.L && ok; ++l) {
+      __nv_bfloat16* k_cache = p.cache + (long long)l * p.cache_layer_stride;
+      __nv_bfloat16* v_cache = k_cache + p.cache_v_off;
+      for (int ph = 0; ph < 4 && ok; ++ph) {
+        if (ph == 1) {
+          // ---------------- attention over the paged cache ----------------
+          if (tid == 0) {
+            if (!wait_counter(p.done, (unsigned int)l * p.per_layer + (unsigned int)(p.ph[0].n_groups * p.ph[0].S), p.status)) {
+              report_status(p.status, kStatusPeerFlagTimeout);
+              sh->abort = 1;
+            }
+          }
+          dec_bar_sync();
+          if (sh->abort) {
+            ok = false;
+            break;
+          }
+          dp.k_cache = k_cache;
+          dp.v_cache = v_cache;
+          const int n_att = p.att_groups * p.splits;
+          for (int it = cta; it < n_att; it += G) {
+            const int split = it % p.splits;
+            const int rest = it / p.splits;
+            const int kvh = rest % p.Hkv, b = rest / p.Hkv;
+            const bool fin = paged_decode_attend(dp, split, kvh, b, xa, cw, tid, &sh->s_last);
+            if (fin) {
+              dec_bar_sync();  // every thread's output stores are issued
+              if (tid == 0) {
+                __threadfence();
+                red_release_gpu_add(p.done, 1u);
+              }
+            }
+          }
+          fence_proxy_async_smem();   // the activation ring is handed back to TMA
+          mbar_arrive(&sh->xa_bar);
+        }
+        // ---------------- GEMM items of this phase ----------------
+        const int S = p.ph[ph].S, n_items = p.ph[ph].n_groups * S;
+        for (int item = cta; item < n_items && ok; item += G) {
+          const int grp = item / S, ks = item - grp * S;
+          bool have_acc = true;
+          if (!mbar_wait_s(&sh->tmem_full[acc], pa, p.status)) {
+            report_status(p.status, kStatusWaitTmemFullTimeout);
+            sh->abort = 1;  // read by every compute thread after the barriers below: they all leave together
+            have_acc = false;
+          }
+          tc_fence_after();
+          float* slot = p.partials + (size_t)item * (BT * kFT);
+          if (have_acc) {
+#pragma unroll 1
+            for (int c = 0; c < BT / 32; ++c) {
+              if (c * 32 >= B) break;  // padding rows
+              uint32_t r[32];
+              tmem_ld_32x32(tmem_base + lane_off + (uint32_t)(acc * BT + c * 32), r);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (c * 32 + i < B) __stcg(slot + (size_t)(c * 32 + i) * kFT + cw * 32 + lane, __uint_as_float(r[i]));
+            }
+          }
+          tc_fence_before();
+          __threadfence();
+          dec_bar_sync();
+          if (tid == 0) {
+            mbar_arrive(&sh->tmem_empty[acc]);
+            unsigned int* ctr = p.arrive + ph * kMaxGroups + grp;
+            red_release_gpu_add(ctr, 1u);
+            if (!wait_counter(ctr, (unsigned int)S * (unsigned int)(l + 1), p.status)) {
+              report_status(p.status, kStatusBarrierTimeout);
+              sh->abort = 1;
+            }
+          }
+          if (++acc == Cfg::kAcc) {
+            acc = 0;
+            pa ^= 1;
+          }
+          dec_bar_sync();
+          if (sh->abort) {
+            ok = false;
+            break;
+          }
+          // ---- my share of the rows: reduce over the S partials, epilogue ----
+          const int r0 = (int)((long long)B * ks / S), r1 = (int)((long long)B * (ks + 1) / S);
+          const float* gbase = p.partials + (size_t)(grp * S) * (BT * kFT);
+          for (int b = r0 + cw; b < r1; b += 4) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < S; ++s) {
+              const float4 t = __ldcg(reinterpret_cast<const float4*>(gbase + ((size_t)s * BT + b) * kFT) + lane);
+              v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
+            }
+            if (ph == 0) {
+              const float rs = rsqrtf(sumsq_from_fixed(p.ss[(size_t)(2 * l) * p.ss_stride + b]) * p.inv_h + p.eps);
+              v.x *= rs; v.y *= rs; v.z *= rs; v.w *= rs;
+              if (p.bqkv != nullptr) {
+                const float4 bb = ld_bf16x4(p.bqkv + (long long)l * p.bqkv_stride + grp * kFT + 4 * lane);
+                v.x += bb.x; v.y += bb.y; v.z += bb.z; v.w += bb.w;
+              }
+              const int len = p.seq_lens[b];
+              const int pos = len > 0 ? len - 1 : 0;
+              const bool is_q = grp < p.Hq, is_k = !is_q && grp < p.Hq + p.Hkv;
+              if (is_q || is_k) {
+                const int pp = pos >= p.max_pos ? p.max_pos - 1 : pos;
+                const float4 o = shfl_xor4(v, 16);
+                const int j = (4 * lane) & 63;
+                const float4 cs = *reinterpret_cast<const float4*>(p.cos_t + (size_t)pp * 64 + j);
+                const float4 sn = *reinterpret_cast<const float4*>(p.sin_t + (size_t)pp * 64 + j);
+                if (lane < 16) {
+                  v = make_float4(v.x * cs.x - o.x * sn.x, v.y * cs.y - o.y * sn.y, v.z * cs.z - o.z * sn.z, v.w * cs.w - o.w * sn.w);
+                } else {
+                  v = make_float4(v.x * cs.x + o.x * sn.x, v.y * cs.y + o.y * sn.y, v.z * cs.z + o.z * sn.z, v.w * cs.w + o.w * sn.w);
+                }
+              }
+              st_bf16x4(p.qkv + (size_t)b * p.Q + grp * kFT + 4 * lane, v);
+              if (!is_q && len > 0) {
+                const int blk = p.block_tables[(long long)b * p.max_blocks + pos / kDecBlock];
+                if (blk < 0 || blk >= p.num_cache_blocks) {
+                  report_status(p.status, kStatusBadIndex);
+                } else {
+                  const int h = grp - p.Hq - (is_k ? 0 : p.Hkv);
+                  __nv_bfloat16* row = (is_k ? k_cache : v_cache) +
+                                       (((long long)blk * p.Hkv + h) * kDecBlock + pos % kDecBlock) * kDecD;
+                  st_bf16x4(row + 4 * lane, v);
+                }
+              }
+            } else if (ph == 2) {
+              const float rs = rsqrtf(sumsq_from_fixed(p.ss[(size_t)(2 * l + 1) * p.ss_stride + b]) * p.inv_h + p.eps);
+              const float4 u = shfl_xor4(v, 16);  // lanes < 16 hold gate features, lanes >= 16 the matching up features
+              if (lane < 16) {
+                float4 o;
+                const float g0 = v.x * rs, g1 = v.y * rs, g2 = v.z * rs, g3 = v.w * rs;
+                o.x = g0 / (1.f + __expf(-g0)) * (u.x * rs);
+                o.y = g1 / (1.f + __expf(-g1)) * (u.y * rs);
+                o.z = g2 / (1.f + __expf(-g2)) * (u.z * rs);
+                o.w = g3 / (1.f + __expf(-g3)) * (u.w * rs);
+                st_bf16x4(p.act + (size_t)b * p.F + grp * 64 + 4 * lane, o);
+              }
+            } else {
+              const __nv_bfloat16* res = (ph == 1 ? p.x : p.x1) + (size_t)b * p.H + grp * kFT + 4 * lane;
+              const float4 rr = ld_bf16x4(res);
+              v.x += rr.x; v.y += rr.y; v.z += rr.z; v.w += rr.w;
+              st_bf16x4((ph == 1 ? p.x1 : p.x) + (size_t)b * p.H + grp * kFT + 4 * lane, v);
+              float sq = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+#pragma unroll
+              for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+              if (lane == 0) sumsq_atomic_add(p.ss + (size_t)(2 * l + (ph == 1 ? 1 : 2)) * p.ss_stride + b, sq);
+            }
+          }
+          dec_bar_sync();
+          if (tid == 0) {
+            __threadfence();
+            red_release_gpu_add(p.done, 1u);
+          }
+        }
+      }
+    }
+    if (!ok && tid == 0) sh->abort = 1;
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 3) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// 3-D map over per-layer weight matrices that sit at a constant stride in one flat buffer:
+// (K inner, rows, layer); box = 64 x box_rows x 1, 128-byte swizzle.
+CUtensorMap make_tmap_w3d(const void* base, uint64_t K, uint64_t rows, uint64_t layers, uint64_t layer_stride_elems,
+                          uint32_t box_rows) {
+  if ((reinterpret_cast<uint64_t>(base) & 15) != 0 || (K * 2) % 16 != 0 || (layer_stride_elems * 2) % 16 != 0)
+    throw std::runtime_error("decode_layers: weight tensor map alignment");
+  CUtensorMap m;
+  cuuint64_t dims[3] = {K, rows, layers};
+  cuuint64_t strides[2] = {K * 2, layer_stride_elems * 2};
+  cuuint32_t box[3] = {kMBK, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = get_encode_tiled()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) throw std::runtime_error("decode_layers: cuTensorMapEncodeTiled failed: " + std::to_string((int)r));
+  return m;
+}
+
+template <int BT>
+void launch_mega(const CUtensorMap* tm, const MegaParams& p, cudaStream_t stream) {
+  using Cfg = MegaCfg<BT>;
+  auto kernel = decode_layers_kernel<BT>;
+  static bool configured = false;
+  if (!configured) {
+    check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem), "decode_layers smem attr");
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.grid, 1, 1);
+  cfg.blockDim = dim3(kMegaThreads, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::kSmem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;  // all CTAs resident together: they wait on one another
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  check_cuda(cudaLaunchKernelEx(&cfg, kernel, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], p), "decode_layers launch");
+}
+
+int split_for(int n_groups, int num_kb, int grid) {
+  int S = grid / n_groups;
+  if (S < 1) S = 1;
+  if (S > num_kb) S = num_kb;
+  if (S > 16) S = 16;
+  return S;
+}
+
+}  // namespace
+
+// Bytes of fp32 scratch the kernel needs for `rows` batch rows (partial tiles of the phase with the most work items).
+long long decode_layers_scratch_bytes(int rows, int H, int Q, int QD, int F, int num_sms) {
+  const int BT = rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : 256;
+  const int groups[4] = {Q / kFT, H / kFT, F / 64, H / kFT};
+  const int kbs[4] = {H / kMBK, QD / kMBK, H / kMBK, F / kMBK};
+  long long items = 0;
+  for (int i = 0; i < 4; ++i) {
+    const long long n = (long long)groups[i] * split_for(groups[i], kbs[i], num_sms);
+    if (n > items) items = n;
+  }
+  return items * BT * kFT * 4;
+}
+
+bool decode_layers_supported(int rows, int H, int Q, int QD, int F, int Hq, int Hkv, int head_dim) {
+  return rows >= 1 && rows <= 256 && head_dim == 128 && H % 128 == 0 && Q % 128 == 0 && QD % 64 == 0 && F % 64 == 0 &&
+         Q == (Hq + 2 * Hkv) * 128 && QD == Hq * 128 && Hkv > 0 && Hq % Hkv == 0 && Hq / Hkv <= 8 && Q / 128 <= kMaxGroups &&
+         F / 64 <= kMaxGroups && H / 128 <= kMaxGroups;
+}
+
+void launch_decode_layers(const DecodeLayersArgs& a, cudaStream_t stream) {
+  if (!decode_layers_supported(a.B, a.H, a.Q, a.QD, a.F, a.Hq, a.Hkv, 128)) throw std::runtime_error("decode_layers: shape not served");
+  MegaParams p;
+  p.L = a.L; p.B = a.B; p.H = a.H; p.Q = a.Q; p.QD = a.QD; p.F = a.F; p.Hq = a.Hq; p.Hkv = a.Hkv;
+  p.grid = a.num_sms;
+  const int groups[4] = {a.Q / kFT, a.H / kFT, a.F / 64, a.H / kFT};
+  const int kbs[4] = {a.H / kMBK, a.QD / kMBK, a.H / kMBK, a.F / kMBK};
+  unsigned int per_layer = 0;
+  long long max_items = 0;
+  for (int i = 0; i < 4; ++i) {
+    p.ph[i].n_groups = groups[i];
+    p.ph[i].num_kb = kbs[i];
+    p.ph[i].S = split_for(groups[i], kbs[i], p.grid);
+    per_layer += (unsigned int)(groups[i] * p.ph[i].S);
+    if ((long long)groups[i] * p.ph[i].S > max_items) max_items = (long long)groups[i] * p.ph[i].S;
+  }
+  p.att_groups = a.B * a.Hkv;
+  p.splits = a.splits < 1 ? 1 : a.splits;
+  p.per_layer = per_layer + (unsigned int)p.att_groups;
+  const int BT = a.B <= 32 ? 32 : a.B <= 64 ? 64 : a.B <= 128 ? 128 : 256;
+  if (max_items * BT * kFT * 4 > a.partials_bytes) throw std::runtime_error("decode_layers: scratch buffer too small");
+  p.x = (__nv_bfloat16*)a.x; p.x1 = (__nv_bfloat16*)a.x1; p.qkv = (__nv_bfloat16*)a.qkv; p.attn = (__nv_bfloat16*)a.attn;
+  p.act = (__nv_bfloat16*)a.act;
+  p.bqkv = (const __nv_bfloat16*)a.bqkv; p.bqkv_stride = a.bqkv_stride;
+  p.ss = a.ss; p.ss_stride = a.ss_stride;
+  p.eps = a.eps; p.inv_h = 1.f / (float)a.H;
+  p.cos_t = a.cos_t; p.sin_t = a.sin_t; p.max_pos = a.max_pos;
+  p.block_tables = a.block_tables; p.max_blocks = a.max_blocks; p.seq_lens = a.seq_lens;
+  p.cache = (__nv_bfloat16*)a.cache; p.cache_layer_stride = a.cache_layer_stride; p.cache_v_off = a.cache_v_off;
+  p.num_cache_blocks = a.num_cache_blocks;
+  p.scale_log2 = a.softmax_scale * 1.4426950408889634f;
+  p.part_o = a.part_o; p.part_ml = a.part_ml; p.att_tickets = a.att_tickets;
+  p.partials = a.partials;
+  p.arrive = a.counters;
+  p.done = a.counters + 4 * kMaxGroups;
+  p.status = a.status;
+  // counters start from zero in every launch (stream-ordered, also inside a captured graph)
+  check_cuda(cudaMemsetAsync(a.counters, 0, (4 * kMaxGroups + 4) * sizeof(unsigned int), stream), "decode_layers counters");
+  CUtensorMap tm[8];
+  tm[0] = make_tmap_w3d(a.wqkv, a.H, a.Q, a.L, a.wqkv_stride, kFT);
+  tm[1] = make_tmap_w3d(a.wo, a.QD, a.H, a.L, a.wo_stride, kFT);
+  tm[2] = make_tmap_w3d(a.wgu, a.H, 2 * (uint64_t)a.F, a.L, a.wgu_stride, 64);
+  tm[3] = make_tmap_w3d(a.wd, a.F, a.H, a.L, a.wd_stride, kFT);
+  tm[4] = make_tmap_2d(a.x, a.H, a.rows_alloc, a.H, kMBK, BT);
+  tm[5] = make_tmap_2d(a.attn, a.QD, a.rows_alloc, a.QD, kMBK, BT);
+  tm[6] = make_tmap_2d(a.x1, a.H, a.rows_alloc, a.H, kMBK, BT);
+  tm[7] = make_tmap_2d(a.act, a.F, a.rows_alloc, a.F, kMBK, BT);
+  switch (BT) {
+    case 32: launch_mega<32>(tm, p, stream); break;
+    case 64: launch_mega<64>(tm, p, stream); break;
+    case 128: launch_mega<128>(tm, p, stream); break;
+    default: launch_mega<256>(tm, p, stream); break;
+  }
+}
+
+int decode_layers_counter_words() { return 4 * kMaxGroups + 4; }
+
+}  // namespace agrpo

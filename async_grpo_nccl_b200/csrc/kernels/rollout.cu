@@ -6,6 +6,7 @@
 
 #include "../common/tensormap.h"
 #include "../launchers.h"
+#include "decode_attn.cuh"
 #include "gemm_tcgen05.cuh"
 
 namespace agrpo {
@@ -129,267 +130,13 @@ __global__ void rope_kv_write_decode_kernel(__nv_bfloat16* __restrict__ qkv, lon
   }
 }
 
-// ------------------------------------------------------------------------------------------------
-// Paged decode attention (one query token per sequence), D = 128, block_size = 16, G = Hq/Hkv <= 8.
-// CTA = (split, kv head, sequence), 4 warps; a warp owns whole 16-token blocks: cp.async double
-// buffering into swizzled shared memory, QK^T and PV on mma.sync m16n8k16 with the query heads of the
-// group as the (zero-padded) M rows, online softmax in registers. Warps and splits are merged with
-// the usual (max, sum, O) rule.
-// ------------------------------------------------------------------------------------------------
-constexpr int kDecD = 128;
-constexpr int kDecBlock = 16;
-constexpr int kDecWarps = 4;
-
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(smem_u32(smem)));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(smem_u32(smem)));
-}
-__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                          uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-struct DecodeParams {
-  const __nv_bfloat16* q;   // [B, row pitch ldq], head h at column q_col0 + h*D
-  long long ldq;
-  int q_col0;
-  const __nv_bfloat16* k_cache;
-  const __nv_bfloat16* v_cache;
-  const int* block_tables;  // [B, max_blocks]
-  const int* seq_lens;      // [B] tokens in the cache including the current one
-  int max_blocks;
-  int Hq, Hkv, G;
-  float scale_log2;
-  int splits;
-  __nv_bfloat16* out;       // [B, ldo]
-  long long ldo;
-  float* part_o;            // [B, Hkv, splits, 8, D]
-  float* part_ml;           // [B, Hkv, splits, 8, 2]
-  int num_cache_blocks;
-  int* status;
-  int* tickets;             // [B, Hkv] zero-initialised arrival counters, or nullptr: the last split CTA to finish merges
-};
-
-// Shared-memory tile of one 16-token block: 16 rows x 256 bytes, 16-byte chunk c of row r stored at c ^ (r & 7).
-__device__ __forceinline__ uint8_t* tile_chunk(uint8_t* tile, int row, int chunk) {
-  return tile + row * 256 + ((chunk ^ (row & 7)) << 4);
-}
-
 __global__ void __launch_bounds__(kDecWarps * 32)
 paged_decode_attn_kernel(const DecodeParams p) {
   extern __shared__ __align__(128) uint8_t dsm[];
+  __shared__ int s_last;
   pdl_wait();
   pdl_launch();
-  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int seq_len = p.seq_lens[b];
-  const int n_blocks = (seq_len + kDecBlock - 1) / kDecBlock;
-  const int blk_begin = (int)((long long)n_blocks * split / p.splits);
-  const int blk_end = (int)((long long)n_blocks * (split + 1) / p.splits);
-  // per-warp staging: 2 stages x (K tile 4 KB + V tile 4 KB)
-  uint8_t* wbuf = dsm + warp * (2 * 2 * 4096);
-  const int* table = p.block_tables + (long long)b * p.max_blocks;
-
-  // Q fragments (A operand, rows = query heads of this kv head, zero above G), pre-scaled later in fp32.
-  uint32_t qa[kDecD / 16][2];
-  {
-    const int g = lane >> 2;
-    const __nv_bfloat16* qrow = p.q + (long long)b * p.ldq + p.q_col0 + (long long)(kvh * p.G + g) * kDecD;
-#pragma unroll
-    for (int kk = 0; kk < kDecD / 16; ++kk) {
-      const int c = kk * 16 + (lane & 3) * 2;
-      qa[kk][0] = (g < p.G) ? *reinterpret_cast<const uint32_t*>(qrow + c) : 0u;
-      qa[kk][1] = (g < p.G) ? *reinterpret_cast<const uint32_t*>(qrow + c + 8) : 0u;
-    }
-  }
-  float o[kDecD / 8][2];
-#pragma unroll
-  for (int n = 0; n < kDecD / 8; ++n) o[n][0] = o[n][1] = 0.f;
-  float m = -INFINITY, l = 0.f;
-
-  auto issue_load = [&](int blk_idx, int stage) {
-    int phys = table[blk_idx];
-    if (phys < 0 || phys >= p.num_cache_blocks) {
-      report_status(p.status, kStatusBadIndex);
-      phys = 0;
-    }
-    const __nv_bfloat16* ksrc = p.k_cache + ((long long)phys * p.Hkv + kvh) * kDecBlock * kDecD;
-    const __nv_bfloat16* vsrc = p.v_cache + ((long long)phys * p.Hkv + kvh) * kDecBlock * kDecD;
-    uint8_t* kt = wbuf + stage * 8192;
-    uint8_t* vt = kt + 4096;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int idx = i * 32 + lane;  // 256 chunks of 16 bytes per tile
-      const int row = idx >> 4, chunk = idx & 15;
-      cp_async16(tile_chunk(kt, row, chunk), ksrc + row * kDecD + chunk * 8);
-      cp_async16(tile_chunk(vt, row, chunk), vsrc + row * kDecD + chunk * 8);
-    }
-    cp_async_commit();
-  };
-
-  int my = blk_begin + warp;
-  if (my < blk_end) issue_load(my, 0);
-  int stage = 0;
-  for (; my < blk_end; my += kDecWarps, stage ^= 1) {
-    const int nxt = my + kDecWarps;
-    if (nxt < blk_end) {
-      issue_load(nxt, stage ^ 1);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncwarp();
-    uint8_t* kt = wbuf + stage * 8192;
-    uint8_t* vt = kt + 4096;
-    // S = Q K^T for 16 tokens: two n-tiles of 8 tokens.
-    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int kk = 0; kk < kDecD / 16; ++kk) {
-      uint32_t kb[4];
-      const int row = (lane & 7) + ((lane >> 4) << 3);
-      const int chunk = kk * 2 + ((lane >> 3) & 1);
-      ldmatrix_x4(kb, tile_chunk(kt, row, chunk));
-      mma_16816(s0, qa[kk][0], 0u, qa[kk][1], 0u, kb[0], kb[1]);
-      mma_16816(s1, qa[kk][0], 0u, qa[kk][1], 0u, kb[2], kb[3]);
-    }
-    // scores of head lane/4 for tokens {2i, 2i+1, 8+2i, 9+2i}, i = lane%4
-    const int tok0 = my * kDecBlock + (lane & 3) * 2;
-    float sc[4] = {s0[0] * p.scale_log2, s0[1] * p.scale_log2, s1[0] * p.scale_log2, s1[1] * p.scale_log2};
-    if (tok0 >= seq_len) sc[0] = -INFINITY;
-    if (tok0 + 1 >= seq_len) sc[1] = -INFINITY;
-    if (tok0 + 8 >= seq_len) sc[2] = -INFINITY;
-    if (tok0 + 9 >= seq_len) sc[3] = -INFINITY;
-    float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    const float m_new = fmaxf(m, mx);
-    const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
-    const float base = (m_new == -INFINITY) ? 0.f : m_new;
-    float pr[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) pr[i] = exp2f(sc[i] - base);
-    float ps = pr[0] + pr[1] + pr[2] + pr[3];
-    ps += __shfl_xor_sync(0xffffffffu, ps, 1);
-    ps += __shfl_xor_sync(0xffffffffu, ps, 2);
-    l = l * alpha + ps;
-    m = m_new;
-    const uint32_t pa0 = pack_bf16x2(pr[0], pr[1]);
-    const uint32_t pa2 = pack_bf16x2(pr[2], pr[3]);
-#pragma unroll
-    for (int n = 0; n < kDecD / 8; ++n) {
-      o[n][0] *= alpha;
-      o[n][1] *= alpha;
-    }
-    // O += P V : V^T fragments through transposing ldmatrix, two n-tiles (16 dims) per instruction.
-#pragma unroll
-    for (int n2 = 0; n2 < kDecD / 16; ++n2) {
-      uint32_t vb[4];
-      const int row = (lane & 7) + (((lane >> 3) & 1) << 3);
-      const int chunk = n2 * 2 + (lane >> 4);
-      ldmatrix_x4_trans(vb, tile_chunk(vt, row, chunk));
-      float c0[4] = {o[n2 * 2][0], o[n2 * 2][1], 0.f, 0.f};
-      float c1[4] = {o[n2 * 2 + 1][0], o[n2 * 2 + 1][1], 0.f, 0.f};
-      mma_16816(c0, pa0, 0u, pa2, 0u, vb[0], vb[1]);
-      mma_16816(c1, pa0, 0u, pa2, 0u, vb[2], vb[3]);
-      o[n2 * 2][0] = c0[0];
-      o[n2 * 2][1] = c0[1];
-      o[n2 * 2 + 1][0] = c1[0];
-      o[n2 * 2 + 1][1] = c1[1];
-    }
-    __syncwarp();
-  }
-
-  // Merge the four warps through shared memory (reusing the staging area after everyone is done).
-  __syncthreads();
-  float* mo = reinterpret_cast<float*>(dsm);           // [warps][8][D]
-  float* mml = mo + kDecWarps * 8 * kDecD;             // [warps][8][2]
-  {
-    const int g = lane >> 2;
-#pragma unroll
-    for (int n = 0; n < kDecD / 8; ++n) {
-      const int d = n * 8 + (lane & 3) * 2;
-      mo[(warp * 8 + g) * kDecD + d] = o[n][0];
-      mo[(warp * 8 + g) * kDecD + d + 1] = o[n][1];
-    }
-    if ((lane & 3) == 0) {
-      mml[(warp * 8 + g) * 2] = m;
-      mml[(warp * 8 + g) * 2 + 1] = l;
-    }
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < p.G * kDecD; idx += blockDim.x) {
-    const int g = idx / kDecD, d = idx % kDecD;
-    float M = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < kDecWarps; ++w) M = fmaxf(M, mml[(w * 8 + g) * 2]);
-    float L = 0.f, acc = 0.f;
-#pragma unroll
-    for (int w = 0; w < kDecWarps; ++w) {
-      const float mw = mml[(w * 8 + g) * 2];
-      const float wgt = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-      L += mml[(w * 8 + g) * 2 + 1] * wgt;
-      acc += mo[(w * 8 + g) * kDecD + d] * wgt;
-    }
-    if (p.splits == 1) {
-      p.out[(long long)b * p.ldo + (long long)(kvh * p.G + g) * kDecD + d] = __float2bfloat16(L > 0.f ? acc / L : 0.f);
-    } else {
-      const long long base = (((long long)b * p.Hkv + kvh) * p.splits + split) * 8 + g;
-      p.part_o[base * kDecD + d] = acc;
-      if (d == 0) {
-        p.part_ml[base * 2] = M;
-        p.part_ml[base * 2 + 1] = L;
-      }
-    }
-  }
-  // Split-KV merge without a second kernel: every split CTA of a (sequence, kv head) takes a ticket after its
-  // partials are visible device-wide; the one that draws the last ticket merges all of them and re-arms the counter.
-  if (p.splits > 1 && p.tickets != nullptr) {
-    __shared__ int s_last;
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      int* t = p.tickets + (long long)b * p.Hkv + kvh;
-      const int ticket = atomicAdd(t, 1);
-      s_last = (ticket == p.splits - 1) ? 1 : 0;
-      if (s_last) *t = 0;
-    }
-    __syncthreads();
-    if (s_last) {
-      __threadfence();
-      for (int idx = threadIdx.x; idx < p.G * kDecD; idx += blockDim.x) {
-        const int g = idx / kDecD, d = idx % kDecD;
-        const long long base0 = (((long long)b * p.Hkv + kvh) * p.splits) * 8 + g;
-        float M = -INFINITY;
-        for (int s = 0; s < p.splits; ++s) M = fmaxf(M, __ldcg(p.part_ml + (base0 + (long long)s * 8) * 2));
-        float L = 0.f, acc = 0.f;
-        for (int s = 0; s < p.splits; ++s) {
-          const long long bs = base0 + (long long)s * 8;
-          const float ms = __ldcg(p.part_ml + bs * 2);
-          const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
-          L += __ldcg(p.part_ml + bs * 2 + 1) * w;
-          acc += __ldcg(p.part_o + bs * kDecD + d) * w;
-        }
-        p.out[(long long)b * p.ldo + (long long)(kvh * p.G + g) * kDecD + d] = __float2bfloat16(L > 0.f ? acc / L : 0.f);
-      }
-    }
-  }
+  paged_decode_attend(p, blockIdx.x, blockIdx.y, blockIdx.z, dsm, threadIdx.x >> 5, threadIdx.x, &s_last);
 }
 
 __global__ void paged_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int splits,

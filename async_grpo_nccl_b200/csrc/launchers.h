@@ -250,4 +250,38 @@ void launch_adamw(float* p, float* m, float* v, float* g, void* p16, long long n
                   cudaStream_t s);
 void launch_cast_f32_bf16(const float* in, void* out, long long n, cudaStream_t s);
 
+// All decoder layers of one decode step in one persistent cooperative launch (csrc/kernels/decode_mega.cu).
+// Per-layer weights sit at constant element strides in flat bf16 buffers; wqkv and wgu are the copies with the RMSNorm
+// weight folded in. Activation buffers have rows_alloc >= the row tile (32 / 64 / 128 / 256) that covers B rows.
+struct DecodeLayersArgs {
+  int L, B, rows_alloc, H, Q, QD, F, Hq, Hkv, num_sms, splits;
+  const void *wqkv, *wo, *wgu, *wd;
+  long long wqkv_stride, wo_stride, wgu_stride, wd_stride;
+  const void* bqkv;  // nullptr = no bias
+  long long bqkv_stride;
+  void *x, *x1, *qkv, *attn, *act;
+  long long* ss;     // [2 L + 1, ss_stride] row sums of squares, fixed point; entry 0 filled, the rest zero on entry
+  int ss_stride;
+  float eps;
+  const float *cos_t, *sin_t;
+  int max_pos;
+  const int* block_tables;
+  int max_blocks;
+  const int* seq_lens;
+  void* cache;       // [L, 2, num_cache_blocks, Hkv, 16, 128]
+  long long cache_layer_stride, cache_v_off;
+  int num_cache_blocks;
+  float softmax_scale;
+  float *part_o, *part_ml;
+  int* att_tickets;
+  float* partials;
+  long long partials_bytes;
+  unsigned int* counters;  // decode_layers_counter_words() words
+  int* status;
+};
+bool decode_layers_supported(int rows, int H, int Q, int QD, int F, int Hq, int Hkv, int head_dim);
+long long decode_layers_scratch_bytes(int rows, int H, int Q, int QD, int F, int num_sms);
+int decode_layers_counter_words();
+void launch_decode_layers(const DecodeLayersArgs& a, cudaStream_t stream);
+
 }  // namespace agrpo
