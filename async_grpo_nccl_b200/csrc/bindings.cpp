@@ -2,6 +2,7 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
+#include <cstdlib>
 
 #include <pybind11/numpy.h>
 #include <pybind11/stl.h>
@@ -447,7 +448,7 @@ void decode_layers(int64_t L, int64_t B, const Tensor& wqkv0, int64_t wqkv_strid
                    int64_t bqkv_stride, Tensor& x, Tensor& x1, Tensor& qkv, Tensor& attn, Tensor& act, Tensor& ss, double eps,
                    const Tensor& cos_t, const Tensor& sin_t, const Tensor& block_tables, const Tensor& seq_lens, Tensor& cache,
                    int64_t Hq, int64_t Hkv, double softmax_scale, int64_t splits, Tensor& part_o, Tensor& part_ml, Tensor& tickets,
-                   Tensor& partials, Tensor& counters, const OptTensor& status) {
+                   Tensor& partials, Tensor& counters, const OptTensor& status, const OptTensor& trace, int64_t trace_layer) {
   check_bf16(wqkv0, "wqkv"); check_bf16(wo0, "wo"); check_bf16(wgu0, "wgu"); check_bf16(wd0, "wd");
   check_bf16(x, "x"); check_bf16(x1, "x1"); check_bf16(qkv, "qkv"); check_bf16(attn, "attn"); check_bf16(act, "act");
   check_i64(ss, "ss"); check_f32(cos_t, "cos"); check_f32(sin_t, "sin"); check_i32(block_tables, "block_tables");
@@ -494,6 +495,17 @@ void decode_layers(int64_t L, int64_t B, const Tensor& wqkv0, int64_t wqkv_strid
   a.partials = partials.data_ptr<float>(); a.partials_bytes = partials.numel() * 4;
   a.counters = reinterpret_cast<unsigned int*>(counters.data_ptr<int>());
   a.status = opt_ptr<int>(status);
+  {
+    static const int pf = [] { const char* e = std::getenv("AGRPO_MEGA_PREFETCH"); return e ? std::atoi(e) : 0; }();
+    a.prefetch_tiles = pf;
+  }
+  if (trace.has_value() && trace->defined()) {
+    check_i64(*trace, "trace");
+    TORCH_CHECK(trace->numel() >= 32 && trace->is_contiguous(), "decode_layers: trace [32]");
+    a.trace = reinterpret_cast<long long*>(trace->data_ptr<int64_t>());
+    a.trace_layer = (int)trace_layer;
+    a.trace_words = trace->numel();
+  }
   const c10::cuda::CUDAGuard guard(x.device());
   agrpo::launch_decode_layers(a, cur_stream());
 }
@@ -852,7 +864,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_skinny_splits", &gemm_skinny_splits);
   m.def("gemm_decode_rope", &gemm_decode_rope, NOGIL);
   m.def("decode_step_inputs", &decode_step_inputs, NOGIL);
-  m.def("decode_layers", &decode_layers, NOGIL);
+  m.def("decode_layers", &decode_layers, py::arg("L"), py::arg("B"), py::arg("wqkv0"), py::arg("wqkv_stride"), py::arg("wo0"),
+        py::arg("wo_stride"), py::arg("wgu0"), py::arg("wgu_stride"), py::arg("wd0"), py::arg("wd_stride"), py::arg("bqkv0"),
+        py::arg("bqkv_stride"), py::arg("x"), py::arg("x1"), py::arg("qkv"), py::arg("attn"), py::arg("act"), py::arg("ss"),
+        py::arg("eps"), py::arg("cos_t"), py::arg("sin_t"), py::arg("block_tables"), py::arg("seq_lens"), py::arg("cache"),
+        py::arg("Hq"), py::arg("Hkv"), py::arg("softmax_scale"), py::arg("splits"), py::arg("part_o"), py::arg("part_ml"),
+        py::arg("tickets"), py::arg("partials"), py::arg("counters"), py::arg("status") = py::none(),
+        py::arg("trace") = py::none(), py::arg("trace_layer") = 0, NOGIL);
   m.def("decode_layers_supported", &decode_layers_supported);
   m.def("decode_layers_scratch_bytes", &decode_layers_scratch_bytes);
   m.def("decode_layers_counter_words", &decode_layers_counter_words);

@@ -257,20 +257,43 @@ __device__ __forceinline__ bool paged_decode_attend(const DecodeParams& p, int s
     if (*s_last) {
       final_writer = true;
       __threadfence();
-      for (int idx = tid; idx < p.G * kDecD; idx += kDecWarps * 32) {
-        const int g = idx / kDecD, d = idx % kDecD;
+      // four output dims per thread (16-byte loads of the partial outputs), eight splits at a time with all their loads
+      // issued before the first use: they are L2 round trips, and the merging CTA is on the step's critical path
+      for (int idx = tid; idx < p.G * (kDecD / 4); idx += kDecWarps * 32) {
+        const int g = idx / (kDecD / 4), d = (idx % (kDecD / 4)) * 4;
         const long long base0 = (((long long)b * p.Hkv + kvh) * p.splits) * 8 + g;
-        float M = -INFINITY;
-        for (int s = 0; s < p.splits; ++s) M = fmaxf(M, __ldcg(p.part_ml + (base0 + (long long)s * 8) * 2));
-        float L = 0.f, acc = 0.f;
-        for (int s = 0; s < p.splits; ++s) {
-          const long long bs = base0 + (long long)s * 8;
-          const float ms = __ldcg(p.part_ml + bs * 2);
-          const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
-          L += __ldcg(p.part_ml + bs * 2 + 1) * w;
-          acc += __ldcg(p.part_o + bs * kDecD + d) * w;
+        float M = -INFINITY, L = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = 0; s0 < p.splits; s0 += 8) {
+          float ms[8], ls[8];
+          float4 os[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const bool on = s0 + j < p.splits;
+            const long long bs = base0 + (long long)(on ? s0 + j : s0) * 8;
+            const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml + bs * 2));
+            ms[j] = on ? ml.x : -INFINITY;
+            ls[j] = on ? ml.y : 0.f;
+            os[j] = __ldcg(reinterpret_cast<const float4*>(p.part_o + bs * kDecD + d));
+          }
+          float Mn = M;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) Mn = fmaxf(Mn, ms[j]);
+          const float keep = (M == -INFINITY) ? 0.f : exp2f(M - Mn);
+          L *= keep;
+          acc.x *= keep; acc.y *= keep; acc.z *= keep; acc.w *= keep;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float w = (ms[j] == -INFINITY) ? 0.f : exp2f(ms[j] - Mn);
+            L += ls[j] * w;
+            acc.x += os[j].x * w; acc.y += os[j].y * w; acc.z += os[j].z * w; acc.w += os[j].w * w;
+          }
+          M = Mn;
         }
-        p.out[(long long)b * p.ldo + (long long)(kvh * p.G + g) * kDecD + d] = __float2bfloat16(L > 0.f ? acc / L : 0.f);
+        uint2 o;  // same expression as the stand-alone combine kernel: both paths give the same bits
+        o.x = pack_bf16x2(L > 0.f ? acc.x / L : 0.f, L > 0.f ? acc.y / L : 0.f);
+        o.y = pack_bf16x2(L > 0.f ? acc.z / L : 0.f, L > 0.f ? acc.w / L : 0.f);
+        *reinterpret_cast<uint2*>(p.out + (long long)b * p.ldo + (long long)(kvh * p.G + g) * kDecD + d) = o;
       }
     }
   }

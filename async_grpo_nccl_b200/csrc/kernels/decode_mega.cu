@@ -73,7 +73,27 @@ struct MegaParams {
   unsigned int* arrive;  // [4][kMaxGroups] monotonic arrival counters
   unsigned int* done;
   int* status;
+  long long* trace;  // optional: clock64 stamps of CTA 0 in layer trace_layer (32 slots), nullptr = off
+  int trace_layer;
+  int prefetch_tiles;  // weight tiles (16 KB) per CTA requested into L2 ahead of the shared-memory ring (0 = off)
+  int trace_all;     // also record 4 global-timer stamps per CTA (trace must hold 32 + 4 * grid words)
 };
+
+__device__ __forceinline__ long long global_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// per-CTA stamps (global nanosecond timer) behind the 32 slots of CTA 0: trace[32 + 4 * cta + k]
+#define MEGA_STAMP_ALL(k)                                                                       \
+  do {                                                                                          \
+    if (p.trace != nullptr && p.trace_all && l == p.trace_layer) p.trace[32 + 4 * cta + (k)] = global_ns(); \
+  } while (0)
+
+#define MEGA_STAMP(slot)                                                                        \
+  do {                                                                                          \
+    if (p.trace != nullptr && cta == 0 && l == p.trace_layer) p.trace[slot] = clock64();        \
+  } while (0)
 
 __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
   unsigned int v;
@@ -204,38 +224,76 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmWqkv, const __grid_co
 
   if (warp == 0) {
     // ================= weight producer: never waits for another CTA =================
+    // Two cursors walk the same sequence of weight tiles (layer, phase, item, K block): `ld` issues the TMA loads into
+    // the shared-memory ring, `pf` runs prefetch_tiles ahead of it and only asks for the tiles to be brought into L2.
+    // The ring alone covers a few microseconds of streaming; the L2 window keeps HBM busy through the attention phase
+    // and the hand-offs between phases, when the ring is full and nobody consumes it.
     if (elect_one()) {
+      struct Cur {
+        int l, ph, item, kb, kb1, ft;
+      };
+      auto seek = [&](Cur& c) -> bool {  // first K block of the item at (l, ph, item), or of the next one that exists
+        while (c.l < p.L) {
+          const int S = p.ph[c.ph].S, nkb = p.ph[c.ph].num_kb;
+          if (c.item < p.ph[c.ph].n_groups * S) {
+            c.ft = c.item / S;
+            const int ks = c.item - c.ft * S;
+            c.kb = (int)((long long)nkb * ks / S);
+            c.kb1 = (int)((long long)nkb * (ks + 1) / S);
+            if (c.kb < c.kb1) return true;
+            c.item += G;
+            continue;
+          }
+          c.item = cta;
+          if (++c.ph == 4) {
+            c.ph = 0;
+            ++c.l;
+          }
+        }
+        return false;
+      };
+      auto step = [&](Cur& c) -> bool {
+        if (++c.kb < c.kb1) return true;
+        c.item += G;
+        return seek(c);
+      };
+      auto tmap = [&](int ph) { return ph == 0 ? &tmWqkv : ph == 1 ? &tmWo : ph == 2 ? &tmWgu : &tmWd; };
+      Cur ld{0, 0, cta, 0, 0, 0}, pf{0, 0, cta, 0, 0, 0};
+      bool ld_on = seek(ld), pf_on = seek(pf);
+      int ahead = 0;
       int st = 0;
       uint32_t par = 0;
       bool ok = true;
-      for (int l = 0; l < p.L && ok; ++l) {
-        for (int ph = 0; ph < 4 && ok; ++ph) {
-          const CUtensorMap* tm = ph == 0 ? &tmWqkv : ph == 1 ? &tmWo : ph == 2 ? &tmWgu : &tmWd;
-          const int S = p.ph[ph].S, nkb = p.ph[ph].num_kb, n_items = p.ph[ph].n_groups * S;
-          for (int item = cta; item < n_items && ok; item += G) {
-            const int ft = item / S, ks = item - ft * S;
-            const int kb0 = (int)((long long)nkb * ks / S), kb1 = (int)((long long)nkb * (ks + 1) / S);
-            for (int kb = kb0; kb < kb1; ++kb) {
-              if (!mbar_wait_s(&sh->empty_w[st], par ^ 1, p.status)) {
-                report_status(p.status, kStatusWaitEmptyTimeout);
-                ok = false;
-                break;
-              }
-              uint8_t* dst = w_ring + st * kWStage;
-              mbar_expect_tx(&sh->full_w[st], kWStage);
-              if (ph == 2) {  // 64 gate features on MMA rows 0..63, the matching 64 up features on rows 64..127
-                tma_load_3d(dst, tm, &sh->full_w[st], kb * kMBK, ft * 64, l);
-                tma_load_3d(dst + 64 * kMBK * 2, tm, &sh->full_w[st], kb * kMBK, p.F + ft * 64, l);
-              } else {
-                tma_load_3d(dst, tm, &sh->full_w[st], kb * kMBK, ft * kFT, l);
-              }
-              if (++st == NSW) {
-                st = 0;
-                par ^= 1;
-              }
-            }
+      while (ld_on) {
+        while (pf_on && ahead < p.prefetch_tiles) {
+          if (pf.ph == 2) {
+            tma_prefetch_l2_3d(tmap(2), pf.kb * kMBK, pf.ft * 64, pf.l);
+            tma_prefetch_l2_3d(tmap(2), pf.kb * kMBK, p.F + pf.ft * 64, pf.l);
+          } else {
+            tma_prefetch_l2_3d(tmap(pf.ph), pf.kb * kMBK, pf.ft * kFT, pf.l);
           }
+          pf_on = step(pf);
+          ++ahead;
         }
+        if (!mbar_wait_s(&sh->empty_w[st], par ^ 1, p.status)) {
+          report_status(p.status, kStatusWaitEmptyTimeout);
+          ok = false;
+          break;
+        }
+        uint8_t* dst = w_ring + st * kWStage;
+        mbar_expect_tx(&sh->full_w[st], kWStage);
+        if (ld.ph == 2) {  // 64 gate features on MMA rows 0..63, the matching 64 up features on rows 64..127
+          tma_load_3d(dst, tmap(2), &sh->full_w[st], ld.kb * kMBK, ld.ft * 64, ld.l);
+          tma_load_3d(dst + 64 * kMBK * 2, tmap(2), &sh->full_w[st], ld.kb * kMBK, p.F + ld.ft * 64, ld.l);
+        } else {
+          tma_load_3d(dst, tmap(ld.ph), &sh->full_w[st], ld.kb * kMBK, ld.ft * kFT, ld.l);
+        }
+        if (++st == NSW) {
+          st = 0;
+          par ^= 1;
+        }
+        ld_on = step(ld);
+        --ahead;
       }
       if (!ok) sh->abort = 1;
     }
@@ -314,6 +372,9 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmWqkv, const __grid_co
                 break;
               }
               tc_fence_after();
+              if (kb == kb0) MEGA_STAMP(ph * 6 + 0);
+              if (kb == kb0 && ph == 1) MEGA_STAMP_ALL(2);
+              if (kb == kb0 && ph == 0) MEGA_STAMP_ALL(3);
               const uint32_t sa = smem_u32(w_ring + sw * kWStage);
               const uint32_t sb = smem_u32(xa + sx * Cfg::kXStage);
 #pragma unroll
@@ -333,6 +394,7 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmWqkv, const __grid_co
             }
             if (!ok) break;
             tc_commit(&sh->tmem_full[acc]);
+            MEGA_STAMP(ph * 6 + 1);
             if (++acc == Cfg::kAcc) {
               acc = 0;
               pa ^= 1;
@@ -375,6 +437,7 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmWqkv, const __grid_co
     for (int l = 0; l < p.L && ok; ++l) {
       __nv_bfloat16* k_cache = p.cache + (long long)l * p.cache_layer_stride;
       __nv_bfloat16* v_cache = k_cache + p.cache_v_off;
+      if (tid == 0) MEGA_STAMP(26);
       for (int ph = 0; ph < 4 && ok; ++ph) {
         if (ph == 1) {
           // ---------------- attention over the paged cache ----------------
@@ -389,6 +452,8 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmWqkv, const __grid_co
             ok = false;
             break;
           }
+          if (tid == 0) MEGA_STAMP(24);
+          if (tid == 0) MEGA_STAMP_ALL(0);
           dp.k_cache = k_cache;
           dp.v_cache = v_cache;
           const int n_att = p.att_groups * p.splits;
@@ -407,6 +472,8 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmWqkv, const __grid_co
           }
           fence_proxy_async_smem();   // the activation ring is handed back to TMA
           mbar_arrive(&sh->xa_bar);
+          if (tid == 0) MEGA_STAMP(25);
+          if (tid == 0) MEGA_STAMP_ALL(1);
         }
         // ---------------- GEMM items of this phase ----------------
         const int S = p.ph[ph].S, n_items = p.ph[ph].n_groups * S;
@@ -419,6 +486,7 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmWqkv, const __grid_co
             have_acc = false;
           }
           tc_fence_after();
+          if (tid == 0) MEGA_STAMP(ph * 6 + 2);
           float* slot = p.partials + (size_t)item * (BT * kFT);
           if (have_acc) {
 #pragma unroll 1
@@ -433,12 +501,41 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmWqkv, const __grid_co
             }
           }
           tc_fence_before();
-          __threadfence();
+          // Row statistics, lengths and the residual of my first rows do not depend on the other splits: request them now,
+          // they arrive while this CTA waits for the tile's other splits.
+          const int r0 = (int)((long long)B * ks / S), r1 = (int)((long long)B * (ks + 1) / S);
+          constexpr int RU = 4;
+          const int b_first = r0 + cw * RU;
+          sumsq_t m_ss[RU];
+          int m_len[RU];
+          float4 m_rr[RU];
+          auto load_meta = [&](int b0) {
+#pragma unroll
+            for (int j = 0; j < RU; ++j) {
+              const int b = (b0 + j < r1) ? b0 + j : r0;
+              m_ss[j] = 0;
+              m_len[j] = 0;
+              m_rr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (b0 < r1) {
+                if (ph == 0) {
+                  m_ss[j] = p.ss[(size_t)(2 * l) * p.ss_stride + b];
+                  m_len[j] = p.seq_lens[b];
+                } else if (ph == 2) {
+                  m_ss[j] = p.ss[(size_t)(2 * l + 1) * p.ss_stride + b];
+                } else {
+                  m_rr[j] = ld_bf16x4((ph == 1 ? p.x : p.x1) + (size_t)b * p.H + grp * kFT + 4 * lane);
+                }
+              }
+            }
+          };
+          load_meta(b_first);
+          // the CTA barrier orders every thread's partial stores before the release below (cumulative at GPU scope)
           dec_bar_sync();
           if (tid == 0) {
             mbar_arrive(&sh->tmem_empty[acc]);
             unsigned int* ctr = p.arrive + ph * kMaxGroups + grp;
             red_release_gpu_add(ctr, 1u);
+            MEGA_STAMP(ph * 6 + 3);
             if (!wait_counter(ctr, (unsigned int)S * (unsigned int)(l + 1), p.status)) {
               report_status(p.status, kStatusBarrierTimeout);
               sh->abort = 1;
@@ -453,76 +550,113 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmWqkv, const __grid_co
             ok = false;
             break;
           }
+          if (tid == 0) MEGA_STAMP(ph * 6 + 4);
           // ---- my share of the rows: reduce over the S partials, epilogue ----
-          const int r0 = (int)((long long)B * ks / S), r1 = (int)((long long)B * (ks + 1) / S);
           const float* gbase = p.partials + (size_t)(grp * S) * (BT * kFT);
-          for (int b = r0 + cw; b < r1; b += 4) {
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int s = 0; s < S; ++s) {
-              const float4 t = __ldcg(reinterpret_cast<const float4*>(gbase + ((size_t)s * BT + b) * kFT) + lane);
-              v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
+          // Four rows per warp pass. Everything a row needs from memory (its S partials, statistics, residual, rotary
+          // table entries, cache slot) is requested before the first use, so that the L2 round trips of the four rows
+          // and of the splits overlap instead of adding up.
+          for (int b0 = b_first; b0 < r1; b0 += 4 * RU) {
+            if (b0 != b_first) load_meta(b0);
+            float4 v[RU];
+            bool on[RU];
+#pragma unroll
+            for (int j = 0; j < RU; ++j) {
+              on[j] = b0 + j < r1;
+              v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            for (int s = 0; s < S; s += 2) {
+              float4 t0[RU], t1[RU];
+              const bool two = s + 1 < S;
+#pragma unroll
+              for (int j = 0; j < RU; ++j) {
+                const float4* src = reinterpret_cast<const float4*>(gbase + ((size_t)s * BT + (on[j] ? b0 + j : r0)) * kFT) + lane;
+                t0[j] = __ldcg(src);
+                t1[j] = two ? __ldcg(src + (size_t)BT * kFT / 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+              }
+#pragma unroll
+              for (int j = 0; j < RU; ++j) {  // fixed order: split s, then split s + 1
+                v[j].x += t0[j].x; v[j].y += t0[j].y; v[j].z += t0[j].z; v[j].w += t0[j].w;
+                v[j].x += t1[j].x; v[j].y += t1[j].y; v[j].z += t1[j].z; v[j].w += t1[j].w;
+              }
             }
             if (ph == 0) {
-              const float rs = rsqrtf(sumsq_from_fixed(p.ss[(size_t)(2 * l) * p.ss_stride + b]) * p.inv_h + p.eps);
-              v.x *= rs; v.y *= rs; v.z *= rs; v.w *= rs;
-              if (p.bqkv != nullptr) {
-                const float4 bb = ld_bf16x4(p.bqkv + (long long)l * p.bqkv_stride + grp * kFT + 4 * lane);
-                v.x += bb.x; v.y += bb.y; v.z += bb.z; v.w += bb.w;
-              }
-              const int len = p.seq_lens[b];
-              const int pos = len > 0 ? len - 1 : 0;
               const bool is_q = grp < p.Hq, is_k = !is_q && grp < p.Hq + p.Hkv;
-              if (is_q || is_k) {
+              int len[RU], blk[RU];
+              float4 cs[RU], sn[RU];
+              float4 bb = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (p.bqkv != nullptr) bb = ld_bf16x4(p.bqkv + (long long)l * p.bqkv_stride + grp * kFT + 4 * lane);
+              const int jr = (4 * lane) & 63;
+#pragma unroll
+              for (int j = 0; j < RU; ++j) len[j] = m_len[j];
+#pragma unroll
+              for (int j = 0; j < RU; ++j) {
+                const int b = on[j] ? b0 + j : r0;
+                const int pos = len[j] > 0 ? len[j] - 1 : 0;
                 const int pp = pos >= p.max_pos ? p.max_pos - 1 : pos;
-                const float4 o = shfl_xor4(v, 16);
-                const int j = (4 * lane) & 63;
-                const float4 cs = *reinterpret_cast<const float4*>(p.cos_t + (size_t)pp * 64 + j);
-                const float4 sn = *reinterpret_cast<const float4*>(p.sin_t + (size_t)pp * 64 + j);
-                if (lane < 16) {
-                  v = make_float4(v.x * cs.x - o.x * sn.x, v.y * cs.y - o.y * sn.y, v.z * cs.z - o.z * sn.z, v.w * cs.w - o.w * sn.w);
-                } else {
-                  v = make_float4(v.x * cs.x + o.x * sn.x, v.y * cs.y + o.y * sn.y, v.z * cs.z + o.z * sn.z, v.w * cs.w + o.w * sn.w);
-                }
+                cs[j] = *reinterpret_cast<const float4*>(p.cos_t + (size_t)pp * 64 + jr);
+                sn[j] = *reinterpret_cast<const float4*>(p.sin_t + (size_t)pp * 64 + jr);
+                blk[j] = (!is_q && len[j] > 0) ? p.block_tables[(long long)b * p.max_blocks + pos / kDecBlock] : 0;
               }
-              st_bf16x4(p.qkv + (size_t)b * p.Q + grp * kFT + 4 * lane, v);
-              if (!is_q && len > 0) {
-                const int blk = p.block_tables[(long long)b * p.max_blocks + pos / kDecBlock];
-                if (blk < 0 || blk >= p.num_cache_blocks) {
-                  report_status(p.status, kStatusBadIndex);
-                } else {
-                  const int h = grp - p.Hq - (is_k ? 0 : p.Hkv);
-                  __nv_bfloat16* row = (is_k ? k_cache : v_cache) +
-                                       (((long long)blk * p.Hkv + h) * kDecBlock + pos % kDecBlock) * kDecD;
-                  st_bf16x4(row + 4 * lane, v);
+#pragma unroll
+              for (int j = 0; j < RU; ++j) {
+                if (!on[j]) continue;  // warp-uniform
+                const int b = b0 + j;
+                const float rs = rsqrtf(sumsq_from_fixed(m_ss[j]) * p.inv_h + p.eps);
+                float4 w = make_float4(v[j].x * rs + bb.x, v[j].y * rs + bb.y, v[j].z * rs + bb.z, v[j].w * rs + bb.w);
+                if (is_q || is_k) {
+                  const float4 o = shfl_xor4(w, 16);
+                  const float sg = lane < 16 ? -1.f : 1.f;  // lanes < 16 hold x1 (x1 c - x2 s), the others x2 (x2 c + x1 s)
+                  w = make_float4(w.x * cs[j].x + sg * o.x * sn[j].x, w.y * cs[j].y + sg * o.y * sn[j].y,
+                                  w.z * cs[j].z + sg * o.z * sn[j].z, w.w * cs[j].w + sg * o.w * sn[j].w);
+                }
+                st_bf16x4(p.qkv + (size_t)b * p.Q + grp * kFT + 4 * lane, w);
+                if (!is_q && len[j] > 0) {
+                  if (blk[j] < 0 || blk[j] >= p.num_cache_blocks) {
+                    report_status(p.status, kStatusBadIndex);
+                  } else {
+                    const int pos = len[j] - 1;
+                    const int h = grp - p.Hq - (is_k ? 0 : p.Hkv);
+                    __nv_bfloat16* row = (is_k ? k_cache : v_cache) +
+                                         (((long long)blk[j] * p.Hkv + h) * kDecBlock + pos % kDecBlock) * kDecD;
+                    st_bf16x4(row + 4 * lane, w);
+                  }
                 }
               }
             } else if (ph == 2) {
-              const float rs = rsqrtf(sumsq_from_fixed(p.ss[(size_t)(2 * l + 1) * p.ss_stride + b]) * p.inv_h + p.eps);
-              const float4 u = shfl_xor4(v, 16);  // lanes < 16 hold gate features, lanes >= 16 the matching up features
-              if (lane < 16) {
-                float4 o;
-                const float g0 = v.x * rs, g1 = v.y * rs, g2 = v.z * rs, g3 = v.w * rs;
-                o.x = g0 / (1.f + __expf(-g0)) * (u.x * rs);
-                o.y = g1 / (1.f + __expf(-g1)) * (u.y * rs);
-                o.z = g2 / (1.f + __expf(-g2)) * (u.z * rs);
-                o.w = g3 / (1.f + __expf(-g3)) * (u.w * rs);
-                st_bf16x4(p.act + (size_t)b * p.F + grp * 64 + 4 * lane, o);
+#pragma unroll
+              for (int j = 0; j < RU; ++j) {
+                if (!on[j]) continue;
+                const float rs = rsqrtf(sumsq_from_fixed(m_ss[j]) * p.inv_h + p.eps);
+                const float4 u = shfl_xor4(v[j], 16);  // lanes < 16 hold gate features, lanes >= 16 the matching up features
+                if (lane < 16) {
+                  float4 o;
+                  const float g0 = v[j].x * rs, g1 = v[j].y * rs, g2 = v[j].z * rs, g3 = v[j].w * rs;
+                  o.x = g0 / (1.f + __expf(-g0)) * (u.x * rs);
+                  o.y = g1 / (1.f + __expf(-g1)) * (u.y * rs);
+                  o.z = g2 / (1.f + __expf(-g2)) * (u.z * rs);
+                  o.w = g3 / (1.f + __expf(-g3)) * (u.w * rs);
+                  st_bf16x4(p.act + (size_t)(b0 + j) * p.F + grp * 64 + 4 * lane, o);
+                }
               }
             } else {
-              const __nv_bfloat16* res = (ph == 1 ? p.x : p.x1) + (size_t)b * p.H + grp * kFT + 4 * lane;
-              const float4 rr = ld_bf16x4(res);
-              v.x += rr.x; v.y += rr.y; v.z += rr.z; v.w += rr.w;
-              st_bf16x4((ph == 1 ? p.x1 : p.x) + (size_t)b * p.H + grp * kFT + 4 * lane, v);
-              float sq = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+              __nv_bfloat16* obase = ph == 1 ? p.x1 : p.x;
 #pragma unroll
-              for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-              if (lane == 0) sumsq_atomic_add(p.ss + (size_t)(2 * l + (ph == 1 ? 1 : 2)) * p.ss_stride + b, sq);
+              for (int j = 0; j < RU; ++j) {
+                if (!on[j]) continue;
+                const float4 w = make_float4(v[j].x + m_rr[j].x, v[j].y + m_rr[j].y, v[j].z + m_rr[j].z, v[j].w + m_rr[j].w);
+                st_bf16x4(obase + (size_t)(b0 + j) * p.H + grp * kFT + 4 * lane, w);
+                float sq = w.x * w.x + w.y * w.y + w.z * w.z + w.w * w.w;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                if (lane == 0) sumsq_atomic_add(p.ss + (size_t)(2 * l + (ph == 1 ? 1 : 2)) * p.ss_stride + b0 + j, sq);
+              }
             }
           }
           dec_bar_sync();
           if (tid == 0) {
-            __threadfence();
             red_release_gpu_add(p.done, 1u);
+            MEGA_STAMP(ph * 6 + 5);
           }
         }
       }
@@ -643,6 +777,10 @@ void launch_decode_layers(const DecodeLayersArgs& a, cudaStream_t stream) {
   p.arrive = a.counters;
   p.done = a.counters + 4 * kMaxGroups;
   p.status = a.status;
+  p.trace = a.trace;
+  p.trace_layer = a.trace_layer;
+  p.prefetch_tiles = a.prefetch_tiles;
+  p.trace_all = a.trace_words >= 32 + 4 * a.num_sms ? 1 : 0;
   // counters start from zero in every launch (stream-ordered, also inside a captured graph)
   check_cuda(cudaMemsetAsync(a.counters, 0, (4 * kMaxGroups + 4) * sizeof(unsigned int), stream), "decode_layers counters");
   CUtensorMap tm[8];

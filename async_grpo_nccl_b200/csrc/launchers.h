@@ -278,6 +278,10 @@ struct DecodeLayersArgs {
   long long partials_bytes;
   unsigned int* counters;  // decode_layers_counter_words() words
   int* status;
+  long long* trace = nullptr;  // optional phase tracer: 32 clock64 stamps of CTA 0 in layer trace_layer
+  int trace_layer = 0;
+  int prefetch_tiles = 0;      // weight tiles per CTA requested into L2 ahead of the shared-memory ring
+  long long trace_words = 0;   // >= 32 + 4 * num_sms: four global-timer stamps per CTA are recorded as well
 };
 bool decode_layers_supported(int rows, int H, int Q, int QD, int F, int Hq, int Hkv, int head_dim);
 long long decode_layers_scratch_bytes(int rows, int H, int Q, int QD, int F, int num_sms);

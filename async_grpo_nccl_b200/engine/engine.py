@@ -107,14 +107,16 @@ class RolloutEngine:
         self.row_ids = torch.arange(S, dtype=torch.int64, device=self.dev)
         self.hist_cap = self.max_model_len
         self.history = torch.zeros(S, self.hist_cap, **i32)
-        # decode activations (persistent: no allocation inside a step, required for graph capture)
-        self.b_x = torch.empty(S, H, **bf)
-        self.b_x1 = torch.empty(S, H, **bf)
+        # decode activations (persistent: no allocation inside a step, required for graph capture); the persistent
+        # layer kernel loads them in row tiles of 32 / 64 / 128 / 256, so the buffers hold at least the tile that covers S
+        SA = next((t for t in (32, 64, 128, 256) if t >= S), S)
+        self.b_x = torch.zeros(SA, H, **bf)
+        self.b_x1 = torch.zeros(SA, H, **bf)
         self.b_h = torch.empty(S, H, **bf)
-        self.b_qkv = torch.empty(S, cfg.qkv_dim, **bf)
-        self.b_attn = torch.empty(S, cfg.q_dim, **bf)
+        self.b_qkv = torch.zeros(SA, cfg.qkv_dim, **bf)
+        self.b_attn = torch.zeros(SA, cfg.q_dim, **bf)
         self.b_gu = torch.empty(S, 2 * cfg.intermediate_size, **bf)
-        self.b_act = torch.empty(S, cfg.intermediate_size, **bf)
+        self.b_act = torch.zeros(SA, cfg.intermediate_size, **bf)
         self.b_tokens = torch.zeros(S, **i32)
         self.max_splits = 8
         self.b_part_o = torch.empty(S * cfg.num_key_value_heads * self.max_splits * 8 * cfg.head_dim, dtype=torch.float32,
@@ -162,6 +164,26 @@ class RolloutEngine:
             self.folded = torch.empty(L * (Q + 2 * F) * H, **bf)
             self.b_ss = torch.zeros(2 * L + 1, S, dtype=torch.int64, device=self.dev)  # fixed point, value * 2^30
             self.refold_weights()
+        # ---- persistent layer kernel: every decoder layer of a step in one cooperative launch (up to 256 rows) ----
+        self.mega_rows = 0
+        self.mega_trace: Optional[torch.Tensor] = None  # int64[32]: phase stamps of CTA 0 in layer mega_trace_layer
+        self.mega_trace_layer = 0
+        if (self.fused_decode and os.environ.get("AGRPO_DECODE_MEGA", "1") != "0"
+                and self.C.decode_layers_supported(min(256, S), H, Q, cfg.q_dim, F, cfg.num_attention_heads,
+                                                   cfg.num_key_value_heads, cfg.head_dim)):
+            self.mega_rows = min(256, S)
+            seg = self.layout.segments
+            nxt = 1 if L > 1 else 0
+            self.mega_strides = {k: seg[f"layers.{nxt}.{k}"].offset - seg[f"layers.0.{k}"].offset
+                                 for k in (("wo", "wd", "bqkv") if cfg.attention_bias else ("wo", "wd"))}
+            uniform = all(seg[f"layers.{i}.{k}"].offset - seg[f"layers.0.{k}"].offset == i * st
+                          for k, st in self.mega_strides.items() for i in range(L))
+            if not uniform:
+                self.mega_rows = 0
+            else:
+                self.b_partials = torch.empty(int(self.C.decode_layers_scratch_bytes(self.mega_rows, H, Q, cfg.q_dim, F)) // 4,
+                                              dtype=torch.float32, device=self.dev)
+                self.b_counters = torch.zeros(int(self.C.decode_layers_counter_words()), **i32)
         self.use_cuda_graph = use_cuda_graph
         self.use_pdl = os.environ.get("AGRPO_DECODE_PDL", "1") != "0"
         # keep running sequences in a dense prefix of the slots: the decode batch has as many rows as the highest slot
@@ -296,6 +318,8 @@ class RolloutEngine:
                     self.h_eos_at[slot] = 0
 
     def _decode_forward(self, B: int, temperature: float, splits: int) -> None:
+        if self.mega_rows and B <= self.mega_rows:
+            return self._decode_forward_mega(B, temperature, splits)
         if self.fused_decode and B <= self.fused_rows:
             # short kernels back to back: let each prologue overlap the tail of the kernel before (this thread only)
             self.C.set_pdl(self.use_pdl)
@@ -386,7 +410,31 @@ class RolloutEngine:
         self.history[self.row_ids[:B], torch.clamp(self.gen_index[:B], max=self.hist_cap - 1)] = self.b_tokens[:B]
         self.gen_index[:B].add_(1)
 
+    def _decode_forward_mega(self, B: int, temperature: float, splits: int) -> None:
+        """Embedding + statistics, ONE launch for all decoder layers, final norm, lm_head + sampling."""
+        cfg, C, dec = self.cfg, self.C, self.dec
+        cos_t, sin_t = dec.rope_tables(1)
+        eps, st, ms = cfg.rms_norm_eps, self.status, self.mega_strides
+        H, F, Q = cfg.hidden_size, cfg.intermediate_size, cfg.qkv_dim
+        per = (Q + 2 * F) * H
+        fq, fg = self._folded(0)
+        C.embedding_sumsq(self.last_tokens[:B], dec.w("embed"), self.b_x[:B], self.b_ss)
+        C.decode_layers(cfg.num_hidden_layers, B, fq, per, dec.w("layers.0.wo"), ms["wo"], fg, per, dec.w("layers.0.wd"), ms["wd"],
+                        dec.w("layers.0.bqkv") if cfg.attention_bias else None, ms.get("bqkv", 0), self.b_x, self.b_x1, self.b_qkv,
+                        self.b_attn, self.b_act, self.b_ss, eps, cos_t, sin_t, self.block_tables, self.seq_lens, self.cache,
+                        cfg.num_attention_heads, cfg.num_key_value_heads, 1.0 / math.sqrt(cfg.head_dim), splits, self.b_part_o,
+                        self.b_part_ml, self.b_tickets, self.b_partials, self.b_counters, st, self.mega_trace, self.mega_trace_layer)
+        h = self.b_h[:B]
+        C.rmsnorm_fwd(self.b_x[:B], dec.w("final_norm"), h, None, eps)
+        wl = self.layout.view(self.params, self.layout.lm_head_name())
+        C.lm_sample(h, wl, temperature, self.step_seeds, self.b_sample_f, self.b_sample_i, self.b_tokens, None, st)
+        self.last_tokens[:B].copy_(self.b_tokens[:B])
+        self.history[self.row_ids[:B], torch.clamp(self.gen_index[:B], max=self.hist_cap - 1)] = self.b_tokens[:B]
+        self.gen_index[:B].add_(1)
+
     def _launch_count_decode(self, splits: int, B: int = 0) -> int:
+        if self.mega_rows and 0 < B <= self.mega_rows:
+            return 1 + 1 + 3
         fused = self.fused_decode and 0 < B <= self.fused_rows
         per_layer = (5 if B <= 128 else 6) if fused else 9
         return 1 + per_layer * self.cfg.num_hidden_layers + 3
@@ -420,7 +468,11 @@ class RolloutEngine:
         self.C.decode_step_inputs(self.d_stage, S, self.seq_lens, self.positions, self.block_tables, self.base_seeds,
                                   self.step_seeds, self.status)
         max_len = int(self.h_lens[:B].max())
-        want = (148 * 3) // max(1, len(active) * self.cfg.num_key_value_heads)
+        if self.mega_rows and B <= self.mega_rows:
+            # the persistent layer kernel works on one attention item per CTA at a time: one wave of items
+            want = 148 // max(1, len(active) * self.cfg.num_key_value_heads)
+        else:
+            want = (148 * 3) // max(1, len(active) * self.cfg.num_key_value_heads)
         splits = int(max(1, min(self.max_splits, want, max(1, max_len // 256))))
         temperature = float(self.temperature or 0.0)
         t_mid = time.perf_counter()

@@ -465,6 +465,28 @@ def bench_decode(args):
          "ms_per_step": ms, "tokens_per_s": args.batch / ms * 1e3, "weight_bytes": layout_bytes, "kv_bytes": kv_bytes,
          "ideal_ms": (layout_bytes + kv_bytes) / pk["hbm_gbs"] / 1e6, "frac_of_hbm": (layout_bytes + kv_bytes) / ms / 1e6 / pk["hbm_gbs"],
          "peak": pk["source"]})
+    if getattr(args, "trace", False) and getattr(eng, "mega_rows", 0):
+        # clock64 stamps of CTA 0 in one middle layer, microseconds from the layer's start (1965 MHz assumed)
+        eng.use_cuda_graph = False
+        eng.mega_trace = torch.zeros(32 + 4 * 160, dtype=torch.int64, device="cuda")
+        eng.mega_trace_layer = cfg.num_hidden_layers // 2
+        eng.step()
+        torch.cuda.synchronize()
+        t = eng.mega_trace.cpu().numpy().astype(np.float64)
+        names = ["mma_first_operands", "mma_committed", "acc_ready", "partial_stored", "splits_arrived", "share_done"]
+        rel = lambda i: round((t[i] - t[26]) / 1965.0, 2) if t[i] > 0 else None
+        rec = {"bench": "decode_layers_trace", "layer": eng.mega_trace_layer, "unit": "us since the layer's start on CTA 0"}
+        for ph, pn in enumerate(["qkv", "o", "gate_up", "down"]):
+            rec[pn] = {n: rel(ph * 6 + i) for i, n in enumerate(names)}
+        rec["attention"] = {"inputs_ready": rel(24), "end": rel(25)}
+        per = t[32:].reshape(-1, 4)
+        per = per[per[:, 0] > 0]
+        if len(per):
+            t0 = per[:, 3][per[:, 3] > 0].min() if (per[:, 3] > 0).any() else per[:, 0].min()
+            us = lambda col: [round(float(x), 2) for x in ((np.percentile(col[col > 0], [0, 50, 100]) - t0) / 1e3)]
+            rec["all_ctas_us_min_med_max"] = {"qkv_first_mma": us(per[:, 3]), "attention_inputs_ready": us(per[:, 0]),
+                                              "attention_end": us(per[:, 1]), "o_first_mma": us(per[:, 2])}
+        out(rec)
 
 
 def bench_train(args):
@@ -529,6 +551,7 @@ def main():
     ap.add_argument("--context", type=int, default=1024)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--graph", action="store_true")
+    ap.add_argument("--trace", action="store_true", help="decode: print the phase stamps of the persistent layer kernel (one eager step)")
     ap.add_argument("--tokens", type=int, default=16384)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--recompute", action="store_true")
