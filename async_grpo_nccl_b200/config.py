@@ -73,7 +73,7 @@ class GRPOConfig:
     # ---- batching ----
     train_minibatch_sample_size: int = 4000
     max_tokens_per_gpu: int = 36000
-    infinite_sampler_seed: int = 42
+    infinite_sampler_seed: int = 42  # reference key; no sampler reads it there either (its data order is fixed)
     experience_batcher_name: str = "experience_batcher"
     # ---- logging / eval / checkpoints ----
     wandb_project: Optional[str] = None
@@ -86,20 +86,25 @@ class GRPOConfig:
     min_samples_per_checkpoint: int = 30000
     keep_last_n_checkpoints: int = 2
     verify_weight_sync_during_init: bool = False
+    # system/* series (GPU memory, utilisation, power, SM clock; read-only NVML queries) once per macro-batch
     enable_manual_system_metrics: bool = False
-    system_metrics_interval_sec: float = 10.0
+    system_metrics_interval_sec: float = 10.0  # reference key; sampling here is per macro-batch
     # ---- new: engine behaviour ----
     weight_sync_every: int = 1  # macro-batches between trainer -> rollout/logprob pushes
     # Feed finished samples to the microbatch planner right away instead of waiting for a whole minibatch: the
     # same samples end up in the same optimizer step, but forward/backward overlaps the rest of the generation.
     eager_microbatch_dispatch: bool = False
     comm_backend: str = "auto"  # "auto" (peer-memory kernels when available) | "peer" | "nccl" (library collectives)
-    kernel_checks: bool = False  # kernels validate indices and report through a status word
+    # The kernels always validate indices and report through a status word; with this switch the host reads that word
+    # after every microbatch and every engine step (a synchronisation each) instead of once per macro-batch
+    kernel_checks: bool = False
     stream_logprobs: bool = True  # request a sample's old-policy logprobs when IT finishes, not when its whole group has
+    # > 0: on a GPU that a rollout engine shares with the trainer or the logprob role, the engine gets this many SMs of
+    # its own and the other roles the rest (CUDA green contexts, utils/sm_partition.py); 0 = all roles use every SM
+    colocated_rollout_sms: int = 0
     colocated_sm_limit: int = 0  # > 0: trainer / logprob GEMMs fill at most this many SMs on a GPU they share with a rollout engine
     param_sharding: str = "zero2"  # "zero2": resident bf16 copy per trainer rank | "zero3": fully sharded, gathered per layer
     activation_recompute: str = "auto"  # "none" | "full" | "auto" (by memory estimate)
-    fsdp_reshard_after_forward: Optional[bool] = None  # None: decide from model size vs HBM
     trainer_completion_timeout_s: float = 300.0
     prompt_timeout_s: float = 1200.0
     dist_timeout_s: float = 600.0
@@ -173,6 +178,7 @@ class GRPOConfig:
         need(self.lr_scheduler in ("constant", "cosine", "constant_with_warmup"), "unknown lr_scheduler")
         need(self.vllm_engine_preset in ("eager", "throughput"), "vllm_engine_preset must be eager or throughput")
         need(self.colocated_sm_limit >= 0, "colocated_sm_limit must be >= 0")
+        need(self.colocated_rollout_sms >= 0, "colocated_rollout_sms must be >= 0")
         need(self.param_sharding in ("zero2", "zero3"), "param_sharding must be zero2/zero3")
         need(self.activation_recompute in ("none", "full", "auto"), "activation_recompute must be none/full/auto")
         need(self.keep_last_n_checkpoints >= 1, "keep_last_n_checkpoints must be >= 1")

@@ -496,7 +496,7 @@ void decode_layers(int64_t L, int64_t B, const Tensor& wqkv0, int64_t wqkv_strid
   a.counters = reinterpret_cast<unsigned int*>(counters.data_ptr<int>());
   a.status = opt_ptr<int>(status);
   {
-    static const int pf = [] { const char* e = std::getenv("AGRPO_MEGA_PREFETCH"); return e ? std::atoi(e) : 0; }();
+    static const int pf = [] { const char* e = std::getenv("AGRPO_MEGA_PREFETCH"); return e ? std::atoi(e) : 8; }();
     a.prefetch_tiles = pf;
   }
   if (trace.has_value() && trace->defined()) {

@@ -31,6 +31,14 @@
  *  - Pointers are device pointers on the current device. hidden and weight must be 16-byte aligned, row pitches
  *    (in elements) multiples of 8; H a multiple of 8.
  *  - The work is enqueued on `stream` (a cudaStream_t, may be 0) and the function returns without waiting.
+ *  - labels[t] must be below V (or negative = no label). They are device data and are not checked: a label >= V selects
+ *    no column, and that row comes back as logp = -lse.
+ *  - A return value of AGRPO_NOALLOC_OK says the work was enqueued, not that it ran correctly. The kernels bound every
+ *    internal wait; should one run out (a device in trouble), they record it in a status word instead of hanging, and the
+ *    outputs of that call are then not valid. Call agrpo_lmhead_noalloc_status(stream) after the call: it waits for the
+ *    stream and returns that word (0 = outputs valid).
+ *  - Within one process the function may be used on several GPUs: each holds its own copy of the array and is set up on
+ *    its own first call.
  */
 #ifndef AGRPO_NOALLOC_H_
 #define AGRPO_NOALLOC_H_
@@ -51,6 +59,11 @@ extern "C" {
 int agrpo_lmhead_logprob_noalloc(const void* hidden_bf16, long long hidden_pitch, const void* weight_bf16,
                                  long long weight_pitch, const int* labels, int T, int H, int V, float temperature,
                                  float* logp, float* entropy, float* lse, void* stream, char* err_msg, int err_cap);
+
+/* Waits for `stream` and returns the status word that the most recent call on the current device left behind: 0 when its
+ * kernels completed normally, a positive code when a bounded wait inside them ran out (discard that call's outputs),
+ * AGRPO_NOALLOC_E_CUDA when the word could not be read. Has no counterpart in the reference project. */
+int agrpo_lmhead_noalloc_status(void* stream);
 
 #ifdef __cplusplus
 }

@@ -371,11 +371,7 @@ void launch_bwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMa
                   const AttnBwdParams& p, int n_tiles, int Hkv, cudaStream_t s) {
   constexpr int smem = 5 * kT * D * 2 + kT * kT * 2 + 4 * kT * 4 + 128 + 1024;
   auto kernel = attn_bwd_kernel<D>;
-  static bool configured = false;
-  if (!configured) {
-    check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "attn_bwd smem attr");
-    configured = true;
-  }
+  AGRPO_SET_MAX_DYN_SMEM(kernel, smem, "attn_bwd smem attr");
   dim3 grid(Hkv, n_tiles);
   kernel<<<grid, kBwdThreads, smem, s>>>(tq, tk, tv, tdo, p);
   check_cuda(cudaGetLastError(), "attn_bwd launch");

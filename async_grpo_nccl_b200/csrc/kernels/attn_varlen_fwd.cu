@@ -283,11 +283,7 @@ void launch_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMa
                   int Hq, cudaStream_t s) {
   constexpr int smem = 3 * kBM * D * 2 + 128 + 1024;
   auto kernel = attn_fwd_kernel<D>;
-  static bool configured = false;
-  if (!configured) {
-    check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "attn_fwd smem attr");
-    configured = true;
-  }
+  AGRPO_SET_MAX_DYN_SMEM(kernel, smem, "attn_fwd smem attr");
   dim3 grid(Hq, n_tiles);
   kernel<<<grid, kAttnThreads, smem, s>>>(tq, tk, tv, p);
   check_cuda(cudaGetLastError(), "attn_fwd launch");

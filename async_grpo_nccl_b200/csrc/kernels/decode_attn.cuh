@@ -78,6 +78,10 @@ __device__ __forceinline__ uint8_t* tile_chunk(uint8_t* tile, int row, int chunk
 // Returns true in every thread of the CTA that produced the final output row group (splits == 1, or the last split).
 __device__ __forceinline__ void dec_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+// STAGES = K/V blocks a warp keeps in shared memory (one being consumed, STAGES - 1 in flight): dsm must hold
+// 4 * STAGES * 8 KB. A decode item is a chain of block loads, so its time is (blocks per warp) x (load latency) /
+// (loads in flight).
+template <int STAGES>
 __device__ __forceinline__ bool paged_decode_attend(const DecodeParams& p, int split, int kvh, int b, uint8_t* dsm, int warp,
                                                     int tid, int* s_last) {
   const int lane = tid & 31;
@@ -86,8 +90,8 @@ __device__ __forceinline__ bool paged_decode_attend(const DecodeParams& p, int s
   const int n_blocks = (seq_len + kDecBlock - 1) / kDecBlock;
   const int blk_begin = (int)((long long)n_blocks * split / p.splits);
   const int blk_end = (int)((long long)n_blocks * (split + 1) / p.splits);
-  // per-warp staging: 2 stages x (K tile 4 KB + V tile 4 KB)
-  uint8_t* wbuf = dsm + warp * (2 * 2 * 4096);
+  // per-warp staging: STAGES x (K tile 4 KB + V tile 4 KB)
+  uint8_t* wbuf = dsm + warp * (STAGES * 8192);
   const int* table = p.block_tables + (long long)b * p.max_blocks;
 
   // Q fragments (A operand, rows = query heads of this kv head, zero above G), pre-scaled later in fp32.
@@ -124,20 +128,22 @@ __device__ __forceinline__ bool paged_decode_attend(const DecodeParams& p, int s
       cp_async16(tile_chunk(kt, row, chunk), ksrc + row * kDecD + chunk * 8);
       cp_async16(tile_chunk(vt, row, chunk), vsrc + row * kDecD + chunk * 8);
     }
-    cp_async_commit();
   };
 
+  // One commit group per loop iteration (empty when there is nothing left to load), so that "at most STAGES - 1 groups
+  // pending" always means: the block about to be consumed has landed.
   int my = blk_begin + warp;
-  if (my < blk_end) issue_load(my, 0);
+#pragma unroll
+  for (int i = 0; i < STAGES - 1; ++i) {
+    if (my + i * kDecWarps < blk_end) issue_load(my + i * kDecWarps, i);
+    cp_async_commit();
+  }
   int stage = 0;
-  for (; my < blk_end; my += kDecWarps, stage ^= 1) {
-    const int nxt = my + kDecWarps;
-    if (nxt < blk_end) {
-      issue_load(nxt, stage ^ 1);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
+  for (; my < blk_end; my += kDecWarps, stage = (stage + 1 == STAGES ? 0 : stage + 1)) {
+    const int nxt = my + (STAGES - 1) * kDecWarps;
+    if (nxt < blk_end) issue_load(nxt, stage == 0 ? STAGES - 1 : stage - 1);
+    cp_async_commit();
+    cp_async_wait<STAGES - 1>();
     __syncwarp();
     uint8_t* kt = wbuf + stage * 8192;
     uint8_t* vt = kt + 4096;

@@ -153,8 +153,9 @@ __device__ __forceinline__ void st_bf16x4(__nv_bfloat16* p, float4 v) {
 template <int BT>
 struct MegaCfg {
   static constexpr int kXStage = BT * kMBK * 2;
-  static constexpr int kNSW = BT <= 128 ? 8 : 7;
-  static constexpr int kXA = BT <= 128 ? 65536 : 98304;  // activation ring; the attention phase stages K/V tiles here
+  static constexpr int kNSW = 7;
+  static constexpr int kXA = 98304;  // activation ring; the attention phase stages K/V tiles here (3 blocks per warp)
+  static constexpr int kAttStages = 3;
   static constexpr int kNSX = (kXA / kXStage) > 8 ? 8 : (kXA / kXStage);
   static constexpr int kAcc = 2;
   static constexpr uint32_t kTmemCols = (kAcc * BT) < 32 ? 32 : (kAcc * BT);
@@ -461,7 +462,12 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmWqkv, const __grid_co
             const int split = it % p.splits;
             const int rest = it / p.splits;
             const int kvh = rest % p.Hkv, b = rest / p.Hkv;
-            const bool fin = paged_decode_attend(dp, split, kvh, b, xa, cw, tid, &sh->s_last);
+            if (p.seq_lens[b] <= 0) {
+              // an idle row (a free slot inside the batch): nothing to attend to, its output is never used
+              if (split == 0 && tid == 0) red_release_gpu_add(p.done, 1u);
+              continue;
+            }
+            const bool fin = paged_decode_attend<Cfg::kAttStages>(dp, split, kvh, b, xa, cw, tid, &sh->s_last);
             if (fin) {
               dec_bar_sync();  // every thread's output stores are issued
               if (tid == 0) {
@@ -508,7 +514,8 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmWqkv, const __grid_co
           const int b_first = r0 + cw * RU;
           sumsq_t m_ss[RU];
           int m_len[RU];
-          float4 m_rr[RU];
+          float4 m_rr[RU], m_cs[RU], m_sn[RU];
+          int m_blk[RU];
           auto load_meta = [&](int b0) {
 #pragma unroll
             for (int j = 0; j < RU; ++j) {
@@ -525,6 +532,19 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmWqkv, const __grid_co
                 } else {
                   m_rr[j] = ld_bf16x4((ph == 1 ? p.x : p.x1) + (size_t)b * p.H + grp * kFT + 4 * lane);
                 }
+              }
+            }
+            if (ph == 0 && b0 < r1) {  // rotary table entries and the cache block of each row's position
+              const bool not_q = grp >= p.Hq;
+              const int jr = (4 * lane) & 63;
+#pragma unroll
+              for (int j = 0; j < RU; ++j) {
+                const int b = (b0 + j < r1) ? b0 + j : r0;
+                const int pos = m_len[j] > 0 ? m_len[j] - 1 : 0;
+                const int pp = pos >= p.max_pos ? p.max_pos - 1 : pos;
+                m_cs[j] = *reinterpret_cast<const float4*>(p.cos_t + (size_t)pp * 64 + jr);
+                m_sn[j] = *reinterpret_cast<const float4*>(p.sin_t + (size_t)pp * 64 + jr);
+                m_blk[j] = (not_q && m_len[j] > 0) ? p.block_tables[(long long)b * p.max_blocks + pos / kDecBlock] : 0;
               }
             }
           };
@@ -582,22 +602,12 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmWqkv, const __grid_co
             }
             if (ph == 0) {
               const bool is_q = grp < p.Hq, is_k = !is_q && grp < p.Hq + p.Hkv;
-              int len[RU], blk[RU];
-              float4 cs[RU], sn[RU];
               float4 bb = make_float4(0.f, 0.f, 0.f, 0.f);
               if (p.bqkv != nullptr) bb = ld_bf16x4(p.bqkv + (long long)l * p.bqkv_stride + grp * kFT + 4 * lane);
-              const int jr = (4 * lane) & 63;
-#pragma unroll
-              for (int j = 0; j < RU; ++j) len[j] = m_len[j];
-#pragma unroll
-              for (int j = 0; j < RU; ++j) {
-                const int b = on[j] ? b0 + j : r0;
-                const int pos = len[j] > 0 ? len[j] - 1 : 0;
-                const int pp = pos >= p.max_pos ? p.max_pos - 1 : pos;
-                cs[j] = *reinterpret_cast<const float4*>(p.cos_t + (size_t)pp * 64 + jr);
-                sn[j] = *reinterpret_cast<const float4*>(p.sin_t + (size_t)pp * 64 + jr);
-                blk[j] = (!is_q && len[j] > 0) ? p.block_tables[(long long)b * p.max_blocks + pos / kDecBlock] : 0;
-              }
+              const int* len = m_len;
+              const int* blk = m_blk;
+              const float4* cs = m_cs;
+              const float4* sn = m_sn;
 #pragma unroll
               for (int j = 0; j < RU; ++j) {
                 if (!on[j]) continue;  // warp-uniform
@@ -694,11 +704,7 @@ template <int BT>
 void launch_mega(const CUtensorMap* tm, const MegaParams& p, cudaStream_t stream) {
   using Cfg = MegaCfg<BT>;
   auto kernel = decode_layers_kernel<BT>;
-  static bool configured = false;
-  if (!configured) {
-    check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem), "decode_layers smem attr");
-    configured = true;
-  }
+  AGRPO_SET_MAX_DYN_SMEM(kernel, Cfg::kSmem, "decode_layers smem attr");
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(p.grid, 1, 1);
   cfg.blockDim = dim3(kMegaThreads, 1, 1);

@@ -463,11 +463,7 @@ template <int BN, int MT, int STAGES>
 void launch_sk(const CUtensorMap& ta, const CUtensorMap& tb, const SkParams& p, int S, int n_tiles, cudaStream_t stream) {
   constexpr int smem = STAGES * (MT * kBM * kBK * 2 + BN * kBK * 2) + BN * MT * kBM * 4 + 256 + 1024;
   auto kernel = gemm_splitk_cluster_kernel<BN, MT, STAGES>;
-  static bool configured = false;
-  if (!configured) {
-    check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "gemm_splitk smem attr");
-    configured = true;
-  }
+  AGRPO_SET_MAX_DYN_SMEM(kernel, smem, "gemm_splitk smem attr");
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(S, n_tiles, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);

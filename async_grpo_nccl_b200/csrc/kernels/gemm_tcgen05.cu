@@ -197,11 +197,7 @@ bool launch_gemm_swiglu_bf16(const void* a, long long lda, const void* b, long l
 bool launch_unit_gather(const GatherArgs& g, int n_ctas, int* status, cudaStream_t stream) {
   if (!gather_args_ok(g) || n_ctas < 1) return false;
   GatherJob gj = make_gather_job(g, n_ctas);
-  static bool configured = false;
-  if (!configured) {
-    check_cuda(cudaFuncSetAttribute(unit_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGatherSmem), "unit_gather attr");
-    configured = true;
-  }
+  AGRPO_SET_MAX_DYN_SMEM(unit_gather_kernel, kGatherSmem, "unit_gather attr");
   unit_gather_kernel<<<n_ctas, 64, kGatherSmem, stream>>>(gj, status);
   check_cuda(cudaGetLastError(), "unit_gather_kernel");
   return true;

@@ -597,12 +597,7 @@ inline void gemm_launch(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
                         cudaStream_t stream, const Gather& gj = Gather{0}) {
   using S = GemmSmem<BN>;
   auto kernel = gemm_tcgen05_kernel<BN, A_MN, B_MN, Epi, Gather>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
-    if (e != cudaSuccess) throw std::runtime_error(std::string("gemm smem attr: ") + cudaGetErrorString(e));
-    configured = true;
-  }
+  AGRPO_SET_MAX_DYN_SMEM(kernel, S::kTotal, "gemm smem attr");
   const int items = gemm_num_items(p.M, p.N, BN, p.group_n);
   // every CTA of the grid must be resident at once when CTAs wait on one another (copiers + workers <= SMs)
   const int n_copy = Gather::kEnabled ? gj.n_copy : 0;

@@ -16,10 +16,14 @@ constexpr int kMaxDevices = 64;
 
 // Part of the library image: one copy per GPU that loads the library.
 static __device__ __align__(256) float g_lmhead_scratch[kScratchFloats];
+// Status word of the kernels behind this entry point (0 = fine; non-zero: a bounded wait inside the GEMM ran out and the
+// outputs of that call are not to be trusted). Cleared by every call, read back by agrpo_lmhead_noalloc_status().
+static __device__ int g_lmhead_status;
 
 // In host code the name above is only a handle for the runtime, not a device address; the address is looked up once
 // per device (with that device current) and cached here.
 float* g_scratch_addr[kMaxDevices] = {nullptr};
+int* g_status_addr[kMaxDevices] = {nullptr};
 int g_num_sms[kMaxDevices] = {0};
 std::mutex g_setup_mutex;
 
@@ -82,7 +86,14 @@ extern "C" int agrpo_lmhead_logprob_noalloc(const void* hidden_bf16, long long h
         set_msg(err_msg, err_cap, e != cudaSuccess ? cudaGetErrorString(e) : "could not read the SM count");
         return AGRPO_NOALLOC_E_CUDA;
       }
+      int* sptr = nullptr;
+      e = cudaGetSymbolAddress(reinterpret_cast<void**>(&sptr), g_lmhead_status);
+      if (e != cudaSuccess || sptr == nullptr) {
+        set_msg(err_msg, err_cap, e != cudaSuccess ? cudaGetErrorString(e) : "cudaGetSymbolAddress returned NULL");
+        return AGRPO_NOALLOC_E_CUDA;
+      }
       g_num_sms[dev] = sms;
+      g_status_addr[dev] = sptr;
       g_scratch_addr[dev] = ptr;
     }
   }
@@ -91,16 +102,33 @@ extern "C" int agrpo_lmhead_logprob_noalloc(const void* hidden_bf16, long long h
   float* label_logit = scratch + 3 * groups * T;   // [T], rows without a valid label are never written: clear it
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   e = cudaMemsetAsync(label_logit, 0, sizeof(float) * (size_t)T, s);
+  if (e == cudaSuccess) e = cudaMemsetAsync(g_status_addr[dev], 0, sizeof(int), s);
   if (e != cudaSuccess) {
     set_msg(err_msg, err_cap, cudaGetErrorString(e));
     return AGRPO_NOALLOC_E_CUDA;
   }
   try {
     agrpo::launch_lmhead_logprob(hidden_bf16, hidden_pitch, weight_bf16, weight_pitch, labels, T, H, V, temperature, partials,
-                                 label_logit, logp, entropy, lse, /*status=*/nullptr, g_num_sms[dev], s);
+                                 label_logit, logp, entropy, lse, g_status_addr[dev], g_num_sms[dev], s);
   } catch (const std::exception& ex) {
     set_msg(err_msg, err_cap, ex.what());
     return AGRPO_NOALLOC_E_CUDA;
   }
   return AGRPO_NOALLOC_OK;
+}
+
+extern "C" int agrpo_lmhead_noalloc_status(void* stream) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return AGRPO_NOALLOC_E_CUDA;
+  int* addr = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_setup_mutex);
+    addr = g_status_addr[dev];
+  }
+  if (addr == nullptr) return 0;  // no call was made on this device yet
+  int word = 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (cudaMemcpyAsync(&word, addr, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess) return AGRPO_NOALLOC_E_CUDA;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return AGRPO_NOALLOC_E_CUDA;
+  return word;
 }

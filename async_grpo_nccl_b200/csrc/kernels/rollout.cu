@@ -136,7 +136,7 @@ paged_decode_attn_kernel(const DecodeParams p) {
   __shared__ int s_last;
   pdl_wait();
   pdl_launch();
-  paged_decode_attend(p, blockIdx.x, blockIdx.y, blockIdx.z, dsm, threadIdx.x >> 5, threadIdx.x, &s_last);
+  paged_decode_attend<2>(p, blockIdx.x, blockIdx.y, blockIdx.z, dsm, threadIdx.x >> 5, threadIdx.x, &s_last);
 }
 
 __global__ void paged_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int splits,
@@ -365,12 +365,7 @@ void launch_paged_decode_attn(const void* q, long long ldq, int q_col0, const vo
   p.status = status;
   p.tickets = tickets;
   constexpr int smem = kDecWarps * 2 * 2 * 4096;  // 64 KB staging (>= merge area of 16.6 KB)
-  static bool configured = false;
-  if (!configured) {
-    check_cuda(cudaFuncSetAttribute(paged_decode_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
-               "paged_decode smem attr");
-    configured = true;
-  }
+  AGRPO_SET_MAX_DYN_SMEM(paged_decode_attn_kernel, smem, "paged_decode smem attr");
   dim3 grid(splits, Hkv, B);
   AGRPO_PREFER_SMEM(paged_decode_attn_kernel);
   launch_kernel(paged_decode_attn_kernel, grid, dim3(kDecWarps * 32), smem, s, "paged_decode_attn", p);

@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <stdexcept>
 #include <string>
 
@@ -27,6 +28,32 @@ inline void prefer_max_shared(K kernel) {
       ::agrpo::prefer_max_shared(kernel);                 \
       agrpo_once_ = true;                                 \
     }                                                     \
+  } while (0)
+
+// cudaFuncSetAttribute applies to the device that is current when it is called, and role threads launch concurrently:
+// one flag per device (atomic) per call site, so that a second GPU driven from the same process is configured too.
+struct PerDeviceOnce {
+  std::atomic<bool> done[64];
+  PerDeviceOnce() {
+    for (auto& d : done) d.store(false);
+  }
+  static int device() {
+    int d = 0;
+    return cudaGetDevice(&d) == cudaSuccess && d >= 0 && d < 64 ? d : -1;
+  }
+  bool need(int d) const { return d < 0 || !done[d].load(std::memory_order_acquire); }
+  void set(int d) {
+    if (d >= 0) done[d].store(true, std::memory_order_release);
+  }
+};
+#define AGRPO_SET_MAX_DYN_SMEM(kernel, bytes, what)                                                                   \
+  do {                                                                                                                \
+    static ::agrpo::PerDeviceOnce agrpo_once_;                                                                        \
+    const int agrpo_dev_ = ::agrpo::PerDeviceOnce::device();                                                          \
+    if (agrpo_once_.need(agrpo_dev_)) {                                                                               \
+      ::agrpo::check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(bytes)), what); \
+      agrpo_once_.set(agrpo_dev_);                                                                                    \
+    }                                                                                                                 \
   } while (0)
 
 // Programmatic dependent launch is a per-thread switch: the rollout engine turns it on around its decode step, whose

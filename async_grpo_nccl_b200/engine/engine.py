@@ -40,6 +40,7 @@ class FinishedSequence:
     output_ids: np.ndarray  # int32
     finish_reason: str  # "stop" (EOS) | "length"
     prompt_len: int
+    output_logprobs: Optional[np.ndarray] = None  # fp32 log-probability of every sampled token (when recorded)
 
 
 @dataclass
@@ -75,6 +76,7 @@ class RolloutEngine:
         self.C = native()
         self.cfg, self.layout, self.params = cfg, layout, params
         self.dev = params.device
+        self.sm_count = torch.cuda.get_device_properties(self.dev).multi_processor_count  # SMs the engine's stream may use
         self.dec = NativeDecoder(cfg, layout, params)
         self.status = self.dec.status
         self.block_size = block_size
@@ -156,10 +158,11 @@ class RolloutEngine:
         # GEMMs' epilogues from sums of squares that the producing GEMMs' epilogues accumulate. Together with the fused
         # gate/up + SwiGLU GEMM a layer is 6 kernels instead of 9.
         L, F, Q = cfg.num_hidden_layers, cfg.intermediate_size, cfg.qkv_dim
-        self.fused_rows = min(256, self.max_seqs)
+        self.fused_chunk = min(256, self.max_seqs)   # rows per launch of the skinny GEMMs
         self.fused_decode = F % 8 == 0 and all(
             int(self.C.gemm_skinny_splits(m, n, k)) > 0
-            for m in range(32, self.fused_rows + 1, 32) for n, k in ((Q, H), (H, cfg.q_dim), (H, F)))
+            for m in range(32, self.fused_chunk + 1, 32) for n, k in ((Q, H), (H, cfg.q_dim), (H, F)))
+        self.fused_rows = self.max_seqs if self.fused_decode else 0  # larger batches go through in chunks
         if self.fused_decode:
             self.folded = torch.empty(L * (Q + 2 * F) * H, **bf)
             self.b_ss = torch.zeros(2 * L + 1, S, dtype=torch.int64, device=self.dev)  # fixed point, value * 2^30
@@ -171,7 +174,9 @@ class RolloutEngine:
         if (self.fused_decode and os.environ.get("AGRPO_DECODE_MEGA", "1") != "0"
                 and self.C.decode_layers_supported(min(256, S), H, Q, cfg.q_dim, F, cfg.num_attention_heads,
                                                    cfg.num_key_value_heads, cfg.head_dim)):
-            self.mega_rows = min(256, S)
+            # it wins where the step is latency-bound (few rows); with more rows both paths are bound by streaming the
+            # KV cache and the per-phase hand-offs of the persistent kernel cost more than separate launches
+            self.mega_rows = min(int(os.environ.get("AGRPO_MEGA_MAX_ROWS", "32")), 256, S)
             seg = self.layout.segments
             nxt = 1 if L > 1 else 0
             self.mega_strides = {k: seg[f"layers.{nxt}.{k}"].offset - seg[f"layers.0.{k}"].offset
@@ -184,6 +189,10 @@ class RolloutEngine:
                 self.b_partials = torch.empty(int(self.C.decode_layers_scratch_bytes(self.mega_rows, H, Q, cfg.q_dim, F)) // 4,
                                               dtype=torch.float32, device=self.dev)
                 self.b_counters = torch.zeros(int(self.C.decode_layers_counter_words()), **i32)
+        # chosen-token log-probabilities (off until a caller asks: one more small tensor op per step)
+        self.record_logprobs = False
+        self.b_lp: Optional[torch.Tensor] = None
+        self.history_lp: Optional[torch.Tensor] = None
         self.use_cuda_graph = use_cuda_graph
         self.use_pdl = os.environ.get("AGRPO_DECODE_PDL", "1") != "0"
         # keep running sequences in a dense prefix of the slots: the decode batch has as many rows as the highest slot
@@ -212,6 +221,17 @@ class RolloutEngine:
             forced = [max(1, min(int(f), max_new)) for f in forced_new_tokens]
         self.pending.append(_Request(request_id, prompt, int(n), max_new, float(temperature), int(seed), forced,
                                      bool(ignore_eos or forced is not None)))
+
+    def enable_logprobs(self) -> None:
+        """From now on the log-probability of every sampled token (under the sampling temperature) is kept next to the
+        token history and returned with finished sequences (what the reference reads from vLLM's ``logprobs`` output,
+        vllm_worker.py:286-392). Captured graphs are dropped: the step gains one output."""
+        if self.record_logprobs:
+            return
+        self.record_logprobs = True
+        self.b_lp = torch.zeros(self.max_seqs, dtype=torch.float32, device=self.dev)
+        self.history_lp = torch.zeros(self.max_seqs, self.hist_cap, dtype=torch.float32, device=self.dev)
+        self.graphs.clear()
 
     def has_work(self) -> bool:
         return bool(self.pending) or self.sched.num_waiting > 0 or self.sched.num_running > 0
@@ -246,9 +266,10 @@ class RolloutEngine:
         self.h2d_bytes += u.numel() * 8
         self.block_tables.index_put_((ud[0], ud[1]), ud[2].to(torch.int32))
 
-    def _sample(self, hidden: torch.Tensor, rows: int, seeds: torch.Tensor, tokens: torch.Tensor, temperature: float) -> None:
+    def _sample(self, hidden: torch.Tensor, rows: int, seeds: torch.Tensor, tokens: torch.Tensor, temperature: float,
+                logprobs: Optional[torch.Tensor] = None) -> None:
         wl = self.layout.view(self.params, self.layout.lm_head_name())
-        self.C.lm_sample(hidden[:rows], wl, temperature, seeds, self.b_sample_f, self.b_sample_i, tokens, None, self.status)
+        self.C.lm_sample(hidden[:rows], wl, temperature, seeds, self.b_sample_f, self.b_sample_i, tokens, logprobs, self.status)
         self.launches += 2
 
     def _prefill(self, plan: Dict[str, Any]) -> None:
@@ -300,13 +321,16 @@ class RolloutEngine:
         seeds = torch.tensor(seeds_host, dtype=torch.int64).pin_memory().to(self.dev, non_blocking=True)
         slot_idx = torch.tensor(seq_slots, dtype=torch.int64).pin_memory().to(self.dev, non_blocking=True)
         toks = torch.empty(n_rows, dtype=torch.int32, device=self.dev)
+        lps = torch.empty(n_rows, dtype=torch.float32, device=self.dev) if self.record_logprobs else None
         # rows are processed in pieces of at most max_seqs so the scratch buffers suffice
         for s in range(0, n_rows, self.max_seqs):
             e = min(n_rows, s + self.max_seqs)
-            self._sample(hrep[s:e], e - s, seeds[s:e], toks[s:e], self.temperature or 0.0)
+            self._sample(hrep[s:e], e - s, seeds[s:e], toks[s:e], self.temperature or 0.0, lps[s:e] if lps is not None else None)
         self.base_seeds.index_copy_(0, slot_idx, seeds)
         self.last_tokens.index_copy_(0, slot_idx, toks)
         self.history[slot_idx, 0] = toks
+        if lps is not None:
+            self.history_lp[slot_idx, 0] = lps
         self.gen_index.index_fill_(0, slot_idx, 1)
         self.tokens_generated += n_rows
         self.launches += dec.launches
@@ -350,10 +374,16 @@ class RolloutEngine:
             C.gemm_bf16(act, dec.w(p + "wd"), x, False, False, None, 1.0, False, self.status, x1)
         C.rmsnorm_fwd(x, dec.w("final_norm"), h, None, cfg.rms_norm_eps)
         wl = self.layout.view(self.params, self.layout.lm_head_name())
-        C.lm_sample(h, wl, temperature, self.step_seeds, self.b_sample_f, self.b_sample_i, self.b_tokens, None, self.status)
-        # feed the sampled token back and record it
+        C.lm_sample(h, wl, temperature, self.step_seeds, self.b_sample_f, self.b_sample_i, self.b_tokens, self.b_lp, self.status)
+        self._feed_back(B)
+
+    def _feed_back(self, B: int) -> None:
+        """The sampled token becomes the next step's input and goes into the history (with its log-probability when kept)."""
+        pos = torch.clamp(self.gen_index[:B], max=self.hist_cap - 1)
         self.last_tokens[:B].copy_(self.b_tokens[:B])
-        self.history[self.row_ids[:B], torch.clamp(self.gen_index[:B], max=self.hist_cap - 1)] = self.b_tokens[:B]
+        self.history[self.row_ids[:B], pos] = self.b_tokens[:B]
+        if self.record_logprobs:
+            self.history_lp[self.row_ids[:B], pos] = self.b_lp[:B]
         self.gen_index[:B].add_(1)
 
     # ---- fused decode path ----
@@ -377,38 +407,44 @@ class RolloutEngine:
         self.launches += 2 * self.cfg.num_hidden_layers
 
     def _decode_forward_fused(self, B: int, temperature: float, splits: int) -> None:
+        """Five kernels per layer for up to 256 rows. Larger batches run layer by layer in row chunks of at most 256: a
+        layer's weights (tens of MB) are still in L2 when the second chunk reads them, so they cross HBM once."""
         cfg, C, dec = self.cfg, self.C, self.dec
         cos_t, sin_t = dec.rope_tables(1)
-        x, x1, h, qkv, attn, act = (self.b_x[:B], self.b_x1[:B], self.b_h[:B], self.b_qkv[:B], self.b_attn[:B], self.b_act[:B])
-        bt, sl, ss = self.block_tables, self.seq_lens, self.b_ss
+        ss = self.b_ss
         scale = 1.0 / math.sqrt(cfg.head_dim)
         eps = cfg.rms_norm_eps
         st = self.status
-        C.embedding_sumsq(self.last_tokens[:B], dec.w("embed"), x, ss)
+        R = self.fused_chunk
+        chunks = [(r0, min(B, r0 + R)) for r0 in range(0, B, R)]
+        C.embedding_sumsq(self.last_tokens[:B], dec.w("embed"), self.b_x[:B], ss)
         for i in range(cfg.num_hidden_layers):
             p = f"layers.{i}."
             fq, fg = self._folded(i)
             bq = dec.w(p + "bqkv") if cfg.attention_bias else None
-            # up to 128 rows: rotary embedding and the KV-cache write happen in the qkv GEMM's epilogue
-            ok = B <= 128 and C.gemm_decode_rope(x, fq, qkv, bq, ss[2 * i], eps, cos_t, sin_t, bt, sl, self._kc(i), self._vc(i),
-                                                 cfg.num_attention_heads, cfg.num_key_value_heads, st)
-            if not ok:
-                ok = C.gemm_decode(x, fq, qkv, bq, None, ss[2 * i], None, eps, st)
-                C.rope_kv_write_decode(qkv, cos_t, sin_t, bt, sl, self._kc(i), self._vc(i), cfg.num_attention_heads,
-                                       cfg.num_key_value_heads, cfg.head_dim, st)
-            C.paged_decode_attn(qkv, self._kc(i), self._vc(i), bt, sl, attn, cfg.num_attention_heads, cfg.num_key_value_heads,
-                                cfg.head_dim, scale, splits, self.b_part_o, self.b_part_ml, st, self.b_tickets)
-            ok = C.gemm_decode(attn, dec.w(p + "wo"), x1, None, x, None, ss[2 * i + 1], eps, st) and ok
-            C.gemm_swiglu(x1, fg, act, ss[2 * i + 1], eps, st)
-            ok = C.gemm_decode(act, dec.w(p + "wd"), x, None, x1, None, ss[2 * i + 2], eps, st) and ok
-            if not ok:
-                raise RuntimeError("fused decode step: a GEMM shape is not served by the split-K kernel")
-        C.rmsnorm_fwd(x, dec.w("final_norm"), h, None, eps)
+            for r0, r1 in chunks:
+                x, x1, qkv, attn, act = (self.b_x[r0:r1], self.b_x1[r0:r1], self.b_qkv[r0:r1], self.b_attn[r0:r1], self.b_act[r0:r1])
+                bt, sl = self.block_tables[r0:r1], self.seq_lens[r0:r1]
+                s0, s1, s2 = ss[2 * i, r0:r1], ss[2 * i + 1, r0:r1], ss[2 * i + 2, r0:r1]
+                # up to 128 rows: rotary embedding and the KV-cache write happen in the qkv GEMM's epilogue
+                ok = (r1 - r0) <= 128 and C.gemm_decode_rope(x, fq, qkv, bq, s0, eps, cos_t, sin_t, bt, sl, self._kc(i), self._vc(i),
+                                                             cfg.num_attention_heads, cfg.num_key_value_heads, st)
+                if not ok:
+                    ok = C.gemm_decode(x, fq, qkv, bq, None, s0, None, eps, st)
+                    C.rope_kv_write_decode(qkv, cos_t, sin_t, bt, sl, self._kc(i), self._vc(i), cfg.num_attention_heads,
+                                           cfg.num_key_value_heads, cfg.head_dim, st)
+                C.paged_decode_attn(qkv, self._kc(i), self._vc(i), bt, sl, attn, cfg.num_attention_heads, cfg.num_key_value_heads,
+                                    cfg.head_dim, scale, splits, self.b_part_o, self.b_part_ml, st, self.b_tickets)
+                ok = C.gemm_decode(attn, dec.w(p + "wo"), x1, None, x, None, s1, eps, st) and ok
+                C.gemm_swiglu(x1, fg, act, s1, eps, st)
+                ok = C.gemm_decode(act, dec.w(p + "wd"), x, None, x1, None, s2, eps, st) and ok
+                if not ok:
+                    raise RuntimeError("fused decode step: a GEMM shape is not served by the split-K kernel")
+        h = self.b_h[:B]
+        C.rmsnorm_fwd(self.b_x[:B], dec.w("final_norm"), h, None, eps)
         wl = self.layout.view(self.params, self.layout.lm_head_name())
-        C.lm_sample(h, wl, temperature, self.step_seeds, self.b_sample_f, self.b_sample_i, self.b_tokens, None, st)
-        self.last_tokens[:B].copy_(self.b_tokens[:B])
-        self.history[self.row_ids[:B], torch.clamp(self.gen_index[:B], max=self.hist_cap - 1)] = self.b_tokens[:B]
-        self.gen_index[:B].add_(1)
+        C.lm_sample(h, wl, temperature, self.step_seeds, self.b_sample_f, self.b_sample_i, self.b_tokens, self.b_lp, st)
+        self._feed_back(B)
 
     def _decode_forward_mega(self, B: int, temperature: float, splits: int) -> None:
         """Embedding + statistics, ONE launch for all decoder layers, final norm, lm_head + sampling."""
@@ -427,16 +463,19 @@ class RolloutEngine:
         h = self.b_h[:B]
         C.rmsnorm_fwd(self.b_x[:B], dec.w("final_norm"), h, None, eps)
         wl = self.layout.view(self.params, self.layout.lm_head_name())
-        C.lm_sample(h, wl, temperature, self.step_seeds, self.b_sample_f, self.b_sample_i, self.b_tokens, None, st)
-        self.last_tokens[:B].copy_(self.b_tokens[:B])
-        self.history[self.row_ids[:B], torch.clamp(self.gen_index[:B], max=self.hist_cap - 1)] = self.b_tokens[:B]
-        self.gen_index[:B].add_(1)
+        C.lm_sample(h, wl, temperature, self.step_seeds, self.b_sample_f, self.b_sample_i, self.b_tokens, self.b_lp, st)
+        self._feed_back(B)
 
     def _launch_count_decode(self, splits: int, B: int = 0) -> int:
         if self.mega_rows and 0 < B <= self.mega_rows:
             return 1 + 1 + 3
         fused = self.fused_decode and 0 < B <= self.fused_rows
-        per_layer = (5 if B <= 128 else 6) if fused else 9
+        if fused:
+            n_chunks = (B + self.fused_chunk - 1) // self.fused_chunk
+            last = B - (n_chunks - 1) * self.fused_chunk
+            per_layer = (n_chunks - 1) * (5 if self.fused_chunk <= 128 else 6) + (5 if last <= 128 else 6)
+        else:
+            per_layer = 9
         return 1 + per_layer * self.cfg.num_hidden_layers + 3
 
     def _decode(self, plan: Dict[str, Any]) -> None:
@@ -470,15 +509,15 @@ class RolloutEngine:
         max_len = int(self.h_lens[:B].max())
         if self.mega_rows and B <= self.mega_rows:
             # the persistent layer kernel works on one attention item per CTA at a time: one wave of items
-            want = 148 // max(1, len(active) * self.cfg.num_key_value_heads)
+            want = self.sm_count // max(1, len(active) * self.cfg.num_key_value_heads)
         else:
-            want = (148 * 3) // max(1, len(active) * self.cfg.num_key_value_heads)
+            want = (self.sm_count * 3) // max(1, len(active) * self.cfg.num_key_value_heads)
         splits = int(max(1, min(self.max_splits, want, max(1, max_len // 256))))
         temperature = float(self.temperature or 0.0)
         t_mid = time.perf_counter()
         self.t_prep += t_mid - t_begin
         if self.use_cuda_graph:
-            key = (B, temperature, splits)
+            key = (B, temperature, splits, self.record_logprobs)
             g = self.graphs.get(key)
             if g is None:
                 # Warm up outside capture (sets function attributes, fills tensor-map caches), then put back what the
@@ -539,13 +578,18 @@ class RolloutEngine:
         width = max(d[2] for d in done_slots)
         rows = self.history[:, :width].index_select(0, idx).cpu().numpy()
         self.d2h_bytes += rows.nbytes
+        lp_rows = None
+        if self.record_logprobs:
+            lp_rows = self.history_lp[:, :width].index_select(0, idx).cpu().numpy()
+            self.d2h_bytes += lp_rows.nbytes
         for j, (slot, info, n_out, reason) in enumerate(done_slots):
             r = info["req"]
             ids = rows[j, :n_out].astype(np.int32).copy()
             if info["forced"] is not None:
                 ids[-1] = self.eos  # EOS forced at the drawn length
                 reason = "stop"
-            out.append(FinishedSequence(r.request_id, info["child"], ids, reason, len(r.prompt)))
+            out.append(FinishedSequence(r.request_id, info["child"], ids, reason, len(r.prompt),
+                                        lp_rows[j, :n_out].astype(np.float32).copy() if lp_rows is not None else None))
             self.sched.finish(info["seq_id"])
             self._free_slot(slot)
         return out
@@ -562,7 +606,10 @@ class RolloutEngine:
         to = np.asarray([m[1] for m in moves], dtype=np.int64)
         idx = torch.from_numpy(np.stack([frm, to])).pin_memory().to(self.dev, non_blocking=True)
         self.h2d_bytes += idx.numel() * 8
-        for t in (self.block_tables, self.last_tokens, self.gen_index, self.base_seeds, self.history):
+        moved = [self.block_tables, self.last_tokens, self.gen_index, self.base_seeds, self.history]
+        if self.record_logprobs:
+            moved.append(self.history_lp)
+        for t in moved:
             t.index_copy_(0, idx[1], t.index_select(0, idx[0]))
         self.launches += 10
         for a, empty in ((self.h_lens, 0), (self.h_gen, 0), (self.h_seq, -1), (self.h_limit, 1 << 60), (self.h_watch, False),
@@ -687,6 +734,7 @@ class OracleEngine:
     def _generate_group(self, r: _Request) -> List[FinishedSequence]:
         dev = self.params.device
         seqs = [list(map(int, r.prompt)) for _ in range(r.n)]
+        lps: List[List[float]] = [[] for _ in range(r.n)]
         done: List[Optional[str]] = [None] * r.n
         gens = [torch.Generator(device="cpu").manual_seed(_mix_seed(r.seed, c) & 0x7FFFFFFF) for c in range(r.n)]
         wl = self.layout.view(self.params, self.layout.lm_head_name())
@@ -705,9 +753,11 @@ class OracleEngine:
             for j, c in enumerate(live):
                 if r.temperature <= 0:
                     tok = int(z[j].argmax())
+                    lps[c].append(float(torch.log_softmax(z[j], -1)[tok]))
                 else:
                     p = torch.softmax(z[j] / r.temperature, -1).cpu()
                     tok = int(torch.multinomial(p, 1, generator=gens[c]))
+                    lps[c].append(float(torch.log(p[tok])))
                 seqs[c].append(tok)
                 self.tokens_generated += 1
                 n_new = len(seqs[c]) - len(r.prompt)
@@ -723,7 +773,7 @@ class OracleEngine:
             if r.forced_new_tokens:
                 ids[-1] = self.eos
                 reason = "stop"
-            out.append(FinishedSequence(r.request_id, c, ids, reason, len(r.prompt)))
+            out.append(FinishedSequence(r.request_id, c, ids, reason, len(r.prompt), np.asarray(lps[c], dtype=np.float32)))
         return out
 
     def step(self) -> List[FinishedSequence]:

@@ -165,6 +165,7 @@ class ExperienceManager:
         self.nonzero_reward = 0
         self.dropped_prompts = 0
         self.batch_start_time: Optional[float] = None
+        self.role_failures: List[str] = []  # roles that could not be reached at all (connection lost), this batch
 
     # ---- generation -------------------------------------------------------------------------
     def _thresholds(self) -> Tuple[int, int]:
@@ -201,6 +202,8 @@ class ExperienceManager:
                                                        max_tokens=self.config.max_generation_tokens)
         except Exception as e:  # generation failure: the prompt is skipped
             logger.error("generation failed: %r", e)
+            if isinstance(e, (ConnectionError, OSError)):
+                self.role_failures.append(f"generation: {e!r}")
             return None, None, None
         finally:
             await self._gen_lb.release(gen, 1)
@@ -227,6 +230,8 @@ class ExperienceManager:
         for r in results:
             if isinstance(r, Exception):
                 logger.error("logprob task failed: %r", r)
+                if isinstance(r, (ConnectionError, OSError)):
+                    self.role_failures.append(f"logprob: {r!r}")
             elif r:
                 valid.append(r)
         return valid, gen_metrics, {"gen_duration": gen_duration, "logprob_duration": time.time() - t1}

@@ -81,16 +81,54 @@ def _tune_interpreter_for_role_threads() -> None:
         sys.setswitchinterval(2e-4)
 
 
-def _role_streams(device: torch.device) -> Dict[str, Any]:
-    """One CUDA stream per role. When roles share a GPU the decode step's short, serially dependent kernels must not
+def _role_streams(device: torch.device, rollout_sms: int = 0) -> Dict[str, Any]:
+    """One CUDA stream per role. With ``rollout_sms`` > 0 the device's SMs are split into two disjoint groups (green
+    contexts): the rollout stream runs on the first, the trainer and logprob streams on the rest; the entries
+    ``rollout_sm_count`` / ``other_sm_count`` then give the group sizes that persistent kernels must respect.
+    Otherwise: When roles share a GPU the decode step's short, serially dependent kernels must not
     queue behind a trainer kernel that fills every SM, so the rollout stream gets the highest priority (its thread
     blocks are placed first whenever an SM frees up), the old-policy logprob stream the next, the trainer the lowest."""
     import os
 
+    if rollout_sms > 0:
+        from .utils import sm_partition
+
+        groups = sm_partition.split(device, rollout_sms)
+        if groups is not None:
+            g_roll, g_other = groups
+            return {"trainer": g_other.stream(0), "logprob": g_other.stream(-1), "rollout": g_roll.stream(-2),
+                    "rollout_sm_count": g_roll.sm_count, "other_sm_count": g_other.sm_count, "_groups": groups}
     if os.environ.get("AGRPO_STREAM_PRIORITIES", "1") == "0":
         return {k: torch.cuda.Stream(device) for k in ("trainer", "logprob", "rollout")}
     return {"trainer": torch.cuda.Stream(device, priority=0), "logprob": torch.cuda.Stream(device, priority=-1),
             "rollout": torch.cuda.Stream(device, priority=-2)}
+
+
+def preflight_placement(place: Dict[str, Sequence[int]], world: int, visible_gpus: Optional[int] = None,
+                        free_bytes: Optional[Sequence[int]] = None, need_bytes: int = 0) -> None:
+    """Fails fast, with the reason, when a placement cannot be honoured: before any rank allocates or enters a
+    collective. Counterpart of the reference's resource check ahead of placement-group creation (ray_utils.py:50-99):
+    roles named, ranks inside the job, one GPU per rank on this node, and (when given) enough free memory on each GPU."""
+    for role in ("trainer", "logprob", "rollout"):
+        ranks = list(place.get(role, []))
+        if not ranks:
+            raise ValueError(f"placement has no rank for role '{role}'")
+        if len(set(ranks)) != len(ranks):
+            raise ValueError(f"placement lists a rank twice for role '{role}': {ranks}")
+        bad = [r for r in ranks if r < 0 or r >= world]
+        if bad:
+            raise ValueError(f"placement puts role '{role}' on ranks {bad}, but the job has {world} rank(s) (0..{world - 1}); "
+                             f"start {max(max(rs) for rs in place.values()) + 1} processes or change the placement")
+    used = sorted({r for rs in place.values() for r in rs})
+    if visible_gpus is not None and visible_gpus < len(used):
+        raise ValueError(f"the placement needs {len(used)} GPUs (one per rank {used}) but only {visible_gpus} are visible "
+                         f"on this node (CUDA_VISIBLE_DEVICES?)")
+    if free_bytes is not None and need_bytes > 0:
+        short = [(i, f) for i, f in enumerate(free_bytes) if i in used and f < need_bytes]
+        if short:
+            raise ValueError("not enough free GPU memory for the placement: " +
+                             ", ".join(f"GPU {i} has {f / 2 ** 30:.1f} GiB free" for i, f in short) +
+                             f"; each rank needs about {need_bytes / 2 ** 30:.1f} GiB (is another job using these GPUs?)")
 
 
 class InProcessRuntime:
@@ -123,7 +161,7 @@ class InProcessRuntime:
             cfg_recompute = want_recompute(cfg, mcfg, act_budget)
             if cfg_recompute and cfg.activation_recompute == "auto":
                 cfg.activation_recompute = "full"
-            self.streams = _role_streams(self.device)
+            self.streams = _role_streams(self.device, cfg.colocated_rollout_sms)
             _tune_interpreter_for_role_threads()
         else:
             self.streams = {"trainer": None, "logprob": None, "rollout": None}
@@ -131,6 +169,7 @@ class InProcessRuntime:
         core = TrainerCore(cfg, mcfg, self.device, 0, 1, None, flat32, cfg.seed)
         # all three roles share this GPU: optionally keep some SMs free for the decode kernels
         lim = cfg.colocated_sm_limit if self.native else 0
+        lim = int(self.streams.get("other_sm_count", lim))  # an SM partition decides the count
         self.trainer = TrainerWorker(core, self.streams["trainer"], sm_limit=lim)
         self.layout = core.layout
         # logprob and rollout keep their own copies: they must hold the PREVIOUS policy while the trainer steps
@@ -155,7 +194,8 @@ class InProcessRuntime:
                                                     cfg.output_dir, name=f"verifier_pool_{id(self)}", timeout_s=cfg.verifier_timeout_s)
         self.tokenizer = load_tokenizer(cfg)
         self.logprob = LogProbWorker(cfg, mcfg, lp_dec, self.device, stream=self.streams["logprob"], sm_limit=lim)
-        self.generation = GenerationWorker(cfg, mcfg, engine, self.verifier, self.tokenizer, stream=self.streams["rollout"])
+        self.generation = GenerationWorker(cfg, mcfg, engine, self.verifier, self.tokenizer, stream=self.streams["rollout"],
+                                           sm_limit=int(self.streams.get("rollout_sm_count", 0)))
         if cfg.stream_logprobs:
             self.generation.logprob_fn = self.logprob.inference
         self.generation_controllers = [self.generation]
@@ -166,17 +206,12 @@ class InProcessRuntime:
 
     def _load_optimizer(self, path: str) -> None:
         core = self.trainer.core
-        st = ckpt.load_optimizer_shard(path, 0, 1, core.layout)
-        if st is not None:
-            core.master.copy_(st["master"])
-            core.exp_avg.copy_(st["exp_avg"])
-            core.exp_avg_sq.copy_(st["exp_avg_sq"])
-            core.params.copy_(core.master.to(core.compute_dtype))
-            sched = ckpt.load_scheduler_state(path)
-            if sched:
-                core.load_scheduler_state(sched)
+        if core.load_optimizer_checkpoint(path):
             self.logprob_params.copy_(core.params)
             self.rollout_params.copy_(core.params)
+            logger.info("optimizer state and schedule reloaded from %s (optimizer step %d)", path, core.opt_step)
+        else:
+            logger.warning("resume_from_path %s holds no optimizer state; starting with zero moments", path)
 
     async def start_trainers(self) -> None:
         self.trainer.set_orchestrator(self.experience_manager, 0)
@@ -391,11 +426,20 @@ class DistributedRuntime:
             self.device = torch.device("cpu")
         place = config.resolved_placement()
         self.place = place
+        free = None
+        if cuda:
+            f, _ = torch.cuda.mem_get_info(self.device)
+            free = [0] * self.world
+            free[self.rank] = int(f)
+        mcfg0 = resolve_model_config(config.model_name_or_path, config.model_config)
+        # parameters in bf16 plus (trainer ranks) fp32 master + moments + gradients of this rank's share: a floor, not a plan
+        need = mcfg0.num_parameters() * 2
+        preflight_placement(place, self.world, torch.cuda.device_count() if cuda else None,
+                            [free[r] if r == self.rank else need for r in range(self.world)] if free else None, need)
         self.trainer_ranks = list(place["trainer"])
         self.logprob_ranks = list(place["logprob"])
         self.rollout_ranks = list(place["rollout"])
         self.infer_ranks = sorted(set(self.logprob_ranks) | set(self.rollout_ranks))
-        assert max(self.trainer_ranks + self.infer_ranks) < self.world, "placement names a rank beyond the world size"
         self.is_trainer = self.rank in self.trainer_ranks
         self.trainer_index = self.trainer_ranks.index(self.rank) if self.is_trainer else None
         self.mcfg = resolve_model_config(config.model_name_or_path, config.model_config)
@@ -440,14 +484,15 @@ class DistributedRuntime:
         self.engine = None
         self.experience_manager: Optional[ExperienceManager] = ExperienceManager(config) if self.rank == 0 else None
         _tune_interpreter_for_role_threads()
-        self.streams = (_role_streams(self.device) if self.native
+        shares_gpu = self.rank in self.rollout_ranks and (self.is_trainer or self.rank in self.logprob_ranks)
+        self.streams = (_role_streams(self.device, config.colocated_rollout_sms if shares_gpu else 0) if self.native
                         else {"trainer": None, "logprob": None, "rollout": None})
+        other_lim = int(self.streams.get("other_sm_count", config.colocated_sm_limit if shares_gpu else 0))
         flat32 = initial_weights(config, self.mcfg, self.layout, self.device if self.native else None)
         if self.is_trainer:
             core = TrainerCore(config, self.mcfg, self.device, self.trainer_index, t, self.trainer_group, flat32, config.seed,
                                comm=self.trainer_comm)
-            self.trainer = TrainerWorker(core, self.streams["trainer"],
-                                         sm_limit=config.colocated_sm_limit if (self.native and self.rank in self.rollout_ranks) else 0)
+            self.trainer = TrainerWorker(core, self.streams["trainer"], sm_limit=other_lim if self.native else 0)
         if self.rank in self.infer_ranks:
             dtype = torch.bfloat16 if self.native else torch.float32
             if self.weight_sync is not None:
@@ -461,7 +506,7 @@ class DistributedRuntime:
         if self.rank in self.logprob_ranks:
             dec = (NativeDecoder if self.native else OracleDecoder)(self.mcfg, self.layout, self.infer_params)
             self.logprob = LogProbWorker(config, self.mcfg, dec, self.device, stream=self.streams["logprob"],
-                                         sm_limit=config.colocated_sm_limit if (self.native and self.rank in self.rollout_ranks) else 0)
+                                         sm_limit=other_lim if self.native else 0)
         if self.rank in self.rollout_ranks:
             self.verifier = get_or_create_verifier_pool(config.global_num_verifiers, config.write_failed_generation_samples,
                                                         config.reward_fns, config.output_dir, name=f"verifier_pool_{self.rank}",
@@ -481,7 +526,7 @@ class DistributedRuntime:
                 self.engine = OracleEngine(self.mcfg, self.layout, self.infer_params, max_seqs=config.max_num_seqs,
                                            max_model_len=min(self.mcfg.max_position_embeddings, config.max_generation_tokens + 2048))
             self.generation = GenerationWorker(config, self.mcfg, self.engine, self.verifier, load_tokenizer(config),
-                                               stream=self.streams["rollout"])
+                                               stream=self.streams["rollout"], sm_limit=int(self.streams.get("rollout_sm_count", 0)))
             if config.stream_logprobs:
                 self.generation.logprob_fn = self._stream_logprob
         self._lp_next = 0
@@ -496,7 +541,38 @@ class DistributedRuntime:
         self._walls: Dict[str, float] = {}
         self.generation_controllers: List[Any] = []
         self.logprob_controllers: List[Any] = []
+        if config.resume_from_path:
+            self._resume_optimizer(config.resume_from_path)
         dist.barrier()
+
+    def _resume_optimizer(self, path: str) -> None:
+        """Every rank calls this during construction. Trainer ranks reload their optimizer shard (re-sharded when the
+        checkpoint was written by another trainer count) and rebuild their parameters from the masters; the first weight
+        push then carries them to the inference ranks, which until then take a copy through the trainer group's
+        leader so that generation never starts from the initial weights."""
+        loaded = False
+        if self.is_trainer:
+            loaded = self.trainer.core.load_optimizer_checkpoint(path)
+            if self.rank == self.trainer_ranks[0]:
+                (logger.info if loaded else logger.warning)(
+                    "resume_from_path %s: %s", path, "optimizer state and schedule reloaded" if loaded
+                    else "no optimizer state found; starting with zero moments")
+        flag = torch.tensor([1 if loaded else 0], device=self.device)
+        self.dist.broadcast(flag, src=self.trainer_ranks[0])
+        if not bool(int(flag.item())):
+            return
+        # inference copies: one broadcast of the full parameters from the first trainer rank (start-up only)
+        core = self.trainer.core if self.is_trainer else None
+        dtype = torch.bfloat16 if self.native else torch.float32
+        if core is not None and not core.zero3:
+            full = core.params.to(dtype)
+        elif core is not None:
+            full = core._gather_full_master().to(dtype)
+        else:
+            full = torch.empty(self.layout.total, dtype=dtype, device=self.device)
+        self.dist.broadcast(full, src=self.trainer_ranks[0])
+        if self.infer_params is not None:
+            self.infer_params.copy_(full)
 
     # ------------------------------------------------------------------ servers / clients
     def _store(self):

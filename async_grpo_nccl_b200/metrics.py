@@ -105,3 +105,25 @@ def aggregate_completions(completions: Sequence[Dict[str, Any]]) -> Dict[str, fl
     out["training/batch_avg_reward"] = sum(float(b.get("total_reward", 0.0)) for b in bm) / n_s if n_s else 0.0
     out["training/optimizer_steps_in_batch"] = max([float(c.get("optimizer_steps_in_batch", 0)) for c in completions] or [0.0])
     return out
+
+
+def system_metrics() -> Dict[str, float]:
+    """GPU memory, utilisation, power and SM clock of every visible GPU (read-only NVML queries) as ``system/*`` series.
+    Empty when NVML is not available. Stands in for the collector behind the reference's ``enable_manual_system_metrics``
+    key (orchestrator.py:168-169)."""
+    out: Dict[str, float] = {}
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        for i in range(pynvml.nvmlDeviceGetCount()):
+            h = pynvml.nvmlDeviceGetHandleByIndex(i)
+            mem = pynvml.nvmlDeviceGetMemoryInfo(h)
+            util = pynvml.nvmlDeviceGetUtilizationRates(h)
+            out[f"system/gpu{i}_mem_used_gb"] = mem.used / 2 ** 30
+            out[f"system/gpu{i}_util_pct"] = float(util.gpu)
+            out[f"system/gpu{i}_power_w"] = pynvml.nvmlDeviceGetPowerUsage(h) / 1000.0
+            out[f"system/gpu{i}_sm_mhz"] = float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+    except Exception:
+        return {}
+    return out

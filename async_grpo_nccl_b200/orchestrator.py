@@ -29,6 +29,8 @@ from . import checkpoint as ckpt
 from .config import GRPOConfig, make_config
 from .metrics import MetricLogger, aggregate_completions
 
+from .protocol import RoleLostError
+
 logger = logging.getLogger(__name__)
 
 
@@ -173,7 +175,9 @@ class Orchestrator:
                 except asyncio.TimeoutError:
                     alive = await rt.ping_trainers()
                     if not all(alive):
-                        raise RuntimeError(f"trainer ranks not responding: {[r for r, a in zip(rt.trainer_ranks, alive) if not a]}")
+                        self._save_training_state()
+                        raise RoleLostError(f"trainer ranks not responding: {[r for r, a in zip(rt.trainer_ranks, alive) if not a]}; "
+                                            f"training state saved, restart with resume_state")
                     logger.warning("still waiting for trainer rank %s (all ranks alive)", rank)
             if isinstance(c, dict) and c.get("error"):
                 raise RuntimeError(f"trainer rank {c.get('gpu_rank')} failed: {c['error']}")
@@ -187,6 +191,13 @@ class Orchestrator:
         await _maybe(em.generate_experience(list(batch), rt.generation_controllers, rt.logprob_controllers))
         em.start_creating_batches()
         completions = await self._wait_completions()
+        lost = list(getattr(em, "role_failures", []))
+        if lost:
+            # a role process is gone: nothing of this macro-batch is committed (no weight sync with a dead rank, which
+            # would block every collective); the counters of the last completed macro-batch are what a restart resumes from
+            self._save_training_state()
+            raise RoleLostError(f"{len(lost)} request(s) failed because a role process is unreachable ({lost[0]}); "
+                                f"training state saved at macro-batch {self.macro_batch_count}, restart with resume_state")
         t_trained = time.time()
         agg = aggregate_completions(completions)
         n_samples = int(agg.get("training/batch_total_samples", 0))
@@ -228,6 +239,10 @@ class Orchestrator:
         for k, v in exp.items():
             if isinstance(v, (int, float)):
                 rec[f"reward/{k}"] = float(v)
+        if cfg.enable_manual_system_metrics:
+            from .metrics import system_metrics
+
+            rec.update(system_metrics())
         self.metrics.log(rec, step=self.global_step)
         for c in completions[:1]:
             for i, s in enumerate(c.get("minibatch_summaries", [])):

@@ -77,3 +77,9 @@ def build_sample(row: Dict[str, Any], prompt_ids: np.ndarray, output_ids: np.nda
 
 def sample_token_count(sample: Dict[str, Any]) -> int:
     return int(sample.get("input_len", 0)) + int(sample.get("output_len", 0))
+
+
+class RoleLostError(RuntimeError):
+    """A role process (trainer, logprob or rollout rank) stopped answering. Raised by the orchestrator after it has
+    written ``training_state.json``; the run is restarted with ``resume_state`` / ``resume_from_path`` (the reference's
+    recovery path as well: it has no elastic restart, orchestrator.py:921-956)."""

@@ -31,10 +31,11 @@ def _uid_seed(uid: Any, base: int) -> int:
 
 class GenerationWorker:
     def __init__(self, config: Any, model_cfg: Any, engine: Any, verifier_pool: Any, tokenizer: Any = None,
-                 stream: Optional[torch.cuda.Stream] = None):
+                 stream: Optional[torch.cuda.Stream] = None, sm_limit: int = 0):
         self.config, self.mcfg, self.engine, self.verifier = config, model_cfg, engine, verifier_pool
         self.tokenizer = tokenizer
         self.stream = stream
+        self.sm_limit = int(sm_limit)  # > 0: the stream runs on an SM group of this size (persistent grids must fit it)
         self._lock = threading.Lock()
         self._incoming: List[Tuple[Any, ...]] = []
         self._futures: Dict[Any, Tuple[Any, ...]] = {}  # request id -> (loop, future, n, finished children, on_child)
@@ -44,6 +45,8 @@ class GenerationWorker:
         # generation phase instead of piling up behind it. The weights it uses are the same either way (they only
         # change at a weight sync, when generation is paused).
         self.logprob_fn: Optional[Any] = None
+        self._want_logprobs = False
+        self._req_counter = 0
         self._wake = threading.Event()
         self._stop = False
         self._paused = threading.Event()
@@ -61,11 +64,25 @@ class GenerationWorker:
 
     # ------------------------------------------------------------------ engine thread
     def _engine_loop(self) -> None:
+        try:
+            self._engine_loop_body()
+        except BaseException as e:  # a dead engine thread must not leave requests waiting for their timeout
+            logger.exception("rollout engine thread stopped: %r", e)
+            self._dead = e
+            self._fail_all(e if isinstance(e, Exception) else RuntimeError(repr(e)))
+
+    def _engine_loop_body(self) -> None:
         ctx = torch.cuda.stream(self.stream) if self.stream is not None else _null()
+        if self.sm_limit > 0 and hasattr(self.engine, "C"):
+            self.engine.C.set_sm_limit(self.sm_limit)  # thread-local: the engine thread only
+            self.engine.sm_count = self.sm_limit
         with ctx:
             while not self._stop:
                 with self._lock:
                     new, self._incoming = self._incoming, []
+                if self._want_logprobs and hasattr(self.engine, "enable_logprobs"):
+                    self.engine.enable_logprobs()  # on the engine's own thread, between steps
+                    self._want_logprobs = False
                 for args in new:
                     self.engine.add_request(*args[0], **args[1])
                 with self._gate:
@@ -81,6 +98,10 @@ class GenerationWorker:
                 t0 = time.time()
                 try:
                     finished = self.engine.step()
+                    # the kernels' status word (bounded waits, index checks): read whenever sequences finish (the step
+                    # synchronised anyway), or after every step with kernel_checks
+                    if finished or getattr(self.config, "kernel_checks", False):
+                        self.engine.check_status()
                 except Exception as e:  # fail every waiter instead of hanging them
                     self._fail_all(e)
                     continue
@@ -109,6 +130,8 @@ class GenerationWorker:
                         forced: Optional[Sequence[int]] = None, ignore_eos: bool = False, on_child: Any = None) -> List[Any]:
         loop = asyncio.get_running_loop()
         fut: asyncio.Future = loop.create_future()
+        if getattr(self, "_dead", None) is not None:
+            raise RuntimeError(f"rollout engine thread has stopped: {self._dead!r}")
         with self._lock:
             self._req_counter += 1
             rid = self._req_counter
@@ -222,11 +245,14 @@ class GenerationWorker:
 
     async def generate_with_logprobs(self, prompt_ids: Sequence[int], max_tokens: int = 32, temperature: float = 1.0,
                                      seed: int = 0) -> Dict[str, Any]:
-        """Probe: sampled token ids so that trainer / logprob-worker values can be compared with the engine's
-        (vllm_worker.py:286-392)."""
+        """Probe: sampled token ids with the engine's own log-probability of each (under the sampling temperature), so
+        that trainer / logprob-worker values can be compared with the engine's numerics (vllm_worker.py:286-392). The
+        first call switches the engine to recording log-probabilities."""
         ids = np.asarray(prompt_ids, dtype=np.int32)
+        self._want_logprobs = not getattr(self.engine, "record_logprobs", False)
         fin = await self._generate(ids, 1, self.get_max_tokens(len(ids), max_tokens), float(temperature), int(seed))
-        return {"output_token_ids": fin[0].output_ids, "finish_reason": fin[0].finish_reason}
+        return {"input_token_ids": ids, "output_token_ids": fin[0].output_ids, "output_logprobs": fin[0].output_logprobs,
+                "finish_reason": fin[0].finish_reason}
 
     # ------------------------------------------------------------------ weight sync (receiver side)
     async def pause_for_sync(self) -> bool:

@@ -38,11 +38,13 @@ from ..packing import PackedBatch, make_dummy_batch, pack_samples
 
 
 def lr_factor(step: int, warmup: int, total: int, kind: str) -> float:
-    """Linear warm-up, then constant or cosine decay (gpu_process_worker.py:734-741)."""
+    """Learning-rate factor of optimizer step ``step`` (0-based): the reference's ``LambdaLR`` lambda, term for term
+    (gpu_process_worker.py:734-741). Linear warm-up from 0 (its first step has learning rate 0 when warm-up is on), then
+    constant, or cosine over ``total`` steps when ``total > 0`` (not clamped past ``total``, as in the reference)."""
     if warmup > 0 and step < warmup:
-        return float(step + 1) / float(warmup)
-    if kind == "cosine" and total > warmup:
-        prog = min(1.0, float(step - warmup) / float(max(1, total - warmup)))
+        return float(step) / float(max(1, warmup))
+    if kind == "cosine" and total > 0:
+        prog = float(step - warmup) / float(max(1, total - warmup))
         return 0.5 * (1.0 + math.cos(math.pi * prog))
     return 1.0
 
@@ -145,6 +147,8 @@ class TrainerCore:
         loss_scale = float(n_real) / float(self.cfg.train_minibatch_sample_size)
         if self.native:
             stats = self.decoder.forward_backward(batch, self.loss_cfg, loss_scale, self.sink)
+            if self.cfg.kernel_checks:
+                self.decoder.check_status()  # one synchronisation per microbatch: a failed kernel is named right away
         else:
             loss, stats = self.decoder.loss(batch, self.loss_cfg, loss_scale)
             if n_real > 0 and batch.total_out > 0:
@@ -367,8 +371,55 @@ class TrainerCore:
                 "lr_warmup_steps": self.cfg.lr_warmup_steps, "total_steps": self.cfg.total_steps()}
 
     def load_scheduler_state(self, st: Dict[str, Any]) -> None:
+        """Restores the position in the schedule. The base learning rate stays the one of the current configuration: a
+        run resumed with another ``learning_rate`` uses it from its first step on."""
         self.opt_step = int(st.get("opt_step", 0))
-        self.base_lr = float(st.get("base_lr", self.base_lr))
+
+    def _gather_full_master(self) -> torch.Tensor:
+        """Full fp32 parameters on EVERY rank (collective over the trainer group when world > 1)."""
+        if self.world == 1:
+            return self.master
+        import torch.distributed as dist
+
+        full = torch.empty(self.layout.total, dtype=torch.float32, device=self.device)
+        for u, (lo, gs, ln) in enumerate(self.shard_map):
+            s, e = self.layout.unit_ranges[u]
+            dist.all_gather_into_tensor(full[s:e], self.master[lo:lo + ln].contiguous(), group=self.group)
+        return full
+
+    def load_optimizer_checkpoint(self, path: str) -> bool:
+        """Reloads this rank's fp32 master shard, Adam moments and the schedule position from a checkpoint directory
+        (re-sharded when it was written by another number of trainer ranks) and rebuilds the compute copy from the
+        masters; collective over the trainer group. What the reference does on resume (orchestrator.py:503-509 ->
+        gpu_process_worker.py:1160-1223). Returns False when the directory holds no optimizer state."""
+        from .. import checkpoint as ckpt
+
+        st = ckpt.load_optimizer_shard(path, self.rank, self.world, self.layout)
+        found = st is not None
+        if self.world > 1:
+            import torch.distributed as dist
+
+            flag = torch.tensor([1 if found else 0], device=self.device if self.native else "cpu")
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+            found = bool(int(flag.item()))
+        if not found:
+            return False
+        self.master.copy_(st["master"])
+        self.exp_avg.copy_(st["exp_avg"])
+        self.exp_avg_sq.copy_(st["exp_avg_sq"])
+        sched = ckpt.load_scheduler_state(path)
+        if sched:
+            self.load_scheduler_state(sched)
+        if self.zero3:
+            self.comm.shard16.copy_(self.master)
+            self.comm.publish_initial()
+            return True
+        full = self._gather_full_master()
+        self.params.copy_(full.to(self.device, dtype=self.compute_dtype))
+        if not self.native:
+            with torch.no_grad():
+                self._oracle_params.copy_(self.params)
+        return True
 
     def load_master_from_full(self, full_fp32: torch.Tensor) -> None:
         for lo, gs, ln in self.shard_map:

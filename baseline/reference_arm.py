@@ -81,15 +81,29 @@ class RefConfig:
 
 # ------------------------------------------------------------------------------------------------ control plane
 class Mail:
-    """Mailboxes on a TCP key-value store: ``post(box, obj)`` / ``take(box)`` in posting order per box."""
+    """Mailboxes on a TCP key-value store: ``post(box, obj)`` / ``take(box)`` in posting order per box. Payloads above
+    1 MB (sample lists of a whole microbatch) travel as a file in a spool directory of this node and only the file name
+    goes through the store, the way Ray keeps large arguments in its object store and sends references."""
 
-    def __init__(self, store):
+    BIG = 1 << 20
+
+    def __init__(self, store, spool: Optional[str] = None):
         self.store = store
         self.next: Dict[str, int] = {}
+        self.spool = spool
+        if spool:
+            os.makedirs(spool, exist_ok=True)
 
     def post(self, box: str, obj: Any) -> None:
         idx = self.store.add(f"{box}/n", 1)
-        self.store.set(f"{box}/{idx}", pickle.dumps(obj, protocol=pickle.HIGHEST_PROTOCOL))
+        data = pickle.dumps(obj, protocol=pickle.HIGHEST_PROTOCOL)
+        if self.spool and len(data) > self.BIG:
+            path = os.path.join(self.spool, f"{box.replace('/', '_')}_{idx}.pkl")
+            with open(path + ".tmp", "wb") as f:
+                f.write(data)
+            os.replace(path + ".tmp", path)
+            data = b"FILE:" + path.encode()
+        self.store.set(f"{box}/{idx}", data)
 
     def ready(self, box: str) -> bool:
         nxt = self.next.get(box, 1)
@@ -101,6 +115,11 @@ class Mail:
         data = self.store.get(key)
         self.store.delete_key(key)
         self.next[box] = nxt + 1
+        if data[:5] == b"FILE:":
+            path = data[5:].decode()
+            with open(path, "rb") as f:
+                data = f.read()
+            os.remove(path)
         return pickle.loads(data)
 
     def barrier(self, name: str, world: int) -> None:
@@ -401,7 +420,7 @@ def _run(args, rank: int, n: int, host: str, port: int) -> Optional[Dict[str, An
     is_t, is_l, is_r = rank in T, rank in L, rank in R
     store = dist.TCPStore(host, port + 21, world_size=n, is_master=(rank == 0), timeout=timedelta(seconds=3600),
                           wait_for_workers=False)
-    mail = Mail(store)
+    mail = Mail(store, spool=os.path.join(os.environ.get("TMPDIR", "/tmp"), f"agrpo_ref_mail_{port}"))
     torch.cuda.set_device(0)
 
     # ---- model directory (rank 0 writes it; same random-init weights for every role) ----

@@ -45,12 +45,15 @@ def parse_args():
     ap.add_argument("--prompt-min", type=int, default=64)
     ap.add_argument("--prompt-max", type=int, default=512)
     ap.add_argument("--max-tokens-per-gpu", type=int, default=32768)
-    ap.add_argument("--max-num-seqs", type=int, default=256)
+    ap.add_argument("--max-num-seqs", type=int, default=512)
     ap.add_argument("--preset", default="throughput", choices=["eager", "throughput"])
     ap.add_argument("--param-sharding", default="zero2", choices=["zero2", "zero3"],
                     help="zero3: fully sharded trainers (all-gather / reduce-scatter fused into the GEMM kernels)")
     ap.add_argument("--colocated-sm-limit", type=int, default=0,
                     help="SMs that trainer / logprob GEMMs may fill on a GPU shared with a rollout engine (0 = all)")
+    ap.add_argument("--colocated-rollout-sms", type=int, default=None,
+                    help="SMs that the rollout engine gets for itself on a GPU it shares with other roles (0 = no partition; "
+                         "default: 96 where roles share a GPU)")
     ap.add_argument("--placement", default=None, help='JSON role placement overriding the default, e.g. '
                     '\'{"trainer": [0, 1], "logprob": [0], "rollout": [1]}\'')
     # reference arm only (its own defaults: orchestrator.py:137, 158 of the reference)
@@ -162,6 +165,7 @@ def main() -> None:
     place = json.loads(args.placement) if args.placement else placement_for(n)
     cfg = make_config({
         "param_sharding": args.param_sharding, "colocated_sm_limit": args.colocated_sm_limit,
+        "colocated_rollout_sms": (args.colocated_rollout_sms if args.colocated_rollout_sms is not None else (96 if n == 1 else 0)),
         "model_name_or_path": args.model, "batch_size": prompts_per_step, "samples_per_question": spq, "num_epochs": 1,
         "train_minibatch_sample_size": prompts_per_step * spq, "max_generation_tokens": args.gen_max,
         "max_tokens_per_gpu": args.max_tokens_per_gpu, "reward_fns": ["bernoulli"], "global_num_verifiers": 0,
@@ -258,7 +262,8 @@ def run_timed(cfg, runtime, rows, args, n, rank, dist, mcfg):
                    "parallelism": par, "max_tokens_per_microbatch": cfg.max_tokens_per_gpu,
                    "l2": "working set (3.1 GB of weights, multi-GB KV cache and activations per step) is far larger than the 126 MB L2; no flush needed",
                    "engine_preset": cfg.vllm_engine_preset, "max_num_seqs": cfg.max_num_seqs,
-                   "eager_microbatch_dispatch": bool(cfg.eager_microbatch_dispatch), "param_sharding": cfg.param_sharding},
+                   "eager_microbatch_dispatch": bool(cfg.eager_microbatch_dispatch), "param_sharding": cfg.param_sharding,
+                   "colocated_rollout_sms": cfg.colocated_rollout_sms},
         "clocks": state["clocks"],
         "e2e": {"value": samples / state["wall"], "unit": "samples/s",
                 "h2d_bytes_per_step": diff.get("h2d_bytes", 0.0) / args.steps, "d2h_bytes_per_step": diff.get("d2h_bytes", 0.0) / args.steps,

@@ -293,3 +293,78 @@ def test_engine_slot_compaction_does_not_change_tokens(monkeypatch):
             got, n = run(True, graph, use_forced)
             assert n > 0, "the workload must trigger at least one compaction"
             assert got == base
+
+
+def test_engine_logprobs_agree_with_the_logprob_path():
+    """The engine's chosen-token log-probabilities (the probe of vllm_worker.py:286-392) against the values the logprob
+    role computes for the same tokens with the training-side kernels: same weights, same temperature."""
+    from async_grpo_nccl_b200.engine.engine import RolloutEngine
+    from async_grpo_nccl_b200.models.config import PRESETS
+    from async_grpo_nccl_b200.models.decoder import NativeDecoder
+    from async_grpo_nccl_b200.models.layout import ParamLayout
+    from async_grpo_nccl_b200.packing import pack_for_logprob
+
+    cfg = PRESETS["tiny128"]
+    layout = ParamLayout(cfg)
+    p32 = torch.empty(layout.total)
+    layout.init_random_(p32, 0)
+    p16 = (p32 * 3.0).to(torch.bfloat16).to(DEV)
+    temp = 0.8
+    rng = np.random.default_rng(1)
+    prompts = [rng.integers(2, cfg.vocab_size, int(rng.integers(5, 40))).astype(np.int32) for _ in range(5)]
+    for graph in (False, True):
+        eng = RolloutEngine(cfg, layout, p16, max_seqs=64, max_model_len=512, num_blocks=512, use_cuda_graph=graph)
+        eng.enable_logprobs()
+        for i, pr in enumerate(prompts):
+            eng.add_request(i, pr, n=2, max_new_tokens=30, temperature=temp, seed=10 + i, ignore_eos=True)
+        outs = eng.run_until_done()
+        eng.check_status()
+        dec = NativeDecoder(cfg, layout, p16)
+        for o in outs:
+            assert o.output_logprobs is not None and len(o.output_logprobs) == len(o.output_ids) == 30
+            pr = prompts[o.request_id]
+            full = np.concatenate([pr, o.output_ids])
+            pb = pack_for_logprob([{"sample_ids": full, "input_len": len(pr), "output_len": len(o.output_ids)}], pin=False).to_device(DEV)
+            with torch.no_grad():
+                logp, _ = dec.logprobs(pb, temp)
+            want = logp.float().cpu().numpy()[len(pr) - 1: len(pr) - 1 + len(o.output_ids)]  # position p-1 holds token p
+            assert np.all(o.output_logprobs <= 1e-4)
+            assert np.abs(o.output_logprobs - want).max() < 0.08, np.abs(o.output_logprobs - want).max()
+
+
+def test_engine_batches_above_256_rows_run_in_row_chunks():
+    """More than 256 running sequences: the fused decode path processes the rows in chunks of 256 per layer. Every greedy
+    token must still be the (bf16-noise tolerant) argmax of the teacher-forced prefill logits."""
+    from async_grpo_nccl_b200.engine.engine import RolloutEngine
+    from async_grpo_nccl_b200.models.config import PRESETS
+    from async_grpo_nccl_b200.models.decoder import NativeDecoder
+    from async_grpo_nccl_b200.models.layout import ParamLayout
+    from async_grpo_nccl_b200.packing import pack_samples
+
+    cfg = PRESETS["tiny128"]
+    layout = ParamLayout(cfg)
+    p32 = torch.empty(layout.total)
+    layout.init_random_(p32, 0)
+    p16 = (p32 * 3.0).to(torch.bfloat16).to(DEV)
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(2, cfg.vocab_size, int(rng.integers(4, 30))).astype(np.int32) for _ in range(150)]
+    eng = RolloutEngine(cfg, layout, p16, max_seqs=320, max_model_len=128, num_blocks=2600, use_cuda_graph=True)
+    for i, pr in enumerate(prompts):
+        eng.add_request(i, pr, n=2, max_new_tokens=10, temperature=0.0, seed=i, ignore_eos=True)
+    outs = eng.run_until_done()
+    eng.check_status()
+    assert len(outs) == 300 and eng.sched.num_free_blocks == 2600
+    assert eng.fused_decode and eng.fused_rows == 320 and eng.fused_chunk == 256
+    nat = NativeDecoder(cfg, layout, p16)
+    wl = layout.view(p16.float(), layout.lm_head_name())
+    for o in outs[::7]:
+        pr = prompts[o.request_id]
+        full = np.concatenate([pr, o.output_ids])
+        pb = pack_samples([{"sample_ids": full, "input_len": len(pr), "output_len": len(o.output_ids)}], pin=False).to_device(DEV)
+        with torch.no_grad():
+            hn, _, _ = nat.hidden(pb)
+            z = hn.float() @ wl.t()
+        for j, tok in enumerate(o.output_ids):
+            row = z[len(pr) - 1 + j]
+            top = row.max().item()
+            assert row[int(tok)].item() >= top - (0.03 * abs(top) + 0.05), (o.request_id, j)

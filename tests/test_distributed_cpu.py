@@ -133,3 +133,116 @@ def test_rollout_rank_streams_logprob_requests_to_another_rank(tmp_path):
     last = out["last"]
     assert last["training/optimizer_steps_in_batch"] == 1
     assert np.isfinite(last["training/avg_loss"]) and last["training/grad_norm"] > 0
+
+
+def _save_rank(rank, world, port, path, q):
+    import os
+
+    import torch
+    import torch.distributed as dist
+
+    from async_grpo_nccl_b200 import checkpoint as ckpt
+    from async_grpo_nccl_b200.config import make_config
+    from async_grpo_nccl_b200.models.config import PRESETS
+    from async_grpo_nccl_b200.models.layout import ParamLayout
+    from async_grpo_nccl_b200.roles.trainer import TrainerCore
+
+    os.environ.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)})
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        mcfg = PRESETS["tiny"]
+        cfg = make_config({"model_name_or_path": "tiny", "train_minibatch_sample_size": 8, "learning_rate": 1e-3,
+                           "global_num_verifiers": 0, "lr_warmup_steps": 2})
+        layout = ParamLayout(mcfg, shard_world=world)
+        flat = torch.empty(layout.total)
+        layout.init_random_(flat, 0)
+        core = TrainerCore(cfg, mcfg, torch.device("cpu"), rank, world, dist.group.WORLD, flat.clone())
+        for step in range(3):
+            core.compute_gradients(_samples(mcfg.vocab_size, 8, 10 + step)[rank * 4:(rank + 1) * 4])
+            core.apply_gradients()
+        ckpt.save_optimizer_shard(path, rank, world, layout, core.optimizer_state(), core.scheduler_state())
+        full = core.full_master_fp32()
+        if rank == 0:
+            q.put(("ok", full.numpy()))
+    except Exception as e:
+        if rank == 0:
+            q.put(("FAILED", repr(e)))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(600)
+def test_optimizer_state_written_by_two_ranks_resumes_on_one(tmp_path):
+    """Resume with another trainer count: shards saved by 2 ranks are re-cut for 1 rank; master weights, both Adam moments
+    and the schedule position come back, the compute copy is rebuilt from the masters, and the next step continues from them."""
+    import torch
+    import torch.multiprocessing as mp
+
+    from async_grpo_nccl_b200 import checkpoint as ckpt
+    from async_grpo_nccl_b200.config import make_config
+    from async_grpo_nccl_b200.models.config import PRESETS
+    from async_grpo_nccl_b200.models.layout import ParamLayout
+    from async_grpo_nccl_b200.roles.trainer import TrainerCore
+
+    path = str(tmp_path / "ck")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_save_rank, args=(r, 2, 29747, path, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    status, full2 = q.get(timeout=500)
+    for p in procs:
+        p.join(timeout=60)
+    assert status == "ok", full2
+    mcfg = PRESETS["tiny"]
+    cfg = make_config({"model_name_or_path": "tiny", "train_minibatch_sample_size": 8, "learning_rate": 5e-4,
+                       "global_num_verifiers": 0, "lr_warmup_steps": 2})
+    one = TrainerCore(cfg, mcfg, torch.device("cpu"))
+    before = one.master.clone()
+    assert one.load_optimizer_checkpoint(path)
+    assert not torch.equal(before, one.master)
+    l1, l2 = one.layout, ParamLayout(mcfg, shard_world=2)
+    f2 = torch.from_numpy(full2)
+    for name in l1.segments:
+        assert torch.equal(l1.view(one.master, name), l2.view(f2, name)), name
+        assert torch.equal(l1.view(one.params, name), l1.view(one.master, name).to(one.params.dtype)), name
+    assert one.opt_step == 3 and one.exp_avg.abs().sum() > 0 and one.exp_avg_sq.abs().sum() > 0
+    assert one.base_lr == 5e-4, "the resumed run's own learning rate applies"
+    # moments agree with the shards on disk, segment by segment
+    saved = [ckpt.load_optimizer_shard(path, r, 2, l2) for r in range(2)]
+    full_m = torch.zeros(l2.total)
+    for r in range(2):
+        for lo, gs, ln in l2.local_to_global_ranges(r):
+            full_m[gs:gs + ln] = saved[r]["exp_avg"][lo:lo + ln]
+    for name in l1.segments:
+        assert torch.equal(l1.view(one.exp_avg, name), l2.view(full_m, name)), name
+    one.compute_gradients(_samples(mcfg.vocab_size, 8, 99))
+    s = one.apply_gradients()
+    assert s["optimizer_step"] == 4 and s["lr"] == 5e-4
+    assert not one.load_optimizer_checkpoint(str(tmp_path / "nothing_here"))
+
+
+@pytest.mark.timeout(600)
+def test_multi_process_runtime_reloads_optimizer_state_on_resume(tmp_path):
+    """Run, checkpoint, then start again with ``resume_from_path`` and a different trainer count: the trainer ranks
+    reload (and re-shard) the optimizer state inside ``DistributedRuntime`` and the run carries on."""
+    from async_grpo_nccl_b200 import checkpoint as ckpt
+
+    base = dict(model_name_or_path="tiny", batch_size=4, samples_per_question=4, num_epochs=1, train_minibatch_sample_size=8,
+                max_generation_tokens=8, max_tokens_per_gpu=200, reward_fns=["token_match"], global_num_verifiers=0,
+                num_logprob_gpu_workers=1, num_generation_gpu_workers=1, learning_rate=1e-3, output_dir=str(tmp_path),
+                eval_at_start=False)
+    rows = synthetic_prompt_rows(8, 1024, 16, 32, seed=0)
+    first = dict(base, num_training_gpu_workers=2, placement={"trainer": [0, 1], "logprob": [2], "rollout": [2]},
+                 min_samples_per_checkpoint=16)
+    out = spawn(first, rows, world=3, max_macro_batches=1, port=29759, timeout_s=500)
+    assert out["global_step"] == 1
+    path = ckpt.latest_checkpoint(str(tmp_path))
+    assert path is not None and ckpt.load_scheduler_state(path)["opt_step"] == 2
+    second = dict(base, num_training_gpu_workers=1, placement={"trainer": [0], "logprob": [1], "rollout": [1]},
+                  min_samples_per_checkpoint=10 ** 9, model_name_or_path=path, model_config="tiny" if False else None,
+                  resume_from_path=path, resume_state=True, verify_weight_sync_during_init=True)
+    second = {k: v for k, v in second.items() if v is not None}
+    out2 = spawn(second, rows, world=2, max_macro_batches=1, port=29771, timeout_s=500)
+    assert out2["global_step"] == 2 and np.isfinite(out2["last"]["training/avg_loss"])

@@ -33,8 +33,22 @@ def test_config_defaults_validation_and_placement():
 
 
 def test_lr_schedule():
-    assert lr_factor(0, 4, 100, "constant") == 0.25 and lr_factor(3, 4, 100, "constant") == 1.0
-    assert lr_factor(50, 0, 0, "constant") == 1.0
+    # the reference's LambdaLR lambda (gpu_process_worker.py:734-741), restated, over warm-up / constant / cosine
+    import math
+
+    def ref(step, warmup, total, kind):
+        if warmup > 0 and step < warmup:
+            return float(step) / float(max(1, warmup))
+        if kind == "cosine" and total > 0:
+            progress = float(step - warmup) / float(max(1, total - warmup))
+            return 0.5 * (1.0 + math.cos(math.pi * progress))
+        return 1.0
+
+    for warmup, total, kind in [(0, 0, "constant"), (4, 100, "constant"), (4, 100, "cosine"), (0, 50, "cosine"), (10, 0, "cosine"),
+                                (8, 8, "cosine")]:
+        for step in range(0, 130):
+            assert lr_factor(step, warmup, total, kind) == ref(step, warmup, total, kind), (step, warmup, total, kind)
+    assert lr_factor(0, 4, 100, "constant") == 0.0 and lr_factor(4, 4, 100, "constant") == 1.0
     assert abs(lr_factor(52, 4, 100, "cosine") - 0.5) < 1e-9 and lr_factor(100, 4, 100, "cosine") < 1e-9
 
 
@@ -310,3 +324,37 @@ def test_logprob_pause_waits_for_the_batch_in_flight_and_holds_the_next_one():
     w.resume()
     fut.result(timeout=5)
     assert order == ["batch-start", "batch-end", "paused", "sync-done", "next-batch"]
+
+
+def test_placement_preflight_names_what_is_wrong():
+    from async_grpo_nccl_b200.launch import preflight_placement
+
+    ok = {"trainer": [0, 1], "logprob": [2], "rollout": [2, 3]}
+    preflight_placement(ok, 4, visible_gpus=4, free_bytes=[100 << 30] * 4, need_bytes=10 << 30)
+    with pytest.raises(ValueError, match="ranks \\[4\\].*job has 4 rank"):
+        preflight_placement({"trainer": [0], "logprob": [1], "rollout": [4]}, 4)
+    with pytest.raises(ValueError, match="only 2 are visible"):
+        preflight_placement(ok, 4, visible_gpus=2)
+    with pytest.raises(ValueError, match="no rank for role 'logprob'"):
+        preflight_placement({"trainer": [0], "logprob": [], "rollout": [1]}, 2)
+    with pytest.raises(ValueError, match="GPU 3 has 1.0 GiB free"):
+        preflight_placement(ok, 4, visible_gpus=4, free_bytes=[100 << 30, 100 << 30, 100 << 30, 1 << 30], need_bytes=10 << 30)
+
+
+def test_epoch_flag_barrier_model_all_interleavings_of_three_ranks():
+    """Every interleaving of the barrier's stores and waits for 3 ranks: nobody leaves an epoch early, everybody finishes;
+    and when one rank skips an arrival, in every interleaving the others end blocked at that epoch (on the device: the
+    bounded wait runs out and the status word is set) and never get past it."""
+    from async_grpo_nccl_b200.parallel.flag_model import explore
+
+    ok = explore(3, 2)
+    assert not ok["violations"] and ok["finals"] == {frozenset()} and ok["states"] > 200
+    for rank in range(3):
+        for epoch in (1, 2):
+            bad = explore(3, 2, skip=(rank, epoch))
+            assert not bad["violations"], bad["violations"][:1]
+            others = {r for r in range(3) if r != rank}
+            for fin in bad["finals"]:
+                blocked = dict(fin)
+                assert others <= set(blocked), "a healthy rank ran to completion past a skipped arrival"
+                assert all(blocked[r] == epoch for r in others)

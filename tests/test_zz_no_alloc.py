@@ -72,6 +72,15 @@ def test_no_alloc_entry_point_matches_regular_path_twice_in_a_row():
         assert rc == OK, msg
         outs.append((logp, ent, lse))
     torch.cuda.synchronize()
+    # the status word of the kernels behind the entry point: 0 = no bounded wait ran out, the outputs are valid
+    import ctypes as _ct
+
+    from async_grpo_nccl_b200 import _build as _b
+
+    lib = _ct.CDLL(str(_b.SO_PATH))
+    lib.agrpo_lmhead_noalloc_status.restype = _ct.c_int
+    lib.agrpo_lmhead_noalloc_status.argtypes = [_ct.c_void_p]
+    assert lib.agrpo_lmhead_noalloc_status(_ct.c_void_p(torch.cuda.current_stream().cuda_stream)) == 0
     for (h, W, labels, temp), (logp, ent, lse) in zip(inputs, outs):
         r_logp, r_ent, r_lse = _reference(h, W, labels, temp)
         torch.cuda.synchronize()
