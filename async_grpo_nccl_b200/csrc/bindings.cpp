@@ -349,7 +349,8 @@ void lmhead_backward(const Tensor& hidden, const Tensor& weight, const Tensor& l
                                 opt_ptr<int>(status), num_sms(), cur_stream());
 }
 
-void kv_cache_write(const Tensor& qkv, const Tensor& slots, Tensor& k_cache, Tensor& v_cache, int64_t Hq, int64_t Hkv, int64_t D) {
+void kv_cache_write(const Tensor& qkv, const Tensor& slots, Tensor& k_cache, Tensor& v_cache, int64_t Hq, int64_t Hkv, int64_t D,
+                    const OptTensor& status) {
   check_bf16(qkv, "qkv"); check_i32(slots, "slots"); check_bf16(k_cache, "k_cache"); check_bf16(v_cache, "v_cache");
   TORCH_CHECK(qkv.dim() == 2 && qkv.stride(1) == 1 && qkv.size(1) == (Hq + 2 * Hkv) * D && qkv.stride(0) % 8 == 0, "kv_cache_write: qkv");
   TORCH_CHECK(k_cache.dim() == 4 && k_cache.is_contiguous() && v_cache.is_contiguous() && k_cache.size(1) == Hkv && k_cache.size(3) == D, "kv_cache_write: cache [blocks, Hkv, bs, D]");
@@ -357,7 +358,7 @@ void kv_cache_write(const Tensor& qkv, const Tensor& slots, Tensor& k_cache, Ten
   const c10::cuda::CUDAGuard guard(qkv.device());
   agrpo::launch_kv_cache_write(qkv.data_ptr(), qkv.stride(0), (int)(Hq * D), (int)((Hq + Hkv) * D), slots.data_ptr<int>(),
                                k_cache.data_ptr(), v_cache.data_ptr(), (int)qkv.size(0), (int)Hkv, (int)D, (int)k_cache.size(2),
-                               cur_stream());
+                               (int)k_cache.size(0), opt_ptr<int>(status), cur_stream());
 }
 
 void kv_cache_write_decode(const Tensor& qkv, const Tensor& block_tables, const Tensor& seq_lens, Tensor& k_cache,
@@ -901,7 +902,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("lmhead_backward", &lmhead_backward, py::arg("hidden"), py::arg("weight"), py::arg("labels"), py::arg("lse"),
         py::arg("dlogp"), py::arg("temperature"), py::arg("dz_chunk"), py::arg("dh_acc"), py::arg("dweight") = py::none(),
         py::arg("status") = py::none(), NOGIL);
-  m.def("kv_cache_write", &kv_cache_write, NOGIL);
+  m.def("kv_cache_write", &kv_cache_write, py::arg("qkv"), py::arg("slots"), py::arg("k_cache"), py::arg("v_cache"), py::arg("Hq"),
+        py::arg("Hkv"), py::arg("D"), py::arg("status") = py::none(), NOGIL);
   m.def("kv_cache_write_decode", &kv_cache_write_decode, py::arg("qkv"), py::arg("block_tables"), py::arg("seq_lens"),
         py::arg("k_cache"), py::arg("v_cache"), py::arg("Hq"), py::arg("Hkv"), py::arg("D"), py::arg("status") = py::none(), NOGIL);
   m.def("rope_kv_write_decode", &rope_kv_write_decode, py::arg("qkv"), py::arg("cos"), py::arg("sin"), py::arg("block_tables"),

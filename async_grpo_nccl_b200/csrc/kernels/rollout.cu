@@ -19,11 +19,16 @@ namespace {
 // ------------------------------------------------------------------------------------------------
 __global__ void kv_cache_write_kernel(const __nv_bfloat16* __restrict__ qkv, long long row_pitch, int k_col0, int v_col0,
                                       const int* __restrict__ slots, __nv_bfloat16* __restrict__ k_cache,
-                                      __nv_bfloat16* __restrict__ v_cache, int T, int Hkv, int D, int block_size) {
+                                      __nv_bfloat16* __restrict__ v_cache, int T, int Hkv, int D, int block_size,
+                                      long long num_slots, int* status) {
   const int t = blockIdx.x;
   if (t >= T) return;
   const int slot = slots[t];
   if (slot < 0) return;
+  if (slot >= num_slots) {  // beyond the cache: record it and skip the write
+    if (threadIdx.x == 0) report_status(status, kStatusBadIndex);
+    return;
+  }
   const int blk = slot / block_size, off = slot % block_size;
   const int per_row = Hkv * D / 8;  // 16-byte chunks per token per tensor
   for (int i = threadIdx.x; i < 2 * per_row; i += blockDim.x) {
@@ -296,11 +301,13 @@ __global__ void lm_sample_combine_kernel(const float* __restrict__ part_best, co
 }  // namespace
 
 void launch_kv_cache_write(const void* qkv, long long row_pitch, int k_col0, int v_col0, const int* slots, void* k_cache,
-                           void* v_cache, int T, int Hkv, int D, int block_size, cudaStream_t s) {
+                           void* v_cache, int T, int Hkv, int D, int block_size, int num_cache_blocks, int* status,
+                           cudaStream_t s) {
   if (T == 0) return;
   AGRPO_PREFER_SMEM(kv_cache_write_kernel);
   kv_cache_write_kernel<<<T, 64, 0, s>>>((const __nv_bfloat16*)qkv, row_pitch, k_col0, v_col0, slots, (__nv_bfloat16*)k_cache,
-                                         (__nv_bfloat16*)v_cache, T, Hkv, D, block_size);
+                                         (__nv_bfloat16*)v_cache, T, Hkv, D, block_size,
+                                         (long long)num_cache_blocks * block_size, status);
   check_cuda(cudaGetLastError(), "kv_cache_write");
 }
 

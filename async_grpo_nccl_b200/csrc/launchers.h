@@ -220,7 +220,8 @@ void launch_lmhead_backward(const void* hidden, long long ldh, const void* weigh
 // ---- rollout engine (rollout.cu) ----
 // KV cache layout per layer: [num_blocks, Hkv, block_size, D] (K and V separately). slots[t] < 0 skips token t.
 void launch_kv_cache_write(const void* qkv, long long row_pitch, int k_col0, int v_col0, const int* slots, void* k_cache,
-                           void* v_cache, int T, int Hkv, int D, int block_size, cudaStream_t s);
+                           void* v_cache, int T, int Hkv, int D, int block_size, int num_cache_blocks, int* status,
+                           cudaStream_t s);
 void launch_kv_cache_write_decode(const void* qkv, long long row_pitch, int k_col0, int v_col0, const int* block_tables,
                                   int max_blocks, const int* seq_lens, void* k_cache, void* v_cache, int B, int Hkv, int D,
                                   int block_size, int num_cache_blocks, int* status, cudaStream_t s);

@@ -104,6 +104,10 @@ def aggregate_completions(completions: Sequence[Dict[str, Any]]) -> Dict[str, fl
     out["training/batch_total_samples"] = n_s
     out["training/batch_avg_reward"] = sum(float(b.get("total_reward", 0.0)) for b in bm) / n_s if n_s else 0.0
     out["training/optimizer_steps_in_batch"] = max([float(c.get("optimizer_steps_in_batch", 0)) for c in completions] or [0.0])
+    # device-timed trainer phases: the slowest rank decides (all ranks step together)
+    for c in completions:
+        for k, v in (c.get("phase_ms") or {}).items():
+            out[f"timing/trainer_{k}_ms"] = max(out.get(f"timing/trainer_{k}_ms", 0.0), float(v))
     return out
 
 

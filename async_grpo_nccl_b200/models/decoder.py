@@ -197,7 +197,7 @@ class NativeDecoder:
         C.rope_inplace(qkv, batch.pos, cos_t, sin_t, cfg.num_attention_heads + cfg.num_key_value_heads, cfg.head_dim, False)
         if kv_write is not None:  # rollout prefill: K/V of every prompt token go to their cache slots
             k_cache, v_cache, slots = kv_write
-            C.kv_cache_write(qkv, slots, k_cache, v_cache, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim)
+            C.kv_cache_write(qkv, slots, k_cache, v_cache, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, self.status)
             self.launches += 1
         attn = self._new(T, cfg.q_dim)
         lse = self._new(cfg.num_attention_heads, T, dtype=torch.float32)

@@ -120,6 +120,10 @@ class TrainerCore:
         self.last_grad_norm = 0.0
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        # device-timed phases (CUDA events on this role's stream, NVTX ranges for a profiler), read once per macro-batch
+        from ..utils.timing import PhaseTimer
+
+        self.timer = PhaseTimer(cuda=self.native)
 
     # ------------------------------------------------------------------ metrics plumbing
     def _reset_batch_accumulators(self) -> None:
@@ -140,13 +144,15 @@ class TrainerCore:
         n_real = len(real)
         if n_real == 0 and self.world == 1:
             return  # single rank, nothing to do (gpu_process_worker.py:975-985)
-        batch_host = pack_samples(samples if n_real else [{"dummy": True}], pin=self.native)
-        self.h2d_bytes += batch_host.h2d_bytes()
-        batch = batch_host.to_device(self.device)
+        with self.timer.phase("pack_h2d"):
+            batch_host = pack_samples(samples if n_real else [{"dummy": True}], pin=self.native)
+            self.h2d_bytes += batch_host.h2d_bytes()
+            batch = batch_host.to_device(self.device)
         # scale so that the sum over microbatches and ranks is (1/N) * sum_mb n_mb * tokenmean_mb
         loss_scale = float(n_real) / float(self.cfg.train_minibatch_sample_size)
         if self.native:
-            stats = self.decoder.forward_backward(batch, self.loss_cfg, loss_scale, self.sink)
+            with self.timer.phase("forward_backward"):
+                stats = self.decoder.forward_backward(batch, self.loss_cfg, loss_scale, self.sink)
             if self.cfg.kernel_checks:
                 self.decoder.check_status()  # one synchronisation per microbatch: a failed kernel is named right away
         else:
@@ -184,6 +190,10 @@ class TrainerCore:
 
     # ------------------------------------------------------------------ GRADIENT_STEP
     def apply_gradients(self) -> Dict[str, float]:
+        with self.timer.phase("optimizer_step"):
+            return self._apply_gradients()
+
+    def _apply_gradients(self) -> Dict[str, float]:
         """Reduce gradients over the trainer ranks, clip by global norm, AdamW on the local shard, publish the bf16
         result into every rank's resident parameter buffer, zero gradients."""
         cfg = self.cfg
@@ -332,6 +342,8 @@ class TrainerCore:
             "grad_clip_ratio_in_batch": self._clipped_steps / self._grad_steps if self._grad_steps else 0.0,
             "exp_batch_metrics": exp,
             "minibatch_summaries": [dict(s) for s in self._step_summaries],
+            # device milliseconds of this rank's phases in this macro-batch (CUDA events on the trainer stream)
+            "phase_ms": {k: float(v) for k, v in self.timer.summary().items()},
         }
         self._reset_batch_accumulators()
         return payload

@@ -30,11 +30,11 @@ def record_function(name: str) -> Iterator[None]:
 class PhaseTimer:
     """``with timer.phase("fwd"):`` records a CUDA-event pair on the current stream (wall clock on CPU)."""
 
-    def __init__(self, enabled: bool = True):
+    def __init__(self, enabled: bool = True, cuda: Optional[bool] = None):
         self.enabled = enabled
         self._pairs: Dict[str, List[Tuple[torch.cuda.Event, torch.cuda.Event]]] = defaultdict(list)
         self._wall: Dict[str, float] = defaultdict(float)
-        self.cuda = torch.cuda.is_available()
+        self.cuda = torch.cuda.is_available() if cuda is None else bool(cuda)
 
     @contextlib.contextmanager
     def phase(self, name: str) -> Iterator[None]:
@@ -58,11 +58,12 @@ class PhaseTimer:
                 self._wall[name] += (time.time() - t0) * 1000.0
 
     def summary(self, reset: bool = True) -> Dict[str, float]:
-        """Milliseconds per phase (synchronises once)."""
+        """Milliseconds per phase. Waits for the recorded events of this timer only (other roles' streams on the same GPU
+        keep running)."""
         out: Dict[str, float] = dict(self._wall)
         if self.cuda and self._pairs:
-            torch.cuda.synchronize()
             for name, pairs in self._pairs.items():
+                pairs[-1][1].synchronize()
                 out[name] = out.get(name, 0.0) + sum(a.elapsed_time(b) for a, b in pairs)
         if reset:
             self._pairs.clear()

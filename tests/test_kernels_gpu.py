@@ -207,10 +207,69 @@ def test_lmhead_loss(T, H, V, temp, beta):
     assert abs(stats[1].item() - loss_sum.item()) < 2e-2 * max(1.0, abs(loss_sum.item()))
     for i in (0, 4, 5, 11, 12, 13):  # counts must agree up to tokens that sit on a clip boundary
         assert abs(stats[i].item() - stats_ref[i].item()) <= max(3.0, 0.01 * stats_ref[0].item())
-    # tokens near a clip boundary may flip branch under bf16 noise; compare directions
+    # (a) d loss / d logp, element by element, on tokens whose ratio is not next to a clip boundary (the kernel's own logp
+    # differs from the fp32 one by bf16 noise, so a token within a few percent of a boundary may take the other branch)
+    leaf = logp_ref.detach().clone().requires_grad_(True)
+    loss2, _ = R.grpo_token_loss(leaf, old, refl, adv, labels, 0.2, 0.28, 3.0, beta, ent_ref.detach())
+    (loss2 * gw).backward()
+    ratio = torch.exp(logp_ref.detach() - old)
+    far = mask.clone()
+    for edge in (0.8, 1.28, 3.0):
+        far &= (ratio - edge).abs() > 0.05 * edge
+    assert far.float().mean().item() > 0.5
+    err = (dlogp - leaf.grad)[far].abs()
+    assert (err <= 0.05 * leaf.grad[far].abs() + 1e-7).all(), err.max().item()
+    assert (dlogp[~mask] == 0).all()
+    # (b) the lm_head backward itself, element by element: gradients of sum_t dlogp[t] * logp[t] for the kernel's dlogp
+    h2, W2 = h.float().requires_grad_(True), W.float().requires_grad_(True)
+    logp2, _ = R.lmhead_logprob_entropy(h2, W2, labels, temp)
+    (logp2 * dlogp.detach() * mask).sum().backward()
+    assert rel_err(dh, h2.grad) < 2e-2, rel_err(dh, h2.grad)
+    assert rel_err(dW, W2.grad) < 2e-2, rel_err(dW, W2.grad)
+    # and the end-to-end direction against the fp32 objective
     cos = torch.nn.functional.cosine_similarity
     assert cos(dh.flatten(), hf.grad.flatten(), dim=0).item() > 0.97
     assert cos(dW.flatten(), Wf.grad.flatten(), dim=0).item() > 0.97
+
+
+def test_lmhead_full_vocabulary_tail_tile():
+    """V = 151936 (1187 column tiles of 128, the last 256-wide tile half empty) with T = 4096: log-probabilities, entropy and
+    both gradients against fp32 PyTorch computed in row chunks."""
+    C = native()
+    from async_grpo_nccl_b200.ops import reference as R
+
+    torch.manual_seed(1)
+    T, H, V, temp = 4096, 256, 151936, 1.0
+    h = torch.randn(T, H, device=DEV).to(torch.bfloat16)
+    W = (torch.randn(V, H, device=DEV) * 0.05).to(torch.bfloat16)
+    labels = torch.randint(0, V, (T,), device=DEV, dtype=torch.int32)
+    labels[:64] = V - 1 - torch.arange(64, device=DEV, dtype=torch.int32)  # labels inside the tail tile
+    labels[torch.rand(T, device=DEV) < 0.1] = -100
+    mask = labels >= 0
+    st = status_word()
+    groups = C.lmhead_num_groups(V, T)
+    partials = torch.empty(3 * groups * T, device=DEV)
+    ll = torch.zeros(T, device=DEV)
+    logp, ent, lse = (torch.empty(T, device=DEV) for _ in range(3))
+    C.lmhead_logprob(h, W, labels, temp, partials, ll, logp, ent, lse, st)
+    dlogp = torch.randn(T, device=DEV) * mask / T
+    dz = torch.empty(T, 1024, device=DEV, dtype=torch.bfloat16)
+    dh, dW = torch.empty(T, H, device=DEV), torch.zeros(V, H, device=DEV)
+    C.lmhead_backward(h, W, labels, lse, dlogp, temp, dz, dh, dW, st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    Wf = W.float().requires_grad_(True)
+    dh_ref = torch.empty(T, H, device=DEV)
+    for r0 in range(0, T, 512):  # fp32 reference in row chunks (a [512, V] fp32 block is 311 MB)
+        hf = h[r0:r0 + 512].float().requires_grad_(True)
+        lp, en = R.lmhead_logprob_entropy(hf, Wf, labels[r0:r0 + 512], temp)
+        assert (logp[r0:r0 + 512] - lp.detach()).abs().max().item() < 2e-2
+        assert (ent[r0:r0 + 512] - en.detach()).abs().max().item() < 2e-2
+        (lp * dlogp[r0:r0 + 512] * mask[r0:r0 + 512]).sum().backward()
+        dh_ref[r0:r0 + 512] = hf.grad
+    assert rel_err(dh, dh_ref) < 2e-2
+    assert rel_err(dW, Wf.grad) < 2e-2
+    assert rel_err(dW[V - 256:], Wf.grad[V - 256:]) < 2e-2  # rows of the tail tile
 
 
 def test_paged_decode_and_kv_write():
@@ -550,3 +609,22 @@ def test_peer_kernels_return_untouched_when_the_group_status_is_set():
         assert torch.equal(dst, src.to(torch.bfloat16)) and torch.equal(out, g)
     finally:
         C.set_comm_guard(None)
+
+
+def test_prefill_kv_write_reports_out_of_range_slots_and_skips_them():
+    """A slot beyond the cache is reported through the status word and not written (index checks never fault)."""
+    C = native()
+    torch.manual_seed(5)
+    Hq, Hkv, D, bs, nblk, T = 4, 2, 128, 16, 8, 6
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device=DEV).to(torch.bfloat16)
+    kc = torch.zeros(nblk, Hkv, bs, D, device=DEV, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    slots = torch.tensor([0, 17, -1, nblk * bs - 1, nblk * bs, nblk * bs + 1000], device=DEV, dtype=torch.int32)
+    st = status_word()
+    C.kv_cache_write(qkv, slots, kc, vc, Hq, Hkv, D, st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 6  # bad index
+    written = (kc.abs().sum(-1) > 0).sum().item()
+    assert written == 3 * Hkv
+    k_rows = qkv[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D)
+    assert torch.equal(kc[0, :, 0], k_rows[0]) and torch.equal(kc[1, :, 1], k_rows[1]) and torch.equal(kc[nblk - 1, :, bs - 1], k_rows[3])
