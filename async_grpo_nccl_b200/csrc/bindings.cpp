@@ -350,14 +350,16 @@ void lmhead_backward(const Tensor& hidden, const Tensor& weight, const Tensor& l
 }
 
 void kv_cache_write(const Tensor& qkv, const Tensor& slots, Tensor& k_cache, Tensor& v_cache, int64_t Hq, int64_t Hkv, int64_t D,
-                    const OptTensor& status) {
+                    const OptTensor& status, int64_t kv_head0) {
   check_bf16(qkv, "qkv"); check_i32(slots, "slots"); check_bf16(k_cache, "k_cache"); check_bf16(v_cache, "v_cache");
   TORCH_CHECK(qkv.dim() == 2 && qkv.stride(1) == 1 && qkv.size(1) == (Hq + 2 * Hkv) * D && qkv.stride(0) % 8 == 0, "kv_cache_write: qkv");
-  TORCH_CHECK(k_cache.dim() == 4 && k_cache.is_contiguous() && v_cache.is_contiguous() && k_cache.size(1) == Hkv && k_cache.size(3) == D, "kv_cache_write: cache [blocks, Hkv, bs, D]");
+  TORCH_CHECK(k_cache.dim() == 4 && k_cache.is_contiguous() && v_cache.is_contiguous() && k_cache.size(1) + kv_head0 <= Hkv && kv_head0 >= 0 && k_cache.size(3) == D,
+              "kv_cache_write: cache [blocks, kv heads of this rank, bs, D]");
   TORCH_CHECK(slots.numel() == qkv.size(0), "kv_cache_write: slots");
   const c10::cuda::CUDAGuard guard(qkv.device());
-  agrpo::launch_kv_cache_write(qkv.data_ptr(), qkv.stride(0), (int)(Hq * D), (int)((Hq + Hkv) * D), slots.data_ptr<int>(),
-                               k_cache.data_ptr(), v_cache.data_ptr(), (int)qkv.size(0), (int)Hkv, (int)D, (int)k_cache.size(2),
+  // a tensor-parallel rank caches kv heads [kv_head0, kv_head0 + k_cache.size(1)) of the Hkv heads in qkv
+  agrpo::launch_kv_cache_write(qkv.data_ptr(), qkv.stride(0), (int)((Hq + kv_head0) * D), (int)((Hq + Hkv + kv_head0) * D), slots.data_ptr<int>(),
+                               k_cache.data_ptr(), v_cache.data_ptr(), (int)qkv.size(0), (int)k_cache.size(1), (int)D, (int)k_cache.size(2),
                                (int)k_cache.size(0), opt_ptr<int>(status), cur_stream());
 }
 
@@ -701,6 +703,24 @@ void rs_pull_sumsq(const PtrList& grad_ptrs, int64_t my_rank, int64_t global_off
   agrpo::launch_rs_pull_sumsq(lptr(grad_ptrs), (int)grad_ptrs.size(), (int)my_rank, global_off, local_off, n,
                               out.data_ptr<float>(), norm_sq.data_ptr<float>(), cur_stream());
 }
+void flag_barrier_auto(const PtrList& flag_ptrs, int64_t my_rank, Tensor& epoch_counter, double budget_s, Tensor& status) {
+  check_i64(epoch_counter, "epoch_counter"); check_i32(status, "status");
+  const c10::cuda::CUDAGuard guard(status.device());
+  agrpo::launch_flag_barrier_auto(lptr(flag_ptrs), (int)flag_ptrs.size(), (int)my_rank,
+                                  reinterpret_cast<unsigned long long*>(epoch_counter.data_ptr<int64_t>()), budget_s,
+                                  status.data_ptr<int>(), cur_stream());
+}
+void tp_allreduce_residual(const PtrList& partial_ptrs, const Tensor& residual, Tensor& out, const OptTensor& ss) {
+  check_bf16(residual, "residual"); check_bf16(out, "out");
+  TORCH_CHECK(residual.dim() == 2 && residual.is_contiguous() && out.is_contiguous() && out.sizes() == residual.sizes(), "tp_allreduce: [rows, H]");
+  TORCH_CHECK(residual.size(1) % 8 == 0 && (reinterpret_cast<uintptr_t>(residual.data_ptr()) & 15) == 0 &&
+              (reinterpret_cast<uintptr_t>(out.data_ptr()) & 15) == 0, "tp_allreduce: alignment");
+  for (auto ptr : partial_ptrs) TORCH_CHECK(ptr != 0 && (ptr & 15) == 0, "tp_allreduce: partial buffers");
+  if (ss.has_value() && ss->defined()) { check_i64(*ss, "ss"); TORCH_CHECK(ss->is_contiguous() && ss->numel() >= residual.size(0), "ss [rows]"); }
+  const c10::cuda::CUDAGuard guard(residual.device());
+  agrpo::launch_tp_allreduce_residual(lptr(partial_ptrs), (int)partial_ptrs.size(), residual.data_ptr(), out.data_ptr(),
+                                      opt_i64(ss), (int)residual.size(0), (int)residual.size(1), cur_stream());
+}
 void set_comm_guard(const c10::optional<Tensor>& status) {
   if (status.has_value()) {
     TORCH_CHECK(status->is_cuda() && status->scalar_type() == torch::kInt32 && status->numel() >= 1, "set_comm_guard: int32 CUDA status word");
@@ -903,7 +923,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("dlogp"), py::arg("temperature"), py::arg("dz_chunk"), py::arg("dh_acc"), py::arg("dweight") = py::none(),
         py::arg("status") = py::none(), NOGIL);
   m.def("kv_cache_write", &kv_cache_write, py::arg("qkv"), py::arg("slots"), py::arg("k_cache"), py::arg("v_cache"), py::arg("Hq"),
-        py::arg("Hkv"), py::arg("D"), py::arg("status") = py::none(), NOGIL);
+        py::arg("Hkv"), py::arg("D"), py::arg("status") = py::none(), py::arg("kv_head0") = 0, NOGIL);
   m.def("kv_cache_write_decode", &kv_cache_write_decode, py::arg("qkv"), py::arg("block_tables"), py::arg("seq_lens"),
         py::arg("k_cache"), py::arg("v_cache"), py::arg("Hq"), py::arg("Hkv"), py::arg("D"), py::arg("status") = py::none(), NOGIL);
   m.def("rope_kv_write_decode", &rope_kv_write_decode, py::arg("qkv"), py::arg("cos"), py::arg("sin"), py::arg("block_tables"),
@@ -938,6 +958,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rs_pull_sumsq", &rs_pull_sumsq, NOGIL);
   m.def("publish_norm", &publish_norm, NOGIL);
   m.def("set_comm_guard", &set_comm_guard, py::arg("status") = py::none());
+  m.def("flag_barrier_auto", &flag_barrier_auto, NOGIL);
+  m.def("tp_allreduce_residual", &tp_allreduce_residual, py::arg("partial_ptrs"), py::arg("residual"), py::arg("out"),
+        py::arg("ss") = py::none(), NOGIL);
   m.def("adamw_push", &adamw_push, NOGIL);
   m.def("sumsq", &sumsq, NOGIL);
   m.def("adamw_step", &adamw_step, py::arg("p"), py::arg("m"), py::arg("v"), py::arg("g"), py::arg("p16") = py::none(),

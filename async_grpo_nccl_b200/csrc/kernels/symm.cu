@@ -62,6 +62,83 @@ __global__ void flag_barrier_kernel(PeerPtrs flags, int my_rank, uint64_t epoch,
   }
 }
 
+// The same barrier with its epoch kept on the device: *epoch_counter is incremented by the kernel itself, so the launch has
+// no per-call argument and can be replayed from a CUDA graph (every rank replays the same number of barriers).
+__global__ void flag_barrier_auto_kernel(PeerPtrs flags, int my_rank, unsigned long long* epoch_counter, long long budget,
+                                         int* status) {
+  __shared__ unsigned long long s_epoch;
+  if (threadIdx.x == 0) s_epoch = ++(*epoch_counter);
+  __syncthreads();
+  const uint64_t epoch = s_epoch;
+  const int r = threadIdx.x;
+  if (r < flags.n) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<uint64_t*>(flags.p[r]) + my_rank, epoch);
+  }
+  __syncthreads();
+  if (r < flags.n) {
+    const uint64_t* mine = reinterpret_cast<const uint64_t*>(flags.p[my_rank]) + r;
+    if (!wait_flag_ge(mine, epoch, budget)) report_status(status, kStatusBarrierTimeout);
+  }
+}
+
+// Tensor-parallel all-reduce of a row-parallel projection, fused with what follows it in a decoder layer:
+//   out[b, :] = residual[b, :] + sum_r partial_r[b, :]     (fp32 sum in rank order: every rank gets the same bits)
+//   ss[b]    += sum_h out[b, h]^2                          (row statistic of the next folded RMSNorm, fixed point)
+// partial_r is rank r's bf16 [rows, H] product in ITS symmetric buffer, read here with plain peer loads (one-shot
+// all-reduce: every rank reads every partial; [rows, H] is a few hundred KB, far below the point where a ring pays).
+// The barrier before this kernel says every partial is written; the barrier of the NEXT all-reduce (on the other
+// buffer) says everybody has finished reading this one before it is overwritten.
+__global__ void tp_allreduce_residual_kernel(PeerPtrs partials, const __nv_bfloat16* __restrict__ residual,
+                                             __nv_bfloat16* __restrict__ out, sumsq_t* __restrict__ ss, int rows, int H,
+                                             const int* guard) {
+  if (guard_tripped(guard)) return;
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int b = blockIdx.x * warps + warp; b < rows; b += gridDim.x * warps) {
+    float sq = 0.f;
+    for (int c = lane * 8; c < H; c += 32 * 8) {
+      float acc[8];
+      {
+        const uint4 u = *reinterpret_cast<const uint4*>(residual + (size_t)b * H + c);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(h2[i]);
+          acc[2 * i] = f.x;
+          acc[2 * i + 1] = f.y;
+        }
+      }
+      uint4 part[kMaxPeers > 8 ? 8 : kMaxPeers];
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+        if (r < partials.n) part[r] = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(partials.p[r]) + (size_t)b * H + c);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        if (r < partials.n) {
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&part[r]);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(h2[i]);
+            acc[2 * i] += f.x;
+            acc[2 * i + 1] += f.y;
+          }
+        }
+      }
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]);
+      o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]);
+      o.w = pack_bf16x2(acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(out + (size_t)b * H + c) = o;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sq += acc[i] * acc[i];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    if (lane == 0 && ss != nullptr) sumsq_atomic_add(ss + b, sq);
+  }
+}
+
 // dst[d][global_off + i] = bf16(src[local_off + i]) for every destination d. SrcT = float or bf16.
 template <typename SrcT>
 __global__ void weight_push_kernel(const SrcT* __restrict__ src, long long local_off, long long global_off, long long n,
@@ -280,6 +357,22 @@ void launch_flag_barrier(const long long* flag_ptrs, int world, int my_rank, uns
                          int* status, cudaStream_t s) {
   flag_barrier_kernel<<<1, 32, 0, s>>>(make_peers(flag_ptrs, world), my_rank, epoch, ticks_for(budget_s), status);
   check_cuda(cudaGetLastError(), "flag_barrier");
+}
+
+void launch_flag_barrier_auto(const long long* flag_ptrs, int world, int my_rank, unsigned long long* epoch_counter,
+                              double budget_s, int* status, cudaStream_t s) {
+  flag_barrier_auto_kernel<<<1, 32, 0, s>>>(make_peers(flag_ptrs, world), my_rank, epoch_counter, ticks_for(budget_s), status);
+  check_cuda(cudaGetLastError(), "flag_barrier_auto");
+}
+
+void launch_tp_allreduce_residual(const long long* partial_ptrs, int world, const void* residual, void* out, long long* ss,
+                                  int rows, int H, cudaStream_t s) {
+  if (rows == 0) return;
+  if (world > 8 || H % 8 != 0) throw std::runtime_error("tp_allreduce_residual: at most 8 ranks, H a multiple of 8");
+  const int blocks = (rows + 3) / 4;
+  tp_allreduce_residual_kernel<<<blocks, 128, 0, s>>>(make_peers(partial_ptrs, world), (const __nv_bfloat16*)residual,
+                                                       (__nv_bfloat16*)out, ss, rows, H, t_guard);
+  check_cuda(cudaGetLastError(), "tp_allreduce_residual");
 }
 
 void launch_weight_push(const void* src, bool src_fp32, long long local_off, long long global_off, long long n,

@@ -67,7 +67,7 @@ class RolloutEngine:
     def __init__(self, cfg: ModelConfig, layout: ParamLayout, params: torch.Tensor, *, max_seqs: int = 256,
                  max_model_len: Optional[int] = None, num_blocks: Optional[int] = None, block_size: int = 16,
                  kv_memory_bytes: Optional[int] = None, max_prefill_tokens: int = 16384, use_cuda_graph: bool = False,
-                 eos_token_id: Optional[int] = None):
+                 eos_token_id: Optional[int] = None, tp: Any = None):
         from ..ops import native
 
         assert params.is_cuda and params.dtype == torch.bfloat16
@@ -76,6 +76,19 @@ class RolloutEngine:
         self.C = native()
         self.cfg, self.layout, self.params = cfg, layout, params
         self.dev = params.device
+        # Tensor parallelism (vllm_worker.py:219-232, tensor_parallel_size): ``tp`` is a parallel.symm.TensorParallelComm.
+        # This rank then holds Hq / tp query heads and Hkv / tp kv heads (projection columns, KV cache) and F / tp MLP
+        # columns; the o and down projections produce partial sums that are all-reduced over peer memory. Embedding,
+        # lm_head and sampling are replicated: every member computes the same token from the same bits.
+        self.tp = tp if (tp is not None and tp.size > 1) else None
+        self.tp_size = self.tp.size if self.tp is not None else 1
+        self.tp_rank = self.tp.rank if self.tp is not None else 0
+        t = self.tp_size
+        if cfg.num_attention_heads % t or cfg.num_key_value_heads % t or cfg.intermediate_size % (8 * t):
+            raise ValueError(f"tensor parallel size {t} must divide the head counts and the MLP width")
+        self.Hq_l, self.Hkv_l, self.F_l = cfg.num_attention_heads // t, cfg.num_key_value_heads // t, cfg.intermediate_size // t
+        self.Q_l = (self.Hq_l + 2 * self.Hkv_l) * cfg.head_dim
+        self.qd_l = self.Hq_l * cfg.head_dim
         self.sm_count = torch.cuda.get_device_properties(self.dev).multi_processor_count  # SMs the engine's stream may use
         self.dec = NativeDecoder(cfg, layout, params)
         self.status = self.dec.status
@@ -84,14 +97,14 @@ class RolloutEngine:
         self.max_model_len = int(max_model_len or cfg.max_position_embeddings)
         self.max_blocks_per_seq = (self.max_model_len + block_size - 1) // block_size
         self.eos = cfg.eos_token_id if eos_token_id is None else int(eos_token_id)
-        per_block = cfg.num_hidden_layers * 2 * cfg.num_key_value_heads * block_size * cfg.head_dim * 2
+        per_block = cfg.num_hidden_layers * 2 * self.Hkv_l * block_size * cfg.head_dim * 2
         if num_blocks is None:
             if kv_memory_bytes is None:
                 free, _ = torch.cuda.mem_get_info(self.dev)
                 kv_memory_bytes = int(free * 0.6)
             num_blocks = max(64, kv_memory_bytes // per_block)
         self.num_blocks = int(num_blocks)
-        self.cache = torch.zeros(cfg.num_hidden_layers, 2, self.num_blocks, cfg.num_key_value_heads, block_size,
+        self.cache = torch.zeros(cfg.num_hidden_layers, 2, self.num_blocks, self.Hkv_l, block_size,
                                  cfg.head_dim, dtype=torch.bfloat16, device=self.dev)
         self.sched = self.C.Scheduler(self.num_blocks, block_size, self.max_seqs, self.max_blocks_per_seq,
                                       int(max_prefill_tokens))
@@ -115,10 +128,10 @@ class RolloutEngine:
         self.b_x = torch.zeros(SA, H, **bf)
         self.b_x1 = torch.zeros(SA, H, **bf)
         self.b_h = torch.empty(S, H, **bf)
-        self.b_qkv = torch.zeros(SA, cfg.qkv_dim, **bf)
-        self.b_attn = torch.zeros(SA, cfg.q_dim, **bf)
-        self.b_gu = torch.empty(S, 2 * cfg.intermediate_size, **bf)
-        self.b_act = torch.zeros(SA, cfg.intermediate_size, **bf)
+        self.b_qkv = torch.zeros(SA, self.Q_l, **bf)
+        self.b_attn = torch.zeros(SA, self.qd_l, **bf)
+        self.b_gu = torch.empty(S, 2 * self.F_l, **bf)
+        self.b_act = torch.zeros(SA, self.F_l, **bf)
         self.b_tokens = torch.zeros(S, **i32)
         self.max_splits = 8
         self.b_part_o = torch.empty(S * cfg.num_key_value_heads * self.max_splits * 8 * cfg.head_dim, dtype=torch.float32,
@@ -157,11 +170,15 @@ class RolloutEngine:
         # of wqkv and wgu, refreshed after every weight sync); the row scale rsqrt(mean(x^2) + eps) is applied in those
         # GEMMs' epilogues from sums of squares that the producing GEMMs' epilogues accumulate. Together with the fused
         # gate/up + SwiGLU GEMM a layer is 6 kernels instead of 9.
-        L, F, Q = cfg.num_hidden_layers, cfg.intermediate_size, cfg.qkv_dim
+        L, F, Q = cfg.num_hidden_layers, self.F_l, self.Q_l   # this rank's share under tensor parallelism
         self.fused_chunk = min(256, self.max_seqs)   # rows per launch of the skinny GEMMs
         self.fused_decode = F % 8 == 0 and all(
             int(self.C.gemm_skinny_splits(m, n, k)) > 0
-            for m in range(32, self.fused_chunk + 1, 32) for n, k in ((Q, H), (H, cfg.q_dim), (H, F)))
+            for m in range(32, self.fused_chunk + 1, 32) for n, k in ((Q, H), (H, self.qd_l), (H, F)))
+        if self.tp is not None:
+            if not self.fused_decode or self.max_seqs > self.fused_chunk:
+                raise ValueError("the tensor-parallel engine needs the fused decode path and at most 256 sequences per replica")
+            self.bq_local = torch.zeros(L, Q, **bf)
         self.fused_rows = self.max_seqs if self.fused_decode else 0  # larger batches go through in chunks
         if self.fused_decode:
             self.folded = torch.empty(L * (Q + 2 * F) * H, **bf)
@@ -171,7 +188,7 @@ class RolloutEngine:
         self.mega_rows = 0
         self.mega_trace: Optional[torch.Tensor] = None  # int64[32]: phase stamps of CTA 0 in layer mega_trace_layer
         self.mega_trace_layer = 0
-        if (self.fused_decode and os.environ.get("AGRPO_DECODE_MEGA", "1") != "0"
+        if (self.fused_decode and self.tp is None and os.environ.get("AGRPO_DECODE_MEGA", "1") != "0"
                 and self.C.decode_layers_supported(min(256, S), H, Q, cfg.q_dim, F, cfg.num_attention_heads,
                                                    cfg.num_key_value_heads, cfg.head_dim)):
             # it wins where the step is latency-bound (few rows); with more rows both paths are bound by streaming the
@@ -287,7 +304,7 @@ class RolloutEngine:
         x = torch.empty(T, cfg.hidden_size, dtype=torch.bfloat16, device=self.dev)
         C.embedding_fwd(batch.ids, dec.w("embed"), x)
         for i in range(cfg.num_hidden_layers):
-            x = dec._layer_fwd(i, x, batch, cos_t, sin_t, None, kv_write=(self._kc(i), self._vc(i), slots))
+            x = dec._layer_fwd(i, x, batch, cos_t, sin_t, None, kv_write=(self._kc(i), self._vc(i), slots, self.tp_rank * self.Hkv_l))
         last = (batch.cu_seqlens[1:] - 1).long()
         xl = x.index_select(0, last)
         hn = torch.empty_like(xl)
@@ -389,7 +406,7 @@ class RolloutEngine:
     # ---- fused decode path ----
     def _folded(self, i: int) -> Tuple[torch.Tensor, torch.Tensor]:
         cfg = self.cfg
-        H, F, Q = cfg.hidden_size, cfg.intermediate_size, cfg.qkv_dim
+        H, F, Q = cfg.hidden_size, self.F_l, self.Q_l
         per = (Q + 2 * F) * H
         base = i * per
         return (self.folded[base: base + Q * H].view(Q, H), self.folded[base + Q * H: base + per].view(2 * F, H))
@@ -398,13 +415,38 @@ class RolloutEngine:
         """Recomputes the norm-folded copies of wqkv and wgu from the current parameters (2 small kernels per layer)."""
         if not self.fused_decode:
             return
-        dec, C = self.dec, self.C
-        for i in range(self.cfg.num_hidden_layers):
+        dec, C, cfg = self.dec, self.C, self.cfg
+        if self.tp is not None:
+            return self._refold_weights_tp()
+        for i in range(cfg.num_hidden_layers):
             p = f"layers.{i}."
             fq, fg = self._folded(i)
             C.fold_norm_weight(dec.w(p + "wqkv"), dec.w(p + "ln1"), fq)
             C.fold_norm_weight(dec.w(p + "wgu"), dec.w(p + "ln2"), fg)
-        self.launches += 2 * self.cfg.num_hidden_layers
+        self.launches += 2 * cfg.num_hidden_layers
+
+    def _refold_weights_tp(self) -> None:
+        """This rank's rows of wqkv (its q, k and v heads) and of wgu (its gate and up columns), norm-folded, plus its
+        slice of the qkv bias."""
+        dec, C, cfg = self.dec, self.C, self.cfg
+        r, D = self.tp_rank, cfg.head_dim
+        qd, kvd, F = cfg.q_dim, cfg.kv_dim, cfg.intermediate_size
+        ql, kl, fl = self.qd_l, self.Hkv_l * D, self.F_l
+        for i in range(cfg.num_hidden_layers):
+            p = f"layers.{i}."
+            fq, fg = self._folded(i)
+            wq, wg = dec.w(p + "wqkv"), dec.w(p + "wgu")
+            ln1, ln2 = dec.w(p + "ln1"), dec.w(p + "ln2")
+            rows = ((r * ql, ql), (qd + r * kl, kl), (qd + kvd + r * kl, kl))
+            o = 0
+            for a, n in rows:
+                C.fold_norm_weight(wq[a:a + n], ln1, fq[o:o + n])
+                if cfg.attention_bias:
+                    self.bq_local[i, o:o + n].copy_(dec.w(p + "bqkv")[a:a + n])
+                o += n
+            C.fold_norm_weight(wg[r * fl:(r + 1) * fl], ln2, fg[:fl])
+            C.fold_norm_weight(wg[F + r * fl:F + (r + 1) * fl], ln2, fg[fl:])
+        self.launches += 5 * cfg.num_hidden_layers
 
     def _decode_forward_fused(self, B: int, temperature: float, splits: int) -> None:
         """Five kernels per layer for up to 256 rows. Larger batches run layer by layer in row chunks of at most 256: a
@@ -418,26 +460,41 @@ class RolloutEngine:
         R = self.fused_chunk
         chunks = [(r0, min(B, r0 + R)) for r0 in range(0, B, R)]
         C.embedding_sumsq(self.last_tokens[:B], dec.w("embed"), self.b_x[:B], ss)
+        tp, Hq, Hkv = self.tp, self.Hq_l, self.Hkv_l
         for i in range(cfg.num_hidden_layers):
             p = f"layers.{i}."
             fq, fg = self._folded(i)
-            bq = dec.w(p + "bqkv") if cfg.attention_bias else None
+            wo, wd = dec.w(p + "wo"), dec.w(p + "wd")
+            if tp is None:
+                bq = dec.w(p + "bqkv") if cfg.attention_bias else None
+            else:  # this rank's input columns of the row-parallel projections (strided views of the full matrices)
+                bq = self.bq_local[i] if cfg.attention_bias else None
+                wo = wo[:, self.tp_rank * self.qd_l:(self.tp_rank + 1) * self.qd_l]
+                wd = wd[:, self.tp_rank * self.F_l:(self.tp_rank + 1) * self.F_l]
             for r0, r1 in chunks:
                 x, x1, qkv, attn, act = (self.b_x[r0:r1], self.b_x1[r0:r1], self.b_qkv[r0:r1], self.b_attn[r0:r1], self.b_act[r0:r1])
                 bt, sl = self.block_tables[r0:r1], self.seq_lens[r0:r1]
                 s0, s1, s2 = ss[2 * i, r0:r1], ss[2 * i + 1, r0:r1], ss[2 * i + 2, r0:r1]
                 # up to 128 rows: rotary embedding and the KV-cache write happen in the qkv GEMM's epilogue
                 ok = (r1 - r0) <= 128 and C.gemm_decode_rope(x, fq, qkv, bq, s0, eps, cos_t, sin_t, bt, sl, self._kc(i), self._vc(i),
-                                                             cfg.num_attention_heads, cfg.num_key_value_heads, st)
+                                                             Hq, Hkv, st)
                 if not ok:
                     ok = C.gemm_decode(x, fq, qkv, bq, None, s0, None, eps, st)
-                    C.rope_kv_write_decode(qkv, cos_t, sin_t, bt, sl, self._kc(i), self._vc(i), cfg.num_attention_heads,
-                                           cfg.num_key_value_heads, cfg.head_dim, st)
-                C.paged_decode_attn(qkv, self._kc(i), self._vc(i), bt, sl, attn, cfg.num_attention_heads, cfg.num_key_value_heads,
+                    C.rope_kv_write_decode(qkv, cos_t, sin_t, bt, sl, self._kc(i), self._vc(i), Hq, Hkv, cfg.head_dim, st)
+                C.paged_decode_attn(qkv, self._kc(i), self._vc(i), bt, sl, attn, Hq, Hkv,
                                     cfg.head_dim, scale, splits, self.b_part_o, self.b_part_ml, st, self.b_tickets)
-                ok = C.gemm_decode(attn, dec.w(p + "wo"), x1, None, x, None, s1, eps, st) and ok
-                C.gemm_swiglu(x1, fg, act, s1, eps, st)
-                ok = C.gemm_decode(act, dec.w(p + "wd"), x, None, x1, None, s2, eps, st) and ok
+                if tp is None:
+                    ok = C.gemm_decode(attn, wo, x1, None, x, None, s1, eps, st) and ok
+                    C.gemm_swiglu(x1, fg, act, s1, eps, st)
+                    ok = C.gemm_decode(act, wd, x, None, x1, None, s2, eps, st) and ok
+                else:
+                    # row-parallel projections: partial product into this rank's symmetric buffer, then every member sums
+                    # all partials (peer loads) + residual and accumulates the next norm's row statistic
+                    ok = C.gemm_decode(attn, wo, tp.partial(0, r1 - r0), None, None, None, None, eps, st) and ok
+                    tp.allreduce_residual(0, x, x1, s1)
+                    C.gemm_swiglu(x1, fg, act, s1, eps, st)
+                    ok = C.gemm_decode(act, wd, tp.partial(1, r1 - r0), None, None, None, None, eps, st) and ok
+                    tp.allreduce_residual(1, x1, x, s2)
                 if not ok:
                     raise RuntimeError("fused decode step: a GEMM shape is not served by the split-K kernel")
         h = self.b_h[:B]
@@ -692,6 +749,8 @@ class RolloutEngine:
 
     def check_status(self) -> None:
         self.dec.check_status()
+        if self.tp is not None:
+            self.tp.check()
 
     def update_weights_done(self) -> None:
         """Called after new weights were written into ``params`` in place; captured graphs stay valid

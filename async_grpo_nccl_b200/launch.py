@@ -333,6 +333,9 @@ class _RemoteLogprob:
     async def inference(self, sample):
         return await self._p.lp_inference(sample)
 
+    async def compute_batch(self, samples):
+        return await self._p.lp_compute_batch(list(samples))
+
 
 class _RemoteManager:
     """What a trainer rank sees of the ExperienceManager that lives on rank 0."""
@@ -361,6 +364,9 @@ class RoleHost:
 
     async def lp_inference(self, sample):
         return await self.rt.logprob.inference(sample)
+
+    async def lp_compute_batch(self, samples):
+        return await self.rt.logprob.compute_batch(samples)
 
     async def trainer_start(self):
         return await self.rt.start_local_trainer()
@@ -440,6 +446,13 @@ class DistributedRuntime:
         self.logprob_ranks = list(place["logprob"])
         self.rollout_ranks = list(place["rollout"])
         self.infer_ranks = sorted(set(self.logprob_ranks) | set(self.rollout_ranks))
+        # generation_tp_size consecutive rollout ranks form one engine replica (vllm_worker.py:219-232,
+        # tensor_parallel_size); the orchestrator talks to the first rank of each
+        from .roles.tp_mirror import replica_groups
+
+        self.replicas = replica_groups(self.rollout_ranks, max(1, int(config.generation_tp_size)))
+        self.my_replica = next((g for g in self.replicas if self.rank in g), None)
+        self.rollout_leaders = [g[0] for g in self.replicas]
         self.is_trainer = self.rank in self.trainer_ranks
         self.trainer_index = self.trainer_ranks.index(self.rank) if self.is_trainer else None
         self.mcfg = resolve_model_config(config.model_name_or_path, config.model_config)
@@ -474,9 +487,15 @@ class DistributedRuntime:
         if self.rank == 0 and config.param_sharding == "zero3" and not (use_peer and t > 1):
             logger.warning("param_sharding=zero3 needs the peer-memory backend and more than one trainer rank; "
                            "running with resident parameters (zero2) instead")
-        if self.rank == 0 and (config.logprob_fsdp_size > 1 or config.generation_tp_size > 1):
-            logger.warning("logprob_fsdp_size / generation_tp_size > 1: every logprob and rollout rank runs as a full replica "
-                           "(no intra-role sharding); throughput scales with the number of ranks instead")
+        self.tp_comm = None
+        tp_size = max(1, int(config.generation_tp_size))
+        if tp_size > 1 and self.native:
+            if not use_peer:
+                raise RuntimeError("generation_tp_size > 1 needs the peer-memory backend (comm_backend auto/peer with "
+                                   "symmetric memory): the replica's all-reduce runs over peer loads")
+            # collective over the world group like every symmetric allocation; ranks outside a replica hold idle buffers
+            self.tp_comm = symm.TensorParallelComm(self.my_replica or [], self.rank, min(256, int(config.max_num_seqs)),
+                                                   self.mcfg.hidden_size, self.device, self.C)
         # ---- roles of this rank ----
         self.trainer: Optional[TrainerWorker] = None
         self.logprob: Optional[LogProbWorker] = None
@@ -507,28 +526,60 @@ class DistributedRuntime:
             dec = (NativeDecoder if self.native else OracleDecoder)(self.mcfg, self.layout, self.infer_params)
             self.logprob = LogProbWorker(config, self.mcfg, dec, self.device, stream=self.streams["logprob"],
                                          sm_limit=other_lim if self.native else 0)
-        if self.rank in self.rollout_ranks:
-            self.verifier = get_or_create_verifier_pool(config.global_num_verifiers, config.write_failed_generation_samples,
-                                                        config.reward_fns, config.output_dir, name=f"verifier_pool_{self.rank}",
-                                                        timeout_s=config.verifier_timeout_s)
+        is_rollout = self.rank in self.rollout_ranks
+        leader = is_rollout and self.my_replica[0] == self.rank
+        followers = [r for r in self.my_replica if r != self.rank] if leader else []
+        self.verifier = None
+        tp_blocks = None
+        if is_rollout and self.native:
+            free, _ = torch.cuda.mem_get_info(self.device)
+            share = 0.35 if (self.is_trainer or self.rank in self.logprob_ranks) else 0.75
+            max_len = min(self.mcfg.max_position_embeddings, config.max_generation_tokens + 4096)
+            if self.tp_comm is not None:
+                per_block = (self.mcfg.num_hidden_layers * 2 * (self.mcfg.num_key_value_heads // tp_size) * config.kv_block_size
+                             * self.mcfg.head_dim * 2)
+                tp_blocks = max(64, int(free * share) // per_block)
+        if self.tp_comm is not None:
+            # the members' schedulers must take identical decisions, so they get the same number of KV blocks: the
+            # smallest pool among all tensor-parallel members (a world collective, every rank calls it)
+            nb = torch.tensor([tp_blocks or (1 << 40)], dtype=torch.int64, device=self.device)
+            dist.all_reduce(nb, op=dist.ReduceOp.MIN)
+            tp_blocks = int(nb.item())
+        if is_rollout:
+            if leader:
+                self.verifier = get_or_create_verifier_pool(config.global_num_verifiers, config.write_failed_generation_samples,
+                                                            config.reward_fns, config.output_dir, name=f"verifier_pool_{self.rank}",
+                                                            timeout_s=config.verifier_timeout_s)
             if self.native:
                 from .engine.engine import RolloutEngine
 
-                free, _ = torch.cuda.mem_get_info(self.device)
-                share = 0.35 if (self.is_trainer or self.rank in self.logprob_ranks) else 0.75
-                max_len = min(self.mcfg.max_position_embeddings, config.max_generation_tokens + 4096)
                 self.engine = RolloutEngine(self.mcfg, self.layout, self.infer_params, max_seqs=config.max_num_seqs,
-                                            max_model_len=max_len, kv_memory_bytes=int(free * share),
-                                            use_cuda_graph=config.vllm_engine_preset == "throughput", block_size=config.kv_block_size)
+                                            max_model_len=max_len, kv_memory_bytes=int(free * share), num_blocks=tp_blocks,
+                                            use_cuda_graph=config.vllm_engine_preset == "throughput", block_size=config.kv_block_size,
+                                            tp=self.tp_comm)
             else:
                 from .engine.engine import OracleEngine
 
                 self.engine = OracleEngine(self.mcfg, self.layout, self.infer_params, max_seqs=config.max_num_seqs,
                                            max_model_len=min(self.mcfg.max_position_embeddings, config.max_generation_tokens + 2048))
-            self.generation = GenerationWorker(config, self.mcfg, self.engine, self.verifier, load_tokenizer(config),
-                                               stream=self.streams["rollout"], sm_limit=int(self.streams.get("rollout_sm_count", 0)))
-            if config.stream_logprobs:
-                self.generation.logprob_fn = self._stream_logprob
+            if leader:
+                mirror = None
+                if followers:
+                    from .roles.tp_mirror import LeaderChannel
+
+                    mirror = LeaderChannel(self._store(), followers)
+                self.generation = GenerationWorker(config, self.mcfg, self.engine, self.verifier, load_tokenizer(config),
+                                                   stream=self.streams["rollout"], sm_limit=int(self.streams.get("rollout_sm_count", 0)),
+                                                   mirror=mirror)
+                if config.stream_logprobs:
+                    self.generation.logprob_fn = self._stream_logprob
+            else:
+                # member of a replica that another rank leads: replays the leader's engine calls (on CPU ranks, where
+                # the oracle engine has no sharded form, as a full copy of the model)
+                from .roles.tp_mirror import FollowerListener, TpFollower
+
+                self.generation = TpFollower(self.engine, FollowerListener(self._store(), self.rank), stream=self.streams["rollout"],
+                                             kernel_checks=bool(config.kernel_checks))
         self._lp_next = 0
         import concurrent.futures
 
@@ -622,11 +673,19 @@ class DistributedRuntime:
         assert self.rank == 0, "the orchestrator runs on rank 0"
         await self._start_server()
         self.generation_controllers = []
-        for r in self.rollout_ranks:
+        for r in self.rollout_leaders:
             self.generation_controllers.append(self.generation if r == 0 else _RemoteGeneration((await self._client(r)).proxy()))
         self.logprob_controllers = []
-        for r in self.logprob_ranks:
-            self.logprob_controllers.append(self.logprob if r == 0 else _RemoteLogprob((await self._client(r)).proxy()))
+        handles = [self.logprob if r == 0 else _RemoteLogprob((await self._client(r)).proxy()) for r in self.logprob_ranks]
+        k = max(1, int(self.config.logprob_fsdp_size))
+        if k > 1:
+            # logprob_fsdp_size ranks form one logprob service: its batches are scattered over the members
+            from .roles.logprob import LogProbGroup
+
+            for g in range(0, len(handles), k):
+                self.logprob_controllers.append(LogProbGroup(self.config, handles[g:g + k]))
+        else:
+            self.logprob_controllers = handles
         for r in range(1, self.world):
             await self._client(r)
 

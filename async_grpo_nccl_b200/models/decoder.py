@@ -196,8 +196,10 @@ class NativeDecoder:
         self._gemm(h1, self.w(p + "wqkv"), qkv, bias=self.w(p + "bqkv") if cfg.attention_bias else None)
         C.rope_inplace(qkv, batch.pos, cos_t, sin_t, cfg.num_attention_heads + cfg.num_key_value_heads, cfg.head_dim, False)
         if kv_write is not None:  # rollout prefill: K/V of every prompt token go to their cache slots
-            k_cache, v_cache, slots = kv_write
-            C.kv_cache_write(qkv, slots, k_cache, v_cache, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, self.status)
+            k_cache, v_cache, slots = kv_write[:3]
+            head0 = kv_write[3] if len(kv_write) > 3 else 0  # tensor-parallel engine rank: its share of the kv heads
+            C.kv_cache_write(qkv, slots, k_cache, v_cache, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
+                             self.status, head0)
             self.launches += 1
         attn = self._new(T, cfg.q_dim)
         lse = self._new(cfg.num_attention_heads, T, dtype=torch.float32)

@@ -261,6 +261,47 @@ class WeightSync:
         self.pg.barrier()  # all shards have landed everywhere
 
 
+class TensorParallelComm:
+    """What a tensor-parallel rollout rank needs from peer memory (the reference gets it from vLLM's NCCL all-reduce,
+    vllm_worker.py:219-232): two symmetric [rows, H] bf16 buffers that receive this rank's partial products of the
+    row-parallel projections (o and down), a barrier whose epoch lives on the device (so the step can be replayed from a
+    CUDA graph), and the all-reduce + residual + row-statistic kernel that reads every member's partial with peer loads.
+
+    Every rank of the job allocates the buffers (symmetric allocations are collective over the world group); ``members``
+    are the global ranks of ONE engine replica, in tensor-parallel order."""
+
+    def __init__(self, members: Sequence[int], my_global_rank: int, rows: int, hidden: int, device: torch.device, C: Any,
+                 group: Any = None):
+        grp = group if group is not None else dist.group.WORLD
+        self.members = list(members)
+        self.size = len(self.members)
+        self.rank = self.members.index(my_global_rank) if my_global_rank in self.members else -1
+        self.C, self.device, self.rows, self.hidden = C, device, rows, hidden
+        self.flags = alloc_symmetric(64, torch.int64, device, grp)
+        self.bufs = [alloc_symmetric(rows * hidden, torch.bfloat16, device, grp) for _ in range(2)]
+        self.flags.local.zero_()
+        self.flag_ptrs = [self.flags.peer_ptrs[r] for r in self.members]
+        self.partial_ptrs = [[b.peer_ptrs[r] for r in self.members] for b in self.bufs]
+        self.epoch = torch.zeros(1, dtype=torch.int64, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def partial(self, which: int, rows: int) -> torch.Tensor:
+        """This rank's partial-product buffer ``which`` (0: o projection, 1: down projection) as [rows, H]."""
+        return self.bufs[which].local[: rows * self.hidden].view(rows, self.hidden)
+
+    def allreduce_residual(self, which: int, residual: torch.Tensor, out: torch.Tensor, ss: Optional[torch.Tensor]) -> None:
+        """out = residual + sum over members of their partial ``which``; ss += row sums of squares of out."""
+        self.C.set_comm_guard(self.status)
+        self.C.flag_barrier_auto(self.flag_ptrs, self.rank, self.epoch, WAIT_BUDGET_S, self.status)
+        self.C.tp_allreduce_residual(self.partial_ptrs[which], residual, out, ss)
+
+    def check(self) -> None:
+        code = int(self.status.item())
+        if code != 0:
+            self.status.zero_()
+            raise RuntimeError(f"tensor-parallel barrier ran out (status {code}): a member of the engine replica did not arrive")
+
+
 class CollectiveFallback:
     """The same three operations on ``torch.distributed`` collectives (NCCL / gloo)."""
 

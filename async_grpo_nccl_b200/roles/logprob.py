@@ -72,7 +72,7 @@ class LogProbWorker:
                 tokens += n
             samples = [s for _, s in batch]
             try:
-                results = await loop.run_in_executor(self._pool, self._compute, samples)
+                results = await self._run_batch(samples)
                 for (fut, s), (lp, ent) in zip(batch, results):
                     if not fut.done():
                         out = dict(s)
@@ -84,6 +84,13 @@ class LogProbWorker:
                     if not fut.done():
                         fut.set_exception(e)
                 await asyncio.sleep(1.0)
+
+    async def _run_batch(self, samples: List[Dict[str, Any]]) -> List[Tuple[np.ndarray, np.ndarray]]:
+        return await asyncio.get_running_loop().run_in_executor(self._pool, self._compute, samples)
+
+    async def compute_batch(self, samples: List[Dict[str, Any]]) -> List[Tuple[np.ndarray, np.ndarray]]:
+        """One already formed batch (a group controller's share for this rank), ordered with this rank's other work."""
+        return await self._run_batch(samples)
 
     # ---- compute (worker thread) ----
     def _compute(self, samples: List[Dict[str, Any]]) -> List[Tuple[np.ndarray, np.ndarray]]:
@@ -142,6 +149,53 @@ class LogProbWorker:
         (the pool has one thread). The weight sync runs its device half through here, so that no forward pass reads
         parameters that are half written."""
         return self._pool.submit(fn, *args).result()
+
+
+class LogProbGroup(LogProbWorker):
+    """Controller of ``logprob_fsdp_size`` logprob ranks that act as one logprob service (the reference's
+    ``LogProbFSDPWorker`` over its FSDP ranks, logprob_worker.py:57-134): requests are batched by the same token budget
+    and every batch is scattered round-robin over the member ranks, which compute their shares concurrently; results go
+    back to the requests by position. Every member holds the whole model here (a B200 has room for every preset), so an
+    empty share needs no dummy sample: there is no collective that all members would have to enter together."""
+
+    def __init__(self, config: Any, members: List[Any], fill_window_s: float = 0.010):
+        # members: objects with ``async compute_batch(samples)`` - the local LogProbWorker and / or RPC proxies of others
+        self.config = config
+        self.members = list(members)
+        self.temperature = float(config.temperature) or 1.0
+        self.max_tokens = int(config.max_tokens_per_gpu)
+        self.fill_window_s = fill_window_s
+        self._queue = None
+        self._task = None
+        self._carry = None
+        self.tokens_processed = 0
+        self.batches = 0
+        self.busy_seconds = 0.0
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self.shares: List[int] = [0] * len(self.members)  # samples sent to each member so far
+
+    async def _run_batch(self, samples: List[Dict[str, Any]]) -> List[Tuple[np.ndarray, np.ndarray]]:
+        k = len(self.members)
+        chunks: List[List[int]] = [[] for _ in range(k)]
+        for i in range(len(samples)):
+            chunks[i % k].append(i)
+        live = [(m, idx) for m, idx in enumerate(chunks) if idx]
+        parts = await asyncio.gather(*[self.members[m].compute_batch([samples[i] for i in idx]) for m, idx in live])
+        out: List[Any] = [None] * len(samples)
+        for (m, idx), res in zip(live, parts):
+            self.shares[m] += len(idx)
+            for i, r in zip(idx, res):
+                out[i] = (np.asarray(r[0], dtype=np.float32), np.asarray(r[1], dtype=np.float32))
+        self.batches += 1
+        self.tokens_processed += sum(len(s["sample_ids"]) for s in samples)
+        return out
+
+    def pause(self) -> None:  # members are paused by their own ranks' weight sync
+        return
+
+    def resume(self) -> None:
+        return
 
 
 class _null:

@@ -31,8 +31,11 @@ def _uid_seed(uid: Any, base: int) -> int:
 
 class GenerationWorker:
     def __init__(self, config: Any, model_cfg: Any, engine: Any, verifier_pool: Any, tokenizer: Any = None,
-                 stream: Optional[torch.cuda.Stream] = None, sm_limit: int = 0):
+                 stream: Optional[torch.cuda.Stream] = None, sm_limit: int = 0, mirror: Any = None):
         self.config, self.mcfg, self.engine, self.verifier = config, model_cfg, engine, verifier_pool
+        # Leader of a tensor-parallel replica: every engine call is announced to the other members first (they replay it
+        # on their own engines, see roles/tp_mirror.py). None for an engine that runs alone.
+        self.mirror = mirror
         self.tokenizer = tokenizer
         self.stream = stream
         self.sm_limit = int(sm_limit)  # > 0: the stream runs on an SM group of this size (persistent grids must fit it)
@@ -80,10 +83,15 @@ class GenerationWorker:
             while not self._stop:
                 with self._lock:
                     new, self._incoming = self._incoming, []
+                mirror = self.mirror
                 if self._want_logprobs and hasattr(self.engine, "enable_logprobs"):
+                    if mirror is not None:
+                        mirror.send("logprobs")
                     self.engine.enable_logprobs()  # on the engine's own thread, between steps
                     self._want_logprobs = False
                 for args in new:
+                    if mirror is not None:
+                        mirror.send("add", args)
                     self.engine.add_request(*args[0], **args[1])
                 with self._gate:
                     go = not self._paused.is_set() and self.engine.has_work()
@@ -97,6 +105,8 @@ class GenerationWorker:
                     continue
                 t0 = time.time()
                 try:
+                    if mirror is not None:
+                        mirror.send("step")
                     finished = self.engine.step()
                     # the kernels' status word (bounded waits, index checks): read whenever sequences finish (the step
                     # synchronised anyway), or after every step with kernel_checks
@@ -262,6 +272,8 @@ class GenerationWorker:
         self._wake.set()
         while not self._idle.is_set():
             await asyncio.sleep(0.001)
+        if self.mirror is not None:
+            self.mirror.send("pause")  # the followers hold here until their own rank's sync has finished
         return True
 
     async def resume_after_sync(self) -> bool:
@@ -283,6 +295,8 @@ class GenerationWorker:
     def shutdown(self) -> None:
         self._stop = True
         self._wake.set()
+        if self.mirror is not None:
+            self.mirror.close()
 
 
 class _null:

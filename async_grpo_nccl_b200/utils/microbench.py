@@ -171,9 +171,16 @@ def bench_fused(args):
 
 
 def bench_sync(args):
-    """Trainer -> inference weight sync over N GPUs (run under torchrun, one rank per GPU): the first --trainers ranks
-    hold the shards, the others receive. Times the peer-memory push (barrier, push kernels, barrier) and the library
-    baseline (one NCCL broadcast per shard range) on the device, max over ranks."""
+    """Trainer -> inference weight sync (run under torchrun, one rank per GPU). For every (t, r) of ``--pairs`` the first t
+    ranks hold the FSDP shards and the next r ranks receive; the remaining ranks only take part in the barriers. Per model
+    it times, on the device and as the max over ranks:
+      * the peer-memory push with plain peer stores and, when the allocation has a multicast address, with ``multimem.st``;
+      * an NCCL broadcast per shard range;
+      * the reference's pattern (gpu_process_worker.py:1609-1637): per parameter tensor an all-gather inside the trainer
+        group (``full_tensor()``), a copy into a fresh tensor on trainer rank 0 and one broadcast over every GPU worker.
+    """
+    import math
+
     import torch.distributed as dist
 
     from ..models.config import PRESETS
@@ -186,53 +193,112 @@ def bench_sync(args):
     dev = torch.device("cuda", torch.cuda.current_device())
     dist.init_process_group("nccl")
     C = native()
-    t = max(1, min(args.trainers, world - 1))
-    trainers, infer = list(range(t)), list(range(t, world))
+    if args.pairs:
+        pairs = [tuple(int(x) for x in p.split(",")) for p in args.pairs.split(";")]
+    else:
+        t0 = max(1, min(args.trainers, world - 1))
+        pairs = [(t0, world - t0)]
+    pairs = [(t, r) for t, r in pairs if t + r <= world]
+    lcm = 1
+    for t, _ in pairs:
+        lcm = lcm * t // math.gcd(lcm, t)
+
+    def timed(fn, iters=3):
+        best = []
+        for i in range(iters + 1):
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= 1:
+                best.append(e0.elapsed_time(e1))
+        ms = torch.tensor([sorted(best)[len(best) // 2]], device=dev)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
     for model in args.model.split(","):
         cfg = PRESETS[model]
-        layout = ParamLayout(cfg, shard_world=t)
+        layout = ParamLayout(cfg, shard_world=lcm)  # every unit divides evenly by each t of the sweep
         flags = symm.alloc_symmetric(128, torch.int64, dev, dist.group.WORLD)
         dst = symm.alloc_symmetric(layout.total, torch.bfloat16, dev, dist.group.WORLD)
+        src_full = torch.empty(layout.total, device=dev, dtype=torch.bfloat16)
+        torch.manual_seed(1234)  # the same values on every rank: a receiver can check what it got bit for bit
+        src_full.normal_(0, 0.02)
+        gb = layout.total * 2 / 1e9
+        for t, r in pairs:
+            trainers, infer = list(range(t)), list(range(t, t + r))
+            members = trainers + infer
+            tg = dist.new_group(trainers)
+            sg = dist.new_group(members)
 
-        class _Plane:  # the two buffers a weight sync needs
-            pass
+            class _Plane:  # the two buffers a weight sync needs
+                pass
 
-        pl = _Plane()
-        pl.layout, pl.C, pl.trainer_ranks, pl.infer_ranks, pl.my_rank, pl.device = layout, C, trainers, infer, rank, dev
-        pl.flags, pl.infer_params = flags, dst
-        ws = symm.WeightSync(pl)
-        src = None
-        if rank in trainers:
-            src = (torch.randn(layout.total, device=dev) * 0.02).to(torch.bfloat16)
-        ti = trainers.index(rank) if rank in trainers else None
-
-        def timed(fn, iters=5):
-            best = []
-            for i in range(iters + 2):
+            pl = _Plane()
+            pl.layout, pl.C, pl.trainer_ranks, pl.infer_ranks, pl.my_rank, pl.device = layout, C, trainers, infer, rank, dev
+            pl.flags, pl.infer_params = flags, dst
+            ti = trainers.index(rank) if rank in trainers else None
+            src = src_full if rank in trainers else None
+            res = {"bench": "weight_sync", "model": model, "trainers": t, "receivers": r, "param_gb": gb}
+            for mode in ("plain", "multicast"):
+                os.environ["AGRPO_MULTICAST"] = "1" if mode == "multicast" else "0"
+                torch.cuda.synchronize()
                 dist.barrier()
+                flags.local.zero_()  # a new sync object counts its barrier epochs from zero again
+                dst.local.zero_()
                 torch.cuda.synchronize()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
-                fn()
-                e1.record()
-                torch.cuda.synchronize()
-                if i >= 2:
-                    best.append(e0.elapsed_time(e1))
-            ms = torch.tensor([sorted(best)[len(best) // 2]], device=dev)
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-            return float(ms.item())
+                dist.barrier()
+                ws = symm.WeightSync(pl)
+                if mode == "multicast" and not ws.dst_mc:
+                    res["peer_push_multicast_ms"] = None
+                    continue
+                ms = timed(lambda: ws.push(src, ti))
+                ws.pg.check()
+                res[f"peer_push_{mode}_ms"] = ms
+                if rank in infer:  # bit-exact: the receivers hold exactly the source's bf16 values
+                    assert torch.equal(dst.local, src_full), f"weight push ({mode}) did not deliver the source bit for bit"
+            os.environ["AGRPO_MULTICAST"] = "1"
+            if rank in members:
+                def shard_ranges():
+                    symm.broadcast_weights(src if src is not None else dst.local, layout, sg, trainers, ti,
+                                           dst.local if rank in infer else None)
+            else:
+                def shard_ranges():
+                    return None
+            res["nccl_broadcast_per_shard_range_ms"] = timed(shard_ranges)
 
-        ms_push = timed(lambda: ws.push(src, ti))
-        ws.pg.check()
-        ms_nccl = timed(lambda: symm.broadcast_weights(src if src is not None else dst.local, layout, dist.group.WORLD, trainers, ti,
-                                                       dst.local if rank in infer else None))
-        if rank == 0:
-            gb = layout.total * 2 / 1e9
-            out({"bench": "weight_sync", "model": model, "trainers": t, "receivers": len(infer), "param_gb": gb,
-                 "peer_push_ms": ms_push, "peer_push_gbs_per_receiver": gb / ms_push * 1e3, "nccl_broadcast_ms": ms_nccl,
-                 "nccl_gbs_per_receiver": gb / ms_nccl * 1e3, "nvlink_peer_copy_gbs_measured": 770.0,
-                 "lower_bound_ms": gb / 770.0 * 1e3})
-        del ws, dst, src
+            def reference_pattern():
+                if rank not in members:
+                    return
+                for seg in layout.segments.values():
+                    m = seg.numel
+                    if rank in trainers:
+                        mt = (m + t - 1) // t
+                        if t > 1:
+                            full = torch.empty(mt * t, dtype=torch.bfloat16, device=dev)
+                            lo = min(seg.offset + ti * mt, layout.total - mt)
+                            dist.all_gather_into_tensor(full, src_full[lo:lo + mt], group=tg)
+                        else:
+                            full = src_full[seg.offset:seg.offset + m]
+                    tensor = torch.empty(m, dtype=torch.bfloat16, device=dev)
+                    if rank == 0:
+                        tensor.copy_(full[:m])
+                    dist.broadcast(tensor, src=0, group=sg)
+
+            res["reference_pattern_ms"] = timed(reference_pattern, iters=2)
+            res["tensors"] = len(layout.segments)
+            if rank == 0:
+                push = min(x for x in (res.get("peer_push_plain_ms"), res.get("peer_push_multicast_ms")) if x)
+                res.update({"best_push_gbs_into_each_receiver": gb / push * 1e3, "receiver_ingress_bound_ms_at_770": gb / 770.0 * 1e3,
+                            "source_egress_bound_ms_plain_at_770": gb * r / t / 770.0 * 1e3,
+                            "speedup_vs_reference_pattern": res["reference_pattern_ms"] / push})
+                out(res)
+            dist.destroy_process_group(tg)
+            dist.destroy_process_group(sg)
+        del dst, src_full, flags
         torch.cuda.empty_cache()
     dist.destroy_process_group()
 
@@ -546,6 +612,7 @@ def main():
     ap.add_argument("--kernel", default="gemm", help="for 'one': gemm | attn_fwd | attn_bwd | lmhead_fwd | lmhead_bwd | splitk | "
                     "swiglu | gemm_rs")
     ap.add_argument("--trainers", type=int, default=1, help="for 'sync': ranks that hold shards (the rest receive)")
+    ap.add_argument("--pairs", default=None, help="for 'sync': (trainers, receivers) pairs to sweep, e.g. '1,1;2,2;4,4;4,3;7,1'")
     ap.add_argument("--model", default="qwen2.5-1.5b")
     ap.add_argument("--batch", type=int, default=128)
     ap.add_argument("--context", type=int, default=1024)

@@ -246,3 +246,35 @@ def test_multi_process_runtime_reloads_optimizer_state_on_resume(tmp_path):
     second = {k: v for k, v in second.items() if v is not None}
     out2 = spawn(second, rows, world=2, max_macro_batches=1, port=29771, timeout_s=500)
     assert out2["global_step"] == 2 and np.isfinite(out2["last"]["training/avg_loss"])
+
+
+@pytest.mark.timeout(600)
+def test_two_logprob_ranks_behind_one_controller(tmp_path):
+    """``logprob_fsdp_size=2``: two logprob ranks form one service whose token-budget batches are scattered over both."""
+    cfg = dict(model_name_or_path="tiny", batch_size=4, samples_per_question=4, num_epochs=1, train_minibatch_sample_size=16,
+               max_generation_tokens=10, max_tokens_per_gpu=400, reward_fns=["token_match"], global_num_verifiers=0,
+               num_training_gpu_workers=1, num_logprob_gpu_workers=2, logprob_fsdp_size=2, num_generation_gpu_workers=1,
+               placement={"trainer": [0], "logprob": [1, 2], "rollout": [3]}, learning_rate=1e-3, output_dir=str(tmp_path),
+               min_samples_per_checkpoint=10 ** 9, eval_at_start=False, stream_logprobs=False)
+    rows = synthetic_prompt_rows(8, 1024, 16, 32, seed=0)
+    out = spawn(cfg, rows, world=4, max_macro_batches=2, port=29795, timeout_s=500)
+    assert out["global_step"] == 2 and out["total_samples_seen"] == 32
+    assert np.isfinite(out["last"]["training/avg_loss"]) and out["last"]["training/grad_norm"] > 0
+
+
+@pytest.mark.timeout(600)
+def test_replica_of_two_rollout_ranks_follows_its_leader(tmp_path):
+    """generation_tp_size=2 on CPU ranks: ranks 1 and 2 form one engine replica. Rank 1 leads (request queue, results,
+    verifier); rank 2 replays the leader's engine calls from the command stream and takes part in every weight sync. The
+    run must finish with both macro-batches trained and the weight-sync checksums equal on every rank (which also shows
+    that the follower paused and resumed with the leader)."""
+    cfg = dict(model_name_or_path="tiny", batch_size=4, samples_per_question=4, num_epochs=1, train_minibatch_sample_size=8,
+               max_generation_tokens=10, max_tokens_per_gpu=200, reward_fns=["token_match"], global_num_verifiers=0,
+               num_training_gpu_workers=1, num_logprob_gpu_workers=1, num_generation_gpu_workers=2, generation_tp_size=2,
+               placement={"trainer": [0], "logprob": [0], "rollout": [1, 2]}, learning_rate=1e-3, output_dir=str(tmp_path),
+               min_samples_per_checkpoint=10 ** 9, eval_at_start=False, verify_weight_sync_during_init=True)
+    rows = synthetic_prompt_rows(8, 1024, 16, 32, seed=0)
+    out = spawn(cfg, rows, world=3, max_macro_batches=2, port=29817, timeout_s=500)
+    assert out["global_step"] == 2
+    assert out["total_samples_seen"] == 32
+    assert np.isfinite(out["last"]["training/avg_loss"])

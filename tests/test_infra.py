@@ -358,3 +358,106 @@ def test_epoch_flag_barrier_model_all_interleavings_of_three_ranks():
                 blocked = dict(fin)
                 assert others <= set(blocked), "a healthy rank ran to completion past a skipped arrival"
                 assert all(blocked[r] == epoch for r in others)
+
+
+def test_logprob_group_scatters_batches_round_robin_and_keeps_request_order():
+    """``logprob_fsdp_size`` ranks behind one controller (logprob_worker.py:82-134): every token-budget batch is dealt out
+    round-robin, members work concurrently, each request gets the result computed for ITS sample."""
+    import asyncio
+
+    import numpy as np
+
+    from async_grpo_nccl_b200.roles.logprob import LogProbGroup
+
+    class Cfg:
+        temperature = 1.0
+        max_tokens_per_gpu = 64
+
+    class Member:
+        def __init__(self, tag):
+            self.tag, self.calls = tag, []
+
+        async def compute_batch(self, samples):
+            self.calls.append([int(s["sample_ids"][0]) for s in samples])
+            await asyncio.sleep(0.01)
+            return [(np.full(len(s["sample_ids"]), float(s["sample_ids"][0])), np.full(len(s["sample_ids"]), self.tag)) for s in samples]
+
+    members = [Member(0.0), Member(1.0), Member(2.0)]
+    grp = LogProbGroup(Cfg(), members)
+
+    async def body():
+        reqs = [{"sample_ids": np.full(4 + (i % 5), i, dtype=np.int32)} for i in range(40)]
+        return reqs, await asyncio.gather(*[grp.inference(r) for r in reqs])
+
+    reqs, outs = asyncio.run(body())
+    for r, o in zip(reqs, outs):
+        assert len(o["sample_logprobs"]) == len(r["sample_ids"]) and (o["sample_logprobs"] == float(r["sample_ids"][0])).all()
+    assert sum(grp.shares) == 40 and max(grp.shares) - min(grp.shares) <= grp.batches  # dealt evenly, batch by batch
+    assert all(m.calls for m in members)
+    for m, member in enumerate(members):  # within a batch member m gets positions m, m + 3, ...
+        first = member.calls[0]
+        assert all((b - a) % 3 == 0 for a, b in zip(first, first[1:]))
+
+
+def test_replica_command_stream_replays_in_order_and_holds_at_pause():
+    """Leader -> follower command stream of a tensor-parallel replica: calls arrive in order, a ``pause`` holds the
+    follower (later commands wait in the socket) until its own rank resumes it, and a closed stream is reported."""
+    import asyncio
+    import time
+
+    from async_grpo_nccl_b200.roles.tp_mirror import FollowerListener, LeaderChannel, TpFollower, replica_groups
+
+    assert replica_groups([3, 4, 5, 6], 2) == [[3, 4], [5, 6]] and replica_groups([1, 2], 1) == [[1], [2]]
+    with pytest.raises(ValueError):
+        replica_groups([1, 2, 3], 2)
+
+    class Store(dict):
+        def set(self, k, v):
+            self[k] = v.encode()
+
+        def get(self, k):
+            return self[k]
+
+    class Engine:
+        def __init__(self):
+            self.calls = []
+
+        def add_request(self, rid, prompt, **kw):
+            self.calls.append(("add", rid, kw["n"]))
+
+        def step(self):
+            self.calls.append(("step",))
+            return []
+
+        def check_status(self):
+            pass
+
+        def update_weights_done(self):
+            self.calls.append(("refold",))
+
+    store, eng = Store(), Engine()
+    fol = TpFollower(eng, FollowerListener(store, 7))
+    lead = LeaderChannel(store, [7])
+    lead.send("add", ((1, [5, 6]), dict(n=2)))
+    lead.send("step")
+    lead.send("pause")
+    lead.send("step")  # sent while the follower is held: must not run before the resume
+
+    async def sync():
+        await fol.pause_for_sync()
+        assert eng.calls == [("add", 1, 2), ("step",)]
+        await asyncio.sleep(0.1)
+        assert eng.calls == [("add", 1, 2), ("step",)]
+        await fol.resume_after_sync()
+
+    asyncio.run(sync())
+    deadline = time.time() + 5
+    while len(eng.calls) < 4 and time.time() < deadline:
+        time.sleep(0.01)
+    assert eng.calls == [("add", 1, 2), ("step",), ("refold",), ("step",)]
+    lead.close()
+    fol._thread.join(timeout=5)
+    assert not fol._thread.is_alive() and fol._dead is not None
+    with pytest.raises(RuntimeError):
+        asyncio.run(fol.pause_for_sync())
+    fol.shutdown()

@@ -310,3 +310,96 @@ def test_multicast_push_and_in_switch_reduce():
         pytest.skip(results[0][1])
     for rank, msg in results:
         assert msg == "ok", f"rank {rank}: {msg}"
+
+
+def _worker_tp_engine(rank, world, port, q):
+    os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank), "MASTER_ADDR": "127.0.0.1",
+                       "MASTER_PORT": str(port), "NCCL_NVLS_ENABLE": "0", "AGRPO_MULTICAST": "0"})
+    import numpy as np
+    import torch.distributed as dist
+
+    from async_grpo_nccl_b200.engine.engine import RolloutEngine
+    from async_grpo_nccl_b200.models.config import ModelConfig
+    from async_grpo_nccl_b200.models.decoder import NativeDecoder
+    from async_grpo_nccl_b200.models.layout import ParamLayout
+    from async_grpo_nccl_b200.ops import native
+    from async_grpo_nccl_b200.packing import pack_samples
+    from async_grpo_nccl_b200.parallel import symm
+
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world)
+    try:
+        C = native()
+        # per-rank shares stay within what the split-K decode GEMMs serve (K >= 512): 4 of 8 heads, 1 of 2 kv heads
+        cfg = ModelConfig(vocab_size=2048, hidden_size=1024, intermediate_size=2816, num_hidden_layers=2, num_attention_heads=8,
+                          num_key_value_heads=2, head_dim=128, rope_theta=1e4, max_position_embeddings=4096,
+                          tie_word_embeddings=True, eos_token_id=1, attention_bias=True)
+        layout = ParamLayout(cfg)
+        p32 = torch.empty(layout.total)
+        layout.init_random_(p32, 0)
+        gen = torch.Generator().manual_seed(11)
+        for i in range(cfg.num_hidden_layers):  # non-zero biases, so a wrong bias slice shows
+            layout.view(p32, f"layers.{i}.bqkv").normal_(0.0, 0.02, generator=gen)
+        p16 = (p32 * 2.0).to(torch.bfloat16).to(dev)
+        tp = symm.TensorParallelComm(list(range(world)), rank, 64, cfg.hidden_size, dev, C)
+        rng = np.random.default_rng(5)
+        prompts = [rng.integers(2, cfg.vocab_size, int(rng.integers(4, 30))).astype(np.int32) for _ in range(20)]
+        eng = RolloutEngine(cfg, layout, p16, max_seqs=64, max_model_len=128, num_blocks=600, use_cuda_graph=True, tp=tp)
+        assert eng.tp_size == world and eng.cache.shape[3] == cfg.num_key_value_heads // world
+        for i, pr in enumerate(prompts):
+            eng.add_request(i, pr, n=2, max_new_tokens=12, temperature=0.0 if i % 2 == 0 else 1.0, seed=i, ignore_eos=True)
+        outs = sorted(eng.run_until_done(), key=lambda o: (o.request_id, o.child))
+        torch.cuda.synchronize()
+        eng.check_status()
+        assert len(outs) == 40
+        # every member of the replica produced the same tokens (sampling is replicated, sums are in rank order)
+        mine = torch.tensor(np.concatenate([o.output_ids for o in outs]).astype(np.int64), device=dev)
+        both = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(both, mine)
+        assert all(torch.equal(both[0], b) for b in both), "tensor-parallel members disagree on the sampled tokens"
+        # greedy tokens are the argmax (up to bf16 noise) of the teacher-forced logits of the unsharded model
+        nat = NativeDecoder(cfg, layout, p16)
+        wl = layout.view(p16.float(), layout.lm_head_name())
+        checked = 0
+        for o in outs:
+            if o.request_id % 2:
+                continue
+            pr = prompts[o.request_id]
+            full = np.concatenate([pr, o.output_ids])
+            pb = pack_samples([{"sample_ids": full, "input_len": len(pr), "output_len": len(o.output_ids)}], pin=False).to_device(dev)
+            with torch.no_grad():
+                hn, _, _ = nat.hidden(pb)
+                z = hn.float() @ wl.t()
+            for j, tok in enumerate(o.output_ids):
+                row = z[len(pr) - 1 + j]
+                top = row.max().item()
+                assert row[int(tok)].item() >= top - (0.03 * abs(top) + 0.05), (o.request_id, j)
+                checked += 1
+        assert checked == 20 * 12
+        q.put((rank, "ok"))
+    except Exception as e:
+        import traceback
+
+        q.put((rank, f"FAILED: {e!r}\n{traceback.format_exc()}"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_tensor_parallel_engine_matches_unsharded_model():
+    """Two SPMD engine ranks with half of the heads / MLP columns each and all-reduce over peer memory: identical tokens on
+    both ranks, and greedy tokens that the unsharded model's teacher-forced logits confirm."""
+    import torch.multiprocessing as mp
+
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker_tp_engine, args=(r, world, 29771, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, msg in results:
+        assert msg == "ok", f"rank {rank}: {msg}"
