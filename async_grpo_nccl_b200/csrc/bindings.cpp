@@ -703,23 +703,23 @@ void rs_pull_sumsq(const PtrList& grad_ptrs, int64_t my_rank, int64_t global_off
   agrpo::launch_rs_pull_sumsq(lptr(grad_ptrs), (int)grad_ptrs.size(), (int)my_rank, global_off, local_off, n,
                               out.data_ptr<float>(), norm_sq.data_ptr<float>(), cur_stream());
 }
-void flag_barrier_auto(const PtrList& flag_ptrs, int64_t my_rank, Tensor& epoch_counter, double budget_s, Tensor& status) {
-  check_i64(epoch_counter, "epoch_counter"); check_i32(status, "status");
-  const c10::cuda::CUDAGuard guard(status.device());
-  agrpo::launch_flag_barrier_auto(lptr(flag_ptrs), (int)flag_ptrs.size(), (int)my_rank,
-                                  reinterpret_cast<unsigned long long*>(epoch_counter.data_ptr<int64_t>()), budget_s,
-                                  status.data_ptr<int>(), cur_stream());
-}
-void tp_allreduce_residual(const PtrList& partial_ptrs, const Tensor& residual, Tensor& out, const OptTensor& ss) {
-  check_bf16(residual, "residual"); check_bf16(out, "out");
+void tp_allreduce_residual(const PtrList& partial_ptrs, const PtrList& flag_ptrs, int64_t my_rank, Tensor& epoch_counter,
+                           Tensor& arrive, const Tensor& residual, Tensor& out, const OptTensor& ss, double budget_s, Tensor& status) {
+  check_bf16(residual, "residual"); check_bf16(out, "out"); check_i64(epoch_counter, "epoch_counter"); check_i32(arrive, "arrive");
+  check_i32(status, "status");
   TORCH_CHECK(residual.dim() == 2 && residual.is_contiguous() && out.is_contiguous() && out.sizes() == residual.sizes(), "tp_allreduce: [rows, H]");
   TORCH_CHECK(residual.size(1) % 8 == 0 && (reinterpret_cast<uintptr_t>(residual.data_ptr()) & 15) == 0 &&
               (reinterpret_cast<uintptr_t>(out.data_ptr()) & 15) == 0, "tp_allreduce: alignment");
+  TORCH_CHECK(partial_ptrs.size() == flag_ptrs.size() && my_rank >= 0 && my_rank < (int64_t)partial_ptrs.size(), "tp_allreduce: members");
   for (auto ptr : partial_ptrs) TORCH_CHECK(ptr != 0 && (ptr & 15) == 0, "tp_allreduce: partial buffers");
+  for (auto ptr : flag_ptrs) TORCH_CHECK(ptr != 0 && (ptr & 7) == 0, "tp_allreduce: flag rows");
   if (ss.has_value() && ss->defined()) { check_i64(*ss, "ss"); TORCH_CHECK(ss->is_contiguous() && ss->numel() >= residual.size(0), "ss [rows]"); }
   const c10::cuda::CUDAGuard guard(residual.device());
-  agrpo::launch_tp_allreduce_residual(lptr(partial_ptrs), (int)partial_ptrs.size(), residual.data_ptr(), out.data_ptr(),
-                                      opt_i64(ss), (int)residual.size(0), (int)residual.size(1), cur_stream());
+  agrpo::launch_tp_allreduce_residual(lptr(partial_ptrs), lptr(flag_ptrs), (int)partial_ptrs.size(), (int)my_rank,
+                                      reinterpret_cast<unsigned long long*>(epoch_counter.data_ptr<int64_t>()),
+                                      reinterpret_cast<unsigned int*>(arrive.data_ptr<int>()), residual.data_ptr(), out.data_ptr(),
+                                      opt_i64(ss), (int)residual.size(0), (int)residual.size(1), budget_s, status.data_ptr<int>(),
+                                      cur_stream());
 }
 void set_comm_guard(const c10::optional<Tensor>& status) {
   if (status.has_value()) {
@@ -958,9 +958,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rs_pull_sumsq", &rs_pull_sumsq, NOGIL);
   m.def("publish_norm", &publish_norm, NOGIL);
   m.def("set_comm_guard", &set_comm_guard, py::arg("status") = py::none());
-  m.def("flag_barrier_auto", &flag_barrier_auto, NOGIL);
-  m.def("tp_allreduce_residual", &tp_allreduce_residual, py::arg("partial_ptrs"), py::arg("residual"), py::arg("out"),
-        py::arg("ss") = py::none(), NOGIL);
+  m.def("tp_allreduce_residual", &tp_allreduce_residual, py::arg("partial_ptrs"), py::arg("flag_ptrs"), py::arg("my_rank"),
+        py::arg("epoch_counter"), py::arg("arrive"), py::arg("residual"), py::arg("out"), py::arg("ss") = py::none(),
+        py::arg("budget_s") = 10.0, py::arg("status"), NOGIL);
   m.def("adamw_push", &adamw_push, NOGIL);
   m.def("sumsq", &sumsq, NOGIL);
   m.def("adamw_step", &adamw_step, py::arg("p"), py::arg("m"), py::arg("v"), py::arg("g"), py::arg("p16") = py::none(),

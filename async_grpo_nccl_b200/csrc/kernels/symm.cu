@@ -62,63 +62,98 @@ __global__ void flag_barrier_kernel(PeerPtrs flags, int my_rank, uint64_t epoch,
   }
 }
 
-// The same barrier with its epoch kept on the device: *epoch_counter is incremented by the kernel itself, so the launch has
-// no per-call argument and can be replayed from a CUDA graph (every rank replays the same number of barriers).
-__global__ void flag_barrier_auto_kernel(PeerPtrs flags, int my_rank, unsigned long long* epoch_counter, long long budget,
-                                         int* status) {
-  __shared__ unsigned long long s_epoch;
-  if (threadIdx.x == 0) s_epoch = ++(*epoch_counter);
-  __syncthreads();
-  const uint64_t epoch = s_epoch;
-  const int r = threadIdx.x;
-  if (r < flags.n) {
-    __threadfence_system();
-    st_release_sys(reinterpret_cast<uint64_t*>(flags.p[r]) + my_rank, epoch);
-  }
-  __syncthreads();
-  if (r < flags.n) {
-    const uint64_t* mine = reinterpret_cast<const uint64_t*>(flags.p[my_rank]) + r;
-    if (!wait_flag_ge(mine, epoch, budget)) report_status(status, kStatusBarrierTimeout);
-  }
-}
-
-// Tensor-parallel all-reduce of a row-parallel projection, fused with what follows it in a decoder layer:
+// Tensor-parallel all-reduce of a row-parallel projection, fused with the arrival barrier before it and with what follows
+// it in a decoder layer:
 //   out[b, :] = residual[b, :] + sum_r partial_r[b, :]     (fp32 sum in rank order: every rank gets the same bits)
 //   ss[b]    += sum_h out[b, h]^2                          (row statistic of the next folded RMSNorm, fixed point)
 // partial_r is rank r's bf16 [rows, H] product in ITS symmetric buffer, read here with plain peer loads (one-shot
 // all-reduce: every rank reads every partial; [rows, H] is a few hundred KB, far below the point where a ring pays).
-// The barrier before this kernel says every partial is written; the barrier of the NEXT all-reduce (on the other
-// buffer) says everybody has finished reading this one before it is overwritten.
-__global__ void tp_allreduce_residual_kernel(PeerPtrs partials, const __nv_bfloat16* __restrict__ residual,
-                                             __nv_bfloat16* __restrict__ out, sumsq_t* __restrict__ ss, int rows, int H,
-                                             const int* guard) {
-  if (guard_tripped(guard)) return;
-  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int b = blockIdx.x * warps + warp; b < rows; b += gridDim.x * warps) {
-    float sq = 0.f;
-    for (int c = lane * 8; c < H; c += 32 * 8) {
-      float acc[8];
-      {
-        const uint4 u = *reinterpret_cast<const uint4*>(residual + (size_t)b * H + c);
-        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+//
+// One CTA per row, one 16-byte vector per thread (two when H > 8192): every peer load of a row is in flight at the same
+// time, so the kernel costs about one NVLink round trip instead of one per loop iteration.
+//
+// Arrival: the GEMM that wrote this rank's partial precedes this kernel in the stream. CTA 0 tells every member "my
+// partial number `epoch` is complete" (release store into the member's flag row), and every CTA waits until all members
+// have said so for this epoch (bounded acquire polls of LOCAL memory). The epoch lives on the device (*epoch_counter,
+// advanced by the last CTA of each launch), so the launch has no per-call argument and replays from a CUDA graph; every
+// member replays the same number of all-reduces. The arrival of the NEXT all-reduce (which uses the other partial
+// buffer) also says that everybody has finished reading this buffer before its owner overwrites it.
+template <int NR>  // upper bound on the number of members (2, 4 or 8): sizes the register tile of loads in flight
+__global__ void __launch_bounds__(1024)
+tp_allreduce_residual_kernel(PeerPtrs partials, PeerPtrs flags, int my_rank, unsigned long long* epoch_counter,
+                             unsigned int* arrive, const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ out,
+                             sumsq_t* __restrict__ ss, int rows, int H, long long budget, int* status) {
+  __shared__ unsigned long long s_epoch;
+  __shared__ int s_ok;
+  __shared__ float s_red[32];
+  const int tid = threadIdx.x, n = partials.n;
+  pdl_wait();    // this rank's partial (and the residual) are complete
+  pdl_launch();  // the next GEMM may start fetching its weights
+  if (tid == 0) {
+    s_epoch = *reinterpret_cast<volatile unsigned long long*>(epoch_counter) + 1ull;
+    s_ok = 1;
+  }
+  __syncthreads();
+  const uint64_t epoch = s_epoch;
+  if (blockIdx.x == 0 && tid < n) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<uint64_t*>(flags.p[tid]) + my_rank, epoch);
+  }
+  if (tid < n) {
+    if (!wait_flag_ge(reinterpret_cast<const uint64_t*>(flags.p[my_rank]) + tid, epoch, budget)) {
+      report_status(status, kStatusBarrierTimeout);
+      s_ok = 0;
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    // every CTA has read the epoch by now; the last one to pass here publishes it for the next launch
+    if (atomicAdd(arrive, 1u) == gridDim.x - 1) {
+      *arrive = 0u;
+      *reinterpret_cast<volatile unsigned long long*>(epoch_counter) = epoch;
+    }
+  }
+  if (!s_ok) return;
+  const int b = blockIdx.x;
+  const int nv = H >> 3;
+  float sq = 0.f;
+  uint4 res[2], part[2][NR];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 f = __bfloat1622float2(h2[i]);
-          acc[2 * i] = f.x;
-          acc[2 * i + 1] = f.y;
+  for (int it = 0; it < 2; ++it) {
+    const int v = tid + it * (int)blockDim.x;
+    if (v < nv) {
+      res[it] = *reinterpret_cast<const uint4*>(residual + (size_t)b * H + v * 8);
+#pragma unroll
+      for (int r = 0; r < NR; ++r) {
+        if (r < n) {
+          const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(partials.p[r]) + (size_t)b * H + v * 8);
+          asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(part[it][r].x), "=r"(part[it][r].y), "=r"(part[it][r].z), "=r"(part[it][r].w)
+                       : "l"(src)
+                       : "memory");
         }
       }
-      uint4 part[kMaxPeers > 8 ? 8 : kMaxPeers];
+    }
+  }
 #pragma unroll
-      for (int r = 0; r < 8; ++r)
-        if (r < partials.n) part[r] = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(partials.p[r]) + (size_t)b * H + c);
+  for (int it = 0; it < 2; ++it) {
+    const int v = tid + it * (int)blockDim.x;
+    if (v < nv) {
+      float acc[8];
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&res[it]);
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        if (r < partials.n) {
-          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&part[r]);
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h2[i]);
+        acc[2 * i] = f.x;
+        acc[2 * i + 1] = f.y;
+      }
+#pragma unroll
+      for (int r = 0; r < NR; ++r) {
+        if (r < n) {
+          const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&part[it][r]);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const float2 f = __bfloat1622float2(h2[i]);
+            const float2 f = __bfloat1622float2(p2[i]);
             acc[2 * i] += f.x;
             acc[2 * i + 1] += f.y;
           }
@@ -129,13 +164,26 @@ __global__ void tp_allreduce_residual_kernel(PeerPtrs partials, const __nv_bfloa
       o.y = pack_bf16x2(acc[2], acc[3]);
       o.z = pack_bf16x2(acc[4], acc[5]);
       o.w = pack_bf16x2(acc[6], acc[7]);
-      *reinterpret_cast<uint4*>(out + (size_t)b * H + c) = o;
+      *reinterpret_cast<uint4*>(out + (size_t)b * H + v * 8) = o;
+      // the statistic is taken from the rounded values, as the GEMM epilogues of the unsharded path take it
+      const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&o);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) sq += acc[i] * acc[i];
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(o2[i]);
+        sq += f.x * f.x + f.y * f.y;
+      }
     }
+  }
+  if (ss == nullptr) return;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-    if (lane == 0 && ss != nullptr) sumsq_atomic_add(ss + b, sq);
+  for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+  if ((tid & 31) == 0) s_red[tid >> 5] = sq;
+  __syncthreads();
+  if (tid < 32) {
+    float t = tid < (int)(blockDim.x >> 5) ? s_red[tid] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (tid == 0) sumsq_atomic_add(ss + b, t);
   }
 }
 
@@ -359,20 +407,17 @@ void launch_flag_barrier(const long long* flag_ptrs, int world, int my_rank, uns
   check_cuda(cudaGetLastError(), "flag_barrier");
 }
 
-void launch_flag_barrier_auto(const long long* flag_ptrs, int world, int my_rank, unsigned long long* epoch_counter,
-                              double budget_s, int* status, cudaStream_t s) {
-  flag_barrier_auto_kernel<<<1, 32, 0, s>>>(make_peers(flag_ptrs, world), my_rank, epoch_counter, ticks_for(budget_s), status);
-  check_cuda(cudaGetLastError(), "flag_barrier_auto");
-}
-
-void launch_tp_allreduce_residual(const long long* partial_ptrs, int world, const void* residual, void* out, long long* ss,
-                                  int rows, int H, cudaStream_t s) {
+void launch_tp_allreduce_residual(const long long* partial_ptrs, const long long* flag_ptrs, int world, int my_rank,
+                                  unsigned long long* epoch_counter, unsigned int* arrive, const void* residual, void* out,
+                                  long long* ss, int rows, int H, double budget_s, int* status, cudaStream_t s) {
   if (rows == 0) return;
-  if (world > 8 || H % 8 != 0) throw std::runtime_error("tp_allreduce_residual: at most 8 ranks, H a multiple of 8");
-  const int blocks = (rows + 3) / 4;
-  tp_allreduce_residual_kernel<<<blocks, 128, 0, s>>>(make_peers(partial_ptrs, world), (const __nv_bfloat16*)residual,
-                                                       (__nv_bfloat16*)out, ss, rows, H, t_guard);
-  check_cuda(cudaGetLastError(), "tp_allreduce_residual");
+  if (world > 8 || H % 8 != 0 || H > 16384) throw std::runtime_error("tp_allreduce_residual: at most 8 ranks, H a multiple of 8 up to 16384");
+  int threads = ((H / 8 + 31) / 32) * 32;
+  if (threads > 1024) threads = ((H / 16 + 31) / 32) * 32;
+  auto kernel = world <= 2 ? tp_allreduce_residual_kernel<2> : world <= 4 ? tp_allreduce_residual_kernel<4> : tp_allreduce_residual_kernel<8>;
+  launch_kernel(kernel, dim3(rows), dim3(threads), 0, s, "tp_allreduce_residual",
+                make_peers(partial_ptrs, world), make_peers(flag_ptrs, world), my_rank, epoch_counter, arrive,
+                (const __nv_bfloat16*)residual, (__nv_bfloat16*)out, ss, rows, H, ticks_for(budget_s), status);
 }
 
 void launch_weight_push(const void* src, bool src_fp32, long long local_off, long long global_off, long long n,

@@ -254,10 +254,9 @@ void launch_flag_barrier(const long long* flag_ptrs, int world, int my_rank, uns
                          int* status, cudaStream_t s);
 // Barrier whose epoch lives in device memory (graph-replayable), and the tensor-parallel all-reduce + residual + row
 // statistic that follows a row-parallel projection of the rollout engine (partials read from peers' symmetric buffers).
-void launch_flag_barrier_auto(const long long* flag_ptrs, int world, int my_rank, unsigned long long* epoch_counter,
-                              double budget_s, int* status, cudaStream_t s);
-void launch_tp_allreduce_residual(const long long* partial_ptrs, int world, const void* residual, void* out, long long* ss,
-                                  int rows, int H, cudaStream_t s);
+void launch_tp_allreduce_residual(const long long* partial_ptrs, const long long* flag_ptrs, int world, int my_rank,
+                                  unsigned long long* epoch_counter, unsigned int* arrive, const void* residual, void* out,
+                                  long long* ss, int rows, int H, double budget_s, int* status, cudaStream_t s);
 void launch_weight_push(const void* src, bool src_fp32, long long local_off, long long global_off, long long n,
                         const long long* dst_ptrs, int n_dst, cudaStream_t s);
 // NVSwitch multicast variants (mc = multicast address of the symmetric buffer): the push is replicated by the switch,

@@ -283,6 +283,7 @@ class TensorParallelComm:
         self.flag_ptrs = [self.flags.peer_ptrs[r] for r in self.members]
         self.partial_ptrs = [[b.peer_ptrs[r] for r in self.members] for b in self.bufs]
         self.epoch = torch.zeros(1, dtype=torch.int64, device=device)
+        self.arrive = torch.zeros(1, dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
 
     def partial(self, which: int, rows: int) -> torch.Tensor:
@@ -291,9 +292,8 @@ class TensorParallelComm:
 
     def allreduce_residual(self, which: int, residual: torch.Tensor, out: torch.Tensor, ss: Optional[torch.Tensor]) -> None:
         """out = residual + sum over members of their partial ``which``; ss += row sums of squares of out."""
-        self.C.set_comm_guard(self.status)
-        self.C.flag_barrier_auto(self.flag_ptrs, self.rank, self.epoch, WAIT_BUDGET_S, self.status)
-        self.C.tp_allreduce_residual(self.partial_ptrs[which], residual, out, ss)
+        self.C.tp_allreduce_residual(self.partial_ptrs[which], self.flag_ptrs, self.rank, self.epoch, self.arrive, residual, out,
+                                     ss, WAIT_BUDGET_S, self.status)
 
     def check(self) -> None:
         code = int(self.status.item())

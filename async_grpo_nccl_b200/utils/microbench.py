@@ -498,9 +498,24 @@ def _engine(args, graph):
 
     cfg = PRESETS[args.model]
     layout = ParamLayout(cfg)
-    params = (torch.randn(layout.total, device="cuda") * 0.02).to(torch.bfloat16)
+    tp = None
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        # launched with torch.distributed.run: the ranks form ONE tensor-parallel engine replica
+        import torch.distributed as dist
+
+        from ..ops import native
+        from ..parallel import symm
+
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        if not dist.is_initialized():
+            dist.init_process_group("nccl")
+        tp = symm.TensorParallelComm(list(range(world)), dist.get_rank(), min(256, max(64, args.batch)), cfg.hidden_size,
+                                     torch.device("cuda", torch.cuda.current_device()), native())
+    params = torch.empty(layout.total, dtype=torch.bfloat16, device="cuda")
+    layout.init_random_device_(params, 0)  # same seed on every rank: identical parameters
     eng = RolloutEngine(cfg, layout, params, max_seqs=max(64, args.batch), max_model_len=args.context + args.steps + 64,
-                        num_blocks=(args.batch * (args.context + args.steps + 64)) // 16 + 1024, use_cuda_graph=graph)
+                        num_blocks=(args.batch * (args.context + args.steps + 64)) // 16 + 1024, use_cuda_graph=graph, tp=tp)
     return cfg, eng
 
 
@@ -525,12 +540,32 @@ def bench_decode(args):
     torch.cuda.synchronize()
     eng.check_status()
     ms = e0.elapsed_time(e1) / args.steps
-    layout_bytes = eng.layout.total * 2
-    kv_bytes = args.batch * (args.context + args.steps // 2) * cfg.num_hidden_layers * 2 * cfg.num_key_value_heads * cfg.head_dim * 2
+    tp_size = eng.tp_size
+    if tp_size > 1:
+        import torch.distributed as dist
+
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)  # device time, max over the replica's ranks
+        ms = float(t.item())
+        if dist.get_rank() != 0:
+            dist.barrier()
+            dist.destroy_process_group()
+            return
+    # bytes one rank streams per step: its share of the layer matrices and of the KV cache, plus the replicated lm_head
+    head = cfg.vocab_size * cfg.hidden_size * 2
+    layout_bytes = (eng.layout.total * 2 - head * (1 if cfg.tie_word_embeddings else 2)) // tp_size + head
+    kv_bytes = (args.batch * (args.context + args.steps // 2) * cfg.num_hidden_layers * 2 * cfg.num_key_value_heads * cfg.head_dim * 2
+                // tp_size)
     out({"bench": "decode_step", "model": args.model, "batch": args.batch, "context": args.context, "graph": bool(args.graph),
+         "tensor_parallel": tp_size,
          "ms_per_step": ms, "tokens_per_s": args.batch / ms * 1e3, "weight_bytes": layout_bytes, "kv_bytes": kv_bytes,
          "ideal_ms": (layout_bytes + kv_bytes) / pk["hbm_gbs"] / 1e6, "frac_of_hbm": (layout_bytes + kv_bytes) / ms / 1e6 / pk["hbm_gbs"],
          "peak": pk["source"]})
+    if tp_size > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
     if getattr(args, "trace", False) and getattr(eng, "mega_rows", 0):
         # clock64 stamps of CTA 0 in one middle layer, microseconds from the layer's start (1965 MHz assumed)
         eng.use_cuda_graph = False

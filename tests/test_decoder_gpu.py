@@ -58,6 +58,62 @@ def test_forward_backward_matches_oracle(preset):
     assert (lpn - lp0).abs().max().item() < 3e-2 and (entn - ent0).abs().max().item() < 3e-2
 
 
+def test_long_packed_microbatch_with_recompute_matches_oracle():
+    """A 32 768-token packed microbatch that holds one 16 384-token sequence next to short ones, through forward_backward
+    with per-layer recompute: loss, token count, log-probabilities and every gradient against the fp32 PyTorch oracle."""
+    import dataclasses
+
+    from async_grpo_nccl_b200.models.config import PRESETS
+    from async_grpo_nccl_b200.models.decoder import GradSink, LossConfig, NativeDecoder, OracleDecoder
+    from async_grpo_nccl_b200.models.layout import ParamLayout
+    from async_grpo_nccl_b200.packing import pack_samples
+
+    cfg = dataclasses.replace(PRESETS["tiny128"], max_position_embeddings=32768)
+    layout = ParamLayout(cfg)
+    p32 = torch.empty(layout.total)
+    layout.init_random_(p32, 0)
+    p16 = p32.to(torch.bfloat16).to(DEV)
+    rng = np.random.default_rng(2)
+
+    def sample(li, lo_):
+        L = li + lo_
+        return dict(sample_ids=rng.integers(0, cfg.vocab_size, L).astype(np.int32), input_len=li, output_len=lo_,
+                    advantage=float(rng.normal()), sample_logprobs=np.zeros(L, np.float32),
+                    sample_entropies=np.zeros(L, np.float32), reward=float(rng.random() < 0.5))
+
+    samples = [sample(40, 16384 - 40)]
+    total = 16384
+    while total < 32768 - 700:
+        li, lo_ = int(rng.integers(4, 100)), int(rng.integers(50, 600))
+        samples.insert(int(rng.integers(0, len(samples) + 1)), sample(li, lo_))
+        total += li + lo_
+    samples.append(sample(20, 32768 - total - 20))
+    pb = pack_samples(samples, pin=False).to_device(DEV)
+    assert pb.T == 32768
+    lc = LossConfig(kl_beta=0.0, temperature=1.0)
+    pref = p16.float().clone().requires_grad_(True)
+    orc = OracleDecoder(cfg, layout, pref)
+    with torch.no_grad():
+        lp0, _ = orc.logprobs(pb, 1.0)
+    pb.old_logprobs.copy_(lp0 + 0.02 * torch.randn_like(lp0))
+    loss, stats_ref = orc.loss(pb, lc, 0.5)
+    loss.backward()
+    nat = NativeDecoder(cfg, layout, p16, recompute=True)
+    sink = GradSink(layout, DEV)
+    stats = nat.forward_backward(pb, lc, 0.5, sink)
+    torch.cuda.synchronize()
+    nat.check_status()
+    lval = stats[1].item() / max(1, stats[0].item()) * 0.5
+    assert abs(lval - loss.item()) < 2e-3 * max(1.0, abs(loss.item()))
+    assert stats[0].item() == stats_ref[0].item()
+    for name in layout.segments:
+        a, b = layout.view(sink.flat, name), layout.view(pref.grad, name)
+        cos = torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0).item()
+        assert cos > 0.99, (name, cos)
+    lpn, _ = nat.logprobs(pb, 1.0)
+    assert (lpn - lp0).abs().max().item() < 4e-2
+
+
 def test_trainer_step_matches_oracle_step():
     """One full optimizer step (two microbatches, clip, AdamW) on the GPU kernels equals the oracle trainer on CPU."""
     from async_grpo_nccl_b200.config import make_config
