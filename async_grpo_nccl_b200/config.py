@@ -54,7 +54,7 @@ class GRPOConfig:
     max_generation_tokens: int = 4096
     max_num_seqs: int = 512
     overhead_seqs: int = 8
-    enable_prefix_caching: bool = True
+    enable_prefix_caching: bool = True  # accepted; the n samples of a prompt always share its KV blocks, nothing is cached across requests
     vllm_engine_preset: str = "eager"  # "eager" | "throughput" (CUDA-graphed decode step)
     kv_block_size: int = 16
     gpu_memory_utilization: float = 0.90

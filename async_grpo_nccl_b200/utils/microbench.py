@@ -12,8 +12,10 @@
         -m async_grpo_nccl_b200.utils.microbench sync --trainers 1 --model qwen2.5-1.5b,qwen2.5-7b
 
 Each line of output is a JSON record with the achieved rate and, where a library kernel exists in the image
-(cuBLAS through torch.matmul, flash-attn 2), the same measurement for it. Roofline denominators come from
-MEASURED_PEAKS.json at the repository root when present.
+(cuBLAS through torch.matmul, flash-attn 2), the same measurement for it. Roofline denominators: ``--peak-hbm-gbs`` and
+``--peak-bf16-tflops`` (or the environment variables AGRPO_PEAK_HBM_GBS / AGRPO_PEAK_BF16_TFLOPS, or a JSON file with
+the keys ``hbm_gbs`` / ``bf16_tflops`` named by AGRPO_PEAKS_FILE); without any of them 6650 GB/s and 1590 TFLOP/s, a
+copy / cuBLAS measurement on a B200, marked "fallback" in the records.
 """
 from __future__ import annotations
 
@@ -28,14 +30,23 @@ import numpy as np
 import torch
 
 
+_PEAK_FLAGS: dict = {}
+
+
 def _peaks():
-    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-    p = os.path.join(root, "MEASURED_PEAKS.json")
-    if os.path.exists(p):
+    out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    p = os.environ.get("AGRPO_PEAKS_FILE")
+    if p and os.path.exists(p):
         with open(p) as f:
             d = json.load(f)
-        return {"hbm_gbs": d.get("hbm_gbs"), "bf16_tflops": d.get("bf16_tflops"), "source": "measured"}
-    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+        for k in ("hbm_gbs", "bf16_tflops"):
+            if d.get(k):
+                out[k], out["source"] = float(d[k]), "measured"
+    for k, env in (("hbm_gbs", "AGRPO_PEAK_HBM_GBS"), ("bf16_tflops", "AGRPO_PEAK_BF16_TFLOPS")):
+        v = _PEAK_FLAGS.get(k) or os.environ.get(env)
+        if v:
+            out[k], out["source"] = float(v), "measured"
+    return out
 
 
 _FLUSH = None
@@ -657,7 +668,10 @@ def main():
     ap.add_argument("--tokens", type=int, default=16384)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--recompute", action="store_true")
+    ap.add_argument("--peak-hbm-gbs", type=float, default=None, help="roofline denominator: measured copy bandwidth, GB/s")
+    ap.add_argument("--peak-bf16-tflops", type=float, default=None, help="roofline denominator: measured cuBLAS bf16 TFLOP/s")
     args = ap.parse_args()
+    _PEAK_FLAGS.update({"hbm_gbs": args.peak_hbm_gbs, "bf16_tflops": args.peak_bf16_tflops})
     {"gemm": bench_gemm, "attn": bench_attn, "lmhead": bench_lmhead, "elementwise": bench_elementwise, "decode": bench_decode,
      "train": bench_train, "fused": bench_fused, "one": bench_one, "sync": bench_sync}[args.what](args)
 

@@ -51,10 +51,9 @@ def parse_args():
                     help="zero3: fully sharded trainers (all-gather / reduce-scatter fused into the GEMM kernels)")
     ap.add_argument("--colocated-sm-limit", type=int, default=0,
                     help="SMs that trainer / logprob GEMMs may fill on a GPU shared with a rollout engine (0 = all)")
-    ap.add_argument("--eager-dispatch", type=int, default=None,
+    ap.add_argument("--eager-dispatch", type=int, default=1,
                     help="1: finished samples go to the trainer at once (overlaps training with generation); 0: the trainer "
-                         "starts when the minibatch is complete. Default: 1 where the trainer has a GPU of its own, 0 where it "
-                         "shares the rollout engine's GPU (one-GPU runs)")
+                         "starts when the minibatch is complete (the two measured the same on one GPU: 5.08 vs 4.98 samples/s)")
     ap.add_argument("--stream-logprobs", type=int, default=1)
     ap.add_argument("--colocated-rollout-sms", type=int, default=None,
                     help="SMs that the rollout engine gets for itself on a GPU it shares with other roles (default 0 = no "
@@ -178,8 +177,7 @@ def main() -> None:
         "num_generation_gpu_workers": len(place["rollout"]), "placement": place, "learning_rate": 1e-6, "kl_beta": 0.001,
         "max_num_seqs": args.max_num_seqs, "vllm_engine_preset": args.preset, "eval_at_start": False, "temperature": 1.0,
         "min_samples_per_checkpoint": 10 ** 12, "seed": 0, "stream_logprobs": bool(args.stream_logprobs),
-        "eager_microbatch_dispatch": bool(args.eager_dispatch if args.eager_dispatch is not None
-                                          else not (set(place["trainer"]) & set(place["rollout"]))),
+        "eager_microbatch_dispatch": bool(args.eager_dispatch),
     })
     rows = synthetic_prompt_rows(prompts_per_step * total_steps, mcfg.vocab_size, args.prompt_min, args.prompt_max, seed=0,
                                  samples_per_question=spq, gen_len_range=(args.gen_min, args.gen_max), reward_p=0.3)
