@@ -102,8 +102,10 @@ __device__ __forceinline__ bool paged_decode_attend(const DecodeParams& p, int s
 #pragma unroll
     for (int kk = 0; kk < kDecD / 16; ++kk) {
       const int c = kk * 16 + (lane & 3) * 2;
-      qa[kk][0] = (g < p.G) ? *reinterpret_cast<const uint32_t*>(qrow + c) : 0u;
-      qa[kk][1] = (g < p.G) ? *reinterpret_cast<const uint32_t*>(qrow + c + 8) : 0u;
+      // L2 loads: inside a persistent kernel the query row was written by another SM during this launch, and this SM
+      // may still hold the previous layer's row at the same address in its L1
+      qa[kk][0] = (g < p.G) ? __ldcg(reinterpret_cast<const uint32_t*>(qrow + c)) : 0u;
+      qa[kk][1] = (g < p.G) ? __ldcg(reinterpret_cast<const uint32_t*>(qrow + c + 8)) : 0u;
     }
   }
   float o[kDecD / 8][2];

@@ -30,6 +30,7 @@
 #include "../common/tensormap.h"
 #include "../launchers.h"
 #include "decode_attn.cuh"
+#include "decode_sync.cuh"
 
 namespace agrpo {
 
@@ -95,61 +96,10 @@ __device__ __forceinline__ long long global_ns() {
     if (p.trace != nullptr && cta == 0 && l == p.trace_layer) p.trace[slot] = clock64();        \
   } while (0)
 
-__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
-  unsigned int v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void red_release_gpu_add(unsigned int* p, unsigned int v) {
-  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ bool status_set(const int* status) {
-  return status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0;
-}
-// Bounded wait until *ctr >= want. Gives up early when another CTA has already reported a failure.
-__device__ __forceinline__ bool wait_counter(const unsigned int* ctr, unsigned int want, const int* status) {
-  if (ld_acquire_gpu(ctr) >= want) return true;
-  const long long t0 = clock64();
-  int it = 0;
-  while (ld_acquire_gpu(ctr) < want) {
-    if ((++it & 31) == 0) {
-      if (status_set(status)) return false;
-      if (clock64() - t0 > kWaitBudgetTicks) return false;
-    }
-  }
-  return true;
-}
-// mbarrier wait that also gives up when the status word is set.
-__device__ __forceinline__ bool mbar_wait_s(uint64_t* bar, uint32_t parity, const int* status) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  int it = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++it & 63) == 0) {
-      if (status_set(status)) return false;
-      if (clock64() - t0 > kWaitBudgetTicks) return false;
-    }
-  }
-  return true;
-}
-
 __device__ __forceinline__ float4 shfl_xor4(float4 v, int m) {
   return make_float4(__shfl_xor_sync(0xffffffffu, v.x, m), __shfl_xor_sync(0xffffffffu, v.y, m),
                      __shfl_xor_sync(0xffffffffu, v.z, m), __shfl_xor_sync(0xffffffffu, v.w, m));
 }
-__device__ __forceinline__ float4 ld_bf16x4(const __nv_bfloat16* p) {
-  const uint2 u = *reinterpret_cast<const uint2*>(p);
-  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
-  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
-  return make_float4(a.x, a.y, b.x, b.y);
-}
-__device__ __forceinline__ void st_bf16x4(__nv_bfloat16* p, float4 v) {
-  uint2 u;
-  u.x = pack_bf16x2(v.x, v.y);
-  u.y = pack_bf16x2(v.z, v.w);
-  *reinterpret_cast<uint2*>(p) = u;
-}
-
 template <int BT>
 struct MegaCfg {
   static constexpr int kXStage = BT * kMBK * 2;
@@ -159,7 +109,8 @@ struct MegaCfg {
   static constexpr int kNSX = (kXA / kXStage) > 8 ? 8 : (kXA / kXStage);
   static constexpr int kAcc = 2;
   static constexpr uint32_t kTmemCols = (kAcc * BT) < 32 ? 32 : (kAcc * BT);
-  static constexpr int kSmem = kNSW * kWStage + kXA + 1024 /* barriers */ + 1024 /* alignment */;
+  static constexpr int kRedBytes = 4 * 4 * 32 * 16;  // split-sum exchange between the compute warps: [warp][row][lane] float4
+  static constexpr int kSmem = kNSW * kWStage + kXA + 1024 /* barriers */ + kRedBytes + 1024 /* alignment */;
 };
 
 // What the roles of one CTA share.
@@ -185,6 +136,7 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmWqkv, const __grid_co
   uint8_t* w_ring = smem;
   uint8_t* xa = smem + NSW * kWStage;
   MegaShared* sh = reinterpret_cast<MegaShared*>(xa + Cfg::kXA);
+  float4* red = reinterpret_cast<float4*>(xa + Cfg::kXA + 1024);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cta = blockIdx.x, G = p.grid;
@@ -511,7 +463,14 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmWqkv, const __grid_co
           // they arrive while this CTA waits for the tile's other splits.
           const int r0 = (int)((long long)B * ks / S), r1 = (int)((long long)B * (ks + 1) / S);
           constexpr int RU = 4;
-          const int b_first = r0 + cw * RU;
+          // How the four compute warps divide the share. Few rows (a small batch over many splits): the warps take
+          // different SPLITS of the same rows, so that all S partials of a row are requested at once instead of in S / 2
+          // dependent round trips, and warp `sub == 0` of each row group adds the warps' sums in a fixed order. Many
+          // rows: the warps take different rows. The choice depends on the shapes only, so results are reproducible.
+          const int share_rows = r1 - r0;
+          const int WS = share_rows <= RU ? 4 : (share_rows <= 2 * RU ? 2 : 1);  // warps per row group
+          const int rg = cw / WS, sub = cw - rg * WS, n_rg = 4 / WS;
+          const int b_first = r0 + rg * RU;
           sumsq_t m_ss[RU];
           int m_len[RU];
           float4 m_rr[RU], m_cs[RU], m_sn[RU];
@@ -525,10 +484,10 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmWqkv, const __grid_co
               m_rr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
               if (b0 < r1) {
                 if (ph == 0) {
-                  m_ss[j] = p.ss[(size_t)(2 * l) * p.ss_stride + b];
+                  m_ss[j] = ld_sumsq_l2(p.ss + (size_t)(2 * l) * p.ss_stride + b);
                   m_len[j] = p.seq_lens[b];
                 } else if (ph == 2) {
-                  m_ss[j] = p.ss[(size_t)(2 * l + 1) * p.ss_stride + b];
+                  m_ss[j] = ld_sumsq_l2(p.ss + (size_t)(2 * l + 1) * p.ss_stride + b);
                 } else {
                   m_rr[j] = ld_bf16x4((ph == 1 ? p.x : p.x1) + (size_t)b * p.H + grp * kFT + 4 * lane);
                 }
@@ -576,8 +535,10 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmWqkv, const __grid_co
           // Four rows per warp pass. Everything a row needs from memory (its S partials, statistics, residual, rotary
           // table entries, cache slot) is requested before the first use, so that the L2 round trips of the four rows
           // and of the splits overlap instead of adding up.
-          for (int b0 = b_first; b0 < r1; b0 += 4 * RU) {
-            if (b0 != b_first) load_meta(b0);
+          // every warp makes the same number of passes (the exchange below is a barrier of all four)
+          for (int base = r0; base < r1; base += n_rg * RU) {
+            const int b0 = base + rg * RU;
+            if (base != r0) load_meta(b0);
             float4 v[RU];
             bool on[RU];
 #pragma unroll
@@ -585,20 +546,42 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmWqkv, const __grid_co
               on[j] = b0 + j < r1;
               v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
-            for (int s = 0; s < S; s += 2) {
-              float4 t0[RU], t1[RU];
-              const bool two = s + 1 < S;
+            for (int s = sub; s < S; s += 4 * WS) {  // up to four partials of each row in flight per pass
+              float4 t[4][RU];
 #pragma unroll
-              for (int j = 0; j < RU; ++j) {
-                const float4* src = reinterpret_cast<const float4*>(gbase + ((size_t)s * BT + (on[j] ? b0 + j : r0)) * kFT) + lane;
-                t0[j] = __ldcg(src);
-                t1[j] = two ? __ldcg(src + (size_t)BT * kFT / 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+              for (int u = 0; u < 4; ++u) {
+                const int sp = s + u * WS;
+#pragma unroll
+                for (int j = 0; j < RU; ++j) {
+                  const float4* src = reinterpret_cast<const float4*>(gbase + ((size_t)(sp < S ? sp : 0) * BT + (on[j] ? b0 + j : r0)) * kFT) + lane;
+                  t[u][j] = sp < S ? __ldcg(src) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
               }
 #pragma unroll
-              for (int j = 0; j < RU; ++j) {  // fixed order: split s, then split s + 1
-                v[j].x += t0[j].x; v[j].y += t0[j].y; v[j].z += t0[j].z; v[j].w += t0[j].w;
-                v[j].x += t1[j].x; v[j].y += t1[j].y; v[j].z += t1[j].z; v[j].w += t1[j].w;
+              for (int u = 0; u < 4; ++u) {  // fixed order
+#pragma unroll
+                for (int j = 0; j < RU; ++j) {
+                  v[j].x += t[u][j].x; v[j].y += t[u][j].y; v[j].z += t[u][j].z; v[j].w += t[u][j].w;
+                }
               }
+            }
+            if (WS > 1) {
+              if (sub != 0) {
+#pragma unroll
+                for (int j = 0; j < RU; ++j) red[(cw * RU + j) * 32 + lane] = v[j];
+              }
+              dec_bar_sync();
+              if (sub == 0) {
+                for (int w2 = 1; w2 < WS; ++w2) {
+#pragma unroll
+                  for (int j = 0; j < RU; ++j) {
+                    const float4 o = red[((cw + w2) * RU + j) * 32 + lane];
+                    v[j].x += o.x; v[j].y += o.y; v[j].z += o.z; v[j].w += o.w;
+                  }
+                }
+              }
+              dec_bar_sync();  // the buffer may be rewritten by the next pass
+              if (sub != 0) continue;  // the epilogue of these rows belongs to the row group's first warp
             }
             if (ph == 0) {
               const bool is_q = grp < p.Hq, is_k = !is_q && grp < p.Hq + p.Hkv;
