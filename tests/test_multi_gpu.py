@@ -118,7 +118,7 @@ def _worker(rank, world, port, q):
 def test_peer_memory_collectives_match_nccl():
     import torch.multiprocessing as mp
 
-    world = min(4, torch.cuda.device_count())
+    world = min(8, torch.cuda.device_count())
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     procs = [ctx.Process(target=_worker, args=(r, world, 29733, q)) for r in range(world)]
@@ -220,14 +220,15 @@ def _worker_sharded(rank, world, port, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
-def test_fully_sharded_trainer_matches_resident_trainer():
+@pytest.mark.parametrize("world", [2, 4])
+def test_fully_sharded_trainer_matches_resident_trainer(world):
     import torch.multiprocessing as mp
 
-    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker_sharded, args=(r, world, 29741, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker_sharded, args=(r, world, 29741 + world, q)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=300) for _ in range(world)]
