@@ -175,8 +175,12 @@ class TrainerCore:
             n_tok = float(row[0])
             token_mean = float(row[1]) / max(1.0, n_tok)
             m = R.stats_to_metrics(row, token_mean, p["num_samples"], self.cfg.entropy_coeff)
+            # the reference subtracts entropy_coeff * (mean entropy of the output tokens) from the microbatch loss it
+            # reports and back-propagates (grpo_loss.py:500-508); its entropy is detached, so only the reported value moves
+            bonus = (float(self.cfg.entropy_coeff) * m["entropy"]
+                     if (self.cfg.apply_entropy_bonus and float(self.cfg.entropy_coeff) != 0.0 and n_tok > 0) else 0.0)
             summ = {
-                "tokens": n_tok, "loss_sum": token_mean * n_tok, "kl_mean": m["kl_div"], "entropy_mean": m["entropy"],
+                "tokens": n_tok, "loss_sum": token_mean * n_tok - bonus, "kl_mean": m["kl_div"], "entropy_mean": m["entropy"],
                 "minibatch_index": p["index"], "log_ratio_mean": m["log_ratio_mean"], "log_ratio_std": m["log_ratio_std"],
                 "clipfrac_upper": m["clipfrac_upper"], "clipfrac_lower": m["clipfrac_lower"], "adv_mean": m["adv_mean"],
                 "adv_std": m["adv_std"], "adv_pos_frac": m["adv_pos_frac"], "adv_zero_frac": m["adv_zero_frac"],
