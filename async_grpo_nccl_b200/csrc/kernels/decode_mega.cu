@@ -109,8 +109,7 @@ struct MegaCfg {
   static constexpr int kNSX = (kXA / kXStage) > 8 ? 8 : (kXA / kXStage);
   static constexpr int kAcc = 2;
   static constexpr uint32_t kTmemCols = (kAcc * BT) < 32 ? 32 : (kAcc * BT);
-  static constexpr int kRedBytes = 4 * 4 * 32 * 16;  // split-sum exchange between the compute warps: [warp][row][lane] float4
-  static constexpr int kSmem = kNSW * kWStage + kXA + 1024 /* barriers */ + kRedBytes + 1024 /* alignment */;
+  static constexpr int kSmem = kNSW * kWStage + kXA + 1024 /* barriers */ + 1024 /* alignment */;
 };
 
 // What the roles of one CTA share.
@@ -136,7 +135,6 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmWqkv, const __grid_co
   uint8_t* w_ring = smem;
   uint8_t* xa = smem + NSW * kWStage;
   MegaShared* sh = reinterpret_cast<MegaShared*>(xa + Cfg::kXA);
-  float4* red = reinterpret_cast<float4*>(xa + Cfg::kXA + 1024);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cta = blockIdx.x, G = p.grid;
@@ -463,14 +461,7 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmWqkv, const __grid_co
           // they arrive while this CTA waits for the tile's other splits.
           const int r0 = (int)((long long)B * ks / S), r1 = (int)((long long)B * (ks + 1) / S);
           constexpr int RU = 4;
-          // How the four compute warps divide the share. Few rows (a small batch over many splits): the warps take
-          // different SPLITS of the same rows, so that all S partials of a row are requested at once instead of in S / 2
-          // dependent round trips, and warp `sub == 0` of each row group adds the warps' sums in a fixed order. Many
-          // rows: the warps take different rows. The choice depends on the shapes only, so results are reproducible.
-          const int share_rows = r1 - r0;
-          const int WS = share_rows <= RU ? 4 : (share_rows <= 2 * RU ? 2 : 1);  // warps per row group
-          const int rg = cw / WS, sub = cw - rg * WS, n_rg = 4 / WS;
-          const int b_first = r0 + rg * RU;
+          const int b_first = r0 + cw * RU;
           sumsq_t m_ss[RU];
           int m_len[RU];
           float4 m_rr[RU], m_cs[RU], m_sn[RU];
@@ -535,10 +526,8 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmWqkv, const __grid_co
           // Four rows per warp pass. Everything a row needs from memory (its S partials, statistics, residual, rotary
           // table entries, cache slot) is requested before the first use, so that the L2 round trips of the four rows
           // and of the splits overlap instead of adding up.
-          // every warp makes the same number of passes (the exchange below is a barrier of all four)
-          for (int base = r0; base < r1; base += n_rg * RU) {
-            const int b0 = base + rg * RU;
-            if (base != r0) load_meta(b0);
+          for (int b0 = b_first; b0 < r1; b0 += 4 * RU) {
+            if (b0 != b_first) load_meta(b0);
             float4 v[RU];
             bool on[RU];
 #pragma unroll
@@ -546,42 +535,20 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmWqkv, const __grid_co
               on[j] = b0 + j < r1;
               v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
-            for (int s = sub; s < S; s += 4 * WS) {  // up to four partials of each row in flight per pass
-              float4 t[4][RU];
+            for (int s = 0; s < S; s += 2) {
+              float4 t0[RU], t1[RU];
+              const bool two = s + 1 < S;
 #pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                const int sp = s + u * WS;
-#pragma unroll
-                for (int j = 0; j < RU; ++j) {
-                  const float4* src = reinterpret_cast<const float4*>(gbase + ((size_t)(sp < S ? sp : 0) * BT + (on[j] ? b0 + j : r0)) * kFT) + lane;
-                  t[u][j] = sp < S ? __ldcg(src) : make_float4(0.f, 0.f, 0.f, 0.f);
-                }
+              for (int j = 0; j < RU; ++j) {
+                const float4* src = reinterpret_cast<const float4*>(gbase + ((size_t)s * BT + (on[j] ? b0 + j : r0)) * kFT) + lane;
+                t0[j] = __ldcg(src);
+                t1[j] = two ? __ldcg(src + (size_t)BT * kFT / 4) : make_float4(0.f, 0.f, 0.f, 0.f);
               }
 #pragma unroll
-              for (int u = 0; u < 4; ++u) {  // fixed order
-#pragma unroll
-                for (int j = 0; j < RU; ++j) {
-                  v[j].x += t[u][j].x; v[j].y += t[u][j].y; v[j].z += t[u][j].z; v[j].w += t[u][j].w;
-                }
+              for (int j = 0; j < RU; ++j) {  // fixed order: split s, then split s + 1
+                v[j].x += t0[j].x; v[j].y += t0[j].y; v[j].z += t0[j].z; v[j].w += t0[j].w;
+                v[j].x += t1[j].x; v[j].y += t1[j].y; v[j].z += t1[j].z; v[j].w += t1[j].w;
               }
-            }
-            if (WS > 1) {
-              if (sub != 0) {
-#pragma unroll
-                for (int j = 0; j < RU; ++j) red[(cw * RU + j) * 32 + lane] = v[j];
-              }
-              dec_bar_sync();
-              if (sub == 0) {
-                for (int w2 = 1; w2 < WS; ++w2) {
-#pragma unroll
-                  for (int j = 0; j < RU; ++j) {
-                    const float4 o = red[((cw + w2) * RU + j) * 32 + lane];
-                    v[j].x += o.x; v[j].y += o.y; v[j].z += o.z; v[j].w += o.w;
-                  }
-                }
-              }
-              dec_bar_sync();  // the buffer may be rewritten by the next pass
-              if (sub != 0) continue;  // the epilogue of these rows belongs to the row group's first warp
             }
             if (ph == 0) {
               const bool is_q = grp < p.Hq, is_k = !is_q && grp < p.Hq + p.Hkv;

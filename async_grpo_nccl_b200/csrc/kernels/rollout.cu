@@ -244,55 +244,73 @@ struct LmSampleEpilogue {
   }
 };
 
-// One warp per row: lanes stride over the column groups, then a warp reduction (argmax of the perturbed value, and
-// the usual (max, sum) merge for the log-sum-exp).
-__global__ void lm_sample_combine_kernel(const float* __restrict__ part_best, const int* __restrict__ part_idx,
-                                         const float* __restrict__ part_z, const float* __restrict__ part_m,
-                                         const float* __restrict__ part_s, int groups, int rows, int* __restrict__ tokens,
-                                         float* __restrict__ logprobs) {
+// One CTA (4 warps) per row: threads stride over the column groups (a handful of iterations even for a 150k vocabulary,
+// every load of an iteration in flight before the first use), then a warp reduction and a 4-way merge through shared
+// memory (argmax of the perturbed value with ties to the lower index, and the usual (max, sum) merge for the
+// log-sum-exp). This kernel sits on the critical path of every decode step.
+__global__ void __launch_bounds__(128)
+lm_sample_combine_kernel(const float* __restrict__ part_best, const int* __restrict__ part_idx,
+                         const float* __restrict__ part_z, const float* __restrict__ part_m,
+                         const float* __restrict__ part_s, int groups, int rows, int* __restrict__ tokens,
+                         float* __restrict__ logprobs) {
   pdl_wait();
   pdl_launch();
-  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (r >= rows) return;
-  const int lane = threadIdx.x & 31;
+  __shared__ float s_best[4], s_bz[4], s_m[4], s_s[4];
+  __shared__ int s_bi[4];
+  const int r = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float best = -INFINITY, bz = 0.f, M = -INFINITY, S = 0.f;
   int bi = 0x7fffffff;
-  for (int g = lane; g < groups; g += 32) {
+  for (int g = threadIdx.x; g < groups; g += 128) {
     const long long o = (long long)g * rows + r;
     const float v = part_best[o];
     const int idx = part_idx[o];
+    const float z = part_z[o];
+    const float m = part_m[o];
+    const float sv = part_s[o];
     if (v > best || (v == best && idx < bi)) {
       best = v;
       bi = idx;
-      bz = part_z[o];
+      bz = z;
     }
-    const float m = part_m[o];
     if (m > M) {
-      S = S * ((M == -INFINITY) ? 0.f : __expf(M - m)) + part_s[o];
+      S = S * ((M == -INFINITY) ? 0.f : __expf(M - m)) + sv;
       M = m;
     } else if (m != -INFINITY) {
-      S += part_s[o] * __expf(m - M);
+      S += sv * __expf(m - M);
     }
   }
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) {
-    const float ob = __shfl_xor_sync(0xffffffffu, best, off);
-    const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
-    const float oz = __shfl_xor_sync(0xffffffffu, bz, off);
+  auto merge = [&](float ob, int oi, float oz, float om, float os) {
     if (ob > best || (ob == best && oi < bi)) {
       best = ob;
       bi = oi;
       bz = oz;
     }
-    const float om = __shfl_xor_sync(0xffffffffu, M, off);
-    const float os = __shfl_xor_sync(0xffffffffu, S, off);
     const float nm = fmaxf(M, om);
     const float sa = (M == -INFINITY) ? 0.f : S * __expf(M - nm);
     const float sb = (om == -INFINITY) ? 0.f : os * __expf(om - nm);
     S = sa + sb;
     M = nm;
+  };
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+    const float oz = __shfl_xor_sync(0xffffffffu, bz, off);
+    const float om = __shfl_xor_sync(0xffffffffu, M, off);
+    const float os = __shfl_xor_sync(0xffffffffu, S, off);
+    merge(ob, oi, oz, om, os);
   }
   if (lane == 0) {
+    s_best[warp] = best;
+    s_bi[warp] = bi;
+    s_bz[warp] = bz;
+    s_m[warp] = M;
+    s_s[warp] = S;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 4; ++w) merge(s_best[w], s_bi[w], s_bz[w], s_m[w], s_s[w]);
     tokens[r] = bi == 0x7fffffff ? 0 : bi;
     if (logprobs != nullptr) logprobs[r] = bz - (M + logf(S));
   }
@@ -412,7 +430,7 @@ void launch_lm_sample(const void* hidden, long long ldh, const void* weight, lon
   e.best = 0.f; e.best_z = 0.f; e.m = 0.f; e.s = 0.f; e.best_idx = 0; e.seed_lo = 0; e.seed_hi = 0;
   gemm_launch<256, false, false>(ta, tb, p, e, num_sms, stream);
   AGRPO_PREFER_SMEM(lm_sample_combine_kernel);
-  launch_kernel(lm_sample_combine_kernel, dim3((rows + 3) / 4), dim3(128), 0, stream, "lm_sample_combine", (const float*)e.part_best,
+  launch_kernel(lm_sample_combine_kernel, dim3(rows), dim3(128), 0, stream, "lm_sample_combine", (const float*)e.part_best,
                 (const int*)e.part_idx, (const float*)e.part_z, (const float*)e.part_m, (const float*)e.part_s, groups, rows, tokens,
                 logprobs);
 }
