@@ -781,6 +781,8 @@ class DistributedRuntime:
     # ------------------------------------------------------------------ rank-local halves of collective operations
     def _sync_on_device(self) -> None:
         """Runs on this rank's communication thread; every rank of the world executes it once per sync."""
+        if self.native:
+            torch.cuda.set_device(self.device)  # the current device is per thread; this thread starts on device 0
         core = self.trainer.core if self.trainer is not None else None
         if self.weight_sync is not None:
             src, sharded = core.sync_source() if core is not None else (None, False)
@@ -894,9 +896,15 @@ def _spawn_entry(rank: int, world: int, port: int, cfg_dict: Dict[str, Any], row
     if rank != 0:
         rt.serve_forever()
         return
-    orch = Orchestrator(cfg, runtime=rt, dataset=rows)
-    orch.max_macro_batches = max_batches
-    result = asyncio.run(orch.run_async())
+    try:
+        orch = Orchestrator(cfg, runtime=rt, dataset=rows)
+        orch.max_macro_batches = max_batches
+        result = asyncio.run(orch.run_async())
+    except BaseException as e:  # the parent must not wait for its timeout to learn that the run failed
+        import traceback
+
+        out_q.put({"error": f"{e!r}\n{traceback.format_exc()}"})
+        raise
     out_q.put({"global_step": result["global_step"], "total_samples_seen": result["total_samples_seen"],
                "last": {k: v for k, v in result["steps"][-1].items() if isinstance(v, (int, float))}})
 
@@ -916,9 +924,12 @@ def spawn(config_dict: Dict[str, Any], rows: Any, world: int, max_macro_batches:
     try:
         result = q.get(timeout=timeout_s)
     finally:
+        failed = "result" not in locals() or "error" in result
         for p in procs:
-            p.join(timeout=30)
+            p.join(timeout=5 if failed else 30)
         for p in procs:
             if p.is_alive():
                 p.kill()
+    if "error" in result:
+        raise RuntimeError("the run failed on rank 0: " + result["error"])
     return result

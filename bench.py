@@ -58,6 +58,8 @@ def parse_args():
     ap.add_argument("--colocated-rollout-sms", type=int, default=None,
                     help="SMs that the rollout engine gets for itself on a GPU it shares with other roles (default 0 = no "
                          "partition: measured slower on the one-GPU configuration, 29.5 s per step with 96 + 52 SMs against 25.3 s)")
+    ap.add_argument("--generation-tp-size", type=int, default=1,
+                    help="consecutive rollout ranks that form one tensor-parallel engine replica (1 = every rank a replica)")
     ap.add_argument("--placement", default=None, help='JSON role placement overriding the default, e.g. '
                     '\'{"trainer": [0, 1], "logprob": [0], "rollout": [1]}\'')
     # reference arm only (its own defaults: orchestrator.py:137, 158 of the reference)
@@ -174,7 +176,7 @@ def main() -> None:
         "train_minibatch_sample_size": prompts_per_step * spq, "max_generation_tokens": args.gen_max,
         "max_tokens_per_gpu": args.max_tokens_per_gpu, "reward_fns": ["bernoulli"], "global_num_verifiers": 0,
         "num_training_gpu_workers": len(place["trainer"]), "num_logprob_gpu_workers": len(place["logprob"]),
-        "num_generation_gpu_workers": len(place["rollout"]), "placement": place, "learning_rate": 1e-6, "kl_beta": 0.001,
+        "num_generation_gpu_workers": len(place["rollout"]), "generation_tp_size": args.generation_tp_size, "placement": place, "learning_rate": 1e-6, "kl_beta": 0.001,
         "max_num_seqs": args.max_num_seqs, "vllm_engine_preset": args.preset, "eval_at_start": False, "temperature": 1.0,
         "min_samples_per_checkpoint": 10 ** 12, "seed": 0, "stream_logprobs": bool(args.stream_logprobs),
         "eager_microbatch_dispatch": bool(args.eager_dispatch),
@@ -267,7 +269,7 @@ def run_timed(cfg, runtime, rows, args, n, rank, dist, mcfg):
                    "parallelism": par, "max_tokens_per_microbatch": cfg.max_tokens_per_gpu,
                    "l2": "working set (3.1 GB of weights, multi-GB KV cache and activations per step) is far larger than the 126 MB L2; no flush needed",
                    "engine_preset": cfg.vllm_engine_preset, "max_num_seqs": cfg.max_num_seqs,
-                   "eager_microbatch_dispatch": bool(cfg.eager_microbatch_dispatch), "param_sharding": cfg.param_sharding,
+                   "eager_microbatch_dispatch": bool(cfg.eager_microbatch_dispatch), "param_sharding": cfg.param_sharding, "generation_tp_size": cfg.generation_tp_size,
                    "colocated_rollout_sms": cfg.colocated_rollout_sms},
         "clocks": state["clocks"],
         "e2e": {"value": samples / state["wall"], "unit": "samples/s",

@@ -404,3 +404,29 @@ def test_tensor_parallel_engine_matches_unsharded_model():
         p.join(timeout=60)
     for rank, msg in results:
         assert msg == "ok", f"rank {rank}: {msg}"
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+@pytest.mark.timeout(900)
+def test_runtime_with_a_tensor_parallel_rollout_replica(tmp_path):
+    """The whole role graph on 2 GPUs with generation_tp_size = 2: rank 0 hosts trainer, logprob and the replica's leader,
+    rank 1 the follower that replays the leader's engine calls. Two macro-batches with a weight push after each (the
+    follower pauses and resumes with the leader) and the weight-sync checksum verified on every rank."""
+    from async_grpo_nccl_b200.data import synthetic_prompt_rows
+    from async_grpo_nccl_b200.launch import spawn
+
+    arch = dict(vocab_size=2048, hidden_size=1024, intermediate_size=2816, num_hidden_layers=2, num_attention_heads=8,
+                num_key_value_heads=2, head_dim=128, rope_theta=1e4, max_position_embeddings=4096, tie_word_embeddings=True,
+                eos_token_id=1, attention_bias=True)
+    cfg = dict(model_name_or_path="tiny128", model_config=arch, batch_size=4, samples_per_question=4, num_epochs=1,
+               train_minibatch_sample_size=8, max_generation_tokens=24, max_tokens_per_gpu=2048, reward_fns=["token_match"],
+               global_num_verifiers=0, num_training_gpu_workers=1, num_logprob_gpu_workers=1, num_generation_gpu_workers=2,
+               generation_tp_size=2, max_num_seqs=64, vllm_engine_preset="throughput",
+               placement={"trainer": [0], "logprob": [0], "rollout": [0, 1]}, learning_rate=1e-4, output_dir=str(tmp_path),
+               min_samples_per_checkpoint=10 ** 9, eval_at_start=False, verify_weight_sync_during_init=True)
+    rows = synthetic_prompt_rows(8, 2048, 16, 32, seed=0)
+    out = spawn(cfg, rows, world=2, max_macro_batches=2, port=29861, timeout_s=300)
+    assert out["global_step"] == 2 and out["total_samples_seen"] == 32
+    import numpy as np
+
+    assert np.isfinite(out["last"]["training/avg_loss"])
