@@ -54,7 +54,7 @@ class GRPOConfig:
     max_generation_tokens: int = 4096
     max_num_seqs: int = 512
     overhead_seqs: int = 8
-    enable_prefix_caching: bool = True  # accepted; the n samples of a prompt always share its KV blocks, nothing is cached across requests
+    enable_prefix_caching: bool = True  # full prompt blocks stay findable by the hash of their token chain until the next weight push
     vllm_engine_preset: str = "eager"  # "eager" | "throughput" (CUDA-graphed decode step)
     kv_block_size: int = 16
     gpu_memory_utilization: float = 0.90

@@ -794,6 +794,8 @@ py::dict prefill_plan_to_dict(const agrpo::PrefillPlan& p) {
   d["group_ids"] = p.group_ids;
   d["prompt_lens"] = p.prompt_lens;
   d["slot_mapping"] = p.slot_mapping;
+  d["cached_lens"] = p.cached_lens;
+  d["prefix_slots"] = p.prefix_slots;
   d["seq_ids"] = p.seq_ids;
   d["seq_slots"] = p.seq_slots;
   d["copy_src"] = p.copy_src;
@@ -841,12 +843,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def(py::init<int, int, int, int, int>(), py::arg("num_blocks"), py::arg("block_size"), py::arg("max_seqs"),
            py::arg("max_blocks_per_seq"), py::arg("max_prefill_tokens"))
       .def("add_group",
-           [](agrpo::Scheduler& s, long long group_id, int prompt_len, int n, int max_new_tokens, std::vector<int> forced) {
-             agrpo::GroupRequest g{group_id, prompt_len, n, max_new_tokens, std::move(forced)};
+           [](agrpo::Scheduler& s, long long group_id, int prompt_len, int n, int max_new_tokens, std::vector<int> forced,
+              std::vector<unsigned long long> block_hashes) {
+             agrpo::GroupRequest g{group_id, prompt_len, n, max_new_tokens, std::move(forced), std::move(block_hashes)};
              s.add_group(g);
            },
            py::arg("group_id"), py::arg("prompt_len"), py::arg("n"), py::arg("max_new_tokens"),
-           py::arg("forced_new_tokens") = std::vector<int>())
+           py::arg("forced_new_tokens") = std::vector<int>(), py::arg("block_hashes") = std::vector<unsigned long long>())
       .def("plan_prefill", [](agrpo::Scheduler& s) { return prefill_plan_to_dict(s.plan_prefill()); })
       .def("plan_decode", [](agrpo::Scheduler& s) { return decode_plan_to_dict(s.plan_decode()); })
       .def("finish", &agrpo::Scheduler::finish)
@@ -865,7 +868,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_property_readonly("num_waiting", &agrpo::Scheduler::num_waiting)
       .def_property_readonly("num_running", &agrpo::Scheduler::num_running)
       .def_property_readonly("num_free_blocks", &agrpo::Scheduler::num_free_blocks)
-      .def_property_readonly("num_free_slots", &agrpo::Scheduler::num_free_slots);
+      .def_property_readonly("num_free_slots", &agrpo::Scheduler::num_free_slots)
+      .def_property_readonly("num_cached_blocks", &agrpo::Scheduler::num_cached_blocks)
+      .def("clear_prefix_cache", &agrpo::Scheduler::clear_prefix_cache);
 
   m.def("gemm_bf16", &gemm_bf16, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("a_mn") = false,
         py::arg("b_mn") = false, py::arg("bias") = py::none(), py::arg("alpha") = 1.0, py::arg("accumulate") = false,

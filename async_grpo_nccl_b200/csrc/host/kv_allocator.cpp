@@ -5,24 +5,83 @@
 
 namespace agrpo {
 
-BlockAllocator::BlockAllocator(int num_blocks) : ref_(num_blocks, 0) {
+BlockAllocator::BlockAllocator(int num_blocks)
+    : ref_(num_blocks, 0), hash_(num_blocks, 0ull), gen_(num_blocks, 0u), evict_stamp_(num_blocks, 0u) {
   free_.reserve(num_blocks);
   for (int i = num_blocks - 1; i >= 0; --i) free_.push_back(i);
 }
 int BlockAllocator::alloc() {
-  if (free_.empty()) return -1;
-  const int b = free_.back();
-  free_.pop_back();
+  int b = -1;
+  if (!free_.empty()) {
+    b = free_.back();
+    free_.pop_back();
+  } else {
+    while (!evictable_.empty()) {  // oldest cached block without users
+      const auto e = evictable_.front();
+      evictable_.pop_front();
+      if (evict_stamp_[e.first] != e.second || ref_[e.first] != 0) continue;  // stale entry
+      b = e.first;
+      evict_stamp_[b] = 0;
+      --n_evictable_;
+      cached_.erase(hash_[b]);
+      hash_[b] = 0;
+      break;
+    }
+    if (b < 0) return -1;
+  }
   ref_[b] = 1;
+  ++gen_[b];
   return b;
 }
 void BlockAllocator::incref(int block) {
   if (block < 0 || block >= (int)ref_.size() || ref_[block] <= 0) throw std::runtime_error("incref of a free block");
   ++ref_[block];
 }
+void BlockAllocator::push_evictable(int block) {
+  evict_stamp_[block] = next_stamp_++;
+  if (next_stamp_ == 0) next_stamp_ = 1;
+  evictable_.emplace_back(block, evict_stamp_[block]);
+  ++n_evictable_;
+}
 void BlockAllocator::release(int block) {
   if (block < 0 || block >= (int)ref_.size() || ref_[block] <= 0) throw std::runtime_error("release of a free block");
-  if (--ref_[block] == 0) free_.push_back(block);
+  if (--ref_[block] == 0) {
+    if (hash_[block] != 0) push_evictable(block);
+    else free_.push_back(block);
+  }
+}
+int BlockAllocator::lookup(unsigned long long hash) const {
+  if (hash == 0) return -1;
+  auto it = cached_.find(hash);
+  return it == cached_.end() ? -1 : it->second;
+}
+void BlockAllocator::acquire(int block) {
+  if (block < 0 || block >= (int)ref_.size() || hash_[block] == 0) throw std::runtime_error("acquire of a block that is not cached");
+  if (ref_[block] == 0) {
+    evict_stamp_[block] = 0;  // its queue entry is now stale
+    --n_evictable_;
+  }
+  ++ref_[block];
+}
+void BlockAllocator::set_hash(int block, unsigned long long hash, unsigned int generation) {
+  if (hash == 0 || block < 0 || block >= (int)ref_.size()) return;
+  if (gen_[block] != generation || ref_[block] <= 0 || hash_[block] != 0) return;  // handed out again, or already known
+  if (cached_.count(hash)) return;  // another block already holds this chain
+  cached_[hash] = block;
+  hash_[block] = hash;
+}
+void BlockAllocator::clear_cache() {
+  for (const auto& kv : cached_) {
+    const int b = kv.second;
+    hash_[b] = 0;
+    if (ref_[b] == 0) {
+      evict_stamp_[b] = 0;
+      free_.push_back(b);
+    }
+  }
+  cached_.clear();
+  evictable_.clear();
+  n_evictable_ = 0;
 }
 
 Scheduler::Scheduler(int num_blocks, int block_size, int max_seqs, int max_blocks_per_seq, int max_prefill_tokens)
@@ -44,28 +103,53 @@ void Scheduler::add_group(const GroupRequest& req) {
 
 PrefillPlan Scheduler::plan_prefill() {
   PrefillPlan plan;
+  commit_pending_hashes();
   int tokens = 0;
   while (!waiting_.empty()) {
     const GroupRequest& g = waiting_.front();
     const int full = g.prompt_len / block_size_;
     const int rem = g.prompt_len % block_size_;
+    // leading full blocks that the prefix cache already holds (at least one prompt token is always computed: its
+    // hidden state is what the first sampled token comes from)
+    std::vector<int> hit_blocks;
+    int hit_unused = 0;
+    {
+      const int lim = std::min(full, (int)g.block_hashes.size());
+      while ((int)hit_blocks.size() < lim) {
+        const int b = alloc_.lookup(g.block_hashes[hit_blocks.size()]);
+        if (b < 0) break;
+        hit_blocks.push_back(b);
+      }
+      if (!hit_blocks.empty() && (int)hit_blocks.size() * block_size_ == g.prompt_len) hit_blocks.pop_back();
+      for (int b : hit_blocks) hit_unused += alloc_.refcount(b) == 0 ? 1 : 0;
+    }
+    const int hit = (int)hit_blocks.size();
+    const int cached = hit * block_size_;
     // blocks: shared full blocks + one private block per child for the partial tail (or the first new token)
-    const int need_blocks = full + g.n;
+    const int need_blocks = (full - hit) + g.n;
     // keep one spare block per running sequence so that the next decode steps do not immediately preempt
     const int reserve = num_running_ + g.n;
     if ((int)free_slots_.size() < g.n) break;
-    if (alloc_.num_free() < need_blocks + reserve) break;
-    if (!plan.group_ids.empty() && tokens + g.prompt_len > max_prefill_tokens_) break;
-    // shared prompt blocks
+    if (alloc_.num_free() - hit_unused < need_blocks + reserve) break;  // hit blocks without users count as free today
+    if (!plan.group_ids.empty() && tokens + (g.prompt_len - cached) > max_prefill_tokens_) break;
+    // shared prompt blocks: the cached ones, then new ones
     std::vector<int> shared(full);
-    for (int b = 0; b < full; ++b) shared[b] = alloc_.alloc();
+    for (int b = 0; b < hit; ++b) {
+      alloc_.acquire(hit_blocks[b]);
+      shared[b] = hit_blocks[b];
+    }
+    for (int b = hit; b < full; ++b) {
+      shared[b] = alloc_.alloc();
+      if (b < (int)g.block_hashes.size())
+        pending_hashes_.push_back({shared[b], g.block_hashes[b], alloc_.generation(shared[b])});
+    }
     std::vector<int> tails(g.n);
     for (int c = 0; c < g.n; ++c) tails[c] = alloc_.alloc();
     // slot mapping for the prompt tokens: full blocks, then child 0's tail block
     for (int p = 0; p < g.prompt_len; ++p) {
       const int bi = p / block_size_;
       const int blk = bi < full ? shared[bi] : tails[0];
-      plan.slot_mapping.push_back(blk * block_size_ + p % block_size_);
+      (p < cached ? plan.prefix_slots : plan.slot_mapping).push_back(blk * block_size_ + p % block_size_);
     }
     for (int c = 0; c < g.n; ++c) {
       SeqState s;
@@ -95,14 +179,23 @@ PrefillPlan Scheduler::plan_prefill() {
     }
     plan.group_ids.push_back(g.group_id);
     plan.prompt_lens.push_back(g.prompt_len);
-    tokens += g.prompt_len;
+    plan.cached_lens.push_back(cached);
+    tokens += g.prompt_len - cached;
     waiting_.pop_front();
   }
   return plan;
 }
 
+// What the last planned prefill computes is in the cache by the time the scheduler is called again: from then on other
+// prompts may find those blocks (and they stay findable after their sequences finish).
+void Scheduler::commit_pending_hashes() {
+  for (const PendingHash& ph : pending_hashes_) alloc_.set_hash(ph.block, ph.hash, ph.generation);
+  pending_hashes_.clear();
+}
+
 DecodePlan Scheduler::plan_decode() {
   DecodePlan plan;
+  commit_pending_hashes();
   // The token produced by the previous step (or by prefill) is written at position `len`; make sure its block exists.
   std::vector<SeqState*> order;
   for (int slot = 0; slot < max_seqs_; ++slot) {
@@ -188,6 +281,7 @@ std::vector<std::pair<int, int>> Scheduler::compact_slots() {
 }
 
 void Scheduler::finish(long long seq_id) {
+  commit_pending_hashes();
   auto it = seqs_.find(seq_id);
   if (it == seqs_.end()) return;
   if (!it->second.finished || it->second.slot >= 0) release_seq(it->second);

@@ -67,7 +67,7 @@ class RolloutEngine:
     def __init__(self, cfg: ModelConfig, layout: ParamLayout, params: torch.Tensor, *, max_seqs: int = 256,
                  max_model_len: Optional[int] = None, num_blocks: Optional[int] = None, block_size: int = 16,
                  kv_memory_bytes: Optional[int] = None, max_prefill_tokens: int = 16384, use_cuda_graph: bool = False,
-                 eos_token_id: Optional[int] = None, tp: Any = None):
+                 eos_token_id: Optional[int] = None, tp: Any = None, prefix_caching: bool = False):
         from ..ops import native
 
         assert params.is_cuda and params.dtype == torch.bfloat16
@@ -89,6 +89,13 @@ class RolloutEngine:
         self.Hq_l, self.Hkv_l, self.F_l = cfg.num_attention_heads // t, cfg.num_key_value_heads // t, cfg.intermediate_size // t
         self.Q_l = (self.Hq_l + 2 * self.Hkv_l) * cfg.head_dim
         self.qd_l = self.Hq_l * cfg.head_dim
+        # Prefix caching across requests (vllm_worker.py:224, enable_prefix_caching): full prompt blocks stay findable by
+        # the hash of their token chain after their last user has gone; a later prompt that starts with the same chain
+        # reuses them and only its remaining tokens go through the GEMMs. Forgotten at every weight update. A
+        # tensor-parallel member caches only its own kv heads while the prefill needs all of them, so it stays off there.
+        self.prefix_caching = bool(prefix_caching) and self.tp is None
+        self.prefix_hit_tokens = 0
+        self.prefix_lookup_tokens = 0
         self.sm_count = torch.cuda.get_device_properties(self.dev).multi_processor_count  # SMs the engine's stream may use
         self.dec = NativeDecoder(cfg, layout, params)
         self.status = self.dec.status
@@ -264,8 +271,21 @@ class RolloutEngine:
             r.group_id = self.next_group
             self.next_group += 1
             self.requests[r.group_id] = r
-            self.sched.add_group(r.group_id, len(r.prompt), r.n, r.max_new_tokens, r.forced_new_tokens or [])
+            self.sched.add_group(r.group_id, len(r.prompt), r.n, r.max_new_tokens, r.forced_new_tokens or [],
+                                 self._block_hashes(r.prompt) if self.prefix_caching else [])
         self.pending = keep
+
+    def _block_hashes(self, prompt: np.ndarray) -> List[int]:
+        """Hash of the token chain up to and including every full block of the prompt (64 bits, never 0)."""
+        import hashlib
+
+        out: List[int] = []
+        prev = b"agrpo-prefix"
+        bs = self.block_size
+        for b in range(len(prompt) // bs):
+            prev = hashlib.blake2b(prev + prompt[b * bs:(b + 1) * bs].tobytes(), digest_size=8).digest()
+            out.append(int.from_bytes(prev, "little") or 1)
+        return out
 
     # ------------------------------------------------------------------ model pieces
     def _kc(self, i: int) -> torch.Tensor:
@@ -301,12 +321,19 @@ class RolloutEngine:
         self._apply_table_updates(plan)
         cos_t, sin_t = dec.rope_tables(1)
         T = batch.T
-        x = torch.empty(T, cfg.hidden_size, dtype=torch.bfloat16, device=self.dev)
-        C.embedding_fwd(batch.ids, dec.w("embed"), x)
-        for i in range(cfg.num_hidden_layers):
-            x = dec._layer_fwd(i, x, batch, cos_t, sin_t, None, kv_write=(self._kc(i), self._vc(i), slots, self.tp_rank * self.Hkv_l))
-        last = (batch.cu_seqlens[1:] - 1).long()
-        xl = x.index_select(0, last)
+        cached = plan.get("cached_lens") or []
+        if self.prefix_caching:
+            self.prefix_lookup_tokens += T
+            self.prefix_hit_tokens += int(sum(cached))
+        if any(cached):
+            xl = self._prefill_suffix(plan, batch, slots, cached, cos_t, sin_t)
+        else:
+            x = torch.empty(T, cfg.hidden_size, dtype=torch.bfloat16, device=self.dev)
+            C.embedding_fwd(batch.ids, dec.w("embed"), x)
+            for i in range(cfg.num_hidden_layers):
+                x = dec._layer_fwd(i, x, batch, cos_t, sin_t, None, kv_write=(self._kc(i), self._vc(i), slots, self.tp_rank * self.Hkv_l))
+            last = (batch.cu_seqlens[1:] - 1).long()
+            xl = x.index_select(0, last)
         hn = torch.empty_like(xl)
         C.rmsnorm_fwd(xl, dec.w("final_norm"), hn, None, cfg.rms_norm_eps)
         if plan["copy_src"]:
@@ -357,6 +384,37 @@ class RolloutEngine:
             for j, slot in enumerate(seq_slots):
                 if self.h_watch[slot] and int(th[j]) == self.eos:
                     self.h_eos_at[slot] = 0
+
+    def _prefill_suffix(self, plan: Dict[str, Any], batch: Any, slots: torch.Tensor, cached: Sequence[int], cos_t, sin_t) -> torch.Tensor:
+        """Prefill of prompts whose leading blocks came from the prefix cache: only the remaining tokens go through the
+        projections and the MLP; their attention runs over the whole prompt, with the keys and values of the cached
+        tokens gathered from the cache. Returns the hidden state of every prompt's last token."""
+        cfg, C, dec = self.cfg, self.C, self.dec
+        cu = np.concatenate([[0], np.cumsum(np.asarray(plan["prompt_lens"], dtype=np.int64))])  # prompts are packed in order
+        sfx_parts, pfx_parts, last_s = [], [], []
+        n_s = 0
+        for g, c in enumerate(cached):
+            a, b = int(cu[g]), int(cu[g + 1])
+            pfx_parts.append(np.arange(a, a + int(c), dtype=np.int64))
+            sfx_parts.append(np.arange(a + int(c), b, dtype=np.int64))
+            n_s += b - a - int(c)
+            last_s.append(n_s - 1)
+        idx_host = torch.from_numpy(np.concatenate(sfx_parts + pfx_parts + [np.asarray(last_s, dtype=np.int64),
+                                                                           np.asarray(plan["prefix_slots"], dtype=np.int64)]))
+        idx = idx_host.pin_memory().to(self.dev, non_blocking=True)
+        self.h2d_bytes += idx.numel() * 8
+        n_p = int(sum(int(c) for c in cached))
+        sfx, pfx = idx[:n_s], idx[n_s:n_s + n_p]
+        last = idx[n_s + n_p:n_s + n_p + len(cached)]
+        pslots = idx[n_s + n_p + len(cached):]
+        ids_s = batch.ids.index_select(0, sfx)
+        pos_s = batch.pos.index_select(0, sfx)
+        x = torch.empty(n_s, cfg.hidden_size, dtype=torch.bfloat16, device=self.dev)
+        C.embedding_fwd(ids_s, dec.w("embed"), x)
+        blk, off = pslots // self.block_size, pslots % self.block_size
+        for i in range(cfg.num_hidden_layers):
+            x = dec.layer_fwd_suffix(i, x, batch, sfx, pfx, pos_s, cos_t, sin_t, self._kc(i), self._vc(i), slots, blk, off)
+        return x.index_select(0, last)
 
     def _decode_forward(self, B: int, temperature: float, splits: int) -> None:
         if self.mega_rows and B <= self.mega_rows:
@@ -725,7 +783,8 @@ class RolloutEngine:
         return {"engine_decode_steps": float(self.n_decode_steps), "engine_prefill_steps": float(self.n_prefill_steps),
                 "engine_plan_s": self.t_plan, "engine_prep_s": self.t_prep, "engine_launch_s": self.t_launch,
                 "engine_post_s": self.t_post, "engine_prefill_s": self.t_prefill, "engine_wait_s": self.t_wait,
-                "engine_compactions": float(self.n_compactions)}
+                "engine_compactions": float(self.n_compactions), "engine_prefix_hit_tokens": float(self.prefix_hit_tokens),
+                "engine_prefix_lookup_tokens": float(self.prefix_lookup_tokens)}
 
     def _requeue_preempted(self, seq_ids: List[int]) -> None:
         # A preempted sample restarts from its prompt with the same seed stream (its progress is dropped).
@@ -756,6 +815,7 @@ class RolloutEngine:
         """Called after new weights were written into ``params`` in place; captured graphs stay valid
         because they reference the same buffers. The norm-folded copies of the fused decode path are refreshed
         here, and the caller's stream is drained so that the engine thread's next step sees them."""
+        self.sched.clear_prefix_cache()  # cached keys and values belong to the previous weights
         if self.fused_decode:
             self.refold_weights()
             torch.cuda.current_stream(self.dev).synchronize()

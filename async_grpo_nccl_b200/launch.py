@@ -182,7 +182,7 @@ class InProcessRuntime:
             max_len = min(mcfg.max_position_embeddings, cfg.max_generation_tokens + 4096)
             engine = RolloutEngine(mcfg, self.layout, self.rollout_params, max_seqs=cfg.max_num_seqs, max_model_len=max_len,
                                    kv_memory_bytes=kv_bytes, use_cuda_graph=cfg.vllm_engine_preset == "throughput",
-                                   block_size=cfg.kv_block_size)
+                                   block_size=cfg.kv_block_size, prefix_caching=cfg.enable_prefix_caching)
         else:
             from .engine.engine import OracleEngine
 
@@ -556,7 +556,7 @@ class DistributedRuntime:
                 self.engine = RolloutEngine(self.mcfg, self.layout, self.infer_params, max_seqs=config.max_num_seqs,
                                             max_model_len=max_len, kv_memory_bytes=int(free * share), num_blocks=tp_blocks,
                                             use_cuda_graph=config.vllm_engine_preset == "throughput", block_size=config.kv_block_size,
-                                            tp=self.tp_comm)
+                                            tp=self.tp_comm, prefix_caching=config.enable_prefix_caching)
             else:
                 from .engine.engine import OracleEngine
 

@@ -221,6 +221,47 @@ class NativeDecoder:
             save.update(x=x, h1=h1, rstd1=rstd1, qkv=qkv, attn=attn, lse=lse, x1=x1, h2=h2, rstd2=rstd2, gu=gu, act=act)
         return x2
 
+    def layer_fwd_suffix(self, i: int, x: torch.Tensor, batch: PackedBatch, sfx: torch.Tensor, pfx: torch.Tensor,
+                         pos_s: torch.Tensor, cos_t, sin_t, k_cache: torch.Tensor, v_cache: torch.Tensor, slots: torch.Tensor,
+                         pfx_blk: torch.Tensor, pfx_off: torch.Tensor) -> torch.Tensor:
+        """Layer forward for a rollout prefill whose leading prompt tokens are already in the KV cache (prefix caching).
+        ``x`` holds the rows of the tokens that still have to be computed (packed positions ``sfx`` of ``batch``, which
+        describes the whole prompts). Projections and MLP run on those rows only; attention runs over the whole prompts
+        with the keys / values of the cached tokens (packed positions ``pfx``, cache block / offset ``pfx_blk`` /
+        ``pfx_off``) gathered from the cache. The query rows of cached tokens are zero and their outputs are dropped."""
+        cfg, C = self.cfg, self.C
+        Ts, T = x.shape[0], batch.T
+        Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        p = f"layers.{i}."
+        self._enter_unit(i + 1, None)
+        h1 = self._new(Ts, cfg.hidden_size)
+        C.rmsnorm_fwd(x, self.w(p + "ln1"), h1, None, cfg.rms_norm_eps)
+        qkv_s = self._new(Ts, cfg.qkv_dim)
+        self._gemm(h1, self.w(p + "wqkv"), qkv_s, bias=self.w(p + "bqkv") if cfg.attention_bias else None)
+        C.rope_inplace(qkv_s, pos_s, cos_t, sin_t, Hq + Hkv, D, False)
+        C.kv_cache_write(qkv_s, slots, k_cache, v_cache, Hq, Hkv, D, self.status, 0)
+        qkv = torch.zeros(T, cfg.qkv_dim, dtype=torch.bfloat16, device=x.device)
+        qkv.index_copy_(0, sfx, qkv_s)
+        heads = qkv.view(T, Hq + 2 * Hkv, D)
+        heads[pfx, Hq:Hq + Hkv] = k_cache[pfx_blk, :, pfx_off]   # [cached tokens, Hkv, D]
+        heads[pfx, Hq + Hkv:] = v_cache[pfx_blk, :, pfx_off]
+        attn = self._new(T, cfg.q_dim)
+        lse = self._new(Hq, T, dtype=torch.float32)
+        C.attn_varlen_fwd(qkv, attn, lse, batch.tiles, Hq, Hkv, D, 1.0 / math.sqrt(D), self.status)
+        attn_s = attn.index_select(0, sfx)
+        x1 = self._new(Ts, cfg.hidden_size)
+        self._gemm(attn_s, self.w(p + "wo"), x1, residual=x)
+        h2 = self._new(Ts, cfg.hidden_size)
+        C.rmsnorm_fwd(x1, self.w(p + "ln2"), h2, None, cfg.rms_norm_eps)
+        gu = self._new(Ts, 2 * cfg.intermediate_size)
+        self._gemm(h2, self.w(p + "wgu"), gu)
+        act = self._new(Ts, cfg.intermediate_size)
+        C.swiglu_fwd(gu, act)
+        x2 = self._new(Ts, cfg.hidden_size)
+        self._gemm(act, self.w(p + "wd"), x2, residual=x1)
+        self.launches += 12
+        return x2
+
     def _layer_bwd(self, i: int, dx: torch.Tensor, s: dict, batch: PackedBatch, cos_t, sin_t, sink: GradSink):
         """dx (bf16 [T, H]) is the gradient w.r.t. the layer output; it is updated in place to the gradient w.r.t. the input."""
         cfg, C = self.cfg, self.C

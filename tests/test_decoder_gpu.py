@@ -437,3 +437,54 @@ def test_engine_batches_above_256_rows_run_in_row_chunks():
             top = top2.values[0].item()
             # the decode path and the teacher-forced pass round differently: a near-tie may go to the runner-up
             assert int(tok) in top2.indices.tolist() or row[int(tok)].item() >= top - (0.03 * abs(top) + 0.05), (o.request_id, j)
+
+
+def test_engine_prefix_cache_hits_do_not_change_tokens():
+    """Prefix caching across requests: prompts that start with an already prefilled chain reuse its KV blocks and only
+    compute their remaining tokens. Tokens must equal those of an engine without the cache (greedy and sampled), the
+    hit counters must show the reuse, and a weight update must empty the cache."""
+    from async_grpo_nccl_b200.engine.engine import RolloutEngine
+    from async_grpo_nccl_b200.models.config import PRESETS
+    from async_grpo_nccl_b200.models.layout import ParamLayout
+
+    cfg = PRESETS["tiny128"]
+    layout = ParamLayout(cfg)
+    p32 = torch.empty(layout.total)
+    layout.init_random_(p32, 0)
+    p16 = (p32 * 3.0).to(torch.bfloat16).to(DEV)
+    rng = np.random.default_rng(11)
+    prefix = rng.integers(6, cfg.vocab_size, 48).astype(np.int32)
+    pa = np.concatenate([prefix, rng.integers(6, cfg.vocab_size, 10).astype(np.int32)])
+    pb = np.concatenate([prefix, rng.integers(6, cfg.vocab_size, 23).astype(np.int32)])
+    other = rng.integers(6, cfg.vocab_size, 37).astype(np.int32)
+
+    def run(cache):
+        eng = RolloutEngine(cfg, layout, p16, max_seqs=32, max_model_len=256, num_blocks=512, use_cuda_graph=False,
+                            prefix_caching=cache)
+        outs = {}
+        eng.add_request("a", pa, n=2, max_new_tokens=8, temperature=0.0, seed=1, ignore_eos=True)
+        for o in eng.run_until_done():
+            outs[(o.request_id, o.child)] = o.output_ids.tolist()
+        first_hits = eng.prefix_hit_tokens
+        # the same chain again (whole prompt known: its last block is recomputed), a longer prompt on the same prefix,
+        # and an unrelated prompt, prefilled together
+        eng.add_request("a2", pa, n=1, max_new_tokens=8, temperature=1.0, seed=2, ignore_eos=True)
+        eng.add_request("b", pb, n=2, max_new_tokens=8, temperature=0.0, seed=3, ignore_eos=True)
+        eng.add_request("c", other, n=1, max_new_tokens=8, temperature=0.0, seed=4, ignore_eos=True)
+        for o in eng.run_until_done():
+            outs[(o.request_id, o.child)] = o.output_ids.tolist()
+        eng.check_status()
+        assert eng.sched.num_running == 0 and eng.sched.num_free_blocks == 512
+        return outs, first_hits, eng
+
+    base, h0, _ = run(False)
+    got, h1, eng = run(True)
+    assert h0 == 0 and h1 == 0
+    assert eng.prefix_hit_tokens == 48 + 48, eng.prefix_hit_tokens
+    assert got == base
+    assert eng.sched.num_cached_blocks > 0
+    eng.update_weights_done()
+    assert eng.sched.num_cached_blocks == 0
+    eng.add_request("a3", pa, n=1, max_new_tokens=4, temperature=0.0, seed=1, ignore_eos=True)
+    eng.run_until_done()
+    assert eng.prefix_hit_tokens == 96

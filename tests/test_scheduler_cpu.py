@@ -85,3 +85,54 @@ def test_block_pool_exhaustion_preempts_the_youngest_sequence():
     assert all(int(u) == survivor_slot for u in d["upd_slot"]), "table updates of the evicted sequence are dropped"
     d2 = s.plan_decode()
     assert d2["num_active"] == 1 and list(d2["preempted"]) == []
+
+
+def test_prefix_cache_reuses_blocks_across_requests_and_evicts_oldest_first():
+    """Prefix caching in the scheduler: a prompt whose leading full blocks carry known hashes takes those blocks instead
+    of new ones (only after the prefill that fills them has been planned in an EARLIER call), at least one token is
+    always left to compute, unused cached blocks count as free and are evicted oldest first, and a cleared cache
+    forgets everything."""
+    from async_grpo_nccl_b200.ops import native
+
+    C = native()
+    bs = 4
+    s = C.Scheduler(num_blocks=24, block_size=bs, max_seqs=8, max_blocks_per_seq=16, max_prefill_tokens=1024)
+    # request 0: 10 prompt tokens = 2 full blocks (hashes 11, 12) + a tail
+    s.add_group(0, 10, 1, 4, [], [11, 12])
+    p0 = s.plan_prefill()
+    assert p0["cached_lens"] == [0] and len(p0["slot_mapping"]) == 10 and p0["prefix_slots"] == []
+    blocks0 = s.seq_info(p0["seq_ids"][0])["blocks"]
+    # request 1, planned in the SAME call as request 2 below, shares the chain; request 0's blocks are registered when the
+    # next planning call starts
+    s.add_group(1, 9, 2, 4, [], [11, 12])
+    s.add_group(2, 8, 1, 4, [], [11, 12])   # exactly 2 full blocks: the last one is recomputed (one token at least)
+    p1 = s.plan_prefill()
+    assert p1["cached_lens"] == [8, 4]
+    assert len(p1["slot_mapping"]) == (9 - 8) + (8 - 4) and len(p1["prefix_slots"]) == 8 + 4
+    b1 = s.seq_info(p1["seq_ids"][0])["blocks"]
+    assert b1[:2] == blocks0[:2]
+    assert p1["prefix_slots"][:8] == [blocks0[0] * bs + i for i in range(4)] + [blocks0[1] * bs + i for i in range(4)]
+    free_before = s.num_free_blocks
+    # everybody finishes: hashed blocks stay cached and count as free
+    for sid in list(p0["seq_ids"]) + list(p1["seq_ids"]):
+        s.finish(sid)
+    assert s.num_cached_blocks == 2 and s.num_free_blocks == 24 and free_before < 24
+    # a new request with the same chain still hits although nobody held the blocks in between
+    s.add_group(3, 12, 1, 4, [], [11, 12, 13])
+    p3 = s.plan_prefill()
+    assert p3["cached_lens"] == [8] and s.seq_info(p3["seq_ids"][0])["blocks"][:2] == blocks0[:2]
+    s.finish(p3["seq_ids"][0])
+    assert s.num_cached_blocks == 3  # block 13 was registered by the call that followed its prefill plan
+    # exhaust the plain free blocks: cached blocks are evicted (oldest release first) and their hashes forgotten
+    s.add_group(4, 4 * 15, 1, 4, [], [])
+    p4 = s.plan_prefill()
+    assert p4["group_ids"] == [4]
+    s.add_group(5, 9, 1, 2, [], [11, 12])
+    p5 = s.plan_prefill()
+    assert p5["group_ids"] == [5] and p5["cached_lens"][0] in (0, 4, 8)
+    s.finish(p4["seq_ids"][0])
+    s.finish(p5["seq_ids"][0])
+    s.clear_prefix_cache()
+    assert s.num_cached_blocks == 0 and s.num_free_blocks == 24
+    s.add_group(6, 9, 1, 2, [], [11, 12])
+    assert s.plan_prefill()["cached_lens"] == [0]
