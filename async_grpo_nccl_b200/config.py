@@ -87,6 +87,11 @@ class GRPOConfig:
     keep_last_n_checkpoints: int = 2
     verify_weight_sync_during_init: bool = False
     # system/* series (GPU memory, utilisation, power, SM clock; read-only NVML queries) once per macro-batch
+    # Chrome trace (torch.profiler, host + CUDA activity of the orchestrator's process) of macro-batch number
+    # profile_macro_batch of this run, written to profile_trace_path; None = off. The reference only has a stub here
+    # (gpu_process_worker.py:49-51).
+    profile_trace_path: Optional[str] = None
+    profile_macro_batch: int = 1
     enable_manual_system_metrics: bool = False
     system_metrics_interval_sec: float = 10.0  # reference key; sampling here is per macro-batch
     # ---- new: engine behaviour ----

@@ -28,8 +28,8 @@ from typing import Any, Dict, List, Optional, Sequence
 from . import checkpoint as ckpt
 from .config import GRPOConfig, make_config
 from .metrics import MetricLogger, aggregate_completions
-
 from .protocol import RoleLostError
+from .utils.timing import profile_window
 
 logger = logging.getLogger(__name__)
 
@@ -154,7 +154,9 @@ class Orchestrator:
                 if epoch == start_epoch and b < start_offset:
                     continue  # resume: fast-forward the data order (orchestrator.py:826-866)
                 batch = rows[b * cfg.batch_size:(b + 1) * cfg.batch_size]
-                rec = await self._run_macro_batch(batch, epoch)
+                # opt-in torch.profiler trace (host + CUDA activity of this process) of one macro-batch
+                with profile_window(cfg.profile_trace_path, active=len(self.step_records) == cfg.profile_macro_batch):
+                    rec = await self._run_macro_batch(batch, epoch)
                 self.step_records.append(rec)
                 if self.max_macro_batches is not None and len(self.step_records) >= self.max_macro_batches:
                     done = True

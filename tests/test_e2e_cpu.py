@@ -20,6 +20,7 @@ def _cfg(tmp_path, **kw):
 
 def test_cpu_end_to_end_two_macro_batches(tmp_path):
     cfg = _cfg(tmp_path)
+    cfg.profile_trace_path = str(tmp_path / "trace.json")  # the second macro-batch is traced
     rows = synthetic_prompt_rows(8, 1024, 16, 32, seed=0)
     rt = build_inprocess_runtime(cfg, device="cpu")
     orch = Orchestrator(cfg, runtime=rt, dataset=rows)
@@ -39,6 +40,11 @@ def test_cpu_end_to_end_two_macro_batches(tmp_path):
     assert core.opt_step == 4
     # metrics JSONL was written
     assert (tmp_path / "training_metrics.jsonl").exists()
+    # the opt-in profiler window wrote a Chrome trace of one macro-batch
+    import json
+
+    with open(tmp_path / "trace.json") as f:
+        assert len(json.load(f)["traceEvents"]) > 0
 
 
 def test_streamed_logprobs_match_group_stage(tmp_path, monkeypatch):
