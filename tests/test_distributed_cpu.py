@@ -278,3 +278,23 @@ def test_replica_of_two_rollout_ranks_follows_its_leader(tmp_path):
     assert out["global_step"] == 2
     assert out["total_samples_seen"] == 32
     assert np.isfinite(out["last"]["training/avg_loss"])
+
+
+@pytest.mark.timeout(900)
+def test_named_eight_rank_placement(tmp_path):
+    """The placement of the 8-GPU configuration (4 sharded trainer ranks, 1 logprob rank, 3 rollout ranks) as 8 CPU ranks:
+    prompts spread over three engines, streamed logprob requests to one rank, microbatches planned over four trainer
+    ranks with dummy batches where a rank has nothing, and the weight push reaching all four inference ranks."""
+    cfg = dict(model_name_or_path="tiny", batch_size=6, samples_per_question=4, num_epochs=1, train_minibatch_sample_size=12,
+               max_generation_tokens=8, max_tokens_per_gpu=150, reward_fns=["token_match"], global_num_verifiers=0,
+               num_training_gpu_workers=4, num_logprob_gpu_workers=1, num_generation_gpu_workers=3,
+               placement={"trainer": [0, 1, 2, 3], "logprob": [4], "rollout": [5, 6, 7]}, learning_rate=1e-3,
+               output_dir=str(tmp_path), min_samples_per_checkpoint=10 ** 9, eval_at_start=False,
+               verify_weight_sync_during_init=True, eager_microbatch_dispatch=True)
+    rows = synthetic_prompt_rows(12, 1024, 16, 32, seed=0)
+    out = spawn(cfg, rows, world=8, max_macro_batches=2, port=29841, timeout_s=800)
+    assert out["global_step"] == 2
+    assert out["total_samples_seen"] == 48
+    last = out["last"]
+    assert last["training/optimizer_steps_in_batch"] == 2
+    assert np.isfinite(last["training/avg_loss"]) and last["training/grad_norm"] > 0
