@@ -90,6 +90,31 @@ def retire(names=("peft", "omegaconf")) -> None:
             del sys.modules[n]
 
 
+def transformers_compat() -> str:
+    """The reference reads ``model._no_split_modules[0]`` (gpu_process_worker.py:402, its FSDP wrapping for more than one
+    trainer rank). The installed transformers 5 keeps that attribute as a set; older versions kept the class's list. This
+    makes the set indexable (sorted order; Qwen2 has a single entry) without touching the reference or the set semantics
+    that transformers itself relies on. Returns a description for the JSON record."""
+    from transformers import PreTrainedModel
+
+    class IndexableSet(set):
+        def __getitem__(self, i):
+            return sorted(self)[i]
+
+    orig = PreTrainedModel.post_init
+    if not getattr(orig, "_agrpo_compat", False):
+        def post_init(self, *a: Any, **k: Any):
+            out = orig(self, *a, **k)
+            ns = getattr(self, "_no_split_modules", None)
+            if isinstance(ns, set) and not isinstance(ns, IndexableSet):
+                self._no_split_modules = IndexableSet(ns)
+            return out
+
+        post_init._agrpo_compat = True  # type: ignore[attr-defined]
+        PreTrainedModel.post_init = post_init
+    return "transformers.PreTrainedModel._no_split_modules made indexable (a set since transformers 5)"
+
+
 def install() -> Dict[str, str]:
     """Registers the stand-in modules. Returns {module name: what it stands for} for the JSON record."""
     made: Dict[str, str] = {}

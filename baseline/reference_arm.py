@@ -450,6 +450,7 @@ def _run(args, rank: int, n: int, host: str, port: int) -> Optional[Dict[str, An
     import gpu_process_worker as gpw
 
     ref_shims.retire()
+    shims["transformers._no_split_modules"] = ref_shims.transformers_compat()
     trainer = logprob = None
     if is_t:
         os.environ["RANK"], os.environ["WORLD_SIZE"] = str(T.index(rank)), str(len(T))
