@@ -27,6 +27,7 @@ import json
 import os
 import pickle
 import sys
+import threading
 import time
 from typing import Any, Dict, List, Optional, Tuple
 
@@ -368,6 +369,24 @@ class LogprobBatcher:
 
 
 # ------------------------------------------------------------------------------------------------ main
+def write_abort(path: str, msg: str) -> None:
+    """Leaves a failure note for the other ranks of this run (first writer wins)."""
+    try:
+        fd = os.open(path, os.O_CREAT | os.O_EXCL | os.O_WRONLY, 0o644)
+    except FileExistsError:
+        return
+    with os.fdopen(fd, "w") as f:
+        f.write(msg)
+
+
+def read_abort(path: str) -> Optional[str]:
+    try:
+        with open(path) as f:
+            return f.read() or "a rank of the reference arm failed"
+    except FileNotFoundError:
+        return None
+
+
 def run(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -391,15 +410,39 @@ def run(args) -> None:
     os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
     sys.path.insert(0, HERE)
     sys.path.insert(0, os.path.join(HERE, "_ref"))
+    # A rank that fails must not leave the others in their rendezvous timeouts (minutes each): it drops a note that every
+    # rank's watchdog thread looks for; rank 0 then reports `unavailable` and all of them leave at once.
+    abort_path = os.path.join(os.environ.get("TMPDIR", "/tmp"), f"agrpo_ref_abort_{port}_{os.getppid() if world > 1 else os.getpid()}")
+    printed = threading.Lock()
+
+    def report(msg: str) -> None:
+        if rank == 0 and printed.acquire(blocking=False):
+            print(json.dumps({"impl": "reference", "unavailable": msg[:400]}), flush=True)
+
+    def watchdog() -> None:
+        while True:
+            time.sleep(2.0)
+            msg = read_abort(abort_path)
+            if msg is not None:
+                report(msg)
+                os._exit(0)
+
+    if world > 1:
+        threading.Thread(target=watchdog, name="abort-watchdog", daemon=True).start()
+    result = None
     try:
         result = _run(args, rank, n, host, port)
     except Exception as e:  # the arm reports instead of failing the round's bench step
         import traceback
 
         traceback.print_exc()
-        result = {"impl": "reference", "unavailable": f"reference arm failed on rank {rank}: {type(e).__name__}: {str(e)[:300]}"} \
-            if rank == 0 else None
-    if rank == 0 and result is not None:
+        msg = f"reference arm failed on rank {rank}: {type(e).__name__}: {str(e)[:300]}"
+        write_abort(abort_path, msg)
+        report(msg)
+        if rank != 0 and world > 1:
+            time.sleep(5.0)  # rank 0's watchdog prints the line; this process must not be the first to vanish
+        os._exit(0)
+    if rank == 0 and result is not None and printed.acquire(blocking=False):
         print(json.dumps(result), flush=True)
     os._exit(0)  # vLLM and NCCL helper threads must not keep the process alive
 

@@ -96,3 +96,14 @@ def test_stand_in_modules_carry_the_names_the_reference_imports():
     if "peft" in made:
         ref_shims.retire()
         assert importlib.util.find_spec("peft") is None  # libraries probing for the real package see it as absent
+
+
+def test_abort_note_first_writer_wins(tmp_path):
+    """A failing rank leaves one note; later failures do not overwrite it, and the other ranks read it."""
+    from reference_arm import read_abort, write_abort
+
+    p = str(tmp_path / "abort")
+    assert read_abort(p) is None
+    write_abort(p, "rank 3 failed: boom")
+    write_abort(p, "rank 1 failed later")
+    assert read_abort(p) == "rank 3 failed: boom"
