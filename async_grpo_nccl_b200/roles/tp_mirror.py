@@ -129,6 +129,12 @@ class TpFollower:
         except BaseException as e:
             logger.exception("tensor-parallel follower stopped: %r", e)
             self._dead = e
+            # the leader must learn of it: with the connection closed its next command raises instead of piling up
+            try:
+                if self.listener.conn is not None:
+                    self.listener.conn.close()
+            except OSError:
+                pass
 
     def _loop(self) -> None:
         import torch
