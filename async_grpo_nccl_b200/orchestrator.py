@@ -245,6 +245,13 @@ class Orchestrator:
             from .metrics import system_metrics
 
             rec.update(system_metrics())
+        if cfg.enable_prefix_caching and hasattr(rt, "collect_stats"):
+            try:  # share of prompt tokens whose keys / values came from the prefix cache (cumulative over the run)
+                st = await rt.collect_stats()
+                if st.get("engine_prefix_lookup_tokens", 0.0) > 0:
+                    rec["generation/prefix_cache_hit_rate"] = st["engine_prefix_hit_tokens"] / st["engine_prefix_lookup_tokens"]
+            except Exception as e:  # statistics never stop a run
+                logger.debug("engine statistics unavailable: %r", e)
         self.metrics.log(rec, step=self.global_step)
         for c in completions[:1]:
             for i, s in enumerate(c.get("minibatch_summaries", [])):

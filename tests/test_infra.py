@@ -461,3 +461,46 @@ def test_replica_command_stream_replays_in_order_and_holds_at_pause():
     with pytest.raises(RuntimeError):
         asyncio.run(fol.pause_for_sync())
     fol.shutdown()
+
+
+def test_leader_learns_that_a_replica_follower_stopped():
+    """A follower whose engine raises closes its connection: the leader's next commands fail with an OSError (which the
+    rollout worker turns into failed requests) instead of piling up in a socket nobody reads."""
+    import time
+
+    from async_grpo_nccl_b200.roles.tp_mirror import FollowerListener, LeaderChannel, TpFollower
+
+    class Store(dict):
+        def set(self, k, v):
+            self[k] = v.encode()
+
+        def get(self, k):
+            return self[k]
+
+    class Engine:
+        def add_request(self, *a, **k):
+            pass
+
+        def step(self):
+            raise RuntimeError("device status 5")
+
+        def check_status(self):
+            pass
+
+    store = Store()
+    fol = TpFollower(Engine(), FollowerListener(store, 3))
+    lead = LeaderChannel(store, [3])
+    lead.send("step")
+    fol._thread.join(timeout=5)
+    assert not fol._thread.is_alive() and isinstance(fol._dead, RuntimeError)
+    failed = False
+    deadline = time.time() + 5
+    while time.time() < deadline and not failed:
+        try:
+            lead.send("step")
+            time.sleep(0.05)
+        except OSError:
+            failed = True
+    assert failed, "writes to a closed follower connection must raise"
+    lead.close()
+    fol.shutdown()
