@@ -108,7 +108,9 @@ class GRPOConfig:
     # its own and the other roles the rest (CUDA green contexts, utils/sm_partition.py); 0 = all roles use every SM
     colocated_rollout_sms: int = 0
     colocated_sm_limit: int = 0  # > 0: trainer / logprob GEMMs fill at most this many SMs on a GPU they share with a rollout engine
-    param_sharding: str = "zero2"  # "zero2": resident bf16 copy per trainer rank | "zero3": fully sharded, gathered per layer
+    # "zero2": resident bf16 copy per trainer rank | "zero3": fully sharded, gathered per layer | "auto": zero3 when the
+    # resident form would take more than 60 % of a GPU's memory (launch.resolve_param_sharding)
+    param_sharding: str = "auto"
     activation_recompute: str = "auto"  # "none" | "full" | "auto" (by memory estimate)
     trainer_completion_timeout_s: float = 300.0
     prompt_timeout_s: float = 1200.0
@@ -184,7 +186,7 @@ class GRPOConfig:
         need(self.vllm_engine_preset in ("eager", "throughput"), "vllm_engine_preset must be eager or throughput")
         need(self.colocated_sm_limit >= 0, "colocated_sm_limit must be >= 0")
         need(self.colocated_rollout_sms >= 0, "colocated_rollout_sms must be >= 0")
-        need(self.param_sharding in ("zero2", "zero3"), "param_sharding must be zero2/zero3")
+        need(self.param_sharding in ("zero2", "zero3", "auto"), "param_sharding must be zero2/zero3/auto")
         need(self.activation_recompute in ("none", "full", "auto"), "activation_recompute must be none/full/auto")
         need(self.keep_last_n_checkpoints >= 1, "keep_last_n_checkpoints must be >= 1")
         need(self.weight_sync_every >= 1, "weight_sync_every must be >= 1")

@@ -65,6 +65,21 @@ def activation_bytes_per_token(m: ModelConfig) -> int:
     return per_layer * m.num_hidden_layers
 
 
+def resolve_param_sharding(mode: str, num_params: int, trainers: int, hbm_bytes: Optional[float], peer: bool) -> str:
+    """``auto`` -> ``zero2`` or ``zero3``. With resident parameters (zero2) a trainer rank holds the bf16 copy (2 bytes per
+    parameter), a full fp32 gradient buffer (4) and its share of master + moments (12 / trainers); fully sharded (zero3)
+    it holds 18 / trainers plus a few layers of staging. zero3 needs the peer-memory backend and more than one trainer
+    rank; it is chosen when the resident form would take more than 60 % of the GPU's memory (from about 14B parameters
+    on 180 GB parts with 4 trainer ranks), because activations, the logits-free loss scratch and, on shared GPUs, a KV
+    cache need the rest."""
+    if mode != "auto":
+        return mode
+    if not peer or trainers <= 1 or not hbm_bytes:
+        return "zero2"
+    resident = num_params * (6.0 + 12.0 / trainers)
+    return "zero3" if resident > 0.6 * hbm_bytes else "zero2"
+
+
 def want_recompute(config: GRPOConfig, mcfg: ModelConfig, budget_bytes: float) -> bool:
     if config.activation_recompute != "auto":
         return config.activation_recompute == "full"
@@ -134,6 +149,8 @@ def preflight_placement(place: Dict[str, Sequence[int]], world: int, visible_gpu
 class InProcessRuntime:
     def __init__(self, config: GRPOConfig, device: Optional[str] = None, kv_memory_bytes: Optional[int] = None):
         self.config = config
+        if config.param_sharding == "auto":
+            config.param_sharding = "zero2"  # one trainer rank: nothing to shard over
         self.device = torch.device(device or ("cuda:0" if torch.cuda.is_available() else "cpu"))
         self.native = self.device.type == "cuda"
         self.kv_memory_bytes = kv_memory_bytes
@@ -471,6 +488,8 @@ class DistributedRuntime:
 
             self.C = _native()
             use_peer = config.comm_backend in ("auto", "peer") and symm.symmetric_available()
+            config.param_sharding = resolve_param_sharding(config.param_sharding, self.mcfg.num_parameters(), t,
+                                                           float(torch.cuda.get_device_properties(self.device).total_memory), use_peer)
             if use_peer:
                 try:
                     # every rank allocates every symmetric buffer, in the same order, over the WORLD group
@@ -484,6 +503,8 @@ class DistributedRuntime:
                     logger.warning("symmetric memory unavailable (%r): falling back to library collectives", e)
                     self.trainer_comm, self.weight_sync, use_peer = None, None, False
         self.use_peer = use_peer
+        if config.param_sharding == "auto":
+            config.param_sharding = "zero2"
         if self.rank == 0 and config.param_sharding == "zero3" and not (use_peer and t > 1):
             logger.warning("param_sharding=zero3 needs the peer-memory backend and more than one trainer rank; "
                            "running with resident parameters (zero2) instead")

@@ -504,3 +504,16 @@ def test_leader_learns_that_a_replica_follower_stopped():
     assert failed, "writes to a closed follower connection must raise"
     lead.close()
     fol.shutdown()
+
+
+def test_auto_parameter_sharding_picks_the_fully_sharded_mode_for_large_models():
+    from async_grpo_nccl_b200.launch import resolve_param_sharding
+    from async_grpo_nccl_b200.models.config import PRESETS
+
+    hbm = 180e9
+    n15, n32 = PRESETS["qwen2.5-1.5b"].num_parameters(), PRESETS["qwen2.5-32b"].num_parameters()
+    assert resolve_param_sharding("auto", n15, 4, hbm, True) == "zero2"
+    assert resolve_param_sharding("auto", n32, 4, hbm, True) == "zero3"      # 6 P + 12 P / 4 = 295 GB resident
+    assert resolve_param_sharding("auto", n32, 4, hbm, False) == "zero2"     # no peer memory: the sharded mode cannot run
+    assert resolve_param_sharding("auto", n32, 1, hbm, True) == "zero2"
+    assert resolve_param_sharding("zero3", n15, 4, hbm, True) == "zero3" and resolve_param_sharding("zero2", n32, 4, hbm, True) == "zero2"
