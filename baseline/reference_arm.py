@@ -369,6 +369,16 @@ class LogprobBatcher:
 
 
 # ------------------------------------------------------------------------------------------------ main
+# Where this rank currently is (name, start time): a watchdog ends the arm when one phase takes longer than the limit, so a
+# deadlock between the reference's workers shows up as an `unavailable` line instead of an hour-long rendezvous timeout.
+PHASE: Dict[str, Any] = {"name": "start", "t": time.time()}
+PHASE_LIMIT_S = float(os.environ.get("AGRPO_REF_PHASE_LIMIT_S", "1200"))
+
+
+def set_phase(name: str) -> None:
+    PHASE["name"], PHASE["t"] = name, time.time()
+
+
 def write_abort(path: str, msg: str) -> None:
     """Leaves a failure note for the other ranks of this run (first writer wins)."""
     try:
@@ -423,12 +433,17 @@ def run(args) -> None:
         while True:
             time.sleep(2.0)
             msg = read_abort(abort_path)
+            if msg is None and time.time() - PHASE["t"] > PHASE_LIMIT_S:
+                msg = f"reference arm timed out on rank {rank} in phase '{PHASE['name']}' after {int(PHASE_LIMIT_S)} s"
+                write_abort(abort_path, msg)
             if msg is not None:
                 report(msg)
+                if rank != 0 and world > 1:
+                    time.sleep(5.0)  # let rank 0 print first
                 os._exit(0)
 
-    if world > 1:
-        threading.Thread(target=watchdog, name="abort-watchdog", daemon=True).start()
+    set_phase("start")
+    threading.Thread(target=watchdog, name="abort-watchdog", daemon=True).start()
     result = None
     try:
         result = _run(args, rank, n, host, port)
@@ -467,6 +482,7 @@ def _run(args, rank: int, n: int, host: str, port: int) -> Optional[Dict[str, An
     torch.cuda.set_device(0)
 
     # ---- model directory (rank 0 writes it; same random-init weights for every role) ----
+    set_phase("model directory")
     model_dir = os.path.join(os.environ.get("TMPDIR", "/tmp"), f"agrpo_ref_{args.model}_{port}")
     if rank == 0:
         build_model_dir(model_dir, args.model, seed=0)
@@ -485,6 +501,7 @@ def _run(args, rank: int, n: int, host: str, port: int) -> Optional[Dict[str, An
 
     # ---- rollout engine first: in a process that also hosts FSDP workers it creates the (single-rank) default
     # process group that those workers then find initialised ----
+    set_phase("rollout engine start")
     rollout = None
     if is_r:
         colocated = is_t or is_l
@@ -494,6 +511,7 @@ def _run(args, rank: int, n: int, host: str, port: int) -> Optional[Dict[str, An
 
     ref_shims.retire()
     shims["transformers._no_split_modules"] = ref_shims.transformers_compat()
+    set_phase("trainer / logprob worker start")
     trainer = logprob = None
     if is_t:
         os.environ["RANK"], os.environ["WORLD_SIZE"] = str(T.index(rank)), str(len(T))
@@ -516,6 +534,7 @@ def _run(args, rank: int, n: int, host: str, port: int) -> Optional[Dict[str, An
         if is_t and len(T) > 1:
             logprob.fsdp_group = solo
     # ---- the sync group: one member per process, order trainer + logprob + rollout ----
+    set_phase("sync group")
     order = list(dict.fromkeys(T + L + R))
     group = ref_shims.SYNC_GROUP
     group.rank, group.world = order.index(rank), len(order)
@@ -564,6 +583,7 @@ def _run(args, rank: int, n: int, host: str, port: int) -> Optional[Dict[str, An
         return (time.time() - t0) * 1000.0
 
     sync_all.n = 0
+    set_phase("initial weight sync")
     sync_all()  # initial sync, as the reference does at the end of its init (orchestrator.py:545)
 
     total_steps = args.warmup + args.steps
@@ -573,6 +593,7 @@ def _run(args, rank: int, n: int, host: str, port: int) -> Optional[Dict[str, An
     stats = {"gen_tokens": 0, "samples": 0, "sync_ms": [], "h2d": 0, "d2h": 0, "gen_s": 0.0, "train_s": 0.0}
 
     def one_step(step: int) -> None:
+        set_phase(f"macro-batch {step}")
         step_rows = rows[step * prompts_per_step:(step + 1) * prompts_per_step]
         # 1. generation: prompt i goes to engine i mod r; finished groups go to logprob worker (group mod l)
         if rollout is not None:
