@@ -19,7 +19,7 @@ from __future__ import annotations
 import math
 import os
 import time
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -28,7 +28,7 @@ import torch
 from ..models.config import ModelConfig
 from ..models.decoder import NativeDecoder, OracleDecoder
 from ..models.layout import ParamLayout
-from ..packing import PackedBatch, pack_samples
+from ..packing import pack_samples
 
 GOLDEN = 0x9E3779B97F4A7C15
 

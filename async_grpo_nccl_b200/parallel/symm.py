@@ -19,7 +19,7 @@ taken when symmetric memory is unavailable.
 from __future__ import annotations
 
 import logging
-from typing import Any, Dict, List, Optional, Sequence, Tuple
+from typing import Any, List, Optional, Sequence
 
 import torch
 import torch.distributed as dist

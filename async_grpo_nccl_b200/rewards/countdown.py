@@ -10,7 +10,7 @@ exactly once, contains only digits / + - * / ( ) / spaces and evaluates to the t
 from __future__ import annotations
 
 import re
-from typing import Any, Dict, List, Optional, Sequence
+from typing import Any, Dict, Optional, Sequence
 
 _THINK = re.compile(r"<think>.*?</think>", re.DOTALL)
 _ANSWER = re.compile(r"<answer>(.*?)</answer>", re.DOTALL)

@@ -20,13 +20,11 @@ B200-first differences:
 """
 from __future__ import annotations
 
-import json
 import math
 import os
 import time
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
-import numpy as np
 import torch
 
 from ..config import GRPOConfig
@@ -34,7 +32,7 @@ from ..models.config import ModelConfig
 from ..models.decoder import GradSink, LossConfig, NativeDecoder, OracleDecoder
 from ..models.layout import ParamLayout
 from ..ops import reference as R
-from ..packing import PackedBatch, make_dummy_batch, pack_samples
+from ..packing import pack_samples
 
 
 def lr_factor(step: int, warmup: int, total: int, kind: str) -> float:

@@ -23,7 +23,6 @@ import argparse
 import json
 import math
 import os
-import sys
 import time
 
 import numpy as np

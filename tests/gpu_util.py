@@ -1,7 +1,6 @@
 """Shared helpers for the GPU kernel tests: every kernel is compared with a plain PyTorch fp32 restatement."""
 import math
 
-import numpy as np
 import torch
 
 

@@ -13,7 +13,7 @@ from async_grpo_nccl_b200.metrics import aggregate_completions, merge_mean_std
 from async_grpo_nccl_b200.models.config import PRESETS, ModelConfig
 from async_grpo_nccl_b200.models.layout import ParamLayout
 from async_grpo_nccl_b200.protocol import Message, MessageType
-from async_grpo_nccl_b200.roles.trainer import TrainerCore, lr_factor
+from async_grpo_nccl_b200.roles.trainer import lr_factor
 from async_grpo_nccl_b200.rpc import RpcClient, RpcServer, dumps, loads
 
 

@@ -1,7 +1,6 @@
 """Numerics of every sm_100a kernel against plain PyTorch fp32 references."""
 import math
 
-import numpy as np
 import pytest
 import torch
 
