@@ -954,3 +954,55 @@ def spawn(config_dict: Dict[str, Any], rows: Any, world: int, max_macro_batches:
     if "error" in result:
         raise RuntimeError("the run failed on rank 0: " + result["error"])
     return result
+
+
+def main(argv: Optional[Sequence[str]] = None) -> int:
+    """``python -m async_grpo_nccl_b200.launch --config run.json [--set key=value ...]``
+
+    Runs the orchestrator on the flat config of a JSON file (the reference takes the same keys as a Python dict,
+    orchestrator.py:92-193, and has no command line). Started plainly it runs every role in this process (one GPU or
+    CPU); started under ``python -m torch.distributed.run --nproc-per-node N`` every rank builds the multi-process runtime,
+    rank 0 drives the orchestrator and the other ranks serve their roles."""
+    import argparse
+    import json as _json
+
+    from .config import make_config
+    from .orchestrator import Orchestrator, configure_logging
+
+    ap = argparse.ArgumentParser(prog="async_grpo_nccl_b200.launch")
+    ap.add_argument("--config", required=True, help="JSON file with the flat configuration keys")
+    ap.add_argument("--set", action="append", default=[], metavar="KEY=VALUE",
+                    help="override one key; the value is parsed as JSON when it parses, else taken as a string")
+    ap.add_argument("--max-macro-batches", type=int, default=None, help="stop after this many macro-batches")
+    args = ap.parse_args(argv)
+    with open(args.config) as f:
+        cfg_dict = dict(_json.load(f))
+    for kv in args.set:
+        k, _, v = kv.partition("=")
+        try:
+            cfg_dict[k] = _json.loads(v)
+        except ValueError:
+            cfg_dict[k] = v
+    configure_logging()
+    cfg = make_config(cfg_dict)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        rt = DistributedRuntime(cfg)
+        if rt.rank != 0:
+            rt.serve_forever()
+            return 0
+        orch = Orchestrator(cfg, runtime=rt)
+        orch.max_macro_batches = args.max_macro_batches
+        result = asyncio.run(orch.run_async())
+    else:
+        orch = Orchestrator(cfg)
+        orch.max_macro_batches = args.max_macro_batches
+        result = orch.run()
+    last = result["steps"][-1] if result["steps"] else {}
+    print(_json.dumps({"global_step": result["global_step"], "total_samples_seen": result["total_samples_seen"],
+                       "last": {k: v for k, v in last.items() if isinstance(v, (int, float))}}, default=float))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

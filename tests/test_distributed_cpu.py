@@ -298,3 +298,41 @@ def test_named_eight_rank_placement(tmp_path):
     last = out["last"]
     assert last["training/optimizer_steps_in_batch"] == 2
     assert np.isfinite(last["training/avg_loss"]) and last["training/grad_norm"] > 0
+
+
+@pytest.mark.timeout(900)
+def test_launcher_command_line_single_process_and_three_ranks(tmp_path):
+    """``python -m async_grpo_nccl_b200.launch --config run.json``: plain (all roles in one process) and under
+    ``torch.distributed.run`` with three CPU ranks (rank 0 drives, the others serve)."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    from async_grpo_nccl_b200.data import synthetic_prompt_rows
+
+    rows = synthetic_prompt_rows(8, 1024, 16, 32, seed=0)
+    data = tmp_path / "train.jsonl"
+    with open(data, "w") as f:
+        for r in rows:
+            f.write(json.dumps({k: (v.tolist() if hasattr(v, "tolist") else v) for k, v in r.items()}) + "\n")
+    cfg = dict(model_name_or_path="tiny", data_path=str(data), batch_size=4, samples_per_question=4, num_epochs=1,
+               train_minibatch_sample_size=8, max_generation_tokens=10, max_tokens_per_gpu=200, reward_fns=["token_match"],
+               global_num_verifiers=0, num_training_gpu_workers=1, learning_rate=1e-3, output_dir=str(tmp_path / "out1"),
+               min_samples_per_checkpoint=10 ** 9, eval_at_start=False)
+    path = tmp_path / "run.json"
+    path.write_text(json.dumps(cfg))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    one = subprocess.run([sys.executable, "-m", "async_grpo_nccl_b200.launch", "--config", str(path), "--max-macro-batches", "1",
+                          "--set", "learning_rate=0.002"], capture_output=True, text=True, env=env, timeout=400)
+    assert one.returncode == 0, one.stderr[-2000:]
+    out = json.loads(one.stdout.strip().splitlines()[-1])
+    assert out["global_step"] == 1 and out["total_samples_seen"] == 16
+    three = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "3", "--master-addr",
+                            "127.0.0.1", "--master-port", "29873", "-m", "async_grpo_nccl_b200.launch", "--config", str(path),
+                            "--max-macro-batches", "1", "--set", f"output_dir={tmp_path / 'out3'}", "--set", "num_training_gpu_workers=2",
+                            "--set", 'placement={"trainer": [0, 1], "logprob": [2], "rollout": [2]}'],
+                           capture_output=True, text=True, env=env, timeout=600)
+    assert three.returncode == 0, three.stderr[-3000:]
+    line = [l for l in three.stdout.strip().splitlines() if l.startswith("{")][-1]
+    assert json.loads(line)["global_step"] == 1
