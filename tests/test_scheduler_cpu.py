@@ -136,3 +136,76 @@ def test_prefix_cache_reuses_blocks_across_requests_and_evicts_oldest_first():
     assert s.num_cached_blocks == 0 and s.num_free_blocks == 24
     s.add_group(6, 9, 1, 2, [], [11, 12])
     assert s.plan_prefill()["cached_lens"] == [0]
+
+
+def test_prefix_cache_randomised_invariants():
+    """Random add / prefill / decode / finish / clear sequences with prompts drawn from a few shared chains. After every
+    operation: blocks of live sequences are distinct unless they are shared prompt blocks of the same chain, the number
+    of free blocks plus the blocks held by live sequences equals the pool, slot mappings never point into a cached
+    prefix, and at the end everything is free again."""
+    rng = np.random.default_rng(7)
+    bs, nb = 4, 96
+    s = _sched(num_blocks=nb, block_size=bs, max_seqs=12, max_blocks_per_seq=24, max_prefill_tokens=256)
+    chains = [[int(h) for h in rng.integers(1, 1 << 60, 8)] for _ in range(3)]  # hash chains of 3 "system prompts"
+    live = {}   # seq_id -> group id
+    gid = 0
+    group_chain = {}
+    hit_tokens = 0
+    for it in range(400):
+        op = rng.integers(0, 10)
+        if op < 3 and s.num_waiting < 4:
+            c = int(rng.integers(0, 3))
+            full = int(rng.integers(0, 8))
+            plen = full * bs + int(rng.integers(0, bs)) or 1
+            hashes = chains[c][:plen // bs] if rng.random() < 0.8 else []
+            s.add_group(gid, plen, int(rng.integers(1, 4)), int(rng.integers(1, 12)), [], hashes)
+            group_chain[gid] = (c, hashes)
+            gid += 1
+        elif op < 5:
+            p = s.plan_prefill()
+            assert len(p["cached_lens"]) == len(p["group_ids"])
+            assert sum(p["prompt_lens"]) - sum(p["cached_lens"]) == len(p["slot_mapping"])
+            assert sum(p["cached_lens"]) == len(p["prefix_slots"])
+            assert not (set(p["slot_mapping"]) & set(p["prefix_slots"]))
+            hit_tokens += sum(p["cached_lens"])
+            for g, c, L in zip(p["group_ids"], p["cached_lens"], p["prompt_lens"]):
+                assert c % bs == 0 and c < L and c <= len(group_chain[g][1]) * bs
+            for sid in p["seq_ids"]:
+                live[sid] = s.seq_info(sid)["group_id"]
+        elif op < 8:
+            d = s.plan_decode()
+            for sid in d["preempted"]:
+                live.pop(sid, None)
+                s.finish(sid)
+            # sequences reaching their length limit finish
+            for sid in list(live):
+                info = s.seq_info(sid)
+                if info is not None and info["len"] >= info["max_len"]:
+                    s.finish(sid)
+                    live.pop(sid)
+        elif op < 9 and live:
+            sid = list(live)[int(rng.integers(0, len(live)))]
+            s.finish(sid)
+            live.pop(sid)
+        else:
+            if rng.random() < 0.2:
+                s.clear_prefix_cache()
+        # ---- invariants ----
+        held = {}
+        for sid in live:
+            info = s.seq_info(sid)
+            assert info is not None
+            for b in info["blocks"]:
+                held.setdefault(b, []).append(sid)
+        for b, owners in held.items():
+            if len(owners) > 1:  # shared blocks: prompt blocks of the same group, or of groups on the same chain
+                cs = {group_chain[live[o]][0] for o in owners}
+                assert len(cs) == 1, (b, owners)
+        assert s.num_free_blocks + len(held) == nb, (it, s.num_free_blocks, len(held))
+        assert s.num_cached_blocks <= nb
+    assert hit_tokens > 0, "the workload must produce prefix hits"
+    for sid in list(live):
+        s.finish(sid)
+    assert s.num_free_blocks == nb and s.num_running == 0
+    s.clear_prefix_cache()
+    assert s.num_cached_blocks == 0 and s.num_free_blocks == nb
