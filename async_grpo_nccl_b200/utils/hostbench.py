@@ -168,10 +168,101 @@ def bench_rpc() -> None:
     _out({"bench": "rpc", "payload_bytes": 2048 * 8, **asyncio.run(run())})
 
 
+class _FileStore:
+    """The two calls of the job's key-value store that the replica channel uses, on files (for two local processes)."""
+
+    def __init__(self, root: str):
+        self.root = root
+
+    def set(self, k: str, v: str) -> None:
+        tmp = os.path.join(self.root, k + ".tmp")
+        with open(tmp, "w") as f:
+            f.write(v)
+        os.replace(tmp, os.path.join(self.root, k))
+
+    def get(self, k: str) -> bytes:
+        path = os.path.join(self.root, k)
+        for _ in range(2000):
+            if os.path.exists(path):
+                with open(path, "rb") as f:
+                    return f.read()
+            time.sleep(0.005)
+        raise TimeoutError(k)
+
+
+class _CountingEngine:
+    """Replays nothing; drops a file when it has seen ``warm`` steps and another at ``warm + want``."""
+
+    def __init__(self, warm: int, want: int, root: str):
+        self.n, self.marks, self.root = 0, {warm: "warm", warm + want: "done"}, root
+
+    def step(self) -> list:
+        self.n += 1
+        name = self.marks.get(self.n)
+        if name:
+            with open(os.path.join(self.root, name), "w") as f:
+                f.write(name)
+        return []
+
+    def add_request(self, *a: Any, **k: Any) -> None:
+        pass
+
+    def check_status(self) -> None:
+        pass
+
+
+def _replica_follower_process(root: str, warm: int, want: int) -> None:
+    from ..roles.tp_mirror import FollowerListener, TpFollower
+
+    fol = TpFollower(_CountingEngine(warm, want, root), FollowerListener(_FileStore(root), 1))
+    fol._thread.join()
+
+
+def bench_replica() -> None:
+    """Host cost of a tensor-parallel replica per decode step: the leader's ``step`` commands reaching a follower in another
+    process over the loopback connection (one-way stream: commands per second until the follower has replayed all of
+    them), and the prefix-cache hashing of one 512-token prompt."""
+    import hashlib
+    import multiprocessing as mp
+    import tempfile
+
+    from ..roles.tp_mirror import LeaderChannel
+
+    warm, n = 100, 20000
+    with tempfile.TemporaryDirectory() as root:
+        proc = mp.get_context("spawn").Process(target=_replica_follower_process, args=(root, warm, n), daemon=True)
+        proc.start()
+        lead = LeaderChannel(_FileStore(root), [1])
+
+        def wait_for(name: str) -> None:
+            t = time.perf_counter()
+            while not os.path.exists(os.path.join(root, name)) and time.perf_counter() - t < 120:
+                time.sleep(0.0002)
+
+        for _ in range(warm):  # the follower imports its libraries while these wait in the socket
+            lead.send("step")
+        wait_for("warm")
+        t0 = time.perf_counter()
+        for _ in range(n):
+            lead.send("step")
+        wait_for("done")
+        per = (time.perf_counter() - t0) / n
+        lead.close()
+        proc.join(timeout=10)
+    prompt = np.arange(512, dtype=np.int32)
+
+    def hashes() -> None:
+        prev = b"agrpo-prefix"
+        for b in range(512 // 16):
+            prev = hashlib.blake2b(prev + prompt[b * 16:(b + 1) * 16].tobytes(), digest_size=8).digest()
+
+    _out({"bench": "replica_host", "step_command_us": per * 1e6, "prefix_hash_512_tokens_us": _median_time(hashes) * 1e6})
+
+
 def main() -> int:
-    which = sys.argv[1:] or ["packer", "planner", "verifier", "checkpoint", "rpc"]
+    which = sys.argv[1:] or ["packer", "planner", "verifier", "checkpoint", "rpc", "replica"]
     table = {"packer": bench_packer, "planner": bench_planner, "verifier": bench_verifier, "checkpoint": bench_checkpoint,
-             "rpc": bench_rpc}
+             "rpc": bench_rpc, "replica": bench_replica}
     for w in which:
         if w not in table:
             raise SystemExit(f"unknown benchmark {w}; choose from {sorted(table)}")
